@@ -1,0 +1,226 @@
+// Memory-bound kernels of a step: embedding gather, residual add fused with
+// RMSNorm, rotary encoding fused with the paged key/value write, SiLU-multiply,
+// row gather.  All arithmetic in float32; operands float32 or bfloat16.
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace sllm {
+
+static thread_local char g_error[256] = "";
+void set_error(const char* msg) {
+  strncpy(g_error, msg, sizeof g_error - 1);
+  g_error[sizeof g_error - 1] = 0;
+}
+
+// ---------------------------------------------------------------------------
+// out[t, :] = float(table[ids[t], :])      (kernels/cuda/kernels.cu:770-787 does one row)
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ out, int H, int V) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);     // the host validates ids; never read outside the table
+  const TW* row = table + (size_t)id * H;
+  float* o = out + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+// ---------------------------------------------------------------------------
+// residual += sum of `parts` delta slices (if any); out = residual * rsqrt(mean(residual^2)+eps) * w
+// Formula ref/standard.py:25-31; fusion with the add as kernels/cuda/kernels.cu:791-839;
+// 1/sqrtf, not rsqrtf (kernels.cu:818-820).  The sum over a row is taken in an order
+// that depends on H and the block size only, never on the batch.
+// ---------------------------------------------------------------------------
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int parts,
+                                   size_t part_stride, const float* __restrict__ w, float eps,
+                                   TO* __restrict__ out, int H) {
+  __shared__ float red[33];
+  const size_t base = (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = residual[base + i];
+    if (delta != nullptr) {
+      for (int p = 0; p < parts; ++p) v += to_f32(delta[p * part_stride + base + i]);
+      residual[base + i] = v;
+    }
+    ss += v * v;
+  }
+  const float total = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(total / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    out[base + i] = from_f32<TO>(residual[base + i] * inv * w[i]);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// out[t, i] = silu(g) * u with g = gu[t, gi(i)], u = gu[t, gi(i) + blk], gi(i) = (i/blk)*2*blk + i%blk
+// silu(z) = z / (1 + exp(-z))  (ref/qwen3_5.py:28-29; kernels/cuda/kernels.cu:898-907)
+// ---------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int I, int blk, size_t n) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n) return;
+  const size_t t = idx / I;
+  const int i = (int)(idx % I);
+  const size_t gi = t * 2 * (size_t)I + (size_t)(i / blk) * 2 * blk + (i % blk);
+  const float g = to_f32(gu[gi]);
+  const float u = to_f32(gu[gi + blk]);
+  out[idx] = from_f32<TO>(g * (1.0f / (1.0f + expf(-g))) * u);
+}
+
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows, T* __restrict__ out,
+                                   int H, int n_src) {
+  int r = rows[blockIdx.x];
+  r = r < 0 ? 0 : (r >= n_src ? n_src - 1 : r);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)blockIdx.x * H + i] = x[(size_t)r * H + i];
+}
+
+// ---------------------------------------------------------------------------
+// Per (token, head) of the fused q|k|v row: add the bias; rotate the first `rot`
+// dims of q and k heads by the token's position, pairs (j, j+rot/2):
+//   o[j] = x[j] c_j - x[j+rot/2] s_j ; o[j+rot/2] = x[j+rot/2] c_j + x[j] s_j
+// (ref/qwen3_5.py:337-370; kernels/cuda/kernels.cu:846-895), dims >= rot pass.
+// q goes to q_out; k (after bias and rotation) and v (after bias) go to the token's
+// slot of the paged cache [page][kv head][slot in page][hd]
+// (cache content: ref/incremental.py:135-139; kernels.cu:923-953 for the contiguous form).
+// table: [max_pos][2][rot/2] cos then sin, float32 made from float64 angles.
+// ---------------------------------------------------------------------------
+template <typename TI, typename TC>
+__global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, const float* __restrict__ bias,
+                                     const int* __restrict__ positions, const float* __restrict__ table,
+                                     int rot, int max_pos, int nq, int nkv, int hd,
+                                     const int* __restrict__ slot_mapping, int page_size, int num_pages,
+                                     TC* __restrict__ k_cache, TC* __restrict__ v_cache, TC* __restrict__ q_out) {
+  const int t = blockIdx.x;
+  const int head = blockIdx.y;                       // 0..nq-1 q, then nkv k, then nkv v
+  const int width = (nq + 2 * nkv) * hd;
+  const TI* x = qkv + (size_t)t * width + (size_t)head * hd;
+  const float* b = bias ? bias + (size_t)head * hd : nullptr;
+  const bool is_q = head < nq;
+  const bool is_k = !is_q && head < nq + nkv;
+  TC* dst;
+  if (is_q) {
+    dst = q_out + (size_t)t * nq * hd + (size_t)head * hd;
+  } else {
+    if (slot_mapping == nullptr) return;             // this run reads another run's cache
+    const int slot = slot_mapping[t];
+    const int page = slot / page_size, off = slot % page_size;
+    if (slot < 0 || page >= num_pages) return;       // the host checks tables; never write outside the pool
+    const int kvh = is_k ? head - nq : head - nq - nkv;
+    TC* base = is_k ? k_cache : v_cache;
+    dst = base + (((size_t)page * nkv + kvh) * page_size + off) * hd;
+  }
+  const bool rotate = (is_q || is_k) && rot > 0 && table != nullptr;
+  if (!rotate) {
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[d] = from_f32<TC>(to_f32(x[d]) + (b ? b[d] : 0.f));
+    return;
+  }
+  int pos = positions[t];
+  pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+  const int half = rot / 2;
+  const float* cs = table + (size_t)pos * rot;       // cos[half] then sin[half]
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    const float x1 = to_f32(x[j]) + (b ? b[j] : 0.f);
+    const float x2 = to_f32(x[j + half]) + (b ? b[j + half] : 0.f);
+    const float c = cs[j], s = cs[half + j];
+    dst[j] = from_f32<TC>(x1 * c - x2 * s);
+    dst[j + half] = from_f32<TC>(x2 * c + x1 * s);
+  }
+  for (int d = rot + threadIdx.x; d < hd; d += blockDim.x) dst[d] = from_f32<TC>(to_f32(x[d]) + (b ? b[d] : 0.f));
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+SLLM_EXPORT const char* sllm_last_error() { return g_error; }
+
+SLLM_EXPORT int sllm_embed_gather(const void* table, int table_dtype, const int* ids, float* out, int T, int H,
+                                  int V, cudaStream_t stream) {
+  SLLM_REQUIRE(T >= 0 && H > 0 && V > 0, "embed_gather: bad sizes T=%d H=%d V=%d", T, H, V);
+  if (T == 0) return SLLM_OK;
+  const int threads = H >= 1024 ? 256 : 128;
+  if (table_dtype == SLLM_F32)
+    embed_gather_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, H, V);
+  else if (table_dtype == SLLM_BF16)
+    embed_gather_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, H, V);
+  else
+    SLLM_REQUIRE(false, "embed_gather: unknown dtype %d", table_dtype);
+  return launch_status("embed_gather");
+}
+
+SLLM_EXPORT int sllm_add_rmsnorm(float* residual, const void* delta, int delta_dtype, int parts,
+                                 size_t part_stride, const float* w, float eps, void* out, int out_dtype,
+                                 int rows, int H, cudaStream_t stream) {
+  SLLM_REQUIRE(rows >= 0 && H > 0, "add_rmsnorm: bad sizes rows=%d H=%d", rows, H);
+  SLLM_REQUIRE(delta == nullptr || parts >= 1, "add_rmsnorm: parts=%d", parts);
+  if (rows == 0) return SLLM_OK;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+#define LAUNCH(TD, TO)                                                                                      \
+  add_rmsnorm_kernel<TD, TO><<<rows, threads, 0, stream>>>(residual, (const TD*)delta, parts, part_stride, w, \
+                                                           eps, (TO*)out, H)
+  if (delta_dtype == SLLM_F32 && out_dtype == SLLM_F32) LAUNCH(float, float);
+  else if (delta_dtype == SLLM_F32 && out_dtype == SLLM_BF16) LAUNCH(float, __nv_bfloat16);
+  else if (delta_dtype == SLLM_BF16 && out_dtype == SLLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else if (delta_dtype == SLLM_BF16 && out_dtype == SLLM_F32) LAUNCH(__nv_bfloat16, float);
+  else SLLM_REQUIRE(false, "add_rmsnorm: unknown dtypes %d %d", delta_dtype, out_dtype);
+#undef LAUNCH
+  return launch_status("add_rmsnorm");
+}
+
+SLLM_EXPORT int sllm_silu_mul(const void* gu, int in_dtype, void* out, int out_dtype, int T, int I, int blk,
+                              cudaStream_t stream) {
+  SLLM_REQUIRE(T >= 0 && I > 0 && blk > 0 && I % blk == 0, "silu_mul: bad sizes T=%d I=%d blk=%d", T, I, blk);
+  const size_t n = (size_t)T * I;
+  if (n == 0) return SLLM_OK;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+#define LAUNCH(TI, TO) silu_mul_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)gu, (TO*)out, I, blk, n)
+  if (in_dtype == SLLM_F32 && out_dtype == SLLM_F32) LAUNCH(float, float);
+  else if (in_dtype == SLLM_F32 && out_dtype == SLLM_BF16) LAUNCH(float, __nv_bfloat16);
+  else if (in_dtype == SLLM_BF16 && out_dtype == SLLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else SLLM_REQUIRE(false, "silu_mul: unsupported dtypes %d -> %d", in_dtype, out_dtype);
+#undef LAUNCH
+  return launch_status("silu_mul");
+}
+
+SLLM_EXPORT int sllm_gather_rows(const void* x, int dtype, const int* rows, void* out, int R, int H, int n_src,
+                                 cudaStream_t stream) {
+  SLLM_REQUIRE(R >= 0 && H > 0 && n_src > 0, "gather_rows: bad sizes R=%d H=%d n=%d", R, H, n_src);
+  if (R == 0) return SLLM_OK;
+  if (dtype == SLLM_F32)
+    gather_rows_kernel<float><<<R, 256, 0, stream>>>((const float*)x, rows, (float*)out, H, n_src);
+  else if (dtype == SLLM_BF16)
+    gather_rows_kernel<__nv_bfloat16><<<R, 256, 0, stream>>>((const __nv_bfloat16*)x, rows, (__nv_bfloat16*)out, H, n_src);
+  else
+    SLLM_REQUIRE(false, "gather_rows: unknown dtype %d", dtype);
+  return launch_status("gather_rows");
+}
+
+SLLM_EXPORT int sllm_rope_kv_write(const void* qkv, int in_dtype, const float* bias, const int* positions,
+                                   const float* table, int rot, int max_pos, int nq, int nkv, int hd,
+                                   const int* slot_mapping, int page_size, int num_pages, void* k_cache,
+                                   void* v_cache, void* q_out, int cache_dtype, int T, cudaStream_t stream) {
+  SLLM_REQUIRE(T >= 0 && nq > 0 && nkv > 0 && hd > 0, "rope_kv_write: bad sizes T=%d nq=%d nkv=%d hd=%d", T, nq, nkv, hd);
+  SLLM_REQUIRE(rot >= 0 && rot <= hd && rot % 2 == 0, "rope_kv_write: rotary_dim=%d must be even and <= head_dim=%d", rot, hd);
+  SLLM_REQUIRE(rot == 0 || (table != nullptr && max_pos > 0), "rope_kv_write: rotary table missing");
+  SLLM_REQUIRE(slot_mapping == nullptr || (page_size > 0 && num_pages > 0 && k_cache && v_cache),
+               "rope_kv_write: cache arguments missing");
+  if (T == 0) return SLLM_OK;
+  dim3 grid(T, nq + 2 * nkv);
+  const int threads = hd / 2 >= 64 ? 64 : 32;
+#define LAUNCH(TI, TC)                                                                                         \
+  rope_kv_write_kernel<TI, TC><<<grid, threads, 0, stream>>>((const TI*)qkv, bias, positions, table, rot,      \
+                                                             max_pos, nq, nkv, hd, slot_mapping, page_size,    \
+                                                             num_pages, (TC*)k_cache, (TC*)v_cache, (TC*)q_out)
+  if (in_dtype == SLLM_F32 && cache_dtype == SLLM_F32) LAUNCH(float, float);
+  else if (in_dtype == SLLM_F32 && cache_dtype == SLLM_BF16) LAUNCH(float, __nv_bfloat16);
+  else if (in_dtype == SLLM_BF16 && cache_dtype == SLLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else SLLM_REQUIRE(false, "rope_kv_write: unsupported dtypes %d -> %d", in_dtype, cache_dtype);
+#undef LAUNCH
+  return launch_status("rope_kv_write");
+}

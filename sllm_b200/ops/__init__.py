@@ -1,0 +1,201 @@
+"""The operations a step is made of, each a hand-written sm_100a kernel.
+
+Tensors must lie on a CUDA device and be contiguous; there is no CPU path and no
+library model code behind these functions.  Matrix products of the bfloat16
+path with many rows go to cuBLAS (as the reference's engine does,
+kernels/cuda/kernels.cu:752-767); everything else, and every product of the
+float32 path, runs in this package's own kernels.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ._lib import KernelError, call, lib  # noqa: F401
+
+F32, BF16 = 0, 1
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported dtype {t.dtype}; the kernels take float32 and bfloat16")
+
+
+def _dtc(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported dtype {dtype}; the kernels take float32 and bfloat16")
+
+
+def _chk(*tensors) -> None:
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise KernelError("the kernels run on a CUDA device only; got a tensor on " + str(t.device))
+        if not t.is_contiguous():
+            raise KernelError("the kernels take contiguous tensors")
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def embed_gather(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """float32 ``[T, H]`` rows of ``table`` (``[V, H]``) at int32 ``ids``."""
+    _chk(table, ids)
+    T, (V, H) = ids.numel(), table.shape
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    call("sllm_embed_gather", _p(table), _dt(table), _p(ids), _p(out), T, H, V, _stream())
+    return out
+
+
+def add_rmsnorm(residual: torch.Tensor, delta, weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype) -> torch.Tensor:
+    """``residual += delta`` (in place, if delta is given; a 3-d delta is a stack of
+    partial sums) and return ``rmsnorm(residual) * weight`` in ``out_dtype``."""
+    _chk(residual, delta, weight)
+    rows, H = residual.shape
+    if residual.dtype != torch.float32 or weight.dtype != torch.float32:
+        raise KernelError("add_rmsnorm: the residual stream and the gain are float32")
+    parts, stride = 1, 0
+    if delta is not None:
+        if delta.dim() == 3:
+            parts, stride = delta.shape[0], delta.shape[1] * delta.shape[2]
+        if tuple(delta.shape[-2:]) != (rows, H):
+            raise KernelError(f"add_rmsnorm: delta {tuple(delta.shape)} does not fit residual {(rows, H)}")
+    out = torch.empty((rows, H), dtype=out_dtype, device=residual.device)
+    call("sllm_add_rmsnorm", _p(residual), _p(delta), _dt(delta) if delta is not None else F32, parts, stride,
+         _p(weight), float(eps), _p(out), _dtc(out_dtype), rows, H, _stream())
+    return out
+
+
+def gemm_f32(x: torch.Tensor, w: torch.Tensor, bias) -> torch.Tensor:
+    """True float32 ``x @ w.T + bias``: CUDA-core FMA, fixed summation order."""
+    _chk(x, w, bias)
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"linear: x {tuple(x.shape)} does not fit w {tuple(w.shape)}")
+    out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    call("sllm_gemm_f32", _p(x), _p(w), _p(bias), _p(out), M, N, K, _stream())
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype) -> torch.Tensor:
+    """``x @ w.T (+ bias)``; ``w`` is ``[N, K]``.  float32 operands: this package's
+    float32 kernel.  bfloat16 operands: float32 accumulation, result in ``out_dtype``."""
+    if x.dtype != w.dtype:
+        raise KernelError(f"linear: x is {x.dtype}, w is {w.dtype}")
+    if x.dtype == torch.float32:
+        if out_dtype != torch.float32:
+            raise KernelError("linear: the float32 path keeps float32 results")
+        return gemm_f32(x, w, bias)
+    _chk(x, w, bias)
+    if not x.is_cuda:
+        raise KernelError("linear: CUDA only")
+    if out_dtype == torch.float32:
+        out = torch.mm(x, w.t(), out_dtype=torch.float32)
+    else:
+        out = torch.mm(x, w.t())
+    if bias is not None:
+        out += bias.to(out.dtype)
+    return out
+
+
+def silu_mul(gu: torch.Tensor, interleave: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """``silu(gate) * up`` of ``gu [T, 2I]`` whose columns alternate between gate
+    and up in blocks of ``interleave``."""
+    _chk(gu)
+    T, two_i = gu.shape
+    I = two_i // 2
+    out = torch.empty((T, I), dtype=out_dtype, device=gu.device)
+    call("sllm_silu_mul", _p(gu), _dt(gu), _p(out), _dtc(out_dtype), T, I, int(interleave), _stream())
+    return out
+
+
+def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """``silu(x Wg^T) * (x Wu^T)`` with gate and up rows interleaved in one matrix."""
+    gu = linear(x, w_gate_up, None, x.dtype)
+    return silu_mul(gu, interleave, out_dtype)
+
+
+def rope_kv_write(qkv, bias, positions, table, rotary_dim, nq, nkv, hd, slot_mapping, k_cache, v_cache,
+                  out_dtype: torch.dtype) -> torch.Tensor:
+    """Bias, rotary encoding and the cache write for the fused q|k|v rows.
+    Returns the rotated queries ``[T, nq*hd]`` in ``out_dtype``; keys and values go
+    to ``slot_mapping`` in ``k_cache``/``v_cache`` ``[pages, nkv, page_size, hd]``
+    (not written when ``slot_mapping`` is None)."""
+    _chk(qkv, bias, positions, table, slot_mapping, k_cache, v_cache)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nq + 2 * nkv) * hd:
+        raise KernelError(f"rope_kv_write: qkv width {qkv.shape[1]} is not (nq+2nkv)*hd")
+    if k_cache.dtype != out_dtype or v_cache.dtype != out_dtype:
+        raise KernelError("rope_kv_write: the cache and the queries share one dtype")
+    num_pages, nkv_c, page_size, hd_c = k_cache.shape
+    if (nkv_c, hd_c) != (nkv, hd) or tuple(v_cache.shape) != tuple(k_cache.shape):
+        raise KernelError(f"rope_kv_write: cache shape {tuple(k_cache.shape)} does not fit nkv={nkv} hd={hd}")
+    max_pos = 0
+    if rotary_dim:
+        if table is None or table.dtype != torch.float32 or tuple(table.shape[1:]) != (2, rotary_dim // 2):
+            raise KernelError("rope_kv_write: rotary table must be float32 [positions, 2, rotary_dim/2]")
+        max_pos = table.shape[0]
+    q = torch.empty((T, nq * hd), dtype=out_dtype, device=qkv.device)
+    call("sllm_rope_kv_write", _p(qkv), _dt(qkv), _p(bias), _p(positions), _p(table), int(rotary_dim), max_pos,
+         nq, nkv, hd, _p(slot_mapping), page_size, num_pages, _p(k_cache), _p(v_cache), _p(q), _dtc(out_dtype),
+         T, _stream())
+    return q
+
+
+def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, nq, nkv, hd, scale, window):
+    """The CUDA-core attention kernel: any head size up to 256, float32 arithmetic."""
+    _chk(q, k_cache, v_cache, block_tables, positions, seq_of_token)
+    T = q.shape[0]
+    if q.dtype != k_cache.dtype:
+        raise KernelError("attention: queries and cache share one dtype")
+    page_size = k_cache.shape[2]
+    out = torch.empty_like(q)
+    call("sllm_attention_simt", _p(q), _p(k_cache), _p(v_cache), _dt(q), _p(block_tables),
+         block_tables.shape[1], _p(positions), _p(seq_of_token), T, nq, nkv, hd, page_size, float(scale),
+         int(window or 0), _p(out), _stream())
+    return out
+
+
+def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, window):
+    """Causal attention of the step's tokens over their requests' pages."""
+    g = step.groups[group]
+    return attention_simt(q, k_cache, v_cache, g.block_tables, step.positions, step.seq_of_token,
+                          nq, nkv, hd, scale, window)
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    _chk(x, rows)
+    R, (n, H) = rows.numel(), x.shape
+    out = torch.empty((R, H), dtype=x.dtype, device=x.device)
+    call("sllm_gather_rows", _p(x), _dt(x), _p(rows), _p(out), R, H, n, _stream())
+    return out
+
+
+def sample_rows(logits: torch.Tensor, temperature=None, uniform=None) -> torch.Tensor:
+    """int32 token per row of float32 ``logits [R, V]``: the first maximum where the
+    row's temperature is <= 0 (or none is given), else inverse-CDF sampling of
+    softmax(logits / temperature) at the row's uniform (float64)."""
+    _chk(logits, temperature, uniform)
+    R, V = logits.shape
+    if logits.dtype != torch.float32:
+        raise KernelError("sample_rows: logits are float32")
+    if temperature is not None and (temperature.dtype != torch.float32 or uniform is None
+                                    or uniform.dtype != torch.float64):
+        raise KernelError("sample_rows: temperature float32 and uniform float64, one per row")
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    call("sllm_sample_rows", _p(logits), R, V, _p(temperature), _p(uniform), _p(out), _stream())
+    return out

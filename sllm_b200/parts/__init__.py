@@ -1,0 +1,9 @@
+from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, FeedForward,
+                   GroupView, LayerCache, Mixer, Norm, PagedKV, Part,
+                   PositionEncoding, Registry, SlotState, StepContext, TensorSpec)
+
+__all__ = [
+    "BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "FeedForward",
+    "GroupView", "LayerCache", "Mixer", "Norm", "PagedKV", "Part",
+    "PositionEncoding", "Registry", "SlotState", "StepContext", "TensorSpec",
+]

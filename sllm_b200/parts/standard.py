@@ -1,0 +1,212 @@
+"""The parts the Qwen2.5 dense architecture is made of: RMSNorm, rotate-half
+rotary tables, GQA attention over the paged cache, SwiGLU, and the pre-norm
+block.  Each takes its sizes and constants as parameters; none names a model.
+
+All arithmetic runs in the hand-written kernels behind `sllm_b200.ops`.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .. import ops
+from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, FeedForward,
+                   LayerCache, Mixer, Norm, PagedKV, Part, PositionEncoding,
+                   StepContext, TensorSpec)
+
+
+class Linear:
+    """y = x W^T (+ b); W is (out, in) row-major as checkpoints store it
+    (ref/qwen3_5.py:59-64).  The matrix is held in the compute dtype, the bias
+    in float32."""
+
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None):
+        self.weight = weight
+        self.bias = bias
+
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        return ops.linear(x, self.weight, self.bias, out_dtype)
+
+    def nbytes(self) -> int:
+        n = self.weight.numel() * self.weight.element_size()
+        if self.bias is not None:
+            n += self.bias.numel() * 4
+        return n
+
+
+@NORMS.register("rmsnorm")
+class RMSNorm(Norm):
+    """y = x * (mean(x^2) + eps)^-1/2 * w with plain gain w, computed in float32
+    on the float32 residual stream (ref/standard.py:25-31).  Fused with the
+    addition that precedes it, as the reference's device path does
+    (kernels/cuda/kernels.cu:791-839)."""
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.weight = None
+
+    def tensor_specs(self):
+        return [TensorSpec("weight", (self.size,), role="gain")]
+
+    def bind(self, fetch):
+        self.weight = self._f32(fetch("weight"))
+
+    def add_norm(self, residual, delta):
+        return ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.dtype)
+
+    def weight_bytes(self):
+        return self.size * 4
+
+
+@POSITIONS.register("rotary")
+class Rotary(PositionEncoding):
+    """Rotate-half rotary encoding over the first ``rotary_dim`` dims of a head:
+    angle(pos, j) = pos * theta^(-2j/rot), j < rot/2 (ref/qwen3_5.py:343-352).
+    The table of cos and sin is computed once in float64 and stored in float32,
+    ``[max_positions, rot/2]`` each."""
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        self.theta = float(params["theta"])
+        self.rotary_dim = int(params["rotary_dim"])
+        self.max_positions = int(params["max_positions"])
+        half = self.rotary_dim // 2
+        inv_freq = 1.0 / (self.theta ** (np.arange(0, self.rotary_dim, 2, dtype=np.float64) / self.rotary_dim))
+        ang = np.arange(self.max_positions, dtype=np.float64)[:, None] * inv_freq[None, :]
+        table = np.stack([np.cos(ang), np.sin(ang)], axis=1).astype(np.float32)   # [P, 2, half]
+        assert table.shape == (self.max_positions, 2, half)
+        self.table = torch.from_numpy(table).to(self.device).contiguous()
+
+
+@MIXERS.register("attention")
+class Attention(Mixer):
+    """Grouped-query attention over a paged cache.
+
+    q = xWq^T+bq, k, v likewise (biases optional); q and k rotated; k (after
+    bias and rotation) and v (after bias) written to the cache before any read;
+    query head h reads kv head h // (nq/nkv); scores scaled, causal (and an
+    optional window), softmax in float32; heads merged; o_proj without bias
+    unless asked (ref/standard.py:34-72; cache content ref/incremental.py:135-139).
+    q|k|v are one matrix, as the reference's device path fuses them
+    (kernels/device_decode.py:84-87).
+    """
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.nq = int(p["num_heads"])
+        self.nkv = int(p["num_kv_heads"])
+        self.hd = int(p["head_dim"])
+        self.qkv_bias = bool(p.get("qkv_bias", False))
+        self.out_bias = bool(p.get("out_bias", False))
+        self.scale = float(p.get("scale", self.hd ** -0.5))
+        self.window = p.get("window")
+        self.names = p.get("names", ("q_proj", "k_proj", "v_proj", "o_proj"))
+        if self.nq % self.nkv:
+            raise ValueError(f"attention: {self.nq} query heads are no multiple of {self.nkv} kv heads")
+        self.qkv = None
+        self.out = None
+
+    def cache_need(self):
+        return PagedKV(self.nkv, self.hd, self.window)
+
+    def tensor_specs(self):
+        nq, nk, h = self.nq * self.hd, self.nkv * self.hd, self.hidden
+        qn, kn, vn, on = self.names
+        specs = [TensorSpec(f"{qn}.weight", (nq, h)), TensorSpec(f"{kn}.weight", (nk, h)),
+                 TensorSpec(f"{vn}.weight", (nk, h)), TensorSpec(f"{on}.weight", (h, nq))]
+        if self.qkv_bias:
+            # present or absent as a set, decided by the checkpoint (ref/standard.py:114-116)
+            specs += [TensorSpec(f"{n}.bias", (s,), role="bias", optional=True, together="qkv_bias")
+                      for n, s in ((qn, nq), (kn, nk), (vn, nk))]
+        if self.out_bias:
+            specs.append(TensorSpec(f"{on}.bias", (h,), role="bias"))
+        return specs
+
+    def bind(self, fetch):
+        qn, kn, vn, on = self.names
+        w = torch.cat([fetch(f"{n}.weight") for n in (qn, kn, vn)], dim=0)
+        bias = None
+        if self.qkv_bias and fetch(f"{qn}.bias") is not None:
+            bias = self._f32(torch.cat([fetch(f"{n}.bias").float() for n in (qn, kn, vn)]))
+        self.qkv = Linear(self._matrix(w))
+        self.qkv_b = bias                       # added in the rotary kernel, before rotation
+        ob = self._f32(fetch(f"{on}.bias")) if self.out_bias else None
+        self.out = Linear(self._matrix(fetch(f"{on}.weight")), ob)
+
+    def forward(self, x, step: StepContext, cache: LayerCache, position, write_cache=True):
+        g = step.groups[cache.group]
+        qkv = self.qkv(x, torch.float32)                      # [T, (nq+2nkv)*hd] float32
+        q = ops.rope_kv_write(
+            qkv, self.qkv_b, step.positions,
+            position.table if position is not None else None,
+            position.rotary_dim if position is not None else 0,
+            self.nq, self.nkv, self.hd,
+            g.slot_mapping if write_cache else None, cache.k, cache.v, self.dtype)
+        o = ops.paged_attention(q, cache.k, cache.v, step, cache.group,
+                                self.nq, self.nkv, self.hd, self.scale, self.window)
+        return self.out(o, torch.float32)
+
+    def weight_bytes(self):
+        return self.qkv.nbytes() + self.out.nbytes() + (self.qkv_b.numel() * 4 if self.qkv_b is not None else 0)
+
+
+@FEED_FORWARDS.register("swiglu")
+class SwiGLU(FeedForward):
+    """down(silu(gate(x)) * up(x)), silu(z) = z/(1+e^-z), no biases
+    (ref/qwen3_5.py:28-29, 444-451).  gate and up are one matrix
+    (kernels/device_decode.py:93-95); their rows alternate in blocks of
+    ``interleave`` so that a tile of the product holds a gate row and its up
+    row together and the activation can be applied where the tile is made."""
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.names = params.get("names", ("gate_proj", "up_proj", "down_proj"))
+        self.interleave = 8 if self.inter % 8 == 0 else self.inter
+        self.gate_up = None
+        self.down = None
+
+    def tensor_specs(self):
+        g, u, d = self.names
+        return [TensorSpec(f"{g}.weight", (self.inter, self.hidden)),
+                TensorSpec(f"{u}.weight", (self.inter, self.hidden)),
+                TensorSpec(f"{d}.weight", (self.hidden, self.inter))]
+
+    def bind(self, fetch):
+        g, u, d = self.names
+        b = self.interleave
+        wg = fetch(f"{g}.weight").reshape(self.inter // b, b, self.hidden)
+        wu = fetch(f"{u}.weight").reshape(self.inter // b, b, self.hidden)
+        gu = torch.stack([wg, wu], dim=1).reshape(2 * self.inter, self.hidden)
+        self.gate_up = Linear(self._matrix(gu))
+        self.down = Linear(self._matrix(fetch(f"{d}.weight")))
+
+    def forward(self, x, step):
+        act = ops.linear_silu_mul(x, self.gate_up.weight, self.interleave, self.dtype)   # [T, I]
+        return self.down(act, torch.float32)
+
+    def weight_bytes(self):
+        return self.gate_up.nbytes() + self.down.nbytes()
+
+
+@BLOCKS.register("pre_norm")
+class PreNormBlock:
+    """h += mixer(norm1(h)); h += ffn(norm2(h)) (ref/standard.py:102-129).  The
+    addition of each term is done by the norm that follows it, so the block
+    takes the pending term of the layer before and hands its own on."""
+
+    def __init__(self, mixer, ffn, mixer_norm, ffn_norm):
+        self.mixer, self.ffn = mixer, ffn
+        self.mixer_norm, self.ffn_norm = mixer_norm, ffn_norm
+
+    def forward(self, residual, delta, step, cache, position, write_cache=True):
+        x = self.mixer_norm.add_norm(residual, delta)
+        d = self.mixer.forward(x, step, cache, position, write_cache)
+        x = self.ffn_norm.add_norm(residual, d)
+        return self.ffn.forward(x, step)

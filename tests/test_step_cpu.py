@@ -1,0 +1,57 @@
+"""Engine logic without a GPU: the step function, the cache and the batch layout,
+with the PyTorch statements of the operations in the kernels' place, compared
+with the plain implementation."""
+
+import numpy as np
+import pytest
+import torch
+
+from sllm_b200.engine import Engine, StepEntry, build_model
+from tests.plain import qwen2_plain as plain
+
+
+def _engine(model_dir, page, num_pages=64, max_requests=4):
+    model, _ = build_model(model_dir, "float32", "cpu")
+    return Engine(model, page_size=page, num_pages=num_pages, max_requests=max_requests)
+
+
+def test_whole_prompt_matches_plain(tiny, cpu_ops):
+    name, model_dir, page = tiny
+    cfg, w = plain.load_model(model_dir)
+    rng = np.random.default_rng(5)
+    ids = rng.integers(0, cfg["vocab_size"], 33).tolist()
+    want = plain.forward(ids, w, cfg)
+    eng = _engine(model_dir, page)
+    got = eng.step([StepEntry("a", ids, list(range(len(ids))))]).numpy()
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5)
+
+
+def test_cuttings_match_plain(tiny, cpu_ops):
+    name, model_dir, page = tiny
+    cfg, w = plain.load_model(model_dir)
+    rng = np.random.default_rng(6)
+    seqs = {k: rng.integers(0, cfg["vocab_size"], n).tolist() for k, n in (("a", 40), ("b", 23), ("c", 57))}
+    want = {k: plain.forward(v, w, cfg) for k, v in seqs.items()}
+    eng = _engine(model_dir, page, num_pages=sum(-(-len(v) // page) for v in seqs.values()))
+    done = {k: 0 for k in seqs}
+    cuts = [7, 2, 13, 1, 5, 2, 9, 3]
+    i = 0
+    while any(done[k] < len(seqs[k]) for k in seqs):
+        entries, keys = [], []
+        for k in seqs:
+            if done[k] >= len(seqs[k]):
+                continue
+            n = min(cuts[i % len(cuts)], len(seqs[k]) - done[k])
+            i += 1
+            entries.append(StepEntry(k, seqs[k][done[k]:done[k] + n], list(range(n))))
+            keys.append((k, done[k], n))
+        got = eng.step(entries).numpy()
+        r = 0
+        for k, start, n in keys:
+            np.testing.assert_allclose(got[r:r + n], want[k][start:start + n], rtol=1e-4, atol=1e-5)
+            r += n
+            done[k] += n
+    for k in seqs:
+        eng.finish(k)
+    eng.cache.check()
+    assert all(g.pool.used_count == 0 for g in eng.cache.groups)

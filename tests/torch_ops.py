@@ -1,0 +1,120 @@
+"""Plain PyTorch float32 statements of the package's operations, with the same
+signatures as `sllm_b200.ops`.
+
+Two uses, both in tests only: (1) the reference each CUDA kernel is compared
+with, on the GPU, at sizes other than the engine's; (2) patched over
+`sllm_b200.ops` (fixture `cpu_ops`), they let the step function, the cache and
+the scheduler be exercised on a machine without a GPU.  The product never
+imports this file; without its kernels it raises.
+"""
+
+from __future__ import annotations
+
+import torch
+
+
+def embed_gather(table, ids):
+    return table[ids.long()].float()
+
+
+def add_rmsnorm(residual, delta, weight, eps, out_dtype):
+    if delta is not None:
+        d = delta.float()
+        if d.dim() == 3:
+            d = d.sum(0)
+        residual += d
+    var = (residual * residual).mean(-1, keepdim=True)
+    return (residual * (var + eps) ** -0.5 * weight).to(out_dtype)
+
+
+def linear(x, w, bias, out_dtype):
+    out = x.float() @ w.float().t()
+    if bias is not None:
+        out = out + bias
+    return out.to(out_dtype)
+
+
+def silu_mul(gu, interleave, out_dtype):
+    T, two_i = gu.shape
+    I = two_i // 2
+    v = gu.float().reshape(T, I // interleave, 2, interleave)
+    g, u = v[:, :, 0, :], v[:, :, 1, :]
+    return (g * (1.0 / (1.0 + torch.exp(-g))) * u).reshape(T, I).to(out_dtype)
+
+
+def linear_silu_mul(x, w_gate_up, interleave, out_dtype):
+    return silu_mul(linear(x, w_gate_up, None, x.dtype), interleave, out_dtype)
+
+
+def rope_kv_write(qkv, bias, positions, table, rotary_dim, nq, nkv, hd, slot_mapping, k_cache, v_cache, out_dtype):
+    T = qkv.shape[0]
+    x = qkv.float()
+    if bias is not None:
+        x = x + bias
+    x = x.reshape(T, nq + 2 * nkv, hd)
+    if rotary_dim:
+        half = rotary_dim // 2
+        cs = table[positions.long()]                     # [T, 2, half]
+        c, s = cs[:, None, 0, :], cs[:, None, 1, :]
+        qk = x[:, :nq + nkv]
+        x1, x2 = qk[..., :half], qk[..., half:rotary_dim]
+        rot = torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, qk[..., rotary_dim:]], dim=-1)
+        x = torch.cat([rot, x[:, nq + nkv:]], dim=1)
+    q = x[:, :nq].reshape(T, nq * hd).to(out_dtype)
+    if slot_mapping is not None:
+        ps = k_cache.shape[2]
+        page, off = slot_mapping.long() // ps, slot_mapping.long() % ps
+        k_cache[page, :, off, :] = x[:, nq:nq + nkv].to(k_cache.dtype)
+        v_cache[page, :, off, :] = x[:, nq + nkv:].to(v_cache.dtype)
+    return q
+
+
+def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, nq, nkv, hd, scale, window):
+    T = q.shape[0]
+    ps = k_cache.shape[2]
+    out = torch.empty((T, nq, hd), dtype=torch.float32, device=q.device)
+    qf = q.float().reshape(T, nq, hd)
+    rep = nq // nkv
+    for t in range(T):
+        pos = int(positions[t])
+        lo = max(0, pos - window + 1) if window else 0
+        j = torch.arange(lo, pos + 1, device=q.device)
+        pages = block_tables[int(seq_of_token[t])].long()[j // ps]
+        k = k_cache[pages, :, j % ps, :].float()          # [n, nkv, hd]
+        v = v_cache[pages, :, j % ps, :].float()
+        k = k.repeat_interleave(rep, dim=1)
+        v = v.repeat_interleave(rep, dim=1)
+        s = torch.einsum("hd,nhd->hn", qf[t], k) * scale
+        p = torch.softmax(s, dim=-1)
+        out[t] = torch.einsum("hn,nhd->hd", p, v)
+    return out.reshape(T, nq * hd).to(q.dtype)
+
+
+def paged_attention(q, k_cache, v_cache, step, group, nq, nkv, hd, scale, window):
+    g = step.groups[group]
+    return attention_simt(q, k_cache, v_cache, g.block_tables, step.positions, step.seq_of_token,
+                          nq, nkv, hd, scale, window)
+
+
+def gather_rows(x, rows):
+    return x[rows.long()].clone()
+
+
+def sample_rows(logits, temperature=None, uniform=None):
+    R, V = logits.shape
+    out = torch.empty(R, dtype=torch.int32, device=logits.device)
+    for r in range(R):
+        t = float(temperature[r]) if temperature is not None else 0.0
+        row = logits[r].double()
+        if not t > 0:
+            out[r] = int(torch.argmax(row))
+            continue
+        p = torch.exp(row / t - (row / t).max())
+        p = p / p.sum()
+        idx = int(torch.searchsorted(torch.cumsum(p, 0), uniform[r].double().reshape(1))[0])
+        out[r] = min(idx, V - 1)
+    return out
+
+
+ALL = ["embed_gather", "add_rmsnorm", "linear", "silu_mul", "linear_silu_mul", "rope_kv_write",
+       "attention_simt", "paged_attention", "gather_rows", "sample_rows"]
