@@ -1,0 +1,244 @@
+"""Each kernel alone against its plain PyTorch float32 statement (tests/torch_ops.py),
+at sizes other than the engine's: widths and vocabularies that are no power of two,
+head sizes in steps of 16, odd head counts and groups."""
+
+import numpy as np
+import pytest
+import torch
+
+from tests import torch_ops as ref
+from tests.conftest import cuda_or_skip
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    cuda_or_skip()
+    import sllm_b200.ops as ops
+    return ops
+
+
+def _close(got, want, dtype, scale=1.0):
+    tol = 2e-5 if dtype == torch.float32 else 1.6e-2
+    torch.testing.assert_close(got.float(), want.float(), rtol=tol, atol=tol * scale)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V,H,T", [(300, 72, 19), (1000, 1000, 3)])
+def test_embed_gather(dtype, V, H, T):
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    table = torch.randn(V, H, device="cuda", generator=g).to(dtype)
+    ids = torch.randint(0, V, (T,), device="cuda", generator=g, dtype=torch.int32)
+    assert torch.equal(ops.embed_gather(table, ids), ref.embed_gather(table, ids))
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("delta_kind", ["none", "f32", "bf16", "parts"])
+@pytest.mark.parametrize("rows,H,eps", [(5, 72, 1e-6), (33, 3584, 1e-5), (2, 1000, 1e-6)])
+def test_add_rmsnorm(out_dtype, delta_kind, rows, H, eps):
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    res = torch.randn(rows, H, device="cuda", generator=g) * 3
+    w = 1 + 0.1 * torch.randn(H, device="cuda", generator=g)
+    delta = None
+    if delta_kind == "f32":
+        delta = torch.randn(rows, H, device="cuda", generator=g)
+    elif delta_kind == "bf16":
+        delta = torch.randn(rows, H, device="cuda", generator=g).bfloat16()
+    elif delta_kind == "parts":
+        delta = torch.randn(3, rows, H, device="cuda", generator=g)
+    r1, r2 = res.clone(), res.clone()
+    got = ops.add_rmsnorm(r1, delta, w, eps, out_dtype)
+    want = ref.add_rmsnorm(r2, delta, w, eps, out_dtype)
+    torch.testing.assert_close(r1, r2, rtol=1e-6, atol=1e-6)
+    _close(got, want, out_dtype, scale=4.0)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 300, 72), (37, 130, 1000), (64, 64, 16), (130, 257, 333), (3, 1000, 18)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_gemm_f32(M, N, K, bias):
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(M, K, device="cuda", generator=g)
+    w = torch.randn(N, K, device="cuda", generator=g) / K ** 0.5
+    b = torch.randn(N, device="cuda", generator=g) if bias else None
+    got = ops.linear(x, w, b, torch.float32)
+    want = (x.double() @ w.double().t() + (b.double() if bias else 0)).float()
+    torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)
+
+
+def test_gemm_f32_rows_do_not_depend_on_the_batch():
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(150, 333, device="cuda", generator=g)
+    w = torch.randn(200, 333, device="cuda", generator=g)
+    full = ops.linear(x, w, None, torch.float32)
+    for lo, hi in ((0, 1), (7, 9), (64, 150), (149, 150)):
+        assert torch.equal(ops.linear(x[lo:hi].contiguous(), w, None, torch.float32), full[lo:hi])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 300, 72), (8, 1000, 336), (77, 130, 1000), (300, 512, 256)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_linear_bf16(M, N, K, out_dtype):
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g)
+    got = ops.linear(x, w, b, out_dtype)
+    want = x.float() @ w.float().t() + b
+    _close(got, want, out_dtype if out_dtype == torch.bfloat16 else torch.float32, scale=4.0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,I,blk", [(5, 40, 8), (3, 37, 37), (17, 1000, 8)])
+def test_silu_mul(dtype, T, I, blk):
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    gu = (torch.randn(T, 2 * I, device="cuda", generator=g) * 2).to(dtype)
+    _close(ops.silu_mul(gu, blk, dtype), ref.silu_mul(gu, blk, dtype), dtype, scale=4.0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,hd,rot,ps", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (6, 3, 48, 24, 4), (7, 7, 80, 80, 32)])
+def test_rope_kv_write(dtype, nq, nkv, hd, rot, ps):
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(6)
+    T, pages, max_pos = 21, 9, 200
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd, device="cuda", generator=g)
+    bias = torch.randn((nq + 2 * nkv) * hd, device="cuda", generator=g)
+    pos = torch.randint(0, max_pos, (T,), device="cuda", generator=g, dtype=torch.int32)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * (1e4 ** (-torch.arange(0, rot, 2, dtype=torch.float64) / rot))[None]
+    table = torch.stack([ang.cos(), ang.sin()], 1).float().cuda()
+    slots = torch.randperm(pages * ps, device="cuda", generator=g)[:T].int()
+    kc = [torch.zeros(pages, nkv, ps, hd, device="cuda", dtype=dtype) for _ in range(2)]
+    vc = [torch.zeros(pages, nkv, ps, hd, device="cuda", dtype=dtype) for _ in range(2)]
+    got = ops.rope_kv_write(qkv, bias, pos, table, rot, nq, nkv, hd, slots, kc[0], vc[0], dtype)
+    want = ref.rope_kv_write(qkv, bias, pos, table, rot, nq, nkv, hd, slots, kc[1], vc[1], dtype)
+    _close(got, want, dtype, scale=4.0)
+    _close(kc[0], kc[1], dtype, scale=4.0)
+    _close(vc[0], vc[1], dtype, scale=4.0)
+    # no bias, no cache write (a run that borrows another run's cache), no rotation
+    k2, v2 = torch.zeros_like(kc[0]), torch.zeros_like(vc[0])
+    got = ops.rope_kv_write(qkv, None, pos, None, 0, nq, nkv, hd, None, k2, v2, dtype)
+    _close(got, qkv[:, :nq * hd].to(dtype), dtype, scale=4.0)
+    assert not k2.any() and not v2.any()
+
+
+def _paged_case(g, lens, q_lens, nq, nkv, hd, ps, dtype, spare_pages=3):
+    """Random cache content for requests of `lens` tokens whose last `q_lens` are queries."""
+    S = len(lens)
+    n_pages = sum(-(-n // ps) for n in lens) + spare_pages
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(9)).tolist()
+    kc = torch.randn(n_pages, nkv, ps, hd, device="cuda", generator=g).to(dtype)
+    vc = torch.randn(n_pages, nkv, ps, hd, device="cuda", generator=g).to(dtype)
+    max_pages = max(-(-n // ps) for n in lens)
+    bt = torch.full((S, max_pages), -1, dtype=torch.int32)
+    for s, n in enumerate(lens):
+        for i in range(-(-n // ps)):
+            bt[s, i] = perm.pop()
+    positions, seq = [], []
+    for s, (n, ql) in enumerate(zip(lens, q_lens)):
+        positions += list(range(n - ql, n))
+        seq += [s] * ql
+    T = len(positions)
+    q = torch.randn(T, nq * hd, device="cuda", generator=g).to(dtype)
+    return q, kc, vc, bt.cuda(), torch.tensor(positions, dtype=torch.int32).cuda(), torch.tensor(seq, dtype=torch.int32).cuda()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,hd,ps,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 2, 48, 4, 10),
+                                                 (5, 5, 80, 16, None), (14, 2, 64, 16, None), (8, 1, 128, 32, 33),
+                                                 (2, 1, 256, 16, None)])
+def test_attention_simt(dtype, nq, nkv, hd, ps, window):
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(7)
+    lens, q_lens = [70, 1, 33, 129], [5, 1, 33, 2]
+    q, kc, vc, bt, pos, seq = _paged_case(g, lens, q_lens, nq, nkv, hd, ps, dtype)
+    scale = hd ** -0.5
+    got = ops.attention_simt(q, kc, vc, bt, pos, seq, nq, nkv, hd, scale, window)
+    want = ref.attention_simt(q.float(), kc.float(), vc.float(), bt, pos, seq, nq, nkv, hd, scale, window)
+    _close(got, want, dtype, scale=2.0)
+
+
+def test_attention_finds_a_far_key():
+    """One key far back among hundreds, made to stand out by scaling it and the query:
+    the output must be that key's value row.  Random weights alone would hide a kernel
+    that drops or misplaces a single far page."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(8)
+    nq, nkv, hd, ps = 4, 2, 32, 16
+    for dtype in (torch.float32, torch.bfloat16):
+        for far in (0, 15, 16, 17, 255, 256, 300, 511):
+            q, kc, vc, bt, pos, seq = _paged_case(g, [512], [1], nq, nkv, hd, ps, dtype)
+            page, off = int(bt[0, far // ps]), far % ps
+            direction = torch.randn(hd, device="cuda", generator=g)
+            direction /= direction.norm()
+            kc[page, :, off, :] = (direction * 12).to(dtype)
+            q[0] = (direction * 12).repeat(nq).to(dtype)
+            got = ops.attention_simt(q, kc, vc, bt, pos, seq, nq, nkv, hd, 1.0, None).float().reshape(nq, hd)
+            want = vc[page, :, off, :].float().repeat_interleave(nq // nkv, dim=0)
+            torch.testing.assert_close(got, want, rtol=2e-2, atol=2e-2)
+
+
+def test_attention_window_edge():
+    """A standing-out key exactly at the window's edge is seen, one step beyond it is not."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(9)
+    nq, nkv, hd, ps, window = 2, 1, 16, 8, 24
+    q, kc, vc, bt, pos, seq = _paged_case(g, [100], [1], nq, nkv, hd, ps, torch.float32)
+    direction = torch.ones(hd, device="cuda") / hd ** 0.5
+    q[0] = (direction * 10).repeat(nq)
+    for key, seen in ((99 - window + 1, True), (99 - window, False)):
+        k2 = kc.clone()
+        page, off = int(bt[0, key // ps]), key % ps
+        k2[page, :, off, :] = direction * 10
+        got = ops.attention_simt(q, k2, vc, bt, pos, seq, nq, nkv, hd, 1.0, window).reshape(nq, hd)
+        is_value = torch.allclose(got[0], vc[page, 0, off], rtol=1e-2, atol=1e-2)
+        assert is_value == seen
+
+
+@pytest.mark.parametrize("R,V", [(1, 256), (5, 1000), (3, 152064)])
+def test_sample_rows(R, V):
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(10)
+    logits = torch.randn(R, V, device="cuda", generator=g) * 3
+    logits[0, 7] = logits[0, 3] = logits[0].max() + 1          # a tie: the first maximum wins
+    assert ops.sample_rows(logits).tolist() == [3] + logits[1:].argmax(-1).tolist()
+    temps = torch.tensor([0.8, 0.0, 1.3, 0.5, 2.0][:R], device="cuda")
+    for trial in range(4):
+        u = torch.rand(R, device="cuda", generator=g, dtype=torch.float64)
+        got = ops.sample_rows(logits, temps, u).tolist()
+        want = ref.sample_rows(logits, temps, u).tolist()
+        assert got == want
+    # the ends of the unit interval
+    lo = ops.sample_rows(logits, temps, torch.zeros(R, device="cuda", dtype=torch.float64)).tolist()
+    hi = ops.sample_rows(logits, temps, torch.ones(R, device="cuda", dtype=torch.float64)).tolist()
+    for r in range(R):
+        if float(temps[r]) > 0:
+            assert lo[r] == 0 and hi[r] >= V - 2
+
+
+def test_gather_rows():
+    ops = _ops()
+    x = torch.randn(40, 1000, device="cuda")
+    rows = torch.tensor([39, 0, 7, 7], dtype=torch.int32, device="cuda")
+    assert torch.equal(ops.gather_rows(x, rows), x[rows.long()])
+    assert torch.equal(ops.gather_rows(x.bfloat16(), rows), x.bfloat16()[rows.long()])
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    ops = _ops()
+    from sllm_b200.ops import KernelError
+    with pytest.raises(KernelError, match="CUDA"):
+        ops.embed_gather(torch.zeros(4, 4), torch.zeros(2, dtype=torch.int32))
+    x = torch.zeros(4, 8, device="cuda")
+    with pytest.raises(KernelError):
+        ops.linear(x, torch.zeros(4, 9, device="cuda"), None, torch.float32)
+    q = torch.zeros(1, 2 * 272, device="cuda")
+    kc = torch.zeros(2, 1, 16, 272, device="cuda")
+    with pytest.raises(KernelError, match="head_dim"):
+        ops.attention_simt(q, kc, kc, torch.zeros(1, 1, dtype=torch.int32, device="cuda"),
+                           torch.zeros(1, dtype=torch.int32, device="cuda"),
+                           torch.zeros(1, dtype=torch.int32, device="cuda"), 2, 1, 272, 1.0, None)

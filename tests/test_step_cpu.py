@@ -55,3 +55,27 @@ def test_cuttings_match_plain(tiny, cpu_ops):
         eng.finish(k)
     eng.cache.check()
     assert all(g.pool.used_count == 0 for g in eng.cache.groups)
+
+
+def _requests(cfg, lengths, seed):
+    rng = np.random.default_rng(seed)
+    return {f"r{i}": rng.integers(0, cfg["vocab_size"], n).tolist() for i, n in enumerate(lengths)}
+
+
+@pytest.mark.parametrize("mode", ["whole", "tail_decode", "portions", "mixed"])
+def test_trace_modes_on_cpu(tiny, cpu_ops, mode):
+    """The four ways of cutting, through the engine with the CPU stand-in kernels."""
+    from tests import traces
+    name, model_dir, page = tiny
+    cfg, w = plain.load_model(model_dir)
+    reqs = _requests(cfg, (50, 37, 64, 45, 41, 58), 11)
+    want = {r: plain.forward(ids, w, cfg) for r, ids in reqs.items()}
+    tr = getattr(traces, mode)(reqs)
+    model, _ = build_model(model_dir, "float32", "cpu")
+    eng = Engine(model, page_size=page, num_pages=tr.max_tokens // page, max_requests=4)
+    out = traces.replay_engine(tr, eng)
+    traces.compare(tr, out, want, rtol=1e-4, atol=1e-5, what=f"{name}/{mode}")
+    eng.cache.check()
+    assert not eng.cache.requests
+    if mode == "mixed":
+        assert eng.cache.reuse_count > 0, "the pool was meant to be so small that pages are used again"
