@@ -1,0 +1,314 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Qwen2.5-7B layer sizes on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step of a batch of requests (default 8) whose contexts end at
+the benchmark's context length (4096).  Prints ONE JSON line: decoded tokens per
+second timed on the device with CUDA events (``value``), the same through the Python
+entry point with host tokens in and out (``e2e``), the prefill of 2,048 tokens,
+the decode step's share of the HBM roofline, and decode at batch 1 and 64.
+Weights are random (drawn on the device), token ids uniform random: there is no
+dataset.  The decode step reads every weight once (15 GB, far more than the 126 MB
+L2), so successive steps cannot be served from cache.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: Qwen2.5-7B sizes
+CONFIG_7B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 28, "hidden_size": 3584, "num_attention_heads": 28, "num_key_value_heads": 4,
+    "head_dim": 128, "intermediate_size": 18944, "vocab_size": 152064, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "max_position_embeddings": 32768, "tie_word_embeddings": False,
+    "hidden_act": "silu",
+}
+FULL_LAYERS = 28
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {k: float(p[k]) for k in FALLBACK_PEAKS}, "measured"
+    except (OSError, KeyError, ValueError):
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi's clocks and throttle reasons, sampled every 200 ms while a timed
+    region runs.  Reading only; no setting of the GPU is touched."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            with open(self.path) as f:
+                for line in f:
+                    parts = [p.strip() for p in line.split(",")]
+                    if len(parts) < 8:
+                        continue
+                    try:
+                        sm.append(float(parts[0]))
+                        mx.append(float(parts[1]))
+                    except ValueError:
+                        continue
+                    for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                         parts[4:8]):
+                        if val.lower().startswith("active"):
+                            reasons.add(name)
+            os.remove(self.path)
+        except OSError:
+            pass
+        if not sm:
+            return None
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+class DeviceTimer:
+    """Sums the device time of the parts of steps bracketed by start()/stop(), with CUDA
+    events on the launching stream."""
+
+    def __init__(self):
+        import torch
+        self.torch = torch
+        self.pairs = []
+        self._open = None
+
+    def start(self):
+        ev = self.torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self._open = ev
+
+    def stop(self):
+        if self._open is None:
+            return
+        ev = self.torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.pairs.append((self._open, ev))
+        self._open = None
+
+    def total_ms(self):
+        self.torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in self.pairs)
+
+
+def flops_of_step(cfg, tokens_per_req, ctx_before, logits_rows):
+    """FLOPs of one step: 2 per multiply-add of every matrix product, and the causal
+    attention's q.k and p.v products over the keys each query sees."""
+    H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    nq, nkv, hd, V = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["vocab_size"]
+    per_layer = (nq + 2 * nkv) * hd * H + nq * hd * H + 3 * I * H
+    T = sum(tokens_per_req)
+    fl = 2.0 * T * per_layer * L + 2.0 * logits_rows * V * H
+    for n, c in zip(tokens_per_req, ctx_before):
+        keys = n * c + n * (n + 1) / 2.0
+        fl += 4.0 * keys * hd * nq * L
+    return fl
+
+
+def decode_run(model, cfg, batch, context, steps, warmup, seed=0):
+    """Prefill `batch` requests through the entry point, then time `steps` decode steps."""
+    import numpy as np
+    import torch
+
+    from sllm_b200 import ops
+    from sllm_b200.engine.llm import LLM
+    from sllm_b200.sampling import SamplingParams
+    prompt_len = context - (steps + warmup)
+    page = 16
+    pages = batch * (-(-(context + 1) // page))
+    # every request gets a portion in every step, so that all prompts end in the same step
+    chunk = 512
+    llm = LLM(model=model, block_size=page, num_pages=pages, max_num_seqs=batch, max_batch_tokens=batch * chunk,
+              chunk_size=chunk, max_model_len=context + 1, policy="reserve")
+    rng = np.random.default_rng(seed)
+    for i in range(batch):
+        llm.add_request(rng.integers(0, cfg["vocab_size"], prompt_len).tolist(),
+                        SamplingParams(max_new=steps + warmup))
+    while any(r.pending > 1 or r.num_computed == 0 for r in llm.scheduler.running) or llm.scheduler.waiting:
+        llm.step()                                    # prompts, in portions under the token budget
+    for _ in range(warmup - 1):                       # the step that ended the prompts made token 1
+        llm.step()
+    torch.cuda.synchronize()
+    timer = DeviceTimer()
+    clocks = ClockSampler()
+    clocks.start()
+    before = dict(ops.launches)
+    h2d = d2h = 0
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        _, sampled = llm.step(device_timer=timer)
+        assert len(sampled) == batch
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    dev_ms = timer.total_ms()
+    clk = clocks.stop()
+    launches = {k: ops.launches[k] - before[k] for k in before}
+    # bytes the step has to read: every weight once, and the live requests' cache
+    ctx_mean = prompt_len + warmup + (steps - 1) / 2.0
+    kv_bytes = llm.engine.cache.bytes_per_token(2 if model.dtype == torch.bfloat16 else 4) * ctx_mean * batch
+    step_bytes = model.weight_bytes() + kv_bytes
+    # per step: the packed int32 batch description goes up, the sampled ids come down
+    mp = -(-(context + 1) // page)
+    h2d = 4 * (3 * batch + (batch + 1) + 2 * batch + batch + batch + batch * mp)
+    d2h = 4 * batch
+    for r in list(llm.scheduler.running):
+        llm.abort(r.req_id)
+    del llm
+    torch.cuda.empty_cache()
+    return {"ms_per_step": dev_ms / steps, "tok_s": batch * steps / (dev_ms / 1e3),
+            "e2e_tok_s": batch * steps / wall, "e2e_ms_per_step": wall * 1e3 / steps,
+            "step_bytes": step_bytes, "clocks": clk, "launches": launches, "h2d": h2d, "d2h": d2h,
+            "prompt_len": prompt_len}
+
+
+def prefill_run(model, cfg, tokens, reps=3, seed=1):
+    import numpy as np
+    import torch
+
+    from sllm_b200.engine import Engine, StepEntry
+    eng = Engine(model, page_size=16, num_pages=-(-tokens // 16) + 1, max_requests=2)
+    rng = np.random.default_rng(seed)
+    times = []
+    for i in range(reps + 1):
+        ids = rng.integers(0, cfg["vocab_size"], tokens).tolist()
+        entries = [StepEntry(i, ids, [tokens - 1])]
+        ctx = eng.prepare(entries)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        eng.run(ctx, entries)
+        b.record()
+        torch.cuda.synchronize()
+        eng.finish(i)
+        if i:                                          # the first is warm-up
+            times.append(a.elapsed_time(b))
+    del eng
+    torch.cuda.empty_cache()
+    return statistics.median(times)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer than 28 only where memory or time needs it")
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64 and the prefill")
+    args = ap.parse_args(argv)
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "skfine24/sLLM has no setup.py or pyproject.toml: pip cannot install it offline "
+                          "(\"Neither 'setup.py' nor 'pyproject.toml' found\"), and its CUDA path is built for "
+                          "sm_121 with one-token decode only"}))
+        return 0
+    if args.gpus != 1:
+        print(json.dumps({"error": f"this engine runs on one GPU; --gpus {args.gpus} is not supported", "n_gpus": args.gpus}))
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    from sllm_b200.engine import build_random_model
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device"}))
+        return 1
+    peaks, peaks_kind = load_peaks()
+    cfg = dict(CONFIG_7B)
+    cfg["num_hidden_layers"] = args.layers
+    model, _ = build_random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0", std=0.02)
+    torch.cuda.synchronize()
+
+    main_run = decode_run(model, cfg, args.batch, args.context, args.steps, args.warmup)
+    points = {}
+    prefill = None
+    if not args.no_points:
+        for b in (1, 64):
+            r = decode_run(model, cfg, b, args.context, max(8, args.steps // 2), 3, seed=b)
+            points[f"decode_b{b}"] = round(r["tok_s"], 1)
+            points[f"decode_b{b}_hbm_frac"] = round(r["step_bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+        ms = prefill_run(model, cfg, PREFILL_TOKENS)
+        fl = flops_of_step(cfg, [PREFILL_TOKENS], [0], 1)
+        prefill = {"value": round(PREFILL_TOKENS / (ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(ms, 3),
+                   "frac": round(fl / (ms / 1e3) / 1e12 / peaks["bf16_tflops"], 4),
+                   "tflops": round(fl / (ms / 1e3) / 1e12, 1), "peak_tflops": peaks["bf16_tflops"]}
+
+    achieved = main_run["step_bytes"] / (main_run["ms_per_step"] / 1e3) / 1e9
+    out = {
+        "metric": "decode tok/s (Qwen2.5-7B sizes, bf16, batch 8, context 4096)",
+        "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02), uniform random token ids",
+        "config": {
+            "model": "Qwen2.5-7B sizes", "layers": args.layers, "layers_full": FULL_LAYERS,
+            "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "global_batch": args.batch, "seq_len": args.context, "prompt_len": main_run["prompt_len"],
+            "page_size": 16, "kv_dtype": "bf16", "parallelism": "1 GPU",
+            "l2": "inputs larger than L2 (15 GB of weights read per step)", "peaks": peaks_kind,
+        },
+        "e2e": {"value": round(main_run["e2e_tok_s"], 1), "unit": "tokens/s",
+                "ms_per_step": round(main_run["e2e_ms_per_step"], 4),
+                "h2d_bytes_per_step": main_run["h2d"], "d2h_bytes_per_step": main_run["d2h"]},
+        "gpu_launches": main_run["launches"]["own"],
+        "library_launches": main_run["launches"]["library"],
+        "clocks": main_run["clocks"],
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+    }
+    if prefill:
+        out["prefill"] = prefill
+    if points:
+        out["points"] = points
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

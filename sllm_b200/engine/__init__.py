@@ -1,4 +1,4 @@
 from .engine import ContextOverflow, Engine, StepEntry
-from .loading import build_model, parse_dtype
+from .loading import build_model, build_random_model, parse_dtype
 
-__all__ = ["ContextOverflow", "Engine", "StepEntry", "build_model", "parse_dtype"]
+__all__ = ["ContextOverflow", "Engine", "StepEntry", "build_model", "build_random_model", "parse_dtype"]

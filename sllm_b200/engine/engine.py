@@ -178,7 +178,10 @@ class Engine:
         device, R the number of wanted places, in the order of the entries and of
         each entry's ``want``."""
         entries = list(entries)
-        ctx = self.prepare(entries)
+        return self.run(self.prepare(entries), entries)
+
+    def run(self, ctx: StepContext, entries) -> torch.Tensor:
+        """The device part of a step prepared by `prepare`."""
         logits = self.model.forward(ctx, self.layer_caches)
         for e, tot in zip(entries, ctx.ctx_lens):
             self.cache.commit(e.req_id, tot)

@@ -1,0 +1,123 @@
+"""The Python entry point: a model folder in, generated token ids out.
+
+The reference's entry points work on text through its own tokenizer
+(``InferenceEngine.complete/chat``, serving/executor.py:536-754) and run each
+sequence's forward on its own (``BatchedInferenceEngine.step``,
+serving/executor.py:1034-1082).  This engine's interface is token ids; every step
+is one batched forward through `Engine.step`, and sampling runs on the device.
+Option names follow the reference where it has them: ``max_new``, ``temperature``,
+``top_k``, ``top_p``, ``seed``, ``repetition_penalty`` (serving/executor.py:334-345),
+``block_size``/``chunk_size``/``max_num_seqs`` (runtime/scheduler.py:62-69; recipe
+``defaults``), ``kv_utilization`` (recipes/schema.py:255).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..sampling import Sampler, SamplingParams
+from .engine import Engine, StepEntry
+from .loading import build_model, parse_dtype
+from .scheduler import Scheduler
+
+
+@dataclass
+class GenerationResult:
+    req_id: object
+    prompt: list
+    ids: list                  # generated token ids (a stop id is not among them)
+    finish_reason: str         # "stop" | "length" | "abort"
+    preemptions: int = 0
+
+
+def plan_num_pages(model, page_size: int, *, kv_utilization: float = 0.9, kv_bytes: int | None = None,
+                   cap_tokens: int | None = None) -> int:
+    """Pages that fit the device memory left after the weights, times the utilisation
+    (runtime/placement.py:48-51: budget * utilisation // (bytes per token * block size)),
+    or an explicit budget in bytes; never more than ``cap_tokens`` worth."""
+    from ..cache.manager import CacheManager
+    probe = CacheManager(model.cache_needs(), page_size=page_size, num_pages=0, max_requests=1)
+    item = 2 if model.dtype == torch.bfloat16 else 4
+    per_token = max(probe.bytes_per_token(item), 1)
+    if kv_bytes is None:
+        free, _ = torch.cuda.mem_get_info(model.device)
+        kv_bytes = int(free * kv_utilization)
+    pages = kv_bytes // (per_token * page_size)
+    if cap_tokens is not None:
+        pages = min(pages, -(-cap_tokens // page_size))
+    return max(int(pages), 1)
+
+
+class LLM:
+    def __init__(self, model_dir: str | None = None, *, model=None, dtype="bfloat16", device="cuda:0",
+                 block_size: int = 16, num_pages: int | None = None, kv_utilization: float = 0.9,
+                 kv_bytes: int | None = None, max_num_seqs: int = 8, max_batch_tokens: int = 2048,
+                 chunk_size: int = 512, max_model_len: int | None = None, policy: str = "reserve",
+                 progress=None):
+        if (model_dir is None) == (model is None):
+            raise ValueError("give a model folder or a built model")
+        if model is None:
+            model, _ = build_model(model_dir, parse_dtype(dtype), device, progress=progress)
+        self.model = model
+        self.max_model_len = min(max_model_len or model.plan.max_positions, model.plan.max_positions)
+        if num_pages is None:
+            num_pages = plan_num_pages(model, block_size, kv_utilization=kv_utilization, kv_bytes=kv_bytes,
+                                       cap_tokens=max_num_seqs * self.max_model_len + block_size * max_num_seqs)
+        self.engine = Engine(model, page_size=block_size, num_pages=num_pages, max_requests=max_num_seqs)
+        self.scheduler = Scheduler(self.engine.cache, max_positions=self.max_model_len, max_num_seqs=max_num_seqs,
+                                   max_batch_tokens=max_batch_tokens, chunk_size=chunk_size, policy=policy)
+        self.sampler = Sampler(model.device)
+        self._next_id = 0
+        self.steps = 0
+
+    # ---- request-level interface ---------------------------------------------------------
+    def add_request(self, prompt_token_ids, params: SamplingParams | None = None, req_id=None):
+        if req_id is None:
+            req_id = self._next_id
+            self._next_id += 1
+        return self.scheduler.add(req_id, prompt_token_ids, params or SamplingParams())
+
+    def abort(self, req_id) -> bool:
+        return self.scheduler.abort(req_id)
+
+    def step(self, device_timer=None):
+        """Schedule, run and sample one step.  Returns (finished requests, new tokens by request).
+        ``device_timer``: an object whose ``start()``/``stop()`` are called around the part of
+        the step that runs on the device (measurement only)."""
+        sched = self.scheduler
+        plan = sched.schedule()
+        if not plan:
+            if sched.has_work:
+                # serving/executor.py:1094-1099: requests remain but nothing can be scheduled
+                raise RuntimeError("scheduler stalled: requests remain but none can be scheduled "
+                                   "(the cache cannot hold the next one)")
+            return [], {}
+        entries = [StepEntry(p.req.req_id, p.req.tokens[p.start:p.start + p.count],
+                             [p.count - 1] if p.sample else []) for p in plan]
+        ctx = self.engine.prepare(entries)
+        rows = [(p.req.params, p.req.rng, p.req.tokens if not p.req.params.on_device else None)
+                for p in plan if p.sample]
+        if device_timer is not None:
+            device_timer.start()
+        logits = self.engine.run(ctx, entries)
+        ids = self.sampler.sample(logits, rows, device_timer=device_timer)
+        sampled = {p.req.req_id: t for p, t in zip((p for p in plan if p.sample), ids)}
+        finished = sched.update(plan, sampled)
+        self.steps += 1
+        return finished, sampled
+
+    # ---- batch interface -------------------------------------------------------------------
+    def generate(self, prompt_token_ids, params=None) -> list[GenerationResult]:
+        """Generate for each prompt (a list of token ids).  ``params``: one
+        `SamplingParams` for all, or one per prompt.  Results in the prompts' order."""
+        prompts = list(prompt_token_ids)
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        if len(params) != len(prompts):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        reqs = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        while any(r.status != "finished" for r in reqs):
+            self.step()
+        return [GenerationResult(r.req_id, r.prompt, list(r.output), r.finish_reason, r.preemptions) for r in reqs]

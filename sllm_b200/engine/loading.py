@@ -29,3 +29,32 @@ def build_model(model_dir: str, dtype="bfloat16", device="cuda:0", *, progress=N
     model = CausalLM(arch.plan(cfg), dtype=parse_dtype(dtype), device=device)
     load_into(model, model_dir, progress=progress)
     return model, cfg
+
+
+def build_random_model(config: dict, seed: int, dtype="bfloat16", device="cuda:0", *, std: float = 0.02,
+                       gain_std: float = 0.0):
+    """A model of ``config`` (config.json's keys) with weights drawn on the device, one
+    tensor at a time, without a model folder: for sizes whose folder would take minutes to
+    write and read.  (model, typed config)."""
+    from ..config.registry import architecture_of
+    arch = architecture_of(config)
+    cfg = arch.config_cls.from_dict(config)
+    dt = parse_dtype(dtype)
+    model = CausalLM(arch.plan(cfg), dtype=dt, device=device)
+    specs = {s.name: s for s in model.tensor_specs()}
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+
+    def fetch(name):
+        s = specs[name]
+        if s.role == "gain":
+            t = torch.ones(s.shape, dtype=torch.float32, device=device)
+            if gain_std:
+                t += gain_std * torch.randn(s.shape, generator=gen, device=device)
+            return t
+        t = torch.empty(s.shape, dtype=dt if s.role != "bias" else torch.float32, device=device)
+        t.normal_(0.0, std, generator=gen)
+        return t
+
+    model.bind(fetch)
+    return model, cfg

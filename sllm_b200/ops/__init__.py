@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import torch
 
-from ._lib import KernelError, call, lib  # noqa: F401
+from ._lib import KernelError, call, launches, lib  # noqa: F401
 
 F32, BF16 = 0, 1
 
@@ -103,6 +103,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype) -> to
     _chk(x, w, bias)
     if not x.is_cuda:
         raise KernelError("linear: CUDA only")
+    launches["library"] += 1
     if out_dtype == torch.float32:
         out = torch.mm(x, w.t(), out_dtype=torch.float32)
     else:

@@ -9,6 +9,7 @@ import threading
 
 _lock = threading.Lock()
 _lib = None
+launches = {"own": 0, "library": 0}     # kernels launched since import: this package's, and library products
 
 
 class KernelError(RuntimeError):
@@ -70,6 +71,7 @@ def declare_optional(name: str, argtypes) -> bool:
 def call(name: str, *args) -> None:
     L = lib()
     rc = getattr(L, name)(*args)
+    launches["own"] += 1
     if rc != 0:
         msg = L.sllm_last_error().decode(errors="replace")
         raise KernelError(f"{name} failed (code {rc}): {msg}")

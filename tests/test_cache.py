@@ -1,0 +1,151 @@
+"""The cache manager without a device: no page lost, held twice or freed twice, under
+random orders of requests; windows give pages back; state slots."""
+
+import random
+
+import pytest
+
+from sllm_b200.cache import CacheManager, OutOfPages, PagePool, SlotPool
+from sllm_b200.parts import PagedKV, SlotState
+
+
+def test_page_pool_lowest_first_and_ownership():
+    p = PagePool(6)
+    assert p.allocate("a", 3) == [0, 1, 2] and p.allocate("b", 2) == [3, 4]
+    with pytest.raises(OutOfPages):
+        p.allocate("c", 2)
+    assert p.free_count == 1                                 # a failed allocation takes nothing
+    with pytest.raises(ValueError, match="not held"):
+        p.free("b", [0])
+    with pytest.raises(ValueError, match="twice"):
+        p.free("a", [1, 1])
+    with pytest.raises(ValueError):
+        p.free("a", [0, 3])                                  # validated before anything is freed
+    assert p.owned("a") == [0, 1, 2]
+    p.free("a", [1])
+    with pytest.raises(ValueError, match="not held"):
+        p.free("a", [1])                                     # freed twice
+    assert p.allocate("c", 2) == [1, 5]                      # lowest ids first
+    p.check()
+
+
+def test_slot_pool():
+    s = SlotPool(2)
+    assert s.allocate("a") == 0 and s.allocate("b") == 1
+    with pytest.raises(OutOfPages):
+        s.allocate("c")
+    with pytest.raises(ValueError):
+        s.free("a", 1)
+    s.free("a", 0)
+    assert s.allocate("c") == 0
+    s.check()
+
+
+def _manager(num_pages=12, page=4, window=None, max_requests=4, layers=3):
+    needs = [("own", PagedKV(2, 16, window)) for _ in range(layers)]
+    return CacheManager(needs, page_size=page, num_pages=num_pages, max_requests=max_requests)
+
+
+def test_reserve_commit_free():
+    m = _manager()
+    assert len(m.groups) == 1 and m.groups[0].runs == [0, 1, 2]
+    assert m.bytes_per_token(2) == 3 * 2 * 2 * 16 * 2
+    m.add_request("a")
+    m.reserve("a", 9)
+    assert m.requests["a"].tables[0] == [0, 1, 2]
+    m.reserve("a", 9)                                        # no more pages for the same count
+    assert m.groups[0].pool.used_count == 3
+    with pytest.raises(ValueError, match="beyond"):
+        m.commit("a", 13)
+    m.commit("a", 9)
+    assert m.slot_of_token("a", 0, 6) == 1 * 4 + 2
+    with pytest.raises(ValueError, match="already live"):
+        m.add_request("a")
+    m.add_request("b")
+    with pytest.raises(OutOfPages):
+        m.reserve("b", 40)
+    assert m.requests["b"].tables[0] == [] and m.groups[0].pool.used_count == 3   # all or nothing
+    assert not m.can_reserve("b", 40) and m.can_reserve("b", 36)
+    m.free_request("a")
+    with pytest.raises(KeyError):
+        m.free_request("a")
+    m.free_request("b")
+    m.check()
+    assert m.groups[0].pool.free_count == 12 and m.slots.free_count == 4
+
+
+def test_groups_by_need_and_borrowed_cache():
+    needs = [("own", PagedKV(2, 16)), ("own", PagedKV(2, 16, 8)), ("own", PagedKV(2, 16)), ("borrow", 0),
+             ("own", SlotState((3, 5))), ("own", None)]
+    m = CacheManager(needs, page_size=4, num_pages=[10, 6], max_requests=2)
+    assert [g.runs for g in m.groups] == [[0, 2], [1]]
+    m.add_request("a")
+    m.reserve("a", 20)
+    assert len(m.requests["a"].tables[0]) == 5 and len(m.requests["a"].tables[1]) == 5
+    m.commit("a", 20)                          # the window group has let go of what lies behind it
+    assert m.requests["a"].tables[1][:3] == [-1, -1, -1] and m.groups[1].pool.used_count == 2
+    assert m.groups[0].pool.used_count == 5
+    import torch
+    caches = m.allocate_storage(torch.float32, "cpu")
+    assert caches[3].k.data_ptr() == caches[0].k.data_ptr() and caches[3].group == 0
+    assert caches[1].group == 1 and caches[4].state.shape == (2, 3, 5) and caches[5].k is None
+
+
+def test_window_gives_pages_back():
+    m = _manager(num_pages=6, page=4, window=6, layers=1)
+    m.add_request("a")
+    total = 0
+    for n in (5, 3, 1, 1, 7, 2, 1, 1, 1, 4):
+        total += n
+        m.reserve("a", total)
+        m.commit("a", total)
+        m.check()
+        first_needed = max(0, total - 6 + 1) // 4
+        table = m.requests["a"].tables[0]
+        assert all(p == -1 for p in table[:first_needed]) and all(p >= 0 for p in table[first_needed:])
+        if first_needed:
+            with pytest.raises(ValueError, match="given back"):
+                m.slot_of_token("a", 0, 0)
+    assert total == 26 and m.groups[0].pool.used_count <= 3     # 26 tokens would need 7 pages without the window
+    assert m.reuse_count > 0
+    m.free_request("a")
+    m.check()
+    assert m.groups[0].pool.free_count == 6
+
+
+@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("window", [None, 10])
+def test_random_orders_keep_the_books(seed, window):
+    rng = random.Random(seed)
+    m = _manager(num_pages=20, page=4, window=window, max_requests=5, layers=2)
+    live = {}
+    next_id = 0
+    for _ in range(400):
+        action = rng.random()
+        if action < 0.25 and len(live) < 5:
+            m.add_request(next_id)
+            live[next_id] = 0
+            next_id += 1
+        elif action < 0.8 and live:
+            r = rng.choice(list(live))
+            n = live[r] + rng.choice([1, 1, 1, 2, 5, 9])
+            if m.can_reserve(r, n):
+                m.reserve(r, n)
+                m.commit(r, n)
+                live[r] = n
+            else:
+                before = m.groups[0].pool.free_count
+                with pytest.raises(OutOfPages):
+                    m.reserve(r, n)
+                assert m.groups[0].pool.free_count == before
+        elif live:
+            r = rng.choice(list(live))
+            m.free_request(r)
+            del live[r]
+        m.check()
+        held = sum(sum(1 for p in m.requests[r].tables[0] if p >= 0) for r in live)
+        assert held == m.groups[0].pool.used_count
+    for r in list(live):
+        m.free_request(r)
+    m.check()
+    assert m.groups[0].pool.free_count == 20 and m.slots.free_count == 5

@@ -79,3 +79,26 @@ def test_trace_modes_on_cpu(tiny, cpu_ops, mode):
     assert not eng.cache.requests
     if mode == "mixed":
         assert eng.cache.reuse_count > 0, "the pool was meant to be so small that pages are used again"
+
+
+def test_generate_on_cpu_matches_plain(tiny, cpu_ops):
+    """Greedy and temperature generation through the entry point (scheduler, engine,
+    sampler) with the CPU stand-in kernels, against the plain implementation."""
+    from sllm_b200.engine.llm import LLM
+    from sllm_b200.sampling import SamplingParams
+    name, model_dir, page = tiny
+    cfg, w = plain.load_model(model_dir)
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (5, 17, 33, 1)]
+    model, _ = build_model(model_dir, "float32", "cpu")
+    for policy, pages in (("reserve", 64), ("on_demand", 9 if page == 16 else 17)):
+        llm = LLM(model=model, block_size=page, num_pages=pages, max_num_seqs=3, chunk_size=24,
+                  max_batch_tokens=40, policy=policy)
+        res = llm.generate(prompts, SamplingParams(max_new=8))
+        for p, r in zip(prompts, res):
+            assert r.ids == plain.generate(p, 8, w, cfg) and r.finish_reason == "length"
+        res = llm.generate(prompts[:2], SamplingParams(max_new=6, temperature=0.8, seed=7))
+        for p, r in zip(prompts, res):
+            assert r.ids == plain.generate(p, 6, w, cfg, temperature=0.8, seed=7)
+        llm.engine.cache.check()
+        assert not llm.engine.cache.requests
