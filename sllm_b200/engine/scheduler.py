@@ -201,12 +201,16 @@ class Scheduler:
             if n > 0:
                 cache.reserve(r.req_id, r.num_computed + n)
             return max(n, 0)
-        # a decoding request: make room by preempting the youngest other request
+        # a decoding request: make room by preempting the youngest running request,
+        # which may be this one
         while not cache.can_reserve(r.req_id, r.num_computed + 1):
-            victims = [v for v in self.running if v is not r and v.status == "running"]
-            if not victims:
-                raise RuntimeError(f"request {r.req_id!r} cannot get a page although it runs alone")
-            v = victims[-1]
+            live = [v for v in self.running if v.status == "running"]
+            v = live[-1]
+            if v is r:
+                if len(live) == 1:
+                    raise RuntimeError(f"request {r.req_id!r} cannot get a page although it runs alone")
+                self._preempt(r)
+                return 0
             for p in [p for p in plan if p.req is v]:
                 plan.remove(p)
                 planned_ids.discard(v.req_id)

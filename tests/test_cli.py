@@ -1,0 +1,68 @@
+"""Command line and recipes: plan mode, precedence, refusals."""
+
+import os
+
+import pytest
+
+from sllm_b200.config import ConfigError
+from sllm_b200.config.recipe import Recipe, resolve_recipe
+from sllm_b200.serving import main as cli
+
+RECIPES = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "recipes")
+
+
+def test_shipped_recipe_loads():
+    r = resolve_recipe("Qwen2.5-Coder-0.5B", RECIPES)
+    cfg = r.config_json()
+    assert (cfg["num_hidden_layers"], cfg["hidden_size"], cfg["head_dim"], cfg["rope_theta"]) == (24, 896, 64, 1e6)
+    assert cfg["tie_word_embeddings"] is True and r.arch == "qwen2" and r.defaults["max_num_seqs"] == 8
+    from sllm_b200.models.qwen2 import Qwen2Config
+    assert Qwen2Config.from_dict(cfg).num_key_value_heads == 2
+
+
+@pytest.mark.parametrize("raw,word", [
+    ({"model_id": "x"}, "arch"), ({"arch": "llama4", "model_id": "x"}, "not served"),
+    ({"arch": "qwen2", "model_id": "x", "dtype": "fp8"}, "dtype"),
+    ({"arch": "qwen2", "model_id": "x", "tp": {"size": 2}}, "one GPU"),
+    ({"arch": "qwen2", "model_id": "x", "defaults": {"max_new": 0}}, "max_new"),
+    ({"arch": "qwen2", "model_id": "x", "memory": {"kv_utilization": 1.5}}, "kv_utilization"),
+])
+def test_recipe_errors_name_the_key(raw, word):
+    with pytest.raises(ConfigError, match=word):
+        Recipe.from_dict(raw)
+
+
+def test_plan_mode_prints_and_runs_nothing(capsys):
+    assert cli.main(["tiny-qwen2"]) == 0
+    out = capsys.readouterr().out
+    assert "tiny-qwen2" in out and "nothing executed" in out and "2 layers" in out and "max_new 16" in out
+    assert cli.main(["tiny-qwen2", "--max-new", "5", "--dtype", "fp32"]) == 0        # command line beats the recipe
+    out = capsys.readouterr().out
+    assert "max_new 5" in out and "float32" in out
+
+
+def test_refusals(capsys):
+    for argv, word in ((["tiny-qwen2", "--mode", "serve"], "serve"), (["tiny-qwen2", "--cpu"], "CPU"),
+                       (["tiny-qwen2", "--placement", "um"], "host-memory"), (["tiny-qwen2", "--tp", "2"], "one GPU"),
+                       (["no-such-recipe"], "not found"),
+                       (["tiny-qwen2", "--mode", "run", "--model-dir", "/nonexistent/dir"], "weights not found")):
+        with pytest.raises(SystemExit) as e:
+            cli.main(argv)
+        assert word in str(e.value)
+    assert cli.main(["--version"]) == 0
+    assert "sllm-b200" in capsys.readouterr().out
+
+
+def test_run_mode_on_cpu_ops(cpu_ops, capsys, monkeypatch):
+    """--mode run with --random-weights, end to end with the CPU stand-in kernels."""
+    import sllm_b200.engine.llm as llm_mod
+    real = llm_mod.LLM
+
+    def on_cpu(model_dir, **kw):
+        kw.update(device="cpu", num_pages=32)
+        return real(model_dir, **kw)
+    monkeypatch.setattr(llm_mod, "LLM", on_cpu)
+    assert cli.main(["tiny-qwen2", "--mode", "run", "--random-weights", "3", "--prompt-ids", "5,6,7", "--max-new", "4",
+                     "--dtype", "float32", "--log-level", "ERROR"]) == 0
+    ids = capsys.readouterr().out.strip().split(",")
+    assert len(ids) == 4 and all(0 <= int(i) < 256 for i in ids)

@@ -1,0 +1,309 @@
+"""The engine on the GPU beyond replay: generation through the entry point, long
+decoding, the first tokens of a sequence, each part alone, and a toy mixer with
+state of its own that is registered, built and stepped from this file alone."""
+
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests.conftest import TINY, cuda_or_skip, make_model_dir
+from tests.plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+TOL = {"float32": dict(rtol=1e-4, atol=2e-5), "bfloat16": dict(rtol=2e-2, atol=2e-2)}
+
+
+def _prompts(cfg, lengths, seed=2):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, cfg["vocab_size"], n).tolist() for n in lengths]
+
+
+@pytest.mark.parametrize("policy", ["reserve", "on_demand"])
+def test_greedy_generation_float32_equals_plain(tiny, policy):
+    from sllm_b200.engine.llm import LLM
+    from sllm_b200.sampling import SamplingParams
+    dev = cuda_or_skip()
+    name, model_dir, page = tiny
+    cfg, w = plain.load_model(model_dir)
+    # on_demand: three requests fill the four pages; the first to need one more while
+    # decoding finds none free and the youngest is preempted
+    prompts = _prompts(cfg, (5, 17, 33, 1) if policy == "reserve" else (page - 2, page - 1, 2 * page - 2, 1))
+    pages = 64 if policy == "reserve" else 4
+    llm = LLM(model_dir, dtype="float32", device=dev, block_size=page, num_pages=pages, max_num_seqs=3,
+              chunk_size=24, max_batch_tokens=40, policy=policy)
+    res = llm.generate(prompts, SamplingParams(max_new=8))
+    for p, r in zip(prompts, res):
+        assert r.ids == plain.generate(p, 8, w, cfg) and r.finish_reason == "length"
+    if policy == "on_demand":
+        assert llm.scheduler.num_preemptions > 0, "the pool was meant to force a preemption"
+    # temperature sampling with the request's own generator reproduces the plain sampler
+    res = llm.generate(prompts[:3], SamplingParams(max_new=16, temperature=0.8, seed=7))
+    for p, r in zip(prompts, res):
+        assert r.ids == plain.generate(p, 16, w, cfg, temperature=0.8, seed=7)
+    # top-k / top-p / penalty rows go through the host sampler
+    res = llm.generate(prompts[:2], SamplingParams(max_new=5, temperature=0.9, top_k=5, top_p=0.9, seed=1,
+                                                   repetition_penalty=1.2))
+    assert all(len(r.ids) == 5 for r in res)
+    # a stop id ends a request and is not part of the output
+    first = plain.generate(prompts[0], 3, w, cfg)
+    (r,) = llm.generate(prompts[:1], SamplingParams(max_new=8, stop_ids=(first[2],)))
+    assert r.finish_reason == "stop" and r.ids == first[:first.index(first[2])]
+    llm.engine.cache.check()
+    assert not llm.engine.cache.requests
+
+
+def test_greedy_generation_bfloat16_stays_within_rounding(tiny):
+    """In bfloat16 a near-tie may fall the other way, so each chosen token is checked
+    against the plain logits of the engine's own sequence: it must be the maximum up to
+    the tolerance of the bfloat16 path."""
+    from sllm_b200.engine.llm import LLM
+    from sllm_b200.sampling import SamplingParams
+    dev = cuda_or_skip()
+    name, model_dir, page = tiny
+    cfg, w = plain.load_model(model_dir)
+    prompts = _prompts(cfg, (5, 17, 33))
+    llm = LLM(model_dir, dtype="bfloat16", device=dev, block_size=page, num_pages=64, max_num_seqs=3, chunk_size=24)
+    for p, r in zip(prompts, llm.generate(prompts, SamplingParams(max_new=12))):
+        seq = p + r.ids
+        logits = plain.forward(seq, w, cfg)
+        for i, tok in enumerate(r.ids):
+            row = logits[len(p) + i - 1]
+            assert row[tok] >= row.max() - 2 * (TOL["bfloat16"]["atol"] + TOL["bfloat16"]["rtol"] * abs(row.max()))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(tiny, dtype):
+    """Three prompt tokens, then one token a step up to the model's position limit; and
+    the first positions of a sequence each as a step of their own."""
+    from sllm_b200.engine import Engine, StepEntry, build_model
+    dev = cuda_or_skip()
+    name, model_dir, page = tiny
+    cfg, w = plain.load_model(model_dir)
+    n = cfg["max_position_embeddings"]
+    ids = _prompts(cfg, (n,), seed=4)[0]
+    want = plain.forward(ids, w, cfg)
+    model, _ = build_model(model_dir, dtype, dev)
+    eng = Engine(model, page_size=page, num_pages=-(-n // page) + 2, max_requests=2)
+    got = [eng.step([StepEntry("a", ids[:3], [0, 1, 2])]).cpu().numpy()]
+    for p in range(3, n):
+        got.append(eng.step([StepEntry("a", ids[p:p + 1], [0])]).cpu().numpy())
+    got = np.concatenate(got)
+    np.testing.assert_allclose(got, want, **TOL[dtype])
+    with pytest.raises(ValueError, match="exceed"):
+        eng.step([StepEntry("a", [0], [0])])                     # past the position limit
+    # the first tokens, one at a time, beside the long request
+    got = np.concatenate([eng.step([StepEntry("b", ids[p:p + 1], [0])]).cpu().numpy() for p in range(4)])
+    np.testing.assert_allclose(got, want[:4], **TOL[dtype])
+
+
+def test_step_refuses_bad_entries(tiny):
+    from sllm_b200.cache import OutOfPages
+    from sllm_b200.engine import Engine, StepEntry, build_model
+    dev = cuda_or_skip()
+    name, model_dir, page = tiny
+    model, _ = build_model(model_dir, "float32", dev)
+    eng = Engine(model, page_size=page, num_pages=2, max_requests=2)
+    with pytest.raises(OutOfPages):
+        eng.step([StepEntry("a", [1] * (2 * page + 1), [0])])
+    assert not eng.cache.requests and eng.cache.groups[0].pool.used_count == 0      # nothing was taken
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.step([StepEntry("a", [10 ** 6], [0])])
+    with pytest.raises(ValueError, match="twice"):
+        eng.step([StepEntry("a", [1], [0]), StepEntry("a", [2], [0])])
+    with pytest.raises(ValueError, match="outside"):
+        eng.step([StepEntry("a", [1, 2], [2])])
+    assert eng.step([StepEntry("a", [1, 2], [])]).shape == (0, model.plan.vocab_size)   # nothing wanted
+
+
+# ---- each part alone, at sizes that are not the tiny models' -------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_parts_alone(dtype):
+    from sllm_b200.cache import CacheManager
+    from sllm_b200.config import PartSpec
+    from sllm_b200.engine.engine import Engine
+    from sllm_b200.parts import FEED_FORWARDS, MIXERS, NORMS, POSITIONS, LayerCache
+    dev = cuda_or_skip()
+    H, nq, nkv, hd, I, eps, theta, rot = 72, 6, 2, 48, 200, 3e-6, 5e4, 24
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+    rng = np.random.default_rng(0)
+    kw = dict(dtype=dtype, device=dev)
+
+    def t(a):
+        return torch.from_numpy(np.asarray(a, dtype=np.float32))
+
+    def r(a):
+        return a.astype(np.float32) if dtype == torch.float32 else t(a).bfloat16().float().numpy()
+
+    # norm, with the fused addition
+    norm = NORMS.build(PartSpec("rmsnorm", {"size": H, "eps": eps}), **kw)
+    gain = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    norm.bind(lambda n: t(gain))
+    res, delta = rng.standard_normal((9, H)).astype(np.float32), rng.standard_normal((9, H)).astype(np.float32)
+    total = res + delta
+    res_d = t(res).clone().to(dev)
+    got = norm.add_norm(res_d, t(delta).to(dev))
+    np.testing.assert_allclose(res_d.cpu().numpy(), total, rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(got.float().cpu().numpy(), plain.rms_norm(total, gain, eps), **tol)
+
+    # position encoding: the table is cos/sin of float64 angles
+    pos = POSITIONS.build(PartSpec("rotary", {"theta": theta, "rotary_dim": rot, "max_positions": 300}), **kw)
+    cos, sin = plain.rotary_tables(theta, np.arange(300), rot)
+    np.testing.assert_allclose(pos.table[:, 0].cpu().numpy(), cos[:, :rot // 2], rtol=0, atol=1e-7)
+    np.testing.assert_allclose(pos.table[:, 1].cpu().numpy(), sin[:, :rot // 2], rtol=0, atol=1e-7)
+
+    # feed-forward
+    ffn = FEED_FORWARDS.build(PartSpec("swiglu", {"hidden_size": H, "intermediate_size": I}), **kw)
+    w = {"mlp.gate_proj.weight": r(0.2 * rng.standard_normal((I, H))), "mlp.up_proj.weight": r(0.2 * rng.standard_normal((I, H))),
+         "mlp.down_proj.weight": r(0.2 * rng.standard_normal((H, I)))}
+    ffn.bind(lambda n: t(w[f"mlp.{n}"]))
+    x = r(rng.standard_normal((11, H)))
+    got = ffn.forward(t(x).to(dev).to(dtype), None)
+    np.testing.assert_allclose(got.float().cpu().numpy(), plain.swiglu(x, {f".{k}": v for k, v in w.items()}, ""),
+                               **{k: v * 4 for k, v in tol.items()})
+
+    # mixer: attention over a paged cache, partial rotary, one request in two portions
+    mixer = MIXERS.build(PartSpec("attention", {"hidden_size": H, "num_heads": nq, "num_kv_heads": nkv, "head_dim": hd,
+                                                "qkv_bias": True, "scale": hd ** -0.5, "window": None}), **kw)
+    aw = {}
+    for n_, rows in (("q", nq * hd), ("k", nkv * hd), ("v", nkv * hd)):
+        aw[f"x.self_attn.{n_}_proj.weight"] = r(0.2 * rng.standard_normal((rows, H)))
+        aw[f"x.self_attn.{n_}_proj.bias"] = (0.3 * rng.standard_normal(rows)).astype(np.float32)
+    aw["x.self_attn.o_proj.weight"] = r(0.2 * rng.standard_normal((H, nq * hd)))
+    mixer.bind(lambda n: t(aw[f"x.self_attn.{n}"]))
+    S = 37
+    xs = r(rng.standard_normal((S, H)))
+    cfg = {"num_attention_heads": nq, "num_key_value_heads": nkv, "head_dim": hd}
+    want = plain.attention_mixer(xs, aw, "x", cfg, cos[:S], sin[:S])
+
+    class _M:            # the least a model must offer the engine: cache needs, sizes, device
+        def __init__(self):
+            self.device, self.dtype = torch.device(dev), dtype
+            self.plan = type("P", (), {"vocab_size": 10, "max_positions": 300})()
+
+        def cache_needs(self):
+            return [("own", mixer.cache_need())]
+    eng = Engine(_M(), page_size=8, num_pages=8, max_requests=1)
+    from sllm_b200.engine import StepEntry
+    outs = []
+    for lo, hi in ((0, 20), (20, 22), (22, S)):
+        ctx = eng.prepare([StepEntry("a", [0] * (hi - lo), [])])
+        outs.append(mixer.forward(t(xs[lo:hi]).to(dev).to(dtype), ctx, eng.layer_caches[0], pos).float().cpu().numpy())
+        eng.cache.commit("a", hi)
+    np.testing.assert_allclose(np.concatenate(outs), want, **{k: v * 4 for k, v in tol.items()})
+
+
+# ---- a toy mixer with state of its own ---------------------------------------------------------
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    """A mixer defined here, with a fixed-size state per request instead of keys and values:
+    s_t = decay * s_{t-1} + x_t W_in ; y_t = s_t W_out.  It is registered under a new kind,
+    stands in every second layer of a new architecture beside attention layers, gets a
+    state slot from the cache manager, and is stepped in portions.  No file of the package
+    is touched."""
+    from sllm_b200.config import (Architecture, LayerSpec, ModelPlan, PartSpec, RunEntry, register_architecture,
+                                  unregister_architecture)
+    from sllm_b200.engine import Engine, StepEntry, build_model
+    from sllm_b200.models.qwen2 import Qwen2Config
+    from sllm_b200.models.qwen2 import plan as qwen2_plan
+    from sllm_b200.parts import MIXERS, Mixer, SlotState, TensorSpec
+    from sllm_b200.weights import write_random_model
+    dev = cuda_or_skip()
+    D, DECAY = 12, 0.9
+
+    @MIXERS.register("toy_decay_state", replace=True)
+    class ToyStateMixer(Mixer):
+        def __init__(self, params, **kw):
+            super().__init__(params, **kw)
+            self.h, self.d, self.decay = params["hidden_size"], params["state_dim"], params["decay"]
+
+        def cache_need(self):
+            return SlotState((self.d,))
+
+        def tensor_specs(self):
+            return [TensorSpec("w_in.weight", (self.d, self.h)), TensorSpec("w_out.weight", (self.h, self.d))]
+
+        def bind(self, fetch):
+            self.w_in, self.w_out = self._f32(fetch("w_in.weight")), self._f32(fetch("w_out.weight"))
+
+        def forward(self, x, step, cache, position, write_cache=True):
+            u = x.float() @ self.w_in.t()                       # [T, d]
+            out = torch.empty_like(u)
+            t0 = 0
+            for s, n in enumerate(step.q_lens):                 # each request's tokens in order
+                slot = int(step.state_slots[s])
+                st = cache.state[slot]
+                for i in range(n):
+                    st = self.decay * st + u[t0 + i]
+                    out[t0 + i] = st
+                cache.state[slot] = st
+                t0 += n
+            return out @ self.w_out.t()
+
+    def toy_plan(cfg):
+        base = qwen2_plan(cfg)
+        toy = PartSpec("toy_decay_state", {"hidden_size": cfg.hidden_size, "state_dim": D, "decay": DECAY})
+        layers = tuple(LayerSpec(prefix=l.prefix, mixer=toy if i % 2 else l.mixer, ffn=l.ffn, norm=l.norm,
+                                 mixer_prefix="toy" if i % 2 else l.mixer_prefix) for i, l in enumerate(base.layers))
+        return ModelPlan(architecture="ToyStateLM", hidden_size=base.hidden_size, vocab_size=base.vocab_size,
+                         max_positions=base.max_positions, embedding_name=base.embedding_name, layers=layers,
+                         run_list=tuple(RunEntry(i) for i in range(len(layers))), final_norm=base.final_norm,
+                         final_norm_name=base.final_norm_name, head_name=base.head_name, position=base.position)
+
+    register_architecture(Architecture("ToyStateLM", Qwen2Config, toy_plan), replace=True)
+    try:
+        config, init, page = TINY["B"]
+        config = dict(config, architectures=["ToyStateLM"], num_hidden_layers=4)
+        model_dir = write_random_model(str(tmp_path / "toy"), config, 5, std=0.05, bias_std=0.2, gain_std=0.1)
+        cfg, w = plain.load_model(model_dir)
+
+        def plain_toy(ids):
+            h = plain.embed(ids, w["model.embed_tokens.weight"])
+            cos, sin = plain.rotary_tables(cfg["rope_theta"], np.arange(len(ids)), cfg["head_dim"])
+            for i in range(cfg["num_hidden_layers"]):
+                p = f"model.layers.{i}"
+                x = plain.rms_norm(h, w[f"{p}.input_layernorm.weight"], cfg["rms_norm_eps"])
+                if i % 2:
+                    u = x @ w[f"{p}.toy.w_in.weight"].T
+                    st, ys = np.zeros(D, np.float32), []
+                    for row in u:
+                        st = DECAY * st + row
+                        ys.append(st.copy())
+                    h = h + np.stack(ys) @ w[f"{p}.toy.w_out.weight"].T
+                else:
+                    h = h + plain.attention_mixer(x, w, p, cfg, cos, sin)
+                x = plain.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+                h = h + plain.swiglu(x, w, p)
+            h = plain.rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
+            return h @ w["lm_head.weight"].T
+
+        model, _ = build_model(model_dir, "float32", dev)
+        assert [type(l.mixer).__name__ for l in model.layers] == ["Attention", "ToyStateMixer"] * 2
+        eng = Engine(model, page_size=page, num_pages=20, max_requests=3)
+        assert len(eng.cache.groups) == 1 and sorted(eng.cache.state_runs) == [1, 3]
+        seqs = {"a": _prompts(cfg, (30,), 1)[0], "b": _prompts(cfg, (19,), 2)[0]}
+        want = {k: plain_toy(v) for k, v in seqs.items()}
+        done = {"a": 0, "b": 0}
+        for cuts in ((7, 3), (2, 1), (11, 9), (1, 1), (9, 5)):
+            entries, keys = [], []
+            for k, n in zip("ab", cuts):
+                n = min(n, len(seqs[k]) - done[k])
+                if n:
+                    entries.append(StepEntry(k, seqs[k][done[k]:done[k] + n], list(range(n))))
+                    keys.append((k, done[k], n))
+            got = eng.step(entries).cpu().numpy()
+            r0 = 0
+            for k, lo, n in keys:
+                np.testing.assert_allclose(got[r0:r0 + n], want[k][lo:lo + n], rtol=1e-4, atol=2e-5)
+                r0 += n
+                done[k] += n
+        # a finished request's slot is zeroed for the next one
+        eng.finish("a")
+        got = eng.step([StepEntry("c", seqs["a"][:5], [4])]).cpu().numpy()
+        np.testing.assert_allclose(got[0], want["a"][4], rtol=1e-4, atol=2e-5)
+    finally:
+        unregister_architecture("ToyStateLM")
+        MIXERS.unregister("toy_decay_state")
