@@ -171,11 +171,88 @@ def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, n
     return out
 
 
+NUM_SMS = 148
+
+
+def attention_tiles(q_lens, group_size: int, device):
+    """Tiles of (token, head-in-group) rows for the tensor-core attention kernel: requests
+    whose rows fit one 16-row tile go to the decode form, the others are cut into 64-row
+    tiles for the prefill form.  Returns ``(small, large)``, each ``None`` or
+    ``(tile_seq, tile_row0, count)`` on the device."""
+    small_s, large_s, large_r = [], [], []
+    for s, n in enumerate(q_lens):
+        rows = n * group_size
+        if rows <= 16:
+            small_s.append(s)
+        else:
+            for r0 in range(0, rows, 64):
+                large_s.append(s)
+                large_r.append(r0)
+
+    def up(seqs, rows):
+        if not seqs:
+            return None
+        t = torch.tensor([seqs, rows], dtype=torch.int32).to(device, non_blocking=True)
+        return t[0], t[1], len(seqs)
+    return up(small_s, [0] * len(small_s)), up(large_s, large_r)
+
+
+def choose_splits(num_small: int, nkv: int, max_ctx: int) -> int:
+    """How many ways the decode form cuts the context: enough CTAs to fill the GPU about
+    twice, never less than 256 keys a split."""
+    ctas = max(num_small * nkv, 1)
+    want = -(-2 * NUM_SMS // ctas)
+    return int(max(1, min(want, max_ctx // 256, 32)))
+
+
+def attention_mma(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, decode: bool, num_splits: int,
+                  nq, nkv, hd, scale, window, out=None):
+    """The tensor-core attention kernel on one tile list (see `attention_tiles`)."""
+    _chk(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles[0], tiles[1])
+    if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
+        raise KernelError("attention_mma: bfloat16 only")
+    T = q.shape[0]
+    if out is None:
+        out = torch.empty_like(q)
+    part_o = part_lse = None
+    if num_splits > 1:
+        part_o = torch.empty((num_splits, T, nq, hd), dtype=torch.float32, device=q.device)
+        part_lse = torch.empty((num_splits, T, nq), dtype=torch.float32, device=q.device)
+    call("sllm_attention_mma", _p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_o), _p(part_lse), _p(block_tables),
+         block_tables.shape[1], _p(q_start), _p(ctx_len), _p(tiles[0]), _p(tiles[1]), tiles[2], 1 if decode else 0,
+         num_splits, T, nq, nkv, hd, k_cache.shape[2], float(scale), int(window or 0), _stream())
+    if num_splits > 1:
+        launches["own"] += 1          # the combine kernel
+    return out
+
+
+def mma_supports(hd: int) -> bool:
+    return bool(lib().sllm_attention_mma_supports(int(hd)))
+
+
 def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, window):
-    """Causal attention of the step's tokens over their requests' pages."""
+    """Causal attention of the step's tokens over their requests' pages.  bfloat16 with a
+    head size the tensor-core kernel takes: that kernel (prompt portions in 64-row tiles,
+    decoded tokens in the split-KV form).  Otherwise the CUDA-core kernel."""
     g = step.groups[group]
-    return attention_simt(q, k_cache, v_cache, g.block_tables, step.positions, step.seq_of_token,
-                          nq, nkv, hd, scale, window)
+    if q.dtype != torch.bfloat16 or not mma_supports(hd):
+        return attention_simt(q, k_cache, v_cache, g.block_tables, step.positions, step.seq_of_token,
+                              nq, nkv, hd, scale, window)
+    G = nq // nkv
+    key = ("mma", G)
+    if key not in step.attn_tiles:
+        small, large = attention_tiles(step.q_lens, G, q.device)
+        splits = choose_splits(small[2], nkv, step.max_ctx_len) if (small and not large) else 1
+        step.attn_tiles[key] = (small, large, splits)
+    small, large, splits = step.attn_tiles[key]
+    out = torch.empty_like(q)
+    if small:
+        attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, True, splits,
+                      nq, nkv, hd, scale, window, out)
+    if large:
+        attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, False, 1,
+                      nq, nkv, hd, scale, window, out)
+    return out
 
 
 def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

@@ -48,6 +48,10 @@ def _declare(L):
         "sllm_attention_simt": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                 c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
         "sllm_sample_rows": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        "sllm_attention_mma_supports": [c_int],
+        "sllm_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                               c_int, c_int, c_float, c_int, c_void_p],
     }
     for name, argtypes in sigs.items():
         fn = getattr(L, name)

@@ -242,3 +242,57 @@ def test_kernels_refuse_what_they_cannot_do():
         ops.attention_simt(q, kc, kc, torch.zeros(1, 1, dtype=torch.int32, device="cuda"),
                            torch.zeros(1, dtype=torch.int32, device="cuda"),
                            torch.zeros(1, dtype=torch.int32, device="cuda"), 2, 1, 272, 1.0, None)
+
+
+def _starts(q_lens, lens):
+    qs = [0]
+    for n in q_lens:
+        qs.append(qs[-1] + n)
+    return (torch.tensor(qs, dtype=torch.int32).cuda(), torch.tensor(lens, dtype=torch.int32).cuda())
+
+
+@pytest.mark.parametrize("nq,nkv,hd,ps,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (14, 2, 64, 16, None),
+                                                 (28, 4, 128, 16, None), (8, 1, 128, 32, 40), (6, 3, 64, 4, 9),
+                                                 (40, 2, 32, 16, None)])
+@pytest.mark.parametrize("case", ["prefill", "decode", "decode_split", "mixed"])
+def test_attention_mma(nq, nkv, hd, ps, window, case):
+    """The tensor-core kernel in both forms against the float32 statement: portions that
+    start in mid-context, single tokens, split contexts, and both in one batch."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(11)
+    lens, q_lens = {"prefill": ([70, 33, 200], [70, 5, 131]), "decode": ([300, 1, 17, 64], [1, 1, 1, 1]),
+                    "decode_split": ([1500, 700, 3], [1, 1, 1]), "mixed": ([90, 400, 2, 65], [37, 1, 2, 1])}[case]
+    q, kc, vc, bt, pos, seq = _paged_case(g, lens, q_lens, nq, nkv, hd, ps, torch.bfloat16)
+    q_start, ctx_len = _starts(q_lens, lens)
+    scale = hd ** -0.5
+    want = ref.attention_simt(q.float(), kc.float(), vc.float(), bt, pos, seq, nq, nkv, hd, scale, window)
+    G = nq // nkv
+    small, large = ops.attention_tiles(q_lens, G, "cuda")
+    out = torch.full_like(q, float("nan"))
+    if small:
+        splits = {"decode_split": 5, "decode": 2}.get(case, 1) if not large else 1
+        ops.attention_mma(q, kc, vc, bt, q_start, ctx_len, small, True, splits, nq, nkv, hd, scale, window, out)
+    if large:
+        ops.attention_mma(q, kc, vc, bt, q_start, ctx_len, large, False, 1, nq, nkv, hd, scale, window, out)
+    assert not out.isnan().any(), "a row was not written"
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
+
+
+def test_attention_mma_far_key_and_page_edges():
+    """A standing-out key at page and tile edges of a long context, in the split form."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(12)
+    nq, nkv, hd, ps = 8, 2, 64, 16
+    for far in (0, 15, 16, 63, 64, 65, 1023, 1024, 2047):
+        q, kc, vc, bt, pos, seq = _paged_case(g, [2048], [1], nq, nkv, hd, ps, torch.bfloat16)
+        q_start, ctx_len = _starts([1], [2048])
+        page, off = int(bt[0, far // ps]), far % ps
+        direction = torch.randn(hd, device="cuda", generator=g)
+        direction /= direction.norm()
+        kc[page, :, off, :] = (direction * 14).bfloat16()
+        q[0] = (direction * 14).repeat(nq).bfloat16()
+        small, _ = ops.attention_tiles([1], nq // nkv, "cuda")
+        for splits in (1, 4):
+            got = ops.attention_mma(q, kc, vc, bt, q_start, ctx_len, small, True, splits, nq, nkv, hd, 1.0, None)
+            want = vc[page, :, off, :].float().repeat_interleave(nq // nkv, dim=0)
+            torch.testing.assert_close(got.float().reshape(nq, hd), want, rtol=2e-2, atol=2e-2)
