@@ -90,8 +90,11 @@ __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restric
 // (cache content: ref/incremental.py:135-139; kernels.cu:923-953 for the contiguous form).
 // table: [max_pos][2][rot/2] cos then sin, float32 made from float64 angles.
 // ---------------------------------------------------------------------------
+// The q|k|v rows may arrive as `parts` partial sums (a k-split product), `part_stride` apart;
+// they are added here in order.
 template <typename TI, typename TC>
-__global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, const float* __restrict__ bias,
+__global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int parts, size_t part_stride,
+                                     const float* __restrict__ bias,
                                      const int* __restrict__ positions, const float* __restrict__ table,
                                      int rot, int max_pos, int nq, int nkv, int hd,
                                      const int* __restrict__ slot_mapping, int page_size, int num_pages,
@@ -101,6 +104,11 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, const float* __
   const int width = (nq + 2 * nkv) * hd;
   const TI* x = qkv + (size_t)t * width + (size_t)head * hd;
   const float* b = bias ? bias + (size_t)head * hd : nullptr;
+  auto ld = [&](int d) {
+    float v = to_f32(x[d]);
+    for (int p = 1; p < parts; ++p) v += to_f32(x[p * part_stride + d]);
+    return v + (b ? b[d] : 0.f);
+  };
   const bool is_q = head < nq;
   const bool is_k = !is_q && head < nq + nkv;
   TC* dst;
@@ -117,7 +125,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, const float* __
   }
   const bool rotate = (is_q || is_k) && rot > 0 && table != nullptr;
   if (!rotate) {
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[d] = from_f32<TC>(to_f32(x[d]) + (b ? b[d] : 0.f));
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[d] = from_f32<TC>(ld(d));
     return;
   }
   int pos = positions[t];
@@ -125,13 +133,13 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, const float* __
   const int half = rot / 2;
   const float* cs = table + (size_t)pos * rot;       // cos[half] then sin[half]
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
-    const float x1 = to_f32(x[j]) + (b ? b[j] : 0.f);
-    const float x2 = to_f32(x[j + half]) + (b ? b[j + half] : 0.f);
+    const float x1 = ld(j);
+    const float x2 = ld(j + half);
     const float c = cs[j], s = cs[half + j];
     dst[j] = from_f32<TC>(x1 * c - x2 * s);
     dst[j + half] = from_f32<TC>(x2 * c + x1 * s);
   }
-  for (int d = rot + threadIdx.x; d < hd; d += blockDim.x) dst[d] = from_f32<TC>(to_f32(x[d]) + (b ? b[d] : 0.f));
+  for (int d = rot + threadIdx.x; d < hd; d += blockDim.x) dst[d] = from_f32<TC>(ld(d));
 }
 
 }  // namespace sllm
@@ -201,11 +209,13 @@ SLLM_EXPORT int sllm_gather_rows(const void* x, int dtype, const int* rows, void
   return launch_status("gather_rows");
 }
 
-SLLM_EXPORT int sllm_rope_kv_write(const void* qkv, int in_dtype, const float* bias, const int* positions,
+SLLM_EXPORT int sllm_rope_kv_write(const void* qkv, int in_dtype, int parts, size_t part_stride, const float* bias,
+                                   const int* positions,
                                    const float* table, int rot, int max_pos, int nq, int nkv, int hd,
                                    const int* slot_mapping, int page_size, int num_pages, void* k_cache,
                                    void* v_cache, void* q_out, int cache_dtype, int T, cudaStream_t stream) {
   SLLM_REQUIRE(T >= 0 && nq > 0 && nkv > 0 && hd > 0, "rope_kv_write: bad sizes T=%d nq=%d nkv=%d hd=%d", T, nq, nkv, hd);
+  SLLM_REQUIRE(parts >= 1, "rope_kv_write: parts=%d", parts);
   SLLM_REQUIRE(rot >= 0 && rot <= hd && rot % 2 == 0, "rope_kv_write: rotary_dim=%d must be even and <= head_dim=%d", rot, hd);
   SLLM_REQUIRE(rot == 0 || (table != nullptr && max_pos > 0), "rope_kv_write: rotary table missing");
   SLLM_REQUIRE(slot_mapping == nullptr || (page_size > 0 && num_pages > 0 && k_cache && v_cache),
@@ -214,7 +224,7 @@ SLLM_EXPORT int sllm_rope_kv_write(const void* qkv, int in_dtype, const float* b
   dim3 grid(T, nq + 2 * nkv);
   const int threads = hd / 2 >= 64 ? 64 : 32;
 #define LAUNCH(TI, TC)                                                                                         \
-  rope_kv_write_kernel<TI, TC><<<grid, threads, 0, stream>>>((const TI*)qkv, bias, positions, table, rot,      \
+  rope_kv_write_kernel<TI, TC><<<grid, threads, 0, stream>>>((const TI*)qkv, parts, part_stride, bias, positions, table, rot, \
                                                              max_pos, nq, nkv, hd, slot_mapping, page_size,    \
                                                              num_pages, (TC*)k_cache, (TC*)v_cache, (TC*)q_out)
   if (in_dtype == SLLM_F32 && cache_dtype == SLLM_F32) LAUNCH(float, float);

@@ -91,9 +91,44 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, bias) -> torch.Tensor:
     return out
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype) -> torch.Tensor:
+def stream_supports(M: int, N: int, K: int) -> bool:
+    return bool(lib().sllm_linear_stream_supports(int(M), int(N), int(K)))
+
+
+def linear_stream(x, w, bias, out_dtype, *, splits: int = 1, silu: bool = False):
+    """The weight-streaming kernel for at most 64 tokens.  With ``splits`` > 1 the result is
+    a float32 stack ``[splits', M, N]`` of partial sums (bias in the first) that the consumer
+    adds; with ``silu`` the matrix is gate|up interleaved in blocks of 8 and the result is
+    ``silu(gate) * up`` of width N/2."""
+    _chk(x, w, bias)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"linear: x {tuple(x.shape)} does not fit w {tuple(w.shape)}")
+    L = lib()
+    real = L.sllm_linear_stream_splits(K, int(splits)) if splits > 1 else 1
+    partial = None
+    if real > 1:
+        partial = torch.empty((real, M, N), dtype=torch.float32, device=x.device)
+        out = None
+    else:
+        out = torch.empty((M, N // 2 if silu else N), dtype=out_dtype, device=x.device)
+    call("sllm_linear_stream", _p(x), _p(w), _p(bias), _p(out), _dtc(out_dtype), _p(partial), M, N, K,
+         real if real > 1 else 1, 1 if silu else 0, _stream())
+    return partial if real > 1 else out
+
+
+def _stream_splits(N: int, K: int) -> int:
+    ctas = -(-N // 128)
+    return max(1, min(2 * NUM_SMS // ctas, K // 128, 16))
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype, allow_partials: bool = False) -> torch.Tensor:
     """``x @ w.T (+ bias)``; ``w`` is ``[N, K]``.  float32 operands: this package's
-    float32 kernel.  bfloat16 operands: float32 accumulation, result in ``out_dtype``."""
+    float32 kernel.  bfloat16 operands, float32 accumulation, result in ``out_dtype``: up
+    to 64 rows the weight-streaming kernel (which, if ``allow_partials``, may return a
+    float32 stack of partial sums ``[parts, M, N]`` for the consumer to add); beyond that
+    the library product."""
     if x.dtype != w.dtype:
         raise KernelError(f"linear: x is {x.dtype}, w is {w.dtype}")
     if x.dtype == torch.float32:
@@ -103,6 +138,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype) -> to
     _chk(x, w, bias)
     if not x.is_cuda:
         raise KernelError("linear: CUDA only")
+    M, K = x.shape
+    N = w.shape[0]
+    if stream_supports(M, N, K):
+        splits = _stream_splits(N, K) if (allow_partials and out_dtype == torch.float32) else 1
+        return linear_stream(x, w, bias, out_dtype, splits=splits)
     launches["library"] += 1
     if out_dtype == torch.float32:
         out = torch.mm(x, w.t(), out_dtype=torch.float32)
@@ -126,6 +166,9 @@ def silu_mul(gu: torch.Tensor, interleave: int, out_dtype: torch.dtype) -> torch
 
 def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, out_dtype: torch.dtype) -> torch.Tensor:
     """``silu(x Wg^T) * (x Wu^T)`` with gate and up rows interleaved in one matrix."""
+    if (x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and interleave == 8 and x.is_cuda
+            and stream_supports(x.shape[0], w_gate_up.shape[0], x.shape[1])):
+        return linear_stream(x, w_gate_up, None, out_dtype, silu=True)
     gu = linear(x, w_gate_up, None, x.dtype)
     return silu_mul(gu, interleave, out_dtype)
 
@@ -137,8 +180,11 @@ def rope_kv_write(qkv, bias, positions, table, rotary_dim, nq, nkv, hd, slot_map
     to ``slot_mapping`` in ``k_cache``/``v_cache`` ``[pages, nkv, page_size, hd]``
     (not written when ``slot_mapping`` is None)."""
     _chk(qkv, bias, positions, table, slot_mapping, k_cache, v_cache)
-    T = qkv.shape[0]
-    if qkv.shape[1] != (nq + 2 * nkv) * hd:
+    parts, part_stride = 1, 0
+    if qkv.dim() == 3:                       # a stack of partial sums from a k-split product
+        parts, part_stride = qkv.shape[0], qkv.shape[1] * qkv.shape[2]
+    T = qkv.shape[-2]
+    if qkv.shape[-1] != (nq + 2 * nkv) * hd:
         raise KernelError(f"rope_kv_write: qkv width {qkv.shape[1]} is not (nq+2nkv)*hd")
     if k_cache.dtype != out_dtype or v_cache.dtype != out_dtype:
         raise KernelError("rope_kv_write: the cache and the queries share one dtype")
@@ -151,7 +197,7 @@ def rope_kv_write(qkv, bias, positions, table, rotary_dim, nq, nkv, hd, slot_map
             raise KernelError("rope_kv_write: rotary table must be float32 [positions, 2, rotary_dim/2]")
         max_pos = table.shape[0]
     q = torch.empty((T, nq * hd), dtype=out_dtype, device=qkv.device)
-    call("sllm_rope_kv_write", _p(qkv), _dt(qkv), _p(bias), _p(positions), _p(table), int(rotary_dim), max_pos,
+    call("sllm_rope_kv_write", _p(qkv), _dt(qkv), parts, part_stride, _p(bias), _p(positions), _p(table), int(rotary_dim), max_pos,
          nq, nkv, hd, _p(slot_mapping), page_size, num_pages, _p(k_cache), _p(v_cache), _p(q), _dtc(out_dtype),
          T, _stream())
     return q
@@ -256,6 +302,8 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
 
 
 def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    if x.dim() == 3:                         # a stack of partial sums: gather each slice
+        return torch.stack([gather_rows(x[i], rows) for i in range(x.shape[0])])
     _chk(x, rows)
     R, (n, H) = rows.numel(), x.shape
     out = torch.empty((R, H), dtype=x.dtype, device=x.device)

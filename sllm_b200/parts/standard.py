@@ -25,8 +25,11 @@ class Linear:
         self.weight = weight
         self.bias = bias
 
-    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-        return ops.linear(x, self.weight, self.bias, out_dtype)
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype, allow_partials: bool = False) -> torch.Tensor:
+        """``allow_partials``: the caller's consumer adds a stack ``[parts, T, N]`` of float32
+        partial sums (the fused add + norm and the rotary kernel do), so a product of few
+        rows may split its k dimension over more SMs."""
+        return ops.linear(x, self.weight, self.bias, out_dtype, allow_partials)
 
     def nbytes(self) -> int:
         n = self.weight.numel() * self.weight.element_size()
@@ -140,7 +143,7 @@ class Attention(Mixer):
 
     def forward(self, x, step: StepContext, cache: LayerCache, position, write_cache=True):
         g = step.groups[cache.group]
-        qkv = self.qkv(x, torch.float32)                      # [T, (nq+2nkv)*hd] float32
+        qkv = self.qkv(x, torch.float32, True)                # [T, (nq+2nkv)*hd] float32, maybe in parts
         q = ops.rope_kv_write(
             qkv, self.qkv_b, step.positions,
             position.table if position is not None else None,
@@ -149,7 +152,7 @@ class Attention(Mixer):
             g.slot_mapping if write_cache else None, cache.k, cache.v, self.dtype)
         o = ops.paged_attention(q, cache.k, cache.v, step, cache.group,
                                 self.nq, self.nkv, self.hd, self.scale, self.window)
-        return self.out(o, torch.float32)
+        return self.out(o, torch.float32, True)
 
     def weight_bytes(self):
         return self.qkv.nbytes() + self.out.nbytes() + (self.qkv_b.numel() * 4 if self.qkv_b is not None else 0)
@@ -189,7 +192,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, step):
         act = ops.linear_silu_mul(x, self.gate_up.weight, self.interleave, self.dtype)   # [T, I]
-        return self.down(act, torch.float32)
+        return self.down(act, torch.float32, True)
 
     def weight_bytes(self):
         return self.gate_up.nbytes() + self.down.nbytes()

@@ -296,3 +296,47 @@ def test_attention_mma_far_key_and_page_edges():
             got = ops.attention_mma(q, kc, vc, bt, q_start, ctx_len, small, True, splits, nq, nkv, hd, 1.0, None)
             want = vc[page, :, off, :].float().repeat_interleave(nq // nkv, dim=0)
             torch.testing.assert_close(got.float().reshape(nq, hd), want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("N,K", [(144, 128), (1000, 384), (4608, 3584), (264, 1152)])
+def test_linear_stream(M, N, K):
+    """The weight-streaming kernel against the float32 statement: every token count up to
+    64, widths that are no multiple of the tile, direct and k-split results, both dtypes."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(13)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g)
+    want = x.float() @ w.float().t() + b
+    assert ops.stream_supports(M, N, K)
+    got = ops.linear_stream(x, w, b, torch.float32)
+    torch.testing.assert_close(got, want, rtol=2e-3, atol=2e-3)
+    got = ops.linear_stream(x, w, b, torch.bfloat16)
+    torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=1.6e-2)
+    for splits in (2, 3, 16):
+        parts = ops.linear_stream(x, w, b, torch.float32, splits=splits)
+        if K // 128 == 1:
+            assert parts.dim() == 2
+        else:
+            assert parts.dim() == 3 and parts.shape[0] <= splits
+            parts = parts.sum(0)
+        torch.testing.assert_close(parts, want, rtol=2e-3, atol=2e-3)
+    # through ops.linear: the same kernel, splits chosen by the width
+    got = ops.linear(x, w, b, torch.float32, True)
+    torch.testing.assert_close(got.sum(0) if got.dim() == 3 else got, want, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("M", [1, 8, 19, 64])
+@pytest.mark.parametrize("I,K", [(72, 128), (4864, 896), (1000, 256)])
+def test_linear_stream_silu(M, I, K):
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(14)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    wg = (torch.randn(I, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    wu = (torch.randn(I, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    gu = torch.stack([wg.reshape(I // 8, 8, K), wu.reshape(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
+    gate, up = x.float() @ wg.float().t(), x.float() @ wu.float().t()
+    want = gate * torch.sigmoid(gate) * up
+    got = ops.linear_silu_mul(x, gu, 8, torch.bfloat16)
+    torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=1.6e-2)

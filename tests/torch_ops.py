@@ -27,7 +27,7 @@ def add_rmsnorm(residual, delta, weight, eps, out_dtype):
     return (residual * (var + eps) ** -0.5 * weight).to(out_dtype)
 
 
-def linear(x, w, bias, out_dtype):
+def linear(x, w, bias, out_dtype, allow_partials=False):
     out = x.float() @ w.float().t()
     if bias is not None:
         out = out + bias
@@ -47,8 +47,10 @@ def linear_silu_mul(x, w_gate_up, interleave, out_dtype):
 
 
 def rope_kv_write(qkv, bias, positions, table, rotary_dim, nq, nkv, hd, slot_mapping, k_cache, v_cache, out_dtype):
-    T = qkv.shape[0]
     x = qkv.float()
+    if x.dim() == 3:
+        x = x.sum(0)
+    T = x.shape[0]
     if bias is not None:
         x = x + bias
     x = x.reshape(T, nq + 2 * nkv, hd)
@@ -97,6 +99,8 @@ def paged_attention(q, k_cache, v_cache, step, group, nq, nkv, hd, scale, window
 
 
 def gather_rows(x, rows):
+    if x.dim() == 3:
+        return x[:, rows.long()].clone()
     return x[rows.long()].clone()
 
 
