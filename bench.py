@@ -146,7 +146,7 @@ def flops_of_step(cfg, tokens_per_req, ctx_before, logits_rows):
     return fl
 
 
-def decode_run(model, cfg, batch, context, steps, warmup, seed=0):
+def decode_run(model, cfg, batch, context, steps, warmup, seed=0, graphs=True):
     """Prefill `batch` requests through the entry point, then time `steps` decode steps."""
     import numpy as np
     import torch
@@ -160,7 +160,7 @@ def decode_run(model, cfg, batch, context, steps, warmup, seed=0):
     # every request gets a portion in every step, so that all prompts end in the same step
     chunk = 512
     llm = LLM(model=model, block_size=page, num_pages=pages, max_num_seqs=batch, max_batch_tokens=batch * chunk,
-              chunk_size=chunk, max_model_len=context + 1, policy="reserve")
+              chunk_size=chunk, max_model_len=context + 1, policy="reserve", cuda_graphs=graphs)
     rng = np.random.default_rng(seed)
     for i in range(batch):
         llm.add_request(rng.integers(0, cfg["vocab_size"], prompt_len).tolist(),
@@ -238,6 +238,7 @@ def main(argv=None) -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer than 28 only where memory or time needs it")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64 and the prefill")
+    ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
@@ -264,7 +265,7 @@ def main(argv=None) -> int:
     model, _ = build_random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0", std=0.02)
     torch.cuda.synchronize()
 
-    main_run = decode_run(model, cfg, args.batch, args.context, args.steps, args.warmup)
+    main_run = decode_run(model, cfg, args.batch, args.context, args.steps, args.warmup, graphs=not args.no_graphs)
     points = {}
     prefill = None
     if not args.no_points:
@@ -290,7 +291,7 @@ def main(argv=None) -> int:
             "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
             "global_batch": args.batch, "seq_len": args.context, "prompt_len": main_run["prompt_len"],
-            "page_size": 16, "kv_dtype": "bf16", "parallelism": "1 GPU",
+            "page_size": 16, "kv_dtype": "bf16", "parallelism": "1 GPU", "cuda_graphs": not args.no_graphs,
             "l2": "inputs larger than L2 (15 GB of weights read per step)", "peaks": peaks_kind,
         },
         "e2e": {"value": round(main_run["e2e_tok_s"], 1), "unit": "tokens/s",

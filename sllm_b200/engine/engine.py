@@ -37,16 +37,18 @@ def _pad4(n: int) -> int:
 
 
 class Engine:
-    def __init__(self, model, *, page_size: int = 16, num_pages: int, max_requests: int = 8):
+    def __init__(self, model, *, page_size: int = 16, num_pages: int, max_requests: int = 8,
+                 max_model_len: int | None = None):
         self.model = model
         self.device = model.device
         self.cache = CacheManager(model.cache_needs(), page_size=page_size, num_pages=num_pages,
                                   max_requests=max_requests)
         self.layer_caches = self.cache.allocate_storage(model.dtype, self.device)
         self.vocab_size = model.plan.vocab_size
-        self.max_positions = model.plan.max_positions
+        self.max_positions = min(max_model_len or model.plan.max_positions, model.plan.max_positions)
         self._pin = self.device.type == "cuda"
         self.steps_run = 0
+        self._graphs = None
 
     # ---- requests ------------------------------------------------------------------
     def is_live(self, req_id) -> bool:
@@ -187,3 +189,15 @@ class Engine:
             self.cache.commit(e.req_id, tot)
         self.steps_run += 1
         return logits
+
+    # ---- decoding through a captured graph -------------------------------------------------
+    def decode_graph_step(self, entries, temperatures, uniforms, device_timer=None):
+        """One decode step (every entry brings one token and wants its logits) replayed from a
+        CUDA graph of the model's forward and the sampling kernel.  The first step of a given
+        batch size and context bucket runs eagerly on the graph's static buffers and is then
+        captured; later ones copy the batch description into those buffers and replay.
+        Returns the sampled ids (int32 tensor on the device, static)."""
+        from .graphs import DecodeGraphs
+        if self._graphs is None:
+            self._graphs = DecodeGraphs(self)
+        return self._graphs.step(list(entries), temperatures, uniforms, device_timer)

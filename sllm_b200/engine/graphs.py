@@ -1,0 +1,169 @@
+"""CUDA graphs of the decode step.
+
+A decode step launches some ten kernels per layer; launched one by one from Python
+they cost more host time than the device needs to run them.  The step's shape is
+fixed by the number of requests alone (one token each), so its forward and the
+sampling kernel are captured once per (batch size, context bucket) and replayed:
+the host fills one pinned buffer with the batch description (token ids, positions,
+slots, block tables, temperatures, uniforms), copies it to the graph's static device
+buffer and launches the graph.  Kernels read lengths and tables from device memory,
+so nothing about a request's context is baked into the graph except the bucket that
+decides how many ways the attention kernel splits the context.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..parts.base import GroupView, StepContext
+
+
+def _pad4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class _Graph:
+    def __init__(self, engine, B: int, bucket: int):
+        cache = engine.cache
+        self.B = B
+        ps = cache.page_size
+        self.cap_pages = -(-engine.max_positions // ps)
+        G = len(cache.groups)
+        sizes = {"token_ids": B, "positions": B, "seq_of_token": B, "q_start": B + 1, "ctx_len": B,
+                 "state_slots": B, "logit_rows": B, "temps": B, "uniforms": 2 * B}
+        for gi in range(G):
+            sizes[f"slot_mapping{gi}"] = B
+            sizes[f"block_tables{gi}"] = B * self.cap_pages
+        self.offs, total = {}, 0
+        for k, n in sizes.items():
+            self.offs[k] = (total, n)
+            total += _pad4(n)
+        self.host = torch.zeros(total, dtype=torch.int32, pin_memory=engine.device.type == "cuda")
+        self.h = self.host.numpy()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=engine.device)
+        # what never changes in a decode step
+        self._hsec("seq_of_token")[:] = np.arange(B)
+        self._hsec("q_start")[:] = np.arange(B + 1)
+        self._hsec("logit_rows")[:] = np.arange(B)
+        for gi in range(G):
+            self._hsec(f"block_tables{gi}")[:] = -1
+        groups = [GroupView(ps, self._dsec(f"block_tables{gi}").view(B, self.cap_pages), self._dsec(f"slot_mapping{gi}"))
+                  for gi in range(G)]
+        self.ctx = StepContext(
+            num_tokens=B, num_seqs=B, token_ids=self._dsec("token_ids"), positions=self._dsec("positions"),
+            seq_of_token=self._dsec("seq_of_token"), q_start=self._dsec("q_start"), ctx_len=self._dsec("ctx_len"),
+            state_slots=self._dsec("state_slots"), logit_rows=self._dsec("logit_rows"), groups=groups,
+            q_lens=[1] * B, ctx_lens=[bucket] * B, max_q_len=1, max_ctx_len=bucket, is_graph_replay=True)
+        self.temps = self._dsec("temps").view(torch.float32)
+        self.uniforms = self._dsec("uniforms").view(torch.float64)
+        self.graph = None
+        self.ids = None
+        self.launches = 0
+
+    def _hsec(self, k):
+        o, n = self.offs[k]
+        return self.h[o:o + n]
+
+    def _dsec(self, k):
+        o, n = self.offs[k]
+        return self.dev[o:o + n]
+
+    def fill(self, engine, entries, totals, temperatures, uniforms):
+        cache = engine.cache
+        ps = cache.page_size
+        B = self.B
+        tok, pos, ctx, slots = (self._hsec(k) for k in ("token_ids", "positions", "ctx_len", "state_slots"))
+        for i, (e, tot) in enumerate(zip(entries, totals)):
+            req = cache.requests[e.req_id]
+            tok[i] = e.tokens[0]
+            pos[i] = tot - 1
+            ctx[i] = tot
+            slots[i] = req.slot
+            for gi in range(len(cache.groups)):
+                table = req.tables[gi]
+                bt = self._hsec(f"block_tables{gi}")
+                row = bt[i * self.cap_pages:(i + 1) * self.cap_pages]
+                n = len(table)
+                row[:n] = table
+                row[n:] = -1
+                page = table[(tot - 1) // ps]
+                if page < 0:
+                    raise RuntimeError(f"request {e.req_id!r}: a token would be written to a page given back")
+                self._hsec(f"slot_mapping{gi}")[i] = page * ps + (tot - 1) % ps
+        self._hsec("temps").view(np.float32)[:] = temperatures
+        self._hsec("uniforms").view(np.float64)[:] = uniforms
+        self.dev.copy_(self.host, non_blocking=True)
+
+
+class DecodeGraphs:
+    def __init__(self, engine):
+        self.engine = engine
+        self.graphs: dict[tuple, _Graph] = {}
+
+    @staticmethod
+    def bucket(max_ctx: int) -> int:
+        b = 256
+        while b < max_ctx:
+            b *= 2
+        return b
+
+    def step(self, entries, temperatures, uniforms, device_timer=None):
+        eng = self.engine
+        cache = eng.cache
+        totals = []
+        for e in entries:
+            if len(e.tokens) != 1:
+                raise ValueError("a graph decode step takes one token per request")
+            req = cache.requests.get(e.req_id)
+            if req is None:
+                raise ValueError(f"request {e.req_id!r} is not live; its prompt runs through step()")
+            tot = req.num_tokens + 1
+            if tot > eng.max_positions:
+                from .engine import ContextOverflow
+                raise ContextOverflow(f"request {e.req_id!r}: {tot} tokens exceed max positions {eng.max_positions}")
+            if not 0 <= int(e.tokens[0]) < eng.vocab_size:
+                raise ValueError(f"request {e.req_id!r}: token id {e.tokens[0]} is outside the vocabulary")
+            totals.append(tot)
+        # pages: all or nothing
+        for gi, g in enumerate(cache.groups):
+            need = sum(max(0, cache.pages_for(t) - len(cache.requests[e.req_id].tables[gi]))
+                       for e, t in zip(entries, totals))
+            if need > g.pool.free_count:
+                from ..cache.pools import OutOfPages
+                raise OutOfPages(f"step needs {need} pages in group {gi}, {g.pool.free_count} free")
+        for e, t in zip(entries, totals):
+            cache.reserve(e.req_id, t)
+        key = (len(entries), self.bucket(max(totals)))
+        gr = self.graphs.get(key)
+        if gr is None:
+            gr = self.graphs[key] = _Graph(eng, *key)
+        gr.fill(eng, entries, totals, temperatures, uniforms)
+        if device_timer is not None:
+            device_timer.start()
+        if gr.graph is None:
+            # first use: run eagerly on the static buffers (this step's result), then capture
+            before = ops.launches["own"]
+            logits = eng.model.forward(gr.ctx, eng.layer_caches)
+            gr.ids = ops.sample_rows(logits, gr.temps, gr.uniforms)
+            gr.launches = ops.launches["own"] - before
+            ids_now = gr.ids.clone()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = eng.model.forward(gr.ctx, eng.layer_caches)
+                gr.ids = ops.sample_rows(logits, gr.temps, gr.uniforms)
+            ops.launches["own"] -= gr.launches          # capturing launched nothing
+            gr.graph = graph
+            out = ids_now
+        else:
+            gr.graph.replay()
+            ops.launches["own"] += gr.launches
+            out = gr.ids
+        if device_timer is not None:
+            device_timer.stop()
+        for e, t in zip(entries, totals):
+            cache.commit(e.req_id, t)
+        eng.steps_run += 1
+        return out

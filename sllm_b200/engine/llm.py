@@ -55,7 +55,7 @@ class LLM:
                  block_size: int = 16, num_pages: int | None = None, kv_utilization: float = 0.9,
                  kv_bytes: int | None = None, max_num_seqs: int = 8, max_batch_tokens: int = 2048,
                  chunk_size: int = 512, max_model_len: int | None = None, policy: str = "reserve",
-                 progress=None):
+                 cuda_graphs: bool = True, progress=None):
         if (model_dir is None) == (model is None):
             raise ValueError("give a model folder or a built model")
         if model is None:
@@ -65,10 +65,12 @@ class LLM:
         if num_pages is None:
             num_pages = plan_num_pages(model, block_size, kv_utilization=kv_utilization, kv_bytes=kv_bytes,
                                        cap_tokens=max_num_seqs * self.max_model_len + block_size * max_num_seqs)
-        self.engine = Engine(model, page_size=block_size, num_pages=num_pages, max_requests=max_num_seqs)
+        self.engine = Engine(model, page_size=block_size, num_pages=num_pages, max_requests=max_num_seqs,
+                             max_model_len=self.max_model_len)
         self.scheduler = Scheduler(self.engine.cache, max_positions=self.max_model_len, max_num_seqs=max_num_seqs,
                                    max_batch_tokens=max_batch_tokens, chunk_size=chunk_size, policy=policy)
         self.sampler = Sampler(model.device)
+        self.cuda_graphs = bool(cuda_graphs) and model.device.type == "cuda"
         self._next_id = 0
         self.steps = 0
 
@@ -96,9 +98,17 @@ class LLM:
             return [], {}
         entries = [StepEntry(p.req.req_id, p.req.tokens[p.start:p.start + p.count],
                              [p.count - 1] if p.sample else []) for p in plan]
-        ctx = self.engine.prepare(entries)
         rows = [(p.req.params, p.req.rng, p.req.tokens if not p.req.params.on_device else None)
                 for p in plan if p.sample]
+        if self.cuda_graphs and all(p.count == 1 and p.sample and p.req.params.on_device for p in plan):
+            # a pure decode step: replayed from a captured graph, sampling included
+            temps, unis = self.sampler.host_inputs(rows)
+            ids = self.engine.decode_graph_step(entries, temps, unis, device_timer).cpu().tolist()
+            sampled = {p.req.req_id: int(t) for p, t in zip(plan, ids)}
+            finished = sched.update(plan, sampled)
+            self.steps += 1
+            return finished, sampled
+        ctx = self.engine.prepare(entries)
         if device_timer is not None:
             device_timer.start()
         logits = self.engine.run(ctx, entries)

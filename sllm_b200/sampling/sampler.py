@@ -71,6 +71,19 @@ class Sampler:
         self.device = torch.device(device)
         self._pin = self.device.type == "cuda"
 
+    @staticmethod
+    def host_inputs(rows):
+        """(temperatures float32[R], uniforms float64[R]) for rows that all sample on the
+        device; a sampled (non-greedy) row draws its one uniform here."""
+        temps = np.zeros(len(rows), dtype=np.float32)
+        unis = np.zeros(len(rows), dtype=np.float64)
+        for i, (p, rng, _) in enumerate(rows):
+            t = float(p.temperature or 0.0)
+            if t > 0:
+                temps[i] = t
+                unis[i] = rng.random()
+        return temps, unis
+
     def sample(self, logits: torch.Tensor, rows, device_timer=None) -> list[int]:
         """rows: list of (SamplingParams, numpy Generator, seen ids or None)."""
         R = logits.shape[0]
