@@ -71,6 +71,8 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 
 constexpr int ATT_BN = 64;     // keys per tile
+constexpr int ATT_BT_CACHE = 2048;   // block-table entries a CTA keeps in shared memory
+template <bool DECODE> struct AttStages { static constexpr int value = DECODE ? 3 : 2; };
 
 template <int HD, bool DECODE>
 __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) {
@@ -80,10 +82,12 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
   constexpr int BM = DECODE ? 16 : 64;
   constexpr int NT = DECODE ? 2 : 8;             // 8-key n-tiles a warp computes per key tile
   constexpr int CHUNKS = HD / 8;                 // 16-byte chunks per row
+  constexpr int STAGES = AttStages<DECODE>::value;   // key/value tiles in flight: the decode form is latency-bound
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* k_s = q_s + BM * STRIDE;
-  __nv_bfloat16* v_s = k_s + 2 * ATT_BN * STRIDE;
+  __nv_bfloat16* v_s = k_s + STAGES * ATT_BN * STRIDE;
+  int* bt_s = reinterpret_cast<int*>(v_s + STAGES * ATT_BN * STRIDE);      // [ATT_BT_CACHE]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
@@ -107,6 +111,16 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
   const int tile0 = key_lo / ATT_BN * ATT_BN;    // tiles start at multiples of 64 keys, whatever the cut
   const int n_tiles = key_hi > tile0 ? (key_hi - tile0 + ATT_BN - 1) / ATT_BN : 0;
 
+  // the pages of this CTA's key range, fetched once: a tile's loads then depend on shared
+  // memory only, not on a global load of the table
+  const int page_first = tile0 / p.page_size;
+  const int page_count = n_tiles > 0 ? (key_hi - 1) / p.page_size - page_first + 1 : 0;
+  const bool bt_cached = page_count <= ATT_BT_CACHE;
+  if (bt_cached) {
+    for (int i = tid; i < page_count; i += 128) bt_s[i] = bt[page_first + i];
+    __syncthreads();
+  }
+
   // ---- loads -----------------------------------------------------------------------
   auto load_q = [&]() {
     for (int c = tid; c < BM * CHUNKS; c += 128) {
@@ -118,27 +132,41 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
       cp_async_16(q_s + r * STRIDE + ch * 8, src, ok);
     }
   };
+  // each thread keeps one 16-byte column of the rows r_first, r_first + R_STEP, ...: the address
+  // arithmetic of a tile is a handful of instructions per row
+  constexpr int R_STEP = 128 / CHUNKS;
+  const int ch8 = (tid % CHUNKS) * 8, r_first = tid / CHUNKS;
+  const int ps = p.page_size;
+  const int ps_shift = (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1;
+  const size_t head_off = (size_t)kvh * ps * HD + ch8;
+  const size_t page_stride = (size_t)p.nkv * ps * HD;
   auto load_kv = [&](int tile, int buf) {
     const int kbase = tile0 + tile * ATT_BN;
-    for (int c = tid; c < ATT_BN * CHUNKS; c += 128) {
-      const int r = c / CHUNKS, ch = c % CHUNKS;
+#pragma unroll
+    for (int r = r_first; r < ATT_BN; r += R_STEP) {
       const int key = kbase + r;
       bool ok = key < key_hi && key >= key_lo;
-      int page = 0;
+      int page = 0, off = 0;
       if (ok) {
-        page = bt[key / p.page_size];
+        const int pi = ps_shift >= 0 ? key >> ps_shift : key / ps;
+        off = key - pi * ps;
+        page = bt_cached ? bt_s[pi - page_first] : bt[pi];
         ok = page >= 0;                           // a page given back is never read
+        if (!ok) page = 0;
       }
-      const size_t off = (((size_t)(ok ? page : 0) * p.nkv + kvh) * p.page_size + (ok ? key % p.page_size : 0)) * HD + ch * 8;
-      cp_async_16(k_s + (buf * ATT_BN + r) * STRIDE + ch * 8, p.k_cache + off, ok);
-      cp_async_16(v_s + (buf * ATT_BN + r) * STRIDE + ch * 8, p.v_cache + off, ok);
+      const size_t src = (size_t)page * page_stride + head_off + (size_t)off * HD;
+      cp_async_16(k_s + (buf * ATT_BN + r) * STRIDE + ch8, p.k_cache + src, ok);
+      cp_async_16(v_s + (buf * ATT_BN + r) * STRIDE + ch8, p.v_cache + src, ok);
     }
   };
 
   load_q();
   cp_async_commit();
-  if (n_tiles > 0) load_kv(0, 0);
-  cp_async_commit();
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (st < n_tiles) load_kv(st, st);
+    cp_async_commit();
+  }
 
   // ---- per-thread rows: g and g+8 of the warp's 16-row block ---------------------------
   const int wrow = DECODE ? 0 : warp * 16;
@@ -162,7 +190,7 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
 #pragma unroll
     for (int c = 0; c < 4; ++c) o[d][c] = 0.f;
 
-  cp_async_wait<1>();                             // the queries have landed
+  cp_async_wait<STAGES - 1>();                    // the queries have landed
   __syncthreads();
   unsigned qf[KSTEPS][4];
 #pragma unroll
@@ -171,10 +199,10 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
 
   const int koff = DECODE ? warp * 16 : 0;        // the warp's keys within a tile
   for (int tile = 0; tile < n_tiles; ++tile) {
-    const int buf = tile & 1;
-    if (tile + 1 < n_tiles) load_kv(tile + 1, buf ^ 1);
+    const int buf = tile % STAGES;
+    if (tile + STAGES - 1 < n_tiles) load_kv(tile + STAGES - 1, (tile + STAGES - 1) % STAGES);
     cp_async_commit();
-    cp_async_wait<1>();                           // tile `tile` has landed
+    cp_async_wait<STAGES - 1>();                  // tile `tile` has landed
     __syncthreads();
     const __nv_bfloat16* kb = k_s + buf * ATT_BN * STRIDE;
     const __nv_bfloat16* vb = v_s + buf * ATT_BN * STRIDE;
@@ -245,7 +273,7 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
         mma_bf16(o[d + 1], pf[kk], b[2], b[3]);
       }
     }
-    __syncthreads();                              // the buffer may be refilled two tiles on
+    __syncthreads();                              // the next iteration refills the buffer just read
   }
   cp_async_wait<0>();
 
@@ -282,7 +310,7 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
     float* mo = reinterpret_cast<float*>(k_s);                 // [4][16][HD]
     float* mm = mo + 4 * 16 * HD;                              // [4][16] maxima, then [4][16] sums
     float* ml = mm + 64;
-    static_assert(sizeof(float) * (4 * 16 * HD + 128) <= sizeof(__nv_bfloat16) * 4 * ATT_BN * STRIDE, "merge buffer");
+    static_assert(sizeof(float) * (4 * 16 * HD + 128) <= sizeof(__nv_bfloat16) * 2 * STAGES * ATT_BN * STRIDE, "merge buffer");
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int r = g + 8 * i;
@@ -354,7 +382,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
 template <int HD, bool DECODE>
 static int launch_attention(const AttnParams& p, int tiles, cudaStream_t stream) {
   constexpr int BM = DECODE ? 16 : 64;
-  constexpr size_t smem = sizeof(__nv_bfloat16) * (size_t)(BM + 4 * ATT_BN) * (HD + 8);
+  constexpr size_t smem = sizeof(__nv_bfloat16) * (size_t)(BM + 2 * AttStages<DECODE>::value * ATT_BN) * (HD + 8) +
+                          sizeof(int) * ATT_BT_CACHE;
   static bool configured = false;                 // per template instance
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -34,25 +34,63 @@ __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __r
 // 1/sqrtf, not rsqrtf (kernels.cu:818-820).  The sum over a row is taken in an order
 // that depends on H and the block size only, never on the batch.
 // ---------------------------------------------------------------------------
-template <typename TD, typename TO>
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<unsigned*>(&a);
+  raw.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// VEC: H and the part stride are multiples of 4 and every pointer is 16-byte aligned; four
+// elements a thread, the partial sums read with independent loads.
+template <typename TD, typename TO, bool VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int parts,
                                    size_t part_stride, const float* __restrict__ w, float eps,
                                    TO* __restrict__ out, int H) {
   __shared__ float red[33];
   const size_t base = (size_t)blockIdx.x * H;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float v = residual[base + i];
-    if (delta != nullptr) {
-      for (int p = 0; p < parts; ++p) v += to_f32(delta[p * part_stride + base + i]);
-      residual[base + i] = v;
+  if constexpr (VEC) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float4 v = load4(residual + base + i);
+      if (delta != nullptr) {
+#pragma unroll 8
+        for (int p = 0; p < parts; ++p) {
+          const float4 d = load4(delta + p * part_stride + base + i);
+          v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        }
+        store4(residual + base + i, v);
+      }
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
-    ss += v * v;
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float v = residual[base + i];
+      if (delta != nullptr) {
+        for (int p = 0; p < parts; ++p) v += to_f32(delta[p * part_stride + base + i]);
+        residual[base + i] = v;
+      }
+      ss += v * v;
+    }
   }
   const float total = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(total / (float)H + eps);
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    out[base + i] = from_f32<TO>(residual[base + i] * inv * w[i]);
+  if constexpr (VEC) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      const float4 v = load4(residual + base + i), g = load4(w + i);
+      store4(out + base + i, make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w));
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[base + i] = from_f32<TO>(residual[base + i] * inv * w[i]);
   }
 }
 
@@ -72,12 +110,21 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out,
   out[idx] = from_f32<TO>(g * (1.0f / (1.0f + expf(-g))) * u);
 }
 
+// out[r, :] = sum over parts of x[part][rows[r], :]
 template <typename T>
-__global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows, T* __restrict__ out,
-                                   int H, int n_src) {
+__global__ void gather_rows_kernel(const T* __restrict__ x, int parts, size_t part_stride,
+                                   const int* __restrict__ rows, T* __restrict__ out, int H, int n_src) {
   int r = rows[blockIdx.x];
   r = r < 0 ? 0 : (r >= n_src ? n_src - 1 : r);
-  for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)blockIdx.x * H + i] = x[(size_t)r * H + i];
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    if (parts == 1) {
+      out[(size_t)blockIdx.x * H + i] = x[(size_t)r * H + i];
+    } else {
+      float v = 0.f;
+      for (int p = 0; p < parts; ++p) v += to_f32(x[p * part_stride + (size_t)r * H + i]);
+      out[(size_t)blockIdx.x * H + i] = from_f32<T>(v);
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -168,10 +215,21 @@ SLLM_EXPORT int sllm_add_rmsnorm(float* residual, const void* delta, int delta_d
   SLLM_REQUIRE(rows >= 0 && H > 0, "add_rmsnorm: bad sizes rows=%d H=%d", rows, H);
   SLLM_REQUIRE(delta == nullptr || parts >= 1, "add_rmsnorm: parts=%d", parts);
   if (rows == 0) return SLLM_OK;
-  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-#define LAUNCH(TD, TO)                                                                                      \
-  add_rmsnorm_kernel<TD, TO><<<rows, threads, 0, stream>>>(residual, (const TD*)delta, parts, part_stride, w, \
-                                                           eps, (TO*)out, H)
+  const bool vec = H % 4 == 0 && part_stride % 4 == 0 && ((uintptr_t)residual % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
+                   ((uintptr_t)out % 16 == 0) && (delta == nullptr || (uintptr_t)delta % 16 == 0);
+  const int per = vec ? 4 : 1;
+  // one pass of the row per thread where it fits: the kernel is bound by load latency, not by work
+  int threads = ((H / per + 31) / 32) * 32;
+  threads = threads > 1024 ? 1024 : (threads < 64 ? 64 : threads);
+#define LAUNCH(TD, TO)                                                                                         \
+  do {                                                                                                         \
+    if (vec)                                                                                                   \
+      add_rmsnorm_kernel<TD, TO, true><<<rows, threads, 0, stream>>>(residual, (const TD*)delta, parts,        \
+                                                                     part_stride, w, eps, (TO*)out, H);        \
+    else                                                                                                       \
+      add_rmsnorm_kernel<TD, TO, false><<<rows, threads, 0, stream>>>(residual, (const TD*)delta, parts,       \
+                                                                      part_stride, w, eps, (TO*)out, H);       \
+  } while (0)
   if (delta_dtype == SLLM_F32 && out_dtype == SLLM_F32) LAUNCH(float, float);
   else if (delta_dtype == SLLM_F32 && out_dtype == SLLM_BF16) LAUNCH(float, __nv_bfloat16);
   else if (delta_dtype == SLLM_BF16 && out_dtype == SLLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -196,14 +254,14 @@ SLLM_EXPORT int sllm_silu_mul(const void* gu, int in_dtype, void* out, int out_d
   return launch_status("silu_mul");
 }
 
-SLLM_EXPORT int sllm_gather_rows(const void* x, int dtype, const int* rows, void* out, int R, int H, int n_src,
-                                 cudaStream_t stream) {
-  SLLM_REQUIRE(R >= 0 && H > 0 && n_src > 0, "gather_rows: bad sizes R=%d H=%d n=%d", R, H, n_src);
+SLLM_EXPORT int sllm_gather_rows(const void* x, int dtype, int parts, size_t part_stride, const int* rows, void* out,
+                                 int R, int H, int n_src, cudaStream_t stream) {
+  SLLM_REQUIRE(R >= 0 && H > 0 && n_src > 0 && parts >= 1, "gather_rows: bad sizes R=%d H=%d n=%d parts=%d", R, H, n_src, parts);
   if (R == 0) return SLLM_OK;
   if (dtype == SLLM_F32)
-    gather_rows_kernel<float><<<R, 256, 0, stream>>>((const float*)x, rows, (float*)out, H, n_src);
+    gather_rows_kernel<float><<<R, 256, 0, stream>>>((const float*)x, parts, part_stride, rows, (float*)out, H, n_src);
   else if (dtype == SLLM_BF16)
-    gather_rows_kernel<__nv_bfloat16><<<R, 256, 0, stream>>>((const __nv_bfloat16*)x, rows, (__nv_bfloat16*)out, H, n_src);
+    gather_rows_kernel<__nv_bfloat16><<<R, 256, 0, stream>>>((const __nv_bfloat16*)x, parts, part_stride, rows, (__nv_bfloat16*)out, H, n_src);
   else
     SLLM_REQUIRE(false, "gather_rows: unknown dtype %d", dtype);
   return launch_status("gather_rows");

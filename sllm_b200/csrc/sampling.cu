@@ -27,9 +27,23 @@ __device__ __forceinline__ MaxIdx better(MaxIdx a, MaxIdx b) {
 
 __device__ MaxIdx block_argmax(const float* __restrict__ row, int V, MaxIdx* sh) {
   MaxIdx best{-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best.v) best = MaxIdx{v, i};             // strict >: the first maximum wins
+  if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    // four values a load, four loads in flight; a thread's indices still ascend
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    const int n4 = V >> 2;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 v = row4[i];
+      if (v.x > best.v) best = MaxIdx{v.x, 4 * i};
+      if (v.y > best.v) best = MaxIdx{v.y, 4 * i + 1};
+      if (v.z > best.v) best = MaxIdx{v.z, 4 * i + 2};
+      if (v.w > best.v) best = MaxIdx{v.w, 4 * i + 3};
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = row[i];
+      if (v > best.v) best = MaxIdx{v, i};           // strict >: the first maximum wins
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {

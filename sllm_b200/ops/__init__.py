@@ -247,7 +247,7 @@ def choose_splits(num_small: int, nkv: int, max_ctx: int) -> int:
     """How many ways the decode form cuts the context: enough CTAs to fill the GPU about
     twice, never less than 256 keys a split."""
     ctas = max(num_small * nkv, 1)
-    want = -(-2 * NUM_SMS // ctas)
+    want = max(1, round(2 * NUM_SMS / ctas))    # about two CTAs per SM
     return int(max(1, min(want, max_ctx // 256, 32)))
 
 
@@ -302,12 +302,14 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
 
 
 def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
-    if x.dim() == 3:                         # a stack of partial sums: gather each slice
-        return torch.stack([gather_rows(x[i], rows) for i in range(x.shape[0])])
+    """``x[rows]``; a 3-d ``x`` is a stack of partial sums, added while gathering."""
     _chk(x, rows)
-    R, (n, H) = rows.numel(), x.shape
+    parts, stride = 1, 0
+    if x.dim() == 3:
+        parts, stride = x.shape[0], x.shape[1] * x.shape[2]
+    R, (n, H) = rows.numel(), x.shape[-2:]
     out = torch.empty((R, H), dtype=x.dtype, device=x.device)
-    call("sllm_gather_rows", _p(x), _dt(x), _p(rows), _p(out), R, H, n, _stream())
+    call("sllm_gather_rows", _p(x), _dt(x), parts, stride, _p(rows), _p(out), R, H, n, _stream())
     return out
 
 

@@ -41,7 +41,7 @@ def _declare(L):
         "sllm_add_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_size_t, c_void_p, c_float, c_void_p, c_int,
                              c_int, c_int, c_void_p],
         "sllm_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-        "sllm_gather_rows": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "sllm_gather_rows": [c_void_p, c_int, c_int, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "sllm_rope_kv_write": [c_void_p, c_int, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "sllm_gemm_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],

@@ -100,7 +100,7 @@ def paged_attention(q, k_cache, v_cache, step, group, nq, nkv, hd, scale, window
 
 def gather_rows(x, rows):
     if x.dim() == 3:
-        return x[:, rows.long()].clone()
+        return x[:, rows.long()].sum(0)
     return x[rows.long()].clone()
 
 
