@@ -71,7 +71,9 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 
 constexpr int ATT_BN = 64;     // keys per tile
-constexpr int ATT_BT_CACHE = 2048;   // block-table entries a CTA keeps in shared memory
+// block-table entries a CTA keeps in shared memory (the decode form reads a split of the
+// context only, and must leave room for two CTAs per SM)
+template <bool DECODE> struct AttBtCache { static constexpr int value = DECODE ? 512 : 2048; };
 template <bool DECODE> struct AttStages { static constexpr int value = DECODE ? 3 : 2; };
 
 template <int HD, bool DECODE>
@@ -87,7 +89,8 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* k_s = q_s + BM * STRIDE;
   __nv_bfloat16* v_s = k_s + STAGES * ATT_BN * STRIDE;
-  int* bt_s = reinterpret_cast<int*>(v_s + STAGES * ATT_BN * STRIDE);      // [ATT_BT_CACHE]
+  constexpr int BT_CACHE = AttBtCache<DECODE>::value;
+  int* bt_s = reinterpret_cast<int*>(v_s + STAGES * ATT_BN * STRIDE);      // [BT_CACHE]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
@@ -115,7 +118,7 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
   // memory only, not on a global load of the table
   const int page_first = tile0 / p.page_size;
   const int page_count = n_tiles > 0 ? (key_hi - 1) / p.page_size - page_first + 1 : 0;
-  const bool bt_cached = page_count <= ATT_BT_CACHE;
+  const bool bt_cached = page_count <= BT_CACHE;
   if (bt_cached) {
     for (int i = tid; i < page_count; i += 128) bt_s[i] = bt[page_first + i];
     __syncthreads();
@@ -383,7 +386,7 @@ template <int HD, bool DECODE>
 static int launch_attention(const AttnParams& p, int tiles, cudaStream_t stream) {
   constexpr int BM = DECODE ? 16 : 64;
   constexpr size_t smem = sizeof(__nv_bfloat16) * (size_t)(BM + 2 * AttStages<DECODE>::value * ATT_BN) * (HD + 8) +
-                          sizeof(int) * ATT_BT_CACHE;
+                          sizeof(int) * AttBtCache<DECODE>::value;
   static bool configured = false;                 // per template instance
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

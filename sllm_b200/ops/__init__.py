@@ -91,8 +91,11 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, bias) -> torch.Tensor:
     return out
 
 
+STREAM_MAX_ROWS = 32      # beyond this the kernel's shared-memory reads of the activations bound it
+
+
 def stream_supports(M: int, N: int, K: int) -> bool:
-    return bool(lib().sllm_linear_stream_supports(int(M), int(N), int(K)))
+    return M <= STREAM_MAX_ROWS and bool(lib().sllm_linear_stream_supports(int(M), int(N), int(K)))
 
 
 def linear_stream(x, w, bias, out_dtype, *, splits: int = 1, silu: bool = False):
