@@ -242,3 +242,72 @@ SLLM_EXPORT int sllm_linear_stream(const void* x, const void* W, const float* bi
   }
 #undef GO
 }
+
+// ---------------------------------------------------------------------------------------------
+// An entry point that allocates nothing (declared in sllm_noalloc.h; see the comment there).
+// ---------------------------------------------------------------------------------------------
+#include <mutex>
+
+#include "sllm_noalloc.h"
+
+namespace sllm {
+
+// Scratch for the k-split partial sums, part of the library's image: every GPU that loads the
+// library holds these 8 MiB until the process exits.
+static __device__ __align__(256) float ls_noalloc_scratch[SLLM_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES];      // device address of the array, per device
+static std::mutex g_noalloc_mutex;
+
+// out[i] = sum over splits of partial[s][i]
+__global__ void sum_partials_kernel(const float* __restrict__ partial, int splits, size_t n, float* __restrict__ out) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v = 0.f;
+  for (int s = 0; s < splits; ++s) v += partial[(size_t)s * n + i];
+  out[i] = v;
+}
+
+}  // namespace sllm
+
+SLLM_EXPORT int sllm_linear_stream_noalloc(const void* x, const void* W, const float* bias, float* out, int M, int N,
+                                           int K, int splits, cudaStream_t stream) {
+  SLLM_REQUIRE(sllm_linear_stream_supports(M, N, K), "linear_stream_noalloc: sizes M=%d N=%d K=%d (needs M<=64, K%%128==0)", M, N, K);
+  SLLM_REQUIRE(splits >= 1, "linear_stream_noalloc: splits=%d", splits);
+  const int real = sllm_linear_stream_splits(K, splits);
+  if (real == 1)        // nothing to add up: the product goes straight to the caller's buffer
+    return sllm_linear_stream(x, W, bias, out, SLLM_F32, nullptr, M, N, K, 1, EPI_STORE, stream);
+  const size_t need = (size_t)real * M * N;
+  SLLM_REQUIRE(need <= (size_t)SLLM_NOALLOC_SCRATCH_FLOATS,
+               "linear_stream_noalloc: %d splits x %d x %d partial sums need %zu floats, the built-in scratch holds %d",
+               real, M, N, need, SLLM_NOALLOC_SCRATCH_FLOATS);
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+    set_error("linear_stream_noalloc: cannot tell the current device");
+    return SLLM_ERR_LAUNCH;
+  }
+  float* scratch;
+  {
+    // The array's name is a host-side handle, not a device address: its address on the
+    // current device is asked for once per device and kept.
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&p, ls_noalloc_scratch);
+      if (e != cudaSuccess || p == nullptr) {
+        char buf[200];
+        snprintf(buf, sizeof buf, "linear_stream_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        set_error(buf);
+        return SLLM_ERR_LAUNCH;
+      }
+      g_noalloc_ptr[dev] = static_cast<float*>(p);
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  int rc = sllm_linear_stream(x, W, bias, nullptr, SLLM_F32, scratch, M, N, K, real, EPI_STORE, stream);
+  if (rc != SLLM_OK) return rc;
+  const size_t n = (size_t)M * N;
+  sum_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(scratch, real, n, out);
+  return launch_status("linear_stream_noalloc");
+}
