@@ -94,6 +94,7 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
+  pdl_wait();       // everything below reads what the step's earlier kernels or its batch upload wrote
   const int seq = p.tile_seq[blockIdx.x], row0 = p.tile_row0[blockIdx.x];
   const int kvh = blockIdx.y, split = blockIdx.z;
   const int G = p.nq / p.nkv;
@@ -279,6 +280,7 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
     __syncthreads();                              // the next iteration refills the buffer just read
   }
   cp_async_wait<0>();
+  pdl_launch_dependents();             // all keys are read; the next kernel may begin during the epilogue
 
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -363,6 +365,7 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
 template <int HD>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                          __nv_bfloat16* __restrict__ out, int rows, int num_splits) {
+  pdl_wait();
   const int row = blockIdx.x;
   float mt = -INFINITY;
   for (int s = 0; s < num_splits; ++s) mt = fmaxf(mt, part_lse[(size_t)s * rows + row]);
@@ -397,12 +400,12 @@ static int launch_attention(const AttnParams& p, int tiles, cudaStream_t stream)
     configured = true;
   }
   dim3 grid(tiles, p.nkv, p.num_splits);
-  attention_mma_kernel<HD, DECODE><<<grid, 128, smem, stream>>>(p);
+  launch_kernel(attention_mma_kernel<HD, DECODE>, grid, 128, smem, stream, p);
   int rc = launch_status("attention_mma");
   if (rc != SLLM_OK) return rc;
   if (p.num_splits > 1) {
-    attention_combine_kernel<HD><<<p.total_tokens * p.nq, HD >= 128 ? 128 : 64, 0, stream>>>(
-        p.part_o, p.part_lse, p.out, p.total_tokens * p.nq, p.num_splits);
+    launch_kernel(attention_combine_kernel<HD>, p.total_tokens * p.nq, HD >= 128 ? 128 : 64, 0, stream,
+                  (const float*)p.part_o, (const float*)p.part_lse, p.out, p.total_tokens * p.nq, p.num_splits);
     rc = launch_status("attention_combine");
   }
   return rc;

@@ -31,6 +31,7 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
   __shared__ float qs[ATT_MAX_HD];
   __shared__ float acc_s[ATT_WARPS][ATT_MAX_HD];
   __shared__ float m_s[ATT_WARPS], l_s[ATT_WARPS];
+  pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const int kvh = h / (nq / nkv);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -106,11 +107,11 @@ SLLM_EXPORT int sllm_attention_simt(const void* q, const void* k_cache, const vo
   if (T == 0) return SLLM_OK;
   dim3 grid(T, nq);
   if (dtype == SLLM_F32)
-    attention_simt_kernel<float, float><<<grid, ATT_WARPS * 32, 0, stream>>>(
+    launch_kernel(attention_simt_kernel<float, float>, grid, ATT_WARPS * 32, 0, stream,
         (const float*)q, (const float*)k_cache, (const float*)v_cache, block_tables, max_pages, positions,
         seq_of_token, nq, nkv, hd, page_size, scale, window, (float*)out);
   else if (dtype == SLLM_BF16)
-    attention_simt_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, ATT_WARPS * 32, 0, stream>>>(
+    launch_kernel(attention_simt_kernel<__nv_bfloat16, __nv_bfloat16>, grid, ATT_WARPS * 32, 0, stream,
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_tables,
         max_pages, positions, seq_of_token, nq, nkv, hd, page_size, scale, window, (__nv_bfloat16*)out);
   else

@@ -2,6 +2,7 @@
 // RMSNorm, rotary encoding fused with the paged key/value write, SiLU-multiply,
 // row gather.  All arithmetic in float32; operands float32 or bfloat16.
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -14,12 +15,21 @@ void set_error(const char* msg) {
   g_error[sizeof g_error - 1] = 0;
 }
 
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("SLLM_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
 // ---------------------------------------------------------------------------
 // out[t, :] = float(table[ids[t], :])      (kernels/cuda/kernels.cu:770-787 does one row)
 // ---------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int H, int V) {
+  pdl_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   id = id < 0 ? 0 : (id >= V ? V - 1 : id);     // the host validates ids; never read outside the table
@@ -57,6 +67,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
                                    size_t part_stride, const float* __restrict__ w, float eps,
                                    TO* __restrict__ out, int H) {
   __shared__ float red[33];
+  pdl_wait();
   const size_t base = (size_t)blockIdx.x * H;
   float ss = 0.f;
   if constexpr (VEC) {
@@ -100,6 +111,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
 // ---------------------------------------------------------------------------
 template <typename TI, typename TO>
 __global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int I, int blk, size_t n) {
+  pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n) return;
   const size_t t = idx / I;
@@ -114,6 +126,7 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out,
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, int parts, size_t part_stride,
                                    const int* __restrict__ rows, T* __restrict__ out, int H, int n_src) {
+  pdl_wait();
   int r = rows[blockIdx.x];
   r = r < 0 ? 0 : (r >= n_src ? n_src - 1 : r);
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
@@ -146,6 +159,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int parts, size
                                      int rot, int max_pos, int nq, int nkv, int hd,
                                      const int* __restrict__ slot_mapping, int page_size, int num_pages,
                                      TC* __restrict__ k_cache, TC* __restrict__ v_cache, TC* __restrict__ q_out) {
+  pdl_wait();
   const int t = blockIdx.x;
   const int head = blockIdx.y;                       // 0..nq-1 q, then nkv k, then nkv v
   const int width = (nq + 2 * nkv) * hd;
@@ -201,9 +215,9 @@ SLLM_EXPORT int sllm_embed_gather(const void* table, int table_dtype, const int*
   if (T == 0) return SLLM_OK;
   const int threads = H >= 1024 ? 256 : 128;
   if (table_dtype == SLLM_F32)
-    embed_gather_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, H, V);
+    launch_kernel(embed_gather_kernel<float>, T, threads, 0, stream, (const float*)table, ids, out, H, V);
   else if (table_dtype == SLLM_BF16)
-    embed_gather_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, H, V);
+    launch_kernel(embed_gather_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, H, V);
   else
     SLLM_REQUIRE(false, "embed_gather: unknown dtype %d", table_dtype);
   return launch_status("embed_gather");
@@ -224,11 +238,11 @@ SLLM_EXPORT int sllm_add_rmsnorm(float* residual, const void* delta, int delta_d
 #define LAUNCH(TD, TO)                                                                                         \
   do {                                                                                                         \
     if (vec)                                                                                                   \
-      add_rmsnorm_kernel<TD, TO, true><<<rows, threads, 0, stream>>>(residual, (const TD*)delta, parts,        \
-                                                                     part_stride, w, eps, (TO*)out, H);        \
+      launch_kernel(add_rmsnorm_kernel<TD, TO, true>, rows, threads, 0, stream, residual, (const TD*)delta,   \
+                    parts, part_stride, w, eps, (TO*)out, H);                                                  \
     else                                                                                                       \
-      add_rmsnorm_kernel<TD, TO, false><<<rows, threads, 0, stream>>>(residual, (const TD*)delta, parts,       \
-                                                                      part_stride, w, eps, (TO*)out, H);       \
+      launch_kernel(add_rmsnorm_kernel<TD, TO, false>, rows, threads, 0, stream, residual, (const TD*)delta,  \
+                    parts, part_stride, w, eps, (TO*)out, H);                                                  \
   } while (0)
   if (delta_dtype == SLLM_F32 && out_dtype == SLLM_F32) LAUNCH(float, float);
   else if (delta_dtype == SLLM_F32 && out_dtype == SLLM_BF16) LAUNCH(float, __nv_bfloat16);
@@ -245,7 +259,7 @@ SLLM_EXPORT int sllm_silu_mul(const void* gu, int in_dtype, void* out, int out_d
   const size_t n = (size_t)T * I;
   if (n == 0) return SLLM_OK;
   const unsigned blocks = (unsigned)((n + 255) / 256);
-#define LAUNCH(TI, TO) silu_mul_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)gu, (TO*)out, I, blk, n)
+#define LAUNCH(TI, TO) launch_kernel(silu_mul_kernel<TI, TO>, blocks, 256, 0, stream, (const TI*)gu, (TO*)out, I, blk, n)
   if (in_dtype == SLLM_F32 && out_dtype == SLLM_F32) LAUNCH(float, float);
   else if (in_dtype == SLLM_F32 && out_dtype == SLLM_BF16) LAUNCH(float, __nv_bfloat16);
   else if (in_dtype == SLLM_BF16 && out_dtype == SLLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -259,9 +273,9 @@ SLLM_EXPORT int sllm_gather_rows(const void* x, int dtype, int parts, size_t par
   SLLM_REQUIRE(R >= 0 && H > 0 && n_src > 0 && parts >= 1, "gather_rows: bad sizes R=%d H=%d n=%d parts=%d", R, H, n_src, parts);
   if (R == 0) return SLLM_OK;
   if (dtype == SLLM_F32)
-    gather_rows_kernel<float><<<R, 256, 0, stream>>>((const float*)x, parts, part_stride, rows, (float*)out, H, n_src);
+    launch_kernel(gather_rows_kernel<float>, R, 256, 0, stream, (const float*)x, parts, part_stride, rows, (float*)out, H, n_src);
   else if (dtype == SLLM_BF16)
-    gather_rows_kernel<__nv_bfloat16><<<R, 256, 0, stream>>>((const __nv_bfloat16*)x, parts, part_stride, rows, (__nv_bfloat16*)out, H, n_src);
+    launch_kernel(gather_rows_kernel<__nv_bfloat16>, R, 256, 0, stream, (const __nv_bfloat16*)x, parts, part_stride, rows, (__nv_bfloat16*)out, H, n_src);
   else
     SLLM_REQUIRE(false, "gather_rows: unknown dtype %d", dtype);
   return launch_status("gather_rows");
@@ -282,9 +296,9 @@ SLLM_EXPORT int sllm_rope_kv_write(const void* qkv, int in_dtype, int parts, siz
   dim3 grid(T, nq + 2 * nkv);
   const int threads = hd / 2 >= 64 ? 64 : 32;
 #define LAUNCH(TI, TC)                                                                                         \
-  rope_kv_write_kernel<TI, TC><<<grid, threads, 0, stream>>>((const TI*)qkv, parts, part_stride, bias, positions, table, rot, \
-                                                             max_pos, nq, nkv, hd, slot_mapping, page_size,    \
-                                                             num_pages, (TC*)k_cache, (TC*)v_cache, (TC*)q_out)
+  launch_kernel(rope_kv_write_kernel<TI, TC>, grid, threads, 0, stream, (const TI*)qkv, parts, part_stride, bias,  \
+                positions, table, rot, max_pos, nq, nkv, hd, slot_mapping, page_size, num_pages,                   \
+                (TC*)k_cache, (TC*)v_cache, (TC*)q_out)
   if (in_dtype == SLLM_F32 && cache_dtype == SLLM_F32) LAUNCH(float, float);
   else if (in_dtype == SLLM_F32 && cache_dtype == SLLM_BF16) LAUNCH(float, __nv_bfloat16);
   else if (in_dtype == SLLM_BF16 && cache_dtype == SLLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);

@@ -18,6 +18,7 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, const 
                 float* __restrict__ C, int M, int N, int K) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
+  pdl_wait();
   const int tid = threadIdx.x;
   const int tx = tid % 16, ty = tid / 16;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -93,6 +94,6 @@ SLLM_EXPORT int sllm_gemm_f32(const float* A, const float* W, const float* bias,
   if (M == 0) return SLLM_OK;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   SLLM_REQUIRE(grid.y <= 65535, "gemm_f32: M=%d is too large for one launch", M);
-  gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, W, bias, C, M, N, K);
+  launch_kernel(gemm_f32_kernel, grid, 256, 0, stream, A, W, bias, C, M, N, K);
   return launch_status("gemm_f32");
 }

@@ -112,16 +112,17 @@ linear_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   };
 
   uint4 wa[8], wb[8];
-  if (n_chunks > 0) {
-    load_x(0, 0);
-    load_w(wa, 0);
-  }
+  // weights do not depend on the step's earlier kernels: start the stream (two chunks) now
+  if (n_chunks > 0) load_w(wa, 0);
+  if (n_chunks > 1) load_w(wb, 1);
+  pdl_wait();                          // the activations do
+  if (n_chunks > 0) load_x(0, 0);
   asm volatile("cp.async.commit_group;\n" ::);
   for (int c = 0; c < n_chunks; c += 2) {
     // chunk c from wa, chunk c+1 from wb
     if (c + 1 < n_chunks) {
       load_x(c + 1, 1);
-      load_w(wb, c + 1);
+      if (c > 0) load_w(wb, c + 1);    // the first pair was fetched before the wait
     }
     asm volatile("cp.async.commit_group;\n" ::);
     asm volatile("cp.async.wait_group 1;\n" ::);
@@ -140,6 +141,7 @@ linear_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
     __syncthreads();
   }
   asm volatile("cp.async.wait_group 0;\n" ::);
+  pdl_launch_dependents();             // the stream is read; the next kernel may begin while the results are stored
 
   // ---- epilogue: acc[j][c]: c0,c1 = (row g, tokens 8j+2t, +1); c2,c3 = (row g+8, same tokens) ----
   const int row_a = n0 + g, row_b = n0 + g + 8;
@@ -196,7 +198,7 @@ static int launch_ls(const __nv_bfloat16* x, const __nv_bfloat16* W, const float
   const int total_chunks = K / LS_KC;
   const int per = (total_chunks + splits - 1) / splits;
   dim3 grid((N + LS_ROWS - 1) / LS_ROWS, (total_chunks + per - 1) / per);
-  linear_stream_kernel<NT, EPI, OUT><<<grid, 256, smem, stream>>>(x, W, bias, (OUT*)out, partial, M, N, K, per);
+  launch_kernel(linear_stream_kernel<NT, EPI, OUT>, grid, 256, smem, stream, x, W, bias, (OUT*)out, partial, M, N, K, per);
   return launch_status("linear_stream");
 }
 
@@ -262,6 +264,7 @@ static std::mutex g_noalloc_mutex;
 
 // out[i] = sum over splits of partial[s][i]
 __global__ void sum_partials_kernel(const float* __restrict__ partial, int splits, size_t n, float* __restrict__ out) {
+  pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float v = 0.f;
@@ -308,6 +311,6 @@ SLLM_EXPORT int sllm_linear_stream_noalloc(const void* x, const void* W, const f
   int rc = sllm_linear_stream(x, W, bias, nullptr, SLLM_F32, scratch, M, N, K, real, EPI_STORE, stream);
   if (rc != SLLM_OK) return rc;
   const size_t n = (size_t)M * N;
-  sum_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(scratch, real, n, out);
+  launch_kernel(sum_partials_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, (const float*)scratch, real, n, out);
   return launch_status("linear_stream_noalloc");
 }

@@ -96,6 +96,7 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
   __shared__ double sh_d[33];
   __shared__ double warp_tot[32];
   __shared__ int found;
+  pdl_wait();
   const float* row = logits + (size_t)blockIdx.x * V;
   const MaxIdx mx = block_argmax(row, V, sh_mi);
   const float temp = temperature ? temperature[blockIdx.x] : 0.f;
@@ -152,6 +153,6 @@ SLLM_EXPORT int sllm_sample_rows(const float* logits, int R, int V, const float*
   SLLM_REQUIRE(R >= 0 && V > 0, "sample_rows: bad sizes R=%d V=%d", R, V);
   SLLM_REQUIRE(temperature == nullptr || uniform != nullptr, "sample_rows: temperatures without uniforms");
   if (R == 0) return SLLM_OK;
-  sample_rows_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, uniform, out);
+  launch_kernel(sample_rows_kernel, R, SAMPLE_THREADS, 0, stream, logits, V, temperature, uniform, out);
   return launch_status("sample_rows");
 }
