@@ -1,0 +1,299 @@
+// bfloat16 matrix product on the 5th-generation tensor cores, for prompt portions:
+//   C[M, N] = A[M, K] W[N, K]^T (+ bias), float32 accumulation in tensor memory.
+//
+// One CTA makes one 128 x 256 tile of C.  Its six warps have three jobs:
+//   warp 0  one lane issues the TMA loads: per 64-wide k block a 128 x 64 box of A and a
+//           256 x 64 box of W land in shared memory in the 128-byte-swizzled layout the tensor
+//           core reads, four stages deep (48 KB a stage), each signalling an mbarrier;
+//   warp 1  allocates 256 columns of tensor memory; one lane issues tcgen05.mma
+//           (cta_group::1, kind::f16, M=128, N=256, K=16) four times per stage and commits the
+//           stage's "empty" barrier, at the end the "accumulator full" barrier;
+//   warps 2-5  wait for the accumulator, read their quarter of its 128 lanes with tcgen05.ld
+//           (32 lanes x 32 columns at a time) and store C, with bias / as bfloat16 / through
+//           SiLU(gate)*up for a gate|up matrix interleaved in blocks of 8.
+// Both operands are K-major (rows contiguous in k) as checkpoints store W and as activations lie.
+// Out-of-range rows and the k tail are zero-filled by the TMA unit, so any M, N and any K that is
+// a multiple of 8 is taken.
+//
+// Every wait on an mbarrier is bounded: after its limit the waiter records a code in the status
+// word the host passes, waits (bounded) for the copies it has in flight, the tensor memory is
+// freed, and the kernel returns; the host reads the status after the launch's stream is synchronised.
+// No multicast, no clusters: each CTA loads both of its operands.
+//
+// The reference has no such kernel: its products are cublasGemmEx calls on one token
+// (kernels/cuda/kernels.cu:752-767) and its prefill runs in numpy (serving/executor.py:255-265).
+#include <cuda.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace sllm {
+
+constexpr int TG_BM = 128, TG_BN = 256, TG_BK = 64, TG_STAGES = 4;
+constexpr int TG_A_BYTES = TG_BM * TG_BK * 2;            // 16 KB
+constexpr int TG_B_BYTES = TG_BN * TG_BK * 2;            // 32 KB
+constexpr int TG_STAGE_BYTES = TG_A_BYTES + TG_B_BYTES;
+constexpr int TG_SMEM = TG_STAGES * TG_STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+constexpr uint32_t TG_WAIT_LIMIT = 1u << 24;             // polls before a wait gives up (tens of ms)
+constexpr int TG_TMEM_COLS = 256;
+
+#define TG_EPI_F32 0
+#define TG_EPI_BF16 1
+#define TG_EPI_SILU 2
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// false if the phase did not complete within `limit` polls
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = TG_WAIT_LIMIT) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < limit; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+// shared-memory matrix descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K, int* __restrict__ status) {
+  extern __shared__ unsigned char tg_smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tg_smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + TG_STAGES * TG_STAGE_BYTES);
+  uint64_t* empty = full + TG_STAGES;
+  uint64_t* accum = empty + TG_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * TG_BM, n0 = blockIdx.x * TG_BN;
+  const int k_blocks = (K + TG_BK - 1) / TG_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TG_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TG_TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                                     // A is the work of the step's earlier kernels
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % TG_STAGES, round = kb / TG_STAGES;
+        if (!mbar_wait(&empty[s], (round & 1) ^ 1) || *failed) {
+          if (!*failed) { *failed = 1; atomicExch(status, 1); }
+          break;
+        }
+        unsigned char* sa = smem + s * TG_STAGE_BYTES;
+        mbar_expect_tx(&full[s], TG_STAGE_BYTES);
+        tma_load_2d(sa, &map_a, kb * TG_BK, m0, &full[s]);
+        tma_load_2d(sa + TG_A_BYTES, &map_w, kb * TG_BK, n0, &full[s]);
+        issued = kb + 1;
+      }
+      if (*failed) {
+        // let the copies already issued land before the CTA gives its shared memory back
+        for (int kb = issued > TG_STAGES ? issued - TG_STAGES : 0; kb < issued; ++kb)
+          mbar_wait(&full[kb % TG_STAGES], (kb / TG_STAGES) & 1, 1u << 16);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      // instruction descriptor: D float32, A and B bfloat16, both K-major, N = 256, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TG_BN >> 3) << 17) | ((uint32_t)(TG_BM >> 4) << 24);
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % TG_STAGES, round = kb / TG_STAGES;
+        if (!mbar_wait(&full[s], round & 1) || *failed) {
+          if (!*failed) { *failed = 2; atomicExch(status, 2); }
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_u32(smem + s * TG_STAGE_BYTES), b_addr = a_addr + TG_A_BYTES;
+#pragma unroll
+        for (int k = 0; k < TG_BK / 16; ++k)        // 16 k = 32 bytes further along the swizzled row
+          umma_bf16(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) ? 1u : 0u);
+        umma_commit(&empty[s]);                     // arrives when these MMAs have read the stage
+      }
+      umma_commit(accum);                           // arrives when every MMA issued so far is done
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5 own TMEM lane quarters 2, 3, 0, 1 ----------------
+    const int quarter = warp & 3;
+    bool ok = mbar_wait(accum, 0);
+    if (!ok && !*failed) { *failed = 3; atomicExch(status, 3); }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok && !*failed) {
+      const int m = m0 + quarter * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TG_BN; c0 += 32) {
+        if (n0 + c0 >= N) break;                    // warp-uniform
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (m >= M) continue;
+        const int n = n0 + c0;
+        if constexpr (EPI == TG_EPI_SILU) {
+          // columns alternate 8 gate, 8 up; out[m, (n/16)*8 + i] = silu(gate_i) * up_i
+          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * (N >> 1) + (n >> 1);
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk) {
+            if (n + blk * 16 + 15 >= N) break;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float g = __uint_as_float(r[blk * 16 + i]), u = __uint_as_float(r[blk * 16 + 8 + i]);
+              o[blk * 8 + i] = __float2bfloat16_rn(g * (1.0f / (1.0f + expf(-g))) * u);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (n + i < N) {
+              const float v = __uint_as_float(r[i]) + (bias ? bias[n + i] : 0.f);
+              if constexpr (EPI == TG_EPI_F32) reinterpret_cast<float*>(out)[(size_t)m * N + n + i] = v;
+              else reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * N + n + i] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  pdl_launch_dependents();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TG_TMEM_COLS));
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+// rows x K bfloat16, row-major; boxes of box_rows x 64 elements, 128-byte swizzle, zeros outside
+static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TG_BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int EPI>
+static int launch_tg(const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, void* out, int M, int N, int K,
+                     int* status, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TG_SMEM) != cudaSuccess) {
+      set_error("gemm_tcgen05: cannot raise the shared memory limit");
+      return SLLM_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  dim3 grid((N + TG_BN - 1) / TG_BN, (M + TG_BM - 1) / TG_BM);
+  launch_kernel(gemm_tcgen05_kernel<EPI>, grid, 192, TG_SMEM, stream, ma, mw, bias, out, M, N, K, status);
+  return launch_status("gemm_tcgen05");
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+SLLM_EXPORT int sllm_gemm_tcgen05_supports(int M, int N, int K) {
+  return M >= 1 && N >= 8 && K >= 8 && K % 8 == 0 && M <= (1 << 24) && encode_fn() != nullptr;
+}
+
+// epilogue 0: float32 out[M, N] (+bias); 1: bfloat16 out[M, N] (+bias); 2: bfloat16 out[M, N/2] =
+// silu(gate) * up for W rows interleaved in blocks of 8 (N a multiple of 16).
+// `status` is one int of device memory, zero before the launch; non-zero afterwards means a wait
+// inside the kernel ran out (1 producer, 2 MMA issuer, 3 epilogue) and `out` is not valid.
+SLLM_EXPORT int sllm_gemm_tcgen05(const void* A, const void* W, const float* bias, void* out, int M, int N, int K,
+                                  int epilogue, int* status, cudaStream_t stream) {
+  SLLM_REQUIRE(M >= 1 && N >= 8 && K >= 8 && K % 8 == 0, "gemm_tcgen05: sizes M=%d N=%d K=%d (K must be a multiple of 8)", M, N, K);
+  SLLM_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
+  SLLM_REQUIRE(status != nullptr, "gemm_tcgen05: a status word is required");
+  SLLM_REQUIRE(epilogue != TG_EPI_SILU || N % 16 == 0, "gemm_tcgen05: the SiLU epilogue needs N %% 16 == 0");
+  CUtensorMap ma, mw;
+  if (!make_map(&ma, A, M, K, TG_BM) || !make_map(&mw, W, N, K, TG_BN)) {
+    set_error("gemm_tcgen05: cuTensorMapEncodeTiled failed");
+    return SLLM_ERR_LAUNCH;
+  }
+  switch (epilogue) {
+    case TG_EPI_F32: return launch_tg<TG_EPI_F32>(ma, mw, bias, out, M, N, K, status, stream);
+    case TG_EPI_BF16: return launch_tg<TG_EPI_BF16>(ma, mw, bias, out, M, N, K, status, stream);
+    case TG_EPI_SILU: return launch_tg<TG_EPI_SILU>(ma, mw, bias, out, M, N, K, status, stream);
+  }
+  SLLM_REQUIRE(false, "gemm_tcgen05: unknown epilogue %d", epilogue);
+}

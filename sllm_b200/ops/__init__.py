@@ -121,6 +121,57 @@ def linear_stream(x, w, bias, out_dtype, *, splits: int = 1, silu: bool = False)
     return partial if real > 1 else out
 
 
+_tc_status: dict = {}      # device -> int32[1]: non-zero once a wait inside a tcgen05 kernel ran out
+_tc_used = {"since_check": 0}
+
+
+def _status_word(device) -> torch.Tensor:
+    t = _tc_status.get(device)
+    if t is None:
+        t = _tc_status[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return t
+
+
+def check_tcgen05_status() -> None:
+    """Raise if a bounded wait inside a tcgen05 kernel gave up since the last check (reads one
+    int from each device that ran such a kernel; synchronises)."""
+    if not _tc_used["since_check"]:
+        return
+    _tc_used["since_check"] = 0
+    for dev, t in _tc_status.items():
+        code = int(t.item())
+        if code:
+            t.zero_()
+            who = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, f"code {code}")
+            raise KernelError(f"gemm_tcgen05 on {dev}: a wait of {who} ran out; the product is not valid")
+
+
+def tcgen05_supports(M: int, N: int, K: int) -> bool:
+    return bool(lib().sllm_gemm_tcgen05_supports(int(M), int(N), int(K)))
+
+
+def gemm_tcgen05(x, w, bias, out_dtype, *, silu: bool = False):
+    """``x @ w.T (+ bias)`` on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory);
+    with ``silu`` the matrix is gate|up interleaved in blocks of 8 and the bfloat16 result is
+    ``silu(gate) * up`` of width N/2."""
+    _chk(x, w, bias)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tcgen05: bfloat16 operands only")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"linear: x {tuple(x.shape)} does not fit w {tuple(w.shape)}")
+    if silu:
+        epi, out = 2, torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    elif out_dtype == torch.float32:
+        epi, out = 0, torch.empty((M, N), dtype=torch.float32, device=x.device)
+    else:
+        epi, out = 1, torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    call("sllm_gemm_tcgen05", _p(x), _p(w), _p(bias), _p(out), M, N, K, epi, _p(_status_word(x.device)), _stream())
+    _tc_used["since_check"] += 1
+    return out
+
+
 def _stream_splits(N: int, K: int) -> int:
     ctas = -(-N // 128)
     return max(1, min(2 * NUM_SMS // ctas, K // 128, 16))

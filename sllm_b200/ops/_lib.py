@@ -49,6 +49,8 @@ def _declare(L):
                                 c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
         "sllm_sample_rows": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
         "sllm_attention_mma_supports": [c_int],
+        "sllm_gemm_tcgen05_supports": [c_int, c_int, c_int],
+        "sllm_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "sllm_linear_stream_supports": [c_int, c_int, c_int],
         "sllm_linear_stream_splits": [c_int, c_int],
         "sllm_linear_stream": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,

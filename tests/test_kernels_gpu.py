@@ -340,3 +340,36 @@ def test_linear_stream_silu(M, I, K):
     want = gate * torch.sigmoid(gate) * up
     got = ops.linear_silu_mul(x, gu, 8, torch.bfloat16)
     torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=1.6e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (200, 300, 72), (2048, 512, 3584), (77, 1000, 336),
+                                   (513, 264, 128)])
+def test_gemm_tcgen05(M, N, K):
+    """The tcgen05 product against the float32 statement: whole tiles, ragged M and N, a k tail."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(15)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g)
+    want = x.float() @ w.float().t() + b
+    got = ops.gemm_tcgen05(x, w, b, torch.float32)
+    ops.check_tcgen05_status()
+    torch.testing.assert_close(got, want, rtol=2e-3, atol=2e-3)
+    got = ops.gemm_tcgen05(x, w, b, torch.bfloat16)
+    ops.check_tcgen05_status()
+    torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=1.6e-2)
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (300, 200, 136), (1024, 4864, 896)])
+def test_gemm_tcgen05_silu(M, I, K):
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(16)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    wg = (torch.randn(I, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    wu = (torch.randn(I, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    gu = torch.stack([wg.reshape(I // 8, 8, K), wu.reshape(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
+    gate, up = x.float() @ wg.float().t(), x.float() @ wu.float().t()
+    want = gate * torch.sigmoid(gate) * up
+    got = ops.gemm_tcgen05(x, gu, None, torch.bfloat16, silu=True)
+    ops.check_tcgen05_status()
+    torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=1.6e-2)
