@@ -238,6 +238,7 @@ def main(argv=None) -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer than 28 only where memory or time needs it")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64 and the prefill")
+    ap.add_argument("--prefill-only", action="store_true", help="run the 2,048-token prefill alone (for profilers)")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
     args = ap.parse_args(argv)
 
@@ -265,6 +266,12 @@ def main(argv=None) -> int:
     model, _ = build_random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0", std=0.02)
     torch.cuda.synchronize()
 
+    if args.prefill_only:
+        ms = prefill_run(model, cfg, PREFILL_TOKENS, reps=2)
+        fl = flops_of_step(cfg, [PREFILL_TOKENS], [0], 1)
+        print(json.dumps({"prefill_only": True, "layers": args.layers, "tokens": PREFILL_TOKENS, "ms": round(ms, 3),
+                          "tflops": round(fl / (ms / 1e3) / 1e12, 1)}))
+        return 0
     main_run = decode_run(model, cfg, args.batch, args.context, args.steps, args.warmup, graphs=not args.no_graphs)
     points = {}
     prefill = None

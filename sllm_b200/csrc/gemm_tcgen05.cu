@@ -1,16 +1,20 @@
 // bfloat16 matrix product on the 5th-generation tensor cores, for prompt portions:
 //   C[M, N] = A[M, K] W[N, K]^T (+ bias), float32 accumulation in tensor memory.
 //
-// One CTA makes one 128 x 256 tile of C.  Its six warps have three jobs:
+// The kernel is persistent: one CTA per SM walks over 128 x 256 tiles of C (M tiles fastest, so
+// that the CTAs working at the same time share few W tiles and all of A through L2).  The
+// accumulator is double-buffered in tensor memory (2 x 256 of its 512 columns), so the epilogue of
+// one tile runs while the next tile's products are issued.  The six warps have three jobs:
 //   warp 0  one lane issues the TMA loads: per 64-wide k block a 128 x 64 box of A and a
 //           256 x 64 box of W land in shared memory in the 128-byte-swizzled layout the tensor
 //           core reads, four stages deep (48 KB a stage), each signalling an mbarrier;
-//   warp 1  allocates 256 columns of tensor memory; one lane issues tcgen05.mma
-//           (cta_group::1, kind::f16, M=128, N=256, K=16) four times per stage and commits the
-//           stage's "empty" barrier, at the end the "accumulator full" barrier;
-//   warps 2-5  wait for the accumulator, read their quarter of its 128 lanes with tcgen05.ld
-//           (32 lanes x 32 columns at a time) and store C, with bias / as bfloat16 / through
-//           SiLU(gate)*up for a gate|up matrix interleaved in blocks of 8.
+//   warp 1  allocates the tensor memory; one lane waits for an accumulator buffer to be free,
+//           issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=256, K=16) four times per stage,
+//           commits the stage's "empty" barrier and, after a tile's last stage, the buffer's
+//           "accumulator full" barrier;
+//   warps 2-5  wait for a full accumulator, read their quarter of its 128 lanes with tcgen05.ld
+//           (32 lanes x 32 columns at a time), store C (with bias / as bfloat16 / through
+//           SiLU(gate)*up for a gate|up matrix interleaved in blocks of 8) and hand the buffer back.
 // Both operands are K-major (rows contiguous in k) as checkpoints store W and as activations lie.
 // Out-of-range rows and the k tail are zero-filled by the TMA unit, so any M, N and any K that is
 // a multiple of 8 is taken.
@@ -35,7 +39,7 @@ constexpr int TG_B_BYTES = TG_BN * TG_BK * 2;            // 32 KB
 constexpr int TG_STAGE_BYTES = TG_A_BYTES + TG_B_BYTES;
 constexpr int TG_SMEM = TG_STAGES * TG_STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 constexpr uint32_t TG_WAIT_LIMIT = 1u << 24;             // polls before a wait gives up (tens of ms)
-constexpr int TG_TMEM_COLS = 256;
+constexpr int TG_TMEM_COLS = 512;                        // two accumulators of 256 columns
 
 #define TG_EPI_F32 0
 #define TG_EPI_BF16 1
@@ -45,6 +49,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
@@ -93,6 +100,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
 }
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 template <int EPI>
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -101,12 +113,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tg_smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + TG_STAGES * TG_STAGE_BYTES);
   uint64_t* empty = full + TG_STAGES;
-  uint64_t* accum = empty + TG_STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  uint64_t* acc_full = empty + TG_STAGES;           // [2]
+  uint64_t* acc_empty = acc_full + 2;               // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * TG_BM, n0 = blockIdx.x * TG_BN;
+  const int m_tiles = (M + TG_BM - 1) / TG_BM, n_tiles = (N + TG_BN - 1) / TG_BN;
+  const int tiles = m_tiles * n_tiles;
   const int k_blocks = (K + TG_BK - 1) / TG_BK;
 
   if (threadIdx.x == 0) {
@@ -114,7 +128,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(accum, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);                  // the four epilogue warps
+    }
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -131,23 +148,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        const int s = kb % TG_STAGES, round = kb / TG_STAGES;
-        if (!mbar_wait(&empty[s], (round & 1) ^ 1) || *failed) {
-          if (!*failed) { *failed = 1; atomicExch(status, 1); }
-          break;
+      int it = 0, issued = 0;                       // k blocks issued so far, over all tiles
+      for (int tile = blockIdx.x; tile < tiles && !*failed; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * TG_BM, n0 = (tile / m_tiles) * TG_BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % TG_STAGES, round = it / TG_STAGES;
+          if (!mbar_wait(&empty[s], (round & 1) ^ 1) || *failed) {
+            if (!*failed) { *failed = 1; atomicExch(status, 1); }
+            break;
+          }
+          unsigned char* sa = smem + s * TG_STAGE_BYTES;
+          mbar_expect_tx(&full[s], TG_STAGE_BYTES);
+          tma_load_2d(sa, &map_a, kb * TG_BK, m0, &full[s]);
+          tma_load_2d(sa + TG_A_BYTES, &map_w, kb * TG_BK, n0, &full[s]);
+          issued = it + 1;
         }
-        unsigned char* sa = smem + s * TG_STAGE_BYTES;
-        mbar_expect_tx(&full[s], TG_STAGE_BYTES);
-        tma_load_2d(sa, &map_a, kb * TG_BK, m0, &full[s]);
-        tma_load_2d(sa + TG_A_BYTES, &map_w, kb * TG_BK, n0, &full[s]);
-        issued = kb + 1;
       }
       if (*failed) {
         // let the copies already issued land before the CTA gives its shared memory back
-        for (int kb = issued > TG_STAGES ? issued - TG_STAGES : 0; kb < issued; ++kb)
-          mbar_wait(&full[kb % TG_STAGES], (kb / TG_STAGES) & 1, 1u << 16);
+        for (int i = issued > TG_STAGES ? issued - TG_STAGES : 0; i < issued; ++i)
+          mbar_wait(&full[i % TG_STAGES], (i / TG_STAGES) & 1, 1u << 16);
       }
     }
   } else if (warp == 1) {
@@ -155,34 +175,48 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       // instruction descriptor: D float32, A and B bfloat16, both K-major, N = 256, M = 128
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TG_BN >> 3) << 17) | ((uint32_t)(TG_BM >> 4) << 24);
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        const int s = kb % TG_STAGES, round = kb / TG_STAGES;
-        if (!mbar_wait(&full[s], round & 1) || *failed) {
+      int it = 0, local = 0;
+      for (int tile = blockIdx.x; tile < tiles && !*failed; tile += gridDim.x, ++local) {
+        const int b = local & 1;
+        if (!mbar_wait(&acc_empty[b], ((local >> 1) & 1) ^ 1) || *failed) {     // the epilogue has drained this buffer
           if (!*failed) { *failed = 2; atomicExch(status, 2); }
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(smem + s * TG_STAGE_BYTES), b_addr = a_addr + TG_A_BYTES;
+        const uint32_t tmem_d = tmem_base + b * TG_BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % TG_STAGES, round = it / TG_STAGES;
+          if (!mbar_wait(&full[s], round & 1) || *failed) {
+            if (!*failed) { *failed = 2; atomicExch(status, 2); }
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(smem + s * TG_STAGE_BYTES), b_addr = a_addr + TG_A_BYTES;
 #pragma unroll
-        for (int k = 0; k < TG_BK / 16; ++k)        // 16 k = 32 bytes further along the swizzled row
-          umma_bf16(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) ? 1u : 0u);
-        umma_commit(&empty[s]);                     // arrives when these MMAs have read the stage
+          for (int k = 0; k < TG_BK / 16; ++k)      // 16 k = 32 bytes further along the swizzled row
+            umma_bf16(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) ? 1u : 0u);
+          umma_commit(&empty[s]);                   // arrives when these MMAs have read the stage
+        }
+        umma_commit(&acc_full[b]);                  // arrives when every MMA issued so far is done
       }
-      umma_commit(accum);                           // arrives when every MMA issued so far is done
     }
   } else {
     // ---------------- epilogue: warps 2..5 own TMEM lane quarters 2, 3, 0, 1 ----------------
     const int quarter = warp & 3;
-    bool ok = mbar_wait(accum, 0);
-    if (!ok && !*failed) { *failed = 3; atomicExch(status, 3); }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok && !*failed) {
+    int local = 0;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+      const int b = local & 1;
+      const int m0 = (tile % m_tiles) * TG_BM, n0 = (tile / m_tiles) * TG_BN;
+      const bool ok = mbar_wait(&acc_full[b], (local >> 1) & 1);
+      if (!ok && !*failed) { *failed = 3; atomicExch(status, 3); }
+      if (!ok || *failed) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m = m0 + quarter * 32 + lane;
 #pragma unroll 1
       for (int c0 = 0; c0 < TG_BN; c0 += 32) {
         if (n0 + c0 >= N) break;                    // warp-uniform
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0, r);
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + b * TG_BN + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (m >= M) continue;
         const int n = n0 + c0;
@@ -192,23 +226,51 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int blk = 0; blk < 2; ++blk) {
             if (n + blk * 16 + 15 >= N) break;
+            float v[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const float g = __uint_as_float(r[blk * 16 + i]), u = __uint_as_float(r[blk * 16 + 8 + i]);
-              o[blk * 8 + i] = __float2bfloat16_rn(g * (1.0f / (1.0f + expf(-g))) * u);
+              v[i] = g * (1.0f / (1.0f + expf(-g))) * u;
+            }
+            if (((N >> 1) & 7) == 0) {               // rows of the result are 16-byte aligned
+              *reinterpret_cast<uint4*>(o + blk * 8) = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[blk * 8 + i] = __float2bfloat16_rn(v[i]);
             }
           }
         } else {
+          float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (n + i < N) {
-              const float v = __uint_as_float(r[i]) + (bias ? bias[n + i] : 0.f);
-              if constexpr (EPI == TG_EPI_F32) reinterpret_cast<float*>(out)[(size_t)m * N + n + i] = v;
-              else reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * N + n + i] = __float2bfloat16_rn(v);
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) + ((bias && n + i < N) ? bias[n + i] : 0.f);
+          const bool whole = n + 32 <= N;
+          if constexpr (EPI == TG_EPI_F32) {
+            float* o = reinterpret_cast<float*>(out) + (size_t)m * N + n;
+            if (whole && (N & 3) == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) if (n + i < N) o[i] = v[i];
+            }
+          } else {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * N + n;
+            if (whole && (N & 7) == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8)
+                *reinterpret_cast<uint4*>(o + i) = make_uint4(pack2(v[i], v[i + 1]), pack2(v[i + 2], v[i + 3]),
+                                                              pack2(v[i + 4], v[i + 5]), pack2(v[i + 6], v[i + 7]));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) if (n + i < N) o[i] = __float2bfloat16_rn(v[i]);
             }
           }
         }
       }
+      // this warp has read its quarter of the buffer: hand it back to the MMA issuer
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[b]);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -262,7 +324,14 @@ static int launch_tg(const CUtensorMap& ma, const CUtensorMap& mw, const float* 
     }
     configured = true;
   }
-  dim3 grid((N + TG_BN - 1) / TG_BN, (M + TG_BM - 1) / TG_BM);
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
+  }
+  const long long tiles = (long long)((M + TG_BM - 1) / TG_BM) * ((N + TG_BN - 1) / TG_BN);
+  dim3 grid((unsigned)(tiles < num_sms ? tiles : num_sms));      // persistent: one CTA per SM walks the tiles
   launch_kernel(gemm_tcgen05_kernel<EPI>, grid, 192, TG_SMEM, stream, ma, mw, bias, out, M, N, K, status);
   return launch_status("gemm_tcgen05");
 }

@@ -188,6 +188,9 @@ class Engine:
         for e, tot in zip(entries, ctx.ctx_lens):
             self.cache.commit(e.req_id, tot)
         self.steps_run += 1
+        if self.device.type == "cuda":
+            from .. import ops
+            ops.check_tcgen05_status()      # reads a status word only if such a kernel ran in this step
         return logits
 
     # ---- decoding through a captured graph -------------------------------------------------

@@ -91,6 +91,7 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, bias) -> torch.Tensor:
     return out
 
 
+TCGEN05_MIN_ROWS = 128    # below this a 128-row tile is mostly padding
 STREAM_MAX_ROWS = 32      # beyond this the kernel's shared-memory reads of the activations bound it
 
 
@@ -220,9 +221,14 @@ def silu_mul(gu: torch.Tensor, interleave: int, out_dtype: torch.dtype) -> torch
 
 def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, out_dtype: torch.dtype) -> torch.Tensor:
     """``silu(x Wg^T) * (x Wu^T)`` with gate and up rows interleaved in one matrix."""
-    if (x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and interleave == 8 and x.is_cuda
-            and stream_supports(x.shape[0], w_gate_up.shape[0], x.shape[1])):
-        return linear_stream(x, w_gate_up, None, out_dtype, silu=True)
+    if x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and interleave == 8 and x.is_cuda:
+        M, K = x.shape
+        N = w_gate_up.shape[0]
+        if stream_supports(M, N, K):
+            return linear_stream(x, w_gate_up, None, out_dtype, silu=True)
+        if M > TCGEN05_MIN_ROWS and N % 16 == 0 and tcgen05_supports(M, N, K):
+            # many rows: the tcgen05 product with the activation applied as the tile leaves tensor memory
+            return gemm_tcgen05(x, w_gate_up, None, out_dtype, silu=True)
     gu = linear(x, w_gate_up, None, x.dtype)
     return silu_mul(gu, interleave, out_dtype)
 
