@@ -7,7 +7,7 @@
 // carries its own position, so a portion that starts anywhere in the context, and a
 // single decoded token, are the same code.
 //
-//   PREFILL form: 64 rows per CTA, 4 warps x 16 rows, every warp walks all keys of a tile.
+//   PREFILL form: 128 rows per CTA, 8 warps x 16 rows, every warp walks all keys of a tile.
 //   DECODE form:  16 rows per CTA (a request's one or two tokens x its group); the four
 //                 warps take different 16-key slices of each 64-key tile and merge at the
 //                 end; the grid's z dimension splits the context further (split-KV), the
@@ -73,15 +73,17 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 constexpr int ATT_BN = 64;     // keys per tile
 // block-table entries a CTA keeps in shared memory (the decode form reads a split of the
 // context only, and must leave room for two CTAs per SM)
-template <bool DECODE> struct AttBtCache { static constexpr int value = DECODE ? 512 : 2048; };
+template <bool DECODE> struct AttBtCache { static constexpr int value = DECODE ? 512 : 1024; };
+template <bool DECODE> struct AttThreads { static constexpr int value = DECODE ? 128 : 256; };
 template <bool DECODE> struct AttStages { static constexpr int value = DECODE ? 3 : 2; };
 
 template <int HD, bool DECODE>
-__global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kernel(const AttnParams p) {
+  constexpr int NTHREADS = AttThreads<DECODE>::value;
   constexpr int STRIDE = HD + 8;                 // 16 bytes of padding: ldmatrix rows fall in distinct banks
   constexpr int KSTEPS = HD / 16;
   constexpr int DT = HD / 8;                     // output n-tiles
-  constexpr int BM = DECODE ? 16 : 64;
+  constexpr int BM = DECODE ? 16 : 128;
   constexpr int NT = DECODE ? 2 : 8;             // 8-key n-tiles a warp computes per key tile
   constexpr int CHUNKS = HD / 8;                 // 16-byte chunks per row
   constexpr int STAGES = AttStages<DECODE>::value;   // key/value tiles in flight: the decode form is latency-bound
@@ -121,13 +123,13 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
   const int page_count = n_tiles > 0 ? (key_hi - 1) / p.page_size - page_first + 1 : 0;
   const bool bt_cached = page_count <= BT_CACHE;
   if (bt_cached) {
-    for (int i = tid; i < page_count; i += 128) bt_s[i] = bt[page_first + i];
+    for (int i = tid; i < page_count; i += NTHREADS) bt_s[i] = bt[page_first + i];
     __syncthreads();
   }
 
   // ---- loads -----------------------------------------------------------------------
   auto load_q = [&]() {
-    for (int c = tid; c < BM * CHUNKS; c += 128) {
+    for (int c = tid; c < BM * CHUNKS; c += NTHREADS) {
       const int r = c / CHUNKS, ch = c % CHUNKS;
       const int row = row0 + r;
       const bool ok = row < rows_total;
@@ -138,7 +140,7 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
   };
   // each thread keeps one 16-byte column of the rows r_first, r_first + R_STEP, ...: the address
   // arithmetic of a tile is a handful of instructions per row
-  constexpr int R_STEP = 128 / CHUNKS;
+  constexpr int R_STEP = NTHREADS / CHUNKS;
   const int ch8 = (tid % CHUNKS) * 8, r_first = tid / CHUNKS;
   const int ps = p.page_size;
   const int ps_shift = (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1;
@@ -387,7 +389,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
 
 template <int HD, bool DECODE>
 static int launch_attention(const AttnParams& p, int tiles, cudaStream_t stream) {
-  constexpr int BM = DECODE ? 16 : 64;
+  constexpr int BM = DECODE ? 16 : 128;
   constexpr size_t smem = sizeof(__nv_bfloat16) * (size_t)(BM + 2 * AttStages<DECODE>::value * ATT_BN) * (HD + 8) +
                           sizeof(int) * AttBtCache<DECODE>::value;
   static bool configured = false;                 // per template instance
@@ -400,7 +402,7 @@ static int launch_attention(const AttnParams& p, int tiles, cudaStream_t stream)
     configured = true;
   }
   dim3 grid(tiles, p.nkv, p.num_splits);
-  launch_kernel(attention_mma_kernel<HD, DECODE>, grid, 128, smem, stream, p);
+  launch_kernel(attention_mma_kernel<HD, DECODE>, grid, AttThreads<DECODE>::value, smem, stream, p);
   int rc = launch_status("attention_mma");
   if (rc != SLLM_OK) return rc;
   if (p.num_splits > 1) {
@@ -418,7 +420,7 @@ using namespace sllm;
 // 1 if the tensor-core kernel takes this head size (others go to the CUDA-core kernel).
 SLLM_EXPORT int sllm_attention_mma_supports(int hd) { return hd == 16 || hd == 32 || hd == 64 || hd == 128; }
 
-// tiles: tile_seq/tile_row0 [tiles] describe 64-row (decode == 0) or 16-row (decode == 1) tiles of
+// tiles: tile_seq/tile_row0 [tiles] describe 128-row (decode == 0) or 16-row (decode == 1) tiles of
 // (token, head-in-group) rows.  part_o/part_lse are scratch for num_splits > 1:
 // float32 [num_splits, T, nq, hd] and [num_splits, T, nq].
 SLLM_EXPORT int sllm_attention_mma(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o,

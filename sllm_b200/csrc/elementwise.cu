@@ -151,56 +151,66 @@ __global__ void gather_rows_kernel(const T* __restrict__ x, int parts, size_t pa
 // table: [max_pos][2][rot/2] cos then sin, float32 made from float64 angles.
 // ---------------------------------------------------------------------------
 // The q|k|v rows may arrive as `parts` partial sums (a k-split product), `part_stride` apart;
-// they are added here in order.
+// they are added here in order.  A block takes `hpb` consecutive heads of one token (one head when
+// few tokens leave the GPU idle otherwise, all heads for prompt portions).
 template <typename TI, typename TC>
 __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int parts, size_t part_stride,
                                      const float* __restrict__ bias,
                                      const int* __restrict__ positions, const float* __restrict__ table,
-                                     int rot, int max_pos, int nq, int nkv, int hd,
+                                     int rot, int max_pos, int nq, int nkv, int hd, int hpb,
                                      const int* __restrict__ slot_mapping, int page_size, int num_pages,
                                      TC* __restrict__ k_cache, TC* __restrict__ v_cache, TC* __restrict__ q_out) {
   pdl_wait();
   const int t = blockIdx.x;
-  const int head = blockIdx.y;                       // 0..nq-1 q, then nkv k, then nkv v
-  const int width = (nq + 2 * nkv) * hd;
-  const TI* x = qkv + (size_t)t * width + (size_t)head * hd;
-  const float* b = bias ? bias + (size_t)head * hd : nullptr;
-  auto ld = [&](int d) {
-    float v = to_f32(x[d]);
-    for (int p = 1; p < parts; ++p) v += to_f32(x[p * part_stride + d]);
-    return v + (b ? b[d] : 0.f);
+  const int heads = nq + 2 * nkv;
+  const int head0 = blockIdx.y * hpb;
+  const int nheads = min(hpb, heads - head0);
+  const int width = heads * hd;
+  const TI* xt = qkv + (size_t)t * width;
+  auto ld = [&](int col) {                           // col: column of the fused row
+    float v = to_f32(xt[col]);
+    for (int p = 1; p < parts; ++p) v += to_f32(xt[p * part_stride + col]);
+    return v + (bias ? bias[col] : 0.f);
   };
-  const bool is_q = head < nq;
-  const bool is_k = !is_q && head < nq + nkv;
-  TC* dst;
-  if (is_q) {
-    dst = q_out + (size_t)t * nq * hd + (size_t)head * hd;
-  } else {
-    if (slot_mapping == nullptr) return;             // this run reads another run's cache
-    const int slot = slot_mapping[t];
-    const int page = slot / page_size, off = slot % page_size;
-    if (slot < 0 || page >= num_pages) return;       // the host checks tables; never write outside the pool
+  // where a head's row goes: q_out, or the token's slot of the key / value pages (null: skip)
+  int slot = -1;
+  if (slot_mapping != nullptr) {
+    slot = slot_mapping[t];
+    if (slot < 0 || slot / page_size >= num_pages) slot = -1;   // the host checks tables; never write outside the pool
+  }
+  auto dst_of = [&](int head) -> TC* {
+    if (head < nq) return q_out + (size_t)t * nq * hd + (size_t)head * hd;
+    if (slot < 0) return nullptr;                    // this run reads another run's cache
+    const bool is_k = head < nq + nkv;
     const int kvh = is_k ? head - nq : head - nq - nkv;
-    TC* base = is_k ? k_cache : v_cache;
-    dst = base + (((size_t)page * nkv + kvh) * page_size + off) * hd;
-  }
-  const bool rotate = (is_q || is_k) && rot > 0 && table != nullptr;
-  if (!rotate) {
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[d] = from_f32<TC>(ld(d));
-    return;
-  }
-  int pos = positions[t];
-  pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const int page = slot / page_size, off = slot % page_size;
+    return (is_k ? k_cache : v_cache) + (((size_t)page * nkv + kvh) * page_size + off) * hd;
+  };
+  const bool rotary = rot > 0 && table != nullptr;
   const int half = rot / 2;
-  const float* cs = table + (size_t)pos * rot;       // cos[half] then sin[half]
-  for (int j = threadIdx.x; j < half; j += blockDim.x) {
-    const float x1 = ld(j);
-    const float x2 = ld(j + half);
-    const float c = cs[j], s = cs[half + j];
-    dst[j] = from_f32<TC>(x1 * c - x2 * s);
-    dst[j + half] = from_f32<TC>(x2 * c + x1 * s);
+  if (rotary) {
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* cs = table + (size_t)pos * rot;     // cos[half] then sin[half]
+    for (int item = threadIdx.x; item < nheads * half; item += blockDim.x) {
+      const int head = head0 + item / half, j = item % half;
+      if (head >= nq + nkv) break;                   // value heads are not rotated (items ascend by head)
+      TC* dst = dst_of(head);
+      if (dst == nullptr) continue;
+      const float x1 = ld(head * hd + j), x2 = ld(head * hd + j + half);
+      const float c = cs[j], sn = cs[half + j];
+      dst[j] = from_f32<TC>(x1 * c - x2 * sn);
+      dst[j + half] = from_f32<TC>(x2 * c + x1 * sn);
+    }
   }
-  for (int d = rot + threadIdx.x; d < hd; d += blockDim.x) dst[d] = from_f32<TC>(ld(d));
+  // what is not rotated: dims >= rot of q and k heads, every dim of v heads
+  for (int item = threadIdx.x; item < nheads * hd; item += blockDim.x) {
+    const int head = head0 + item / hd, d = item % hd;
+    if (rotary && head < nq + nkv && d < rot) continue;
+    TC* dst = dst_of(head);
+    if (dst == nullptr) continue;
+    dst[d] = from_f32<TC>(ld(head * hd + d));
+  }
 }
 
 }  // namespace sllm
@@ -293,11 +303,14 @@ SLLM_EXPORT int sllm_rope_kv_write(const void* qkv, int in_dtype, int parts, siz
   SLLM_REQUIRE(slot_mapping == nullptr || (page_size > 0 && num_pages > 0 && k_cache && v_cache),
                "rope_kv_write: cache arguments missing");
   if (T == 0) return SLLM_OK;
-  dim3 grid(T, nq + 2 * nkv);
-  const int threads = hd / 2 >= 64 ? 64 : 32;
+  const int heads = nq + 2 * nkv;
+  // few tokens: a block per head, so that the launch fills the GPU; many: a block per token
+  const int hpb = T >= 128 ? heads : 1;
+  dim3 grid(T, (heads + hpb - 1) / hpb);
+  const int threads = hpb == 1 ? (hd / 2 >= 64 ? 64 : 32) : 256;
 #define LAUNCH(TI, TC)                                                                                         \
   launch_kernel(rope_kv_write_kernel<TI, TC>, grid, threads, 0, stream, (const TI*)qkv, parts, part_stride, bias,  \
-                positions, table, rot, max_pos, nq, nkv, hd, slot_mapping, page_size, num_pages,                   \
+                positions, table, rot, max_pos, nq, nkv, hd, hpb, slot_mapping, page_size, num_pages,              \
                 (TC*)k_cache, (TC*)v_cache, (TC*)q_out)
   if (in_dtype == SLLM_F32 && cache_dtype == SLLM_F32) LAUNCH(float, float);
   else if (in_dtype == SLLM_F32 && cache_dtype == SLLM_BF16) LAUNCH(float, __nv_bfloat16);

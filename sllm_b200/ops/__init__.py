@@ -280,20 +280,25 @@ def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, n
 NUM_SMS = 148
 
 
-def attention_tiles(q_lens, group_size: int, device):
+def attention_tiles(q_lens, group_size: int, device, ctx_lens=None):
     """Tiles of (token, head-in-group) rows for the tensor-core attention kernel: requests
-    whose rows fit one 16-row tile go to the decode form, the others are cut into 64-row
+    whose rows fit one 16-row tile go to the decode form, the others are cut into 128-row
     tiles for the prefill form.  Returns ``(small, large)``, each ``None`` or
     ``(tile_seq, tile_row0, count)`` on the device."""
     small_s, large_s, large_r = [], [], []
+    ctx_before = [(c - n) for c, n in zip(ctx_lens, q_lens)] if ctx_lens else [0] * len(q_lens)
     for s, n in enumerate(q_lens):
         rows = n * group_size
         if rows <= 16:
             small_s.append(s)
         else:
-            for r0 in range(0, rows, 64):
+            for r0 in range(0, rows, 128):
                 large_s.append(s)
                 large_r.append(r0)
+
+    # the tiles with the most keys to walk first: a long tile that starts last would run alone
+    order = sorted(range(len(large_s)), key=lambda i: -(large_r[i] // max(group_size, 1) + ctx_before[large_s[i]]))
+    large_s, large_r = [large_s[i] for i in order], [large_r[i] for i in order]
 
     def up(seqs, rows):
         if not seqs:
@@ -347,7 +352,7 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
     G = nq // nkv
     key = ("mma", G)
     if key not in step.attn_tiles:
-        small, large = attention_tiles(step.q_lens, G, q.device)
+        small, large = attention_tiles(step.q_lens, G, q.device, step.ctx_lens)
         splits = choose_splits(small[2], nkv, step.max_ctx_len) if (small and not large) else 1
         step.attn_tiles[key] = (small, large, splits)
     small, large, splits = step.attn_tiles[key]
