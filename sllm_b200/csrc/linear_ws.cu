@@ -1,0 +1,176 @@
+// Weight-streaming linear layer for at most 16 tokens and a modest number of output rows (the
+// attention and down projections of a decode step): y[M, N] = x[M, K] W[N, K]^T.
+//
+// linear_stream.cu gives 128 weight rows to a CTA and, when N is small, splits K over the grid,
+// leaving partial sums for the consumer.  Here a CTA owns 16 output rows over the whole of K and
+// its 8 warps split K among themselves: warp w takes the 32-wide k blocks w, w+8, w+16, ...
+// (so the CTA reads 512 contiguous bytes of each row at a time), four blocks in flight per warp,
+// weights and activations both loaded straight into MMA fragments (same k permutation as in
+// linear_stream.cu), no shared memory and no barrier inside the loop.  At the end the warps'
+// partial tiles are added through shared memory in warp order (a fixed order), and since the CTA
+// holds complete sums the epilogue can finish the layer's job:
+//   store      out[M, N] (+ bias), float32 or bfloat16
+//   residual   residual[M, N] += y (+ bias): the float32 stream is updated in place, so the next
+//              norm has nothing to add
+// N/16 CTAs (224 at N = 3584) keep every SM busy without splitting K over the grid.
+//
+// The reference calls cublasGemmEx for these products and adds the residual in its next
+// add_rms kernel (kernels/cuda/kernels.cu:752-767, 791-839; kernels/device_decode.py:312-325).
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace sllm {
+
+#define WS_EPI_STORE 0
+#define WS_EPI_RESID 1
+
+__device__ __forceinline__ uint4 ws_ldg_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ws_ldg(const void* p) {       // activations: small, shared by all CTAs, keep in L1
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void ws_mma(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                       unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int WS_WARPS = 8;
+constexpr int WS_DEPTH = 4;      // k blocks a warp keeps in flight
+
+// NT: 8-token tiles (M <= 8 * NT).  OUT: float or __nv_bfloat16 (store epilogue only).
+template <int NT, int EPI, typename OUT>
+__global__ void __launch_bounds__(WS_WARPS * 32)
+linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W,
+                 const float* __restrict__ bias, OUT* __restrict__ out, float* __restrict__ residual,
+                 int M, int N, int K) {
+  __shared__ float red[WS_WARPS][16][8 * NT + 1];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int n0 = blockIdx.x * 16;
+  const int k_blocks = K / 32;
+
+  const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);     // rows past N: clamped loads, skipped stores
+  const __nv_bfloat16* w0 = W + (size_t)r0 * K + t4 * 8;
+  const __nv_bfloat16* w1 = W + (size_t)r1 * K + t4 * 8;
+  const __nv_bfloat16* xr[NT];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) xr[j] = x + (size_t)min(8 * j + g, M - 1) * K + t4 * 8;   // tokens past M: clamped, skipped
+
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
+
+  // Two groups of WS_DEPTH k blocks are in flight per warp: while one is multiplied, the loads of
+  // the next (weights and activations) are already under way.  The first weights do not depend
+  // on the step's earlier kernels and are fetched before the wait; the activations after it.
+  uint4 wa0[WS_DEPTH], wb0[WS_DEPTH], wa1[WS_DEPTH], wb1[WS_DEPTH];
+  uint4 x0[WS_DEPTH][NT], x1[WS_DEPTH][NT];
+  auto load_w = [&](uint4 (&wa)[WS_DEPTH], uint4 (&wb)[WS_DEPTH], int kb) {
+#pragma unroll
+    for (int d = 0; d < WS_DEPTH; ++d) {
+      const int b = kb + d * WS_WARPS;
+      if (b < k_blocks) {
+        wa[d] = ws_ldg_stream(w0 + (size_t)b * 32);
+        wb[d] = ws_ldg_stream(w1 + (size_t)b * 32);
+      }
+    }
+  };
+  auto load_x = [&](uint4 (&xv)[WS_DEPTH][NT], int kb) {
+#pragma unroll
+    for (int d = 0; d < WS_DEPTH; ++d) {
+      const int b = kb + d * WS_WARPS;
+      if (b < k_blocks) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j) xv[d][j] = ws_ldg(xr[j] + (size_t)b * 32);
+      }
+    }
+  };
+  auto compute = [&](const uint4 (&wa)[WS_DEPTH], const uint4 (&wb)[WS_DEPTH], const uint4 (&xv)[WS_DEPTH][NT], int kb) {
+#pragma unroll
+    for (int d = 0; d < WS_DEPTH; ++d) {
+      if (kb + d * WS_WARPS < k_blocks) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          ws_mma(acc[j], wa[d].x, wb[d].x, wa[d].y, wb[d].y, xv[d][j].x, xv[d][j].y);
+          ws_mma(acc[j], wa[d].z, wb[d].z, wa[d].w, wb[d].w, xv[d][j].z, xv[d][j].w);
+        }
+      }
+    }
+  };
+  constexpr int GROUP = WS_DEPTH * WS_WARPS;        // k blocks the CTA covers per group
+  int kb = warp;
+  load_w(wa0, wb0, kb);
+  pdl_wait();
+  load_x(x0, kb);
+  for (; kb < k_blocks; kb += 2 * GROUP) {
+    load_w(wa1, wb1, kb + GROUP);
+    load_x(x1, kb + GROUP);
+    compute(wa0, wb0, x0, kb);
+    load_w(wa0, wb0, kb + 2 * GROUP);
+    load_x(x0, kb + 2 * GROUP);
+    compute(wa1, wb1, x1, kb + GROUP);
+  }
+  pdl_launch_dependents();
+
+  // ---- add the warps' tiles in warp order; acc[j][c]: c0,c1 = (row g, tokens 8j+2t, +1); c2,c3 = (row g+8, ...) ----
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) red[warp][g + ((c & 2) ? 8 : 0)][8 * j + 2 * t4 + (c & 1)] = acc[j][c];
+  __syncthreads();
+  for (int idx = tid; idx < 16 * 8 * NT; idx += WS_WARPS * 32) {
+    const int row = idx % 16, tok = idx / 16;           // consecutive threads -> consecutive rows of one token
+    const int n = n0 + row;
+    if (tok >= M || n >= N) continue;
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < WS_WARPS; ++w) v += red[w][row][tok];
+    if (bias) v += bias[n];
+    if constexpr (EPI == WS_EPI_RESID) residual[(size_t)tok * N + n] += v;
+    else out[(size_t)tok * N + n] = from_f32<OUT>(v);
+  }
+}
+
+template <int NT, int EPI, typename OUT>
+static int launch_ws(const __nv_bfloat16* x, const __nv_bfloat16* W, const float* bias, void* out, float* residual,
+                     int M, int N, int K, cudaStream_t stream) {
+  launch_kernel(linear_ws_kernel<NT, EPI, OUT>, (N + 15) / 16, WS_WARPS * 32, 0, stream, x, W, bias, (OUT*)out, residual, M, N, K);
+  return launch_status("linear_ws");
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+SLLM_EXPORT int sllm_linear_ws_supports(int M, int N, int K) {
+  return M >= 1 && M <= 16 && N >= 16 && K >= 32 && K % 32 == 0;
+}
+
+// residual != null: residual[M, N] (float32) += x W^T (+ bias) and `out` is ignored;
+// else out[M, N] = x W^T (+ bias) in out_dtype.
+SLLM_EXPORT int sllm_linear_ws(const void* x, const void* W, const float* bias, void* out, int out_dtype, float* residual,
+                               int M, int N, int K, cudaStream_t stream) {
+  SLLM_REQUIRE(sllm_linear_ws_supports(M, N, K), "linear_ws: sizes M=%d N=%d K=%d (needs M<=16, K%%32==0)", M, N, K);
+  SLLM_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)W & 15) == 0, "linear_ws: operands must be 16-byte aligned");
+  SLLM_REQUIRE(residual != nullptr || out != nullptr, "linear_ws: no destination");
+  const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+  const __nv_bfloat16* wb = (const __nv_bfloat16*)W;
+#define GO(NT_)                                                                                                        \
+  if (residual) return launch_ws<NT_, WS_EPI_RESID, float>(xb, wb, bias, nullptr, residual, M, N, K, stream);          \
+  if (out_dtype == SLLM_BF16) return launch_ws<NT_, WS_EPI_STORE, __nv_bfloat16>(xb, wb, bias, out, nullptr, M, N, K, stream); \
+  return launch_ws<NT_, WS_EPI_STORE, float>(xb, wb, bias, out, nullptr, M, N, K, stream);
+  if (M <= 8) { GO(1) }
+  GO(2)
+#undef GO
+}

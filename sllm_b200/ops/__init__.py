@@ -173,6 +173,42 @@ def gemm_tcgen05(x, w, bias, out_dtype, *, silu: bool = False):
     return out
 
 
+WS_MAX_COLS = 8192        # wider products have CTAs enough for the 128-row streaming kernel
+WS_MAX_ROWS = 8           # with 9..16 tokens its second token tile costs registers and it falls behind
+
+
+def ws_supports(M: int, N: int, K: int) -> bool:
+    return M <= WS_MAX_ROWS and N <= WS_MAX_COLS and bool(lib().sllm_linear_ws_supports(int(M), int(N), int(K)))
+
+
+def linear_ws(x, w, bias, out_dtype, residual=None):
+    """The warp-split streaming kernel (at most 16 tokens): ``x @ w.T (+ bias)`` in ``out_dtype``,
+    or, given ``residual`` (float32 ``[M, N]``), added into it in place (returns None)."""
+    _chk(x, w, bias, residual)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"linear: x {tuple(x.shape)} does not fit w {tuple(w.shape)}")
+    out = None
+    if residual is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    elif residual.dtype != torch.float32 or tuple(residual.shape) != (M, N):
+        raise KernelError(f"linear: residual {tuple(residual.shape)} {residual.dtype} does not fit [{M}, {N}] float32")
+    call("sllm_linear_ws", _p(x), _p(w), _p(bias), _p(out), _dtc(out_dtype), _p(residual), M, N, K, _stream())
+    return out
+
+
+def can_accumulate(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether `linear_accumulate` has a kernel for these operands."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda
+            and ws_supports(x.shape[0], w.shape[0], x.shape[1]))
+
+
+def linear_accumulate(x, w, bias, residual) -> None:
+    """``residual += x @ w.T (+ bias)`` in one kernel (see `can_accumulate`)."""
+    linear_ws(x, w, bias, torch.float32, residual=residual)
+
+
 def _stream_splits(N: int, K: int) -> int:
     ctas = -(-N // 128)
     return max(1, min(2 * NUM_SMS // ctas, K // 128, 16))
@@ -195,6 +231,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype, allow
         raise KernelError("linear: CUDA only")
     M, K = x.shape
     N = w.shape[0]
+    if ws_supports(M, N, K):
+        return linear_ws(x, w, bias, out_dtype)
     if stream_supports(M, N, K):
         splits = _stream_splits(N, K) if (allow_partials and out_dtype == torch.float32) else 1
         return linear_stream(x, w, bias, out_dtype, splits=splits)

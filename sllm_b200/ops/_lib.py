@@ -51,6 +51,8 @@ def _declare(L):
         "sllm_attention_mma_supports": [c_int],
         "sllm_gemm_tcgen05_supports": [c_int, c_int, c_int],
         "sllm_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+        "sllm_linear_ws_supports": [c_int, c_int, c_int],
+        "sllm_linear_ws": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
         "sllm_linear_stream_supports": [c_int, c_int, c_int],
         "sllm_linear_stream_splits": [c_int, c_int],
         "sllm_linear_stream": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,

@@ -20,6 +20,9 @@ Interfaces (all tensors are torch tensors on the engine's device):
                     returns the ``[T, H]`` term to add to the residual stream.
                     ``cache_need()`` says what it wants of the cache manager.
 ``FeedForward``     ``forward(x, step) -> delta``.
+                    A mixer or feed-forward whose class sets ``accepts_residual = True``
+                    is also given ``residual=`` (the float32 stream) and may add its
+                    term into it in place and return None.
 ``Block``           ``forward(residual, delta, step, cache) -> delta``: arranges
                     norms, mixer and feed-forward around the residual stream; the
                     last term is handed on un-added, so that the next norm fuses

@@ -31,6 +31,14 @@ class Linear:
         rows may split its k dimension over more SMs."""
         return ops.linear(x, self.weight, self.bias, out_dtype, allow_partials)
 
+    def into(self, x: torch.Tensor, residual: torch.Tensor | None):
+        """The layer's term for the residual stream: added into ``residual`` in place where a
+        kernel does that (returns None), else returned for the next norm to add."""
+        if residual is not None and ops.can_accumulate(x, self.weight):
+            ops.linear_accumulate(x, self.weight, self.bias, residual)
+            return None
+        return ops.linear(x, self.weight, self.bias, torch.float32, True)
+
     def nbytes(self) -> int:
         n = self.weight.numel() * self.weight.element_size()
         if self.bias is not None:
@@ -141,7 +149,9 @@ class Attention(Mixer):
         ob = self._f32(fetch(f"{on}.bias")) if self.out_bias else None
         self.out = Linear(self._matrix(fetch(f"{on}.weight")), ob)
 
-    def forward(self, x, step: StepContext, cache: LayerCache, position, write_cache=True):
+    accepts_residual = True
+
+    def forward(self, x, step: StepContext, cache: LayerCache, position, write_cache=True, residual=None):
         g = step.groups[cache.group]
         qkv = self.qkv(x, torch.float32, True)                # [T, (nq+2nkv)*hd] float32, maybe in parts
         q = ops.rope_kv_write(
@@ -152,7 +162,7 @@ class Attention(Mixer):
             g.slot_mapping if write_cache else None, cache.k, cache.v, self.dtype)
         o = ops.paged_attention(q, cache.k, cache.v, step, cache.group,
                                 self.nq, self.nkv, self.hd, self.scale, self.window)
-        return self.out(o, torch.float32, True)
+        return self.out.into(o, residual)
 
     def weight_bytes(self):
         return self.qkv.nbytes() + self.out.nbytes() + (self.qkv_b.numel() * 4 if self.qkv_b is not None else 0)
@@ -190,9 +200,11 @@ class SwiGLU(FeedForward):
         self.gate_up = Linear(self._matrix(gu))
         self.down = Linear(self._matrix(fetch(f"{d}.weight")))
 
-    def forward(self, x, step):
+    accepts_residual = True
+
+    def forward(self, x, step, residual=None):
         act = ops.linear_silu_mul(x, self.gate_up.weight, self.interleave, self.dtype)   # [T, I]
-        return self.down(act, torch.float32, True)
+        return self.down.into(act, residual)
 
     def weight_bytes(self):
         return self.gate_up.nbytes() + self.down.nbytes()
@@ -210,6 +222,12 @@ class PreNormBlock:
 
     def forward(self, residual, delta, step, cache, position, write_cache=True):
         x = self.mixer_norm.add_norm(residual, delta)
-        d = self.mixer.forward(x, step, cache, position, write_cache)
+        # a part that says so may add its term into the stream itself and hand back None
+        if getattr(self.mixer, "accepts_residual", False):
+            d = self.mixer.forward(x, step, cache, position, write_cache, residual=residual)
+        else:
+            d = self.mixer.forward(x, step, cache, position, write_cache)
         x = self.ffn_norm.add_norm(residual, d)
+        if getattr(self.ffn, "accepts_residual", False):
+            return self.ffn.forward(x, step, residual=residual)
         return self.ffn.forward(x, step)

@@ -373,3 +373,27 @@ def test_gemm_tcgen05_silu(M, I, K):
     got = ops.gemm_tcgen05(x, gu, None, torch.bfloat16, silu=True)
     ops.check_tcgen05_status()
     torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=1.6e-2)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(16, 32), (100, 96), (3584, 3584), (4608, 3584), (200, 18944), (1000, 320)])
+def test_linear_ws(M, N, K):
+    """The warp-split streaming kernel: stores in both dtypes, and the fused residual add."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(17)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g)
+    want = x.float() @ w.float().t() + b
+    assert ops.ws_supports(min(M, ops.WS_MAX_ROWS), N, K)
+    torch.testing.assert_close(ops.linear_ws(x, w, b, torch.float32), want, rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(ops.linear_ws(x, w, None, torch.bfloat16).float(), want - b, rtol=1.6e-2, atol=1.6e-2)
+    res = torch.randn(M, N, device="cuda", generator=g)
+    expect = res + want
+    assert ops.can_accumulate(x, w) == (M <= ops.WS_MAX_ROWS)
+    ops.linear_accumulate(x, w, b, res)
+    torch.testing.assert_close(res, expect, rtol=2e-3, atol=2e-3)
+    # the sum does not depend on the other tokens of the batch
+    if M > 1:
+        one = ops.linear_ws(x[M - 1:].contiguous(), w, b, torch.float32)
+        assert torch.equal(one[0], ops.linear_ws(x, w, b, torch.float32)[M - 1])

@@ -34,6 +34,14 @@ def linear(x, w, bias, out_dtype, allow_partials=False):
     return out.to(out_dtype)
 
 
+def can_accumulate(x, w):
+    return x.dtype == torch.bfloat16 and x.shape[0] <= 8 and x.shape[1] % 32 == 0 and 16 <= w.shape[0] <= 8192
+
+
+def linear_accumulate(x, w, bias, residual):
+    residual += linear(x, w, bias, torch.float32)
+
+
 def silu_mul(gu, interleave, out_dtype):
     T, two_i = gu.shape
     I = two_i // 2
@@ -120,5 +128,5 @@ def sample_rows(logits, temperature=None, uniform=None):
     return out
 
 
-ALL = ["embed_gather", "add_rmsnorm", "linear", "silu_mul", "linear_silu_mul", "rope_kv_write",
+ALL = ["embed_gather", "add_rmsnorm", "linear", "can_accumulate", "linear_accumulate", "silu_mul", "linear_silu_mul", "rope_kv_write",
        "attention_simt", "paged_attention", "gather_rows", "sample_rows"]
