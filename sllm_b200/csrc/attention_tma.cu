@@ -1,0 +1,456 @@
+// Decode-form attention fed by the tensor memory accelerator.
+//
+// Same arithmetic and the same split-KV scheme as the decode form of attention_mma.cu (16 rows per
+// CTA: a request's one or two tokens times its group of query heads; four warps take 16-key slices
+// of each 64-key tile; partial results per context split, a combine kernel afterwards).  What
+// differs is how keys and values reach shared memory.  There, every thread computes addresses and
+// issues sixteen 16-byte cp.async per tile, and the kernel is bound by those instructions.  Here a
+// fifth warp's one lane issues one TMA box copy per page and 64-column half of a head
+// (cp.async.bulk.tensor.2d over the cache seen as a [pages * kv heads * page size, head size]
+// matrix, 128-byte swizzle); the copies signal an mbarrier per stage, the compute warps read the
+// swizzled tile with ldmatrix and hand the stage back through a second mbarrier.  No thread of the
+// compute warps touches an address of the cache.
+//
+// A whole page is always copied, also where it reaches past the context (its rows are masked by
+// position); slots of a tile that have no page (past the last page, or a page a window gave back)
+// are zero-filled on the stage's first use so that a masked probability of zero never meets an
+// uninitialised value.  Every mbarrier wait is bounded; a wait that runs out records a code in the
+// status word and the CTA leaves through the common exit.
+//
+// Takes head sizes 64 and 128 and page sizes that divide 64; the host falls back to
+// attention_mma.cu otherwise.
+#include <math.h>
+#include <stdio.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "mma.cuh"
+#include "tma.cuh"
+
+namespace sllm {
+
+constexpr int TA_BN = 64;          // keys per tile
+constexpr int TA_STAGES = 3;
+constexpr int TA_THREADS = 160;    // four compute warps and the producer warp
+
+struct AttnTmaParams {
+  const __nv_bfloat16* q;        // [T, nq, HD]
+  __nv_bfloat16* out;            // [T, nq, HD]   (num_splits == 1)
+  float* part_o;                 // [splits, T, nq, HD]
+  float* part_lse;               // [splits, T, nq]
+  const int* block_tables;       // [S, max_pages]
+  const int* q_start;            // [S+1]
+  const int* ctx_len;            // [S]
+  const int* tile_seq;           // [tiles]
+  const int* tile_row0;          // [tiles]
+  int* status;
+  int max_pages, page_size, nq, nkv, window, num_splits, total_tokens;
+  float scale_log2;
+};
+
+// byte offset of the 16-byte chunk `chunk` (of the head's HD/8) of key row `row` within a stage's K or V
+template <int HD>
+__device__ __forceinline__ int swz(int row, int chunk) {
+  return (chunk >> 3) * (TA_BN * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(TA_THREADS)
+attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const AttnTmaParams p) {
+  constexpr int STRIDE = HD + 8;
+  constexpr int KSTEPS = HD / 16;
+  constexpr int DT = HD / 8;
+  constexpr int HALVES = HD / 64;
+  constexpr int KV_BYTES = TA_BN * HD * 2;               // one of K or V of a stage
+  extern __shared__ unsigned char ta_smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(ta_smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* kv_s = smem;                                                    // [STAGES][K | V]
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem + TA_STAGES * 2 * KV_BYTES);   // [16][STRIDE]
+  uint64_t* full = reinterpret_cast<uint64_t*>(q_s + 16 * STRIDE);
+  uint64_t* empty = full + TA_STAGES;
+  volatile int* failed = reinterpret_cast<volatile int*>(empty + TA_STAGES);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  if (tid == 0) {
+    for (int s = 0; s < TA_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 4);                          // the four compute warps
+    }
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_wait();          // the queries, the new keys and values, and the batch description come from earlier work
+
+  const int seq = p.tile_seq[blockIdx.x], row0 = p.tile_row0[blockIdx.x];
+  const int kvh = blockIdx.y, split = blockIdx.z;
+  const int G = p.nq / p.nkv;
+  const int q0 = p.q_start[seq], q_len = p.q_start[seq + 1] - q0, ctx = p.ctx_len[seq];
+  const int rows_total = q_len * G;
+  const int pos0 = ctx - q_len;
+  const int row_hi = min(row0 + 16, rows_total);
+  const int* bt = p.block_tables + (size_t)seq * p.max_pages;
+  const int ps = p.page_size;
+  const int pages_per_tile = TA_BN / ps;
+  const int pages_in_ctx = (ctx + ps - 1) / ps;
+
+  int key_hi = pos0 + (row_hi - 1) / G + 1;
+  int key_lo = 0;
+  if (p.window > 0) key_lo = max(0, pos0 + row0 / G - p.window + 1);
+  if (p.num_splits > 1) {
+    const int chunk = ((ctx + p.num_splits - 1) / p.num_splits + TA_BN - 1) / TA_BN * TA_BN;
+    key_lo = max(key_lo, split * chunk);
+    key_hi = min(key_hi, (split + 1) * chunk);
+  }
+  const int tile0 = key_lo / TA_BN * TA_BN;
+  const int n_tiles = key_hi > tile0 ? (key_hi - tile0 + TA_BN - 1) / TA_BN : 0;
+
+  if (warp == 4) {
+    // ---------------- producer ----------------
+    for (int tile = 0; tile < n_tiles; ++tile) {
+      const int s = tile % TA_STAGES, round = tile / TA_STAGES;
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(&empty[s], (round & 1) ^ 1) && !*failed;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) {
+        if (lane == 0 && !*failed) { *failed = 1; atomicExch(p.status, 11); }
+        break;
+      }
+      unsigned char* ks = kv_s + s * 2 * KV_BYTES;
+      unsigned char* vs = ks + KV_BYTES;
+      const int page0 = (tile0 + tile * TA_BN) / ps;
+      // which slots of the tile have a page to copy (the same answer in every lane)
+      unsigned valid = 0;
+      for (int i = 0; i < pages_per_tile; ++i) {
+        const int pi = page0 + i;
+        if (pi < pages_in_ctx && bt[pi] >= 0) valid |= 1u << i;          // at most 8 pages a tile (page size >= 8)
+      }
+      if (round == 0 && valid != (1u << pages_per_tile) - 1) {
+        // first use of this stage: slots without a page must not hold garbage
+        for (int i = 0; i < pages_per_tile; ++i) {
+          if (valid & (1u << i)) continue;
+          for (int h = 0; h < HALVES; ++h)
+            for (int o = lane * 16; o < ps * 128; o += 32 * 16) {
+              *reinterpret_cast<uint4*>(ks + h * (TA_BN * 128) + i * ps * 128 + o) = make_uint4(0, 0, 0, 0);
+              *reinterpret_cast<uint4*>(vs + h * (TA_BN * 128) + i * ps * 128 + o) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+      }
+      if (lane == 0) {
+        const uint32_t bytes = (uint32_t)__popc(valid) * ps * HD * 2 * 2;
+        if (bytes == 0) {
+          mbar_arrive(&full[s]);
+        } else {
+          mbar_expect_tx(&full[s], bytes);
+          for (int i = 0; i < pages_per_tile; ++i) {
+            if (!(valid & (1u << i))) continue;
+            const int y = (bt[page0 + i] * p.nkv + kvh) * ps;
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) {
+              tma_load_2d(ks + h * (TA_BN * 128) + i * ps * 128, &map_k, h * 64, y, &full[s]);
+              tma_load_2d(vs + h * (TA_BN * 128) + i * ps * 128, &map_v, h * 64, y, &full[s]);
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------- compute warps ----------------
+    // queries: 16 rows of (token, head-in-group)
+    constexpr int CHUNKS = HD / 8;
+    for (int c = tid; c < 16 * CHUNKS; c += 128) {
+      const int r = c / CHUNKS, ch = c % CHUNKS;
+      const int row = row0 + r;
+      const bool okr = row < rows_total;
+      const int tok = okr ? row / G : 0, hg = okr ? row % G : 0;
+      cp_async_16(q_s + r * STRIDE + ch * 8, p.q + ((size_t)(q0 + tok) * p.nq + kvh * G + hg) * HD + ch * 8, okr);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    asm volatile("bar.sync 1, 128;" ::: "memory");          // the four compute warps only
+    unsigned qf[KSTEPS][4];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks)
+      ldmatrix_x4(qf[ks], q_s + (lane & 15) * STRIDE + ks * 16 + (lane >> 4) * 8);
+
+    int hi_r[2], lo_r[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = row0 + g + 8 * i;
+      if (row < rows_total) {
+        const int pos = pos0 + row / G;
+        hi_r[i] = min(pos + 1, key_hi);
+        lo_r[i] = p.window > 0 ? max(key_lo, pos - p.window + 1) : key_lo;
+      } else {
+        hi_r[i] = 0;
+        lo_r[i] = 1;
+      }
+    }
+    float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.f, 0.f};
+    float o[DT][4];
+#pragma unroll
+    for (int d = 0; d < DT; ++d)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o[d][c] = 0.f;
+
+    const int koff = warp * 16;
+    bool alive = true;
+    for (int tile = 0; tile < n_tiles && alive; ++tile) {
+      const int s = tile % TA_STAGES, round = tile / TA_STAGES;
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(&full[s], round & 1) && !*failed;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) {
+        if (lane == 0 && !*failed) { *failed = 2; atomicExch(p.status, 12); }
+        alive = false;
+        break;
+      }
+      const unsigned char* kb = kv_s + s * 2 * KV_BYTES;
+      const unsigned char* vb = kb + KV_BYTES;
+
+      float sc[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sc[n][c] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        unsigned b[4];
+        ldmatrix_x4(b, kb + swz<HD>(koff + (lane >> 4) * 8 + (lane & 7), ks * 2 + ((lane >> 3) & 1)));
+        mma_bf16(sc[0], qf[ks], b[0], b[1]);
+        mma_bf16(sc[1], qf[ks], b[2], b[3]);
+      }
+      const int kbase = tile0 + tile * TA_BN + koff;
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int key = kbase + n * 8 + 2 * t4 + (c & 1);
+          const int i = c >> 1;
+          const float v = (key < hi_r[i] && key >= lo_r[i]) ? sc[n][c] * p.scale_log2 : -INFINITY;
+          sc[n][c] = v;
+          mx[i] = fmaxf(mx[i], v);
+        }
+      float corr[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+        const float m_new = fmaxf(m_r[i], mx[i]);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        corr[i] = exp2f(m_r[i] - m_use);
+        m_r[i] = m_new;
+        mx[i] = m_use;
+        l_r[i] *= corr[i];
+      }
+#pragma unroll
+      for (int d = 0; d < DT; ++d) {
+        o[d][0] *= corr[0]; o[d][1] *= corr[0];
+        o[d][2] *= corr[1]; o[d][3] *= corr[1];
+      }
+      unsigned pf[4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        const float p0 = exp2f(sc[n][0] - mx[0]), p1 = exp2f(sc[n][1] - mx[0]);
+        const float p2 = exp2f(sc[n][2] - mx[1]), p3 = exp2f(sc[n][3] - mx[1]);
+        l_r[0] += p0 + p1;
+        l_r[1] += p2 + p3;
+        pf[n * 2 + 0] = pack_bf16(p0, p1);
+        pf[n * 2 + 1] = pack_bf16(p2, p3);
+      }
+#pragma unroll
+      for (int d = 0; d < DT; d += 2) {
+        unsigned b[4];
+        ldmatrix_x4_trans(b, vb + swz<HD>(koff + (lane & 7) + ((lane >> 3) & 1) * 8, d + (lane >> 4)));
+        mma_bf16(o[d], pf, b[0], b[1]);
+        mma_bf16(o[d + 1], pf, b[2], b[3]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);             // this warp has read the stage
+    }
+
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      l_r[i] += __shfl_xor_sync(0xffffffffu, l_r[i], 1);
+      l_r[i] += __shfl_xor_sync(0xffffffffu, l_r[i], 2);
+    }
+    // the four warps hold partial results for the same 16 rows over different keys: merge them.
+    // The merge buffer lies over the stages, which nobody reads or fills any more once all four warps
+    // are here (every copy that was issued has been waited for).
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    float* mo = reinterpret_cast<float*>(kv_s);                // [4][16][HD]
+    float* mm = mo + 4 * 16 * HD;                              // [4][16] maxima, then [4][16] sums
+    float* ml = mm + 64;
+    static_assert(sizeof(float) * (4 * 16 * HD + 128) <= TA_STAGES * 2 * KV_BYTES, "merge buffer");
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = g + 8 * i;
+#pragma unroll
+      for (int d = 0; d < DT; ++d)
+        *reinterpret_cast<float2*>(mo + (warp * 16 + r) * HD + d * 8 + 2 * t4) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
+      if (t4 == 0) {
+        mm[warp * 16 + r] = m_r[i];
+        ml[warp * 16 + r] = l_r[i];
+      }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (!*failed) {
+      for (int idx = tid; idx < 16 * (HD / 4); idx += 128) {
+        const int r = idx / (HD / 4), d4 = (idx % (HD / 4)) * 4;
+        const int row = row0 + r;
+        if (row >= rows_total) continue;
+        float mt = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mt = fmaxf(mt, mm[w * 16 + r]);
+        float lt = 0.f, f[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          f[w] = ml[w * 16 + r] > 0.f ? exp2f(mm[w * 16 + r] - mt) : 0.f;
+          lt += ml[w * 16 + r] * f[w];
+        }
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const float4 v = *reinterpret_cast<const float4*>(mo + (w * 16 + r) * HD + d4);
+          acc.x += v.x * f[w]; acc.y += v.y * f[w]; acc.z += v.z * f[w]; acc.w += v.w * f[w];
+        }
+        const float inv = lt > 0.f ? 1.f / lt : 0.f;
+        const size_t orow = (size_t)(q0 + row / G) * p.nq + kvh * G + row % G;
+        if (p.num_splits > 1) {
+          float* po = p.part_o + ((size_t)split * p.total_tokens * p.nq + orow) * HD + d4;
+          *reinterpret_cast<float4*>(po) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+          if (d4 == 0) p.part_lse[(size_t)split * p.total_tokens * p.nq + orow] = lt > 0.f ? mt + log2f(lt) : -INFINITY;
+        } else {
+          *reinterpret_cast<uint2*>(p.out + orow * HD + d4) =
+              make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
+        }
+      }
+    }
+  }
+  // common exit: if something gave up, let the copies that were issued land before the shared
+  // memory goes back (bounded), then leave
+  __syncthreads();
+  pdl_launch_dependents();
+  if (*failed && tid == 0) {
+    for (int s = 0; s < TA_STAGES; ++s) mbar_wait(&full[s], 0, 1u << 14);
+  }
+}
+
+template <int HD>
+__global__ void attention_tma_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                             __nv_bfloat16* __restrict__ out, int rows, int num_splits) {
+  pdl_wait();
+  const int row = blockIdx.x;
+  float mt = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) mt = fmaxf(mt, part_lse[(size_t)s * rows + row]);
+  float tot = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float l = part_lse[(size_t)s * rows + row];
+    tot += l == -INFINITY ? 0.f : exp2f(l - mt);
+  }
+  const float inv = tot > 0.f ? 1.f / tot : 0.f;
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float l = part_lse[(size_t)s * rows + row];
+      if (l != -INFINITY) acc += part_o[((size_t)s * rows + row) * HD + d] * exp2f(l - mt);
+    }
+    out[(size_t)row * HD + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+// tensor maps of the caches seen so far: (base, rows, page size, head size) -> map
+struct MapKey {
+  const void* base; long long rows; int ps, hd;
+  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && ps == o.ps && hd == o.hd; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.base) ^ (std::hash<long long>()(k.rows) * 31) ^ (size_t)(k.ps * 131 + k.hd);
+  }
+};
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+static std::mutex g_maps_mutex;
+
+static bool cache_map(const void* base, long long rows, int ps, int hd, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lock(g_maps_mutex);
+  MapKey key{base, rows, ps, hd};
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *out = it->second;
+    return true;
+  }
+  if (rows > 0x7fffffffLL) return false;
+  if (!make_map(out, base, (int)rows, hd, ps)) return false;
+  if (g_maps.size() > 4096) g_maps.clear();
+  g_maps.emplace(key, *out);
+  return true;
+}
+
+template <int HD>
+static int launch_ta(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTmaParams& p, int tiles, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)TA_STAGES * 2 * TA_BN * HD * 2 + 16 * (HD + 8) * 2 + 2 * TA_STAGES * 8 + 16 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_tma_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      set_error("attention_tma: cannot raise the shared memory limit");
+      return SLLM_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  dim3 grid(tiles, p.nkv, p.num_splits);
+  launch_kernel(attention_tma_decode_kernel<HD>, grid, TA_THREADS, smem, stream, mk, mv, p);
+  int rc = launch_status("attention_tma");
+  if (rc != SLLM_OK) return rc;
+  if (p.num_splits > 1) {
+    launch_kernel(attention_tma_combine_kernel<HD>, p.total_tokens * p.nq, HD >= 128 ? 128 : 64, 0, stream,
+                  (const float*)p.part_o, (const float*)p.part_lse, p.out, p.total_tokens * p.nq, p.num_splits);
+    rc = launch_status("attention_tma_combine");
+  }
+  return rc;
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+SLLM_EXPORT int sllm_attention_tma_supports(int hd, int page_size) {
+  // a page's box must start on a 1024-byte boundary of the swizzled tile: page sizes 8, 16, 32, 64
+  return (hd == 64 || hd == 128) && page_size >= 8 && page_size <= 64 && 64 % page_size == 0 && encode_fn() != nullptr;
+}
+
+// The decode form only: every tile holds at most 16 (token, head-in-group) rows.  num_pages: pages in the
+// cache tensors [num_pages, nkv, page_size, hd].  status: one int of device memory, zero before the launch.
+SLLM_EXPORT int sllm_attention_tma_decode(const void* q, const void* k_cache, const void* v_cache, long long num_pages,
+                                          void* out, float* part_o, float* part_lse, const int* block_tables,
+                                          int max_pages, const int* q_start, const int* ctx_len, const int* tile_seq,
+                                          const int* tile_row0, int tiles, int num_splits, int total_tokens, int nq,
+                                          int nkv, int hd, int page_size, float scale, int window, int* status,
+                                          cudaStream_t stream) {
+  SLLM_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tma: bad head counts nq=%d nkv=%d", nq, nkv);
+  SLLM_REQUIRE(sllm_attention_tma_supports(hd, page_size), "attention_tma: head_dim=%d page_size=%d not taken", hd, page_size);
+  SLLM_REQUIRE(max_pages > 0 && tiles >= 0 && total_tokens >= 0 && num_pages > 0, "attention_tma: bad sizes");
+  SLLM_REQUIRE(num_splits >= 1 && num_splits <= 65535 && nkv <= 65535, "attention_tma: bad grid nkv=%d splits=%d", nkv, num_splits);
+  SLLM_REQUIRE(num_splits == 1 || (part_o && part_lse), "attention_tma: split-KV needs scratch");
+  SLLM_REQUIRE(status != nullptr, "attention_tma: a status word is required");
+  SLLM_REQUIRE(((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0, "attention_tma: the cache must be 16-byte aligned");
+  if (tiles == 0) return SLLM_OK;
+  CUtensorMap mk, mv;
+  const long long rows = num_pages * nkv * page_size;
+  if (!cache_map(k_cache, rows, page_size, hd, &mk) || !cache_map(v_cache, rows, page_size, hd, &mv)) {
+    set_error("attention_tma: cuTensorMapEncodeTiled failed");
+    return SLLM_ERR_LAUNCH;
+  }
+  AttnTmaParams p;
+  p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.part_o = part_o; p.part_lse = part_lse;
+  p.block_tables = block_tables; p.q_start = q_start; p.ctx_len = ctx_len; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
+  p.status = status; p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.window = window;
+  p.num_splits = num_splits; p.total_tokens = total_tokens; p.scale_log2 = scale * 1.4426950408889634f;
+  return hd == 128 ? launch_ta<128>(mk, mv, p, tiles, stream) : launch_ta<64>(mk, mv, p, tiles, stream);
+}

@@ -166,4 +166,6 @@ class DecodeGraphs:
         for e, t in zip(entries, totals):
             cache.commit(e.req_id, t)
         eng.steps_run += 1
+        if eng.steps_run % 64 == 0:
+            ops.check_tcgen05_status()      # a wait that ran out inside a TMA-fed kernel, if any
         return out

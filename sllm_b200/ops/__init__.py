@@ -134,8 +134,8 @@ def _status_word(device) -> torch.Tensor:
 
 
 def check_tcgen05_status() -> None:
-    """Raise if a bounded wait inside a tcgen05 kernel gave up since the last check (reads one
-    int from each device that ran such a kernel; synchronises)."""
+    """Raise if a bounded wait inside a TMA-fed kernel (the tcgen05 product, the TMA attention) gave
+    up since the last check (reads one int from each device that ran such a kernel; synchronises)."""
     if not _tc_used["since_check"]:
         return
     _tc_used["since_check"] = 0
@@ -143,8 +143,9 @@ def check_tcgen05_status() -> None:
         code = int(t.item())
         if code:
             t.zero_()
-            who = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, f"code {code}")
-            raise KernelError(f"gemm_tcgen05 on {dev}: a wait of {who} ran out; the product is not valid")
+            who = {1: "gemm_tcgen05: the TMA producer", 2: "gemm_tcgen05: the MMA issuer", 3: "gemm_tcgen05: the epilogue",
+                   11: "attention_tma: the producer", 12: "attention_tma: a compute warp"}.get(code, f"code {code}")
+            raise KernelError(f"{who} on {dev}: a bounded wait ran out; the result is not valid")
 
 
 def tcgen05_supports(M: int, N: int, K: int) -> bool:
@@ -375,6 +376,33 @@ def attention_mma(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, de
     return out
 
 
+def tma_attention_supports(hd: int, page_size: int) -> bool:
+    return bool(lib().sllm_attention_tma_supports(int(hd), int(page_size)))
+
+
+def attention_tma_decode(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, num_splits: int,
+                         nq, nkv, hd, scale, window, out=None):
+    """The decode form fed by TMA (16-row tiles only; see `attention_tiles`)."""
+    _chk(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles[0], tiles[1])
+    if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
+        raise KernelError("attention_tma: bfloat16 only")
+    T = q.shape[0]
+    if out is None:
+        out = torch.empty_like(q)
+    part_o = part_lse = None
+    if num_splits > 1:
+        part_o = torch.empty((num_splits, T, nq, hd), dtype=torch.float32, device=q.device)
+        part_lse = torch.empty((num_splits, T, nq), dtype=torch.float32, device=q.device)
+    call("sllm_attention_tma_decode", _p(q), _p(k_cache), _p(v_cache), k_cache.shape[0], _p(out), _p(part_o),
+         _p(part_lse), _p(block_tables), block_tables.shape[1], _p(q_start), _p(ctx_len), _p(tiles[0]), _p(tiles[1]),
+         tiles[2], num_splits, T, nq, nkv, hd, k_cache.shape[2], float(scale), int(window or 0),
+         _p(_status_word(q.device)), _stream())
+    _tc_used["since_check"] += 1
+    if num_splits > 1:
+        launches["own"] += 1
+    return out
+
+
 def mma_supports(hd: int) -> bool:
     return bool(lib().sllm_attention_mma_supports(int(hd)))
 
@@ -395,7 +423,10 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
         step.attn_tiles[key] = (small, large, splits)
     small, large, splits = step.attn_tiles[key]
     out = torch.empty_like(q)
-    if small:
+    if small and tma_attention_supports(hd, k_cache.shape[2]):
+        attention_tma_decode(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, splits,
+                             nq, nkv, hd, scale, window, out)
+    elif small:
         attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, True, splits,
                       nq, nkv, hd, scale, window, out)
     if large:

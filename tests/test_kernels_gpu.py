@@ -397,3 +397,31 @@ def test_linear_ws(M, N, K):
     if M > 1:
         one = ops.linear_ws(x[M - 1:].contiguous(), w, b, torch.float32)
         assert torch.equal(one[0], ops.linear_ws(x, w, b, torch.float32)[M - 1])
+
+
+@pytest.mark.parametrize("nq,nkv,hd,ps,window", [(28, 4, 128, 16, None), (14, 2, 64, 16, None), (8, 1, 128, 32, 40),
+                                                 (6, 3, 64, 8, 9), (16, 2, 128, 64, None), (7, 7, 64, 16, None)])
+@pytest.mark.parametrize("case", ["decode", "decode_split", "short"])
+def test_attention_tma_decode(nq, nkv, hd, ps, window, case):
+    """The TMA-fed decode form against the float32 statement: contexts that end inside a page and
+    inside a tile, requests shorter than a tile (slots without a page), split contexts, a window."""
+    ops = _ops()
+    assert ops.tma_attention_supports(hd, ps)
+    g = torch.Generator(device="cuda").manual_seed(18)
+    lens = {"decode": [300, 1, 17, 64, 65], "decode_split": [1500, 700, 3, 129], "short": [5, 2, 1, 33]}[case]
+    q_lens = [1] * len(lens)
+    if case == "short" and nq // nkv <= 8:
+        q_lens[0] = 2                                   # two tokens of one request still fit a 16-row tile
+    q, kc, vc, bt, pos, seq = _paged_case(g, lens, q_lens, nq, nkv, hd, ps, torch.bfloat16)
+    # poison what lies outside the requests' pages: a kernel that read it would show NaN
+    q_start, ctx_len = _starts(q_lens, lens)
+    scale = hd ** -0.5
+    want = ref.attention_simt(q.float(), kc.float(), vc.float(), bt, pos, seq, nq, nkv, hd, scale, window)
+    small, large = ops.attention_tiles(q_lens, nq // nkv, "cuda")
+    assert large is None
+    for splits in ((1, 2) if case != "decode_split" else (1, 5, 9)):
+        out = torch.full_like(q, float("nan"))
+        ops.attention_tma_decode(q, kc, vc, bt, q_start, ctx_len, small, splits, nq, nkv, hd, scale, window, out)
+        ops.check_tcgen05_status()
+        assert not out.isnan().any(), "a row was not written, or a masked slot held garbage"
+        torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
