@@ -127,9 +127,10 @@ class DeviceTimer:
         self.pairs.append((self._open, ev))
         self._open = None
 
-    def total_ms(self):
+    def total_ms(self, first=None):
+        """Device time of the first ``first`` bracketed parts (all by default)."""
         self.torch.cuda.synchronize()
-        return sum(a.elapsed_time(b) for a, b in self.pairs)
+        return sum(a.elapsed_time(b) for a, b in self.pairs[:first])
 
 
 def flops_of_step(cfg, tokens_per_req, ctx_before, logits_rows):
@@ -181,7 +182,7 @@ def decode_run(model, cfg, batch, context, steps, warmup, seed=0, graphs=True):
         assert len(sampled) == batch
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
-    dev_ms = timer.total_ms()
+    dev_ms = timer.total_ms(steps)        # a step queued ahead of the last one read is not among the K
     clk = clocks.stop()
     launches = {k: ops.launches[k] - before[k] for k in before}
     # bytes the step has to read: every weight once, and the live requests' cache

@@ -194,13 +194,17 @@ class Engine:
         return logits
 
     # ---- decoding through a captured graph -------------------------------------------------
-    def decode_graph_step(self, entries, temperatures, uniforms, device_timer=None):
-        """One decode step (every entry brings one token and wants its logits) replayed from a
-        CUDA graph of the model's forward and the sampling kernel.  The first step of a given
-        batch size and context bucket runs eagerly on the graph's static buffers and is then
-        captured; later ones copy the batch description into those buffers and replay.
-        Returns the sampled ids (int32 tensor on the device, static)."""
+    @property
+    def graphs(self):
+        """CUDA graphs of the decode step (forward and sampling kernel), one per batch size and
+        context bucket: the first step of a kind runs eagerly on the graph's static buffers and is
+        then captured; later ones copy the batch description into those buffers and replay."""
         from .graphs import DecodeGraphs
         if self._graphs is None:
             self._graphs = DecodeGraphs(self)
-        return self._graphs.step(list(entries), temperatures, uniforms, device_timer)
+        return self._graphs
+
+    def decode_graph_step(self, entries, temperatures, uniforms, device_timer=None):
+        """One decode step (every entry brings one token and wants its logits) through a graph.
+        Returns the sampled ids (int32 tensor on the host)."""
+        return self.graphs.step(list(entries), temperatures, uniforms, device_timer)

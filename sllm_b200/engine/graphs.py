@@ -40,15 +40,24 @@ class _Graph:
         for k, n in sizes.items():
             self.offs[k] = (total, n)
             total += _pad4(n)
-        self.host = torch.zeros(total, dtype=torch.int32, pin_memory=engine.device.type == "cuda")
+        # two host staging buffers: a step may be filled while the copy of the one before is still queued
+        pin = engine.device.type == "cuda"
+        self.hosts = [torch.zeros(total, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self.ids_host = [torch.zeros(B, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self.ids_ready = [torch.cuda.Event() if pin else None for _ in range(2)]
+        self.turn = 0
+        self.host = self.hosts[0]
         self.h = self.host.numpy()
         self.dev = torch.zeros(total, dtype=torch.int32, device=engine.device)
         # what never changes in a decode step
-        self._hsec("seq_of_token")[:] = np.arange(B)
-        self._hsec("q_start")[:] = np.arange(B + 1)
-        self._hsec("logit_rows")[:] = np.arange(B)
-        for gi in range(G):
-            self._hsec(f"block_tables{gi}")[:] = -1
+        for hb in self.hosts:
+            self.h = hb.numpy()
+            self._hsec("seq_of_token")[:] = np.arange(B)
+            self._hsec("q_start")[:] = np.arange(B + 1)
+            self._hsec("logit_rows")[:] = np.arange(B)
+            for gi in range(G):
+                self._hsec(f"block_tables{gi}")[:] = -1
+        self.h = self.host.numpy()
         groups = [GroupView(ps, self._dsec(f"block_tables{gi}").view(B, self.cap_pages), self._dsec(f"slot_mapping{gi}"))
                   for gi in range(G)]
         self.ctx = StepContext(
@@ -70,14 +79,20 @@ class _Graph:
         o, n = self.offs[k]
         return self.dev[o:o + n]
 
-    def fill(self, engine, entries, totals, temperatures, uniforms):
+    def fill(self, engine, entries, totals, temperatures, uniforms, tokens_on_device: bool = False):
+        """Describe the step in the next host buffer and queue its copy to the device.  With
+        ``tokens_on_device`` the token ids are not the host's to give: they are the ids the graph's
+        previous replay sampled, copied on the device."""
+        self.turn ^= 1
+        self.host = self.hosts[self.turn]
+        self.h = self.host.numpy()
         cache = engine.cache
         ps = cache.page_size
         B = self.B
         tok, pos, ctx, slots = (self._hsec(k) for k in ("token_ids", "positions", "ctx_len", "state_slots"))
         for i, (e, tot) in enumerate(zip(entries, totals)):
             req = cache.requests[e.req_id]
-            tok[i] = e.tokens[0]
+            tok[i] = e.tokens[0] if not tokens_on_device else 0
             pos[i] = tot - 1
             ctx[i] = tot
             slots[i] = req.slot
@@ -95,6 +110,15 @@ class _Graph:
         self._hsec("temps").view(np.float32)[:] = temperatures
         self._hsec("uniforms").view(np.float64)[:] = uniforms
         self.dev.copy_(self.host, non_blocking=True)
+        if tokens_on_device:
+            self._dsec("token_ids").copy_(self.ids)          # after the host's copy, before the replay
+
+
+class Launched:
+    """A decode step that has been queued on the device and whose ids have not been read yet."""
+
+    def __init__(self, graph, turn, ids_now=None):
+        self.graph, self.turn, self.ids_now = graph, turn, ids_now
 
 
 class DecodeGraphs:
@@ -110,6 +134,31 @@ class DecodeGraphs:
         return b
 
     def step(self, entries, temperatures, uniforms, device_timer=None):
+        """Launch and read one decode step (see `launch`, `read`)."""
+        h = self.launch(entries, temperatures, uniforms, device_timer=device_timer)
+        return torch.tensor(self.read(h), dtype=torch.int32)
+
+    def can_chain(self, entries) -> bool:
+        """Whether a step for these requests, one token further each, can be queued behind the
+        step in flight with its token ids taken from that step's samples on the device: the same
+        requests in the same order, a graph already captured for their number and context bucket,
+        and pages at hand."""
+        eng, cache = self.engine, self.engine.cache
+        totals = []
+        for e in entries:
+            req = cache.requests.get(e.req_id)
+            if req is None or req.num_tokens + 1 > eng.max_positions:
+                return False
+            totals.append(req.num_tokens + 1)
+        gr = self.graphs.get((len(entries), self.bucket(max(totals))))
+        if gr is None or gr.graph is None:
+            return False
+        return all(cache.can_reserve(e.req_id, t) for e, t in zip(entries, totals))
+
+    def launch(self, entries, temperatures, uniforms, device_timer=None, tokens_on_device: bool = False) -> Launched:
+        """Queue one decode step: reserve pages, describe the batch, replay the graph, queue the copy
+        of the sampled ids to pinned host memory.  Does not wait for the device, except the first
+        time a (batch size, context bucket) is seen: that step runs eagerly and is then captured."""
         eng = self.engine
         cache = eng.cache
         totals = []
@@ -123,7 +172,7 @@ class DecodeGraphs:
             if tot > eng.max_positions:
                 from .engine import ContextOverflow
                 raise ContextOverflow(f"request {e.req_id!r}: {tot} tokens exceed max positions {eng.max_positions}")
-            if not 0 <= int(e.tokens[0]) < eng.vocab_size:
+            if not tokens_on_device and not 0 <= int(e.tokens[0]) < eng.vocab_size:
                 raise ValueError(f"request {e.req_id!r}: token id {e.tokens[0]} is outside the vocabulary")
             totals.append(tot)
         # pages: all or nothing
@@ -139,33 +188,46 @@ class DecodeGraphs:
         gr = self.graphs.get(key)
         if gr is None:
             gr = self.graphs[key] = _Graph(eng, *key)
-        gr.fill(eng, entries, totals, temperatures, uniforms)
+        if tokens_on_device and gr.graph is None:
+            raise RuntimeError("a chained step needs a captured graph (see can_chain)")
+        gr.fill(eng, entries, totals, temperatures, uniforms, tokens_on_device)
         if device_timer is not None:
             device_timer.start()
+        ids_now = None
         if gr.graph is None:
             # first use: run eagerly on the static buffers (this step's result), then capture
             before = ops.launches["own"]
             logits = eng.model.forward(gr.ctx, eng.layer_caches)
             gr.ids = ops.sample_rows(logits, gr.temps, gr.uniforms)
             gr.launches = ops.launches["own"] - before
-            ids_now = gr.ids.clone()
-            torch.cuda.synchronize()
+            ids_now = gr.ids.cpu().tolist()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 logits = eng.model.forward(gr.ctx, eng.layer_caches)
                 gr.ids = ops.sample_rows(logits, gr.temps, gr.uniforms)
             ops.launches["own"] -= gr.launches          # capturing launched nothing
             gr.graph = graph
-            out = ids_now
+            # the graph's own output buffer must hold this step's ids for a step chained behind it
+            gr.ids.copy_(torch.tensor(ids_now, dtype=torch.int32, device=eng.device))
         else:
             gr.graph.replay()
             ops.launches["own"] += gr.launches
-            out = gr.ids
+            gr.ids_host[gr.turn].copy_(gr.ids, non_blocking=True)
+            gr.ids_ready[gr.turn].record()
         if device_timer is not None:
             device_timer.stop()
         for e, t in zip(entries, totals):
             cache.commit(e.req_id, t)
         eng.steps_run += 1
-        if eng.steps_run % 64 == 0:
+        return Launched(gr, gr.turn, ids_now)
+
+    def read(self, h: Launched) -> list:
+        """The ids a launched step sampled (waits for that step, not for any queued behind it)."""
+        if h.ids_now is not None:
+            out = h.ids_now
+        else:
+            h.graph.ids_ready[h.turn].synchronize()
+            out = h.graph.ids_host[h.turn].tolist()
+        if self.engine.steps_run % 64 == 0:
             ops.check_tcgen05_status()      # a wait that ran out inside a TMA-fed kernel, if any
         return out

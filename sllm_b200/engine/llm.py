@@ -55,7 +55,7 @@ class LLM:
                  block_size: int = 16, num_pages: int | None = None, kv_utilization: float = 0.9,
                  kv_bytes: int | None = None, max_num_seqs: int = 8, max_batch_tokens: int = 2048,
                  chunk_size: int = 512, max_model_len: int | None = None, policy: str = "reserve",
-                 cuda_graphs: bool = True, progress=None):
+                 cuda_graphs: bool = True, pipeline_decode: bool = True, progress=None):
         if (model_dir is None) == (model is None):
             raise ValueError("give a model folder or a built model")
         if model is None:
@@ -71,6 +71,8 @@ class LLM:
                                    max_batch_tokens=max_batch_tokens, chunk_size=chunk_size, policy=policy)
         self.sampler = Sampler(model.device)
         self.cuda_graphs = bool(cuda_graphs) and model.device.type == "cuda"
+        self.pipeline_decode = self.cuda_graphs and bool(pipeline_decode)
+        self._inflight = None
         self._next_id = 0
         self.steps = 0
 
@@ -87,36 +89,80 @@ class LLM:
     def step(self, device_timer=None):
         """Schedule, run and sample one step.  Returns (finished requests, new tokens by request).
         ``device_timer``: an object whose ``start()``/``stop()`` are called around the part of
-        the step that runs on the device (measurement only)."""
+        the step that runs on the device (measurement only).
+
+        Pure decode steps run from a CUDA graph and are pipelined: while the device runs one, the
+        next is already queued behind it with its token ids taken on the device from the first
+        one's samples, and only then does the host wait for the first one's ids.  The host's
+        scheduling and bookkeeping thus overlap the device's work.  The queued step assumes that
+        no request stops; one that does (a stop id) has a token computed in vain, which is dropped.
+        """
         sched = self.scheduler
-        plan = sched.schedule()
-        if not plan:
-            if sched.has_work:
-                # serving/executor.py:1094-1099: requests remain but nothing can be scheduled
-                raise RuntimeError("scheduler stalled: requests remain but none can be scheduled "
-                                   "(the cache cannot hold the next one)")
-            return [], {}
-        entries = [StepEntry(p.req.req_id, p.req.tokens[p.start:p.start + p.count],
-                             [p.count - 1] if p.sample else []) for p in plan]
-        rows = [(p.req.params, p.req.rng, p.req.tokens if not p.req.params.on_device else None)
-                for p in plan if p.sample]
-        if self.cuda_graphs and all(p.count == 1 and p.sample and p.req.params.on_device for p in plan):
+        if self._inflight is None:
+            plan = sched.schedule()
+            if not plan:
+                if sched.has_work:
+                    # serving/executor.py:1094-1099: requests remain but nothing can be scheduled
+                    raise RuntimeError("scheduler stalled: requests remain but none can be scheduled "
+                                       "(the cache cannot hold the next one)")
+                return [], {}
+            entries = [StepEntry(p.req.req_id, p.req.token_slice(p.start, p.count),
+                                 [p.count - 1] if p.sample else []) for p in plan]
+            rows = [(p.req.params, p.req.rng, p.req.tokens if not p.req.params.on_device else None)
+                    for p in plan if p.sample]
+            if not (self.cuda_graphs and all(p.count == 1 and p.sample and p.req.params.on_device for p in plan)):
+                ctx = self.engine.prepare(entries)
+                if device_timer is not None:
+                    device_timer.start()
+                logits = self.engine.run(ctx, entries)
+                ids = self.sampler.sample(logits, rows, device_timer=device_timer)
+                sampled = {p.req.req_id: t for p, t in zip((p for p in plan if p.sample), ids)}
+                finished = sched.update(plan, sampled)
+                self.steps += 1
+                return finished, sampled
             # a pure decode step: replayed from a captured graph, sampling included
             temps, unis = self.sampler.host_inputs(rows)
-            ids = self.engine.decode_graph_step(entries, temps, unis, device_timer).cpu().tolist()
-            sampled = {p.req.req_id: int(t) for p, t in zip(plan, ids)}
-            finished = sched.update(plan, sampled)
-            self.steps += 1
-            return finished, sampled
-        ctx = self.engine.prepare(entries)
-        if device_timer is not None:
-            device_timer.start()
-        logits = self.engine.run(ctx, entries)
-        ids = self.sampler.sample(logits, rows, device_timer=device_timer)
-        sampled = {p.req.req_id: t for p, t in zip((p for p in plan if p.sample), ids)}
+            handle = self.engine.graphs.launch(entries, temps, unis, device_timer=device_timer)
+            self._inflight = (plan, handle)
+        plan, handle = self._inflight
+        self._inflight = self._chain(plan, device_timer)
+        ids = self.engine.graphs.read(handle)
+        sampled = {p.req.req_id: int(t) for p, t in zip(plan, ids) if p.req.status == "running"}
         finished = sched.update(plan, sampled)
         self.steps += 1
         return finished, sampled
+
+    def _chain(self, plan, device_timer):
+        """Queue the decode step after ``plan``'s behind it, if nothing can change who runs: no
+        request waits for admission, none of the plan's requests ends by length with this token,
+        and the graph and the pages are there.  Returns (next plan, handle) or None."""
+        sched = self.scheduler
+        if not self.pipeline_decode or sched.waiting or len(plan) != len(sched.running):
+            return None
+        for p in plan:
+            r = p.req
+            if (r.status != "running" or len(r.output) + 1 >= r.params.max_new
+                    or r.num_tokens + 1 >= sched.max_positions):
+                return None
+        entries = [StepEntry(p.req.req_id, [0], [0]) for p in plan]
+        if not self.engine.graphs.can_chain(entries):
+            return None
+        rows = [(p.req.params, p.req.rng, None) for p in plan]
+        temps, unis = self.sampler.host_inputs(rows)
+        handle = self.engine.graphs.launch(entries, temps, unis, device_timer=device_timer, tokens_on_device=True)
+        from .scheduler import Planned
+        nxt = [Planned(p.req, p.start + 1, 1, True) for p in plan]
+        return nxt, handle
+
+    def drain(self) -> None:
+        """Wait for a decode step still queued on the device and drop its result (its requests
+        have all ended)."""
+        if self._inflight is not None:
+            plan, handle = self._inflight
+            self._inflight = None
+            self.engine.graphs.read(handle)
+            if any(p.req.status == "running" for p in plan):
+                raise RuntimeError("a decode step in flight was dropped while its requests still run")
 
     # ---- batch interface -------------------------------------------------------------------
     def generate(self, prompt_token_ids, params=None) -> list[GenerationResult]:
@@ -130,4 +176,6 @@ class LLM:
         reqs = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
         while any(r.status != "finished" for r in reqs):
             self.step()
+        if not self.scheduler.has_work:
+            self.drain()
         return [GenerationResult(r.req_id, r.prompt, list(r.output), r.finish_reason, r.preemptions) for r in reqs]

@@ -53,6 +53,20 @@ class Request:
         return self.prompt + self.output
 
     @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    def token_slice(self, start: int, count: int) -> list:
+        """``tokens[start:start+count]`` without building the whole list (a decode step asks for
+        the last token of thousands)."""
+        n = len(self.prompt)
+        if start >= n:
+            return self.output[start - n:start - n + count]
+        if start + count <= n:
+            return self.prompt[start:start + count]
+        return self.prompt[start:] + self.output[:start + count - n]
+
+    @property
     def pending(self) -> int:
         return len(self.prompt) + len(self.output) - self.num_computed
 
@@ -135,7 +149,7 @@ class Scheduler:
                 n = self._take_pages(r, n, plan, planned_ids)
                 if n <= 0:
                     continue
-                plan.append(Planned(r, r.num_computed, n, r.num_computed + n == len(r.tokens)))
+                plan.append(Planned(r, r.num_computed, n, r.num_computed + n == r.num_tokens))
                 planned_ids.add(r.req_id)
                 budget -= n
         # admission (pump): skip what does not fit, keep its place
@@ -154,7 +168,7 @@ class Scheduler:
             self.cache.reserve(r.req_id, total)
             r.status = "running"
             self.running.append(r)
-            plan.append(Planned(r, r.num_computed, n, r.num_computed + n == len(r.tokens)))
+            plan.append(Planned(r, r.num_computed, n, r.num_computed + n == r.num_tokens))
             planned_ids.add(r.req_id)
             budget -= n
         self.waiting.extendleft(reversed(skipped))
@@ -169,7 +183,8 @@ class Scheduler:
             if r.status != "running":
                 continue
             r.num_computed += p.count
-            self.cache.commit(r.req_id, r.num_computed)
+            if self.cache.requests[r.req_id].num_tokens < r.num_computed:   # the engine may be a queued step ahead
+                self.cache.commit(r.req_id, r.num_computed)
             if not p.sample:
                 continue
             tok = int(sampled[r.req_id])
@@ -177,7 +192,7 @@ class Scheduler:
                 self._finish(r, "stop")
             else:
                 r.output.append(tok)
-                if len(r.output) >= r.params.max_new or len(r.tokens) >= self.max_positions:
+                if len(r.output) >= r.params.max_new or r.num_tokens >= self.max_positions:
                     self._finish(r, "length")                  # serving/executor.py:388-389
             if r.status == "finished":
                 finished.append(r)

@@ -307,3 +307,32 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     finally:
         unregister_architecture("ToyStateLM")
         MIXERS.unregister("toy_decay_state")
+
+
+def test_pipelined_decode_equals_unpipelined(tiny):
+    """Decode steps queued one ahead of the host (token ids chained on the device) give exactly the
+    tokens of the step-by-step path: greedy and sampled, with stop ids that end requests while a
+    step computed for them is already queued, and with requests joining and leaving."""
+    from sllm_b200.engine import build_model
+    from sllm_b200.engine.llm import LLM
+    from sllm_b200.sampling import SamplingParams
+    dev = cuda_or_skip()
+    name, model_dir, page = tiny
+    cfg, w = plain.load_model(model_dir)
+    model, _ = build_model(model_dir, "float32", dev)
+    prompts = _prompts(cfg, (5, 17, 33, 9, 2), seed=12)
+    first = plain.generate(prompts[1], 6, w, cfg)
+    params = [SamplingParams(max_new=20), SamplingParams(max_new=30, stop_ids=(first[5],)),
+              SamplingParams(max_new=11, temperature=0.7, seed=3), SamplingParams(max_new=25, temperature=1.1, seed=4),
+              SamplingParams(max_new=7)]
+    outs = []
+    for pipelined in (False, True):
+        llm = LLM(model=model, block_size=page, num_pages=64, max_num_seqs=3, chunk_size=24, pipeline_decode=pipelined)
+        res = llm.generate(prompts, params)
+        outs.append([(r.ids, r.finish_reason) for r in res])
+        llm.engine.cache.check()
+        assert not llm.engine.cache.requests and llm._inflight is None
+    assert outs[0] == outs[1]
+    assert outs[0][0][0] == plain.generate(prompts[0], 20, w, cfg)
+    assert outs[0][1] == (first[:first.index(first[5])], "stop")     # ends at the stop id's first appearance
+    assert outs[0][2][0] == plain.generate(prompts[2], 11, w, cfg, temperature=0.7, seed=3)
