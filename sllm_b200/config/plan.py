@@ -65,6 +65,7 @@ class ModelPlan:
     final_norm_name: str
     head_name: str | None          # None: the head is the embedding table (tied)
     position: PartSpec | None      # the position encoding the mixers share
+    position_name: str | None = None   # prefix of the position encoding's own tensors, if it has any
 
     def validate(self) -> None:
         from .errors import ConfigError

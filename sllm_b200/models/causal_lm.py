@@ -52,6 +52,8 @@ class CausalLM:
         for layer in self.layers:
             out.extend(layer.named_parts())
         out.append((self.plan.final_norm_name, self.final_norm))
+        if self.position is not None and self.plan.position_name:
+            out.append((self.plan.position_name, self.position))
         return out
 
     def tensor_specs(self) -> list[TensorSpec]:
@@ -105,6 +107,8 @@ class CausalLM:
         """Run the batch's tokens through every entry of the run list and return
         float32 logits ``[R, V]`` at ``step.logit_rows``."""
         residual = ops.embed_gather(self.embedding, step.token_ids)       # [T, H] float32
+        if self.position is not None:
+            self.position.on_embedding(residual, step)
         delta = None
         for i, e in enumerate(self.plan.run_list):
             layer = self.layers[e.layer]

@@ -12,7 +12,8 @@ Interfaces (all tensors are torch tensors on the engine's device):
                     float32 stream ``[T, H]``; if ``delta`` is given it is added
                     into ``residual`` in place first; the normed copy comes back
                     in the compute dtype.
-``PositionEncoding`` owns what mixers need to encode positions (tables).
+``PositionEncoding`` owns what encodes positions: tables the mixers apply (rotary), or
+                    ``on_embedding(residual, step)`` for encodings added to the input.
 ``Mixer``           ``forward(x, step, cache, position, write_cache) -> delta``:
                     ``x`` normed ``[T, H]``; ``step`` the batch description
                     (`StepContext`); ``cache`` the run's `LayerCache` (paged
@@ -200,4 +201,9 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    pass
+    """Owns what encodes positions.  Mixers receive the object (rotary encodings expose ``table``
+    and ``rotary_dim``, which the attention mixer applies to queries and keys); an encoding that
+    acts on the input instead overrides `on_embedding`."""
+
+    def on_embedding(self, residual, step: StepContext) -> None:
+        """Called once per step on the float32 stream right after the embedding lookup."""

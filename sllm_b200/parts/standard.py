@@ -156,8 +156,8 @@ class Attention(Mixer):
         qkv = self.qkv(x, torch.float32, True)                # [T, (nq+2nkv)*hd] float32, maybe in parts
         q = ops.rope_kv_write(
             qkv, self.qkv_b, step.positions,
-            position.table if position is not None else None,
-            position.rotary_dim if position is not None else 0,
+            getattr(position, "table", None),          # an encoding without a rotary table: no rotation
+            getattr(position, "rotary_dim", 0) if getattr(position, "table", None) is not None else 0,
             self.nq, self.nkv, self.hd,
             g.slot_mapping if write_cache else None, cache.k, cache.v, self.dtype)
         o = ops.paged_attention(q, cache.k, cache.v, step, cache.group,

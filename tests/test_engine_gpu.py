@@ -336,3 +336,188 @@ def test_pipelined_decode_equals_unpipelined(tiny):
     assert outs[0][0][0] == plain.generate(prompts[0], 20, w, cfg)
     assert outs[0][1] == (first[:first.index(first[5])], "stop")     # ends at the stop id's first appearance
     assert outs[0][2][0] == plain.generate(prompts[2], 11, w, cfg, temperature=0.7, seed=3)
+
+
+def test_toy_routed_feed_forward_and_learned_positions(tmp_path):
+    """Two more parts defined here and nowhere in the package: a feed-forward that routes each
+    token to one of four small experts (router logits and their softmax in float32), and a position
+    encoding that is a learned table added to the embeddings (the attention then rotates nothing).
+    Registered, given tensors by the random-weights writer, built through the registry, stepped in
+    portions and one token at a time, and compared with a plain numpy statement of the same model."""
+    from sllm_b200.config import (Architecture, LayerSpec, ModelPlan, PartSpec, RunEntry, register_architecture,
+                                  unregister_architecture)
+    from sllm_b200.engine import Engine, StepEntry, build_model
+    from sllm_b200.models.qwen2 import Qwen2Config
+    from sllm_b200.models.qwen2 import plan as qwen2_plan
+    from sllm_b200.parts import FEED_FORWARDS, POSITIONS, FeedForward, PositionEncoding, TensorSpec
+    from sllm_b200.weights import write_random_model
+    dev = cuda_or_skip()
+    E, D = 4, 24
+
+    @FEED_FORWARDS.register("toy_routed", replace=True)
+    class ToyRouted(FeedForward):
+        def __init__(self, params, **kw):
+            super().__init__(params, **kw)
+            self.h = params["hidden_size"]
+
+        def tensor_specs(self):
+            specs = [TensorSpec("router.weight", (E, self.h))]
+            for e in range(E):
+                specs += [TensorSpec(f"experts.{e}.w_in.weight", (D, self.h)), TensorSpec(f"experts.{e}.w_out.weight", (self.h, D))]
+            return specs
+
+        def bind(self, fetch):
+            self.router = self._f32(fetch("router.weight"))
+            self.w_in = torch.stack([self._f32(fetch(f"experts.{e}.w_in.weight")) for e in range(E)])
+            self.w_out = torch.stack([self._f32(fetch(f"experts.{e}.w_out.weight")) for e in range(E)])
+
+        def forward(self, x, step):
+            xf = x.float()
+            probs = torch.softmax(xf @ self.router.t(), dim=-1)                # float32 router
+            top = probs.argmax(-1)
+            hid = torch.relu(torch.einsum("th,tdh->td", xf, self.w_in[top]))
+            return torch.einsum("td,thd->th", hid, self.w_out[top]) * probs.gather(1, top[:, None])
+
+    @POSITIONS.register("toy_learned_abs", replace=True)
+    class LearnedPositions(PositionEncoding):
+        def tensor_specs(self):
+            return [TensorSpec("weight", (self.params["max_positions"], self.params["hidden_size"]), role="embedding")]
+
+        def bind(self, fetch):
+            self.weight = self._f32(fetch("weight"))
+
+        def on_embedding(self, residual, step):
+            residual += self.weight[step.positions.long()]
+
+    def toy_plan(cfg):
+        base = qwen2_plan(cfg)
+        routed = PartSpec("toy_routed", {"hidden_size": cfg.hidden_size})
+        layers = tuple(LayerSpec(prefix=l.prefix, mixer=l.mixer, ffn=routed if i % 2 else l.ffn, norm=l.norm,
+                                 ffn_prefix="moe" if i % 2 else l.ffn_prefix) for i, l in enumerate(base.layers))
+        pos = PartSpec("toy_learned_abs", {"max_positions": cfg.max_position_embeddings, "hidden_size": cfg.hidden_size})
+        return ModelPlan(architecture="ToyRoutedLM", hidden_size=base.hidden_size, vocab_size=base.vocab_size,
+                         max_positions=base.max_positions, embedding_name=base.embedding_name, layers=layers,
+                         run_list=tuple(RunEntry(i) for i in range(len(layers))), final_norm=base.final_norm,
+                         final_norm_name=base.final_norm_name, head_name=base.head_name, position=pos,
+                         position_name="model.pos_embed")
+
+    register_architecture(Architecture("ToyRoutedLM", Qwen2Config, toy_plan), replace=True)
+    try:
+        config, init, page = TINY["A"]
+        config = dict(config, architectures=["ToyRoutedLM"], num_hidden_layers=4)
+        model_dir = write_random_model(str(tmp_path / "toy"), config, 6, std=0.08, bias_std=0.2, gain_std=0.1)
+        cfg, w = plain.load_model(model_dir)
+        nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+
+        def plain_toy(ids):
+            s = len(ids)
+            h = plain.embed(ids, w["model.embed_tokens.weight"]) + w["model.pos_embed.weight"][:s]
+            for i in range(cfg["num_hidden_layers"]):
+                p = f"model.layers.{i}"
+                x = plain.rms_norm(h, w[f"{p}.input_layernorm.weight"], cfg["rms_norm_eps"])
+                a = f"{p}.self_attn"
+                q = plain.linear(x, w[f"{a}.q_proj.weight"], w[f"{a}.q_proj.bias"]).reshape(s, nq, hd).transpose(1, 0, 2)
+                k = plain.linear(x, w[f"{a}.k_proj.weight"], w[f"{a}.k_proj.bias"]).reshape(s, nkv, hd).transpose(1, 0, 2)
+                v = plain.linear(x, w[f"{a}.v_proj.weight"], w[f"{a}.v_proj.bias"]).reshape(s, nkv, hd).transpose(1, 0, 2)
+                k, v = np.repeat(k, nq // nkv, axis=0), np.repeat(v, nq // nkv, axis=0)
+                o = plain.causal_attention(q, k, v, hd ** -0.5).transpose(1, 0, 2).reshape(s, nq * hd)
+                h = h + plain.linear(o, w[f"{a}.o_proj.weight"])
+                x = plain.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+                if i % 2:
+                    logits = x @ w[f"{p}.moe.router.weight"].T
+                    pr = np.exp(logits - logits.max(-1, keepdims=True))
+                    pr = pr / pr.sum(-1, keepdims=True)
+                    top = pr.argmax(-1)
+                    out = np.zeros_like(x)
+                    for t in range(s):
+                        e = top[t]
+                        hid = np.maximum(x[t] @ w[f"{p}.moe.experts.{e}.w_in.weight"].T, 0)
+                        out[t] = hid @ w[f"{p}.moe.experts.{e}.w_out.weight"].T * pr[t, e]
+                    h = h + out
+                else:
+                    h = h + plain.swiglu(x, w, p)
+            h = plain.rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
+            return h @ w["model.embed_tokens.weight"].T
+
+        model, _ = build_model(model_dir, "float32", dev)
+        assert [type(l.ffn).__name__ for l in model.layers] == ["SwiGLU", "ToyRouted"] * 2
+        assert type(model.position).__name__ == "LearnedPositions"
+        eng = Engine(model, page_size=page, num_pages=12, max_requests=2)
+        ids = _prompts(cfg, (45,), 5)[0]
+        want = plain_toy(ids)
+        got, p0 = [], 0
+        for n in (11, 2, 1, 17, 1, 1, 12):
+            got.append(eng.step([StepEntry("a", ids[p0:p0 + n], list(range(n)))]).cpu().numpy())
+            p0 += n
+        np.testing.assert_allclose(np.concatenate(got), want, rtol=1e-4, atol=2e-5)
+    finally:
+        unregister_architecture("ToyRoutedLM")
+        FEED_FORWARDS.unregister("toy_routed")
+        POSITIONS.unregister("toy_learned_abs")
+
+
+def test_run_list_names_a_layer_twice_and_borrows_a_cache(tmp_path):
+    """The order in which layers run is data: here layer 0 runs twice (each run with a cache of its
+    own) and the last run of layer 1 reads the keys and values that layer 1's first run wrote,
+    writing none itself.  Compared with a plain numpy statement, in portions and token by token."""
+    from sllm_b200.config import Architecture, ModelPlan, RunEntry, register_architecture, unregister_architecture
+    from sllm_b200.engine import Engine, StepEntry, build_model
+    from sllm_b200.models.qwen2 import Qwen2Config
+    from sllm_b200.models.qwen2 import plan as qwen2_plan
+    from sllm_b200.weights import write_random_model
+    dev = cuda_or_skip()
+    RUNS = (RunEntry(0), RunEntry(1), RunEntry(0), RunEntry(1, cache_from=1))
+
+    def loop_plan(cfg):
+        b = qwen2_plan(cfg)
+        return ModelPlan(architecture="ToyLoopLM", hidden_size=b.hidden_size, vocab_size=b.vocab_size,
+                         max_positions=b.max_positions, embedding_name=b.embedding_name, layers=b.layers,
+                         run_list=RUNS, final_norm=b.final_norm, final_norm_name=b.final_norm_name,
+                         head_name=b.head_name, position=b.position)
+
+    register_architecture(Architecture("ToyLoopLM", Qwen2Config, loop_plan), replace=True)
+    try:
+        config, init, page = TINY["B"]
+        config = dict(config, architectures=["ToyLoopLM"], num_hidden_layers=2)
+        model_dir = write_random_model(str(tmp_path / "loop"), config, 9, std=0.05, bias_std=0.2, gain_std=0.1)
+        cfg, w = plain.load_model(model_dir)
+        nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+
+        def plain_loop(ids):
+            s = len(ids)
+            h = plain.embed(ids, w["model.embed_tokens.weight"])
+            cos, sin = plain.rotary_tables(cfg["rope_theta"], np.arange(s), hd)
+            kv_of_run = {}
+            for run, e in enumerate(RUNS):
+                p = f"model.layers.{e.layer}"
+                a = f"{p}.self_attn"
+                x = plain.rms_norm(h, w[f"{p}.input_layernorm.weight"], cfg["rms_norm_eps"])
+                q = plain.linear(x, w[f"{a}.q_proj.weight"], w[f"{a}.q_proj.bias"]).reshape(s, nq, hd).transpose(1, 0, 2)
+                q = plain.apply_rotary(q, cos, sin)
+                if e.cache_from is None:
+                    k = plain.linear(x, w[f"{a}.k_proj.weight"], w[f"{a}.k_proj.bias"]).reshape(s, nkv, hd).transpose(1, 0, 2)
+                    v = plain.linear(x, w[f"{a}.v_proj.weight"], w[f"{a}.v_proj.bias"]).reshape(s, nkv, hd).transpose(1, 0, 2)
+                    kv_of_run[run] = (plain.apply_rotary(k, cos, sin), v)
+                k, v = kv_of_run[run if e.cache_from is None else e.cache_from]
+                o = plain.causal_attention(q, np.repeat(k, nq // nkv, axis=0), np.repeat(v, nq // nkv, axis=0), hd ** -0.5)
+                h = h + plain.linear(o.transpose(1, 0, 2).reshape(s, nq * hd), w[f"{a}.o_proj.weight"])
+                x = plain.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+                h = h + plain.swiglu(x, w, p)
+            h = plain.rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
+            return h @ w["lm_head.weight"].T
+
+        for dtype, tol in (("float32", dict(rtol=1e-4, atol=2e-5)), ("bfloat16", dict(rtol=2e-2, atol=2e-2))):
+            model, _ = build_model(model_dir, dtype, dev)
+            eng = Engine(model, page_size=page, num_pages=16, max_requests=2)
+            # three caching runs share one group; the borrowing run has the cache of run 1
+            assert eng.cache.groups[0].runs == [0, 1, 2]
+            assert eng.layer_caches[3].k.data_ptr() == eng.layer_caches[1].k.data_ptr()
+            ids = _prompts(cfg, (40,), 6)[0]
+            want = plain_loop(ids)
+            got, p0 = [], 0
+            for n in (13, 2, 1, 1, 20, 3):
+                got.append(eng.step([StepEntry("a", ids[p0:p0 + n], list(range(n)))]).cpu().numpy())
+                p0 += n
+            np.testing.assert_allclose(np.concatenate(got), want, **tol)
+    finally:
+        unregister_architecture("ToyLoopLM")
