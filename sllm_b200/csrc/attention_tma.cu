@@ -5,9 +5,9 @@
 // of each 64-key tile; partial results per context split, a combine kernel afterwards).  What
 // differs is how keys and values reach shared memory.  There, every thread computes addresses and
 // issues sixteen 16-byte cp.async per tile, and the kernel is bound by those instructions.  Here a
-// fifth warp's one lane issues one TMA box copy per page and 64-column half of a head
-// (cp.async.bulk.tensor.2d over the cache seen as a [pages * kv heads * page size, head size]
-// matrix, 128-byte swizzle); the copies signal an mbarrier per stage, the compute warps read the
+// fifth warp's one lane issues one TMA box copy per page (cp.async.bulk.tensor.3d over the cache
+// seen as [pages * kv heads * page size rows][head size / 64][64], all rows and halves of a page in
+// one box, 128-byte swizzle; the TMA unit spends a fixed time per copy, so few large boxes); the copies signal an mbarrier per stage, the compute warps read the
 // swizzled tile with ldmatrix and hand the stage back through a second mbarrier.  No thread of the
 // compute warps touches an address of the cache.
 //
@@ -33,6 +33,7 @@ namespace sllm {
 constexpr int TA_BN = 64;          // keys per tile
 constexpr int TA_STAGES = 3;
 constexpr int TA_THREADS = 160;    // four compute warps and the producer warp
+constexpr int TA_BT_CACHE = 2048;  // block-table entries the producer keeps in shared memory
 
 struct AttnTmaParams {
   const __nv_bfloat16* q;        // [T, nq, HD]
@@ -49,10 +50,13 @@ struct AttnTmaParams {
   float scale_log2;
 };
 
-// byte offset of the 16-byte chunk `chunk` (of the head's HD/8) of key row `row` within a stage's K or V
+// Byte offset of the 16-byte chunk `chunk` (of the head's HD/8) of key row `row` within a stage's K or V.
+// A page arrives as one box of whole rows; a row is HD/64 consecutive 128-byte units, and the TMA unit
+// swizzles the eight chunks of a unit by the unit's index.
 template <int HD>
 __device__ __forceinline__ int swz(int row, int chunk) {
-  return (chunk >> 3) * (TA_BN * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+  const int unit = row * (HD / 64) + (chunk >> 3);
+  return unit * 128 + (((chunk & 7) ^ (unit & 7)) << 4);
 }
 
 template <int HD>
@@ -71,6 +75,7 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   uint64_t* full = reinterpret_cast<uint64_t*>(q_s + 16 * STRIDE);
   uint64_t* empty = full + TA_STAGES;
   volatile int* failed = reinterpret_cast<volatile int*>(empty + TA_STAGES);
+  int* bt_s = const_cast<int*>(reinterpret_cast<volatile int*>(failed + 2));      // [TA_BT_CACHE]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
@@ -110,6 +115,17 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
   if (warp == 4) {
     // ---------------- producer ----------------
+    // The pages of this CTA's key range, fetched once by the whole warp: a tile's copies then wait
+    // for nothing but a free stage (one lane reading the table from global memory page by page
+    // took longer per tile than the copies themselves).
+    const int page_first = tile0 / ps;
+    const int page_count = n_tiles > 0 ? min(pages_in_ctx, (tile0 + n_tiles * TA_BN + ps - 1) / ps) - page_first : 0;
+    const bool bt_cached = page_count <= TA_BT_CACHE;
+    if (bt_cached) {
+      for (int i = lane; i < page_count; i += 32) bt_s[i] = bt[page_first + i];
+      __syncwarp();
+    }
+    auto page_of = [&](int pi) { return bt_cached ? bt_s[pi - page_first] : bt[pi]; };
     for (int tile = 0; tile < n_tiles; ++tile) {
       const int s = tile % TA_STAGES, round = tile / TA_STAGES;
       bool ok = true;
@@ -126,17 +142,16 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       unsigned valid = 0;
       for (int i = 0; i < pages_per_tile; ++i) {
         const int pi = page0 + i;
-        if (pi < pages_in_ctx && bt[pi] >= 0) valid |= 1u << i;          // at most 8 pages a tile (page size >= 8)
+        if (pi < pages_in_ctx && page_of(pi) >= 0) valid |= 1u << i;     // at most 8 pages a tile (page size >= 8)
       }
       if (round == 0 && valid != (1u << pages_per_tile) - 1) {
         // first use of this stage: slots without a page must not hold garbage
         for (int i = 0; i < pages_per_tile; ++i) {
           if (valid & (1u << i)) continue;
-          for (int h = 0; h < HALVES; ++h)
-            for (int o = lane * 16; o < ps * 128; o += 32 * 16) {
-              *reinterpret_cast<uint4*>(ks + h * (TA_BN * 128) + i * ps * 128 + o) = make_uint4(0, 0, 0, 0);
-              *reinterpret_cast<uint4*>(vs + h * (TA_BN * 128) + i * ps * 128 + o) = make_uint4(0, 0, 0, 0);
-            }
+          for (int o = lane * 16; o < ps * HALVES * 128; o += 32 * 16) {
+            *reinterpret_cast<uint4*>(ks + i * ps * HALVES * 128 + o) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(vs + i * ps * HALVES * 128 + o) = make_uint4(0, 0, 0, 0);
+          }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
@@ -149,12 +164,9 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
           mbar_expect_tx(&full[s], bytes);
           for (int i = 0; i < pages_per_tile; ++i) {
             if (!(valid & (1u << i))) continue;
-            const int y = (bt[page0 + i] * p.nkv + kvh) * ps;
-#pragma unroll
-            for (int h = 0; h < HALVES; ++h) {
-              tma_load_2d(ks + h * (TA_BN * 128) + i * ps * 128, &map_k, h * 64, y, &full[s]);
-              tma_load_2d(vs + h * (TA_BN * 128) + i * ps * 128, &map_v, h * 64, y, &full[s]);
-            }
+            const int y = (page_of(page0 + i) * p.nkv + kvh) * ps;
+            tma_load_3d(ks + i * ps * HALVES * 128, &map_k, 0, 0, y, &full[s]);
+            tma_load_3d(vs + i * ps * HALVES * 128, &map_v, 0, 0, y, &full[s]);
           }
         }
       }
@@ -213,30 +225,57 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       const unsigned char* kb = kv_s + s * 2 * KV_BYTES;
       const unsigned char* vb = kb + KV_BYTES;
 
-      float sc[2][4];
-#pragma unroll
-      for (int n = 0; n < 2; ++n)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) sc[n][c] = 0.f;
-#pragma unroll
-      for (int ks = 0; ks < KSTEPS; ++ks) {
-        unsigned b[4];
-        ldmatrix_x4(b, kb + swz<HD>(koff + (lane >> 4) * 8 + (lane & 7), ks * 2 + ((lane >> 3) & 1)));
-        mma_bf16(sc[0], qf[ks], b[0], b[1]);
-        mma_bf16(sc[1], qf[ks], b[2], b[3]);
-      }
-      const int kbase = tile0 + tile * TA_BN + koff;
-      float mx[2] = {-INFINITY, -INFINITY};
+      // mma.sync has a long latency on this part and a warp's MMAs into one accumulator run one
+      // after the other: the k steps go to four accumulator sets in turn, added at the end
+      float sc[2][4], sx[3][2][4];
 #pragma unroll
       for (int n = 0; n < 2; ++n)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const int key = kbase + n * 8 + 2 * t4 + (c & 1);
-          const int i = c >> 1;
-          const float v = (key < hi_r[i] && key >= lo_r[i]) ? sc[n][c] * p.scale_log2 : -INFINITY;
-          sc[n][c] = v;
-          mx[i] = fmaxf(mx[i], v);
+          sc[n][c] = 0.f;
+#pragma unroll
+          for (int a = 0; a < 3; ++a) sx[a][n][c] = 0.f;
         }
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        unsigned b[4];
+        ldmatrix_x4(b, kb + swz<HD>(koff + (lane >> 4) * 8 + (lane & 7), ks * 2 + ((lane >> 3) & 1)));
+        if ((ks & 3) == 0) {
+          mma_bf16(sc[0], qf[ks], b[0], b[1]);
+          mma_bf16(sc[1], qf[ks], b[2], b[3]);
+        } else {
+          mma_bf16(sx[(ks & 3) - 1][0], qf[ks], b[0], b[1]);
+          mma_bf16(sx[(ks & 3) - 1][1], qf[ks], b[2], b[3]);
+        }
+      }
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sc[n][c] += (sx[0][n][c] + sx[1][n][c]) + sx[2][n][c];
+      const int kbase = tile0 + tile * TA_BN + koff;
+      float mx[2] = {-INFINITY, -INFINITY};
+      // Only a tile at an edge of some row's key range needs the mask; the warp decides once.
+      const bool edge = kbase < lo_r[0] || kbase < lo_r[1] || kbase + 16 > hi_r[0] || kbase + 16 > hi_r[1];
+      if (__any_sync(0xffffffffu, edge)) {
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int key = kbase + n * 8 + 2 * t4 + (c & 1);
+            const int i = c >> 1;
+            const float v = (key < hi_r[i] && key >= lo_r[i]) ? sc[n][c] * p.scale_log2 : -INFINITY;
+            sc[n][c] = v;
+            mx[i] = fmaxf(mx[i], v);
+          }
+      } else {
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            sc[n][c] *= p.scale_log2;
+            mx[c >> 1] = fmaxf(mx[c >> 1], sc[n][c]);
+          }
+      }
       float corr[2];
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
@@ -249,10 +288,13 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         mx[i] = m_use;
         l_r[i] *= corr[i];
       }
+      // the running maximum seldom moves after the first tiles: rescale the output only when it did
+      if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-      for (int d = 0; d < DT; ++d) {
-        o[d][0] *= corr[0]; o[d][1] *= corr[0];
-        o[d][2] *= corr[1]; o[d][3] *= corr[1];
+        for (int d = 0; d < DT; ++d) {
+          o[d][0] *= corr[0]; o[d][1] *= corr[0];
+          o[d][2] *= corr[1]; o[d][3] *= corr[1];
+        }
       }
       unsigned pf[4];
 #pragma unroll
@@ -387,7 +429,7 @@ static bool cache_map(const void* base, long long rows, int ps, int hd, CUtensor
     return true;
   }
   if (rows > 0x7fffffffLL) return false;
-  if (!make_map(out, base, (int)rows, hd, ps)) return false;
+  if (!make_map_rows(out, base, rows, hd / 64, ps)) return false;
   if (g_maps.size() > 4096) g_maps.clear();
   g_maps.emplace(key, *out);
   return true;
@@ -395,7 +437,8 @@ static bool cache_map(const void* base, long long rows, int ps, int hd, CUtensor
 
 template <int HD>
 static int launch_ta(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTmaParams& p, int tiles, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)TA_STAGES * 2 * TA_BN * HD * 2 + 16 * (HD + 8) * 2 + 2 * TA_STAGES * 8 + 16 + 1024;
+  constexpr size_t smem = (size_t)TA_STAGES * 2 * TA_BN * HD * 2 + 16 * (HD + 8) * 2 + 2 * TA_STAGES * 8 + 16 +
+                          TA_BT_CACHE * 4 + 1024;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_tma_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {

@@ -72,5 +72,24 @@ inline bool make_map(CUtensorMap* map, const void* base, int rows, int K, int bo
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// rows x (halves * 64) bfloat16, row-major, seen as [rows][halves][64]: one box takes box_rows whole
+// rows (all halves), stored as consecutive 128-byte units (row-major, half fastest), 128-byte swizzle
+inline bool make_map_rows(CUtensorMap* map, const void* base, long long rows, int halves, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {64, (cuuint64_t)halves, (cuuint64_t)rows};
+  cuuint64_t strides[2] = {128, (cuuint64_t)halves * 128};
+  cuuint32_t box[3] = {64, (cuuint32_t)halves, (cuuint32_t)box_rows};
+  cuuint32_t elem[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+__device__ __forceinline__ void tma_load_3d(void* smem, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
 
 }  // namespace sllm
