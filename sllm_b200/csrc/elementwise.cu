@@ -105,6 +105,47 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
   }
 }
 
+// Many rows (prompt portions): the kernel is bound by memory, so a thread keeps VPT vectors of its
+// row in registers (one read of the stream, no second pass) and a row takes few threads, which
+// leaves many rows resident per SM and many loads in flight.  One part only.
+template <typename TD, typename TO, int VPT>
+__global__ void add_rmsnorm_rows_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+                                        const float* __restrict__ w, float eps, TO* __restrict__ out, int H) {
+  __shared__ float red[33];
+  pdl_wait();
+  const size_t base = (size_t)blockIdx.x * H;
+  float4 v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * 4;
+    v[k] = i < H ? load4(residual + base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (delta != nullptr) {
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = (threadIdx.x + k * blockDim.x) * 4;
+      if (i < H) {
+        const float4 d = load4(delta + base + i);
+        v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
+        store4(residual + base + i, v[k]);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+  const float total = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(total / (float)H + eps);
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * 4;
+    if (i < H) {
+      const float4 g = load4(w + i);
+      store4(out + base + i, make_float4(v[k].x * inv * g.x, v[k].y * inv * g.y, v[k].z * inv * g.z, v[k].w * inv * g.w));
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // out[t, i] = silu(g) * u with g = gu[t, gi(i)], u = gu[t, gi(i) + blk], gi(i) = (i/blk)*2*blk + i%blk
 // silu(z) = z / (1 + exp(-z))  (ref/qwen3_5.py:28-29; kernels/cuda/kernels.cu:898-907)
@@ -213,6 +254,98 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int parts, size
   }
 }
 
+// The same for a bfloat16 cache, one part, eight elements a thread (16-byte loads and stores):
+// the form for prompt portions, where the kernel is bound by memory.  Needs rot % 16 == 0 and
+// hd % 8 == 0.  An item is (head, chunk of 8 dims); the chunk below rot/2 also takes its partner
+// rot/2 further, the chunks between rot/2 and rot are done by their partners.
+template <typename TI>
+__global__ void rope_kv_write_vec_kernel(const TI* __restrict__ qkv, const float* __restrict__ bias,
+                                         const int* __restrict__ positions, const float* __restrict__ table,
+                                         int rot, int max_pos, int nq, int nkv, int hd, int hpb,
+                                         const int* __restrict__ slot_mapping, int page_size, int num_pages,
+                                         __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                         __nv_bfloat16* __restrict__ q_out) {
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int heads = nq + 2 * nkv;
+  const int head0 = blockIdx.y * hpb;
+  const int nheads = min(hpb, heads - head0);
+  const TI* xt = qkv + (size_t)t * heads * hd;
+  int slot = -1;
+  if (slot_mapping != nullptr) {
+    slot = slot_mapping[t];
+    if (slot < 0 || slot / page_size >= num_pages) slot = -1;
+  }
+  const bool rotary = rot > 0 && table != nullptr;
+  const int half = rot / 2, cph = hd / 8;
+  const float* cs = nullptr;
+  if (rotary) {
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    cs = table + (size_t)pos * rot;
+  }
+  auto ld8 = [&](int col, float* f) {
+    if constexpr (sizeof(TI) == 4) {
+      const float4 x0 = load4(xt + col), x1 = load4(xt + col + 4);
+      f[0] = x0.x; f[1] = x0.y; f[2] = x0.z; f[3] = x0.w;
+      f[4] = x1.x; f[5] = x1.y; f[6] = x1.z; f[7] = x1.w;
+    } else {
+      const uint4 raw = *reinterpret_cast<const uint4*>(xt + col);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 p = __bfloat1622float2(h2[k]);
+        f[2 * k] = p.x; f[2 * k + 1] = p.y;
+      }
+    }
+    if (bias != nullptr) {
+      const float4 b0 = load4(bias + col), b1 = load4(bias + col + 4);
+      f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w;
+      f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
+    }
+  };
+  auto st8 = [&](__nv_bfloat16* dst, const float* f) {
+    uint4 raw;
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h2[k] = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+    *reinterpret_cast<uint4*>(dst) = raw;
+  };
+  for (int item = threadIdx.x; item < nheads * cph; item += blockDim.x) {
+    const int head = head0 + item / cph, d = (item % cph) * 8;
+    __nv_bfloat16* dst;
+    if (head < nq) {
+      dst = q_out + (size_t)t * nq * hd + (size_t)head * hd;
+    } else {
+      if (slot < 0) continue;
+      const bool is_k = head < nq + nkv;
+      const int kvh = is_k ? head - nq : head - nq - nkv;
+      const int page = slot / page_size, off = slot % page_size;
+      dst = (is_k ? k_cache : v_cache) + (((size_t)page * nkv + kvh) * page_size + off) * hd;
+    }
+    const bool rotated = rotary && head < nq + nkv && d < rot;
+    float a[8];
+    if (!rotated) {
+      ld8(head * hd + d, a);
+      st8(dst + d, a);
+    } else if (d < half) {
+      float b[8], o1[8], o2[8];
+      ld8(head * hd + d, a);
+      ld8(head * hd + d + half, b);
+      const float4 c0 = load4(cs + d), c1 = load4(cs + d + 4), s0 = load4(cs + half + d), s1 = load4(cs + half + d + 4);
+      const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        o1[k] = a[k] * c[k] - b[k] * sn[k];
+        o2[k] = b[k] * c[k] + a[k] * sn[k];
+      }
+      st8(dst + d, o1);
+      st8(dst + d + half, o2);
+    }
+  }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -245,9 +378,15 @@ SLLM_EXPORT int sllm_add_rmsnorm(float* residual, const void* delta, int delta_d
   // one pass of the row per thread where it fits: the kernel is bound by load latency, not by work
   int threads = ((H / per + 31) / 32) * 32;
   threads = threads > 1024 ? 1024 : (threads < 64 ? 64 : threads);
+  constexpr int VPT = 4;
+  const int row_threads = ((H / 4 + VPT - 1) / VPT + 31) / 32 * 32;
+  const bool many = vec && rows >= 64 && (delta == nullptr || parts == 1) && row_threads <= 1024;
 #define LAUNCH(TD, TO)                                                                                         \
   do {                                                                                                         \
-    if (vec)                                                                                                   \
+    if (many)                                                                                                  \
+      launch_kernel(add_rmsnorm_rows_kernel<TD, TO, VPT>, rows, row_threads, 0, stream, residual,             \
+                    (const TD*)delta, w, eps, (TO*)out, H);                                                    \
+    else if (vec)                                                                                              \
       launch_kernel(add_rmsnorm_kernel<TD, TO, true>, rows, threads, 0, stream, residual, (const TD*)delta,   \
                     parts, part_stride, w, eps, (TO*)out, H);                                                  \
     else                                                                                                       \
@@ -308,6 +447,20 @@ SLLM_EXPORT int sllm_rope_kv_write(const void* qkv, int in_dtype, int parts, siz
   const int hpb = T >= 128 ? heads : 1;
   dim3 grid(T, (heads + hpb - 1) / hpb);
   const int threads = hpb == 1 ? (hd / 2 >= 64 ? 64 : 32) : 256;
+  auto al16 = [](const void* p) { return (uintptr_t)p % 16 == 0; };
+  if (cache_dtype == SLLM_BF16 && parts == 1 && rot % 16 == 0 && hd % 8 == 0 && al16(qkv) &&
+      al16(bias) && al16(table) && al16(q_out) && al16(k_cache) && al16(v_cache)) {
+    const int vthreads = hpb == 1 ? 32 : 256;
+#define LAUNCH_VEC(TI)                                                                                           \
+  launch_kernel(rope_kv_write_vec_kernel<TI>, grid, vthreads, 0, stream, (const TI*)qkv, bias, positions, table, rot, \
+                max_pos, nq, nkv, hd, hpb, slot_mapping, page_size, num_pages, (__nv_bfloat16*)k_cache,            \
+                (__nv_bfloat16*)v_cache, (__nv_bfloat16*)q_out)
+    if (in_dtype == SLLM_F32) LAUNCH_VEC(float);
+    else if (in_dtype == SLLM_BF16) LAUNCH_VEC(__nv_bfloat16);
+    else SLLM_REQUIRE(false, "rope_kv_write: unsupported input dtype %d", in_dtype);
+#undef LAUNCH_VEC
+    return launch_status("rope_kv_write");
+  }
 #define LAUNCH(TI, TC)                                                                                         \
   launch_kernel(rope_kv_write_kernel<TI, TC>, grid, threads, 0, stream, (const TI*)qkv, parts, part_stride, bias,  \
                 positions, table, rot, max_pos, nq, nkv, hd, hpb, slot_mapping, page_size, num_pages,              \

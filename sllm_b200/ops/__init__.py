@@ -403,6 +403,24 @@ def attention_tma_decode(q, k_cache, v_cache, block_tables, q_start, ctx_len, ti
     return out
 
 
+def tc_attention_supports(hd: int, page_size: int) -> bool:
+    return bool(lib().sllm_attention_tc_supports(int(hd), int(page_size)))
+
+
+def attention_tc(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, nq, nkv, hd, scale, out=None):
+    """The prefill form on tcgen05 (128-row tiles; no window, no context split; see `attention_tiles`)."""
+    _chk(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles[0], tiles[1])
+    if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
+        raise KernelError("attention_tc: bfloat16 only")
+    if out is None:
+        out = torch.empty_like(q)
+    call("sllm_attention_tc", _p(q), _p(k_cache), _p(v_cache), k_cache.shape[0], _p(out), _p(block_tables),
+         block_tables.shape[1], _p(q_start), _p(ctx_len), _p(tiles[0]), _p(tiles[1]), tiles[2], nq, nkv, hd,
+         k_cache.shape[2], float(scale), _p(_status_word(q.device)), _stream())
+    _tc_used["since_check"] += 1
+    return out
+
+
 def mma_supports(hd: int) -> bool:
     return bool(lib().sllm_attention_mma_supports(int(hd)))
 
@@ -429,7 +447,9 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
     elif small:
         attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, True, splits,
                       nq, nkv, hd, scale, window, out)
-    if large:
+    if large and not window and tc_attention_supports(hd, k_cache.shape[2]):
+        attention_tc(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, nq, nkv, hd, scale, out)
+    elif large:
         attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, False, 1,
                       nq, nkv, hd, scale, window, out)
     return out

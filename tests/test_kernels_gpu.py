@@ -35,7 +35,8 @@ def test_embed_gather(dtype, V, H, T):
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("delta_kind", ["none", "f32", "bf16", "parts"])
-@pytest.mark.parametrize("rows,H,eps", [(5, 72, 1e-6), (33, 3584, 1e-5), (2, 1000, 1e-6)])
+@pytest.mark.parametrize("rows,H,eps", [(5, 72, 1e-6), (33, 3584, 1e-5), (2, 1000, 1e-6), (130, 1000, 1e-6),
+                                        (200, 3584, 1e-5), (70, 16400, 1e-6)])
 def test_add_rmsnorm(out_dtype, delta_kind, rows, H, eps):
     ops = _ops()
     g = torch.Generator(device="cuda").manual_seed(1)
@@ -123,6 +124,36 @@ def test_rope_kv_write(dtype, nq, nkv, hd, rot, ps):
     k2, v2 = torch.zeros_like(kc[0]), torch.zeros_like(vc[0])
     got = ops.rope_kv_write(qkv, None, pos, None, 0, nq, nkv, hd, None, k2, v2, dtype)
     _close(got, qkv[:, :nq * hd].to(dtype), dtype, scale=4.0)
+    assert not k2.any() and not v2.any()
+
+
+@pytest.mark.parametrize("in_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T", [21, 150])
+@pytest.mark.parametrize("nq,nkv,hd,rot,ps", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (5, 1, 64, 32, 4), (7, 7, 80, 80, 32),
+                                             (6, 2, 128, 128, 16)])
+def test_rope_kv_write_wide_form(in_dtype, T, nq, nkv, hd, rot, ps):
+    """A bfloat16 cache, one part, rotary_dim a multiple of 16: the 16-byte form of the kernel, few and many tokens."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(16)
+    pages, max_pos = -(-T // ps) + 3, 300
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd, device="cuda", generator=g).to(in_dtype)
+    bias = torch.randn((nq + 2 * nkv) * hd, device="cuda", generator=g)
+    pos = torch.randint(0, max_pos, (T,), device="cuda", generator=g, dtype=torch.int32)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * (1e4 ** (-torch.arange(0, rot, 2, dtype=torch.float64) / rot))[None]
+    table = torch.stack([ang.cos(), ang.sin()], 1).float().cuda()
+    slots = torch.randperm(pages * ps, device="cuda", generator=g)[:T].int()
+    dtype = torch.bfloat16
+    for b in (bias, None):
+        kc = [torch.zeros(pages, nkv, ps, hd, device="cuda", dtype=dtype) for _ in range(2)]
+        vc = [torch.zeros(pages, nkv, ps, hd, device="cuda", dtype=dtype) for _ in range(2)]
+        got = ops.rope_kv_write(qkv, b, pos, table, rot, nq, nkv, hd, slots, kc[0], vc[0], dtype)
+        want = ref.rope_kv_write(qkv, b, pos, table, rot, nq, nkv, hd, slots, kc[1], vc[1], dtype)
+        _close(got, want, dtype, scale=4.0)
+        _close(kc[0], kc[1], dtype, scale=4.0)
+        _close(vc[0], vc[1], dtype, scale=4.0)
+    k2, v2 = torch.zeros_like(kc[0]), torch.zeros_like(vc[0])
+    got = ops.rope_kv_write(qkv, None, pos, None, 0, nq, nkv, hd, None, k2, v2, dtype)
+    assert torch.equal(got, qkv[:, :nq * hd].bfloat16())
     assert not k2.any() and not v2.any()
 
 
@@ -276,6 +307,59 @@ def test_attention_mma(nq, nkv, hd, ps, window, case):
         ops.attention_mma(q, kc, vc, bt, q_start, ctx_len, large, False, 1, nq, nkv, hd, scale, window, out)
     assert not out.isnan().any(), "a row was not written"
     torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("nq,nkv,hd,ps", [(28, 4, 128, 16), (14, 2, 64, 16), (8, 8, 128, 8), (6, 1, 64, 32), (4, 2, 128, 64)])
+@pytest.mark.parametrize("case", ["prefill", "long", "mixed", "peaked"])
+def test_attention_tc(nq, nkv, hd, ps, case):
+    """The tcgen05 prefill form against the float32 statement: portions that start in mid-context, rows
+    of several requests, many key tiles, and scores so peaked that the running maximum jumps from tile
+    to tile (the output in tensor memory is rescaled)."""
+    ops = _ops()
+    if not ops.tc_attention_supports(hd, ps):
+        pytest.skip("not taken by the tcgen05 form")
+    g = torch.Generator(device="cuda").manual_seed(21)
+    lens, q_lens = {"prefill": ([70, 33, 200], [70, 5, 131]), "long": ([1000, 2100], [1000, 300]),
+                    "mixed": ([90, 400, 2, 65, 129], [37, 1, 2, 1, 128]), "peaked": ([700], [650])}[case]
+    q, kc, vc, bt, pos, seq = _paged_case(g, lens, q_lens, nq, nkv, hd, ps, torch.bfloat16)
+    q_start, ctx_len = _starts(q_lens, lens)
+    scale = 1.0 if case == "peaked" else hd ** -0.5
+    want = ref.attention_simt(q.float(), kc.float(), vc.float(), bt, pos, seq, nq, nkv, hd, scale, None)
+    G = nq // nkv
+    small, large = ops.attention_tiles(q_lens, G, "cuda")
+    out = torch.full_like(q, float("nan"))
+    if small:
+        ops.attention_mma(q, kc, vc, bt, q_start, ctx_len, small, True, 1, nq, nkv, hd, scale, None, out)
+    assert large
+    ops.attention_tc(q, kc, vc, bt, q_start, ctx_len, large, nq, nkv, hd, scale, out)
+    ops.check_tcgen05_status()
+    assert not out.isnan().any(), "a row was not written"
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
+
+
+def test_attention_tc_far_key_and_page_edges():
+    """One key stands out for every query, at page and tile edges of a long prompt."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(22)
+    nq, nkv, hd, ps = 8, 2, 128, 16
+    n = 1100
+    for far in (0, 15, 16, 63, 64, 65, 127, 128, 1023, 1024):
+        q, kc, vc, bt, pos, seq = _paged_case(g, [n], [n], nq, nkv, hd, ps, torch.bfloat16)
+        q_start, ctx_len = _starts([n], [n])
+        page, off = int(bt[0, far // ps]), far % ps
+        direction = torch.randn(hd, device="cuda", generator=g)
+        direction /= direction.norm()
+        kc[page, :, off, :] = (direction * 16).bfloat16()
+        q[:] = (direction * 16).repeat(nq).bfloat16()
+        _, large = ops.attention_tiles([n], nq // nkv, "cuda")
+        got = ops.attention_tc(q, kc, vc, bt, q_start, ctx_len, large, nq, nkv, hd, 1.0)
+        ops.check_tcgen05_status()
+        # queries at or after the far key return its value; the ones before it cannot see it
+        want = vc[page, :, off, :].float().repeat_interleave(nq // nkv, dim=0)
+        torch.testing.assert_close(got.float().reshape(n, nq, hd)[far:], want.expand(n - far, nq, hd), rtol=2e-2, atol=2e-2)
+        if far > 0:
+            full = ref.attention_simt(q.float(), kc.float(), vc.float(), bt, pos, seq, nq, nkv, hd, 1.0, None)
+            torch.testing.assert_close(got.float()[:far], full[:far], rtol=2e-2, atol=2e-2)
 
 
 def test_attention_mma_far_key_and_page_edges():
