@@ -2,24 +2,32 @@
 // (tcgen05, accumulators in tensor memory): causal GQA with an online softmax, bfloat16 in,
 // float32 scores, softmax and output accumulation.
 //
-// A CTA takes one 128-row tile of (token, head-in-group) rows of one request and one kv head,
-// as the mma.sync prefill form does, and walks the keys in tiles of 64.  Two CTAs share an SM
-// (112 KB of shared memory and 256 columns of tensor memory each), so that one CTA's softmax
-// runs while the other's products do.  Six warps, three jobs:
-//   warps 0-3  softmax: thread r owns row r.  It reads its row of S = Q K^T from tensor memory
+// A CTA takes RT (one or two) 128-row tiles of (token, head-in-group) rows of one request and one kv
+// head and walks the keys in tiles of 64; with two row tiles a key/value tile fetched once serves
+// both, and the shared memory of a whole SM holds four key/value tiles in flight.  The one-row-tile
+// form runs two CTAs per SM with two tiles in flight each; it is kept for steps with too few rows to
+// fill the GPU with 256-row CTAs.
+// Per row tile four softmax warps, then one warp for TMA and one for the MMAs:
+//   softmax    thread r owns row r.  It reads its row of S = Q K^T from tensor memory
 //              (tcgen05.ld), scales and masks it, keeps the row's running maximum and sum, writes
-//              P = exp2(S - max) as bfloat16 into shared memory in the swizzled layout the tensor
-//              core reads, and at the end reads O, divides by the sum and stores the row.
+//              P = exp2(S - max) as bfloat16 back into the first half of the same columns
+//              (tcgen05.st, two keys per 32-bit column), from where the tensor core takes it as the
+//              A operand, and at the end reads O, divides by the sum and stores the row.
 //              The maximum in use only moves when a tile's maximum exceeds it by more than 2^8
 //              (then O in tensor memory is rescaled: tcgen05.ld, multiply, tcgen05.st); the result
 //              is the same sum with a different common factor, which cancels in O / sum.
-//   warp 4     one lane issues the TMA loads: per page and 64-column half of the head one box of
-//              K and one of V (page_size x 64 elements, 128-byte swizzle), two tiles deep;
-//   warp 5     allocates the tensor memory; one lane issues S(j+1) = Q K(j+1)^T (M=128, N=64, K=16,
-//              head_dim/16 times) before it waits for P(j), so the score product of the next tile
-//              runs under the softmax of this one; then O += P(j) V(j) (M=128, N=head_dim, K=16, four
-//              times; V is read as stored, keys down the rows: an MN-major operand).
-// S is double-buffered in tensor memory (2 x 64 columns), O takes head_dim columns.
+//   producer   one lane issues the TMA loads: per page and 64-column half of the head one box of
+//              K and one of V (page_size x 64 elements, 128-byte swizzle);
+//   issuer     allocates the tensor memory; one lane issues S(j) = Q K(j)^T (M=128, N=64, K=16,
+//              head_dim/16 times) two tiles ahead of the softmax, and O += P(j) V(j) (M=128,
+//              N=head_dim, K=16, four times; V is read as stored, keys down the rows: an MN-major
+//              operand) when P(j) is written.  The products of one issuer run in the order issued, so
+//              S(j+2) overwrites the columns of P(j) only after P(j) V(j) has read them.  With two row
+//              tiles it serves whichever has an event pending, so one's products run under the
+//              other's softmax.
+// Per row tile S/P is double-buffered in tensor memory (2 x 64 columns) and O takes head_dim columns.
+// Nothing in the loop waits for a round trip: the softmax of tile j+1 needs S(j+1), issued long
+// before, and only a rescale of O waits for the product before it.
 //
 // What lies in the cache beyond a request's last key inside its last page, and in the part of a
 // stage that no page fills, meets a probability of exactly zero; it must be finite, so the stages
@@ -56,61 +64,84 @@ struct AttnTcParams {
   float scale_log2;              // scale * log2(e)
 };
 
-constexpr int TC_BM = 128, TC_BN = 64, TC_STAGES = 2, TC_THREADS = 192;
+constexpr int TC_BM = 128, TC_BN = 64;
 constexpr float TC_RESCALE_STEP = 8.0f;     // log2 units the maximum may lag behind before O is rescaled
 
-template <int HD> struct TcLayout {
+template <int HD, int RT> struct TcLayout {
   static constexpr int HALVES = HD / 64;
-  static constexpr int Q_BYTES = HALVES * TC_BM * 128;
+  static constexpr int STAGES = RT == 1 ? 2 : 4;
+  static constexpr int THREADS = 128 * RT + 64;
+  static constexpr int Q_BYTES = HALVES * TC_BM * 128;       // one row tile
   static constexpr int KV_BYTES = HALVES * TC_BN * 128;      // one of K or V, one stage
-  static constexpr int P_BYTES = TC_BM * 128;
-  static constexpr int K_OFF = Q_BYTES;
-  static constexpr int V_OFF = K_OFF + TC_STAGES * KV_BYTES;
-  static constexpr int P_OFF = V_OFF + TC_STAGES * KV_BYTES;
-  static constexpr int BAR_OFF = P_OFF + P_BYTES;
-  static constexpr int SMEM = BAR_OFF + 128;
-  static constexpr int TMEM_COLS = 256;                      // 2 x 64 (S) + HD (O), a power of two
+  static constexpr int K_OFF = RT * Q_BYTES;
+  static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
+  static constexpr int BAR_OFF = V_OFF + STAGES * KV_BYTES;
+  static constexpr int SMEM = BAR_OFF + 256;
+  static constexpr int TMEM_TILE = 256;                      // per row tile: 2 x 64 (S) + HD (O), a power of two
+  static constexpr int TMEM_COLS = RT * TMEM_TILE;
   static constexpr int O_COL = 2 * TC_BN;
 };
 
-template <int HD>
-__global__ void __launch_bounds__(TC_THREADS, 2)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int HD, int RT>
+__global__ void __launch_bounds__(TcLayout<HD, RT>::THREADS, RT == 1 ? 2 : 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                     const AttnTcParams p) {
-  using L = TcLayout<HD>;
+  using L = TcLayout<HD, RT>;
   constexpr int HALVES = L::HALVES;
   constexpr int CHUNKS = HD / 8;
+  constexpr int TC_STAGES = L::STAGES, TC_THREADS = L::THREADS;
+  constexpr int PRODUCER = 4 * RT, ISSUER = 4 * RT + 1;      // warp numbers
   extern __shared__ __align__(1024) unsigned char tc_smem[];
   unsigned char* smem = tc_smem;
-  uint64_t* full_kv = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);   // [2] a stage's K and V have landed
-  uint64_t* empty_kv = full_kv + 2;                                     // [2] P.V of the stage's tile is done
-  uint64_t* s_full = empty_kv + 2;                                      // [2] S buffer holds Q K^T
-  uint64_t* s_empty = s_full + 2;                                       // [2] the softmax warps have read it
-  uint64_t* p_full = s_empty + 2;                                       // P is written, O is rescaled
-  uint64_t* o_done = p_full + 1;                                        // P.V done: P may be rewritten, O read
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
+  uint64_t* full_kv = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);   // [STAGES] a stage's K and V have landed
+  uint64_t* empty_kv = full_kv + TC_STAGES;                             // [STAGES] P.V of the stage's tile is done
+  uint64_t* s_full = empty_kv + TC_STAGES;                              // [RT][2] S buffer holds Q K^T
+  uint64_t* p_full = s_full + 2 * RT;                                   // [RT][2] the buffer holds P, O is rescaled
+  uint64_t* o_done = p_full + 2 * RT;                                   // [RT] a P.V product is done
+  uint64_t* q_full = o_done + RT;                                       // [RT] the row tile's queries are in place
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + RT);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < TC_STAGES; ++s) {
       mbar_init(&full_kv[s], 1);
       mbar_init(&empty_kv[s], 1);
-      mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4);                  // the four softmax warps
     }
-    mbar_init(p_full, 4);
-    mbar_init(o_done, 1);
-    *failed = 0;
+    for (int s = 0; s < 2 * RT; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 4);                   // the four softmax warps of the row tile
+    }
+    for (int t = 0; t < RT; ++t) {
+      mbar_init(&o_done[t], 1);
+      mbar_init(&q_full[t], 4);
+    }
+    // a wait that ran out in another CTA voids the result anyway: the CTAs that start after it do nothing
+    *failed = *reinterpret_cast<volatile int*>(p.status);
+    if ((smem_u32(smem) & 1023u) != 0) {            // the swizzled layouts need a 1024-byte base
+      *failed = 20;
+      atomicExch(p.status, 20);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == ISSUER) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(L::TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   // the stages start as zeros (see the header)
   for (int o = tid * 16; o < 2 * TC_STAGES * L::KV_BYTES; o += TC_THREADS * 16)
     *reinterpret_cast<uint4*>(smem + L::K_OFF + o) = make_uint4(0, 0, 0, 0);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
 
   pdl_wait();       // everything below reads what the step's earlier kernels or its batch upload wrote
   const int seq = p.tile_seq[blockIdx.x], row0 = p.tile_row0[blockIdx.x];
@@ -119,34 +150,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   const int q0 = p.q_start[seq], q_len = p.q_start[seq + 1] - q0, ctx = p.ctx_len[seq];
   const int rows_total = q_len * G;
   const int pos0 = ctx - q_len;                  // position of the request's first token of this step
-  const int row_hi = min(row0 + TC_BM, rows_total);
-  const int key_hi = row_hi > row0 ? pos0 + (row_hi - 1) / G + 1 : 0;   // exclusive
+  // per row tile t: its keys end at key_end[t] (exclusive), in n_of[t] key tiles; later rows see more keys
+  int key_end[RT], n_of[RT];
+#pragma unroll
+  for (int t = 0; t < RT; ++t) {
+    const int lo = row0 + t * TC_BM, hi = min(lo + TC_BM, rows_total);
+    key_end[t] = hi > lo ? pos0 + (hi - 1) / G + 1 : 0;
+    n_of[t] = (key_end[t] + TC_BN - 1) / TC_BN;
+  }
+  const int key_hi = RT == 1 ? key_end[0] : max(key_end[0], key_end[RT - 1]);
   const int n_tiles = (key_hi + TC_BN - 1) / TC_BN;
   const int* bt = p.block_tables + (size_t)seq * p.max_pages;
 
-  // Q: rows of the tile into the swizzled K-major layout [half][row][128 bytes]
-  for (int c = tid; c < TC_BM * CHUNKS; c += TC_THREADS) {
-    const int r = c / CHUNKS, ch = c % CHUNKS;
-    const int row = row0 + r;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < rows_total) {
-      const int tok = row / G, hg = row % G;
-      v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(q0 + tok) * p.nq + kvh * G + hg) * HD + ch * 8);
-    }
-    *reinterpret_cast<uint4*>(smem + (ch >> 3) * (TC_BM * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = v;
-  }
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  if ((smem_u32(smem) & 1023u) != 0 && tid == 0) {      // the swizzled layouts need a 1024-byte base
-    *failed = 20;
-    atomicExch(p.status, 20);
-  }
-  __syncthreads();
-
-  if (warp == 4) {
+  if (warp == PRODUCER) {
     // ---------------- TMA producer ----------------
     if (lane == 0 && !*failed) {
       const int ps = p.page_size, per_tile = TC_BN / ps;
@@ -178,107 +194,167 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       if (*failed) {
         // let the copies already issued land before the CTA gives its shared memory back
         for (int i = issued > TC_STAGES ? issued - TC_STAGES : 0; i < issued; ++i)
-          mbar_wait(&full_kv[i % TC_STAGES], (i / TC_STAGES) & 1, 1u << 16);
+          mbar_wait(&full_kv[i % TC_STAGES], (i / TC_STAGES) & 1, TMA_DRAIN_NS);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == ISSUER) {
     // ---------------- MMA issuer ----------------
     if (lane == 0 && !*failed) {
       // D float32, A and B bfloat16; scores: both K-major, N = 64; output: B (V) MN-major, N = HD
       const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
       const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-      const uint32_t q_addr = smem_u32(smem), p_addr = smem_u32(smem + L::P_OFF);
       bool ok = true;
-      auto issue_scores = [&](int j) {
+      // scores of key tile j for row tile t (the stage is known to have landed)
+      auto issue_scores = [&](int j, int t) {
         const int s = j % TC_STAGES, b = j & 1;
-        if (!mbar_wait(&full_kv[s], (j / TC_STAGES) & 1) || !mbar_wait(&s_empty[b], ((j >> 1) & 1) ^ 1) || *failed) {
-          ok = false;
-          return;
-        }
         tc_fence_after();
         const uint32_t k_addr = smem_u32(smem + L::K_OFF + s * L::KV_BYTES);
+        const uint32_t q_addr = smem_u32(smem + t * L::Q_BYTES);
 #pragma unroll
         for (int h = 0; h < HALVES; ++h)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_base + b * TC_BN, umma_desc(q_addr + h * (TC_BM * 128) + k * 32),
+            umma_bf16(tmem_base + t * L::TMEM_TILE + b * TC_BN, umma_desc(q_addr + h * (TC_BM * 128) + k * 32),
                       umma_desc(k_addr + h * (TC_BN * 128) + k * 32), idesc_qk, (h | k) ? 1u : 0u);
-        umma_commit(&s_full[b]);
+        umma_commit(&s_full[t * 2 + b]);
       };
-      if (n_tiles > 0) issue_scores(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) issue_scores(j + 1);
-        if (!ok) break;
-        if (!mbar_wait(p_full, j & 1) || *failed) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const int s = j % TC_STAGES;
-        const uint32_t v_addr = smem_u32(smem + L::V_OFF + s * L::KV_BYTES);
+      // The row tiles are served as their events come, not in turn, so that one's products run under
+      // the other's softmax.  Per row tile: jq = next key tile whose scores are to be issued (at most
+      // two ahead of the softmax: S(j+2) goes into the columns P(j) V(j) has read), jp = next key tile
+      // whose P.V is to be issued (when its P is written).  A stage is handed back to the producer when
+      // every row tile that reaches its key tile has issued its P.V.
+      int jq[RT], jp[RT], q_ready[RT];
 #pragma unroll
-        for (int k = 0; k < TC_BN / 16; ++k)         // 16 keys: 32 bytes along P's rows, 16 rows of V
-          umma_bf16(tmem_base + L::O_COL, umma_desc(p_addr + k * 32), umma_desc_mn(v_addr + k * 16 * 128, TC_BN * 128),
-                    idesc_pv, (j | k) ? 1u : 0u);
-        umma_commit(&empty_kv[s]);
-        umma_commit(o_done);
+      for (int t = 0; t < RT; ++t) jq[t] = jp[t] = q_ready[t] = 0;
+      int released = 0;
+      uint64_t idle_since = 0;
+      uint32_t spins = 0;
+      while (ok) {
+        bool pending = false, progress = false;
+#pragma unroll
+        for (int t = 0; t < RT; ++t) {
+          if (jp[t] < n_of[t]) {
+            pending = true;
+            const int j = jp[t], s = j % TC_STAGES, b = j & 1;
+            if (mbar_test(&p_full[t * 2 + b], (j >> 1) & 1)) {
+              tc_fence_after();
+              const uint32_t v_addr = smem_u32(smem + L::V_OFF + s * L::KV_BYTES);
+              const uint32_t p_tmem = tmem_base + t * L::TMEM_TILE + b * TC_BN;
+#pragma unroll
+              for (int k = 0; k < TC_BN / 16; ++k)     // 16 keys: 8 columns of P, 16 rows of V
+                umma_bf16_ta(tmem_base + t * L::TMEM_TILE + L::O_COL, p_tmem + k * 8,
+                             umma_desc_mn(v_addr + k * 16 * 128, TC_BN * 128), idesc_pv, (j | k) ? 1u : 0u);
+              umma_commit(&o_done[t]);
+              jp[t] = j + 1;
+              progress = true;
+            }
+          }
+          if (jq[t] < n_of[t] && jq[t] < jp[t] + 2) {
+            const int j = jq[t];
+            if (!q_ready[t]) q_ready[t] = mbar_test(&q_full[t], 0);
+            if (q_ready[t] && mbar_test(&full_kv[j % TC_STAGES], (j / TC_STAGES) & 1)) {
+              issue_scores(j, t);
+              jq[t] = j + 1;
+              progress = true;
+            }
+          }
+        }
+        // stages that every row tile is done with
+        while (released < n_tiles) {
+          bool all = true;
+#pragma unroll
+          for (int t = 0; t < RT; ++t) all = all && (released >= n_of[t] || jp[t] > released);
+          if (!all) break;
+          umma_commit(&empty_kv[released % TC_STAGES]);
+          ++released;
+        }
+        if (!pending) break;
+        if (*failed) ok = false;
+        if (progress) {
+          idle_since = 0;
+          spins = 0;
+        } else if ((++spins & 255u) == 0) {
+          const uint64_t now = global_ns();
+          if (idle_since == 0) idle_since = now;
+          else if (now - idle_since > TMA_WAIT_NS) ok = false;
+        }
       }
       if (!ok && !*failed) { *failed = 22; atomicExch(p.status, 22); }
     }
   } else {
     // ---------------- softmax: thread r owns row r (TMEM lane r) ----------------
-    const int r = warp * 32 + lane;
-    const int row = row0 + r;
+    const int t = warp >> 2;                                           // row tile of this warp
+    const int r = (warp & 3) * 32 + lane;
+    const int row = row0 + t * TC_BM + r;
     const bool valid = row < rows_total;
-    const int hi = valid ? min(pos0 + row / G + 1, key_hi) : 0;       // keys [0, hi) are this row's
-    const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
-    unsigned char* p_row = smem + L::P_OFF + r * 128;
-    float m_used = -INFINITY, l = 0.f;
+    const int my_tiles = RT == 1 ? n_of[0] : (t == 0 ? n_of[0] : n_of[RT - 1]);
+    const int hi = valid ? pos0 + row / G + 1 : 0;                     // keys [0, hi) are this row's
+    const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + t * L::TMEM_TILE;
+    uint64_t* my_s_full = s_full + t * 2;
+    uint64_t* my_p_full = p_full + t * 2;
+    {
+      // the row tile's queries into the swizzled K-major layout [half][row][128 bytes]: all loads first
+      constexpr int ROWS_PER_IT = TC_BM / CHUNKS;
+      uint4 qv[CHUNKS];
+#pragma unroll
+      for (int it = 0; it < CHUNKS; ++it) {
+        const int qr = it * ROWS_PER_IT + r / CHUNKS, qrow = row0 + t * TC_BM + qr;
+        qv[it] = make_uint4(0, 0, 0, 0);
+        if (qrow < rows_total)
+          qv[it] = *reinterpret_cast<const uint4*>(p.q + ((size_t)(q0 + qrow / G) * p.nq + kvh * G + qrow % G) * HD + (r % CHUNKS) * 8);
+      }
+#pragma unroll
+      for (int it = 0; it < CHUNKS; ++it) {
+        const int qr = it * ROWS_PER_IT + r / CHUNKS, ch = r % CHUNKS;
+        *reinterpret_cast<uint4*>(smem + t * L::Q_BYTES + (ch >> 3) * (TC_BM * 128) + qr * 128 + (((ch & 7) ^ (qr & 7)) << 4)) = qv[it];
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_full[t]);
+    }
+    float m_used = -INFINITY, l = 0.f;                                 // the maximum in scaled (log2) units
     bool ok = !*failed;
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    for (int j = 0; j < my_tiles && ok; ++j) {
       const int b = j & 1;
-      if (!mbar_wait(&s_full[b], (j >> 1) & 1) || *failed) { ok = false; break; }
+      if (!mbar_wait(&my_s_full[b], (j >> 1) & 1) || *failed) { ok = false; break; }
       tc_fence_after();
       uint32_t s0[32], s1[32];
       tmem_ld32(t_lane + b * TC_BN, s0);
       tmem_ld32(t_lane + b * TC_BN + 32, s1);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[b]);
       const int kbase = j * TC_BN;
+      // the scale is positive, so the maximum of the scaled scores is the scaled maximum: the
+      // scaling itself is folded into the exponent's multiply-add below
       float mx = -INFINITY;
       if (__all_sync(0xffffffffu, kbase + TC_BN <= hi)) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float a = __uint_as_float(s0[i]) * p.scale_log2, c = __uint_as_float(s1[i]) * p.scale_log2;
-          s0[i] = __float_as_uint(a);
-          s1[i] = __float_as_uint(c);
-          mx = fmaxf(mx, fmaxf(a, c));
-        }
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float a = kbase + i < hi ? __uint_as_float(s0[i]) * p.scale_log2 : -INFINITY;
-          const float c = kbase + 32 + i < hi ? __uint_as_float(s1[i]) * p.scale_log2 : -INFINITY;
-          s0[i] = __float_as_uint(a);
-          s1[i] = __float_as_uint(c);
-          mx = fmaxf(mx, fmaxf(a, c));
+          if (kbase + i >= hi) s0[i] = 0xff800000u;          // -inf
+          if (kbase + 32 + i >= hi) s1[i] = 0xff800000u;
+          mx = fmaxf(mx, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
         }
       }
+      mx *= p.scale_log2;
       const bool grow = mx > m_used + TC_RESCALE_STEP;      // also the first tile with a key (m_used = -inf)
-      // P.V of the tile before must be done: it reads P, and O must not change under a rescale
-      if (j > 0) {
-        if (!mbar_wait(o_done, (j - 1) & 1) || *failed) { ok = false; break; }
-        tc_fence_after();
-      }
-      if (__any_sync(0xffffffffu, grow)) {
-        const float corr = grow ? exp2f(m_used - mx) : 1.f; // 0 when m_used = -inf (nothing summed yet)
+      // Every tile waits once for the product of the tile before it (phase j-1 of o_done; a parity
+      // names a phase only among two neighbours, so none may be skipped): before a rescale of O,
+      // which must not change under that product, else just before P is handed over, when the
+      // product is long done and the wait costs nothing.
+      const bool rescale = __any_sync(0xffffffffu, grow);
+      bool waited = false;
+      if (rescale) {
+        const float corr = grow ? ex2(m_used - mx) : 1.f;   // 0 when m_used = -inf (nothing summed yet)
         if (grow) {
           m_used = mx;
           l *= corr;
         }
         if (j > 0) {
+          if (!mbar_wait(&o_done[t], (j - 1) & 1) || *failed) { ok = false; break; }
+          waited = true;
+          tc_fence_after();
 #pragma unroll 1
           for (int c0 = 0; c0 < HD; c0 += 32) {
             uint32_t o[32];
@@ -291,29 +367,32 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
-      const float m_eff = m_used == -INFINITY ? 0.f : m_used;
+      const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+      uint32_t pk[32];                                      // column i: keys 2i (low half) and 2i+1
 #pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8) {
-        float e[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int idx = c8 * 8 + i;
-          e[i] = exp2f(__uint_as_float(idx < 32 ? s0[idx] : s1[idx - 32]) - m_eff);
-          l += e[i];
-        }
-        *reinterpret_cast<uint4*>(p_row + ((c8 ^ (r & 7)) << 4)) =
-            make_uint4(pack2(e[0], e[1]), pack2(e[2], e[3]), pack2(e[4], e[5]), pack2(e[6], e[7]));
+      for (int i = 0; i < 16; ++i) {
+        const float e0 = ex2(fmaf(__uint_as_float(s0[2 * i]), p.scale_log2, neg_m));
+        const float e1 = ex2(fmaf(__uint_as_float(s0[2 * i + 1]), p.scale_log2, neg_m));
+        const float e2 = ex2(fmaf(__uint_as_float(s1[2 * i]), p.scale_log2, neg_m));
+        const float e3 = ex2(fmaf(__uint_as_float(s1[2 * i + 1]), p.scale_log2, neg_m));
+        l += (e0 + e1) + (e2 + e3);
+        pk[i] = pack2(e0, e1);
+        pk[16 + i] = pack2(e2, e3);
       }
-      fence_async_smem();
+      tmem_st32(t_lane + b * TC_BN, pk);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      if (j > 0 && !waited) {
+        if (!mbar_wait(&o_done[t], (j - 1) & 1) || *failed) { ok = false; break; }
+      }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&my_p_full[b]);
     }
-    if (ok && n_tiles > 0) {
-      if (!mbar_wait(o_done, (n_tiles - 1) & 1) || *failed) ok = false;
+    if (ok && my_tiles > 0) {
+      if (!mbar_wait(&o_done[t], (my_tiles - 1) & 1) || *failed) ok = false;
     }
     if (!ok && !*failed) { *failed = 23; atomicExch(p.status, 23); }
-    if (ok && n_tiles > 0) {
+    if (ok && my_tiles > 0) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* po = nullptr;
@@ -338,7 +417,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   tc_fence_before();
   __syncthreads();
   pdl_launch_dependents();
-  if (warp == 5) {
+  if (warp == ISSUER) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS));
   }
@@ -374,19 +453,19 @@ static bool tc_cache_map(const void* base, long long rows, int ps, int hd, CUten
   return true;
 }
 
-template <int HD>
+template <int HD, int RT>
 static int launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, int tiles, cudaStream_t stream) {
-  constexpr int smem = TcLayout<HD>::SMEM;
+  constexpr int smem = TcLayout<HD, RT>::SMEM;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attention_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+    if (cudaFuncSetAttribute(attention_tc_kernel<HD, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
       set_error("attention_tc: cannot raise the shared memory limit");
       return SLLM_ERR_LAUNCH;
     }
     configured = true;
   }
   dim3 grid(tiles, p.nkv);
-  launch_kernel(attention_tc_kernel<HD>, grid, TC_THREADS, (size_t)smem, stream, mk, mv, p);
+  launch_kernel(attention_tc_kernel<HD, RT>, grid, TcLayout<HD, RT>::THREADS, (size_t)smem, stream, mk, mv, p);
   return launch_status("attention_tc");
 }
 
@@ -399,17 +478,20 @@ SLLM_EXPORT int sllm_attention_tc_supports(int hd, int page_size) {
   return (hd == 64 || hd == 128) && page_size >= 8 && page_size <= 64 && 64 % page_size == 0 && encode_fn() != nullptr;
 }
 
-// The prefill form: tiles of up to 128 (token, head-in-group) rows, no window, no context split.
+// The prefill form: tiles of up to 128 * row_tiles (token, head-in-group) rows (row_tiles 1 or 2; tile_row0
+// in steps of that many rows), no window, no context split.
 // num_pages: pages in the cache tensors [num_pages, nkv, page_size, hd].  status: one int of device
 // memory, zero before the launch; non-zero afterwards means a wait ran out and `out` is not valid.
 SLLM_EXPORT int sllm_attention_tc(const void* q, const void* k_cache, const void* v_cache, long long num_pages, void* out,
                                   const int* block_tables, int max_pages, const int* q_start, const int* ctx_len,
-                                  const int* tile_seq, const int* tile_row0, int tiles, int nq, int nkv, int hd,
-                                  int page_size, float scale, int* status, cudaStream_t stream) {
+                                  const int* tile_seq, const int* tile_row0, int tiles, int row_tiles, int nq, int nkv,
+                                  int hd, int page_size, float scale, int* status, cudaStream_t stream) {
+  SLLM_REQUIRE(row_tiles == 1 || row_tiles == 2, "attention_tc: row_tiles=%d must be 1 or 2", row_tiles);
   SLLM_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tc: bad head counts nq=%d nkv=%d", nq, nkv);
   SLLM_REQUIRE(sllm_attention_tc_supports(hd, page_size), "attention_tc: head_dim=%d page_size=%d not taken", hd, page_size);
   SLLM_REQUIRE(max_pages > 0 && tiles >= 0 && num_pages > 0 && nkv <= 65535, "attention_tc: bad sizes");
   SLLM_REQUIRE(status != nullptr, "attention_tc: a status word is required");
+  SLLM_REQUIRE(scale > 0.f, "attention_tc: the score scale must be positive (the row maximum is taken before scaling)");
   SLLM_REQUIRE(((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 && ((uintptr_t)q & 15) == 0 &&
                    ((uintptr_t)out & 15) == 0, "attention_tc: operands must be 16-byte aligned");
   if (tiles == 0) return SLLM_OK;
@@ -423,5 +505,7 @@ SLLM_EXPORT int sllm_attention_tc(const void* q, const void* k_cache, const void
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.block_tables = block_tables; p.q_start = q_start;
   p.ctx_len = ctx_len; p.tile_seq = tile_seq; p.tile_row0 = tile_row0; p.status = status; p.max_pages = max_pages;
   p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.scale_log2 = scale * 1.4426950408889634f;
-  return hd == 128 ? launch_tc<128>(mk, mv, p, tiles, stream) : launch_tc<64>(mk, mv, p, tiles, stream);
+  if (row_tiles == 2)
+    return hd == 128 ? launch_tc<128, 2>(mk, mv, p, tiles, stream) : launch_tc<64, 2>(mk, mv, p, tiles, stream);
+  return hd == 128 ? launch_tc<128, 1>(mk, mv, p, tiles, stream) : launch_tc<64, 1>(mk, mv, p, tiles, stream);
 }

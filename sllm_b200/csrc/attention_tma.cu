@@ -380,7 +380,7 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __syncthreads();
   pdl_launch_dependents();
   if (*failed && tid == 0) {
-    for (int s = 0; s < TA_STAGES; ++s) mbar_wait(&full[s], 0, 1u << 14);
+    for (int s = 0; s < TA_STAGES; ++s) mbar_wait(&full[s], 0, TMA_DRAIN_NS);
   }
 }
 

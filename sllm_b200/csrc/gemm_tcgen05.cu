@@ -105,7 +105,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (*failed) {
         // let the copies already issued land before the CTA gives its shared memory back
         for (int i = issued > TG_STAGES ? issued - TG_STAGES : 0; i < issued; ++i)
-          mbar_wait(&full[i % TG_STAGES], (i / TG_STAGES) & 1, 1u << 16);
+          mbar_wait(&full[i % TG_STAGES], (i / TG_STAGES) & 1, TMA_DRAIN_NS);
       }
     }
   } else if (warp == 1) {

@@ -1,5 +1,5 @@
 // TMA and mbarrier helpers shared by the kernels that are fed by the tensor memory accelerator.
-// Every wait is bounded: mbar_wait gives up after `limit` polls and says so.
+// Every wait is bounded in time: mbar_wait gives up after `limit_ns` nanoseconds and says so.
 #pragma once
 
 #include <cuda.h>
@@ -8,7 +8,8 @@
 
 namespace sllm {
 
-constexpr uint32_t TMA_WAIT_LIMIT = 1u << 24;            // polls before a wait gives up (tens of ms)
+constexpr uint64_t TMA_WAIT_NS = 1000000000ull;          // a wait gives up after a second
+constexpr uint64_t TMA_DRAIN_NS = 1000000ull;            // waiting for copies in flight after a failure: a millisecond
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -21,10 +22,16 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// false if the phase did not complete within `limit` polls
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = TMA_WAIT_LIMIT) {
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// false if the phase did not complete within `limit_ns` (the clock is read every 256 polls)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns = TMA_WAIT_NS) {
   const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < limit; ++i) {
+  uint64_t start = 0;
+  for (uint32_t i = 0;; ++i) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -32,8 +39,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
     if (ok) return true;
+    if ((i & 255u) == 255u) {
+      const uint64_t now = global_ns();
+      if (start == 0) start = now;
+      else if (now - start > limit_ns) return false;
+    }
   }
-  return false;
+}
+// one test of the phase that never suspends the thread
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
 }
 __device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(

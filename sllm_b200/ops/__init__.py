@@ -9,6 +9,8 @@ float32 path, runs in this package's own kernels.
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ._lib import KernelError, call, launches, lib  # noqa: F401
@@ -319,10 +321,11 @@ def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, n
 NUM_SMS = 148
 
 
-def attention_tiles(q_lens, group_size: int, device, ctx_lens=None):
-    """Tiles of (token, head-in-group) rows for the tensor-core attention kernel: requests
-    whose rows fit one 16-row tile go to the decode form, the others are cut into 128-row
-    tiles for the prefill form.  Returns ``(small, large)``, each ``None`` or
+def attention_tiles(q_lens, group_size: int, device, ctx_lens=None, large_rows: int = 128):
+    """Tiles of (token, head-in-group) rows for the tensor-core attention kernels: requests
+    whose rows fit one 16-row tile go to the decode form, the others are cut into tiles of
+    `large_rows` rows (128, or 256 for the tcgen05 form with two row tiles a CTA) for the
+    prefill form.  Returns ``(small, large)``, each ``None`` or
     ``(tile_seq, tile_row0, count)`` on the device."""
     small_s, large_s, large_r = [], [], []
     ctx_before = [(c - n) for c, n in zip(ctx_lens, q_lens)] if ctx_lens else [0] * len(q_lens)
@@ -331,7 +334,7 @@ def attention_tiles(q_lens, group_size: int, device, ctx_lens=None):
         if rows <= 16:
             small_s.append(s)
         else:
-            for r0 in range(0, rows, 128):
+            for r0 in range(0, rows, large_rows):
                 large_s.append(s)
                 large_r.append(r0)
 
@@ -403,20 +406,25 @@ def attention_tma_decode(q, k_cache, v_cache, block_tables, q_start, ctx_len, ti
     return out
 
 
+_TC_ATTENTION = os.environ.get("SLLM_ATTENTION_TCGEN05", "1") != "0"     # 0: prompt portions on the mma.sync form
+
+
 def tc_attention_supports(hd: int, page_size: int) -> bool:
     return bool(lib().sllm_attention_tc_supports(int(hd), int(page_size)))
 
 
-def attention_tc(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, nq, nkv, hd, scale, out=None):
-    """The prefill form on tcgen05 (128-row tiles; no window, no context split; see `attention_tiles`)."""
+def attention_tc(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, nq, nkv, hd, scale, out=None,
+                 row_tiles: int = 1):
+    """The prefill form on tcgen05 (tiles of 128 * row_tiles rows, row_tiles 1 or 2; no window, no
+    context split; see `attention_tiles`)."""
     _chk(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles[0], tiles[1])
     if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
         raise KernelError("attention_tc: bfloat16 only")
     if out is None:
         out = torch.empty_like(q)
     call("sllm_attention_tc", _p(q), _p(k_cache), _p(v_cache), k_cache.shape[0], _p(out), _p(block_tables),
-         block_tables.shape[1], _p(q_start), _p(ctx_len), _p(tiles[0]), _p(tiles[1]), tiles[2], nq, nkv, hd,
-         k_cache.shape[2], float(scale), _p(_status_word(q.device)), _stream())
+         block_tables.shape[1], _p(q_start), _p(ctx_len), _p(tiles[0]), _p(tiles[1]), tiles[2], int(row_tiles), nq, nkv,
+         hd, k_cache.shape[2], float(scale), _p(_status_word(q.device)), _stream())
     _tc_used["since_check"] += 1
     return out
 
@@ -434,12 +442,18 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
         return attention_simt(q, k_cache, v_cache, g.block_tables, step.positions, step.seq_of_token,
                               nq, nkv, hd, scale, window)
     G = nq // nkv
-    key = ("mma", G)
+    use_tc = not window and _TC_ATTENTION and tc_attention_supports(hd, k_cache.shape[2])
+    key = ("mma", G, nkv, use_tc)
     if key not in step.attn_tiles:
-        small, large = attention_tiles(step.q_lens, G, q.device, step.ctx_lens)
+        # two row tiles a CTA (one CTA per SM) once such CTAs fill the GPU twice (measured: 235 against
+        # 245 us for 4096 tokens of 28/4 heads, but 102 against 100 us for 2048), else 128-row CTAs, two per SM
+        rows = 128
+        if use_tc and sum(-(-n * G // 256) for n in step.q_lens if n * G > 16) * nkv >= 2 * NUM_SMS:
+            rows = 256
+        small, large = attention_tiles(step.q_lens, G, q.device, step.ctx_lens, rows)
         splits = choose_splits(small[2], nkv, step.max_ctx_len) if (small and not large) else 1
-        step.attn_tiles[key] = (small, large, splits)
-    small, large, splits = step.attn_tiles[key]
+        step.attn_tiles[key] = (small, large, splits, rows)
+    small, large, splits, rows = step.attn_tiles[key]
     out = torch.empty_like(q)
     if small and tma_attention_supports(hd, k_cache.shape[2]):
         attention_tma_decode(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, splits,
@@ -447,8 +461,9 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
     elif small:
         attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, True, splits,
                       nq, nkv, hd, scale, window, out)
-    if large and not window and tc_attention_supports(hd, k_cache.shape[2]):
-        attention_tc(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, nq, nkv, hd, scale, out)
+    if large and use_tc:
+        attention_tc(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, nq, nkv, hd, scale, out,
+                     row_tiles=rows // 128)
     elif large:
         attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, False, 1,
                       nq, nkv, hd, scale, window, out)

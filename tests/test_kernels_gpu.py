@@ -311,7 +311,8 @@ def test_attention_mma(nq, nkv, hd, ps, window, case):
 
 @pytest.mark.parametrize("nq,nkv,hd,ps", [(28, 4, 128, 16), (14, 2, 64, 16), (8, 8, 128, 8), (6, 1, 64, 32), (4, 2, 128, 64)])
 @pytest.mark.parametrize("case", ["prefill", "long", "mixed", "peaked"])
-def test_attention_tc(nq, nkv, hd, ps, case):
+@pytest.mark.parametrize("row_tiles", [1, 2])
+def test_attention_tc(nq, nkv, hd, ps, case, row_tiles):
     """The tcgen05 prefill form against the float32 statement: portions that start in mid-context, rows
     of several requests, many key tiles, and scores so peaked that the running maximum jumps from tile
     to tile (the output in tensor memory is rescaled)."""
@@ -326,12 +327,12 @@ def test_attention_tc(nq, nkv, hd, ps, case):
     scale = 1.0 if case == "peaked" else hd ** -0.5
     want = ref.attention_simt(q.float(), kc.float(), vc.float(), bt, pos, seq, nq, nkv, hd, scale, None)
     G = nq // nkv
-    small, large = ops.attention_tiles(q_lens, G, "cuda")
+    small, large = ops.attention_tiles(q_lens, G, "cuda", lens, 128 * row_tiles)
     out = torch.full_like(q, float("nan"))
     if small:
         ops.attention_mma(q, kc, vc, bt, q_start, ctx_len, small, True, 1, nq, nkv, hd, scale, None, out)
     assert large
-    ops.attention_tc(q, kc, vc, bt, q_start, ctx_len, large, nq, nkv, hd, scale, out)
+    ops.attention_tc(q, kc, vc, bt, q_start, ctx_len, large, nq, nkv, hd, scale, out, row_tiles=row_tiles)
     ops.check_tcgen05_status()
     assert not out.isnan().any(), "a row was not written"
     torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
@@ -351,8 +352,9 @@ def test_attention_tc_far_key_and_page_edges():
         direction /= direction.norm()
         kc[page, :, off, :] = (direction * 16).bfloat16()
         q[:] = (direction * 16).repeat(nq).bfloat16()
-        _, large = ops.attention_tiles([n], nq // nkv, "cuda")
-        got = ops.attention_tc(q, kc, vc, bt, q_start, ctx_len, large, nq, nkv, hd, 1.0)
+        row_tiles = 1 + (far % 2)
+        _, large = ops.attention_tiles([n], nq // nkv, "cuda", [n], 128 * row_tiles)
+        got = ops.attention_tc(q, kc, vc, bt, q_start, ctx_len, large, nq, nkv, hd, 1.0, row_tiles=row_tiles)
         ops.check_tcgen05_status()
         # queries at or after the far key return its value; the ones before it cannot see it
         want = vc[page, :, off, :].float().repeat_interleave(nq // nkv, dim=0)
