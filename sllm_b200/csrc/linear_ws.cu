@@ -12,7 +12,9 @@
 //   store      out[M, N] (+ bias), float32 or bfloat16
 //   residual   residual[M, N] += y (+ bias): the float32 stream is updated in place, so the next
 //              norm has nothing to add
-// N/16 CTAs (224 at N = 3584) keep every SM busy without splitting K over the grid.
+// About N/16 CTAs keep every SM busy without splitting K over the grid; their number is rounded up
+// to a multiple of the SM count and the rows dealt evenly (N = 3584: 296 CTAs of 12 or 13 rows
+// instead of 224 of 16, of which 76 SMs would get two and 72 one).
 //
 // The reference calls cublasGemmEx for these products and adds the residual in its next
 // add_rms kernel (kernels/cuda/kernels.cu:752-767, 791-839; kernels/device_decode.py:312-325).
@@ -55,10 +57,12 @@ linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
   __shared__ float red[WS_WARPS][16][8 * NT + 1];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
-  const int n0 = blockIdx.x * 16;
+  // the CTA's rows [n0, n1): at most 16, the N rows dealt evenly over the grid (so that a grid of a
+  // whole number of CTAs per SM gives every SM the same bytes to stream)
+  const int n0 = (int)(((long long)blockIdx.x * N) / gridDim.x), n1 = (int)(((long long)(blockIdx.x + 1) * N) / gridDim.x);
   const int k_blocks = K / 32;
 
-  const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);     // rows past N: clamped loads, skipped stores
+  const int r0 = min(n0 + g, n1 - 1), r1 = min(n0 + g + 8, n1 - 1);   // rows past the CTA's: clamped loads, skipped stores
   const __nv_bfloat16* w0 = W + (size_t)r0 * K + t4 * 8;
   const __nv_bfloat16* w1 = W + (size_t)r1 * K + t4 * 8;
   const __nv_bfloat16* xr[NT];
@@ -132,7 +136,7 @@ linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
   for (int idx = tid; idx < 16 * 8 * NT; idx += WS_WARPS * 32) {
     const int row = idx % 16, tok = idx / 16;           // consecutive threads -> consecutive rows of one token
     const int n = n0 + row;
-    if (tok >= M || n >= N) continue;
+    if (tok >= M || n >= n1) continue;
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < WS_WARPS; ++w) v += red[w][row][tok];
@@ -145,7 +149,19 @@ linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
 template <int NT, int EPI, typename OUT>
 static int launch_ws(const __nv_bfloat16* x, const __nv_bfloat16* W, const float* bias, void* out, float* residual,
                      int M, int N, int K, cudaStream_t stream) {
-  launch_kernel(linear_ws_kernel<NT, EPI, OUT>, (N + 15) / 16, WS_WARPS * 32, 0, stream, x, W, bias, (OUT*)out, residual, M, N, K);
+  // CTAs of 16 rows, or, when those would fill the SMs unevenly, the next multiple of the SM count
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
+  }
+  int ctas = (N + 15) / 16;
+  if (ctas > num_sms && ctas % num_sms != 0) {
+    const int even = (ctas + num_sms - 1) / num_sms * num_sms;
+    if (even <= N) ctas = even;
+  }
+  launch_kernel(linear_ws_kernel<NT, EPI, OUT>, ctas, WS_WARPS * 32, 0, stream, x, W, bias, (OUT*)out, residual, M, N, K);
   return launch_status("linear_ws");
 }
 
