@@ -409,6 +409,15 @@ def attention_tma_decode(q, k_cache, v_cache, block_tables, q_start, ctx_len, ti
 _TC_ATTENTION = os.environ.get("SLLM_ATTENTION_TCGEN05", "1") != "0"     # 0: prompt portions on the mma.sync form
 
 
+def wait_probe(limit_ns: int, device="cuda"):
+    """Run the kernel that waits on a barrier nothing arrives at (see csrc/wait_probe.cu); returns
+    ``(status, waited_ns)``: 99 and about ``limit_ns`` when the bounded wait gave up as it must."""
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    waited = torch.zeros(1, dtype=torch.int64, device=device)
+    call("sllm_wait_probe", _p(status), int(limit_ns), _p(waited), _stream())
+    return int(status.item()), int(waited.item())
+
+
 def tc_attention_supports(hd: int, page_size: int) -> bool:
     return bool(lib().sllm_attention_tc_supports(int(hd), int(page_size)))
 

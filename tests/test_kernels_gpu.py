@@ -338,6 +338,19 @@ def test_attention_tc(nq, nkv, hd, ps, case, row_tiles):
     torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
 
 
+def test_a_wait_that_nothing_ends_gives_up_and_says_so():
+    """The bounded wait of the TMA-fed kernels: a barrier nothing arrives at, a limit of 3 ms; the kernel
+    returns with its status word set, in about that time, and the device goes on working."""
+    ops = _ops()
+    status, waited = ops.wait_probe(3_000_000)
+    assert status == 99
+    assert 3_000_000 <= waited < 50_000_000
+    x = torch.arange(1000, device="cuda", dtype=torch.float32)
+    assert float(x.sum()) == 499500.0
+    with pytest.raises(ops.KernelError):
+        ops.wait_probe(10 ** 9)             # longer than the probe allows: refused on the host
+
+
 def test_attention_tc_far_key_and_page_edges():
     """One key stands out for every query, at page and tile edges of a long prompt."""
     ops = _ops()
