@@ -341,6 +341,7 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
 template <int HD>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                          __nv_bfloat16* __restrict__ out, int rows, int num_splits) {
+  pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
   const int row = blockIdx.x;
   float mt = -INFINITY;

@@ -387,6 +387,7 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 template <int HD>
 __global__ void attention_tma_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                              __nv_bfloat16* __restrict__ out, int rows, int num_splits) {
+  pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
   const int row = blockIdx.x;
   float mt = -INFINITY;

@@ -29,6 +29,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
     "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
 ]
+NVCC_FLAGS += os.environ.get("SLLM_NVCC_EXTRA", "").split()     # e.g. -DSLLM_PDL_EARLY=1 for an experiment
 
 
 def sources() -> list[str]:

@@ -29,6 +29,7 @@ bool pdl_enabled() {
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int H, int V) {
+  pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
   const int t = blockIdx.x;
   int id = ids[t];
@@ -67,6 +68,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
                                    size_t part_stride, const float* __restrict__ w, float eps,
                                    TO* __restrict__ out, int H) {
   __shared__ float red[33];
+  pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
   const size_t base = (size_t)blockIdx.x * H;
   float ss = 0.f;
@@ -112,6 +114,7 @@ template <typename TD, typename TO, int VPT>
 __global__ void add_rmsnorm_rows_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
                                         const float* __restrict__ w, float eps, TO* __restrict__ out, int H) {
   __shared__ float red[33];
+  pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
   const size_t base = (size_t)blockIdx.x * H;
   float4 v[VPT];
@@ -152,6 +155,7 @@ __global__ void add_rmsnorm_rows_kernel(float* __restrict__ residual, const TD* 
 // ---------------------------------------------------------------------------
 template <typename TI, typename TO>
 __global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int I, int blk, size_t n) {
+  pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n) return;
@@ -167,6 +171,7 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out,
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, int parts, size_t part_stride,
                                    const int* __restrict__ rows, T* __restrict__ out, int H, int n_src) {
+  pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
   int r = rows[blockIdx.x];
   r = r < 0 ? 0 : (r >= n_src ? n_src - 1 : r);
@@ -201,6 +206,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int parts, size
                                      int rot, int max_pos, int nq, int nkv, int hd, int hpb,
                                      const int* __restrict__ slot_mapping, int page_size, int num_pages,
                                      TC* __restrict__ k_cache, TC* __restrict__ v_cache, TC* __restrict__ q_out) {
+  pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
   const int t = blockIdx.x;
   const int heads = nq + 2 * nkv;
@@ -265,6 +271,7 @@ __global__ void rope_kv_write_vec_kernel(const TI* __restrict__ qkv, const float
                                          const int* __restrict__ slot_mapping, int page_size, int num_pages,
                                          __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                                          __nv_bfloat16* __restrict__ q_out) {
+  pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
   const int t = blockIdx.x;
   const int heads = nq + 2 * nkv;

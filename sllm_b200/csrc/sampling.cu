@@ -96,6 +96,7 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
   __shared__ double sh_d[33];
   __shared__ double warp_tot[32];
   __shared__ int found;
+  pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
   const float* row = logits + (size_t)blockIdx.x * V;
   const MaxIdx mx = block_argmax(row, V, sh_mi);
