@@ -13,6 +13,8 @@ decides how many ways the attention kernel splits the context.
 
 from __future__ import annotations
 
+import gc
+
 import numpy as np
 import torch
 
@@ -202,9 +204,18 @@ class DecodeGraphs:
             gr.launches = ops.launches["own"] - before
             ids_now = gr.ids.cpu().tolist()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                logits = eng.model.forward(gr.ctx, eng.layer_caches)
-                gr.ids = ops.sample_rows(logits, gr.temps, gr.uniforms)
+            # Nothing may free device memory or destroy a graph while the capture runs: a collection
+            # of garbage (an engine dropped earlier, say) in the middle of it would invalidate it.
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    logits = eng.model.forward(gr.ctx, eng.layer_caches)
+                    gr.ids = ops.sample_rows(logits, gr.temps, gr.uniforms)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             ops.launches["own"] -= gr.launches          # capturing launched nothing
             gr.graph = graph
             # the graph's own output buffer must hold this step's ids for a step chained behind it

@@ -338,6 +338,33 @@ def test_pipelined_decode_equals_unpipelined(tiny):
     assert outs[0][2][0] == plain.generate(prompts[2], 11, w, cfg, temperature=0.7, seed=3)
 
 
+def test_graph_capture_survives_garbage_of_earlier_engines(tiny):
+    """Engines made and dropped one after the other, with the collector set to run all the time: the
+    capture of a decode graph must not be invalidated by the collection of an earlier engine's graphs
+    and buffers in the middle of it."""
+    import gc
+    from sllm_b200.engine import build_model
+    from sllm_b200.engine.llm import LLM
+    from sllm_b200.sampling import SamplingParams
+    dev = cuda_or_skip()
+    name, model_dir, page = tiny
+    cfg, w = plain.load_model(model_dir)
+    model, _ = build_model(model_dir, "float32", dev)
+    prompts = _prompts(cfg, (7, 12), seed=21)
+    want = [plain.generate(p, 6, w, cfg) for p in prompts]
+    old = gc.get_threshold()
+    gc.set_threshold(1, 1, 1)
+    try:
+        for _ in range(4):
+            llm = LLM(model=model, block_size=page, num_pages=32, max_num_seqs=2)
+            res = llm.generate(prompts, SamplingParams(max_new=6))
+            assert [r.ids for r in res] == want
+            assert llm.engine.graphs.graphs, "the decode steps ran without a graph"
+            del llm, res
+    finally:
+        gc.set_threshold(*old)
+
+
 def test_toy_routed_feed_forward_and_learned_positions(tmp_path):
     """Two more parts defined here and nowhere in the package: a feed-forward that routes each
     token to one of four small experts (router logits and their softmax in float32), and a position
