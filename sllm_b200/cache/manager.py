@@ -46,6 +46,8 @@ class CacheManager:
             raise ValueError("page_size must be >= 1")
         self.page_size = int(page_size)
         self.max_requests = int(max_requests)
+        # one state slot beyond the requests': rows that pad a batch to a captured size use it
+        self.padding_slot = self.max_requests
         self.needs = list(needs)
         self.groups: list[CacheGroup] = []
         self.run_group: dict[int, int] = {}        # run -> group (owning runs)
@@ -202,7 +204,7 @@ class CacheManager:
             shape = (len(g.runs), 2, max(g.pool.capacity, 1), g.need.num_kv_heads, self.page_size, g.need.head_dim)
             self.kv_storage.append(torch.zeros(shape, dtype=dtype, device=device))
         self.state_storage = {
-            run: torch.zeros((max(self.max_requests, 1),) + tuple(s.shape), dtype=torch.float32, device=device)
+            run: torch.zeros((self.max_requests + 1,) + tuple(s.shape), dtype=torch.float32, device=device)
             for run, s in self.state_runs.items()}
         caches: list[LayerCache] = []
         for run, (how, what) in enumerate(self.needs):

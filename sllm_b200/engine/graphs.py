@@ -9,6 +9,13 @@ slots, block tables, temperatures, uniforms), copies it to the graph's static de
 buffer and launches the graph.  Kernels read lengths and tables from device memory,
 so nothing about a request's context is baked into the graph except the bucket that
 decides how many ways the attention kernel splits the context.
+
+A capture costs tens of milliseconds, so batch sizes are rounded up to a few sizes
+(`DecodeGraphs.batch_bucket`) and the rows beyond the live requests are padding: token 0
+at position 0 with no context, no page to write to (slot -1: the rotary kernel skips the
+write, the attention kernels find no key) and the cache's spare state slot; what the
+padding rows sample is dropped.  A decode step is bound by reading the weights, which the
+padding does not add to.
 """
 
 from __future__ import annotations
@@ -28,6 +35,7 @@ def _pad4(n: int) -> int:
 
 class _Graph:
     def __init__(self, engine, B: int, bucket: int):
+        """``B``: rows of the captured step (live requests plus padding)."""
         cache = engine.cache
         self.B = B
         ps = cache.page_size
@@ -92,6 +100,7 @@ class _Graph:
         ps = cache.page_size
         B = self.B
         tok, pos, ctx, slots = (self._hsec(k) for k in ("token_ids", "positions", "ctx_len", "state_slots"))
+        n = len(entries)
         for i, (e, tot) in enumerate(zip(entries, totals)):
             req = cache.requests[e.req_id]
             tok[i] = e.tokens[0] if not tokens_on_device else 0
@@ -102,15 +111,26 @@ class _Graph:
                 table = req.tables[gi]
                 bt = self._hsec(f"block_tables{gi}")
                 row = bt[i * self.cap_pages:(i + 1) * self.cap_pages]
-                n = len(table)
-                row[:n] = table
-                row[n:] = -1
+                m = len(table)
+                row[:m] = table
+                row[m:] = -1
                 page = table[(tot - 1) // ps]
                 if page < 0:
                     raise RuntimeError(f"request {e.req_id!r}: a token would be written to a page given back")
                 self._hsec(f"slot_mapping{gi}")[i] = page * ps + (tot - 1) % ps
-        self._hsec("temps").view(np.float32)[:] = temperatures
-        self._hsec("uniforms").view(np.float64)[:] = uniforms
+        if n < B:                                    # padding rows: no context, nothing written, the spare state slot
+            tok[n:] = 0
+            pos[n:] = 0
+            ctx[n:] = 0
+            slots[n:] = cache.padding_slot
+            for gi in range(len(cache.groups)):
+                self._hsec(f"block_tables{gi}")[n * self.cap_pages:] = -1
+                self._hsec(f"slot_mapping{gi}")[n:] = -1
+        t_host, u_host = self._hsec("temps").view(np.float32), self._hsec("uniforms").view(np.float64)
+        t_host[:n] = temperatures
+        u_host[:n] = uniforms
+        t_host[n:] = 0.0
+        u_host[n:] = 0.0
         self.dev.copy_(self.host, non_blocking=True)
         if tokens_on_device:
             self._dsec("token_ids").copy_(self.ids)          # after the host's copy, before the replay
@@ -119,8 +139,8 @@ class _Graph:
 class Launched:
     """A decode step that has been queued on the device and whose ids have not been read yet."""
 
-    def __init__(self, graph, turn, ids_now=None):
-        self.graph, self.turn, self.ids_now = graph, turn, ids_now
+    def __init__(self, graph, turn, ids_now=None, n=None):
+        self.graph, self.turn, self.ids_now, self.n = graph, turn, ids_now, n
 
 
 class DecodeGraphs:
@@ -134,6 +154,19 @@ class DecodeGraphs:
         while b < max_ctx:
             b *= 2
         return b
+
+    @staticmethod
+    def batch_bucket(n: int) -> int:
+        """Rows of the graph that serves ``n`` requests: n up to 4, then 6, 8, 12, 16, 24, 32, ...
+        (at most a third of the rows are padding)."""
+        if n <= 4:
+            return n
+        b = 4
+        while True:
+            for c in (b + b // 2, 2 * b):
+                if c >= n:
+                    return c
+            b *= 2
 
     def step(self, entries, temperatures, uniforms, device_timer=None):
         """Launch and read one decode step (see `launch`, `read`)."""
@@ -152,7 +185,7 @@ class DecodeGraphs:
             if req is None or req.num_tokens + 1 > eng.max_positions:
                 return False
             totals.append(req.num_tokens + 1)
-        gr = self.graphs.get((len(entries), self.bucket(max(totals))))
+        gr = self.graphs.get((self.batch_bucket(len(entries)), self.bucket(max(totals))))
         if gr is None or gr.graph is None:
             return False
         return all(cache.can_reserve(e.req_id, t) for e, t in zip(entries, totals))
@@ -186,7 +219,7 @@ class DecodeGraphs:
                 raise OutOfPages(f"step needs {need} pages in group {gi}, {g.pool.free_count} free")
         for e, t in zip(entries, totals):
             cache.reserve(e.req_id, t)
-        key = (len(entries), self.bucket(max(totals)))
+        key = (self.batch_bucket(len(entries)), self.bucket(max(totals)))
         gr = self.graphs.get(key)
         if gr is None:
             gr = self.graphs[key] = _Graph(eng, *key)
@@ -202,11 +235,11 @@ class DecodeGraphs:
             logits = eng.model.forward(gr.ctx, eng.layer_caches)
             gr.ids = ops.sample_rows(logits, gr.temps, gr.uniforms)
             gr.launches = ops.launches["own"] - before
-            ids_now = gr.ids.cpu().tolist()
+            ids_now = gr.ids.cpu().tolist()[:len(entries)]
             graph = torch.cuda.CUDAGraph()
             # Nothing may free device memory or destroy a graph while the capture runs: a collection
             # of garbage (an engine dropped earlier, say) in the middle of it would invalidate it.
-            gc.collect()
+            # (torch's graph context collects once before it begins; here the collector stays off.)
             gc_was_on = gc.isenabled()
             gc.disable()
             try:
@@ -219,7 +252,7 @@ class DecodeGraphs:
             ops.launches["own"] -= gr.launches          # capturing launched nothing
             gr.graph = graph
             # the graph's own output buffer must hold this step's ids for a step chained behind it
-            gr.ids.copy_(torch.tensor(ids_now, dtype=torch.int32, device=eng.device))
+            gr.ids[:len(ids_now)].copy_(torch.tensor(ids_now, dtype=torch.int32, device=eng.device))
         else:
             gr.graph.replay()
             ops.launches["own"] += gr.launches
@@ -230,7 +263,7 @@ class DecodeGraphs:
         for e, t in zip(entries, totals):
             cache.commit(e.req_id, t)
         eng.steps_run += 1
-        return Launched(gr, gr.turn, ids_now)
+        return Launched(gr, gr.turn, ids_now, len(entries))
 
     def read(self, h: Launched) -> list:
         """The ids a launched step sampled (waits for that step, not for any queued behind it)."""
@@ -238,7 +271,7 @@ class DecodeGraphs:
             out = h.ids_now
         else:
             h.graph.ids_ready[h.turn].synchronize()
-            out = h.graph.ids_host[h.turn].tolist()
+            out = h.graph.ids_host[h.turn].tolist()[:h.n]
         if self.engine.steps_run % 64 == 0:
             ops.check_tcgen05_status()      # a wait that ran out inside a TMA-fed kernel, if any
         return out

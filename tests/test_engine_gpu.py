@@ -338,6 +338,35 @@ def test_pipelined_decode_equals_unpipelined(tiny):
     assert outs[0][2][0] == plain.generate(prompts[2], 11, w, cfg, temperature=0.7, seed=3)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_graphs_pad_the_batch_to_a_captured_size(tiny, dtype):
+    """Five and seven live requests run on the graphs of six and eight rows: the padding rows write
+    nothing, and the live rows' tokens are those of each request alone."""
+    from sllm_b200.engine import build_model
+    from sllm_b200.engine.graphs import DecodeGraphs
+    from sllm_b200.engine.llm import LLM
+    from sllm_b200.sampling import SamplingParams
+    dev = cuda_or_skip()
+    name, model_dir, page = tiny
+    cfg, w = plain.load_model(model_dir)
+    assert [DecodeGraphs.batch_bucket(n) for n in (1, 4, 5, 7, 9, 13, 17, 33)] == [1, 4, 6, 8, 12, 16, 24, 48]
+    model, _ = build_model(model_dir, dtype, dev)
+    prompts = _prompts(cfg, (5, 9, 14, 3, 21, 8, 11), seed=33)
+    llm = LLM(model=model, block_size=page, num_pages=96, max_num_seqs=7, chunk_size=64)
+    # requests end at different times: 7 live, then 5, then fewer
+    params = [SamplingParams(max_new=n) for n in (12, 12, 12, 12, 12, 4, 4)]
+    res = llm.generate(prompts, params)
+    sizes = sorted({k[0] for k in llm.engine.graphs.graphs})
+    assert 8 in sizes and 6 in sizes and 7 not in sizes and 5 not in sizes
+    llm.engine.cache.check()
+    for p, sp, r in zip(prompts, params, res):
+        want = plain.generate(p, sp.max_new, w, cfg)
+        if dtype == "float32":
+            assert r.ids == want
+        else:
+            assert r.ids[:2] == want[:2] and len(r.ids) == sp.max_new
+
+
 def test_graph_capture_survives_garbage_of_earlier_engines(tiny):
     """Engines made and dropped one after the other, with the collector set to run all the time: the
     capture of a decode graph must not be invalidated by the collection of an earlier engine's graphs
