@@ -47,11 +47,13 @@ def test_wide_layers_all_cuttings(wide_model, dtype):
     spread = float(np.concatenate([v.ravel() for v in want.values()]).std())
     tol = dict(rtol=1e-4, atol=1e-4) if dtype == "float32" else dict(rtol=2e-2, atol=0.08 * spread)
     model, _ = build_model(model_dir, dtype, dev)
-    for mode in ("whole", "tail_decode", "portions", "mixed"):
+    # pages of 16 tokens, and in bfloat16 of 64 too (one TMA box per page in the attention kernels)
+    for mode, ps in [(m, 16) for m in ("whole", "tail_decode", "portions", "mixed")] + \
+                    ([(m, 64) for m in ("whole", "tail_decode", "mixed")] if dtype == "bfloat16" else []):
         tr = getattr(traces, mode)(reqs)
-        eng = Engine(model, page_size=16, num_pages=tr.max_tokens // 16, max_requests=4)
+        eng = Engine(model, page_size=ps, num_pages=tr.max_tokens // ps, max_requests=4)
         out = traces.replay_engine(tr, eng)
-        traces.compare(tr, out, want, what=f"wide/{dtype}/{mode}", **tol)
+        traces.compare(tr, out, want, what=f"wide/{dtype}/{mode}/pages of {ps}", **tol)
         if dtype == "bfloat16":
             sq = [(out[st["step"]][i] - want[r][p]) ** 2 for st in tr.steps for i, (r, p) in enumerate(st["expect"])]
             assert float(np.sqrt(np.mean(sq))) <= 0.02 * spread
