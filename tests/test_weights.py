@@ -140,3 +140,27 @@ def test_missing_folder_and_shards(tmp_path):
     os.remove(os.path.join(d, "model.safetensors"))
     model, _ = build_model(d, "float32", "cpu")
     assert model.embedding.shape == (256, 64)
+
+
+def test_upload_is_refused_when_the_device_has_no_room(monkeypatch):
+    """The guard before the upload: the bytes come from the tensor specs, the free bytes from the device
+    (a fake here); too little room is a MemoryError that says how much is needed and how much is free."""
+    import torch
+    from sllm_b200.engine import loading
+    from sllm_b200.config.registry import architecture_of
+    from sllm_b200.models.causal_lm import CausalLM
+    cfg = dict(TINY_A)
+    arch = architecture_of(cfg)
+    model = CausalLM(arch.plan(arch.config_cls.from_dict(cfg)), dtype=torch.bfloat16, device="cpu")
+    need = loading.resident_bytes(model)
+    specs = model.tensor_specs()
+    by_hand = sum(int(torch.tensor(s.shape).prod()) * (4 if s.role in ("gain", "bias") else 2) for s in specs)
+    assert need == by_hand and need > 0
+    loading.check_device_memory(model)                      # a CPU model: nothing to check
+    model.device = torch.device("cuda:0")
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda dev=None: (need + loading.SLACK_BYTES - 1, 10 * need))
+    with pytest.raises(MemoryError) as e:
+        loading.check_device_memory(model)
+    assert "GiB" in str(e.value) and "free" in str(e.value)
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda dev=None: (need + loading.SLACK_BYTES, 10 * need))
+    loading.check_device_memory(model)
