@@ -61,6 +61,7 @@ struct AttnTcParams {
   const int* tile_row0;          // [tiles]
   int* status;
   int max_pages, page_size, nq, nkv;
+  int page_runs;                 // the run maps are valid: a key tile whose pages have consecutive ids is one box of K and one of V
   float scale_log2;              // scale * log2(e)
 };
 
@@ -91,6 +92,7 @@ __device__ __forceinline__ float ex2(float x) {
 template <int HD, int RT>
 __global__ void __launch_bounds__(TcLayout<HD, RT>::THREADS, RT == 1 ? 2 : 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                    const __grid_constant__ CUtensorMap run_k, const __grid_constant__ CUtensorMap run_v,
                     const AttnTcParams p) {
   using L = TcLayout<HD, RT>;
   constexpr int HALVES = L::HALVES;
@@ -175,9 +177,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         }
         const int kbase = j * TC_BN;
         const int pages = min(per_tile, (key_hi - kbase + ps - 1) / ps);
-        mbar_expect_tx(&full_kv[s], (uint32_t)(pages * 2 * HALVES * ps * 128));
         unsigned char* ks = smem + L::K_OFF + s * L::KV_BYTES;
         unsigned char* vs = smem + L::V_OFF + s * L::KV_BYTES;
+        // a tile whose pages have consecutive ids is one box of K and one of V (the run maps walk the
+        // pages with a stride of their own): the TMA unit's time goes by the box, not by the byte
+        const int first_pi = kbase / ps;
+        bool run = p.page_runs && pages == per_tile && first_pi + per_tile <= p.max_pages && bt[first_pi] >= 0;
+        for (int i = 1; run && i < per_tile; ++i) run = bt[first_pi + i] == bt[first_pi] + i;
+        if (run) {
+          mbar_expect_tx(&full_kv[s], (uint32_t)(2 * L::KV_BYTES));
+          tma_load_5d(ks, &run_k, 0, 0, bt[first_pi], 0, kvh, &full_kv[s]);
+          tma_load_5d(vs, &run_v, 0, 0, bt[first_pi], 0, kvh, &full_kv[s]);
+          issued = j + 1;
+          continue;
+        }
+        mbar_expect_tx(&full_kv[s], (uint32_t)(pages * 2 * HALVES * ps * 128));
         for (int i = 0; i < pages; ++i) {
           const int pi = kbase / ps + i;
           int page = pi < p.max_pages ? bt[pi] : 0;
@@ -427,34 +441,41 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 
 // tensor maps of the caches seen so far: (base, rows, page size, head size) -> map
 struct TcMapKey {
-  const void* base; long long rows; int ps, hd;
-  bool operator==(const TcMapKey& o) const { return base == o.base && rows == o.rows && ps == o.ps && hd == o.hd; }
+  const void* base; long long rows; int ps, hd, nkv_run;      // nkv_run: 0 for the per-page map, else the kv heads of the run map
+  bool operator==(const TcMapKey& o) const {
+    return base == o.base && rows == o.rows && ps == o.ps && hd == o.hd && nkv_run == o.nkv_run;
+  }
 };
 struct TcMapKeyHash {
   size_t operator()(const TcMapKey& k) const {
-    return std::hash<const void*>()(k.base) ^ (std::hash<long long>()(k.rows) * 31) ^ (size_t)(k.ps * 131 + k.hd);
+    return std::hash<const void*>()(k.base) ^ (std::hash<long long>()(k.rows) * 31) ^ (size_t)(k.ps * 131 + k.hd + k.nkv_run * 7919);
   }
 };
 static std::unordered_map<TcMapKey, CUtensorMap, TcMapKeyHash> g_tc_maps;
 static std::mutex g_tc_maps_mutex;
 
-static bool tc_cache_map(const void* base, long long rows, int ps, int hd, CUtensorMap* out) {
+static bool tc_cache_map(const void* base, long long rows, int ps, int hd, CUtensorMap* out, int nkv_run = 0) {
   std::lock_guard<std::mutex> lock(g_tc_maps_mutex);
-  TcMapKey key{base, rows, ps, hd};
+  TcMapKey key{base, rows, ps, hd, nkv_run};
   auto it = g_tc_maps.find(key);
   if (it != g_tc_maps.end()) {
     *out = it->second;
     return true;
   }
   if (rows > 0x7fffffffLL) return false;
-  if (!make_map(out, base, (int)rows, hd, ps)) return false;
+  if (nkv_run == 0) {
+    if (!make_map(out, base, (int)rows, hd, ps)) return false;
+  } else {
+    if (!make_map_page_run(out, base, rows / ((long long)nkv_run * ps), nkv_run, ps, hd, TC_BN / ps, false)) return false;
+  }
   if (g_tc_maps.size() > 4096) g_tc_maps.clear();
   g_tc_maps.emplace(key, *out);
   return true;
 }
 
 template <int HD, int RT>
-static int launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, int tiles, cudaStream_t stream) {
+static int launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& rk, const CUtensorMap& rv,
+                     const AttnTcParams& p, int tiles, cudaStream_t stream) {
   constexpr int smem = TcLayout<HD, RT>::SMEM;
   static bool configured = false;
   if (!configured) {
@@ -465,7 +486,7 @@ static int launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcP
     configured = true;
   }
   dim3 grid(tiles, p.nkv);
-  launch_kernel(attention_tc_kernel<HD, RT>, grid, TcLayout<HD, RT>::THREADS, (size_t)smem, stream, mk, mv, p);
+  launch_kernel(attention_tc_kernel<HD, RT>, grid, TcLayout<HD, RT>::THREADS, (size_t)smem, stream, mk, mv, rk, rv, p);
   return launch_status("attention_tc");
 }
 
@@ -501,11 +522,15 @@ SLLM_EXPORT int sllm_attention_tc(const void* q, const void* k_cache, const void
     set_error("attention_tc: cuTensorMapEncodeTiled failed");
     return SLLM_ERR_LAUNCH;
   }
+  CUtensorMap rk = mk, rv = mv;
+  const bool runs = page_size < TC_BN && tc_cache_map(k_cache, rows, page_size, hd, &rk, nkv) &&
+                    tc_cache_map(v_cache, rows, page_size, hd, &rv, nkv);
   AttnTcParams p;
+  p.page_runs = runs ? 1 : 0;
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.block_tables = block_tables; p.q_start = q_start;
   p.ctx_len = ctx_len; p.tile_seq = tile_seq; p.tile_row0 = tile_row0; p.status = status; p.max_pages = max_pages;
   p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.scale_log2 = scale * 1.4426950408889634f;
   if (row_tiles == 2)
-    return hd == 128 ? launch_tc<128, 2>(mk, mv, p, tiles, stream) : launch_tc<64, 2>(mk, mv, p, tiles, stream);
-  return hd == 128 ? launch_tc<128, 1>(mk, mv, p, tiles, stream) : launch_tc<64, 1>(mk, mv, p, tiles, stream);
+    return hd == 128 ? launch_tc<128, 2>(mk, mv, rk, rv, p, tiles, stream) : launch_tc<64, 2>(mk, mv, rk, rv, p, tiles, stream);
+  return hd == 128 ? launch_tc<128, 1>(mk, mv, rk, rv, p, tiles, stream) : launch_tc<64, 1>(mk, mv, rk, rv, p, tiles, stream);
 }

@@ -47,6 +47,7 @@ struct AttnTmaParams {
   const int* tile_row0;          // [tiles]
   int* status;
   int max_pages, page_size, nq, nkv, window, num_splits, total_tokens;
+  int page_runs;                 // the run maps are valid: a tile of pages with consecutive ids is fetched as one box
   float scale_log2;
 };
 
@@ -62,6 +63,7 @@ __device__ __forceinline__ int swz(int row, int chunk) {
 template <int HD>
 __global__ void __launch_bounds__(TA_THREADS)
 attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const __grid_constant__ CUtensorMap run_k, const __grid_constant__ CUtensorMap run_v,
                             const AttnTmaParams p) {
   constexpr int STRIDE = HD + 8;
   constexpr int KSTEPS = HD / 16;
@@ -156,7 +158,15 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
       }
-      if (lane == 0) {
+      // a tile whose pages have consecutive ids is one box of K and one of V (the page dimension of
+      // the run maps has its own stride); the TMA unit's time goes by the box, not by the byte
+      bool run = p.page_runs && valid == (1u << pages_per_tile) - 1;
+      for (int i = 1; run && i < pages_per_tile; ++i) run = page_of(page0 + i) == page_of(page0) + i;
+      if (lane == 0 && run) {
+        mbar_expect_tx(&full[s], (uint32_t)(2 * KV_BYTES));
+        tma_load_5d(ks, &run_k, 0, 0, 0, kvh, page_of(page0), &full[s]);
+        tma_load_5d(vs, &run_v, 0, 0, 0, kvh, page_of(page0), &full[s]);
+      } else if (lane == 0) {
         const uint32_t bytes = (uint32_t)__popc(valid) * ps * HD * 2 * 2;
         if (bytes == 0) {
           mbar_arrive(&full[s]);
@@ -410,34 +420,42 @@ __global__ void attention_tma_combine_kernel(const float* __restrict__ part_o, c
 
 // tensor maps of the caches seen so far: (base, rows, page size, head size) -> map
 struct MapKey {
-  const void* base; long long rows; int ps, hd;
-  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && ps == o.ps && hd == o.hd; }
+  const void* base; long long rows; int ps, hd, nkv_run;      // nkv_run: 0 for the per-page map, else the kv heads of the run map
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && ps == o.ps && hd == o.hd && nkv_run == o.nkv_run;
+  }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.base) ^ (std::hash<long long>()(k.rows) * 31) ^ (size_t)(k.ps * 131 + k.hd);
+    return std::hash<const void*>()(k.base) ^ (std::hash<long long>()(k.rows) * 31) ^ (size_t)(k.ps * 131 + k.hd + k.nkv_run * 7919);
   }
 };
 static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 static std::mutex g_maps_mutex;
 
-static bool cache_map(const void* base, long long rows, int ps, int hd, CUtensorMap* out) {
+// nkv_run == 0: the map of one page a box; else the map whose box is the TA_BN / ps pages of a tile with consecutive ids
+static bool cache_map(const void* base, long long rows, int ps, int hd, CUtensorMap* out, int nkv_run = 0) {
   std::lock_guard<std::mutex> lock(g_maps_mutex);
-  MapKey key{base, rows, ps, hd};
+  MapKey key{base, rows, ps, hd, nkv_run};
   auto it = g_maps.find(key);
   if (it != g_maps.end()) {
     *out = it->second;
     return true;
   }
   if (rows > 0x7fffffffLL) return false;
-  if (!make_map_rows(out, base, rows, hd / 64, ps)) return false;
+  if (nkv_run == 0) {
+    if (!make_map_rows(out, base, rows, hd / 64, ps)) return false;
+  } else {
+    if (!make_map_page_run(out, base, rows / ((long long)nkv_run * ps), nkv_run, ps, hd, TA_BN / ps, true)) return false;
+  }
   if (g_maps.size() > 4096) g_maps.clear();
   g_maps.emplace(key, *out);
   return true;
 }
 
 template <int HD>
-static int launch_ta(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTmaParams& p, int tiles, cudaStream_t stream) {
+static int launch_ta(const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& rk, const CUtensorMap& rv,
+                     const AttnTmaParams& p, int tiles, cudaStream_t stream) {
   constexpr size_t smem = (size_t)TA_STAGES * 2 * TA_BN * HD * 2 + 16 * (HD + 8) * 2 + 2 * TA_STAGES * 8 + 16 +
                           TA_BT_CACHE * 4 + 1024;
   static bool configured = false;
@@ -449,7 +467,7 @@ static int launch_ta(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTma
     configured = true;
   }
   dim3 grid(tiles, p.nkv, p.num_splits);
-  launch_kernel(attention_tma_decode_kernel<HD>, grid, TA_THREADS, smem, stream, mk, mv, p);
+  launch_kernel(attention_tma_decode_kernel<HD>, grid, TA_THREADS, smem, stream, mk, mv, rk, rv, p);
   int rc = launch_status("attention_tma");
   if (rc != SLLM_OK) return rc;
   if (p.num_splits > 1) {
@@ -491,10 +509,16 @@ SLLM_EXPORT int sllm_attention_tma_decode(const void* q, const void* k_cache, co
     set_error("attention_tma: cuTensorMapEncodeTiled failed");
     return SLLM_ERR_LAUNCH;
   }
+  // the maps whose box is a whole tile's pages, for tiles whose pages have consecutive ids (not needed
+  // when a page is a tile already)
+  CUtensorMap rk = mk, rv = mv;
+  const bool runs = page_size < TA_BN && cache_map(k_cache, rows, page_size, hd, &rk, nkv) &&
+                    cache_map(v_cache, rows, page_size, hd, &rv, nkv);
   AttnTmaParams p;
+  p.page_runs = runs ? 1 : 0;
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.part_o = part_o; p.part_lse = part_lse;
   p.block_tables = block_tables; p.q_start = q_start; p.ctx_len = ctx_len; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
   p.status = status; p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.window = window;
   p.num_splits = num_splits; p.total_tokens = total_tokens; p.scale_log2 = scale * 1.4426950408889634f;
-  return hd == 128 ? launch_ta<128>(mk, mv, p, tiles, stream) : launch_ta<64>(mk, mv, p, tiles, stream);
+  return hd == 128 ? launch_ta<128>(mk, mv, rk, rv, p, tiles, stream) : launch_ta<64>(mk, mv, rk, rv, p, tiles, stream);
 }

@@ -107,6 +107,39 @@ inline bool make_map_rows(CUtensorMap* map, const void* base, long long rows, in
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The paged cache [pages][kv heads][page_size][hd] bfloat16 seen as a 5-d tensor whose last dimension
+// walks the pages: one box then takes `run_pages` pages with CONSECUTIVE IDS of one kv head (they are
+// not adjacent in memory; the page dimension has its own stride).  rows_major: the box lands as
+// [page][row][half][64] (the decode kernel's tile layout); else as [half][page][row][64] (the K-major
+// operand layout of the tcgen05 kernel).  128-byte swizzle either way.
+inline bool make_map_page_run(CUtensorMap* map, const void* base, long long num_pages, int nkv, int ps, int hd, int run_pages,
+                              bool rows_major) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t halves = (cuuint64_t)hd / 64, row_b = (cuuint64_t)hd * 2, head_b = row_b * ps, page_b = head_b * nkv;
+  cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+  if (rows_major) {
+    cuuint64_t dims[5] = {64, halves, (cuuint64_t)ps, (cuuint64_t)nkv, (cuuint64_t)num_pages};
+    cuuint64_t strides[4] = {128, row_b, head_b, page_b};
+    cuuint32_t box[5] = {64, (cuuint32_t)halves, (cuuint32_t)ps, 1, (cuuint32_t)run_pages};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
+  cuuint64_t dims[5] = {64, (cuuint64_t)ps, (cuuint64_t)num_pages, halves, (cuuint64_t)nkv};
+  cuuint64_t strides[4] = {row_b, page_b, 128, head_b};
+  cuuint32_t box[5] = {64, (cuuint32_t)ps, (cuuint32_t)run_pages, (cuuint32_t)halves, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+__device__ __forceinline__ void tma_load_5d(void* smem, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+
 __device__ __forceinline__ void tma_load_3d(void* smem, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"

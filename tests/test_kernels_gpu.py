@@ -157,11 +157,14 @@ def test_rope_kv_write_wide_form(in_dtype, T, nq, nkv, hd, rot, ps):
     assert not k2.any() and not v2.any()
 
 
-def _paged_case(g, lens, q_lens, nq, nkv, hd, ps, dtype, spare_pages=3):
-    """Random cache content for requests of `lens` tokens whose last `q_lens` are queries."""
+def _paged_case(g, lens, q_lens, nq, nkv, hd, ps, dtype, spare_pages=3, consecutive=False):
+    """Random cache content for requests of `lens` tokens whose last `q_lens` are queries; their pages
+    scattered over the pool, or (`consecutive`) each request's pages with consecutive ids."""
     S = len(lens)
     n_pages = sum(-(-n // ps) for n in lens) + spare_pages
     perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(9)).tolist()
+    if consecutive:
+        perm = list(range(n_pages - 1, -1, -1))           # popped from the end: 0, 1, 2, ...
     kc = torch.randn(n_pages, nkv, ps, hd, device="cuda", generator=g).to(dtype)
     vc = torch.randn(n_pages, nkv, ps, hd, device="cuda", generator=g).to(dtype)
     max_pages = max(-(-n // ps) for n in lens)
@@ -312,7 +315,8 @@ def test_attention_mma(nq, nkv, hd, ps, window, case):
 @pytest.mark.parametrize("nq,nkv,hd,ps", [(28, 4, 128, 16), (14, 2, 64, 16), (8, 8, 128, 8), (6, 1, 64, 32), (4, 2, 128, 64)])
 @pytest.mark.parametrize("case", ["prefill", "long", "mixed", "peaked"])
 @pytest.mark.parametrize("row_tiles", [1, 2])
-def test_attention_tc(nq, nkv, hd, ps, case, row_tiles):
+@pytest.mark.parametrize("consecutive", [False, True])
+def test_attention_tc(nq, nkv, hd, ps, case, row_tiles, consecutive):
     """The tcgen05 prefill form against the float32 statement: portions that start in mid-context, rows
     of several requests, many key tiles, and scores so peaked that the running maximum jumps from tile
     to tile (the output in tensor memory is rescaled)."""
@@ -322,7 +326,7 @@ def test_attention_tc(nq, nkv, hd, ps, case, row_tiles):
     g = torch.Generator(device="cuda").manual_seed(21)
     lens, q_lens = {"prefill": ([70, 33, 200], [70, 5, 131]), "long": ([1000, 2100], [1000, 300]),
                     "mixed": ([90, 400, 2, 65, 129], [37, 1, 2, 1, 128]), "peaked": ([700], [650])}[case]
-    q, kc, vc, bt, pos, seq = _paged_case(g, lens, q_lens, nq, nkv, hd, ps, torch.bfloat16)
+    q, kc, vc, bt, pos, seq = _paged_case(g, lens, q_lens, nq, nkv, hd, ps, torch.bfloat16, consecutive=consecutive)
     q_start, ctx_len = _starts(q_lens, lens)
     scale = 1.0 if case == "peaked" else hd ** -0.5
     want = ref.attention_simt(q.float(), kc.float(), vc.float(), bt, pos, seq, nq, nkv, hd, scale, None)
@@ -501,9 +505,11 @@ def test_linear_ws(M, N, K):
 @pytest.mark.parametrize("nq,nkv,hd,ps,window", [(28, 4, 128, 16, None), (14, 2, 64, 16, None), (8, 1, 128, 32, 40),
                                                  (6, 3, 64, 8, 9), (16, 2, 128, 64, None), (7, 7, 64, 16, None)])
 @pytest.mark.parametrize("case", ["decode", "decode_split", "short"])
-def test_attention_tma_decode(nq, nkv, hd, ps, window, case):
+@pytest.mark.parametrize("consecutive", [False, True])
+def test_attention_tma_decode(nq, nkv, hd, ps, window, case, consecutive):
     """The TMA-fed decode form against the float32 statement: contexts that end inside a page and
-    inside a tile, requests shorter than a tile (slots without a page), split contexts, a window."""
+    inside a tile, requests shorter than a tile (slots without a page), split contexts, a window;
+    pages scattered (a box a page) and with consecutive ids (a box a tile)."""
     ops = _ops()
     assert ops.tma_attention_supports(hd, ps)
     g = torch.Generator(device="cuda").manual_seed(18)
@@ -511,7 +517,7 @@ def test_attention_tma_decode(nq, nkv, hd, ps, window, case):
     q_lens = [1] * len(lens)
     if case == "short" and nq // nkv <= 8:
         q_lens[0] = 2                                   # two tokens of one request still fit a 16-row tile
-    q, kc, vc, bt, pos, seq = _paged_case(g, lens, q_lens, nq, nkv, hd, ps, torch.bfloat16)
+    q, kc, vc, bt, pos, seq = _paged_case(g, lens, q_lens, nq, nkv, hd, ps, torch.bfloat16, consecutive=consecutive)
     # poison what lies outside the requests' pages: a kernel that read it would show NaN
     q_start, ctx_len = _starts(q_lens, lens)
     scale = hd ** -0.5
