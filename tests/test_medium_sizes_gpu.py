@@ -1,0 +1,61 @@
+"""Three configurations between the tiny ones and the benchmark's, against the plain implementation,
+in float32 and bfloat16, all four ways of cutting, pages of 16 and of 64 tokens: head size 64 with a
+group of 3 and an odd vocabulary (tied head); head size 128 with as many kv heads as query heads, a
+width of 1000 and an intermediate width of 2744; and the Qwen2.5-0.5B sizes, two layers deep (group of
+7, head size 64, vocabulary 151936).  They reach the kernels the tiny configurations do not (the
+tcgen05 and TMA attention forms at head size 64, the streaming products at widths that are no power
+of two) with other head counts and groups than the benchmark's."""
+
+import numpy as np
+import pytest
+
+from tests import traces
+from tests.conftest import cuda_or_skip
+from tests.plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+BASE = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu"}
+MEDIUM = {
+    "group3_hd64_tied": dict(BASE, num_hidden_layers=3, hidden_size=768, num_attention_heads=12, num_key_value_heads=4,
+                             head_dim=64, intermediate_size=2048, vocab_size=50257, rope_theta=10000.0,
+                             rms_norm_eps=1e-5, max_position_embeddings=2048, tie_word_embeddings=True),
+    "mha_hd128_odd_widths": dict(BASE, num_hidden_layers=2, hidden_size=1000, num_attention_heads=10,
+                                 num_key_value_heads=10, head_dim=128, intermediate_size=2744, vocab_size=32003,
+                                 rope_theta=500000.0, rms_norm_eps=1e-6, max_position_embeddings=4096,
+                                 tie_word_embeddings=False),
+    "qwen2.5_0.5b_widths": dict(BASE, num_hidden_layers=2, hidden_size=896, num_attention_heads=14,
+                                num_key_value_heads=2, head_dim=64, intermediate_size=4864, vocab_size=151936,
+                                rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=32768,
+                                tie_word_embeddings=True),
+}
+
+
+@pytest.mark.parametrize("name", sorted(MEDIUM))
+def test_medium_sizes_all_cuttings(name, tmp_path):
+    from sllm_b200.engine import Engine, build_model
+    from sllm_b200.weights import write_random_model
+    dev = cuda_or_skip()
+    cfg = MEDIUM[name]
+    d = str(tmp_path / "model")
+    write_random_model(d, cfg, 5 + sorted(MEDIUM).index(name), std=0.03, bias_std=0.2, gain_std=0.1)
+    c, w = plain.load_model(d)
+    rng = np.random.default_rng(17)
+    reqs = {f"r{i}": rng.integers(0, cfg["vocab_size"], n).tolist() for i, n in enumerate((150, 37, 260))}
+    want = {r: plain.forward(ids, w, c) for r, ids in reqs.items()}
+    spread = float(np.concatenate([v.ravel() for v in want.values()]).std())
+    for dtype in ("float32", "bfloat16"):
+        # bfloat16: bounds relative to the logits' spread, as for the benchmark's widths (measured here:
+        # rms error 0.6 % of the spread, largest single error 5 %)
+        tol = dict(rtol=1e-4, atol=1e-4) if dtype == "float32" else dict(rtol=2e-2, atol=0.08 * spread)
+        model, _ = build_model(d, dtype, dev)
+        for ps in ((8,) if dtype == "float32" else (16, 64)):
+            for mode in ("whole", "tail_decode", "portions", "mixed"):
+                tr = getattr(traces, mode)(reqs)
+                eng = Engine(model, page_size=ps, num_pages=-(-tr.max_tokens // ps), max_requests=4)
+                out = traces.replay_engine(tr, eng)
+                traces.compare(tr, out, want, what=f"{name}/{dtype}/{mode}/pages of {ps}", **tol)
+                if dtype == "bfloat16":
+                    sq = [(out[st["step"]][i] - want[r][p]) ** 2 for st in tr.steps for i, (r, p) in enumerate(st["expect"])]
+                    assert float(np.sqrt(np.mean(sq))) <= 0.02 * spread
+                assert not eng.cache.requests
