@@ -27,7 +27,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: Qwen2.5-7B sizes
+# the baseline's third configuration: Qwen2.5-7B sizes
 CONFIG_7B = {
     "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
     "num_hidden_layers": 28, "hidden_size": 3584, "num_attention_heads": 28, "num_key_value_heads": 4,

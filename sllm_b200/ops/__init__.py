@@ -443,9 +443,11 @@ def mma_supports(hd: int) -> bool:
 
 
 def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, window):
-    """Causal attention of the step's tokens over their requests' pages.  bfloat16 with a
-    head size the tensor-core kernel takes: that kernel (prompt portions in 64-row tiles,
-    decoded tokens in the split-KV form).  Otherwise the CUDA-core kernel."""
+    """Causal attention of the step's tokens over their requests' pages.  bfloat16 with a head size
+    the tensor-core kernels take: requests of at most 16 (token, head-in-group) rows go to the decode
+    form (fed by TMA where the head and page sizes allow, split over the context), the others to the
+    prefill form in 128-row tiles (on tcgen05 where there is no window and the sizes allow, else on
+    mma.sync).  Otherwise the CUDA-core kernel."""
     g = step.groups[group]
     if q.dtype != torch.bfloat16 or not mma_supports(hd):
         return attention_simt(q, k_cache, v_cache, g.block_tables, step.positions, step.seq_of_token,
