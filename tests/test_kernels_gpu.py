@@ -163,7 +163,14 @@ def _paged_case(g, lens, q_lens, nq, nkv, hd, ps, dtype, spare_pages=3, consecut
     S = len(lens)
     n_pages = sum(-(-n // ps) for n in lens) + spare_pages
     perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(9)).tolist()
-    if consecutive:
+    if consecutive == "runs":
+        # runs of six consecutive ids, the runs in scrambled order: some key tiles lie inside a run
+        # (one box), some straddle two (a box a page)
+        ids = list(range(n_pages))
+        blocks = [ids[i:i + 6] for i in range(0, n_pages, 6)]
+        order = torch.randperm(len(blocks), generator=torch.Generator().manual_seed(10)).tolist()
+        perm = [x for b in order for x in blocks[b]][::-1]
+    elif consecutive:
         perm = list(range(n_pages - 1, -1, -1))           # popped from the end: 0, 1, 2, ...
     kc = torch.randn(n_pages, nkv, ps, hd, device="cuda", generator=g).to(dtype)
     vc = torch.randn(n_pages, nkv, ps, hd, device="cuda", generator=g).to(dtype)
@@ -315,7 +322,7 @@ def test_attention_mma(nq, nkv, hd, ps, window, case):
 @pytest.mark.parametrize("nq,nkv,hd,ps", [(28, 4, 128, 16), (14, 2, 64, 16), (8, 8, 128, 8), (6, 1, 64, 32), (4, 2, 128, 64)])
 @pytest.mark.parametrize("case", ["prefill", "long", "mixed", "peaked"])
 @pytest.mark.parametrize("row_tiles", [1, 2])
-@pytest.mark.parametrize("consecutive", [False, True])
+@pytest.mark.parametrize("consecutive", [False, True, "runs"])
 def test_attention_tc(nq, nkv, hd, ps, case, row_tiles, consecutive):
     """The tcgen05 prefill form against the float32 statement: portions that start in mid-context, rows
     of several requests, many key tiles, and scores so peaked that the running maximum jumps from tile
@@ -505,7 +512,7 @@ def test_linear_ws(M, N, K):
 @pytest.mark.parametrize("nq,nkv,hd,ps,window", [(28, 4, 128, 16, None), (14, 2, 64, 16, None), (8, 1, 128, 32, 40),
                                                  (6, 3, 64, 8, 9), (16, 2, 128, 64, None), (7, 7, 64, 16, None)])
 @pytest.mark.parametrize("case", ["decode", "decode_split", "short"])
-@pytest.mark.parametrize("consecutive", [False, True])
+@pytest.mark.parametrize("consecutive", [False, True, "runs"])
 def test_attention_tma_decode(nq, nkv, hd, ps, window, case, consecutive):
     """The TMA-fed decode form against the float32 statement: contexts that end inside a page and
     inside a tile, requests shorter than a tile (slots without a page), split contexts, a window;
