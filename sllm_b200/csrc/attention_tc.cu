@@ -21,8 +21,8 @@
 //   issuer     allocates the tensor memory; one lane issues S(j) = Q K(j)^T (M=128, N=64, K=16,
 //              head_dim/16 times) two tiles ahead of the softmax, and O += P(j) V(j) (M=128,
 //              N=head_dim, K=16, four times; V is read as stored, keys down the rows: an MN-major
-//              operand) when P(j) is written.  The products of one issuer run in the order issued, so
-//              S(j+2) overwrites the columns of P(j) only after P(j) V(j) has read them.  With two row
+//              operand) when P(j) is written.  S(j+2) overwrites the columns of P(j): it is issued
+//              only when a barrier committed behind P(j) V(j) says that product is complete.  With two row
 //              tiles it serves whichever has an event pending, so one's products run under the
 //              other's softmax.
 // Per row tile S/P is double-buffered in tensor memory (2 x 64 columns) and O takes head_dim columns.
@@ -107,7 +107,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   uint64_t* p_full = s_full + 2 * RT;                                   // [RT][2] the buffer holds P, O is rescaled
   uint64_t* o_done = p_full + 2 * RT;                                   // [RT] a P.V product is done
   uint64_t* q_full = o_done + RT;                                       // [RT] the row tile's queries are in place
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + RT);
+  uint64_t* s_free = q_full + RT;                                       // [RT][2] P.V has read the buffer's P: S may be written again
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2 * RT);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -118,6 +119,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     }
     for (int s = 0; s < 2 * RT; ++s) {
       mbar_init(&s_full[s], 1);
+      mbar_init(&s_free[s], 1);
       mbar_init(&p_full[s], 4);                   // the four softmax warps of the row tile
     }
     for (int t = 0; t < RT; ++t) {
@@ -259,6 +261,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 umma_bf16_ta(tmem_base + t * L::TMEM_TILE + L::O_COL, p_tmem + k * 8,
                              umma_desc_mn(v_addr + k * 16 * 128, TC_BN * 128), idesc_pv, (j | k) ? 1u : 0u);
               umma_commit(&o_done[t]);
+              umma_commit(&s_free[t * 2 + b]);
               jp[t] = j + 1;
               progress = true;
             }
@@ -266,7 +269,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
           if (jq[t] < n_of[t] && jq[t] < jp[t] + 2) {
             const int j = jq[t];
             if (!q_ready[t]) q_ready[t] = mbar_test(&q_full[t], 0);
-            if (q_ready[t] && mbar_test(&full_kv[j % TC_STAGES], (j / TC_STAGES) & 1)) {
+            // S(j) goes into the columns of P(j-2): the product that read them must be complete, not
+            // only issued (products with different accumulators are not promised to run in order)
+            const bool s_is_free = j < 2 || mbar_test(&s_free[t * 2 + (j & 1)], ((j >> 1) - 1) & 1);
+            if (q_ready[t] && s_is_free && mbar_test(&full_kv[j % TC_STAGES], (j / TC_STAGES) & 1)) {
               issue_scores(j, t);
               jq[t] = j + 1;
               progress = true;
