@@ -3,10 +3,11 @@
 // float32 scores, softmax and output accumulation.
 //
 // A CTA takes RT (one or two) 128-row tiles of (token, head-in-group) rows of one request and one kv
-// head and walks the keys in tiles of 64; with two row tiles a key/value tile fetched once serves
-// both, and the shared memory of a whole SM holds four key/value tiles in flight.  The one-row-tile
-// form runs two CTAs per SM with two tiles in flight each; it is kept for steps with too few rows to
-// fill the GPU with 256-row CTAs.
+// head and walks the keys in tiles of 64.  The form in use has one row tile: two CTAs share an SM
+// (96 KB of shared memory and 256 columns of tensor memory each), so that one CTA's softmax runs
+// while the other's products do.  With two row tiles a key/value tile fetched once serves both and
+// the shared memory of a whole SM holds four key/value tiles in flight; it is kept and tested, but
+// measured slower at every prompt length tried (the engine does not choose it).
 // Per row tile four softmax warps, then one warp for TMA and one for the MMAs:
 //   softmax    thread r owns row r.  It reads its row of S = Q K^T from tensor memory
 //              (tcgen05.ld), scales and masks it, keeps the row's running maximum and sum, writes

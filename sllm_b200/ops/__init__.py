@@ -456,11 +456,10 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
     use_tc = not window and _TC_ATTENTION and tc_attention_supports(hd, k_cache.shape[2])
     key = ("mma", G, nkv, use_tc)
     if key not in step.attn_tiles:
-        # two row tiles a CTA (one CTA per SM) once such CTAs fill the GPU twice (measured: 235 against
-        # 245 us for 4096 tokens of 28/4 heads, but 102 against 100 us for 2048), else 128-row CTAs, two per SM
+        # 128-row CTAs, two per SM.  (The kernel also has a form with two row tiles a CTA, one CTA per SM,
+        # that fetches each key/value tile once for 256 rows; measured at 28/4 heads of 128 it is the
+        # slower one at every length: 106 against 99 us for 2048 tokens, 787 against 733 us for 8192.)
         rows = 128
-        if use_tc and sum(-(-n * G // 256) for n in step.q_lens if n * G > 16) * nkv >= 2 * NUM_SMS:
-            rows = 256
         small, large = attention_tiles(step.q_lens, G, q.device, step.ctx_lens, rows)
         splits = choose_splits(small[2], nkv, step.max_ctx_len) if (small and not large) else 1
         step.attn_tiles[key] = (small, large, splits, rows)
