@@ -106,9 +106,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   uint64_t* empty_kv = full_kv + TC_STAGES;                             // [STAGES] P.V of the stage's tile is done
   uint64_t* s_full = empty_kv + TC_STAGES;                              // [RT][2] S buffer holds Q K^T
   uint64_t* p_full = s_full + 2 * RT;                                   // [RT][2] the buffer holds P, O is rescaled
-  uint64_t* o_done = p_full + 2 * RT;                                   // [RT] a P.V product is done
-  uint64_t* q_full = o_done + RT;                                       // [RT] the row tile's queries are in place
-  uint64_t* s_free = q_full + RT;                                       // [RT][2] P.V has read the buffer's P: S may be written again
+  uint64_t* q_full = p_full + 2 * RT;                                   // [RT] the row tile's queries are in place
+  uint64_t* s_free = q_full + RT;                                       // [RT][2] the P.V that read the buffer's P is complete
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2 * RT);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -124,7 +123,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       mbar_init(&p_full[s], 4);                   // the four softmax warps of the row tile
     }
     for (int t = 0; t < RT; ++t) {
-      mbar_init(&o_done[t], 1);
       mbar_init(&q_full[t], 4);
     }
     // a wait that ran out in another CTA voids the result anyway: the CTAs that start after it do nothing
@@ -261,8 +259,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
               for (int k = 0; k < TC_BN / 16; ++k)     // 16 keys: 8 columns of P, 16 rows of V
                 umma_bf16_ta(tmem_base + t * L::TMEM_TILE + L::O_COL, p_tmem + k * 8,
                              umma_desc_mn(v_addr + k * 16 * 128, TC_BN * 128), idesc_pv, (j | k) ? 1u : 0u);
-              umma_commit(&o_done[t]);
-              umma_commit(&s_free[t * 2 + b]);
+              umma_commit(&s_free[t * 2 + b]);          // the product is complete: P's columns are free, O is still
               jp[t] = j + 1;
               progress = true;
             }
@@ -360,12 +357,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       }
       mx *= p.scale_log2;
       const bool grow = mx > m_used + TC_RESCALE_STEP;      // also the first tile with a key (m_used = -inf)
-      // Every tile waits once for the product of the tile before it (phase j-1 of o_done; a parity
-      // names a phase only among two neighbours, so none may be skipped): before a rescale of O,
-      // which must not change under that product, else just before P is handed over, when the
-      // product is long done and the wait costs nothing.
+      // Only a rescale of O waits for the product of the tile before it (O must not change under it).
+      // The barrier is the one behind that product, s_free of its buffer: its phases go by every
+      // second tile, and S(j) being there means the product of tile j-2, hence of j-3, is complete,
+      // so the phase asked for is the pending one or the one before: a parity tells them apart.
       const bool rescale = __any_sync(0xffffffffu, grow);
-      bool waited = false;
       if (rescale) {
         const float corr = grow ? ex2(m_used - mx) : 1.f;   // 0 when m_used = -inf (nothing summed yet)
         if (grow) {
@@ -373,8 +369,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
           l *= corr;
         }
         if (j > 0) {
-          if (!mbar_wait(&o_done[t], (j - 1) & 1) || *failed) { ok = false; break; }
-          waited = true;
+          if (!mbar_wait(&s_free[t * 2 + ((j - 1) & 1)], ((j - 1) >> 1) & 1) || *failed) { ok = false; break; }
           tc_fence_after();
 #pragma unroll 1
           for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -402,15 +397,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       }
       tmem_st32(t_lane + b * TC_BN, pk);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      if (j > 0 && !waited) {
-        if (!mbar_wait(&o_done[t], (j - 1) & 1) || *failed) { ok = false; break; }
-      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&my_p_full[b]);
     }
     if (ok && my_tiles > 0) {
-      if (!mbar_wait(&o_done[t], (my_tiles - 1) & 1) || *failed) ok = false;
+      // the last product: the barrier behind it (see the rescale above for why a parity suffices)
+      if (!mbar_wait(&s_free[t * 2 + ((my_tiles - 1) & 1)], ((my_tiles - 1) >> 1) & 1) || *failed) ok = false;
     }
     if (!ok && !*failed) { *failed = 23; atomicExch(p.status, 23); }
     if (ok && my_tiles > 0) {
