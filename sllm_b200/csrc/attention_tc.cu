@@ -18,7 +18,9 @@
 //              (then O in tensor memory is rescaled: tcgen05.ld, multiply, tcgen05.st); the result
 //              is the same sum with a different common factor, which cancels in O / sum.
 //   producer   one lane issues the TMA loads: per page and 64-column half of the head one box of
-//              K and one of V (page_size x 64 elements, 128-byte swizzle);
+//              K and one of V (page_size x 64 elements, 128-byte swizzle), or one box each for a
+//              tile whose pages have consecutive ids; K and V in rings of their own, so that the
+//              next keys load as soon as the scores that read a K buffer are done;
 //   issuer     allocates the tensor memory; one lane issues S(j) = Q K(j)^T (M=128, N=64, K=16,
 //              head_dim/16 times) two tiles ahead of the softmax, and O += P(j) V(j) (M=128,
 //              N=head_dim, K=16, four times; V is read as stored, keys down the rows: an MN-major
@@ -102,9 +104,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   constexpr int PRODUCER = 4 * RT, ISSUER = 4 * RT + 1;      // warp numbers
   extern __shared__ __align__(1024) unsigned char tc_smem[];
   unsigned char* smem = tc_smem;
-  uint64_t* full_kv = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);   // [STAGES] a stage's K and V have landed
-  uint64_t* empty_kv = full_kv + TC_STAGES;                             // [STAGES] P.V of the stage's tile is done
-  uint64_t* s_full = empty_kv + TC_STAGES;                              // [RT][2] S buffer holds Q K^T
+  // K and V have rings of their own: a K buffer is free again when the scores of its tile are done,
+  // long before the tile's P.V, so the next keys load under the softmax
+  uint64_t* k_full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);    // [STAGES] the buffer's K has landed
+  uint64_t* k_empty = k_full + TC_STAGES;                               // [STAGES] the scores that read it are done
+  uint64_t* v_full = k_empty + TC_STAGES;                               // [STAGES] the buffer's V has landed
+  uint64_t* v_empty = v_full + TC_STAGES;                               // [STAGES] the P.V that read it is done
+  uint64_t* s_full = v_empty + TC_STAGES;                               // [RT][2] S buffer holds Q K^T
   uint64_t* p_full = s_full + 2 * RT;                                   // [RT][2] the buffer holds P, O is rescaled
   uint64_t* q_full = p_full + 2 * RT;                                   // [RT] the row tile's queries are in place
   uint64_t* s_free = q_full + RT;                                       // [RT][2] the P.V that read the buffer's P is complete
@@ -114,8 +120,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     for (int s = 0; s < TC_STAGES; ++s) {
-      mbar_init(&full_kv[s], 1);
-      mbar_init(&empty_kv[s], 1);
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     for (int s = 0; s < 2 * RT; ++s) {
       mbar_init(&s_full[s], 1);
@@ -169,47 +177,68 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     // ---------------- TMA producer ----------------
     if (lane == 0 && !*failed) {
       const int ps = p.page_size, per_tile = TC_BN / ps;
-      int issued = 0;
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j % TC_STAGES, round = j / TC_STAGES;
-        if (!mbar_wait(&empty_kv[s], (round & 1) ^ 1) || *failed) {
-          if (!*failed) { *failed = 21; atomicExch(p.status, 21); }
-          break;
-        }
+      // the copies of one of K (which = 0) or V (1) for key tile j into its ring buffer
+      auto load_tile = [&](int which, int j) {
+        const int s = j % TC_STAGES;
+        uint64_t* full = which ? &v_full[s] : &k_full[s];
+        unsigned char* dst = smem + (which ? L::V_OFF : L::K_OFF) + s * L::KV_BYTES;
         const int kbase = j * TC_BN;
         const int pages = min(per_tile, (key_hi - kbase + ps - 1) / ps);
-        unsigned char* ks = smem + L::K_OFF + s * L::KV_BYTES;
-        unsigned char* vs = smem + L::V_OFF + s * L::KV_BYTES;
-        // a tile whose pages have consecutive ids is one box of K and one of V (the run maps walk the
-        // pages with a stride of their own): the TMA unit's time goes by the box, not by the byte
+        // a tile whose pages have consecutive ids is one box (the run maps walk the pages with a stride
+        // of their own): the TMA unit's time goes by the box, not by the byte
         const int first_pi = kbase / ps;
         bool run = p.page_runs && pages == per_tile && first_pi + per_tile <= p.max_pages && bt[first_pi] >= 0;
         for (int i = 1; run && i < per_tile; ++i) run = bt[first_pi + i] == bt[first_pi] + i;
         if (run) {
-          mbar_expect_tx(&full_kv[s], (uint32_t)(2 * L::KV_BYTES));
-          tma_load_5d(ks, &run_k, 0, 0, bt[first_pi], 0, kvh, &full_kv[s]);
-          tma_load_5d(vs, &run_v, 0, 0, bt[first_pi], 0, kvh, &full_kv[s]);
-          issued = j + 1;
-          continue;
+          mbar_expect_tx(full, (uint32_t)L::KV_BYTES);
+          tma_load_5d(dst, which ? &run_v : &run_k, 0, 0, bt[first_pi], 0, kvh, full);
+          return;
         }
-        mbar_expect_tx(&full_kv[s], (uint32_t)(pages * 2 * HALVES * ps * 128));
+        mbar_expect_tx(full, (uint32_t)(pages * HALVES * ps * 128));
         for (int i = 0; i < pages; ++i) {
-          const int pi = kbase / ps + i;
+          const int pi = first_pi + i;
           int page = pi < p.max_pages ? bt[pi] : 0;
           if (page < 0) page = 0;                   // no page lies inside a causal range without a window
           const int y = (page * p.nkv + kvh) * ps;
 #pragma unroll
-          for (int h = 0; h < HALVES; ++h) {
-            tma_load_2d(ks + h * (TC_BN * 128) + i * ps * 128, &map_k, h * 64, y, &full_kv[s]);
-            tma_load_2d(vs + h * (TC_BN * 128) + i * ps * 128, &map_v, h * 64, y, &full_kv[s]);
+          for (int h = 0; h < HALVES; ++h)
+            tma_load_2d(dst + h * (TC_BN * 128) + i * ps * 128, which ? &map_v : &map_k, h * 64, y, full);
+        }
+      };
+      // two streams, served as their buffers come free (the keys first: the scores come first)
+      int jk = 0, jv = 0;
+      uint64_t idle_since = 0;
+      uint32_t spins = 0;
+      while ((jk < n_tiles || jv < n_tiles) && !*failed) {
+        bool progress = false;
+        if (jk < n_tiles && mbar_test(&k_empty[jk % TC_STAGES], ((jk / TC_STAGES) & 1) ^ 1)) {
+          load_tile(0, jk);
+          ++jk;
+          progress = true;
+        }
+        if (jv < n_tiles && jv < jk && mbar_test(&v_empty[jv % TC_STAGES], ((jv / TC_STAGES) & 1) ^ 1)) {
+          load_tile(1, jv);
+          ++jv;
+          progress = true;
+        }
+        if (progress) {
+          idle_since = 0;
+          spins = 0;
+        } else if ((++spins & 255u) == 0) {
+          const uint64_t now = global_ns();
+          if (idle_since == 0) idle_since = now;
+          else if (now - idle_since > TMA_WAIT_NS) {
+            *failed = 21;
+            atomicExch(p.status, 21);
           }
         }
-        issued = j + 1;
       }
       if (*failed) {
         // let the copies already issued land before the CTA gives its shared memory back
-        for (int i = issued > TC_STAGES ? issued - TC_STAGES : 0; i < issued; ++i)
-          mbar_wait(&full_kv[i % TC_STAGES], (i / TC_STAGES) & 1, TMA_DRAIN_NS);
+        for (int i = jk > TC_STAGES ? jk - TC_STAGES : 0; i < jk; ++i)
+          mbar_wait(&k_full[i % TC_STAGES], (i / TC_STAGES) & 1, TMA_DRAIN_NS);
+        for (int i = jv > TC_STAGES ? jv - TC_STAGES : 0; i < jv; ++i)
+          mbar_wait(&v_full[i % TC_STAGES], (i / TC_STAGES) & 1, TMA_DRAIN_NS);
       }
     }
   } else if (warp == ISSUER) {
@@ -236,12 +265,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       // The row tiles are served as their events come, not in turn, so that one's products run under
       // the other's softmax.  Per row tile: jq = next key tile whose scores are to be issued (at most
       // two ahead of the softmax: S(j+2) goes into the columns P(j) V(j) has read), jp = next key tile
-      // whose P.V is to be issued (when its P is written).  A stage is handed back to the producer when
-      // every row tile that reaches its key tile has issued its P.V.
+      // whose P.V is to be issued (when its P is written).
       int jq[RT], jp[RT], q_ready[RT];
 #pragma unroll
       for (int t = 0; t < RT; ++t) jq[t] = jp[t] = q_ready[t] = 0;
-      int released = 0;
+      int k_released = 0, v_released = 0;
       uint64_t idle_since = 0;
       uint32_t spins = 0;
       while (ok) {
@@ -251,7 +279,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
           if (jp[t] < n_of[t]) {
             pending = true;
             const int j = jp[t], s = j % TC_STAGES, b = j & 1;
-            if (mbar_test(&p_full[t * 2 + b], (j >> 1) & 1)) {
+            if (mbar_test(&p_full[t * 2 + b], (j >> 1) & 1) && mbar_test(&v_full[s], (j / TC_STAGES) & 1)) {
               tc_fence_after();
               const uint32_t v_addr = smem_u32(smem + L::V_OFF + s * L::KV_BYTES);
               const uint32_t p_tmem = tmem_base + t * L::TMEM_TILE + b * TC_BN;
@@ -270,21 +298,30 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             // S(j) goes into the columns of P(j-2): the product that read them must be complete, not
             // only issued (products with different accumulators are not promised to run in order)
             const bool s_is_free = j < 2 || mbar_test(&s_free[t * 2 + (j & 1)], ((j >> 1) - 1) & 1);
-            if (q_ready[t] && s_is_free && mbar_test(&full_kv[j % TC_STAGES], (j / TC_STAGES) & 1)) {
+            if (q_ready[t] && s_is_free && mbar_test(&k_full[j % TC_STAGES], (j / TC_STAGES) & 1)) {
               issue_scores(j, t);
               jq[t] = j + 1;
               progress = true;
             }
           }
         }
-        // stages that every row tile is done with
-        while (released < n_tiles) {
+        // a K buffer goes back when every row tile that reaches its key tile has issued its scores, a V
+        // buffer when every such row tile has issued its P.V (a commit covers all that was issued before it)
+        while (k_released < n_tiles) {
           bool all = true;
 #pragma unroll
-          for (int t = 0; t < RT; ++t) all = all && (released >= n_of[t] || jp[t] > released);
+          for (int t = 0; t < RT; ++t) all = all && (k_released >= n_of[t] || jq[t] > k_released);
           if (!all) break;
-          umma_commit(&empty_kv[released % TC_STAGES]);
-          ++released;
+          umma_commit(&k_empty[k_released % TC_STAGES]);
+          ++k_released;
+        }
+        while (v_released < n_tiles) {
+          bool all = true;
+#pragma unroll
+          for (int t = 0; t < RT; ++t) all = all && (v_released >= n_of[t] || jp[t] > v_released);
+          if (!all) break;
+          umma_commit(&v_empty[v_released % TC_STAGES]);
+          ++v_released;
         }
         if (!pending) break;
         if (*failed) ok = false;
