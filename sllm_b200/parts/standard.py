@@ -119,6 +119,11 @@ class Attention(Mixer):
         self.names = p.get("names", ("q_proj", "k_proj", "v_proj", "o_proj"))
         if self.nq % self.nkv:
             raise ValueError(f"attention: {self.nq} query heads are no multiple of {self.nkv} kv heads")
+        if not 1 <= self.hd <= self.MAX_HEAD_DIM:
+            # said when the model is built, not at the first step: the attention kernels keep a head in
+            # registers and shared memory (tensor-core forms 16..128, the CUDA-core form up to 256)
+            raise ValueError(f"attention: head_dim={self.hd} is outside 1..{self.MAX_HEAD_DIM}, the largest head the "
+                             f"attention kernels take")
         self.qkv = None
         self.out = None
 
@@ -150,6 +155,7 @@ class Attention(Mixer):
         self.out = Linear(self._matrix(fetch(f"{on}.weight")), ob)
 
     accepts_residual = True
+    MAX_HEAD_DIM = 256
 
     def forward(self, x, step: StepContext, cache: LayerCache, position, write_cache=True, residual=None):
         g = step.groups[cache.group]

@@ -59,3 +59,47 @@ def test_medium_sizes_all_cuttings(name, tmp_path):
                     sq = [(out[st["step"]][i] - want[r][p]) ** 2 for st in tr.steps for i, (r, p) in enumerate(st["expect"])]
                     assert float(np.sqrt(np.mean(sq))) <= 0.02 * spread
                 assert not eng.cache.requests
+
+
+OTHER_HEADS = {
+    "mha_hd48": dict(BASE, num_hidden_layers=2, hidden_size=336, num_attention_heads=7, num_key_value_heads=7, head_dim=48,
+                     intermediate_size=1000, vocab_size=1003, rope_theta=10000.0, rms_norm_eps=1e-5,
+                     max_position_embeddings=1024, tie_word_embeddings=True),
+    "group3_hd80": dict(BASE, num_hidden_layers=2, hidden_size=400, num_attention_heads=6, num_key_value_heads=2, head_dim=80,
+                        intermediate_size=1112, vocab_size=777, rope_theta=10000.0, rms_norm_eps=1e-6,
+                        max_position_embeddings=1024, tie_word_embeddings=False),
+    "group2_hd256": dict(BASE, num_hidden_layers=2, hidden_size=512, num_attention_heads=2, num_key_value_heads=1, head_dim=256,
+                         intermediate_size=1024, vocab_size=2000, rope_theta=10000.0, rms_norm_eps=1e-6,
+                         max_position_embeddings=1024, tie_word_embeddings=False),
+}
+
+
+@pytest.mark.parametrize("name", sorted(OTHER_HEADS))
+def test_head_sizes_the_tensor_core_forms_do_not_take(name, tmp_path):
+    """Head sizes 48, 80 and 256 in bfloat16 go to the CUDA-core attention kernel; whole and cut, against
+    the plain implementation.  A head larger than any kernel takes is refused when the model is built."""
+    from sllm_b200.engine import Engine, build_model
+    from sllm_b200.weights import write_random_model
+    dev = cuda_or_skip()
+    cfg = OTHER_HEADS[name]
+    d = str(tmp_path / "model")
+    write_random_model(d, cfg, 31, std=0.03, bias_std=0.2, gain_std=0.1)
+    c, w = plain.load_model(d)
+    rng = np.random.default_rng(19)
+    reqs = {f"r{i}": rng.integers(0, cfg["vocab_size"], n).tolist() for i, n in enumerate((90, 37, 140))}
+    want = {r: plain.forward(ids, w, c) for r, ids in reqs.items()}
+    spread = float(np.concatenate([v.ravel() for v in want.values()]).std())
+    for dtype in ("float32", "bfloat16"):
+        tol = dict(rtol=1e-4, atol=1e-4) if dtype == "float32" else dict(rtol=2e-2, atol=0.08 * spread)
+        model, _ = build_model(d, dtype, dev)
+        for mode in ("whole", "portions", "mixed"):
+            tr = getattr(traces, mode)(reqs)
+            eng = Engine(model, page_size=16, num_pages=tr.max_tokens // 16, max_requests=4)
+            out = traces.replay_engine(tr, eng)
+            traces.compare(tr, out, want, what=f"{name}/{dtype}/{mode}", **tol)
+    if name == "group2_hd256":
+        big = dict(cfg, head_dim=272, hidden_size=544)
+        d2 = str(tmp_path / "big")
+        with pytest.raises(ValueError, match="head_dim=272"):     # already when its parts are made to name its tensors
+            write_random_model(d2, big, 32, std=0.03)
+            build_model(d2, "bfloat16", dev)
