@@ -367,6 +367,57 @@ def test_decode_graphs_pad_the_batch_to_a_captured_size(tiny, dtype):
             assert r.ids[:2] == want[:2] and len(r.ids) == sp.max_new
 
 
+@pytest.mark.parametrize("policy", ["reserve", "on_demand"])
+@pytest.mark.parametrize("pipelined", [False, True])
+def test_random_arrivals_aborts_and_a_small_pool(tiny, policy, pipelined):
+    """Requests arrive at random steps, some are aborted while they wait, are being prefilled or have a
+    decode step in flight, the pool is small enough for pages to be used again (and, on demand, for
+    preemptions): every request that ends has the plain implementation's tokens, greedy or sampled
+    with its own seed, and no page or slot is lost."""
+    from sllm_b200.engine import build_model
+    from sllm_b200.engine.llm import LLM
+    from sllm_b200.sampling import SamplingParams
+    dev = cuda_or_skip()
+    name, model_dir, page = tiny
+    cfg, w = plain.load_model(model_dir)
+    model, _ = build_model(model_dir, "float32", dev)
+    rng = np.random.default_rng(41 + pipelined)
+    n = 14
+    prompts = [rng.integers(0, cfg["vocab_size"], int(rng.integers(1, 40))).tolist() for _ in range(n)]
+    params = []
+    for i in range(n):
+        kw = dict(max_new=int(rng.integers(1, 20)))
+        if i % 3 == 1:
+            kw.update(temperature=0.9, seed=100 + i)
+        params.append(SamplingParams(**kw))
+    llm = LLM(model=model, block_size=page, num_pages=-(-60 // page) + 2, max_num_seqs=3, chunk_size=8, max_batch_tokens=24,
+              policy=policy, pipeline_decode=pipelined)
+    reqs, aborted, nxt, steps = {}, set(), 0, 0
+    while nxt < n or llm.scheduler.has_work:
+        if nxt < n and rng.random() < 0.5:
+            reqs[nxt] = llm.add_request(prompts[nxt], params[nxt], req_id=nxt)
+            nxt += 1
+        live = [i for i, r in reqs.items() if r.status != "finished" and i not in aborted]
+        if live and rng.random() < 0.07:
+            victim = int(rng.choice(live))
+            assert llm.abort(victim)
+            aborted.add(victim)
+        if llm.scheduler.has_work:
+            llm.step()
+        steps += 1
+        assert steps < 3000, "the run does not end"
+    llm.drain()
+    llm.engine.cache.check()
+    assert not llm.engine.cache.requests
+    assert len(aborted) >= 1 and len(aborted) < n
+    for i, r in reqs.items():
+        if i in aborted:
+            continue
+        sp = params[i]
+        want = plain.generate(prompts[i], sp.max_new, w, cfg, temperature=sp.temperature or 0.0, seed=sp.seed)
+        assert r.output == want, f"request {i} ({policy}, pipelined={pipelined})"
+
+
 def test_graph_capture_survives_garbage_of_earlier_engines(tiny):
     """Engines made and dropped one after the other, with the collector set to run all the time: the
     capture of a decode graph must not be invalidated by the collection of an earlier engine's graphs
