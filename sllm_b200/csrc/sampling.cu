@@ -5,6 +5,9 @@
 // temperature: p = softmax(logits / T) with the maximum subtracted; the token is the
 // first index whose cumulative probability reaches the uniform u, clamped to V-1
 // (runtime/sampler.py:54-58, 81-88); temperature <= 0 is greedy (runtime/sampler.py:50-53).
+// top-k, then top-p over what it kept, restrict the tokens that can be drawn
+// (runtime/sampler.py:60-79); a token outside the kept set is never returned, also at u = 0 and
+// beyond the last cumulative value, where the reference's searchsorted would name token 0 or V-1.
 // The host draws u, one per sampled token, from the request's own generator.
 // Sums are kept in float64 as the reference's sampler works in float64.
 #include <math.h>
@@ -70,32 +73,268 @@ __device__ MaxIdx block_argmax(const float* __restrict__ row, int V, MaxIdx* sh)
   return r;
 }
 
-__device__ double block_sum_f64(double v, double* sh) {
+// ---- the kept set of top-k / top-p: {key > tau} and, of {key == tau}, the indices up to i_eq --------
+//
+// Keys are the logits' bits mapped so that unsigned order is float order.  The k-th largest key, and
+// the key at which the descending cumulative probability first reaches top_p, are found by a
+// five-level select over the row.  Each level builds a histogram of counts and of probability mass
+// (one histogram per warp, summed afterwards) of the eligible logits in the range chosen so far,
+// walks it from the largest logits down and chooses the bin that holds the target.  The first level's
+// 256 bins are linear in the distance from the row's maximum (logits share few exponents, so their
+// top bits would put a whole row on a handful of counters); the other four take 8 bits of the key
+// each, within the chosen linear bin, and end at one key.
+//
+// Probabilities are p = expf((logit - max) / T), exact to float32 as the logits are; sums are float64.
+
+constexpr int SEL_BINS = 256, SEL_WARPS = SAMPLE_THREADS / 32;
+constexpr int SAMPLE_SMEM = SEL_WARPS * SEL_BINS * (int)(sizeof(int) + sizeof(float));
+constexpr float SEL_LINEAR_SPAN = 24.f;     // the linear bins cover (max - logit) / T up to this; the last takes the rest
+
+__device__ __forceinline__ uint32_t order_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+__device__ __forceinline__ int linear_bin(float l, float mx, float lscale) {
+  const float d = (mx - l) * lscale;               // >= 0, monotone in the logit
+  return d >= (float)(SEL_BINS - 1) ? SEL_BINS - 1 : (int)d;
+}
+__device__ __forceinline__ float prob(float l, float mx, float inv_t) { return expf((l - mx) * inv_t); }
+
+struct Select {
+  int lbin;                   // the linear bin chosen at the first level
+  uint32_t prefix, mask;      // the key bits chosen so far
+  int cnt_above;              // eligible logits greater than the chosen range
+  double mass_above;          // their probability mass
+  int group_cnt;              // logits in the chosen range (after the last level: equal to the key)
+  double group_mass;
+  double target;              // by mass: the cumulative mass to reach
+  int chosen;                 // the last level's bin, -1: the target lies beyond every eligible logit
+};
+
+// f(logit, index) over the row, eight loads in flight a thread
+template <class F>
+__device__ __forceinline__ void for_row(const float* __restrict__ row, int V, F f) {
+  for (int i0 = threadIdx.x; i0 < V; i0 += SAMPLE_THREADS * 8) {
+    float l[8];
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  __syncthreads();
-  if (lane == 0) sh[warp] = v;
-  __syncthreads();
-  if (warp == 0) {
-    double t = lane < (blockDim.x >> 5) ? sh[lane] : 0.0;
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * SAMPLE_THREADS;
+      l[u] = i < V ? row[i] : 0.f;
+    }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    if (lane == 0) sh[32] = t;
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * SAMPLE_THREADS;
+      if (i < V) f(l[u], i);
+    }
   }
-  __syncthreads();
-  const double r = sh[32];
-  __syncthreads();
-  return r;
+}
+// the same over [base, base + len) cut at `end`, by one warp
+template <class F>
+__device__ __forceinline__ void for_part(const float* __restrict__ row, int base, int len, int end, F f) {
+  const int lane = threadIdx.x & 31;
+  for (int o = 0; o < len; o += 32 * 8) {
+    float l[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + o + u * 32 + lane;
+      l[u] = (o + u * 32 < len && i < end) ? row[i] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + o + u * 32 + lane;
+      if (o + u * 32 < len && i < end) f(l[u], i);
+    }
+  }
+}
+
+// Warp 0 walks the 256 bins from the largest logits down (eight bins a lane, the lanes' sums
+// scanned) and records in *st the first bin at which the count reaches k or the mass the target.
+__device__ void choose_bin(int level, bool by_mass, int k, bool target_is_fraction, double fraction,
+                           const int* bin_c, const double* bin_m, Select* st) {
+  const int lane = threadIdx.x & 31;
+  int c[8], lc = 0;
+  double m[8], lm = 0.0;
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const int j = 8 * lane + u, b = level == 0 ? j : SEL_BINS - 1 - j;
+    c[u] = bin_c[b];
+    m[u] = bin_m[b];
+    lc += c[u];
+    lm += m[u];
+  }
+  int ic = lc;
+  double im = lm;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int nc = __shfl_up_sync(0xffffffffu, ic, d);
+    const double nm = __shfl_up_sync(0xffffffffu, im, d);
+    if (lane >= d) { ic += nc; im += nm; }
+  }
+  const double all_m = __shfl_sync(0xffffffffu, im, 31);
+  const double target = (level == 0 && by_mass && target_is_fraction) ? fraction * all_m : st->target;
+  int ca = st->cnt_above + ic - lc;                  // above this lane's bins
+  double ma = st->mass_above + im - lm;
+  __syncwarp();
+  int hit = -1, last = -1;
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    if (c[u] == 0 || hit >= 0) continue;
+    last = u;
+    if (by_mass ? (ma + m[u] >= target) : (ca + c[u] >= k)) {
+      hit = u;
+    } else {
+      ca += c[u];
+      ma += m[u];
+    }
+  }
+  const uint32_t hits = __ballot_sync(0xffffffffu, hit >= 0), nonempty = __ballot_sync(0xffffffffu, last >= 0);
+  int who = -1, u_sel = -1;
+  if (hits) {
+    who = __ffs(hits) - 1;
+    u_sel = hit;
+  } else if (level > 0 && nonempty) {
+    // the range chosen one level up held the target; its parts were summed in another order and
+    // fall short by rounding: the target is in the last part
+    who = 31 - __clz(nonempty);
+    u_sel = last;
+    if (lane == who) { ca -= c[last]; ma -= m[last]; }
+  }
+  if (lane == 0) { st->chosen = -1; st->target = target; }
+  __syncwarp();
+  if (lane == who) {
+    int cu = 0;
+    double mu = 0.0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) if (u == u_sel) { cu = c[u]; mu = m[u]; }
+    const int j = 8 * lane + u_sel, b = level == 0 ? j : SEL_BINS - 1 - j;
+    st->chosen = b;
+    st->cnt_above = ca;
+    st->mass_above = ma;
+    st->group_cnt = cu;
+    st->group_mass = mu;
+    if (level == 0) {
+      st->lbin = b;
+    } else {
+      const int shift = 32 - 8 * level;
+      st->prefix |= (uint32_t)b << shift;
+      st->mask |= 255u << shift;
+    }
+  }
+}
+
+constexpr int SEL_CANDIDATES = 4096;        // the chosen linear bin's keys are gathered if they are no more than this
+
+// by_mass false: the key of the k-th largest eligible logit.  by_mass true: the first key, going
+// down, at which the cumulative mass reaches `target` (`target_is_fraction`: of the eligible total).
+// Eligible: key > floor_key where has_floor.  The result is in *st (shared), the same for all threads.
+__device__ void select_key(const float* __restrict__ row, int V, float mx, float inv_t, bool by_mass, int k,
+                           double target, bool target_is_fraction, bool has_floor, uint32_t floor_key,
+                           int* hist_c, float* hist_m, int* bin_c, double* bin_m, uint32_t* cand, int* n_cand, Select* st) {
+  const int warp = threadIdx.x >> 5;
+  const float lscale = inv_t * ((float)(SEL_BINS - 1) / SEL_LINEAR_SPAN);
+  if (threadIdx.x == 0) { *st = Select{0, 0u, 0u, 0, 0.0, 0, 0.0, target, 0}; *n_cand = 0; }
+  bool gathered = false;
+  for (int level = 0; level < 5; ++level) {
+    const int shift = 32 - 8 * level;              // levels 1..4: bits 24, 16, 8, 0
+    for (int i = threadIdx.x; i < SEL_WARPS * SEL_BINS; i += blockDim.x) { hist_c[i] = 0; hist_m[i] = 0.f; }
+    __syncthreads();
+    const uint32_t prefix = st->prefix, mask = st->mask;
+    const int lbin = st->lbin;
+    if (level == 1 && st->group_cnt <= SEL_CANDIDATES) {
+      // the keys of the chosen linear bin, in any order: the levels below read these, not the row
+      for_row(row, V, [&](float l, int) {
+        const uint32_t key = order_key(l);
+        if ((!has_floor || key > floor_key) && linear_bin(l, mx, lscale) == lbin) cand[atomicAdd(n_cand, 1)] = key;
+      });
+      gathered = true;
+      __syncthreads();
+    }
+    if (gathered) {
+      const int n = *n_cand;
+      for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        const uint32_t key = cand[j];
+        if ((key & mask) != prefix) continue;
+        const int b = (int)((key >> shift) & 255u);
+        atomicAdd(&hist_c[warp * SEL_BINS + b], 1);
+        atomicAdd(&hist_m[warp * SEL_BINS + b], prob(key_value(key), mx, inv_t));
+      }
+    } else {
+      // The last linear bin takes every logit far below the maximum, most of a peaked row: those are
+      // counted in registers, not on one shared counter.
+      int far_c = 0;
+      float far_m = 0.f;
+      for_row(row, V, [&](float l, int) {
+        const uint32_t key = order_key(l);
+        if (has_floor && key <= floor_key) return;
+        int b = linear_bin(l, mx, lscale);
+        if (level > 0) {
+          if (b != lbin || (key & mask) != prefix) return;
+          b = (int)((key >> shift) & 255u);
+        } else if (b == SEL_BINS - 1) {
+          ++far_c;
+          far_m += prob(l, mx, inv_t);
+          return;
+        }
+        atomicAdd(&hist_c[warp * SEL_BINS + b], 1);
+        atomicAdd(&hist_m[warp * SEL_BINS + b], prob(l, mx, inv_t));
+      });
+      if (level == 0) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          far_c += __shfl_xor_sync(0xffffffffu, far_c, o);
+          far_m += __shfl_xor_sync(0xffffffffu, far_m, o);
+        }
+        if ((threadIdx.x & 31) == 0 && far_c) {
+          atomicAdd(&hist_c[warp * SEL_BINS + SEL_BINS - 1], far_c);
+          atomicAdd(&hist_m[warp * SEL_BINS + SEL_BINS - 1], far_m);
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < SEL_BINS) {
+      int c = 0;
+      double m = 0.0;
+      for (int w = 0; w < SEL_WARPS; ++w) { c += hist_c[w * SEL_BINS + threadIdx.x]; m += (double)hist_m[w * SEL_BINS + threadIdx.x]; }
+      bin_c[threadIdx.x] = c;
+      bin_m[threadIdx.x] = m;
+    }
+    __syncthreads();
+    if (warp == 0) choose_bin(level, by_mass, k, target_is_fraction, target, bin_c, bin_m, st);
+    __syncthreads();
+    if (st->chosen < 0) break;
+  }
+}
+
+// What a thread needs to know of the kept set.
+struct Kept {
+  bool filtered;
+  uint32_t tau;
+  int i_eq;                   // ties at tau stay up to this index
+};
+__device__ __forceinline__ bool is_kept(const Kept& kp, float l, int i) {
+  if (!kp.filtered) return true;
+  const uint32_t key = order_key(l);
+  return key > kp.tau || (key == kp.tau && i <= kp.i_eq);
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
-                   const double* __restrict__ uniform, int* __restrict__ out) {
+                   const double* __restrict__ uniform, const int* __restrict__ top_k, const float* __restrict__ top_p,
+                   int* __restrict__ out) {
+  extern __shared__ unsigned char sample_smem[];
   __shared__ MaxIdx sh_mi[32];
-  __shared__ double sh_d[33];
-  __shared__ double warp_tot[32];
-  __shared__ int found;
+  __shared__ double part_sum[SEL_WARPS];
+  __shared__ int part_cnt[SEL_WARPS], part_last[SEL_WARPS];
+  __shared__ int bin_c[SEL_BINS];
+  __shared__ double bin_m[SEL_BINS];
+  __shared__ Select sel;
+  __shared__ uint32_t cand[SEL_CANDIDATES];
+  __shared__ int n_cand;
+  __shared__ int pick_part, pick_need, i_eq_s, result;
+  __shared__ double pick_before;
   pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
   const float* row = logits + (size_t)blockIdx.x * V;
@@ -105,43 +344,207 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
     if (threadIdx.x == 0) out[blockIdx.x] = mx.i;
     return;
   }
-  const double inv_t = 1.0 / (double)temp;
-  const double top = (double)mx.v * inv_t;
-  double part = 0.0;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) part += exp((double)row[i] * inv_t - top);
-  const double total = block_sum_f64(part, sh_d);
-  const double target = uniform[blockIdx.x] * total;
-  // walk the row in index order, blockDim elements at a time, with a running prefix
-  if (threadIdx.x == 0) found = 0x7fffffff;
-  __syncthreads();
-  double running = 0.0;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int base = 0; base < V; base += blockDim.x) {
-    const int i = base + threadIdx.x;
-    const double p = i < V ? exp((double)row[i] * inv_t - top) : 0.0;
-    double incl = p;                                  // inclusive scan within the warp
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const double n = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += n;
+  const float inv_t = 1.0f / temp;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // the row in 32 parts of whole 32-element groups, one per warp, in index order
+  const int part_len = (((V + SEL_WARPS - 1) / SEL_WARPS) + 31) & ~31;
+
+  // ---- the kept set (runtime/sampler.py:60-79): top-k first, then top-p over what it kept ----
+  const int k = top_k ? top_k[blockIdx.x] : 0;
+  const float pfrac = top_p ? top_p[blockIdx.x] : -1.f;
+  const bool has_k = k > 0 && k < V, has_p = pfrac >= 0.f;
+  Kept kp{has_k || has_p, 0u, 0x7fffffff};
+  if (kp.filtered) {
+    int* hist_c = reinterpret_cast<int*>(sample_smem);
+    float* hist_m = reinterpret_cast<float*>(hist_c + SEL_WARPS * SEL_BINS);
+    uint32_t tau = 0u;                     // with no top-k every key is above the floor
+    int n_eq = 0x7fffffff, ties = 0;       // ties at tau: how many stay, how many there are
+    double kept_mass = 0.0, above_k = 0.0;
+    if (has_k) {
+      select_key(row, V, mx.v, inv_t, false, k, 0.0, false, false, 0u, hist_c, hist_m, bin_c, bin_m, cand, &n_cand, &sel);
+      tau = sel.prefix;
+      n_eq = k - sel.cnt_above;            // of the ties at the k-th value, the first ones by index
+      ties = sel.group_cnt;
+      above_k = sel.mass_above;
+      kept_mass = above_k + (double)n_eq * (double)prob(key_value(tau), mx.v, inv_t);
+      __syncthreads();
     }
-    if (lane == 31) warp_tot[warp] = incl;
-    __syncthreads();
-    double before = running;
-    for (int w = 0; w < warp; ++w) before += warp_tot[w];
-    const double cum = before + incl;
-    if (i < V && cum >= target) atomicMin(&found, i);  // the lowest such index is the first
-    double chunk = 0.0;
-    for (int w = 0; w < nw; ++w) chunk += warp_tot[w];
-    running += chunk;
-    __syncthreads();
-    if (found != 0x7fffffff) break;
+    if (has_p) {
+      // the cumulative probability in descending order first reaches top_p at the last token that
+      // stays (runtime/sampler.py:70-75); the probabilities are those renormalised after top-k, so
+      // the target is top_p times the mass top-k kept
+      select_key(row, V, mx.v, inv_t, true, 0, has_k ? (double)pfrac * kept_mass : (double)pfrac, !has_k, has_k, tau,
+                 hist_c, hist_m, bin_c, bin_m, cand, &n_cand, &sel);
+      if (sel.chosen >= 0) {
+        const double q = (double)prob(key_value(sel.prefix), mx.v, inv_t);
+        const double m = fmin(fmax(ceil((sel.target - sel.mass_above) / q), 1.0), (double)sel.group_cnt);
+        tau = sel.prefix;
+        n_eq = (int)m;
+        ties = sel.group_cnt;
+      } else if (has_k) {
+        // not reached above the k-th value: the cut falls among its ties, or top-k's set stays whole
+        const double q = (double)prob(key_value(tau), mx.v, inv_t);
+        const double m = ceil(((double)pfrac * kept_mass - above_k) / q);
+        if (m < (double)n_eq) n_eq = (int)fmax(m, 1.0);
+      }
+      __syncthreads();
+    }
+    if (tau == 0u && n_eq == 0x7fffffff) {
+      kp.filtered = false;                 // top_p lies beyond the whole row: everything stays
+    } else {
+      kp.tau = tau;
+      if (n_eq < ties) {
+        // some ties go: find the index of the n_eq-th one
+        int c = 0;
+        const int base = warp * part_len;
+        for (int o = 0; o < part_len; o += 32) {
+          const int i = base + o + lane;
+          c += __popc(__ballot_sync(0xffffffffu, i < V && order_key(row[i]) == tau));
+        }
+        if (lane == 0) part_cnt[warp] = c;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          int before = 0, w = 0;
+          for (; w < SEL_WARPS - 1 && before + part_cnt[w] < n_eq; ++w) before += part_cnt[w];
+          pick_part = w;
+          pick_need = n_eq - before;       // the tie of this rank (from 1) within the part
+          i_eq_s = 0x7fffffff;
+        }
+        __syncthreads();
+        if (warp == pick_part) {
+          int need = pick_need;
+          for (int o = 0; o < part_len; o += 32) {
+            const int i = base + o + lane;
+            const uint32_t b = __ballot_sync(0xffffffffu, i < V && order_key(row[i]) == tau);
+            const int c2 = __popc(b);
+            if (need <= c2) {
+              if (lane == 0) i_eq_s = base + o + (int)__fns(b, 0, need);
+              break;
+            }
+            need -= c2;
+          }
+        }
+        __syncthreads();
+        kp.i_eq = i_eq_s;
+      }
+    }
   }
+
+  // ---- inverse CDF over the kept tokens in index order (runtime/sampler.py:81-88) ----
+  // 1: each warp sums its part of the row
+  {
+    double s = 0.0;
+    int last = -1;
+    for_part(row, warp * part_len, part_len, V, [&](float l, int i) {
+      if (is_kept(kp, l, i)) { s += (double)prob(l, mx.v, inv_t); last = i; }
+    });
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s += __shfl_xor_sync(0xffffffffu, s, o);
+      last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
+    }
+    if (lane == 0) { part_sum[warp] = s; part_last[warp] = last; }
+  }
+  __syncthreads();
+  // 2: the part in which the cumulative sum reaches u times the total
   if (threadIdx.x == 0) {
-    int r = found;
-    if (r < 0 || r >= V) r = V - 1;                    // u beyond the last cumulative value: clamp
-    out[blockIdx.x] = r;
+    double total = 0.0;
+    for (int w = 0; w < SEL_WARPS; ++w) total += part_sum[w];
+    const double target = uniform[blockIdx.x] * total;
+    double before = 0.0;
+    int pick = -1, last = -1;
+    for (int w = 0; w < SEL_WARPS; ++w) {
+      if (part_last[w] >= 0) last = max(last, part_last[w]);
+      if (pick < 0 && part_last[w] >= 0 && before + part_sum[w] >= target) pick = w;
+      if (pick < 0) before += part_sum[w];
+    }
+    pick_part = pick;
+    pick_before = pick >= 0 ? target - before : 0.0;      // what remains to be reached inside the part
+    // u beyond the last cumulative value: the last kept token (the reference's clamp to V-1,
+    // runtime/sampler.py:88, could name a token that a filter removed)
+    result = last >= 0 ? last : V - 1;
   }
+  __syncthreads();
+  if (pick_part < 0) {
+    if (threadIdx.x == 0) out[blockIdx.x] = result;
+    return;
+  }
+  // 3: the chosen part, again in 32 pieces of whole groups; 4: the chosen piece, group by group
+  const int part_base = pick_part * part_len;
+  const int piece_len = (((part_len + SEL_WARPS - 1) / SEL_WARPS) + 31) & ~31;
+  const double remain = pick_before;
+  __syncthreads();
+  {
+    double s = 0.0;
+    int last = -1;
+    for_part(row, part_base + warp * piece_len, piece_len, min(part_base + part_len, V), [&](float l, int i) {
+      if (is_kept(kp, l, i)) { s += (double)prob(l, mx.v, inv_t); last = i; }
+    });
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s += __shfl_xor_sync(0xffffffffu, s, o);
+      last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
+    }
+    if (lane == 0) { part_sum[warp] = s; part_last[warp] = last; }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double before = 0.0;
+    int pick = -1, last_piece = -1;
+    for (int w = 0; w < SEL_WARPS; ++w) {
+      if (part_last[w] < 0) continue;
+      last_piece = w;
+      if (before + part_sum[w] >= remain) { pick = w; break; }
+      before += part_sum[w];
+    }
+    pick_need = pick >= 0 ? pick : last_piece;
+    // short by rounding against the part's own sum: nothing inside reaches it, and the walk below
+    // ends at the piece's last kept token
+    pick_before = pick >= 0 ? remain - before : INFINITY;
+  }
+  __syncthreads();
+  if (pick_need < 0) {
+    if (threadIdx.x == 0) out[blockIdx.x] = result;
+    return;
+  }
+  if (warp == pick_need) {
+    const int base = part_base + warp * piece_len, end = min(part_base + part_len, V);
+    double left = pick_before;             // still to be reached
+    int answer = -1, last = -1;
+    for (int o = 0; o < piece_len && answer < 0; o += 32) {
+      const int i = base + o + lane;
+      const float l = i < end ? row[i] : 0.f;
+      const bool keep = i < end && is_kept(kp, l, i);
+      const double p = keep ? (double)prob(l, mx.v, inv_t) : 0.0;
+      double incl = p;                     // inclusive scan within the group
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const double n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += n;
+      }
+      const uint32_t hit = __ballot_sync(0xffffffffu, keep && incl >= left);
+      const uint32_t kept_lanes = __ballot_sync(0xffffffffu, keep);
+      if (kept_lanes) last = base + o + (31 - __clz(kept_lanes));
+      if (hit) answer = base + o + (__ffs(hit) - 1);
+      left -= __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) out[blockIdx.x] = answer >= 0 ? answer : (last >= 0 ? last : result);
+  }
+}
+
+// Repetition penalty in place (runtime/sampler.py:12-33): for each (row, id) pair, a positive logit is
+// divided by the row's penalty and a negative one multiplied.  The pairs name each (row, id) once.
+__global__ void repetition_penalty_kernel(float* __restrict__ logits, int V, const int* __restrict__ pair_row,
+                                          const int* __restrict__ pair_id, const float* __restrict__ pair_penalty, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int id = pair_id[i];
+  if (id < 0 || id >= V) return;
+  float* p = logits + (size_t)pair_row[i] * V + id;
+  const double v = (double)*p, pen = (double)pair_penalty[i];
+  *p = (float)(v < 0 ? v * pen : v / pen);
 }
 
 }  // namespace sllm
@@ -149,11 +552,31 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
 using namespace sllm;
 
 // temperature may be null (all rows greedy); uniform must hold R doubles when any temperature > 0.
+// top_k (int per row, <= 0: none) and top_p (float per row, < 0: none) may be null.
 SLLM_EXPORT int sllm_sample_rows(const float* logits, int R, int V, const float* temperature,
-                                 const double* uniform, int* out, cudaStream_t stream) {
+                                 const double* uniform, const int* top_k, const float* top_p, int* out, cudaStream_t stream) {
   SLLM_REQUIRE(R >= 0 && V > 0, "sample_rows: bad sizes R=%d V=%d", R, V);
   SLLM_REQUIRE(temperature == nullptr || uniform != nullptr, "sample_rows: temperatures without uniforms");
+  SLLM_REQUIRE(temperature != nullptr || (top_k == nullptr && top_p == nullptr), "sample_rows: filters without temperatures");
   if (R == 0) return SLLM_OK;
-  launch_kernel(sample_rows_kernel, R, SAMPLE_THREADS, 0, stream, logits, V, temperature, uniform, out);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(sample_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SAMPLE_SMEM) != cudaSuccess) {
+      set_error("sample_rows: cannot raise the shared memory limit");
+      return SLLM_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  const int smem = (top_k || top_p) ? SAMPLE_SMEM : 0;
+  launch_kernel(sample_rows_kernel, R, SAMPLE_THREADS, smem, stream, logits, V, temperature, uniform, top_k, top_p, out);
   return launch_status("sample_rows");
+}
+
+// n (row, id, penalty) triples, each (row, id) named once; logits [R, V] float32 are changed in place
+SLLM_EXPORT int sllm_repetition_penalty(float* logits, int R, int V, const int* pair_row, const int* pair_id,
+                                        const float* pair_penalty, int n, cudaStream_t stream) {
+  SLLM_REQUIRE(R >= 0 && V > 0 && n >= 0, "repetition_penalty: bad sizes R=%d V=%d n=%d", R, V, n);
+  if (n == 0 || R == 0) return SLLM_OK;
+  launch_kernel(repetition_penalty_kernel, (n + 255) / 256, 256, 0, stream, logits, V, pair_row, pair_id, pair_penalty, n);
+  return launch_status("repetition_penalty");
 }

@@ -42,7 +42,7 @@ class _Graph:
         self.cap_pages = -(-engine.max_positions // ps)
         G = len(cache.groups)
         sizes = {"token_ids": B, "positions": B, "seq_of_token": B, "q_start": B + 1, "ctx_len": B,
-                 "state_slots": B, "logit_rows": B, "temps": B, "uniforms": 2 * B}
+                 "state_slots": B, "logit_rows": B, "temps": B, "uniforms": 2 * B, "top_k": B, "top_p": B}
         for gi in range(G):
             sizes[f"slot_mapping{gi}"] = B
             sizes[f"block_tables{gi}"] = B * self.cap_pages
@@ -77,6 +77,8 @@ class _Graph:
             q_lens=[1] * B, ctx_lens=[bucket] * B, max_q_len=1, max_ctx_len=bucket, is_graph_replay=True)
         self.temps = self._dsec("temps").view(torch.float32)
         self.uniforms = self._dsec("uniforms").view(torch.float64)
+        self.top_k = self._dsec("top_k")
+        self.top_p = self._dsec("top_p").view(torch.float32)
         self.graph = None
         self.ids = None
         self.launches = 0
@@ -89,7 +91,7 @@ class _Graph:
         o, n = self.offs[k]
         return self.dev[o:o + n]
 
-    def fill(self, engine, entries, totals, temperatures, uniforms, tokens_on_device: bool = False):
+    def fill(self, engine, entries, totals, temperatures, uniforms, tokens_on_device: bool = False, top_k=None, top_p=None):
         """Describe the step in the next host buffer and queue its copy to the device.  With
         ``tokens_on_device`` the token ids are not the host's to give: they are the ids the graph's
         previous replay sampled, copied on the device."""
@@ -131,6 +133,13 @@ class _Graph:
         u_host[:n] = uniforms
         t_host[n:] = 0.0
         u_host[n:] = 0.0
+        k_host, p_host = self._hsec("top_k"), self._hsec("top_p").view(np.float32)
+        k_host[:] = 0                                # no filter unless the step names one
+        p_host[:] = -1.0
+        if top_k is not None:
+            k_host[:n] = top_k
+        if top_p is not None:
+            p_host[:n] = top_p
         self.dev.copy_(self.host, non_blocking=True)
         if tokens_on_device:
             self._dsec("token_ids").copy_(self.ids)          # after the host's copy, before the replay
@@ -190,7 +199,8 @@ class DecodeGraphs:
             return False
         return all(cache.can_reserve(e.req_id, t) for e, t in zip(entries, totals))
 
-    def launch(self, entries, temperatures, uniforms, device_timer=None, tokens_on_device: bool = False) -> Launched:
+    def launch(self, entries, temperatures, uniforms, device_timer=None, tokens_on_device: bool = False,
+               top_k=None, top_p=None) -> Launched:
         """Queue one decode step: reserve pages, describe the batch, replay the graph, queue the copy
         of the sampled ids to pinned host memory.  Does not wait for the device, except the first
         time a (batch size, context bucket) is seen: that step runs eagerly and is then captured."""
@@ -225,7 +235,7 @@ class DecodeGraphs:
             gr = self.graphs[key] = _Graph(eng, *key)
         if tokens_on_device and gr.graph is None:
             raise RuntimeError("a chained step needs a captured graph (see can_chain)")
-        gr.fill(eng, entries, totals, temperatures, uniforms, tokens_on_device)
+        gr.fill(eng, entries, totals, temperatures, uniforms, tokens_on_device, top_k, top_p)
         if device_timer is not None:
             device_timer.start()
         ids_now = None
@@ -233,7 +243,7 @@ class DecodeGraphs:
             # first use: run eagerly on the static buffers (this step's result), then capture
             before = ops.launches["own"]
             logits = eng.model.forward(gr.ctx, eng.layer_caches)
-            gr.ids = ops.sample_rows(logits, gr.temps, gr.uniforms)
+            gr.ids = ops.sample_rows(logits, gr.temps, gr.uniforms, gr.top_k, gr.top_p)
             gr.launches = ops.launches["own"] - before
             ids_now = gr.ids.cpu().tolist()[:len(entries)]
             graph = torch.cuda.CUDAGraph()
@@ -245,7 +255,7 @@ class DecodeGraphs:
             try:
                 with torch.cuda.graph(graph):
                     logits = eng.model.forward(gr.ctx, eng.layer_caches)
-                    gr.ids = ops.sample_rows(logits, gr.temps, gr.uniforms)
+                    gr.ids = ops.sample_rows(logits, gr.temps, gr.uniforms, gr.top_k, gr.top_p)
             finally:
                 if gc_was_on:
                     gc.enable()

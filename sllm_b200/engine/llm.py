@@ -108,9 +108,9 @@ class LLM:
                 return [], {}
             entries = [StepEntry(p.req.req_id, p.req.token_slice(p.start, p.count),
                                  [p.count - 1] if p.sample else []) for p in plan]
-            rows = [(p.req.params, p.req.rng, p.req.tokens if not p.req.params.on_device else None)
+            rows = [(p.req.params, p.req.rng, p.req.tokens if p.req.params.needs_history else None)
                     for p in plan if p.sample]
-            if not (self.cuda_graphs and all(p.count == 1 and p.sample and p.req.params.on_device for p in plan)):
+            if not (self.cuda_graphs and all(p.count == 1 and p.sample and not p.req.params.needs_history for p in plan)):
                 ctx = self.engine.prepare(entries)
                 if device_timer is not None:
                     device_timer.start()
@@ -121,8 +121,8 @@ class LLM:
                 self.steps += 1
                 return finished, sampled
             # a pure decode step: replayed from a captured graph, sampling included
-            temps, unis = self.sampler.host_inputs(rows)
-            handle = self.engine.graphs.launch(entries, temps, unis, device_timer=device_timer)
+            temps, unis, top_k, top_p = self.sampler.host_inputs(rows)
+            handle = self.engine.graphs.launch(entries, temps, unis, device_timer=device_timer, top_k=top_k, top_p=top_p)
             self._inflight = (plan, handle)
         plan, handle = self._inflight
         self._inflight = self._chain(plan, device_timer)
@@ -148,8 +148,9 @@ class LLM:
         if not self.engine.graphs.can_chain(entries):
             return None
         rows = [(p.req.params, p.req.rng, None) for p in plan]
-        temps, unis = self.sampler.host_inputs(rows)
-        handle = self.engine.graphs.launch(entries, temps, unis, device_timer=device_timer, tokens_on_device=True)
+        temps, unis, top_k, top_p = self.sampler.host_inputs(rows)
+        handle = self.engine.graphs.launch(entries, temps, unis, device_timer=device_timer, tokens_on_device=True,
+                                           top_k=top_k, top_p=top_p)
         from .scheduler import Planned
         nxt = [Planned(p.req, p.start + 1, 1, True) for p in plan]
         return nxt, handle

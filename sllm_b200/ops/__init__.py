@@ -492,17 +492,40 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def sample_rows(logits: torch.Tensor, temperature=None, uniform=None) -> torch.Tensor:
+def sample_rows(logits: torch.Tensor, temperature=None, uniform=None, top_k=None, top_p=None) -> torch.Tensor:
     """int32 token per row of float32 ``logits [R, V]``: the first maximum where the
     row's temperature is <= 0 (or none is given), else inverse-CDF sampling of
-    softmax(logits / temperature) at the row's uniform (float64)."""
-    _chk(logits, temperature, uniform)
+    softmax(logits / temperature) at the row's uniform (float64), over the tokens that
+    the row's ``top_k`` (int32, <= 0: no filter) and then ``top_p`` (float32, < 0: no
+    filter) keep."""
+    _chk(logits, temperature, uniform, top_k, top_p)
     R, V = logits.shape
     if logits.dtype != torch.float32:
         raise KernelError("sample_rows: logits are float32")
     if temperature is not None and (temperature.dtype != torch.float32 or uniform is None
                                     or uniform.dtype != torch.float64):
         raise KernelError("sample_rows: temperature float32 and uniform float64, one per row")
+    if (top_k is not None or top_p is not None) and temperature is None:
+        raise KernelError("sample_rows: top_k/top_p filter sampled rows; give temperatures")
+    if (top_k is not None and (top_k.dtype != torch.int32 or top_k.numel() != R)) or \
+            (top_p is not None and (top_p.dtype != torch.float32 or top_p.numel() != R)):
+        raise KernelError("sample_rows: top_k int32 and top_p float32, one per row")
     out = torch.empty((R,), dtype=torch.int32, device=logits.device)
-    call("sllm_sample_rows", _p(logits), R, V, _p(temperature), _p(uniform), _p(out), _stream())
+    call("sllm_sample_rows", _p(logits), R, V, _p(temperature), _p(uniform), _p(top_k), _p(top_p), _p(out), _stream())
     return out
+
+
+def repetition_penalty_(logits: torch.Tensor, pair_row, pair_id, pair_penalty) -> torch.Tensor:
+    """In place on float32 ``logits [R, V]``: for each (row, id, penalty) triple a positive
+    logit is divided by the penalty and a negative one multiplied.  A (row, id) pair must
+    appear once; ids outside the vocabulary are ignored."""
+    _chk(logits, pair_row, pair_id, pair_penalty)
+    R, V = logits.shape
+    n = pair_row.numel()
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise KernelError("repetition_penalty_: logits are contiguous float32")
+    if pair_row.dtype != torch.int32 or pair_id.dtype != torch.int32 or pair_penalty.dtype != torch.float32 \
+            or pair_id.numel() != n or pair_penalty.numel() != n:
+        raise KernelError("repetition_penalty_: rows and ids int32, penalties float32, one per pair")
+    call("sllm_repetition_penalty", _p(logits), R, V, _p(pair_row), _p(pair_id), _p(pair_penalty), n, _stream())
+    return logits

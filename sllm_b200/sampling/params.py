@@ -29,12 +29,8 @@ class SamplingParams:
         self.stop_ids = tuple(int(s) for s in self.stop_ids)
 
     @property
-    def on_device(self) -> bool:
-        """Greedy and plain temperature sampling run in the sampling kernel; the
-        filters and the penalty take the row to the host."""
-        return self.top_k is None and self.top_p is None and not self._penalised
-
-    @property
-    def _penalised(self) -> bool:
+    def needs_history(self) -> bool:
+        """The repetition penalty reads the ids the request has seen, a list of any length;
+        such a row is sampled outside the captured decode step."""
         p = self.repetition_penalty
         return p is not None and p > 0 and p != 1.0

@@ -1,12 +1,13 @@
 """Sampling over the logits a step returns.
 
-Greedy and temperature sampling run on the device for all rows at once
-(`ops.sample_rows`); only the chosen ids cross to the host.  Rows that ask for
-top-k, top-p or a repetition penalty are taken to the host and sampled in float64
-exactly as the reference does (runtime/sampler.py:12-88).  Either way a sampled
+Every row is sampled on the device, all rows at once (`ops.sample_rows`): greedy,
+temperature, top-k and top-p as runtime/sampler.py:36-88 defines them, after the
+repetition penalty (runtime/sampler.py:12-33) has changed the seen ids' logits in
+place (`ops.repetition_penalty_`).  Only the chosen ids cross to the host.  A sampled
 token consumes one uniform from the request's own ``numpy.random.default_rng(seed)``
 (runtime/sampler.py:86; serving/executor.py:358), so equal logits give the
-reference's tokens.
+reference's tokens.  `sample_host` is the same sampler in numpy on one row; the
+engine does not call it.
 """
 
 from __future__ import annotations
@@ -64,8 +65,8 @@ def sample_host(logits: np.ndarray, params: SamplingParams, rng: np.random.Gener
 
 
 class Sampler:
-    """Picks one token per logits row.  ``rows`` pairs each row with its request's
-    parameters, generator and the ids seen so far (for the penalty)."""
+    """Picks one token per logits row on the device.  ``rows`` pairs each row with its
+    request's parameters, generator and the ids seen so far (for the penalty)."""
 
     def __init__(self, device):
         self.device = torch.device(device)
@@ -73,19 +74,51 @@ class Sampler:
 
     @staticmethod
     def host_inputs(rows):
-        """(temperatures float32[R], uniforms float64[R]) for rows that all sample on the
-        device; a sampled (non-greedy) row draws its one uniform here."""
-        temps = np.zeros(len(rows), dtype=np.float32)
-        unis = np.zeros(len(rows), dtype=np.float64)
+        """(temperatures float32[R], uniforms float64[R], top_k int32[R], top_p float32[R]) as
+        the sampling kernel takes them: temperature 0 is greedy, top_k 0 and top_p -1 filter
+        nothing; a sampled (non-greedy) row draws its one uniform here."""
+        n = len(rows)
+        temps = np.zeros(n, dtype=np.float32)
+        unis = np.zeros(n, dtype=np.float64)
+        top_k = np.zeros(n, dtype=np.int32)
+        top_p = np.full(n, -1.0, dtype=np.float32)
         for i, (p, rng, _) in enumerate(rows):
             t = float(p.temperature or 0.0)
             if t > 0:
                 temps[i] = t
-                unis[i] = rng.random()
-        return temps, unis
+                unis[i] = rng.random()              # one uniform per sampled token
+                if p.top_k is not None:
+                    top_k[i] = min(int(p.top_k), 2 ** 31 - 1)
+                if p.top_p is not None:
+                    top_p[i] = max(float(p.top_p), 0.0)
+        return temps, unis, top_k, top_p
+
+    @staticmethod
+    def penalty_pairs(rows):
+        """(row, id, penalty) arrays naming each seen id of each penalised row once, or None."""
+        r, t, q = [], [], []
+        for i, (p, _, seen) in enumerate(rows):
+            if p.needs_history and seen is not None and len(seen):
+                ids = np.unique(np.asarray(list(seen), dtype=np.int64))
+                r.append(np.full(ids.size, i, dtype=np.int32))
+                t.append(ids.astype(np.int32))
+                q.append(np.full(ids.size, p.repetition_penalty, dtype=np.float32))
+        if not r:
+            return None
+        return np.concatenate(r), np.concatenate(t), np.concatenate(q)
+
+    def _to_device(self, *arrays):
+        out = []
+        for a in arrays:
+            h = torch.from_numpy(a)
+            if self._pin:
+                h = h.pin_memory()
+            out.append(h.to(self.device, non_blocking=True))
+        return out
 
     def sample(self, logits: torch.Tensor, rows, device_timer=None) -> list[int]:
-        """rows: list of (SamplingParams, numpy Generator, seen ids or None)."""
+        """rows: list of (SamplingParams, numpy Generator, seen ids or None).  The penalty
+        changes ``logits`` in place."""
         R = logits.shape[0]
         if R != len(rows):
             raise ValueError(f"{R} logits rows for {len(rows)} requests")
@@ -93,26 +126,16 @@ class Sampler:
             if device_timer is not None:
                 device_timer.stop()
             return []
-        any_temp = any(p.temperature and p.temperature > 0 for p, _, _ in rows)
-        host_rows = [i for i, (p, _, _) in enumerate(rows) if not p.on_device]
-        temps = uni = None
-        if any_temp:
-            buf = torch.empty(R, dtype=torch.float32, pin_memory=self._pin)
-            ubuf = torch.zeros(R, dtype=torch.float64, pin_memory=self._pin)
-            for i, (p, rng, _) in enumerate(rows):
-                t = float(p.temperature or 0.0)
-                buf[i] = t if p.on_device else 0.0
-                if p.on_device and t > 0:
-                    ubuf[i] = rng.random()          # one uniform per sampled token
-            temps = buf.to(self.device, non_blocking=True)
-            uni = ubuf.to(self.device, non_blocking=True)
-        picked = ops.sample_rows(logits, temps, uni)
+        pairs = self.penalty_pairs(rows)
+        if pairs is not None:
+            ops.repetition_penalty_(logits, *self._to_device(*pairs))
+        temps, unis, top_k, top_p = self.host_inputs(rows)
+        if not (temps > 0).any():
+            picked = ops.sample_rows(logits)
+        elif not top_k.any() and not (top_p >= 0).any():
+            picked = ops.sample_rows(logits, *self._to_device(temps, unis))
+        else:
+            picked = ops.sample_rows(logits, *self._to_device(temps, unis, top_k, top_p))
         if device_timer is not None:
             device_timer.stop()
-        ids = picked.cpu().tolist()
-        for i in host_rows:
-            p, rng, seen = rows[i]
-            row = logits[i].float().cpu().numpy()
-            row = apply_repetition_penalty(row, seen, p.repetition_penalty)
-            ids[i] = sample_host(row, p, rng)
-        return [int(t) for t in ids]
+        return [int(t) for t in picked.cpu().tolist()]

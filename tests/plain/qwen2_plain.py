@@ -267,17 +267,21 @@ def sample(logits, temperature=1.0, top_k=None, top_p=None, u=None) -> int:
     return min(idx, probs.size - 1)
 
 
-def generate(prompt, max_new, w, cfg, temperature=0.0, seed=None, stop_ids=()):
+def generate(prompt, max_new, w, cfg, temperature=0.0, seed=None, stop_ids=(), top_k=None, top_p=None,
+             repetition_penalty=None):
     """Token-by-token generation by recomputing the whole sequence each time:
-    sample from the last row, a stop id ends the request and is not appended,
-    the context limit ends it too (serving/executor.py:366-393)."""
+    sample from the last row (after the repetition penalty over every id so far), a
+    stop id ends the request and is not appended, the context limit ends it too
+    (serving/executor.py:366-393)."""
     ids = list(prompt)
     rng = np.random.default_rng(seed)
     out = []
     for _ in range(max_new):
         logits = forward(ids, w, cfg)[-1]
+        if repetition_penalty is not None and repetition_penalty != 1.0:      # serving/executor.py:430-433
+            logits = apply_repetition_penalty(logits, ids, repetition_penalty)
         if temperature and temperature > 0:
-            nxt = sample(logits, temperature, u=rng.random())
+            nxt = sample(logits, temperature, top_k, top_p, u=rng.random())
         else:
             nxt = greedy(logits)
         if nxt in stop_ids:

@@ -43,10 +43,14 @@ def test_greedy_generation_float32_equals_plain(tiny, policy):
     res = llm.generate(prompts[:3], SamplingParams(max_new=16, temperature=0.8, seed=7))
     for p, r in zip(prompts, res):
         assert r.ids == plain.generate(p, 16, w, cfg, temperature=0.8, seed=7)
-    # top-k / top-p / penalty rows go through the host sampler
-    res = llm.generate(prompts[:2], SamplingParams(max_new=5, temperature=0.9, top_k=5, top_p=0.9, seed=1,
-                                                   repetition_penalty=1.2))
-    assert all(len(r.ids) == 5 for r in res)
+    # top-k, top-p and the repetition penalty, each alone and together (decode steps with filters run
+    # from the captured graph; rows with a penalty are sampled outside it)
+    for kw in (dict(top_k=5), dict(top_p=0.7), dict(repetition_penalty=1.3), dict(top_k=7, top_p=0.9, repetition_penalty=1.2),
+               dict(temperature=0.0, repetition_penalty=1.5)):
+        kw = {"temperature": 0.9, **kw}
+        res = llm.generate(prompts[:3], SamplingParams(max_new=12, seed=1, **kw))
+        for p, r in zip(prompts, res):
+            assert r.ids == plain.generate(p, 12, w, cfg, seed=1, **kw), kw
     # a stop id ends a request and is not part of the output
     first = plain.generate(prompts[0], 3, w, cfg)
     (r,) = llm.generate(prompts[:1], SamplingParams(max_new=8, stop_ids=(first[2],)))

@@ -261,6 +261,79 @@ def test_sample_rows(R, V):
             assert lo[r] == 0 and hi[r] >= V - 2
 
 
+@pytest.mark.parametrize("V", [97, 1000, 50257, 152064])
+def test_sample_rows_top_k_and_top_p(V):
+    """The kept set against the float64 sampler, over many uniforms: a token outside the set is
+    never returned and the kept ones come at the uniforms the plain sampler gives them."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(V)
+    cases = [(0.7, 5, -1.0), (1.0, 0, 0.8), (1.3, 40, 0.5), (0.9, 1, -1.0), (0.5, 0, 0.0), (1.0, 3, 1.0),
+             (2.0, V, 0.95), (1.0, V + 5, -1.0), (0.0, 4, 0.3), (1.1, 1000, 0.999)]
+    R = len(cases)
+    logits = torch.randn(R, V, device="cuda", generator=g) * 2.5
+    logits[1, V // 2] = logits[1].max() + 3                   # one token holds most of the mass
+    temps = torch.tensor([c[0] for c in cases], device="cuda")
+    top_k = torch.tensor([c[1] for c in cases], device="cuda", dtype=torch.int32)
+    top_p = torch.tensor([c[2] for c in cases], device="cuda")
+    for trial in range(6):
+        u = torch.rand(R, device="cuda", generator=g, dtype=torch.float64)
+        if trial == 4:
+            u.fill_(1e-300)                                   # (at exactly 0 the plain sampler names token 0, kept or not)
+        if trial == 5:
+            u.fill_(1.0 - 1e-12)
+        got = ops.sample_rows(logits, temps, u, top_k, top_p).tolist()
+        want = ref.sample_rows(logits, temps, u, top_k, top_p).tolist()
+        assert got == want, (trial, got, want)
+    # only one of the two filters given
+    u = torch.rand(R, device="cuda", generator=g, dtype=torch.float64)
+    assert ops.sample_rows(logits, temps, u, top_k, None).tolist() == ref.sample_rows(logits, temps, u, top_k, None).tolist()
+    assert ops.sample_rows(logits, temps, u, None, top_p).tolist() == ref.sample_rows(logits, temps, u, None, top_p).tolist()
+    with pytest.raises(ops.KernelError):
+        ops.sample_rows(logits, None, None, top_k, None)
+
+
+def test_sample_rows_filters_with_ties():
+    """Equal logits at the cut: top-k keeps exactly k tokens and top-p exactly as many of the
+    ties as reach its mass, the first ones by index; every kept token can be drawn, no other."""
+    ops = _ops()
+    V = 300
+    logits = torch.full((3, V), -4.0, device="cuda")
+    tied = [250, 11, 40, 199, 120, 77]                        # six tokens share the top value
+    logits[:, tied] = 2.0
+    logits[:, 5] = 3.0                                        # and one lies above them
+    temps = torch.ones(3, device="cuda")
+    top_k = torch.tensor([4, 0, 5], device="cuda", dtype=torch.int32)     # 5 and three of the ties; -; 5 and four ties
+    p5, p_tie = np.exp(3.0), np.exp(2.0)
+    tot = p5 + 6 * p_tie + (V - 7) * np.exp(-4.0)
+    # row 1: top-p reaches its mass inside the ties: after the top token and two of them
+    tp1 = (p5 + 1.5 * p_tie) / tot
+    # row 2: top-k keeps 5 (the top token and four ties); top-p of that set ends after three ties
+    tp2 = (p5 + 2.5 * p_tie) / (p5 + 4 * p_tie)
+    top_p = torch.tensor([-1.0, tp1, tp2], device="cuda", dtype=torch.float32)
+    want = [sorted([5] + sorted(tied)[:3]), sorted([5] + sorted(tied)[:2]), sorted([5] + sorted(tied)[:3])]
+    seen = [set(), set(), set()]
+    for i in range(400):
+        u = torch.full((3,), (i + 0.5) / 400, device="cuda", dtype=torch.float64)
+        for r, t in enumerate(ops.sample_rows(logits, temps, u, top_k, top_p).tolist()):
+            seen[r].add(t)
+    assert [sorted(s) for s in seen] == want
+
+
+def test_repetition_penalty_in_place():
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(4)
+    R, V = 4, 1000
+    logits = torch.randn(R, V, device="cuda", generator=g) * 3
+    rows = torch.tensor([0, 0, 0, 2, 2, 3, 3], device="cuda", dtype=torch.int32)
+    ids = torch.tensor([5, 999, 17, 0, 5, 1000, -1], device="cuda", dtype=torch.int32)      # the last two lie outside
+    pen = torch.tensor([1.5, 1.5, 1.5, 0.7, 0.7, 2.0, 2.0], device="cuda")
+    want = ref.repetition_penalty_(logits.clone(), rows, ids, pen)
+    got = ops.repetition_penalty_(logits.clone(), rows, ids, pen)
+    torch.testing.assert_close(got, want, rtol=1e-6, atol=0)
+    assert torch.equal(got[1], logits[1]) and torch.equal(got[3], logits[3])
+    assert not torch.equal(got[0], logits[0])
+
+
 def test_gather_rows():
     ops = _ops()
     x = torch.randn(40, 1000, device="cuda")

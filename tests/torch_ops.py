@@ -112,21 +112,26 @@ def gather_rows(x, rows):
     return x[rows.long()].clone()
 
 
-def sample_rows(logits, temperature=None, uniform=None):
+def sample_rows(logits, temperature=None, uniform=None, top_k=None, top_p=None):
+    from tests.plain import qwen2_plain as plain
     R, V = logits.shape
     out = torch.empty(R, dtype=torch.int32, device=logits.device)
     for r in range(R):
         t = float(temperature[r]) if temperature is not None else 0.0
-        row = logits[r].double()
-        if not t > 0:
-            out[r] = int(torch.argmax(row))
-            continue
-        p = torch.exp(row / t - (row / t).max())
-        p = p / p.sum()
-        idx = int(torch.searchsorted(torch.cumsum(p, 0), uniform[r].double().reshape(1))[0])
-        out[r] = min(idx, V - 1)
+        k = int(top_k[r]) if top_k is not None and int(top_k[r]) > 0 else None
+        p = float(top_p[r]) if top_p is not None and float(top_p[r]) >= 0 else None
+        out[r] = plain.sample(logits[r].double().cpu().numpy(), t, k, p, u=float(uniform[r]) if t > 0 else None)
     return out
 
 
+def repetition_penalty_(logits, pair_row, pair_id, pair_penalty):
+    V = logits.shape[1]
+    for r, i, q in zip(pair_row.tolist(), pair_id.tolist(), pair_penalty.tolist()):
+        if 0 <= i < V:
+            v = float(logits[r, i])
+            logits[r, i] = v * q if v < 0 else v / q
+    return logits
+
+
 ALL = ["embed_gather", "add_rmsnorm", "linear", "can_accumulate", "linear_accumulate", "silu_mul", "linear_silu_mul", "rope_kv_write",
-       "attention_simt", "paged_attention", "gather_rows", "sample_rows"]
+       "attention_simt", "paged_attention", "gather_rows", "sample_rows", "repetition_penalty_"]
