@@ -75,12 +75,16 @@ def main(argv=None) -> int:
     ap.add_argument("--host", default=None)
     ap.add_argument("--port", default=None)
     ap.add_argument("--chat", default=None, help="text of one user turn (byte-level stand-in tokenizer)")
+    ap.add_argument("--prompt", default=None, help="raw completion prompt (byte-level stand-in tokenizer)")
+    ap.add_argument("--batch", nargs="+", default=None, metavar="PROMPT",
+                    help="several prompts served together with continuous batching")
     ap.add_argument("--prompt-ids", default=None, help="comma-separated token ids of the prompt")
     ap.add_argument("--max-new", type=int, default=None)
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--top-p", type=float, default=None)
     ap.add_argument("--top-k", type=int, default=None)
     ap.add_argument("--seed", type=int, default=None)
+    ap.add_argument("--repetition-penalty", type=float, default=None)
     ap.add_argument("--dtype", choices=("bfloat16", "float32", "bf16", "fp32"), default=None)
     ap.add_argument("--random-weights", type=int, default=None, metavar="SEED",
                     help="write a random model folder from the recipe's geometry and run it")
@@ -138,24 +142,33 @@ def main(argv=None) -> int:
                   kv_utilization=recipe.kv_utilization,
                   progress=lambda d, t: log("INFO", f"load: {d}/{t} tensors"))
         vocab = llm.model.plan.vocab_size
+        tok = None
         if args.prompt_ids:
-            prompt = [int(x) for x in args.prompt_ids.replace(" ", "").split(",") if x]
-            tok = None
+            prompts = [[int(x) for x in args.prompt_ids.replace(" ", "").split(",") if x]]
         else:
             from .tokenizer import ByteTokenizer
             tok = ByteTokenizer(vocab)
-            prompt = tok.encode(args.chat or "hello")                                   # serving/main.py:256
+            # serving/cli.py:33-54: --batch, else --chat, else --prompt; serving/main.py:256: "hello"
+            texts = args.batch or [args.chat if args.chat is not None else (args.prompt if args.prompt is not None else "hello")]
+            prompts = [tok.encode(t) for t in texts]
         params = SamplingParams(max_new=settings["max_new"], temperature=args.temperature, top_k=args.top_k,
-                                top_p=args.top_p, seed=args.seed)
+                                top_p=args.top_p, seed=args.seed, repetition_penalty=args.repetition_penalty)
         import time
         t0 = time.perf_counter()
-        (res,) = llm.generate([prompt], params)
+        results = llm.generate(prompts, params)
         dt = time.perf_counter() - t0
-        log("INFO", f"prompt={len(prompt)} out={len(res.ids)} wall={dt:.3f}s ({len(res.ids) / max(dt, 1e-9):.1f} tok/s) "
-                    f"finish={res.finish_reason}")                                       # serving/executor.py:422-427
-        print(",".join(str(i) for i in res.ids))
-        if tok is not None:
-            print(tok.decode(res.ids))
+        n_out = sum(len(r.ids) for r in results)
+        log("INFO", f"prompt={sum(len(p) for p in prompts)} out={n_out} wall={dt:.3f}s ({n_out / max(dt, 1e-9):.1f} tok/s) "
+                    f"finish={','.join(r.finish_reason for r in results)}")           # serving/executor.py:422-427
+        for i, res in enumerate(results):
+            ids = ",".join(str(t) for t in res.ids)
+            if args.batch:                                                              # serving/cli.py:40-41
+                print(f"[{args.batch[i]!r}] -> {ids}")
+                print(f"[{args.batch[i]!r}] -> {tok.decode(res.ids)!r}")
+            else:
+                print(ids)
+                if tok is not None:
+                    print(tok.decode(res.ids))
         return 0
     except ConfigError as e:
         raise SystemExit(f"sllm: {e}") from None

@@ -66,3 +66,13 @@ def test_run_mode_on_cpu_ops(cpu_ops, capsys, monkeypatch):
                      "--dtype", "float32", "--log-level", "ERROR"]) == 0
     ids = capsys.readouterr().out.strip().split(",")
     assert len(ids) == 4 and all(0 <= int(i) < 256 for i in ids)
+    # several prompts at once, with the filters and the penalty of the sampler
+    assert cli.main(["tiny-qwen2", "--mode", "run", "--random-weights", "3", "--batch", "one two", "three", "--max-new", "3",
+                     "--temperature", "0.8", "--top-k", "5", "--top-p", "0.9", "--seed", "1", "--repetition-penalty", "1.2",
+                     "--dtype", "float32", "--log-level", "ERROR"]) == 0
+    out = capsys.readouterr().out.strip().splitlines()
+    assert len(out) == 4 and out[0].startswith("['one two'] -> ") and out[2].startswith("['three'] -> ")
+    assert len(out[0].split(" -> ")[1].split(",")) == 3
+    assert cli.main(["tiny-qwen2", "--mode", "run", "--random-weights", "3", "--prompt", "abc", "--max-new", "2",
+                     "--dtype", "float32", "--log-level", "ERROR"]) == 0
+    assert len(capsys.readouterr().out.strip().splitlines()) == 2               # ids, then text
