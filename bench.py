@@ -230,15 +230,96 @@ def prefill_run(model, cfg, tokens, reps=5, seed=1, warmup=3):
     return statistics.median(times)
 
 
+# The baseline's serving workloads (its fourth and fifth configurations): many requests of mixed length through
+# the scheduler, prompt portions beside decoded tokens, timed by wall clock around `LLM.generate`.
+SERVING = {
+    "serve-0.5b": {
+        "name": "Qwen2.5-Coder-0.5B sizes",
+        "config": {"num_hidden_layers": 24, "hidden_size": 896, "num_attention_heads": 14, "num_key_value_heads": 2,
+                   "head_dim": 64, "intermediate_size": 4864, "vocab_size": 151936, "rms_norm_eps": 1e-6,
+                   "tie_word_embeddings": True},
+        "batch": 32, "prompt_lens": (128, 4096), "max_new": 128, "temperature": 0.7, "chunk": 512, "context": 8192,
+    },
+    "serve-32b": {
+        "name": "Qwen2.5-32B sizes",
+        "config": {"num_hidden_layers": 64, "hidden_size": 5120, "num_attention_heads": 40, "num_key_value_heads": 8,
+                   "head_dim": 128, "intermediate_size": 27648, "vocab_size": 152064, "rms_norm_eps": 1e-5,
+                   "tie_word_embeddings": False},
+        "batch": 16, "prompt_lens": (512, 6144), "max_new": 256, "temperature": 0.0, "chunk": 1024, "context": 8192,
+    },
+}
+
+
+def serving_run(which: str, layers: int | None = None) -> dict:
+    """One JSON record for a serving workload: the wall time of `LLM.generate` over the whole batch of
+    requests (second of two runs: the first captures the decode graphs), host tokens in and out."""
+    import numpy as np
+    import torch
+
+    from sllm_b200 import ops
+    from sllm_b200.engine import build_random_model
+    from sllm_b200.engine.llm import LLM
+    from sllm_b200.sampling import SamplingParams
+    w = SERVING[which]
+    cfg = dict(CONFIG_7B)
+    cfg.update(w["config"])
+    full = cfg["num_hidden_layers"]
+    if layers:
+        cfg["num_hidden_layers"] = layers
+    model, _ = build_random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0", std=0.02)
+    rng = np.random.default_rng(0)
+    lo, hi = w["prompt_lens"]
+    prompts = [rng.integers(0, cfg["vocab_size"], size=int(rng.integers(lo, hi + 1))).tolist() for _ in range(w["batch"])]
+    llm = LLM(model=model, block_size=PAGE_SIZE, max_num_seqs=w["batch"], chunk_size=w["chunk"],
+              max_batch_tokens=w["batch"] * w["chunk"], max_model_len=w["context"])     # the reference bounds a step's
+    # tokens by requests x portion (runtime/scheduler.py:57-58): every running request may bring a portion
+    runs = []
+    for rep in range(2):
+        params = [SamplingParams(max_new=w["max_new"], temperature=w["temperature"], seed=100 * rep + i)
+                  for i in range(len(prompts))]
+        sampler = ClockSampler()
+        sampler.start()
+        before = dict(ops.launches)
+        steps0 = llm.steps
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        res = llm.generate(prompts, params)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        runs.append({"s": dt, "clocks": sampler.stop(), "steps": llm.steps - steps0,
+                     "own": ops.launches["own"] - before["own"], "library": ops.launches["library"] - before["library"],
+                     "out": sum(len(r.ids) for r in res)})
+    ops.check_tcgen05_status()
+    llm.engine.cache.check()
+    n_in = sum(len(p) for p in prompts)
+    r = runs[-1]
+    return {
+        "metric": f"tokens/s through LLM.generate ({w['name']}, bf16, {w['batch']} requests, prompts of "
+                  f"{lo}..{hi} tokens, {w['max_new']} new tokens each, prompt portions of {w['chunk']} beside decoded tokens)",
+        "value": round((n_in + r["out"]) / r["s"], 1), "unit": "tokens/s (prompt and generated)", "n_gpus": 1,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), uniform random token ids",
+        "wall_s": round(r["s"], 3), "first_run_s": round(runs[0]["s"], 3), "prompt_tokens": n_in, "generated_tokens": r["out"],
+        "generated_tok_s": round(r["out"] / r["s"], 1), "steps": r["steps"],
+        "config": {"model": w["name"], "layers": cfg["num_hidden_layers"], "layers_full": full, "hidden": cfg["hidden_size"],
+                   "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": w["batch"],
+                   "seq_len": w["context"], "chunk": w["chunk"], "step_token_budget": w["batch"] * w["chunk"], "temperature": w["temperature"], "page_size": PAGE_SIZE,
+                   "kv_dtype": "bf16", "parallelism": "1 GPU"},
+        "gpu_launches": r["own"], "library_launches": r["library"], "clocks": r["clocks"],
+    }
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", choices=("decode",) + tuple(SERVING), default="decode",
+                    help="decode: the default run; serve-*: the baseline's serving workloads through LLM.generate")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer than 28 only where memory or time needs it")
+    ap.add_argument("--layers", type=int, default=None, help="fewer than the configuration has, only where memory or time needs it")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64 and the prefill")
     ap.add_argument("--prefill-only", action="store_true", help="run the 2,048-token prefill alone (for profilers)")
@@ -264,6 +345,10 @@ def main(argv=None) -> int:
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device"}))
         return 1
+    if args.workload != "decode":
+        print(json.dumps(serving_run(args.workload, args.layers)))
+        return 0
+    args.layers = args.layers or FULL_LAYERS
     peaks, peaks_kind = load_peaks()
     cfg = dict(CONFIG_7B)
     cfg["num_hidden_layers"] = args.layers

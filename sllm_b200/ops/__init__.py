@@ -48,7 +48,14 @@ def _p(t):
     return None if t is None else t.data_ptr()
 
 
+# the raw handle of the current stream: torch's quick accessor where this torch has it (the public
+# `current_stream()` builds a Stream object, several microseconds a launch)
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
