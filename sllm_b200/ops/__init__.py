@@ -153,7 +153,9 @@ def check_tcgen05_status() -> None:
         if code:
             t.zero_()
             who = {1: "gemm_tcgen05: the TMA producer", 2: "gemm_tcgen05: the MMA issuer", 3: "gemm_tcgen05: the epilogue",
-                   11: "attention_tma: the producer", 12: "attention_tma: a compute warp"}.get(code, f"code {code}")
+                   11: "attention_tma: the producer", 12: "attention_tma: a compute warp",
+                   31: "linear_tc: the TMA producer", 32: "linear_tc: the MMA issuer", 33: "linear_tc: the epilogue",
+                   }.get(code, f"code {code}")
             raise KernelError(f"{who} on {dev}: a bounded wait ran out; the result is not valid")
 
 
@@ -179,6 +181,53 @@ def gemm_tcgen05(x, w, bias, out_dtype, *, silu: bool = False):
     else:
         epi, out = 1, torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     call("sllm_gemm_tcgen05", _p(x), _p(w), _p(bias), _p(out), M, N, K, epi, _p(_status_word(x.device)), _stream())
+    _tc_used["since_check"] += 1
+    return out
+
+
+LINEAR_TC_MAX_ROWS = 128  # the tokens are the tensor core's N side: one tile of at most 128
+# Plain products go to it only where it beats the library: a reduction of at least this length with at
+# most this many tokens (at 7B sizes, 64 tokens: down 29.3 against 30.7 us; qkv 11.6 against 9.2 us).
+LINEAR_TC_SPLIT_MIN_K = 8192
+LINEAR_TC_SPLIT_MAX_ROWS = 64
+
+
+_LINEAR_TC = os.environ.get("SLLM_LINEAR_TCGEN05", "1") != "0"     # 0: 33..128 tokens on the library product
+
+
+def linear_tc_supports(M: int, N: int, K: int) -> bool:
+    return _LINEAR_TC and STREAM_MAX_ROWS < M <= LINEAR_TC_MAX_ROWS and bool(lib().sllm_linear_tc_supports(int(M), int(N), int(K)))
+
+
+def _tc_splits(N: int, K: int) -> int:
+    """Slices of K so that (tiles of 128 rows) x slices comes to about one unit per SM, each slice
+    at least eight 64-wide k blocks long."""
+    tiles = -(-N // 128)
+    return max(1, min(NUM_SMS // tiles, (K // 64) // 8))
+
+
+def linear_tc(x, w, bias, out_dtype, *, splits: int = 1, silu: bool = False):
+    """The weight-streaming product on the tcgen05 tensor cores for up to 128 tokens.  With
+    ``splits`` > 1 the result is a float32 stack ``[splits', M, N]`` of partial sums (bias in the
+    first) that the consumer adds; with ``silu`` the matrix is gate|up interleaved in blocks of 8
+    and the bfloat16 result is ``silu(gate) * up`` of width N/2."""
+    _chk(x, w, bias)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("linear_tc: bfloat16 operands only")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"linear: x {tuple(x.shape)} does not fit w {tuple(w.shape)}")
+    real = 1
+    if silu:
+        epi, out = 2, torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    elif out_dtype == torch.float32:
+        real = int(lib().sllm_linear_tc_splits(K, int(splits))) if splits > 1 else 1
+        epi = 0
+        out = torch.empty((real, M, N) if real > 1 else (M, N), dtype=torch.float32, device=x.device)
+    else:
+        epi, out = 1, torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    call("sllm_linear_tc", _p(x), _p(w), _p(bias), _p(out), M, N, K, real, epi, _p(_status_word(x.device)), _stream())
     _tc_used["since_check"] += 1
     return out
 
@@ -246,6 +295,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype, allow
     if stream_supports(M, N, K):
         splits = _stream_splits(N, K) if (allow_partials and out_dtype == torch.float32) else 1
         return linear_stream(x, w, bias, out_dtype, splits=splits)
+    if allow_partials and out_dtype == torch.float32 and M <= LINEAR_TC_SPLIT_MAX_ROWS and K >= LINEAR_TC_SPLIT_MIN_K \
+            and linear_tc_supports(M, N, K):
+        # a long reduction into few columns (the down projection): slices of K over all the SMs
+        return linear_tc(x, w, bias, out_dtype, splits=_tc_splits(N, K))
     launches["library"] += 1
     if out_dtype == torch.float32:
         out = torch.mm(x, w.t(), out_dtype=torch.float32)
@@ -274,6 +327,8 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, o
         N = w_gate_up.shape[0]
         if stream_supports(M, N, K):
             return linear_stream(x, w_gate_up, None, out_dtype, silu=True)
+        if N % 16 == 0 and linear_tc_supports(M, N, K):
+            return linear_tc(x, w_gate_up, None, out_dtype, silu=True)
         if M > TCGEN05_MIN_ROWS and N % 16 == 0 and tcgen05_supports(M, N, K):
             # many rows: the tcgen05 product with the activation applied as the tile leaves tensor memory
             return gemm_tcgen05(x, w_gate_up, None, out_dtype, silu=True)

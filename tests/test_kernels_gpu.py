@@ -558,6 +558,54 @@ def test_gemm_tcgen05_silu(M, I, K):
     torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=1.6e-2)
 
 
+@pytest.mark.parametrize("M", [33, 64, 65, 100, 128])
+@pytest.mark.parametrize("N,K", [(128, 64), (136, 72), (1000, 264), (4608, 3584), (3584, 18944)])
+def test_linear_tc(M, N, K):
+    """The tcgen05 streaming product against the float32 statement: one and several slices of K (their
+    sum is the product, bias once), ragged rows, a k tail, both accumulator widths, and a row's result
+    does not depend on the other rows of the batch."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(18)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g)
+    want = x.float() @ w.float().t() + b
+    assert ops.linear_tc_supports(M, N, K)
+    whole = ops.linear_tc(x, w, b, torch.float32)
+    torch.testing.assert_close(whole, want, rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(ops.linear_tc(x, w, None, torch.bfloat16).float(), want - b, rtol=1.6e-2, atol=1.6e-2)
+    for splits in (2, 5, 1000):
+        parts = ops.linear_tc(x, w, b, torch.float32, splits=splits)
+        if K > 64:
+            assert parts.dim() == 3 and 2 <= parts.shape[0] <= min(splits, -(-K // 64))
+            parts = parts.sum(0)
+        torch.testing.assert_close(parts, want, rtol=2e-3, atol=2e-3)
+    ops.check_tcgen05_status()
+    fewer = ops.linear_tc(x[M - 33:].contiguous(), w, b, torch.float32)
+    assert torch.equal(fewer[-1], whole[-1])
+    # and through the dispatch, as the engine calls it
+    torch.testing.assert_close(ops.linear(x, w, b, torch.float32), want, rtol=2e-3, atol=2e-3)
+    stack = ops.linear(x, w, b, torch.float32, allow_partials=True)
+    assert (stack.dim() == 3) == (K >= ops.LINEAR_TC_SPLIT_MIN_K and M <= ops.LINEAR_TC_SPLIT_MAX_ROWS)
+    torch.testing.assert_close(stack.sum(0) if stack.dim() == 3 else stack, want, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("M,I,K", [(40, 128, 64), (64, 200, 136), (128, 4864, 896), (96, 18944, 3584)])
+def test_linear_tc_silu(M, I, K):
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(19)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    wg = (torch.randn(I, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    wu = (torch.randn(I, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    gu = torch.stack([wg.reshape(I // 8, 8, K), wu.reshape(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
+    gate, up = x.float() @ wg.float().t(), x.float() @ wu.float().t()
+    want = gate * torch.sigmoid(gate) * up
+    got = ops.linear_tc(x, gu, None, torch.bfloat16, silu=True)
+    ops.check_tcgen05_status()
+    torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=1.6e-2)
+    torch.testing.assert_close(ops.linear_silu_mul(x, gu, 8, torch.bfloat16).float(), want, rtol=1.6e-2, atol=1.6e-2)
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("N,K", [(16, 32), (100, 96), (3584, 3584), (4608, 3584), (200, 18944), (1000, 320)])
 def test_linear_ws(M, N, K):
