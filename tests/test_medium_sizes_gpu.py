@@ -103,3 +103,43 @@ def test_head_sizes_the_tensor_core_forms_do_not_take(name, tmp_path):
         with pytest.raises(ValueError, match="head_dim=272"):     # already when its parts are made to name its tensors
             write_random_model(d2, big, 32, std=0.03)
             build_model(d2, "bfloat16", dev)
+
+
+ODD_WIDTHS = {
+    # rows of 200 and 180 bytes: no 16-byte alignment for the vector loads and TMA boxes of the fast forms
+    "h100_i90_v777": dict(BASE, num_hidden_layers=2, hidden_size=100, num_attention_heads=3, num_key_value_heads=1, head_dim=32,
+                          intermediate_size=90, vocab_size=777, rope_theta=10000.0, rms_norm_eps=1e-6,
+                          max_position_embeddings=512, tie_word_embeddings=False),
+    "h36_i52_v130": dict(BASE, num_hidden_layers=3, hidden_size=36, num_attention_heads=2, num_key_value_heads=2, head_dim=16,
+                         intermediate_size=52, vocab_size=130, rope_theta=1000000.0, rms_norm_eps=1e-5,
+                         max_position_embeddings=512, tie_word_embeddings=True),
+    "h250_i1000_v5003": dict(BASE, num_hidden_layers=2, hidden_size=250, num_attention_heads=7, num_key_value_heads=1, head_dim=64,
+                             intermediate_size=1000, vocab_size=5003, rope_theta=10000.0, rms_norm_eps=1e-6,
+                             max_position_embeddings=512, tie_word_embeddings=False),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ODD_WIDTHS))
+def test_widths_that_are_multiples_of_nothing(name, tmp_path):
+    """A hidden size, an intermediate size and a vocabulary that are multiples of neither 8 nor 16: every
+    kernel takes them or hands them to a form that does; whole and cut, both dtypes, against the plain
+    implementation."""
+    from sllm_b200.engine import Engine, build_model
+    from sllm_b200.weights import write_random_model
+    dev = cuda_or_skip()
+    cfg = ODD_WIDTHS[name]
+    d = str(tmp_path / "model")
+    write_random_model(d, cfg, 41, std=0.05, bias_std=0.2, gain_std=0.1)
+    c, w = plain.load_model(d)
+    rng = np.random.default_rng(23)
+    reqs = {f"r{i}": rng.integers(0, cfg["vocab_size"], n).tolist() for i, n in enumerate((70, 9, 150))}
+    want = {r: plain.forward(ids, w, c) for r, ids in reqs.items()}
+    spread = float(np.concatenate([v.ravel() for v in want.values()]).std())
+    for dtype in ("float32", "bfloat16"):
+        tol = dict(rtol=1e-4, atol=1e-4) if dtype == "float32" else dict(rtol=2e-2, atol=0.08 * spread)
+        model, _ = build_model(d, dtype, dev)
+        for mode in ("whole", "tail_decode", "portions", "mixed"):
+            tr = getattr(traces, mode)(reqs)
+            eng = Engine(model, page_size=16, num_pages=tr.max_tokens // 16, max_requests=4)
+            out = traces.replay_engine(tr, eng)
+            traces.compare(tr, out, want, what=f"{name}/{dtype}/{mode}", **tol)
