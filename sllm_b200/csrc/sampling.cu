@@ -320,6 +320,186 @@ __device__ __forceinline__ bool is_kept(const Kept& kp, float l, int i) {
   return key > kp.tau || (key == kp.tau && i <= kp.i_eq);
 }
 
+// ---- a small top-k in one pass over the row ------------------------------------------------------
+//
+// Each thread keeps the five largest logits of its share of the row; the four largest of every
+// thread are the candidates (4096 of them), the fifth bounds what the thread let go.  If the k-th
+// largest candidate lies above every such bound, the k largest logits of the row are all among the
+// candidates and the rest of the work (top-k's cut, top-p over what it kept, the draw in index
+// order) runs on at most k values in shared memory.  Otherwise (a thread held more than four of the
+// row's k largest) the general path above takes the row.  The probabilities of top-k's set are
+// renormalised, so the sum over the whole row is never needed here.
+
+constexpr int FAST_K = 64;                  // rows with top_k up to this try the one-pass form
+constexpr int FAST_PER_THREAD = 4;
+constexpr int FAST_CANDIDATES = SAMPLE_THREADS * FAST_PER_THREAD;
+constexpr int FAST_TIES = 1024;
+static_assert(FAST_CANDIDATES * 8 <= SAMPLE_SMEM, "the candidates live in the histograms' shared memory");
+
+struct FastShared {
+  uint32_t kept_key[FAST_K], sorted_key[FAST_K];
+  int kept_idx[FAST_K], sorted_idx[FAST_K], by_index[FAST_K];
+  int tie_idx[FAST_TIES];
+  int n_kept, n_ties, max_let_go, answer, ok;
+};
+
+// true: out[row] is written.  false: the general path must take the row.  `mx` is set either way.
+__device__ bool sample_top_k_fast(const float* __restrict__ row, int V, float inv_t, int k, float pfrac, double u,
+                                  unsigned char* dyn_smem, int* bin_c, double* bin_m, Select* sel, MaxIdx* sh_mi,
+                                  FastShared* fs, MaxIdx* mx_out, int* out) {
+  uint32_t* cand_key = reinterpret_cast<uint32_t*>(dyn_smem);
+  int* cand_idx = reinterpret_cast<int*>(cand_key + FAST_CANDIDATES);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float v0 = -INFINITY, v1 = -INFINITY, v2 = -INFINITY, v3 = -INFINITY, v4 = -INFINITY;
+  int i0 = -1, i1 = -1, i2 = -1, i3 = -1, i4 = -1;
+  for_row(row, V, [&](float l, int i) {
+    if (l > v4 || i4 < 0) {                         // an equal later logit does not displace an earlier one
+      if (l != l) return;                           // not a number: never a candidate
+      v4 = l; i4 = i;
+      if (v4 > v3 || i3 < 0) {
+        float tv = v3; v3 = v4; v4 = tv; int ti = i3; i3 = i4; i4 = ti;
+        if (v3 > v2 || i2 < 0) {
+          tv = v2; v2 = v3; v3 = tv; ti = i2; i2 = i3; i3 = ti;
+          if (v2 > v1 || i1 < 0) {
+            tv = v1; v1 = v2; v2 = tv; ti = i1; i1 = i2; i2 = ti;
+            if (v1 > v0 || i0 < 0) { tv = v0; v0 = v1; v1 = tv; ti = i0; i0 = i1; i1 = ti; }
+          }
+        }
+      }
+    }
+  });
+  // the row's maximum (first index among equals) from the threads' own
+  {
+    MaxIdx best{i0 >= 0 ? v0 : -INFINITY, i0 >= 0 ? i0 : 0x7fffffff};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      MaxIdx other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+      best = better(best, other);
+    }
+    if (lane == 0) sh_mi[warp] = best;
+    if (threadIdx.x == 0) { fs->n_kept = 0; fs->n_ties = 0; fs->max_let_go = 0; fs->answer = -1; fs->ok = 1; }
+    __syncthreads();
+    if (warp == 0) {
+      MaxIdx b = sh_mi[lane];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        MaxIdx other{__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
+        b = better(b, other);
+      }
+      if (lane == 0) { if (b.i == 0x7fffffff) b.i = 0; sh_mi[0] = b; }
+    }
+  }
+  // the candidates, and the largest logit any thread let go
+  {
+    const float vs[FAST_PER_THREAD] = {v0, v1, v2, v3};
+    const int is[FAST_PER_THREAD] = {i0, i1, i2, i3};
+#pragma unroll
+    for (int j = 0; j < FAST_PER_THREAD; ++j) {
+      cand_key[threadIdx.x * FAST_PER_THREAD + j] = is[j] >= 0 ? order_key(vs[j]) : 0u;
+      cand_idx[threadIdx.x * FAST_PER_THREAD + j] = is[j];
+    }
+    if (i4 >= 0) atomicMax(&fs->max_let_go, (int)(order_key(v4) >> 1));     // (31 bits: compared again below)
+  }
+  __syncthreads();
+  const MaxIdx mx = sh_mi[0];
+  *mx_out = mx;
+  // the k-th largest candidate: four levels of 8 bits over the candidates' keys
+  if (threadIdx.x == 0) *sel = Select{0, 0u, 0u, 0, 0.0, 0, 0.0, 0.0, 0};
+  for (int level = 1; level <= 4; ++level) {
+    const int shift = 32 - 8 * level;
+    if (threadIdx.x < SEL_BINS) { bin_c[threadIdx.x] = 0; bin_m[threadIdx.x] = 0.0; }
+    __syncthreads();
+    const uint32_t prefix = sel->prefix, mask = sel->mask;
+#pragma unroll
+    for (int j = 0; j < FAST_PER_THREAD; ++j) {
+      const int c = threadIdx.x * FAST_PER_THREAD + j;
+      if (cand_idx[c] >= 0 && (cand_key[c] & mask) == prefix) atomicAdd(&bin_c[(cand_key[c] >> shift) & 255u], 1);
+    }
+    __syncthreads();
+    if (warp == 0) choose_bin(level, false, k, false, 0.0, bin_c, bin_m, sel);
+    __syncthreads();
+  }
+  const uint32_t tau = sel->prefix;
+  const int n_eq = k - sel->cnt_above, ties = sel->group_cnt;
+  // every logit a thread let go must lie below tau (the bound was kept to 31 bits: compare those)
+  if ((int)(tau >> 1) <= fs->max_let_go || ties > FAST_TIES) return false;
+  // top-k's set: above tau, and the first n_eq of the ties by index
+#pragma unroll
+  for (int j = 0; j < FAST_PER_THREAD; ++j) {
+    const int c = threadIdx.x * FAST_PER_THREAD + j;
+    if (cand_idx[c] < 0) continue;
+    if (cand_key[c] > tau) {
+      const int at = atomicAdd(&fs->n_kept, 1);
+      fs->kept_key[at] = cand_key[c];
+      fs->kept_idx[at] = cand_idx[c];
+    } else if (cand_key[c] == tau) {
+      fs->tie_idx[atomicAdd(&fs->n_ties, 1)] = cand_idx[c];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < ties) {
+    const int mine = fs->tie_idx[threadIdx.x];
+    int rank = 0;
+    for (int j = 0; j < ties; ++j) rank += fs->tie_idx[j] < mine;
+    if (rank < n_eq) {
+      const int at = atomicAdd(&fs->n_kept, 1);
+      fs->kept_key[at] = tau;
+      fs->kept_idx[at] = mine;
+    }
+  }
+  __syncthreads();
+  int m = fs->n_kept;                               // == k
+  // top-p over the kept values in descending order, ties by index (runtime/sampler.py:68-79)
+  if (pfrac >= 0.f) {
+    if (threadIdx.x < m) {
+      const uint32_t key = fs->kept_key[threadIdx.x];
+      const int idx = fs->kept_idx[threadIdx.x];
+      int rank = 0;
+      for (int j = 0; j < m; ++j) rank += fs->kept_key[j] > key || (fs->kept_key[j] == key && fs->kept_idx[j] < idx);
+      fs->sorted_key[rank] = key;
+      fs->sorted_idx[rank] = idx;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      double total = 0.0, c = 0.0;
+      for (int j = 0; j < m; ++j) total += (double)prob(key_value(fs->sorted_key[j]), mx.v, inv_t);
+      int cutoff = m;
+      for (int j = 0; j < m; ++j) {
+        c += (double)prob(key_value(fs->sorted_key[j]), mx.v, inv_t);
+        if (c >= (double)pfrac * total) { cutoff = j + 1; break; }
+      }
+      fs->n_kept = cutoff;
+    }
+    __syncthreads();
+    m = fs->n_kept;
+    if (threadIdx.x < m) {
+      fs->kept_key[threadIdx.x] = fs->sorted_key[threadIdx.x];
+      fs->kept_idx[threadIdx.x] = fs->sorted_idx[threadIdx.x];
+    }
+    __syncthreads();
+  }
+  // the draw: cumulative probability over the kept tokens in index order (runtime/sampler.py:81-88)
+  if (threadIdx.x < m) {
+    const int idx = fs->kept_idx[threadIdx.x];
+    int rank = 0;
+    for (int j = 0; j < m; ++j) rank += fs->kept_idx[j] < idx;
+    fs->by_index[rank] = threadIdx.x;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double total = 0.0, c = 0.0;
+    for (int r = 0; r < m; ++r) total += (double)prob(key_value(fs->kept_key[fs->by_index[r]]), mx.v, inv_t);
+    const double target = u * total;
+    int answer = fs->kept_idx[fs->by_index[m - 1]];          // u beyond the last cumulative value: the last kept token
+    for (int r = 0; r < m; ++r) {
+      c += (double)prob(key_value(fs->kept_key[fs->by_index[r]]), mx.v, inv_t);
+      if (c >= target) { answer = fs->kept_idx[fs->by_index[r]]; break; }
+    }
+    *out = answer;
+  }
+  return true;
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
                    const double* __restrict__ uniform, const int* __restrict__ top_k, const float* __restrict__ top_p,
@@ -337,22 +517,31 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
   __shared__ double pick_before;
   pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
+  __shared__ FastShared fast;
   const float* row = logits + (size_t)blockIdx.x * V;
-  const MaxIdx mx = block_argmax(row, V, sh_mi);
   const float temp = temperature ? temperature[blockIdx.x] : 0.f;
+  const int k = (top_k && temp > 0.f) ? top_k[blockIdx.x] : 0;
+  const float pfrac = (top_p && temp > 0.f) ? top_p[blockIdx.x] : -1.f;
+  const bool has_k = k > 0 && k < V, has_p = pfrac >= 0.f;
+  const float inv_t = temp > 0.f ? 1.0f / temp : 0.f;
+  MaxIdx mx;
+  if (has_k && k <= FAST_K) {
+    if (sample_top_k_fast(row, V, inv_t, k, pfrac, uniform[blockIdx.x], sample_smem, bin_c, bin_m, &sel, sh_mi, &fast, &mx,
+                          out + blockIdx.x))
+      return;
+    __syncthreads();                                 // the general path reuses what the attempt wrote
+  } else {
+    mx = block_argmax(row, V, sh_mi);
+  }
   if (!(temp > 0.f)) {
     if (threadIdx.x == 0) out[blockIdx.x] = mx.i;
     return;
   }
-  const float inv_t = 1.0f / temp;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // the row in 32 parts of whole 32-element groups, one per warp, in index order
   const int part_len = (((V + SEL_WARPS - 1) / SEL_WARPS) + 31) & ~31;
 
   // ---- the kept set (runtime/sampler.py:60-79): top-k first, then top-p over what it kept ----
-  const int k = top_k ? top_k[blockIdx.x] : 0;
-  const float pfrac = top_p ? top_p[blockIdx.x] : -1.f;
-  const bool has_k = k > 0 && k < V, has_p = pfrac >= 0.f;
   Kept kp{has_k || has_p, 0u, 0x7fffffff};
   if (kp.filtered) {
     int* hist_c = reinterpret_cast<int*>(sample_smem);

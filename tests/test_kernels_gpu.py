@@ -319,6 +319,26 @@ def test_sample_rows_filters_with_ties():
     assert [sorted(s) for s in seen] == want
 
 
+def test_sample_rows_small_top_k_when_one_thread_holds_the_largest():
+    """The one-pass form for a small top_k keeps four candidates a thread; a row whose largest logits
+    all fall to one thread (indices 1024 apart) must come out the same, through the general form."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(77)
+    V, R = 20000, 4
+    logits = torch.randn(R, V, device="cuda", generator=g)
+    for r in range(R):
+        logits[r, 7 + 1024 * torch.arange(8 + r, device="cuda")] = 6.0 + torch.rand(8 + r, device="cuda", generator=g)
+    temps = torch.tensor([1.0, 0.7, 1.5, 1.0], device="cuda")
+    top_k = torch.tensor([6, 8, 5, 10], device="cuda", dtype=torch.int32)       # 5: four candidates are not enough either
+    top_p = torch.tensor([-1.0, 0.9, -1.0, 0.6], device="cuda")
+    for trial in range(8):
+        u = torch.rand(R, device="cuda", generator=g, dtype=torch.float64)
+        got = ops.sample_rows(logits, temps, u, top_k, top_p).tolist()
+        want = ref.sample_rows(logits, temps, u, top_k, top_p).tolist()
+        assert got == want, (trial, got, want)
+        assert all((t - 7) % 1024 == 0 for t in got)
+
+
 def test_repetition_penalty_in_place():
     ops = _ops()
     g = torch.Generator(device="cuda").manual_seed(4)
