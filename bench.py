@@ -176,7 +176,9 @@ def decode_run(model, cfg, batch, context, steps, warmup, seed=0, graphs=True):
     clocks = ClockSampler()
     clocks.start()
     before = dict(ops.launches)
-    h2d = d2h = 0
+    def copied_bytes():
+        return (llm.engine.h2d_bytes + llm.sampler.h2d_bytes, llm.engine.d2h_bytes + llm.sampler.d2h_bytes)
+    copied, launched = copied_bytes(), llm.engine.steps_run
     t0 = time.perf_counter()
     for _ in range(steps):
         _, sampled = llm.step(device_timer=timer)
@@ -190,10 +192,12 @@ def decode_run(model, cfg, batch, context, steps, warmup, seed=0, graphs=True):
     ctx_mean = prompt_len + warmup + (steps - 1) / 2.0
     kv_bytes = llm.engine.cache.bytes_per_token(2 if model.dtype == torch.bfloat16 else 4) * ctx_mean * batch
     step_bytes = model.weight_bytes() + kv_bytes
-    # per step: the packed int32 batch description goes up, the sampled ids come down
-    mp = -(-(context + 1) // page)
-    h2d = 4 * (3 * batch + (batch + 1) + 2 * batch + batch + batch + batch * mp)
-    d2h = 4 * batch
+    # per step: the packed batch description (one pinned buffer: ids, positions, slots, block tables, sampling
+    # inputs) goes up, the sampled ids come down; counted from the tensors the engine copied
+    # (per step the device ran: with a step queued ahead, the window may hold one launch more or less than `steps`)
+    ran = max(1, llm.engine.steps_run - launched)
+    h2d = (copied_bytes()[0] - copied[0]) // ran
+    d2h = (copied_bytes()[1] - copied[1]) // ran
     for r in list(llm.scheduler.running):
         llm.abort(r.req_id)
     del llm

@@ -49,6 +49,8 @@ class Engine:
         self._pin = self.device.type == "cuda"
         self.steps_run = 0
         self._graphs = None
+        self.h2d_bytes = 0          # bytes of step descriptions copied to the device so far (measurement)
+        self.d2h_bytes = 0          # bytes of sampled ids copied back from captured steps so far
 
     # ---- requests ------------------------------------------------------------------
     def is_live(self, req_id) -> bool:
@@ -162,6 +164,7 @@ class Engine:
                 sec(f"slot_mapping{gi}")[t0:t0 + n] = (pages.astype(np.int64) * ps + p % ps).astype(np.int32)
             t0 += n
         dev = host.to(self.device, non_blocking=True)
+        self.h2d_bytes += host.numel() * host.element_size()
 
         def dsec(k):
             return dev[offs[k]: offs[k] + sizes[k]]

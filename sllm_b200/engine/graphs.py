@@ -236,6 +236,8 @@ class DecodeGraphs:
         if tokens_on_device and gr.graph is None:
             raise RuntimeError("a chained step needs a captured graph (see can_chain)")
         gr.fill(eng, entries, totals, temperatures, uniforms, tokens_on_device, top_k, top_p)
+        eng.h2d_bytes += gr.host.numel() * gr.host.element_size()
+        eng.d2h_bytes += gr.ids_host[0].numel() * gr.ids_host[0].element_size()
         if device_timer is not None:
             device_timer.start()
         ids_now = None

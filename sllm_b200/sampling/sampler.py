@@ -71,6 +71,8 @@ class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
         self._pin = self.device.type == "cuda"
+        self.h2d_bytes = 0          # bytes of sampling inputs copied to the device so far (measurement)
+        self.d2h_bytes = 0          # bytes of sampled ids copied back so far
 
     @staticmethod
     def host_inputs(rows):
@@ -114,6 +116,7 @@ class Sampler:
             if self._pin:
                 h = h.pin_memory()
             out.append(h.to(self.device, non_blocking=True))
+            self.h2d_bytes += h.numel() * h.element_size()
         return out
 
     def sample(self, logits: torch.Tensor, rows, device_timer=None) -> list[int]:
@@ -138,4 +141,5 @@ class Sampler:
             picked = ops.sample_rows(logits, *self._to_device(temps, unis, top_k, top_p))
         if device_timer is not None:
             device_timer.stop()
+        self.d2h_bytes += picked.numel() * picked.element_size()
         return [int(t) for t in picked.cpu().tolist()]
