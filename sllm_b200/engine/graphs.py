@@ -82,6 +82,7 @@ class _Graph:
         self.graph = None
         self.ids = None
         self.launches = 0
+        self.reporting = 0
 
     def _hsec(self, k):
         o, n = self.offs[k]
@@ -254,6 +255,7 @@ class DecodeGraphs:
             # (torch's graph context collects once before it begins; here the collector stays off.)
             gc_was_on = gc.isenabled()
             gc.disable()
+            reporting = ops.status_word_launches()
             try:
                 with torch.cuda.graph(graph):
                     logits = eng.model.forward(gr.ctx, eng.layer_caches)
@@ -262,12 +264,15 @@ class DecodeGraphs:
                 if gc_was_on:
                     gc.enable()
             ops.launches["own"] -= gr.launches          # capturing launched nothing
+            gr.reporting = ops.status_word_launches() - reporting      # kernels of the graph that report through the status word
+            ops.note_status_word_launches(-gr.reporting)
             gr.graph = graph
             # the graph's own output buffer must hold this step's ids for a step chained behind it
             gr.ids[:len(ids_now)].copy_(torch.tensor(ids_now, dtype=torch.int32, device=eng.device))
         else:
             gr.graph.replay()
             ops.launches["own"] += gr.launches
+            ops.note_status_word_launches(gr.reporting)
             gr.ids_host[gr.turn].copy_(gr.ids, non_blocking=True)
             gr.ids_ready[gr.turn].record()
         if device_timer is not None:

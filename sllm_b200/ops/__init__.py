@@ -142,6 +142,16 @@ def _status_word(device) -> torch.Tensor:
     return t
 
 
+def status_word_launches() -> int:
+    """Launches since the last check of kernels that report through the status word."""
+    return _tc_used["since_check"]
+
+
+def note_status_word_launches(n: int) -> None:
+    """A replayed CUDA graph launched ``n`` such kernels (the capture counted them once)."""
+    _tc_used["since_check"] += int(n)
+
+
 def check_tcgen05_status() -> None:
     """Raise if a bounded wait inside a TMA-fed kernel (the tcgen05 product, the TMA attention) gave
     up since the last check (reads one int from each device that ran such a kernel; synchronises)."""

@@ -632,3 +632,33 @@ def test_run_list_names_a_layer_twice_and_borrows_a_cache(tmp_path):
             np.testing.assert_allclose(np.concatenate(got), want, **tol)
     finally:
         unregister_architecture("ToyLoopLM")
+
+
+def test_replayed_graphs_keep_the_status_word_checked(tmp_path):
+    """Kernels fed by TMA report a wait that ran out through a status word; a decode step replayed from
+    a graph launches them without passing through their wrappers, and must still be counted so that
+    the word is read."""
+    from sllm_b200 import ops
+    from sllm_b200.engine.llm import LLM
+    from sllm_b200.sampling import SamplingParams
+    from sllm_b200.weights import write_random_model
+    dev = cuda_or_skip()
+    cfg = {"architectures": ["Qwen2ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 128, "num_attention_heads": 2,
+           "num_key_value_heads": 1, "head_dim": 64, "intermediate_size": 256, "vocab_size": 300, "rope_theta": 10000.0,
+           "rms_norm_eps": 1e-6, "max_position_embeddings": 256, "tie_word_embeddings": True}
+    d = write_random_model(str(tmp_path / "m"), cfg, 5, std=0.05)
+    llm = LLM(d, dtype="bfloat16", device=dev, block_size=16, num_pages=32, max_num_seqs=2)
+    ops.check_tcgen05_status()
+    assert ops.status_word_launches() == 0
+    rid = llm.add_request([1, 2, 3, 4, 5], SamplingParams(max_new=40))
+    llm.step()                                          # the prompt
+    llm.step()                                          # first decode step: run eagerly, then captured; the next is queued
+    ops.check_tcgen05_status()
+    assert ops.status_word_launches() == 0
+    for _ in range(4):
+        llm.step()                                      # each queues one replay
+    assert ops.status_word_launches() >= 4 * cfg["num_hidden_layers"]
+    ops.check_tcgen05_status()                          # reads the word: nothing gave up
+    assert ops.status_word_launches() == 0
+    llm.abort(getattr(rid, "req_id", rid))
+    llm.drain()
