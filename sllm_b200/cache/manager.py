@@ -77,6 +77,7 @@ class CacheManager:
         self.requests: dict[object, RequestCache] = {}
         self.kv_storage = []       # per group: tensor [runs, 2, pages, nkv, page_size, hd]
         self.state_storage = {}    # run -> tensor [slots, *shape]
+        self.slot_tables = {}      # name -> tensor [slots, ...] of per-request state that others own (`register_slot_table`)
         self.reuse_count = 0       # pages handed out that had been held before
         self._ever_used = [set() for _ in self.groups]
 
@@ -120,9 +121,17 @@ class CacheManager:
         slot = self.slots.allocate(req_id)
         req = RequestCache(req_id, slot, 0, [[] for _ in self.groups])
         self.requests[req_id] = req
-        for t in self.state_storage.values():
+        for t in (*self.state_storage.values(), *self.slot_tables.values()):
             t[slot].zero_()
         return req
+
+    def register_slot_table(self, name: str, table) -> None:
+        """Per-request state of fixed size that lives outside the model (the sampler's table of
+        seen ids): one row per state slot and one for padding rows; a request's row is zeroed when
+        it is admitted, like the mixers' own state."""
+        if table.shape[0] != self.max_requests + 1:
+            raise ValueError(f"slot table {name!r} has {table.shape[0]} rows, the cache has {self.max_requests} + 1 slots")
+        self.slot_tables[name] = table
 
     def reserve(self, req_id, total_tokens: int) -> None:
         """Grow the request's tables to hold ``total_tokens``.  Takes all pages

@@ -736,6 +736,42 @@ __global__ void repetition_penalty_kernel(float* __restrict__ logits, int V, con
   *p = (float)(v < 0 ? v * pen : v / pen);
 }
 
+// The same penalty from a table of seen ids kept on the device: seen[slot, id] != 0 once request
+// `slot` has consumed token `id`.  mark_seen_kernel records a step's tokens (prompt portions and
+// decoded tokens alike) before the step runs; penalty_seen_kernel changes the wanted logits rows of
+// requests whose penalty is neither 0 nor 1.  Both read the step's description on the device, so they
+// can be part of a captured decode step.
+__global__ void mark_seen_kernel(unsigned char* __restrict__ seen, int V, const int* __restrict__ token_ids,
+                                 const int* __restrict__ seq_of_token, const int* __restrict__ state_slots, int T, int slots) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  const int id = token_ids[t], slot = state_slots[seq_of_token[t]];
+  if (id >= 0 && id < V && slot >= 0 && slot < slots) seen[(size_t)slot * V + id] = 1;
+}
+
+__global__ void penalty_seen_kernel(float* __restrict__ logits, int V, const unsigned char* __restrict__ seen,
+                                    const int* __restrict__ logit_rows, const int* __restrict__ seq_of_token,
+                                    const int* __restrict__ state_slots, const float* __restrict__ penalty, int slots) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.y;
+  const float pf = penalty[row];
+  if (!(pf > 0.f) || pf == 1.0f) return;
+  const int slot = state_slots[seq_of_token[logit_rows[row]]];
+  if (slot < 0 || slot >= slots) return;
+  const unsigned char* mine = seen + (size_t)slot * V;
+  float* lr = logits + (size_t)row * V;
+  const double pen = (double)pf;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < V; i += gridDim.x * blockDim.x) {
+    if (mine[i]) {
+      const double v = (double)lr[i];
+      lr[i] = (float)(v < 0 ? v * pen : v / pen);
+    }
+  }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -768,4 +804,24 @@ SLLM_EXPORT int sllm_repetition_penalty(float* logits, int R, int V, const int* 
   if (n == 0 || R == 0) return SLLM_OK;
   launch_kernel(repetition_penalty_kernel, (n + 255) / 256, 256, 0, stream, logits, V, pair_row, pair_id, pair_penalty, n);
   return launch_status("repetition_penalty");
+}
+
+// seen [slots, V] bytes; the step's T tokens with the request (row of state_slots) each belongs to
+SLLM_EXPORT int sllm_mark_seen(unsigned char* seen, int slots, int V, const int* token_ids, const int* seq_of_token,
+                               const int* state_slots, int T, cudaStream_t stream) {
+  SLLM_REQUIRE(slots > 0 && V > 0 && T >= 0, "mark_seen: bad sizes slots=%d V=%d T=%d", slots, V, T);
+  if (T == 0) return SLLM_OK;
+  launch_kernel(mark_seen_kernel, (T + 255) / 256, 256, 0, stream, seen, V, token_ids, seq_of_token, state_slots, T, slots);
+  return launch_status("mark_seen");
+}
+
+// logits [R, V] float32, changed in place; logit_rows [R] names the token each row belongs to;
+// penalty [R] (0 or 1: the row stays as it is)
+SLLM_EXPORT int sllm_penalty_seen(float* logits, int R, int V, const unsigned char* seen, int slots, const int* logit_rows,
+                                  const int* seq_of_token, const int* state_slots, const float* penalty, cudaStream_t stream) {
+  SLLM_REQUIRE(R >= 0 && V > 0 && slots > 0, "penalty_seen: bad sizes R=%d V=%d slots=%d", R, V, slots);
+  if (R == 0) return SLLM_OK;
+  const int bx = (V + 1023) / 1024 < 148 ? (V + 1023) / 1024 : 148;
+  launch_kernel(penalty_seen_kernel, dim3(bx, R), 256, 0, stream, logits, V, seen, logit_rows, seq_of_token, state_slots, penalty, slots);
+  return launch_status("penalty_seen");
 }

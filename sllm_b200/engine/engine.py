@@ -49,6 +49,7 @@ class Engine:
         self._pin = self.device.type == "cuda"
         self.steps_run = 0
         self._graphs = None
+        self._seen = None
         self.h2d_bytes = 0          # bytes of step descriptions copied to the device so far (measurement)
         self.d2h_bytes = 0          # bytes of sampled ids copied back from captured steps so far
 
@@ -58,6 +59,16 @@ class Engine:
 
     def num_tokens(self, req_id) -> int:
         return self.cache.requests[req_id].num_tokens
+
+    def seen_table(self) -> torch.Tensor:
+        """uint8 ``[state slots + 1, vocabulary]``: the ids each live request has consumed, for the
+        repetition penalty (a row per state slot, the last for padding rows).  Made when first asked for
+        (all zeros, so a request whose first step asks for it starts with an empty row); from then
+        on the cache manager zeroes a request's row at its admission."""
+        if self._seen is None:
+            self._seen = torch.zeros((self.cache.max_requests + 1, self.vocab_size), dtype=torch.uint8, device=self.device)
+            self.cache.register_slot_table("seen_ids", self._seen)      # a request's row is zeroed at its admission
+        return self._seen
 
     def finish(self, req_id) -> None:
         """The request is over: its pages and its slot go back."""

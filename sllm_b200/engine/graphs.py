@@ -34,15 +34,18 @@ def _pad4(n: int) -> int:
 
 
 class _Graph:
-    def __init__(self, engine, B: int, bucket: int):
-        """``B``: rows of the captured step (live requests plus padding)."""
+    def __init__(self, engine, B: int, bucket: int, penalised: bool = False):
+        """``B``: rows of the captured step (live requests plus padding).  ``penalised``: the step also
+        records its tokens in the engine's table of seen ids and applies the rows' repetition
+        penalties before it samples."""
+        self.penalised = bool(penalised)
         cache = engine.cache
         self.B = B
         ps = cache.page_size
         self.cap_pages = -(-engine.max_positions // ps)
         G = len(cache.groups)
         sizes = {"token_ids": B, "positions": B, "seq_of_token": B, "q_start": B + 1, "ctx_len": B,
-                 "state_slots": B, "logit_rows": B, "temps": B, "uniforms": 2 * B, "top_k": B, "top_p": B}
+                 "state_slots": B, "logit_rows": B, "temps": B, "uniforms": 2 * B, "top_k": B, "top_p": B, "penalty": B}
         for gi in range(G):
             sizes[f"slot_mapping{gi}"] = B
             sizes[f"block_tables{gi}"] = B * self.cap_pages
@@ -79,10 +82,20 @@ class _Graph:
         self.uniforms = self._dsec("uniforms").view(torch.float64)
         self.top_k = self._dsec("top_k")
         self.top_p = self._dsec("top_p").view(torch.float32)
+        self.penalty = self._dsec("penalty").view(torch.float32)
         self.graph = None
         self.ids = None
         self.launches = 0
         self.reporting = 0
+
+    def run(self, engine):
+        """The step's kernels on the static buffers: what is run once eagerly and then captured."""
+        if self.penalised:
+            ops.mark_seen(engine.seen_table(), self.ctx)
+        logits = engine.model.forward(self.ctx, engine.layer_caches)
+        if self.penalised:
+            ops.penalty_from_seen_(logits, engine.seen_table(), self.ctx, self.penalty)
+        self.ids = ops.sample_rows(logits, self.temps, self.uniforms, self.top_k, self.top_p)
 
     def _hsec(self, k):
         o, n = self.offs[k]
@@ -92,7 +105,8 @@ class _Graph:
         o, n = self.offs[k]
         return self.dev[o:o + n]
 
-    def fill(self, engine, entries, totals, temperatures, uniforms, tokens_on_device: bool = False, top_k=None, top_p=None):
+    def fill(self, engine, entries, totals, temperatures, uniforms, tokens_on_device: bool = False, top_k=None, top_p=None,
+             penalties=None):
         """Describe the step in the next host buffer and queue its copy to the device.  With
         ``tokens_on_device`` the token ids are not the host's to give: they are the ids the graph's
         previous replay sampled, copied on the device."""
@@ -141,6 +155,10 @@ class _Graph:
             k_host[:n] = top_k
         if top_p is not None:
             p_host[:n] = top_p
+        pen_host = self._hsec("penalty").view(np.float32)
+        pen_host[:] = 1.0
+        if penalties is not None:
+            pen_host[:n] = penalties
         self.dev.copy_(self.host, non_blocking=True)
         if tokens_on_device:
             self._dsec("token_ids").copy_(self.ids)          # after the host's copy, before the replay
@@ -183,7 +201,7 @@ class DecodeGraphs:
         h = self.launch(entries, temperatures, uniforms, device_timer=device_timer)
         return torch.tensor(self.read(h), dtype=torch.int32)
 
-    def can_chain(self, entries) -> bool:
+    def can_chain(self, entries, penalised: bool = False) -> bool:
         """Whether a step for these requests, one token further each, can be queued behind the
         step in flight with its token ids taken from that step's samples on the device: the same
         requests in the same order, a graph already captured for their number and context bucket,
@@ -195,13 +213,13 @@ class DecodeGraphs:
             if req is None or req.num_tokens + 1 > eng.max_positions:
                 return False
             totals.append(req.num_tokens + 1)
-        gr = self.graphs.get((self.batch_bucket(len(entries)), self.bucket(max(totals))))
+        gr = self.graphs.get((self.batch_bucket(len(entries)), self.bucket(max(totals)), bool(penalised)))
         if gr is None or gr.graph is None:
             return False
         return all(cache.can_reserve(e.req_id, t) for e, t in zip(entries, totals))
 
     def launch(self, entries, temperatures, uniforms, device_timer=None, tokens_on_device: bool = False,
-               top_k=None, top_p=None) -> Launched:
+               top_k=None, top_p=None, penalties=None) -> Launched:
         """Queue one decode step: reserve pages, describe the batch, replay the graph, queue the copy
         of the sampled ids to pinned host memory.  Does not wait for the device, except the first
         time a (batch size, context bucket) is seen: that step runs eagerly and is then captured."""
@@ -230,13 +248,13 @@ class DecodeGraphs:
                 raise OutOfPages(f"step needs {need} pages in group {gi}, {g.pool.free_count} free")
         for e, t in zip(entries, totals):
             cache.reserve(e.req_id, t)
-        key = (self.batch_bucket(len(entries)), self.bucket(max(totals)))
+        key = (self.batch_bucket(len(entries)), self.bucket(max(totals)), penalties is not None)
         gr = self.graphs.get(key)
         if gr is None:
             gr = self.graphs[key] = _Graph(eng, *key)
         if tokens_on_device and gr.graph is None:
             raise RuntimeError("a chained step needs a captured graph (see can_chain)")
-        gr.fill(eng, entries, totals, temperatures, uniforms, tokens_on_device, top_k, top_p)
+        gr.fill(eng, entries, totals, temperatures, uniforms, tokens_on_device, top_k, top_p, penalties)
         eng.h2d_bytes += gr.host.numel() * gr.host.element_size()
         eng.d2h_bytes += gr.ids_host[0].numel() * gr.ids_host[0].element_size()
         if device_timer is not None:
@@ -245,8 +263,7 @@ class DecodeGraphs:
         if gr.graph is None:
             # first use: run eagerly on the static buffers (this step's result), then capture
             before = ops.launches["own"]
-            logits = eng.model.forward(gr.ctx, eng.layer_caches)
-            gr.ids = ops.sample_rows(logits, gr.temps, gr.uniforms, gr.top_k, gr.top_p)
+            gr.run(eng)
             gr.launches = ops.launches["own"] - before
             ids_now = gr.ids.cpu().tolist()[:len(entries)]
             graph = torch.cuda.CUDAGraph()
@@ -258,8 +275,7 @@ class DecodeGraphs:
             reporting = ops.status_word_launches()
             try:
                 with torch.cuda.graph(graph):
-                    logits = eng.model.forward(gr.ctx, eng.layer_caches)
-                    gr.ids = ops.sample_rows(logits, gr.temps, gr.uniforms, gr.top_k, gr.top_p)
+                    gr.run(eng)
             finally:
                 if gc_was_on:
                     gc.enable()

@@ -17,6 +17,7 @@ from dataclasses import dataclass
 
 import torch
 
+from .. import ops
 from ..sampling import Sampler, SamplingParams
 from .engine import Engine, StepEntry
 from .loading import build_model, parse_dtype
@@ -108,13 +109,23 @@ class LLM:
                 return [], {}
             entries = [StepEntry(p.req.req_id, p.req.token_slice(p.start, p.count),
                                  [p.count - 1] if p.sample else []) for p in plan]
-            rows = [(p.req.params, p.req.rng, p.req.tokens if p.req.params.needs_history else None)
-                    for p in plan if p.sample]
-            if not (self.cuda_graphs and all(p.count == 1 and p.sample and not p.req.params.needs_history for p in plan)):
+            rows = [(p.req.params, p.req.rng, None) for p in plan if p.sample]
+            # repetition penalties come from the engine's table of seen ids, which every step that
+            # holds a penalised request keeps up to date (its prompt portions included)
+            track = any(p.req.params.penalised for p in plan)
+            penalties = self.sampler.penalties([p.req.params for p in plan if p.sample]) if track else None
+            if not (self.cuda_graphs and all(p.count == 1 and p.sample for p in plan)):
                 ctx = self.engine.prepare(entries)
                 if device_timer is not None:
                     device_timer.start()
+                if track:
+                    seen = self.engine.seen_table()
+                    ops.mark_seen(seen, ctx)
                 logits = self.engine.run(ctx, entries)
+                if penalties is not None and logits.shape[0]:
+                    pen = torch.from_numpy(penalties)
+                    ops.penalty_from_seen_(logits, seen, ctx, (pen.pin_memory() if self.sampler._pin else pen).to(
+                        logits.device, non_blocking=True))
                 ids = self.sampler.sample(logits, rows, device_timer=device_timer)
                 sampled = {p.req.req_id: t for p, t in zip((p for p in plan if p.sample), ids)}
                 finished = sched.update(plan, sampled)
@@ -122,7 +133,8 @@ class LLM:
                 return finished, sampled
             # a pure decode step: replayed from a captured graph, sampling included
             temps, unis, top_k, top_p = self.sampler.host_inputs(rows)
-            handle = self.engine.graphs.launch(entries, temps, unis, device_timer=device_timer, top_k=top_k, top_p=top_p)
+            handle = self.engine.graphs.launch(entries, temps, unis, device_timer=device_timer, top_k=top_k, top_p=top_p,
+                                               penalties=penalties)
             self._inflight = (plan, handle)
         plan, handle = self._inflight
         self._inflight = self._chain(plan, device_timer)
@@ -145,12 +157,13 @@ class LLM:
                     or r.num_tokens + 1 >= sched.max_positions):
                 return None
         entries = [StepEntry(p.req.req_id, [0], [0]) for p in plan]
-        if not self.engine.graphs.can_chain(entries):
+        penalties = self.sampler.penalties([p.req.params for p in plan])
+        if not self.engine.graphs.can_chain(entries, penalties is not None):
             return None
         rows = [(p.req.params, p.req.rng, None) for p in plan]
         temps, unis, top_k, top_p = self.sampler.host_inputs(rows)
         handle = self.engine.graphs.launch(entries, temps, unis, device_timer=device_timer, tokens_on_device=True,
-                                           top_k=top_k, top_p=top_p)
+                                           top_k=top_k, top_p=top_p, penalties=penalties)
         from .scheduler import Planned
         nxt = [Planned(p.req, p.start + 1, 1, True) for p in plan]
         return nxt, handle

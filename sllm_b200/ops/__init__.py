@@ -601,3 +601,29 @@ def repetition_penalty_(logits: torch.Tensor, pair_row, pair_id, pair_penalty) -
         raise KernelError("repetition_penalty_: rows and ids int32, penalties float32, one per pair")
     call("sllm_repetition_penalty", _p(logits), R, V, _p(pair_row), _p(pair_id), _p(pair_penalty), n, _stream())
     return logits
+
+
+def mark_seen(seen: torch.Tensor, step) -> None:
+    """Record the step's tokens in ``seen [slots, V]`` (uint8): ``seen[slot of the token's request,
+    token id] = 1``.  ``step`` is the `StepContext` (token ids, request of each token, state slots,
+    all on the device)."""
+    _chk(seen, step.token_ids, step.seq_of_token, step.state_slots)
+    if seen.dtype != torch.uint8 or seen.dim() != 2:
+        raise KernelError("mark_seen: the table is uint8 [slots, V]")
+    call("sllm_mark_seen", _p(seen), seen.shape[0], seen.shape[1], _p(step.token_ids), _p(step.seq_of_token),
+         _p(step.state_slots), int(step.num_tokens), _stream())
+
+
+def penalty_from_seen_(logits: torch.Tensor, seen: torch.Tensor, step, penalty: torch.Tensor) -> torch.Tensor:
+    """The repetition penalty in place on float32 ``logits [R, V]`` (row r belongs to the request of
+    token ``step.logit_rows[r]``): every id that request has seen has a positive logit divided by
+    ``penalty[r]`` and a negative one multiplied; rows with penalty 0 or 1 stay as they are."""
+    _chk(logits, seen, penalty, step.logit_rows, step.seq_of_token, step.state_slots)
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or seen.dtype != torch.uint8 or seen.shape[1] != V:
+        raise KernelError("penalty_from_seen_: float32 logits [R, V] and a uint8 table [slots, V]")
+    if penalty.dtype != torch.float32 or penalty.numel() != R or step.logit_rows.numel() < R:
+        raise KernelError("penalty_from_seen_: one float32 penalty and one wanted row per logits row")
+    call("sllm_penalty_seen", _p(logits), R, V, _p(seen), seen.shape[0], _p(step.logit_rows), _p(step.seq_of_token),
+         _p(step.state_slots), _p(penalty), _stream())
+    return logits

@@ -29,8 +29,7 @@ class SamplingParams:
         self.stop_ids = tuple(int(s) for s in self.stop_ids)
 
     @property
-    def needs_history(self) -> bool:
-        """The repetition penalty reads the ids the request has seen, a list of any length;
-        such a row is sampled outside the captured decode step."""
+    def penalised(self) -> bool:
+        """Whether a repetition penalty applies (runtime/sampler.py:24: none, <= 0 and 1 change nothing)."""
         p = self.repetition_penalty
         return p is not None and p > 0 and p != 1.0

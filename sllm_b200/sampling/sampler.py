@@ -3,7 +3,10 @@
 Every row is sampled on the device, all rows at once (`ops.sample_rows`): greedy,
 temperature, top-k and top-p as runtime/sampler.py:36-88 defines them, after the
 repetition penalty (runtime/sampler.py:12-33) has changed the seen ids' logits in
-place (`ops.repetition_penalty_`).  Only the chosen ids cross to the host.  A sampled
+place: from the engine's table of seen ids on the device (`ops.penalty_from_seen_`,
+what `LLM` uses: it needs nothing from the host and is part of a captured decode
+step), or from the lists of seen ids a caller of `Sampler.sample` hands over
+(`ops.repetition_penalty_`).  Only the chosen ids cross to the host.  A sampled
 token consumes one uniform from the request's own ``numpy.random.default_rng(seed)``
 (runtime/sampler.py:86; serving/executor.py:358), so equal logits give the
 reference's tokens.  `sample_host` is the same sampler in numpy on one row; the
@@ -96,11 +99,18 @@ class Sampler:
         return temps, unis, top_k, top_p
 
     @staticmethod
+    def penalties(params_list):
+        """float32[R] repetition penalties (1 where a request has none), or None if no request has one."""
+        if not any(p.penalised for p in params_list):
+            return None
+        return np.array([p.repetition_penalty if p.penalised else 1.0 for p in params_list], dtype=np.float32)
+
+    @staticmethod
     def penalty_pairs(rows):
         """(row, id, penalty) arrays naming each seen id of each penalised row once, or None."""
         r, t, q = [], [], []
         for i, (p, _, seen) in enumerate(rows):
-            if p.needs_history and seen is not None and len(seen):
+            if p.penalised and seen is not None and len(seen):
                 ids = np.unique(np.asarray(list(seen), dtype=np.int64))
                 r.append(np.full(ids.size, i, dtype=np.int32))
                 t.append(ids.astype(np.int32))

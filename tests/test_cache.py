@@ -149,3 +149,24 @@ def test_random_orders_keep_the_books(seed, window):
         m.free_request(r)
     m.check()
     assert m.groups[0].pool.free_count == 20 and m.slots.free_count == 5
+
+
+def test_slot_tables_of_others_are_zeroed_at_admission():
+    """Per-request state that lives outside the model (the sampler's seen ids) registers with the
+    cache manager: one row per state slot and one for padding; a row is zeroed when a request takes
+    the slot, and only then."""
+    import torch
+    cm = CacheManager([("own", PagedKV(2, 16, None))], page_size=4, num_pages=8, max_requests=2)
+    with pytest.raises(ValueError):
+        cm.register_slot_table("seen", torch.ones(2, 5))
+    table = torch.ones(3, 5)
+    cm.register_slot_table("seen", table)
+    a = cm.add_request("a")
+    assert table[a.slot].sum() == 0 and table.sum() == 10
+    table[a.slot] = 7
+    b = cm.add_request("b")
+    assert table[b.slot].sum() == 0 and table[a.slot].sum() == 35
+    cm.free_request("a")
+    assert table[a.slot].sum() == 35                       # giving the slot back changes nothing
+    c = cm.add_request("c")
+    assert c.slot == a.slot and table[c.slot].sum() == 0

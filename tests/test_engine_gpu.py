@@ -662,3 +662,33 @@ def test_replayed_graphs_keep_the_status_word_checked(tmp_path):
     assert ops.status_word_launches() == 0
     llm.abort(getattr(rid, "req_id", rid))
     llm.drain()
+
+
+@pytest.mark.parametrize("policy", ["reserve", "on_demand"])
+def test_repetition_penalty_through_graphs_preemption_and_one_token_prompts(tiny, policy):
+    """The penalty reads the engine's table of seen ids: rows are zeroed at admission (a slot is
+    used again, a preempted request starts over), prompts of one token go straight to a captured
+    decode step, penalised and plain requests share steps."""
+    from sllm_b200.engine.llm import LLM
+    from sllm_b200.sampling import SamplingParams
+    dev = cuda_or_skip()
+    name, model_dir, page = tiny
+    cfg, w = plain.load_model(model_dir)
+    rng = np.random.default_rng(11)
+    lengths = (1, page - 1, 2 * page - 2, 1, 7, page + 3)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in lengths]
+    params = [SamplingParams(max_new=10, temperature=0.0 if i % 3 == 0 else 0.8, seed=i,
+                             repetition_penalty=None if i == 2 else 1.0 + 0.25 * (i + 1), top_k=6 if i == 4 else None)
+              for i in range(len(prompts))]
+    llm = LLM(model_dir, dtype="float32", device=dev, block_size=page, num_pages=64 if policy == "reserve" else 5,
+              max_num_seqs=3, chunk_size=24, max_batch_tokens=40, policy=policy)
+    for round_ in range(2):                                    # the second round takes slots the first one used
+        res = llm.generate(prompts, params)
+        for p, q, r in zip(prompts, params, res):
+            want = plain.generate(p, q.max_new, w, cfg, temperature=q.temperature, seed=q.seed, top_k=q.top_k,
+                                  repetition_penalty=q.repetition_penalty)
+            assert r.ids == want, (round_, len(p), q)
+    if policy == "on_demand":
+        assert llm.scheduler.num_preemptions > 0, "the pool was meant to force a preemption"
+    assert any(key[2] for key in llm.engine.graphs.graphs), "decode steps with a penalty were meant to run from a graph"
+    llm.engine.cache.check()

@@ -339,6 +339,37 @@ def test_sample_rows_small_top_k_when_one_thread_holds_the_largest():
         assert all((t - 7) % 1024 == 0 for t in got)
 
 
+def test_seen_table_marks_and_penalises():
+    """The table of seen ids on the device: a step's tokens are recorded under their requests' slots
+    (ids and slots out of range ignored), and the penalty changes exactly the seen ids of the rows
+    that have one."""
+    from types import SimpleNamespace
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    V, slots = 1000, 5
+    seen = torch.zeros(slots, V, dtype=torch.uint8, device="cuda")
+    seen[3, 17] = 1                                            # what an earlier step left
+    i32 = dict(device="cuda", dtype=torch.int32)
+    step = SimpleNamespace(num_tokens=7, token_ids=torch.tensor([5, 999, 5, 17, 1000, 2, 8], **i32),
+                           seq_of_token=torch.tensor([0, 0, 0, 1, 1, 2, 3], **i32),
+                           state_slots=torch.tensor([3, 0, 4, 7], **i32),          # the last slot lies outside the table
+                           logit_rows=torch.tensor([2, 4, 5], **i32))
+    want_seen = seen.clone()
+    ref.mark_seen(want_seen, step)
+    ops.mark_seen(seen, step)
+    assert torch.equal(seen, want_seen)
+    assert seen[3].nonzero().flatten().tolist() == [5, 17, 999] and seen[0].nonzero().flatten().tolist() == [17]
+    assert seen[4].nonzero().flatten().tolist() == [2] and int(seen.sum()) == 5
+    logits = torch.randn(3, V, device="cuda", generator=g) * 3
+    pen = torch.tensor([1.3, 1.0, 0.5], device="cuda")
+    want = ref.penalty_from_seen_(logits.clone(), seen, step, pen)
+    got = ops.penalty_from_seen_(logits.clone(), seen, step, pen)
+    torch.testing.assert_close(got, want, rtol=1e-6, atol=0)
+    assert torch.equal(got[1], logits[1])                      # penalty 1: untouched
+    assert (got[0] != logits[0]).nonzero().flatten().tolist() == [5, 17, 999]
+    assert (got[2] != logits[2]).nonzero().flatten().tolist() == [2]
+
+
 def test_repetition_penalty_in_place():
     ops = _ops()
     g = torch.Generator(device="cuda").manual_seed(4)

@@ -31,8 +31,8 @@ def test_penalty_and_params():
         SamplingParams(top_k=0)
     with pytest.raises(ValueError):
         SamplingParams(max_new=0)
-    assert not SamplingParams(temperature=0.8, top_p=0.9, top_k=3).needs_history
-    assert SamplingParams(repetition_penalty=1.1).needs_history and not SamplingParams(repetition_penalty=1.0).needs_history
+    assert not SamplingParams(temperature=0.8, top_p=0.9, top_k=3).penalised
+    assert SamplingParams(repetition_penalty=1.1).penalised and not SamplingParams(repetition_penalty=1.0).penalised
 
 
 def test_kernel_inputs_of_the_sampler():
@@ -47,3 +47,5 @@ def test_kernel_inputs_of_the_sampler():
     r, t, q = Sampler.penalty_pairs(rows)
     assert r.tolist() == [2, 2, 2] and t.tolist() == [1, 3, 9] and q.tolist() == [1.5] * 3   # each id once
     assert Sampler.penalty_pairs(rows[:2]) is None
+    assert Sampler.penalties([p for p, _, _ in rows]).tolist() == [1.0, 1.0, 1.5]
+    assert Sampler.penalties([p for p, _, _ in rows[:2]]) is None

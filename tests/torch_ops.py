@@ -133,5 +133,24 @@ def repetition_penalty_(logits, pair_row, pair_id, pair_penalty):
     return logits
 
 
+def mark_seen(seen, step):
+    slots = step.state_slots[step.seq_of_token[:step.num_tokens].long()].long()
+    ids = step.token_ids[:step.num_tokens].long()
+    ok = (ids >= 0) & (ids < seen.shape[1]) & (slots >= 0) & (slots < seen.shape[0])
+    seen[slots[ok], ids[ok]] = 1
+
+
+def penalty_from_seen_(logits, seen, step, penalty):
+    for r in range(logits.shape[0]):
+        q = float(penalty[r])
+        if not q > 0 or q == 1.0:
+            continue
+        slot = int(step.state_slots[step.seq_of_token[step.logit_rows[r]]])
+        mine = seen[slot].bool()
+        row = logits[r].double()
+        logits[r] = torch.where(mine, torch.where(row < 0, row * q, row / q), row).float()
+    return logits
+
+
 ALL = ["embed_gather", "add_rmsnorm", "linear", "can_accumulate", "linear_accumulate", "silu_mul", "linear_silu_mul", "rope_kv_write",
-       "attention_simt", "paged_attention", "gather_rows", "sample_rows", "repetition_penalty_"]
+       "attention_simt", "paged_attention", "gather_rows", "sample_rows", "repetition_penalty_", "mark_seen", "penalty_from_seen_"]
