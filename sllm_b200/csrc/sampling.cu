@@ -152,8 +152,10 @@ __device__ __forceinline__ void for_part(const float* __restrict__ row, int base
 
 // Warp 0 walks the 256 bins from the largest logits down (eight bins a lane, the lanes' sums
 // scanned) and records in *st the first bin at which the count reaches k or the mass the target.
+// `may_miss`: this is the select's first level, where no bin may reach the target (chosen = -1); at
+// a later level the range chosen one level up held it.
 __device__ void choose_bin(int level, bool by_mass, int k, bool target_is_fraction, double fraction,
-                           const int* bin_c, const double* bin_m, Select* st) {
+                           const int* bin_c, const double* bin_m, Select* st, bool may_miss) {
   const int lane = threadIdx.x & 31;
   int c[8], lc = 0;
   double m[8], lm = 0.0;
@@ -195,7 +197,7 @@ __device__ void choose_bin(int level, bool by_mass, int k, bool target_is_fracti
   if (hits) {
     who = __ffs(hits) - 1;
     u_sel = hit;
-  } else if (level > 0 && nonempty) {
+  } else if (!may_miss && nonempty) {
     // the range chosen one level up held the target; its parts were summed in another order and
     // fall short by rounding: the target is in the last part
     who = 31 - __clz(nonempty);
@@ -302,7 +304,7 @@ __device__ void select_key(const float* __restrict__ row, int V, float mx, float
       bin_m[threadIdx.x] = m;
     }
     __syncthreads();
-    if (warp == 0) choose_bin(level, by_mass, k, target_is_fraction, target, bin_c, bin_m, st);
+    if (warp == 0) choose_bin(level, by_mass, k, target_is_fraction, target, bin_c, bin_m, st, level == 0);
     __syncthreads();
     if (st->chosen < 0) break;
   }
@@ -334,27 +336,31 @@ constexpr int FAST_K = 64;                  // rows with top_k up to this try th
 constexpr int FAST_PER_THREAD = 4;
 constexpr int FAST_CANDIDATES = SAMPLE_THREADS * FAST_PER_THREAD;
 constexpr int FAST_TIES = 1024;
-static_assert(FAST_CANDIDATES * 8 <= SAMPLE_SMEM, "the candidates live in the histograms' shared memory");
+static_assert(FAST_CANDIDATES * 8 + SEL_BINS * 4 <= SAMPLE_SMEM, "the candidates live in the histograms' shared memory");
 
 struct FastShared {
   uint32_t kept_key[FAST_K], sorted_key[FAST_K];
   int kept_idx[FAST_K], sorted_idx[FAST_K], by_index[FAST_K];
   int tie_idx[FAST_TIES];
-  int n_kept, n_ties, max_let_go, answer, ok;
+  int n_kept, n_ties, max_let_go, answer, last;
+  double red[33];
 };
 
-// true: out[row] is written.  false: the general path must take the row.  `mx` is set either way.
-__device__ bool sample_top_k_fast(const float* __restrict__ row, int V, float inv_t, int k, float pfrac, double u,
-                                  unsigned char* dyn_smem, int* bin_c, double* bin_m, Select* sel, MaxIdx* sh_mi,
-                                  FastShared* fs, MaxIdx* mx_out, int* out) {
+// One pass over the row: every thread's four largest logits become the candidates (keys and
+// indices in `dyn_smem`), the largest fifth one is recorded in fs->max_let_go (31 bits), *mx_out is
+// the row's maximum (first index among equals).  WITH_SUM: *sum_out is the sum over the whole row of
+// expf((logit - max) / T), from a second pass.
+template <bool WITH_SUM>
+__device__ void collect_candidates(const float* __restrict__ row, int V, float inv_t, unsigned char* dyn_smem, MaxIdx* sh_mi,
+                                   double* red, FastShared* fs, MaxIdx* mx_out, double* sum_out) {
   uint32_t* cand_key = reinterpret_cast<uint32_t*>(dyn_smem);
   int* cand_idx = reinterpret_cast<int*>(cand_key + FAST_CANDIDATES);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float v0 = -INFINITY, v1 = -INFINITY, v2 = -INFINITY, v3 = -INFINITY, v4 = -INFINITY;
   int i0 = -1, i1 = -1, i2 = -1, i3 = -1, i4 = -1;
   for_row(row, V, [&](float l, int i) {
+    if (l != l) return;                             // not a number: never a candidate
     if (l > v4 || i4 < 0) {                         // an equal later logit does not displace an earlier one
-      if (l != l) return;                           // not a number: never a candidate
       v4 = l; i4 = i;
       if (v4 > v3 || i3 < 0) {
         float tv = v3; v3 = v4; v4 = tv; int ti = i3; i3 = i4; i4 = ti;
@@ -377,7 +383,7 @@ __device__ bool sample_top_k_fast(const float* __restrict__ row, int V, float in
       best = better(best, other);
     }
     if (lane == 0) sh_mi[warp] = best;
-    if (threadIdx.x == 0) { fs->n_kept = 0; fs->n_ties = 0; fs->max_let_go = 0; fs->answer = -1; fs->ok = 1; }
+    if (threadIdx.x == 0) { fs->n_kept = 0; fs->n_ties = 0; fs->max_let_go = 0; fs->answer = 0x7fffffff; fs->last = -1; }
     __syncthreads();
     if (warp == 0) {
       MaxIdx b = sh_mi[lane];
@@ -398,27 +404,137 @@ __device__ bool sample_top_k_fast(const float* __restrict__ row, int V, float in
       cand_key[threadIdx.x * FAST_PER_THREAD + j] = is[j] >= 0 ? order_key(vs[j]) : 0u;
       cand_idx[threadIdx.x * FAST_PER_THREAD + j] = is[j];
     }
-    if (i4 >= 0) atomicMax(&fs->max_let_go, (int)(order_key(v4) >> 1));     // (31 bits: compared again below)
+    if (i4 >= 0) atomicMax(&fs->max_let_go, (int)(order_key(v4) >> 1));     // (31 bits: compared as such below)
   }
   __syncthreads();
   const MaxIdx mx = sh_mi[0];
   *mx_out = mx;
-  // the k-th largest candidate: four levels of 8 bits over the candidates' keys
-  if (threadIdx.x == 0) *sel = Select{0, 0u, 0u, 0, 0.0, 0, 0.0, 0.0, 0};
-  for (int level = 1; level <= 4; ++level) {
+  if constexpr (WITH_SUM) {
+    double part = 0.0;                              // a second, plain pass: the sum needs the maximum
+    for_row(row, V, [&](float l, int) {
+      if (l == l) part += (double)prob(l, mx.v, inv_t);
+    });
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (lane == 0) red[warp] = part;
+    __syncthreads();
+    if (warp == 0) {
+      double t = red[lane];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+      if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    *sum_out = red[32];
+  }
+}
+
+// The select of select_key over the candidates in shared memory (a linear level, then the key's four
+// bytes): the k-th largest candidate, or the candidate at which the descending cumulative probability
+// reaches `target`.  sel->chosen < 0 afterwards: the candidates' mass does not reach the target.
+__device__ void select_in_candidates(const uint32_t* cand_key, const int* cand_idx, float mx, float inv_t, bool by_mass, int k,
+                                     double target, int* bin_c, float* hist_m, double* bin_m, Select* sel) {
+  const float lscale = inv_t * ((float)(SEL_BINS - 1) / SEL_LINEAR_SPAN);
+  if (threadIdx.x == 0) *sel = Select{0, 0u, 0u, 0, 0.0, 0, 0.0, target, 0};
+  for (int level = 0; level < 5; ++level) {
     const int shift = 32 - 8 * level;
-    if (threadIdx.x < SEL_BINS) { bin_c[threadIdx.x] = 0; bin_m[threadIdx.x] = 0.0; }
+    if (threadIdx.x < SEL_BINS) { bin_c[threadIdx.x] = 0; hist_m[threadIdx.x] = 0.f; }
     __syncthreads();
     const uint32_t prefix = sel->prefix, mask = sel->mask;
+    const int lbin = sel->lbin;
+    int far_c = 0;                                   // the last linear bin: most candidates of a peaked row
+    float far_m = 0.f;
 #pragma unroll
     for (int j = 0; j < FAST_PER_THREAD; ++j) {
       const int c = threadIdx.x * FAST_PER_THREAD + j;
-      if (cand_idx[c] >= 0 && (cand_key[c] & mask) == prefix) atomicAdd(&bin_c[(cand_key[c] >> shift) & 255u], 1);
+      if (cand_idx[c] < 0) continue;
+      const uint32_t key = cand_key[c];
+      const float l = key_value(key);
+      int b = linear_bin(l, mx, lscale);
+      if (level > 0) {
+        if (b != lbin || (key & mask) != prefix) continue;
+        b = (int)((key >> shift) & 255u);
+      } else if (b == SEL_BINS - 1) {
+        ++far_c;
+        if (by_mass) far_m += prob(l, mx, inv_t);
+        continue;
+      }
+      atomicAdd(&bin_c[b], 1);
+      if (by_mass) atomicAdd(&hist_m[b], prob(l, mx, inv_t));
+    }
+    if (level == 0) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        far_c += __shfl_xor_sync(0xffffffffu, far_c, o);
+        far_m += __shfl_xor_sync(0xffffffffu, far_m, o);
+      }
+      if ((threadIdx.x & 31) == 0 && far_c) {
+        atomicAdd(&bin_c[SEL_BINS - 1], far_c);
+        atomicAdd(&hist_m[SEL_BINS - 1], far_m);
+      }
     }
     __syncthreads();
-    if (warp == 0) choose_bin(level, false, k, false, 0.0, bin_c, bin_m, sel);
+    if (threadIdx.x < SEL_BINS) bin_m[threadIdx.x] = (double)hist_m[threadIdx.x];
     __syncthreads();
+    if ((threadIdx.x >> 5) == 0) choose_bin(level, by_mass, k, false, 0.0, bin_c, bin_m, sel, level == 0);
+    __syncthreads();
+    // a target in the last linear bin lies among logits far below the maximum: the general form's business
+    if (sel->chosen < 0 || (level == 0 && sel->lbin == SEL_BINS - 1)) {
+      __syncthreads();
+      if (threadIdx.x == 0) sel->chosen = -1;
+      __syncthreads();
+      return;
+    }
   }
+}
+
+// The draw from a short list of kept tokens (keys, indices; n at most one a thread): the cumulative
+// probability in index order reaches u times the total at the answer (runtime/sampler.py:81-88).
+__device__ void draw_from_list(const uint32_t* key, const int* idx, int n, float mx, float inv_t, double u, double* red,
+                               FastShared* fs, int* out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  double cum = 0.0;
+  int mine = -1;
+  if (threadIdx.x < n) {
+    mine = idx[threadIdx.x];
+    for (int j = 0; j < n; ++j)
+      if (idx[j] <= mine) cum += (double)prob(key_value(key[j]), mx, inv_t);
+  }
+  double total = cum;                               // the token with the largest index holds the total
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) total = fmax(total, __shfl_xor_sync(0xffffffffu, total, o));
+  if (lane == 0) red[warp] = total;
+  __syncthreads();
+  if (warp == 0) {
+    double t = red[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t = fmax(t, __shfl_xor_sync(0xffffffffu, t, o));
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  const double target = u * red[32];
+  if (mine >= 0) {
+    atomicMax(&fs->last, mine);
+    if (cum >= target) atomicMin(&fs->answer, mine);
+  }
+  __syncthreads();
+  // u beyond the last cumulative value: the last kept token
+  if (threadIdx.x == 0) *out = fs->answer != 0x7fffffff ? fs->answer : fs->last;
+}
+
+// true: out[row] is written.  false: the general path must take the row.  `mx` is set either way.
+__device__ bool sample_top_k_fast(const float* __restrict__ row, int V, float inv_t, int k, float pfrac, double u,
+                                  unsigned char* dyn_smem, int* bin_c, double* bin_m, Select* sel, MaxIdx* sh_mi,
+                                  FastShared* fs, MaxIdx* mx_out, int* out) {
+  uint32_t* cand_key = reinterpret_cast<uint32_t*>(dyn_smem);
+  int* cand_idx = reinterpret_cast<int*>(cand_key + FAST_CANDIDATES);
+  const int warp = threadIdx.x >> 5;
+  collect_candidates<false>(row, V, inv_t, dyn_smem, sh_mi, nullptr, fs, mx_out, nullptr);
+  const MaxIdx mx = *mx_out;
+  // the k-th largest candidate
+  select_in_candidates(cand_key, cand_idx, mx.v, inv_t, false, k, 0.0, bin_c, reinterpret_cast<float*>(cand_idx + FAST_CANDIDATES),
+                       bin_m, sel);
+  if (sel->chosen < 0) return false;
   const uint32_t tau = sel->prefix;
   const int n_eq = k - sel->cnt_above, ties = sel->group_cnt;
   // every logit a thread let go must lie below tau (the bound was kept to 31 bits: compare those)
@@ -478,25 +594,67 @@ __device__ bool sample_top_k_fast(const float* __restrict__ row, int V, float in
     }
     __syncthreads();
   }
-  // the draw: cumulative probability over the kept tokens in index order (runtime/sampler.py:81-88)
-  if (threadIdx.x < m) {
-    const int idx = fs->kept_idx[threadIdx.x];
-    int rank = 0;
-    for (int j = 0; j < m; ++j) rank += fs->kept_idx[j] < idx;
-    fs->by_index[rank] = threadIdx.x;
+  draw_from_list(fs->kept_key, fs->kept_idx, m, mx.v, inv_t, u, fs->red, fs, out);
+  return true;
+}
+
+// ---- top-p alone, in one pass over the row where the row is peaked ------------------------------
+//
+// The same candidates, and the sum over the whole row from the same pass.  The descending cumulative
+// probability is followed over the candidates (a select by mass on their keys); if it reaches top_p
+// times the row's sum at a key above everything a thread let go, the kept set is exact and (at most
+// FAST_P_KEPT tokens) is drawn from in shared memory.  A flat row, whose top_p set runs into the
+// thousands, goes to the general path.
+
+constexpr int FAST_P_KEPT = SAMPLE_THREADS;
+
+__device__ bool sample_top_p_fast(const float* __restrict__ row, int V, float inv_t, float pfrac, double u,
+                                  unsigned char* dyn_smem, int* bin_c, double* bin_m, Select* sel, MaxIdx* sh_mi,
+                                  FastShared* fs, MaxIdx* mx_out, int* out) {
+  uint32_t* cand_key = reinterpret_cast<uint32_t*>(dyn_smem);
+  int* cand_idx = reinterpret_cast<int*>(cand_key + FAST_CANDIDATES);
+  float* hist_m = reinterpret_cast<float*>(cand_idx + FAST_CANDIDATES);             // [256]
+  uint32_t* kept_key = reinterpret_cast<uint32_t*>(hist_m + SEL_BINS);              // [FAST_P_KEPT]
+  int* kept_idx = reinterpret_cast<int*>(kept_key + FAST_P_KEPT);
+  static_assert(FAST_CANDIDATES * 8 + SEL_BINS * 4 + FAST_P_KEPT * 8 <= SAMPLE_SMEM, "the lists live in the histograms' shared memory");
+  const int warp = threadIdx.x >> 5;
+  double row_sum;
+  collect_candidates<true>(row, V, inv_t, dyn_smem, sh_mi, fs->red, fs, mx_out, &row_sum);
+  const MaxIdx mx = *mx_out;
+  // the key at which the descending cumulative probability first reaches top_p of the row's sum
+  select_in_candidates(cand_key, cand_idx, mx.v, inv_t, true, 0, (double)pfrac * row_sum, bin_c, hist_m, bin_m, sel);
+  if (sel->chosen < 0) return false;                 // the candidates' mass does not reach it
+  const uint32_t tau = sel->prefix;
+  const int ties = sel->group_cnt;
+  const double q = (double)prob(key_value(tau), mx.v, inv_t);
+  const int n_eq = (int)fmin(fmax(ceil((sel->target - sel->mass_above) / q), 1.0), (double)ties);
+  // exact only if every logit a thread let go lies below tau; short enough to be drawn from here
+  if ((int)(tau >> 1) <= fs->max_let_go || ties > FAST_TIES || sel->cnt_above + n_eq > FAST_P_KEPT) return false;
+#pragma unroll
+  for (int j = 0; j < FAST_PER_THREAD; ++j) {
+    const int c = threadIdx.x * FAST_PER_THREAD + j;
+    if (cand_idx[c] < 0) continue;
+    if (cand_key[c] > tau) {
+      const int at = atomicAdd(&fs->n_kept, 1);
+      kept_key[at] = cand_key[c];
+      kept_idx[at] = cand_idx[c];
+    } else if (cand_key[c] == tau) {
+      fs->tie_idx[atomicAdd(&fs->n_ties, 1)] = cand_idx[c];
+    }
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    double total = 0.0, c = 0.0;
-    for (int r = 0; r < m; ++r) total += (double)prob(key_value(fs->kept_key[fs->by_index[r]]), mx.v, inv_t);
-    const double target = u * total;
-    int answer = fs->kept_idx[fs->by_index[m - 1]];          // u beyond the last cumulative value: the last kept token
-    for (int r = 0; r < m; ++r) {
-      c += (double)prob(key_value(fs->kept_key[fs->by_index[r]]), mx.v, inv_t);
-      if (c >= target) { answer = fs->kept_idx[fs->by_index[r]]; break; }
+  if (threadIdx.x < ties) {                          // of the ties, the first n_eq by index
+    const int mine = fs->tie_idx[threadIdx.x];
+    int rank = 0;
+    for (int j = 0; j < ties; ++j) rank += fs->tie_idx[j] < mine;
+    if (rank < n_eq) {
+      const int at = atomicAdd(&fs->n_kept, 1);
+      kept_key[at] = tau;
+      kept_idx[at] = mine;
     }
-    *out = answer;
   }
+  __syncthreads();
+  draw_from_list(kept_key, kept_idx, fs->n_kept, mx.v, inv_t, u, fs->red, fs, out);
   return true;
 }
 
@@ -530,6 +688,11 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
                           out + blockIdx.x))
       return;
     __syncthreads();                                 // the general path reuses what the attempt wrote
+  } else if (has_p && !has_k) {
+    if (sample_top_p_fast(row, V, inv_t, pfrac, uniform[blockIdx.x], sample_smem, bin_c, bin_m, &sel, sh_mi, &fast, &mx,
+                          out + blockIdx.x))
+      return;
+    __syncthreads();
   } else {
     mx = block_argmax(row, V, sh_mi);
   }
