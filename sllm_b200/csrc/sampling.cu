@@ -1,15 +1,33 @@
-// Sampling on the device: greedy argmax and temperature sampling by inverse CDF over
-// float32 logits [R, V], one block per row.
+// Sampling on the device over float32 logits [R, V], one block of 1024 threads per row, and the
+// repetition penalty that goes before it.
 //
 // greedy: the first maximum (runtime/sampler.py:8-9).
-// temperature: p = softmax(logits / T) with the maximum subtracted; the token is the
-// first index whose cumulative probability reaches the uniform u, clamped to V-1
-// (runtime/sampler.py:54-58, 81-88); temperature <= 0 is greedy (runtime/sampler.py:50-53).
+// temperature: p = softmax(logits / T) with the maximum subtracted; the token is the first index
+// whose cumulative probability reaches the uniform u (runtime/sampler.py:54-58, 81-88);
+// temperature <= 0 is greedy (runtime/sampler.py:50-53).
 // top-k, then top-p over what it kept, restrict the tokens that can be drawn
 // (runtime/sampler.py:60-79); a token outside the kept set is never returned, also at u = 0 and
 // beyond the last cumulative value, where the reference's searchsorted would name token 0 or V-1.
+// Of logits that tie at a cut, those with the lowest indices stay.
 // The host draws u, one per sampled token, from the request's own generator.
-// Sums are kept in float64 as the reference's sampler works in float64.
+// Probabilities are expf((logit - max) / T), exact to float32 as the logits are; every sum is float64
+// as the reference's sampler works in float64.
+//
+// In this file, in order:
+//   block_argmax                     the greedy row;
+//   select_key / choose_bin          the general top-k / top-p: a five-level select over the row for the
+//                                    key of the cut (by count or by mass), then the kept set is
+//                                    {key > tau} and the ties at tau up to an index;
+//   collect_candidates, select_in_candidates, draw_from_list
+//                                    the one-pass forms: every thread keeps its largest logits, and if
+//                                    the cut provably lies among those candidates the rest runs on a
+//                                    short list in shared memory (sample_top_k_fast for top_k <= 64,
+//                                    sample_top_p_fast for top_p alone on a peaked row);
+//   sample_rows_kernel               picks the form for its row; the general inverse CDF walks the row
+//                                    in index order (32 parts, the chosen part in 32 pieces, one warp's scan);
+//   repetition_penalty_kernel        the penalty from explicit (row, id) pairs;
+//   mark_seen_kernel, penalty_seen_kernel
+//                                    the penalty from a table of seen ids kept on the device.
 #include <math.h>
 #include <stdio.h>
 
