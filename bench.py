@@ -8,6 +8,9 @@ the benchmark's context length (4096).  Prints ONE JSON line: decoded tokens per
 second timed on the device with CUDA events (``value``), the same through the Python
 entry point with host tokens in and out (``e2e``), the prefill of 2,048 tokens,
 the decode step's share of the HBM roofline, and decode at batch 1 and 64.
+``--workload serve-0.5b | serve-32b`` runs one of the baseline's serving workloads through
+``LLM.generate`` instead and prints a record of its own (wall clock, prompt and generated
+tokens a second).
 Weights are random (drawn on the device), token ids uniform random: there is no
 dataset.  The decode step reads every weight once (15 GB, far more than the 126 MB
 L2), so successive steps cannot be served from cache.
