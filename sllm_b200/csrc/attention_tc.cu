@@ -66,6 +66,12 @@ struct AttnTcParams {
   int max_pages, page_size, nq, nkv;
   int page_runs;                 // the run maps are valid: a key tile whose pages have consecutive ids is one box of K and one of V
   float scale_log2;              // scale * log2(e)
+  // the context cut in num_splits ranges of tiles_per_split key tiles each (grid z); with more than one,
+  // a CTA writes what its range gives to part_o [splits, T, nq, HD] (normalised) and part_lse
+  // [splits, T, nq] (log2 of its sum of exponentials, -inf where its range holds no key of the row)
+  int num_splits, tiles_per_split, total_tokens;
+  float* part_o;
+  float* part_lse;
 };
 
 constexpr int TC_BM = 128, TC_BN = 64;
@@ -162,15 +168,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   const int rows_total = q_len * G;
   const int pos0 = ctx - q_len;                  // position of the request's first token of this step
   // per row tile t: its keys end at key_end[t] (exclusive), in n_of[t] key tiles; later rows see more keys
+  // This CTA's range of the context: key tiles [tile0, tile0 + tiles_per_split).  Key tile j below is
+  // the range's j-th, key tile tile0 + j of the request.
+  const int tile0 = (int)blockIdx.z * p.tiles_per_split;
   int key_end[RT], n_of[RT];
 #pragma unroll
   for (int t = 0; t < RT; ++t) {
     const int lo = row0 + t * TC_BM, hi = min(lo + TC_BM, rows_total);
     key_end[t] = hi > lo ? pos0 + (hi - 1) / G + 1 : 0;
-    n_of[t] = (key_end[t] + TC_BN - 1) / TC_BN;
+    n_of[t] = min(max((key_end[t] + TC_BN - 1) / TC_BN - tile0, 0), p.tiles_per_split);
   }
   const int key_hi = RT == 1 ? key_end[0] : max(key_end[0], key_end[RT - 1]);
-  const int n_tiles = (key_hi + TC_BN - 1) / TC_BN;
+  const int n_tiles = RT == 1 ? n_of[0] : max(n_of[0], n_of[RT - 1]);
   const int* bt = p.block_tables + (size_t)seq * p.max_pages;
 
   if (warp == PRODUCER) {
@@ -182,7 +191,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         const int s = j % TC_STAGES;
         uint64_t* full = which ? &v_full[s] : &k_full[s];
         unsigned char* dst = smem + (which ? L::V_OFF : L::K_OFF) + s * L::KV_BYTES;
-        const int kbase = j * TC_BN;
+        const int kbase = (tile0 + j) * TC_BN;
         const int pages = min(per_tile, (key_hi - kbase + ps - 1) / ps);
         // a tile whose pages have consecutive ids is one box (the run maps walk the pages with a stride
         // of their own): the TMA unit's time goes by the box, not by the byte
@@ -377,7 +386,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       tmem_ld32(t_lane + b * TC_BN, s0);
       tmem_ld32(t_lane + b * TC_BN + 32, s1);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      const int kbase = j * TC_BN;
+      const int kbase = (tile0 + j) * TC_BN;
       // the scale is positive, so the maximum of the scaled scores is the scaled maximum: the
       // scaling itself is folded into the exponent's multiply-add below
       float mx = -INFINITY;
@@ -443,17 +452,26 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       if (!mbar_wait(&s_free[t * 2 + ((my_tiles - 1) & 1)], ((my_tiles - 1) >> 1) & 1) || *failed) ok = false;
     }
     if (!ok && !*failed) { *failed = 23; atomicExch(p.status, 23); }
+    const size_t orow = valid ? (size_t)(q0 + row / G) * p.nq + kvh * G + row % G : 0;
+    if (ok && valid && p.num_splits > 1)
+      p.part_lse[(size_t)blockIdx.z * p.total_tokens * p.nq + orow] = (my_tiles > 0 && l > 0.f) ? m_used + log2f(l) : -INFINITY;
     if (ok && my_tiles > 0) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* po = nullptr;
-      if (valid) po = p.out + ((size_t)(q0 + row / G) * p.nq + kvh * G + row % G) * HD;
+      if (valid) po = p.out + orow * HD;
+      float* pp = p.num_splits > 1 ? p.part_o + ((size_t)blockIdx.z * p.total_tokens * p.nq + orow) * HD : nullptr;
 #pragma unroll 1
       for (int c0 = 0; c0 < HD; c0 += 32) {
         uint32_t o[32];
         tmem_ld32(t_lane + L::O_COL + c0, o);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (valid) {
+        if (valid && pp) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<float4*>(pp + c0 + i) = make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
+                                                                  __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+        } else if (valid) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8)
             *reinterpret_cast<uint4*>(po + c0 + i) =
@@ -471,6 +489,32 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   if (warp == ISSUER) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS));
+  }
+}
+
+// The ranges' results of one (token, head) row merged: weights 2^(lse - max lse), ranges without a key skipped.
+template <int HD>
+__global__ void attention_tc_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                            __nv_bfloat16* __restrict__ out, int rows, int num_splits) {
+  pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
+  pdl_wait();
+  const int row = blockIdx.x;
+  float mt = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) mt = fmaxf(mt, part_lse[(size_t)s * rows + row]);
+  if (mt == -INFINITY) return;   // no range wrote this row: it belongs to another kernel of the step (a decoded token's)
+  float tot = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float l = part_lse[(size_t)s * rows + row];
+    tot += l == -INFINITY ? 0.f : exp2f(l - mt);
+  }
+  const float inv = tot > 0.f ? 1.f / tot : 0.f;
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float l = part_lse[(size_t)s * rows + row];
+      if (l != -INFINITY) acc += part_o[((size_t)s * rows + row) * HD + d] * exp2f(l - mt);
+    }
+    out[(size_t)row * HD + d] = __float2bfloat16_rn(acc * inv);
   }
 }
 
@@ -522,9 +566,13 @@ static int launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const CUtenso
     }
     configured = true;
   }
-  dim3 grid(tiles, p.nkv);
+  dim3 grid(tiles, p.nkv, p.num_splits);
   launch_kernel(attention_tc_kernel<HD, RT>, grid, TcLayout<HD, RT>::THREADS, (size_t)smem, stream, mk, mv, rk, rv, p);
-  return launch_status("attention_tc");
+  int rc = launch_status("attention_tc");
+  if (rc != SLLM_OK || p.num_splits == 1) return rc;
+  launch_kernel(attention_tc_combine_kernel<HD>, p.total_tokens * p.nq, HD >= 128 ? 128 : 64, 0, stream,
+                (const float*)p.part_o, (const float*)p.part_lse, p.out, p.total_tokens * p.nq, p.num_splits);
+  return launch_status("attention_tc_combine");
 }
 
 }  // namespace sllm
@@ -537,14 +585,22 @@ SLLM_EXPORT int sllm_attention_tc_supports(int hd, int page_size) {
 }
 
 // The prefill form: tiles of up to 128 * row_tiles (token, head-in-group) rows (row_tiles 1 or 2; tile_row0
-// in steps of that many rows), no window, no context split.
+// in steps of that many rows), no window.  num_splits > 1 cuts the context into that many ranges of
+// tiles_per_split 64-key tiles (num_splits * tiles_per_split must cover the longest context), each range a
+// CTA of its own; part_o [num_splits, total_tokens, nq, hd] and part_lse [num_splits, total_tokens, nq]
+// float32 are the scratch the ranges' results pass through; part_lse must be -inf everywhere before the
+// launch: the merge writes the rows some range has written and leaves the others as they are.
 // num_pages: pages in the cache tensors [num_pages, nkv, page_size, hd].  status: one int of device
 // memory, zero before the launch; non-zero afterwards means a wait ran out and `out` is not valid.
 SLLM_EXPORT int sllm_attention_tc(const void* q, const void* k_cache, const void* v_cache, long long num_pages, void* out,
                                   const int* block_tables, int max_pages, const int* q_start, const int* ctx_len,
                                   const int* tile_seq, const int* tile_row0, int tiles, int row_tiles, int nq, int nkv,
-                                  int hd, int page_size, float scale, int* status, cudaStream_t stream) {
+                                  int hd, int page_size, float scale, int num_splits, int tiles_per_split, int total_tokens,
+                                  float* part_o, float* part_lse, int* status, cudaStream_t stream) {
   SLLM_REQUIRE(row_tiles == 1 || row_tiles == 2, "attention_tc: row_tiles=%d must be 1 or 2", row_tiles);
+  SLLM_REQUIRE(num_splits >= 1 && num_splits <= 65535 && tiles_per_split >= 1, "attention_tc: bad context split %d x %d",
+               num_splits, tiles_per_split);
+  SLLM_REQUIRE(num_splits == 1 || (part_o && part_lse && total_tokens > 0), "attention_tc: a context split needs scratch");
   SLLM_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tc: bad head counts nq=%d nkv=%d", nq, nkv);
   SLLM_REQUIRE(sllm_attention_tc_supports(hd, page_size), "attention_tc: head_dim=%d page_size=%d not taken", hd, page_size);
   SLLM_REQUIRE(max_pages > 0 && tiles >= 0 && num_pages > 0 && nkv <= 65535, "attention_tc: bad sizes");
@@ -567,6 +623,8 @@ SLLM_EXPORT int sllm_attention_tc(const void* q, const void* k_cache, const void
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.block_tables = block_tables; p.q_start = q_start;
   p.ctx_len = ctx_len; p.tile_seq = tile_seq; p.tile_row0 = tile_row0; p.status = status; p.max_pages = max_pages;
   p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.scale_log2 = scale * 1.4426950408889634f;
+  p.num_splits = num_splits; p.tiles_per_split = num_splits == 1 ? (1 << 30) / TC_BN : tiles_per_split;
+  p.total_tokens = total_tokens; p.part_o = part_o; p.part_lse = part_lse;
   if (row_tiles == 2)
     return hd == 128 ? launch_tc<128, 2>(mk, mv, rk, rv, p, tiles, stream) : launch_tc<64, 2>(mk, mv, rk, rv, p, tiles, stream);
   return hd == 128 ? launch_tc<128, 1>(mk, mv, rk, rv, p, tiles, stream) : launch_tc<64, 1>(mk, mv, rk, rv, p, tiles, stream);

@@ -494,18 +494,40 @@ def tc_attention_supports(hd: int, page_size: int) -> bool:
     return bool(lib().sllm_attention_tc_supports(int(hd), int(page_size)))
 
 
+def choose_tc_splits(num_tiles: int, nkv: int, max_ctx: int) -> tuple[int, int]:
+    """(ranges, 64-key tiles a range) for the prefill form: few row tiles over a long context are cut
+    so that about two CTAs an SM run, each range at least 16 key tiles long."""
+    key_tiles = max(1, -(-max_ctx // 64))
+    ctas = max(num_tiles * nkv, 1)
+    want = max(1, min(2 * NUM_SMS // ctas, key_tiles // 16, 32))
+    per = -(-key_tiles // want)
+    return -(-key_tiles // per), per
+
+
 def attention_tc(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, nq, nkv, hd, scale, out=None,
-                 row_tiles: int = 1):
-    """The prefill form on tcgen05 (tiles of 128 * row_tiles rows, row_tiles 1 or 2; no window, no
-    context split; see `attention_tiles`)."""
+                 row_tiles: int = 1, splits: tuple[int, int] = (1, 0)):
+    """The prefill form on tcgen05 (tiles of 128 * row_tiles rows, row_tiles 1 or 2; no window; see
+    `attention_tiles`).  ``splits`` = (ranges, 64-key tiles a range) cuts the context into ranges
+    that run as CTAs of their own and are merged afterwards; ranges x tiles must cover the longest
+    context among the tiles' requests."""
     _chk(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles[0], tiles[1])
     if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
         raise KernelError("attention_tc: bfloat16 only")
     if out is None:
         out = torch.empty_like(q)
+    n_splits, per = int(splits[0]), int(splits[1])
+    part_o = part_lse = None
+    T = q.shape[0]
+    if n_splits > 1:
+        part_o = torch.empty((n_splits, T, nq, hd), dtype=torch.float32, device=q.device)
+        part_lse = torch.full((n_splits, T, nq), float("-inf"), dtype=torch.float32, device=q.device)
+        launches["library"] += 1           # the fill
     call("sllm_attention_tc", _p(q), _p(k_cache), _p(v_cache), k_cache.shape[0], _p(out), _p(block_tables),
          block_tables.shape[1], _p(q_start), _p(ctx_len), _p(tiles[0]), _p(tiles[1]), tiles[2], int(row_tiles), nq, nkv,
-         hd, k_cache.shape[2], float(scale), _p(_status_word(q.device)), _stream())
+         hd, k_cache.shape[2], float(scale), n_splits, max(per, 1), T, _p(part_o), _p(part_lse),
+         _p(_status_word(q.device)), _stream())
+    if n_splits > 1:
+        launches["own"] += 1               # the merge kernel
     _tc_used["since_check"] += 1
     return out
 
@@ -534,8 +556,9 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
         rows = 128
         small, large = attention_tiles(step.q_lens, G, q.device, step.ctx_lens, rows)
         splits = choose_splits(small[2], nkv, step.max_ctx_len) if (small and not large) else 1
-        step.attn_tiles[key] = (small, large, splits, rows)
-    small, large, splits, rows = step.attn_tiles[key]
+        tc_splits = choose_tc_splits(large[2], nkv, step.max_ctx_len) if (large and use_tc) else (1, 0)
+        step.attn_tiles[key] = (small, large, splits, rows, tc_splits)
+    small, large, splits, rows, tc_splits = step.attn_tiles[key]
     out = torch.empty_like(q)
     if small and tma_attention_supports(hd, k_cache.shape[2]):
         attention_tma_decode(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, splits,
@@ -545,7 +568,7 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
                       nq, nkv, hd, scale, window, out)
     if large and use_tc:
         attention_tc(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, nq, nkv, hd, scale, out,
-                     row_tiles=rows // 128)
+                     row_tiles=rows // 128, splits=tc_splits)
     elif large:
         attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, False, 1,
                       nq, nkv, hd, scale, window, out)

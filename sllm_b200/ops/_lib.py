@@ -59,7 +59,8 @@ def _declare(L):
         "sllm_wait_probe": [c_void_p, ctypes.c_ulonglong, c_void_p, c_void_p],
         "sllm_attention_tc_supports": [c_int, c_int],
         "sllm_attention_tc": [c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
+                              c_void_p, c_void_p, c_void_p, c_void_p],
         "sllm_gemm_tcgen05_supports": [c_int, c_int, c_int],
         "sllm_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "sllm_linear_tc_supports": [c_int, c_int, c_int],

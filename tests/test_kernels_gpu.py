@@ -473,6 +473,56 @@ def test_attention_tc(nq, nkv, hd, ps, case, row_tiles, consecutive):
     torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("nq,nkv,hd,ps", [(28, 4, 128, 16), (6, 1, 64, 32), (4, 2, 128, 64)])
+@pytest.mark.parametrize("case", ["long", "mixed", "peaked", "far"])
+@pytest.mark.parametrize("splits", [(2, 20), (3, 11), (5, 7), (9, 4), (40, 1)])
+def test_attention_tc_context_split(nq, nkv, hd, ps, case, splits):
+    """The prefill form with its context cut into ranges that run as CTAs of their own and are merged:
+    ranges that hold no key of a row tile (a portion's early rows), ranges of one key tile, rows of
+    decoded tokens that another kernel wrote and the merge must leave alone, and a key that stands
+    out in one range."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(23)
+    lens, q_lens = {"long": ([1000, 2100], [1000, 300]), "mixed": ([90, 400, 2, 65, 2200], [37, 1, 2, 1, 128]),
+                    "peaked": ([2300], [650]), "far": ([2500], [200])}[case]
+    if splits[0] * splits[1] * 64 < max(lens):
+        splits = (-(-max(lens) // (64 * splits[1])), splits[1])         # the ranges must cover the longest context
+    q, kc, vc, bt, pos, seq = _paged_case(g, lens, q_lens, nq, nkv, hd, ps, torch.bfloat16, consecutive="runs")
+    q_start, ctx_len = _starts(q_lens, lens)
+    scale = 1.0 if case == "peaked" else hd ** -0.5
+    if case == "far":
+        far = 777                                                       # one key of the second range or so wins every row
+        direction = torch.randn(hd, device="cuda", generator=g)
+        direction /= direction.norm()
+        kc[int(bt[0, far // ps]), :, far % ps, :] = (direction * 16).bfloat16()
+        q[:] = (direction * 16).repeat(nq).bfloat16()
+        scale = 1.0
+    want = ref.attention_simt(q.float(), kc.float(), vc.float(), bt, pos, seq, nq, nkv, hd, scale, None)
+    small, large = ops.attention_tiles(q_lens, nq // nkv, "cuda", lens, 128)
+    out = torch.full_like(q, float("nan"))
+    if small:
+        ops.attention_mma(q, kc, vc, bt, q_start, ctx_len, small, True, 1, nq, nkv, hd, scale, None, out)
+    before = out.clone()
+    ops.attention_tc(q, kc, vc, bt, q_start, ctx_len, large, nq, nkv, hd, scale, out, splits=splits)
+    ops.check_tcgen05_status()
+    assert not out.isnan().any(), "a row was not written"
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
+    kept = ~before.isnan().any(dim=1)
+    assert torch.equal(out[kept], before[kept]), "the merge touched rows of another kernel"
+    if case == "far":
+        torch.testing.assert_close(out.float().reshape(-1, nq, hd)[0], vc[int(bt[0, far // ps]), :, far % ps, :].float()
+                                   .repeat_interleave(nq // nkv, dim=0), rtol=2e-2, atol=2e-2)
+
+
+def test_choose_tc_splits_covers_the_context():
+    ops = _ops()
+    for tiles, nkv, ctx in ((112, 4, 2048), (28, 4, 32768), (7, 4, 32768), (1, 1, 100), (3, 2, 5000), (28, 4, 1025)):
+        n, per = ops.choose_tc_splits(tiles, nkv, ctx)
+        assert n >= 1 and n * per * 64 >= ctx and (n - 1) * per * 64 < ctx
+        assert n == 1 or per >= 16
+    assert ops.choose_tc_splits(112, 4, 2048)[0] == 1 and ops.choose_tc_splits(28, 4, 32768)[0] == 2
+
+
 def test_a_wait_that_nothing_ends_gives_up_and_says_so():
     """The bounded wait of the TMA-fed kernels: a barrier nothing arrives at, a limit of 3 ms; the kernel
     returns with its status word set, in about that time, and the device goes on working."""
