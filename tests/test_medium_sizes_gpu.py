@@ -143,3 +143,41 @@ def test_widths_that_are_multiples_of_nothing(name, tmp_path):
             eng = Engine(model, page_size=16, num_pages=tr.max_tokens // 16, max_requests=4)
             out = traces.replay_engine(tr, eng)
             traces.compare(tr, out, want, what=f"{name}/{dtype}/{mode}", **tol)
+
+
+def test_portions_of_a_long_prompt_beside_decoded_tokens(tmp_path):
+    """A prompt of 2,700 tokens fed in portions of 150 while another request decodes: from 2,048 tokens of
+    context on, the few row tiles of a portion are cut over the context and merged, in the same step
+    in which the decode form writes the other request's rows.  The logits at the portions' ends, at
+    the decoded tokens and after the prompt, against the plain implementation."""
+    from sllm_b200.engine import Engine, StepEntry, build_model
+    from sllm_b200.weights import write_random_model
+    dev = cuda_or_skip()
+    cfg = dict(BASE, num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+               intermediate_size=512, vocab_size=1000, rope_theta=10000.0, rms_norm_eps=1e-6,
+               max_position_embeddings=4096, tie_word_embeddings=True)
+    d = str(tmp_path / "model")
+    write_random_model(d, cfg, 51, std=0.04, bias_std=0.2, gain_std=0.1)
+    c, w = plain.load_model(d)
+    rng = np.random.default_rng(29)
+    long_ids = rng.integers(0, cfg["vocab_size"], 2700).tolist()
+    short_ids = rng.integers(0, cfg["vocab_size"], 40).tolist()
+    want_long, want_short = plain.forward(long_ids, w, c), plain.forward(short_ids, w, c)
+    spread = float(want_long.std())
+    model, _ = build_model(d, "bfloat16", dev)
+    eng = Engine(model, page_size=16, num_pages=(2700 + 64) // 16 + 4, max_requests=2)
+    eng.step([StepEntry("s", short_ids[:20], [])])
+    at, worst = 20, 0.0
+    for start in range(0, 2700, 150):
+        entries = [StepEntry("l", long_ids[start:start + 150], [149])]
+        if at < 40:
+            entries.append(StepEntry("s", [short_ids[at]], [0]))
+        got = eng.step(entries).float().cpu().numpy()
+        err = np.abs(got[0] - want_long[start + 149]).max()
+        if at < 40:
+            err = max(err, np.abs(got[1] - want_short[at]).max())
+            at += 1
+        worst = max(worst, float(err))
+    assert worst <= 0.08 * spread, (worst, spread)
+    eng.finish("l"), eng.finish("s")
+    eng.cache.check()
