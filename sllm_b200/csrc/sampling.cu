@@ -21,7 +21,7 @@
 //   collect_candidates, select_in_candidates, draw_from_list
 //                                    the one-pass forms: every thread keeps its largest logits, and if
 //                                    the cut provably lies among those candidates the rest runs on a
-//                                    short list in shared memory (sample_top_k_fast for top_k <= 64,
+//                                    short list in shared memory (sample_top_k_fast for top_k <= 256,
 //                                    sample_top_p_fast for top_p alone on a peaked row);
 //   sample_rows_kernel               picks the form for its row; the general inverse CDF walks the row
 //                                    in index order (32 parts, the chosen part in 32 pieces, one warp's scan);
@@ -350,7 +350,7 @@ __device__ __forceinline__ bool is_kept(const Kept& kp, float l, int i) {
 // row's k largest) the general path above takes the row.  The probabilities of top-k's set are
 // renormalised, so the sum over the whole row is never needed here.
 
-constexpr int FAST_K = 64;                  // rows with top_k up to this try the one-pass form
+constexpr int FAST_K = 256;                 // rows with top_k up to this try the one-pass form
 constexpr int FAST_PER_THREAD = 4;
 constexpr int FAST_CANDIDATES = SAMPLE_THREADS * FAST_PER_THREAD;
 constexpr int FAST_TIES = 1024;
@@ -358,7 +358,8 @@ static_assert(FAST_CANDIDATES * 8 + SEL_BINS * 4 <= SAMPLE_SMEM, "the candidates
 
 struct FastShared {
   uint32_t kept_key[FAST_K], sorted_key[FAST_K];
-  int kept_idx[FAST_K], sorted_idx[FAST_K], by_index[FAST_K];
+  int kept_idx[FAST_K], sorted_idx[FAST_K];
+  double q[FAST_K];
   int tie_idx[FAST_TIES];
   int n_kept, n_ties, max_let_go, answer, last;
   double red[33];
@@ -594,16 +595,16 @@ __device__ bool sample_top_k_fast(const float* __restrict__ row, int V, float in
       fs->sorted_idx[rank] = idx;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      double total = 0.0, c = 0.0;
-      for (int j = 0; j < m; ++j) total += (double)prob(key_value(fs->sorted_key[j]), mx.v, inv_t);
-      int cutoff = m;
-      for (int j = 0; j < m; ++j) {
-        c += (double)prob(key_value(fs->sorted_key[j]), mx.v, inv_t);
-        if (c >= (double)pfrac * total) { cutoff = j + 1; break; }
-      }
-      fs->n_kept = cutoff;
-    }
+    // the cumulative probability at every place of the sorted list, one place a thread
+    if (threadIdx.x < m) fs->q[threadIdx.x] = (double)prob(key_value(fs->sorted_key[threadIdx.x]), mx.v, inv_t);
+    if (threadIdx.x == 0) fs->n_kept = m;
+    __syncthreads();
+    double cum = 0.0;
+    if (threadIdx.x < m)
+      for (int j = 0; j <= (int)threadIdx.x; ++j) cum += fs->q[j];
+    if ((int)threadIdx.x == m - 1) fs->red[0] = cum;        // the total
+    __syncthreads();
+    if (threadIdx.x < m && cum >= (double)pfrac * fs->red[0]) atomicMin(&fs->n_kept, (int)threadIdx.x + 1);
     __syncthreads();
     m = fs->n_kept;
     if (threadIdx.x < m) {
