@@ -268,7 +268,7 @@ def test_sample_rows_top_k_and_top_p(V):
     ops = _ops()
     g = torch.Generator(device="cuda").manual_seed(V)
     cases = [(0.7, 5, -1.0), (1.0, 0, 0.8), (1.3, 40, 0.5), (0.9, 1, -1.0), (0.5, 0, 0.0), (1.0, 3, 1.0),
-             (2.0, V, 0.95), (1.0, V + 5, -1.0), (0.0, 4, 0.3), (1.1, 1000, 0.999)]
+             (2.0, V, 0.95), (1.0, V + 5, -1.0), (0.0, 4, 0.3), (1.1, 1000, 0.999), (0.9, 200, 0.7), (1.2, 256, -1.0)]
     R = len(cases)
     logits = torch.randn(R, V, device="cuda", generator=g) * 2.5
     logits[1, V // 2] = logits[1].max() + 3                   # one token holds most of the mass
