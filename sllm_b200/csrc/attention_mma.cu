@@ -71,8 +71,10 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
   pdl_wait();       // everything below reads what the step's earlier kernels or its batch upload wrote
-  const int seq = p.tile_seq[blockIdx.x], row0 = p.tile_row0[blockIdx.x];
-  const int kvh = blockIdx.y, split = blockIdx.z;
+  // the KV head is the grid's fastest index: tiles come longest first and CTAs start in grid order,
+  // so every head's long tiles start in the first wave
+  const int tile_i = blockIdx.x / p.nkv, kvh = blockIdx.x % p.nkv, split = blockIdx.z;
+  const int seq = p.tile_seq[tile_i], row0 = p.tile_row0[tile_i];
   const int G = p.nq / p.nkv;
   const int q0 = p.q_start[seq], q_len = p.q_start[seq + 1] - q0, ctx = p.ctx_len[seq];
   const int rows_total = q_len * G;
@@ -376,7 +378,7 @@ static int launch_attention(const AttnParams& p, int tiles, cudaStream_t stream)
     }
     configured = true;
   }
-  dim3 grid(tiles, p.nkv, p.num_splits);
+  dim3 grid((unsigned)tiles * p.nkv, 1, p.num_splits);
   launch_kernel(attention_mma_kernel<HD, DECODE>, grid, AttThreads<DECODE>::value, smem, stream, p);
   int rc = launch_status("attention_mma");
   if (rc != SLLM_OK) return rc;

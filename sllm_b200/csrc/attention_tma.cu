@@ -92,8 +92,10 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __syncthreads();
   pdl_wait();          // the queries, the new keys and values, and the batch description come from earlier work
 
-  const int seq = p.tile_seq[blockIdx.x], row0 = p.tile_row0[blockIdx.x];
-  const int kvh = blockIdx.y, split = blockIdx.z;
+  // the KV head is the grid's fastest index: tiles come longest first and CTAs start in grid order,
+  // so every head's long tiles start in the first wave
+  const int tile_i = blockIdx.x / p.nkv, kvh = blockIdx.x % p.nkv, split = blockIdx.z;
+  const int seq = p.tile_seq[tile_i], row0 = p.tile_row0[tile_i];
   const int G = p.nq / p.nkv;
   const int q0 = p.q_start[seq], q_len = p.q_start[seq + 1] - q0, ctx = p.ctx_len[seq];
   const int rows_total = q_len * G;
@@ -466,7 +468,7 @@ static int launch_ta(const CUtensorMap& mk, const CUtensorMap& mv, const CUtenso
     }
     configured = true;
   }
-  dim3 grid(tiles, p.nkv, p.num_splits);
+  dim3 grid((unsigned)tiles * p.nkv, 1, p.num_splits);
   launch_kernel(attention_tma_decode_kernel<HD>, grid, TA_THREADS, smem, stream, mk, mv, rk, rv, p);
   int rc = launch_status("attention_tma");
   if (rc != SLLM_OK) return rc;
