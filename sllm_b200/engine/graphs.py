@@ -39,6 +39,8 @@ class _Graph:
         records its tokens in the engine's table of seen ids and applies the rows' repetition
         penalties before it samples."""
         self.penalised = bool(penalised)
+        if self.penalised:
+            engine.seen_table()                      # made here, never inside a capture
         cache = engine.cache
         self.B = B
         ps = cache.page_size
