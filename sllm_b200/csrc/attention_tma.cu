@@ -90,7 +90,10 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  pdl_wait();          // the queries, the new keys and values, and the batch description come from earlier work
+  // The batch description (tiles, lengths, block tables) was copied to the device before the step's
+  // first kernel started, so it is read before the wait for the step's earlier kernels: the chain of
+  // dependent loads (tile -> request -> lengths -> pages) runs under their tails.  The queries and the
+  // new keys and values come from those kernels: each role waits before it touches them.
 
   // the KV head is the grid's fastest index: tiles come longest first and CTAs start in grid order,
   // so every head's long tiles start in the first wave
@@ -130,6 +133,7 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       __syncwarp();
     }
     auto page_of = [&](int pi) { return bt_cached ? bt_s[pi - page_first] : bt[pi]; };
+    pdl_wait();
     for (int tile = 0; tile < n_tiles; ++tile) {
       const int s = tile % TA_STAGES, round = tile / TA_STAGES;
       bool ok = true;
@@ -187,6 +191,7 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     // ---------------- compute warps ----------------
     // queries: 16 rows of (token, head-in-group)
     constexpr int CHUNKS = HD / 8;
+    pdl_wait();
     for (int c = tid; c < 16 * CHUNKS; c += 128) {
       const int r = c / CHUNKS, ch = c % CHUNKS;
       const int row = row0 + r;
