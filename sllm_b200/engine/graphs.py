@@ -220,6 +220,52 @@ class DecodeGraphs:
             return False
         return all(cache.can_reserve(e.req_id, t) for e, t in zip(entries, totals))
 
+    def _capture(self, gr: _Graph) -> torch.Tensor:
+        """Run the step that `gr`'s static buffers describe once, launch by launch, then capture the same
+        launches as a graph.  Returns the ids the eager run sampled."""
+        eng = self.engine
+        before = ops.launches["own"]
+        gr.run(eng)
+        gr.launches = ops.launches["own"] - before
+        eager_ids = gr.ids
+        graph = torch.cuda.CUDAGraph()
+        # Nothing may free device memory or destroy a graph while the capture runs: a collection
+        # of garbage (an engine dropped earlier, say) in the middle of it would invalidate it.
+        # (torch's graph context collects once before it begins; here the collector stays off.)
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        reporting = ops.status_word_launches()
+        try:
+            with torch.cuda.graph(graph):
+                gr.run(eng)
+        finally:
+            if gc_was_on:
+                gc.enable()
+        ops.launches["own"] -= gr.launches          # capturing launched nothing
+        gr.reporting = ops.status_word_launches() - reporting      # kernels of the graph that report through the status word
+        ops.note_status_word_launches(-gr.reporting)
+        gr.graph = graph
+        return eager_ids
+
+    def warmup(self, batch_sizes, contexts, penalised: bool = False) -> int:
+        """Capture the graphs for these numbers of requests and context lengths ahead of the first
+        request (a capture costs tens of milliseconds, which the first step of each shape pays
+        otherwise).  The captured step is made of padding rows only: it reads no page and writes
+        none.  Returns how many graphs were captured."""
+        eng = self.engine
+        made = 0
+        for rows in sorted({self.batch_bucket(int(n)) for n in batch_sizes}):
+            for bucket in sorted({self.bucket(min(int(c), eng.max_positions)) for c in contexts}):
+                key = (rows, bucket, bool(penalised))
+                if key in self.graphs and self.graphs[key].graph is not None:
+                    continue
+                gr = self.graphs[key] = _Graph(eng, *key)
+                gr.fill(eng, [], [], np.zeros(0, np.float32), np.zeros(0, np.float64))
+                self._capture(gr)
+                made += 1
+        torch.cuda.synchronize(eng.device)
+        return made
+
     def launch(self, entries, temperatures, uniforms, device_timer=None, tokens_on_device: bool = False,
                top_k=None, top_p=None, penalties=None) -> Launched:
         """Queue one decode step: reserve pages, describe the batch, replay the graph, queue the copy
@@ -264,27 +310,7 @@ class DecodeGraphs:
         ids_now = None
         if gr.graph is None:
             # first use: run eagerly on the static buffers (this step's result), then capture
-            before = ops.launches["own"]
-            gr.run(eng)
-            gr.launches = ops.launches["own"] - before
-            ids_now = gr.ids.cpu().tolist()[:len(entries)]
-            graph = torch.cuda.CUDAGraph()
-            # Nothing may free device memory or destroy a graph while the capture runs: a collection
-            # of garbage (an engine dropped earlier, say) in the middle of it would invalidate it.
-            # (torch's graph context collects once before it begins; here the collector stays off.)
-            gc_was_on = gc.isenabled()
-            gc.disable()
-            reporting = ops.status_word_launches()
-            try:
-                with torch.cuda.graph(graph):
-                    gr.run(eng)
-            finally:
-                if gc_was_on:
-                    gc.enable()
-            ops.launches["own"] -= gr.launches          # capturing launched nothing
-            gr.reporting = ops.status_word_launches() - reporting      # kernels of the graph that report through the status word
-            ops.note_status_word_launches(-gr.reporting)
-            gr.graph = graph
+            ids_now = self._capture(gr).cpu().tolist()[:len(entries)]
             # the graph's own output buffer must hold this step's ids for a step chained behind it
             gr.ids[:len(ids_now)].copy_(torch.tensor(ids_now, dtype=torch.int32, device=eng.device))
         else:

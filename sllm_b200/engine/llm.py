@@ -84,6 +84,23 @@ class LLM:
             self._next_id += 1
         return self.scheduler.add(req_id, prompt_token_ids, params or SamplingParams())
 
+    def warmup(self, batch_sizes=None, contexts=None, penalised: bool = False) -> int:
+        """Capture the decode graphs ahead of the first request: for every number of requests up to
+        ``max_num_seqs`` (or those given) and every context bucket up to the model length (or those
+        that hold the given lengths).  Returns the number of graphs captured; 0 without CUDA graphs."""
+        if not self.cuda_graphs:
+            return 0
+        if batch_sizes is None:
+            batch_sizes = range(1, self.scheduler.max_num_seqs + 1)
+        if contexts is None:
+            contexts, c = [], 256                     # the buckets: powers of two from 256 up to the model length
+            while True:
+                contexts.append(min(c, self.max_model_len))
+                if c >= self.max_model_len:
+                    break
+                c *= 2
+        return self.engine.graphs.warmup(batch_sizes, contexts, penalised)
+
     def abort(self, req_id) -> bool:
         return self.scheduler.abort(req_id)
 

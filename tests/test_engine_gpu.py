@@ -692,3 +692,31 @@ def test_repetition_penalty_through_graphs_preemption_and_one_token_prompts(tiny
         assert llm.scheduler.num_preemptions > 0, "the pool was meant to force a preemption"
     assert any(key[2] for key in llm.engine.graphs.graphs), "decode steps with a penalty were meant to run from a graph"
     llm.engine.cache.check()
+
+
+def test_warmup_captures_the_graphs_ahead(tiny):
+    """`LLM.warmup` captures decode graphs from padding rows only; generation afterwards finds them
+    (no step of those shapes runs launch by launch), gives the plain implementation's tokens, and the
+    cache was not touched by the warm-up."""
+    from sllm_b200.engine.llm import LLM
+    from sllm_b200.sampling import SamplingParams
+    dev = cuda_or_skip()
+    name, model_dir, page = tiny
+    cfg, w = plain.load_model(model_dir)
+    llm = LLM(model_dir, dtype="float32", device=dev, block_size=page, num_pages=64, max_num_seqs=3, chunk_size=24,
+              max_batch_tokens=40)
+    made = llm.warmup()
+    graphs = llm.engine.graphs.graphs
+    assert made == len(graphs) >= 3 and all(g.graph is not None for g in graphs.values())
+    assert llm.warmup() == 0                                    # nothing left to capture
+    llm.engine.cache.check()
+    assert not llm.engine.cache.requests and all(g.pool.used_count == 0 for g in llm.engine.cache.groups)
+    prompts = _prompts(cfg, (5, 17, 33))
+    res = llm.generate(prompts, SamplingParams(max_new=8))
+    for p, r in zip(prompts, res):
+        assert r.ids == plain.generate(p, 8, w, cfg)
+    assert len(llm.engine.graphs.graphs) == made                # every decode step found its graph
+    assert llm.warmup(batch_sizes=[2], contexts=[64], penalised=True) == 1
+    res = llm.generate(prompts[:2], SamplingParams(max_new=6, temperature=0.7, seed=3, repetition_penalty=1.4))
+    for p, r in zip(prompts, res):
+        assert r.ids == plain.generate(p, 6, w, cfg, temperature=0.7, seed=3, repetition_penalty=1.4)
