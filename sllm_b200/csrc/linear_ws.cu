@@ -12,6 +12,12 @@
 //   store      out[M, N] (+ bias), float32 or bfloat16
 //   residual   residual[M, N] += y (+ bias): the float32 stream is updated in place, so the next
 //              norm has nothing to add
+//   rotary     for the fused q|k|v matrix of an attention layer: bias, rotary encoding and the write
+//              of the new keys and values into their cache pages, so that the decode step needs no
+//              kernel between this product and the attention.  A CTA then takes the 8 rows j..j+7
+//              of a head and the 8 rows hd/2 apart: the two rows of a rotation pair are the two
+//              rows (g, g+8) of one MMA accumulator, and meet in one thread of the epilogue
+//              (ref/qwen3_5.py:355-370; cache content ref/incremental.py:135-139).
 // About N/16 CTAs keep every SM busy without splitting K over the grid; their number is rounded up
 // to a multiple of the SM count and the rows dealt evenly (N = 3584: 296 CTAs of 12 or 13 rows
 // instead of 224 of 16, of which 76 SMs would get two and 72 one).
@@ -26,6 +32,21 @@ namespace sllm {
 
 #define WS_EPI_STORE 0
 #define WS_EPI_RESID 1
+#define WS_EPI_ROPE 2
+
+// what the rotary epilogue needs beside the product: the rows of W are q heads, then k heads, then v
+// heads of `hd` rows each; table [max_pos][2][hd/2] holds cos then sin (rotary_dim == hd), or is null
+// (no rotation); a token's key and value go to slot_mapping[token] of the paged caches
+// [page][kv head][slot in page][hd] (null: not written), its queries to q_out [M, nq * hd].
+struct WsRope {
+  const int* positions;
+  const float* table;
+  const int* slot_mapping;
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  __nv_bfloat16* q_out;
+  int max_pos, nq, nkv, hd, page_size, num_pages;
+};
 
 __device__ __forceinline__ uint4 ws_ldg_stream(const void* p) {
   uint4 v;
@@ -53,16 +74,24 @@ template <int NT, int EPI, typename OUT>
 __global__ void __launch_bounds__(WS_WARPS * 32)
 linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W,
                  const float* __restrict__ bias, OUT* __restrict__ out, float* __restrict__ residual,
-                 int M, int N, int K) {
+                 int M, int N, int K, const WsRope rope) {
   __shared__ float red[WS_WARPS][16][8 * NT + 1];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
   // the CTA's rows [n0, n1): at most 16, the N rows dealt evenly over the grid (so that a grid of a
   // whole number of CTAs per SM gives every SM the same bytes to stream)
-  const int n0 = (int)(((long long)blockIdx.x * N) / gridDim.x), n1 = (int)(((long long)(blockIdx.x + 1) * N) / gridDim.x);
+  int n0 = (int)(((long long)blockIdx.x * N) / gridDim.x), n1 = (int)(((long long)(blockIdx.x + 1) * N) / gridDim.x);
   const int k_blocks = K / 32;
 
-  const int r0 = min(n0 + g, n1 - 1), r1 = min(n0 + g + 8, n1 - 1);   // rows past the CTA's: clamped loads, skipped stores
+  int r0 = min(n0 + g, n1 - 1), r1 = min(n0 + g + 8, n1 - 1);   // rows past the CTA's: clamped loads, skipped stores
+  if constexpr (EPI == WS_EPI_ROPE) {
+    // CTA b of a head's hd/16: rows [8c, 8c+8) of the head and the 8 rows hd/2 further
+    const int per_head = rope.hd / 16;
+    n0 = ((int)blockIdx.x / per_head) * rope.hd + ((int)blockIdx.x % per_head) * 8;
+    n1 = n0 + 16;                                  // (not a range: local row r is n0 + (r & 7) + (r >> 3) * hd/2)
+    r0 = n0 + g;
+    r1 = n0 + rope.hd / 2 + g;
+  }
   const __nv_bfloat16* w0 = W + (size_t)r0 * K + t4 * 8;
   const __nv_bfloat16* w1 = W + (size_t)r1 * K + t4 * 8;
   const __nv_bfloat16* xr[NT];
@@ -133,6 +162,41 @@ linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
 #pragma unroll
     for (int c = 0; c < 4; ++c) red[warp][g + ((c & 2) ? 8 : 0)][8 * j + 2 * t4 + (c & 1)] = acc[j][c];
   __syncthreads();
+  if constexpr (EPI == WS_EPI_ROPE) {
+    const int half = rope.hd / 2;
+    const int head = n0 / rope.hd, j0 = n0 % rope.hd;            // j0 = 8c: the pair's lower dimension starts here
+    for (int idx = tid; idx < 8 * 8 * NT; idx += WS_WARPS * 32) {
+      const int i = idx % 8, tok = idx / 8;                        // consecutive threads -> consecutive dimensions of one token
+      if (tok >= M) continue;
+      float lo = 0.f, hi = 0.f;
+#pragma unroll
+      for (int w = 0; w < WS_WARPS; ++w) { lo += red[w][i][tok]; hi += red[w][i + 8][tok]; }
+      if (bias) { lo += bias[n0 + i]; hi += bias[n0 + half + i]; }
+      __nv_bfloat16* dst;
+      if (head < rope.nq) {
+        dst = rope.q_out + ((size_t)tok * rope.nq + head) * rope.hd;
+      } else {
+        int slot = rope.slot_mapping ? rope.slot_mapping[tok] : -1;
+        if (slot < 0 || slot / rope.page_size >= rope.num_pages) continue;     // not written (padding row, borrowed cache)
+        const bool is_k = head < rope.nq + rope.nkv;
+        const int kvh = is_k ? head - rope.nq : head - rope.nq - rope.nkv;
+        dst = (is_k ? rope.k_cache : rope.v_cache) +
+              (((size_t)(slot / rope.page_size) * rope.nkv + kvh) * rope.page_size + slot % rope.page_size) * rope.hd;
+      }
+      if (rope.table != nullptr && head < rope.nq + rope.nkv) {
+        int pos = rope.positions[tok];
+        pos = pos < 0 ? 0 : (pos >= rope.max_pos ? rope.max_pos - 1 : pos);
+        const float* cs = rope.table + (size_t)pos * rope.hd;        // cos[half] then sin[half]
+        const float c = cs[j0 + i], sn = cs[half + j0 + i];
+        const float a = lo * c - hi * sn, b = hi * c + lo * sn;
+        lo = a;
+        hi = b;
+      }
+      dst[j0 + i] = __float2bfloat16_rn(lo);
+      dst[j0 + half + i] = __float2bfloat16_rn(hi);
+    }
+    return;
+  }
   for (int idx = tid; idx < 16 * 8 * NT; idx += WS_WARPS * 32) {
     const int row = idx % 16, tok = idx / 16;           // consecutive threads -> consecutive rows of one token
     const int n = n0 + row;
@@ -148,7 +212,7 @@ linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
 
 template <int NT, int EPI, typename OUT>
 static int launch_ws(const __nv_bfloat16* x, const __nv_bfloat16* W, const float* bias, void* out, float* residual,
-                     int M, int N, int K, cudaStream_t stream) {
+                     int M, int N, int K, cudaStream_t stream, const WsRope& rope = WsRope{}) {
   // CTAs of 16 rows, or, when those would fill the SMs unevenly, the next multiple of the SM count
   static int num_sms = 0;
   if (num_sms == 0) {
@@ -157,11 +221,11 @@ static int launch_ws(const __nv_bfloat16* x, const __nv_bfloat16* W, const float
     if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
   }
   int ctas = (N + 15) / 16;
-  if (ctas > num_sms && ctas % num_sms != 0) {
+  if (EPI != WS_EPI_ROPE && ctas > num_sms && ctas % num_sms != 0) {
     const int even = (ctas + num_sms - 1) / num_sms * num_sms;
     if (even <= N) ctas = even;
   }
-  launch_kernel(linear_ws_kernel<NT, EPI, OUT>, ctas, WS_WARPS * 32, 0, stream, x, W, bias, (OUT*)out, residual, M, N, K);
+  launch_kernel(linear_ws_kernel<NT, EPI, OUT>, ctas, WS_WARPS * 32, 0, stream, x, W, bias, (OUT*)out, residual, M, N, K, rope);
   return launch_status("linear_ws");
 }
 
@@ -189,4 +253,32 @@ SLLM_EXPORT int sllm_linear_ws(const void* x, const void* W, const float* bias, 
   if (M <= 8) { GO(1) }
   GO(2)
 #undef GO
+}
+
+SLLM_EXPORT int sllm_linear_ws_rope_supports(int M, int N, int K, int nq, int nkv, int hd, int rot) {
+  return sllm_linear_ws_supports(M, N, K) && nq > 0 && nkv > 0 && hd >= 16 && hd % 16 == 0 && N == (nq + 2 * nkv) * hd &&
+         (rot == 0 || rot == hd);
+}
+
+// The fused q|k|v product of an attention layer with its bias, rotary encoding and cache write:
+// x [M, K] and W [(nq + 2 nkv) * hd, K] bfloat16; table null or rot == 0: no rotation, else rot == hd and
+// table [max_pos][2][hd/2] float32; slot_mapping null: keys and values are not written.
+SLLM_EXPORT int sllm_linear_ws_rope(const void* x, const void* W, const float* bias, int M, int N, int K, const int* positions,
+                                    const float* table, int rot, int max_pos, int nq, int nkv, int hd, const int* slot_mapping,
+                                    int page_size, int num_pages, void* k_cache, void* v_cache, void* q_out,
+                                    cudaStream_t stream) {
+  SLLM_REQUIRE(sllm_linear_ws_rope_supports(M, N, K, nq, nkv, hd, rot),
+               "linear_ws_rope: sizes M=%d N=%d K=%d nq=%d nkv=%d hd=%d rot=%d", M, N, K, nq, nkv, hd, rot);
+  SLLM_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)W & 15) == 0, "linear_ws_rope: operands must be 16-byte aligned");
+  SLLM_REQUIRE(q_out != nullptr && (rot == 0 || (table != nullptr && positions != nullptr && max_pos > 0)),
+               "linear_ws_rope: destination or rotary table missing");
+  SLLM_REQUIRE(slot_mapping == nullptr || (k_cache && v_cache && page_size > 0 && num_pages > 0), "linear_ws_rope: cache arguments missing");
+  WsRope r;
+  r.positions = positions; r.table = rot > 0 ? table : nullptr; r.slot_mapping = slot_mapping;
+  r.k_cache = (__nv_bfloat16*)k_cache; r.v_cache = (__nv_bfloat16*)v_cache; r.q_out = (__nv_bfloat16*)q_out;
+  r.max_pos = max_pos; r.nq = nq; r.nkv = nkv; r.hd = hd; r.page_size = page_size; r.num_pages = num_pages;
+  const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+  const __nv_bfloat16* wb = (const __nv_bfloat16*)W;
+  if (M <= 8) return launch_ws<1, WS_EPI_ROPE, __nv_bfloat16>(xb, wb, bias, nullptr, nullptr, M, N, K, stream, r);
+  return launch_ws<2, WS_EPI_ROPE, __nv_bfloat16>(xb, wb, bias, nullptr, nullptr, M, N, K, stream, r);
 }

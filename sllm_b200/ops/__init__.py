@@ -346,6 +346,41 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, o
     return silu_mul(gu, interleave, out_dtype)
 
 
+_QKV_ROPE = os.environ.get("SLLM_QKV_ROPE_FUSED", "1") != "0"     # 0: the product, then the rotary kernel
+
+
+def qkv_rope_supports(x, w, table, rotary_dim, nq, nkv, hd, k_cache) -> bool:
+    """Whether `linear_rope_kv_write` takes the product: bfloat16, few tokens, the whole head rotated
+    (or no rotation at all), a head size that is a multiple of 16."""
+    if not (_QKV_ROPE and x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16):
+        return False
+    rot = int(rotary_dim) if table is not None else 0
+    M, K = x.shape
+    return M <= WS_MAX_ROWS and bool(lib().sllm_linear_ws_rope_supports(int(M), int(w.shape[0]), int(K), int(nq), int(nkv),
+                                                                          int(hd), rot))
+
+
+def linear_rope_kv_write(x, w, bias, positions, table, rotary_dim, nq, nkv, hd, slot_mapping, k_cache, v_cache):
+    """``x @ w.T`` for the fused q|k|v matrix with what follows it in an attention layer done in the
+    product's epilogue: bias, rotary encoding of the query and key heads by the tokens' positions,
+    the new keys and values written to ``slot_mapping`` of the paged caches (not written when it is
+    None).  Returns the rotated queries ``[T, nq*hd]`` bfloat16.  Few tokens only (`qkv_rope_supports`)."""
+    _chk(x, w, bias, positions, table, slot_mapping, k_cache, v_cache)
+    M, K = x.shape
+    N = w.shape[0]
+    rot = int(rotary_dim) if table is not None else 0
+    num_pages, nkv_c, page_size, hd_c = k_cache.shape
+    if (nkv_c, hd_c) != (nkv, hd) or tuple(v_cache.shape) != tuple(k_cache.shape):
+        raise KernelError("linear_rope_kv_write: the caches are [pages, kv heads, page size, head size]")
+    if table is not None and (table.dtype != torch.float32 or tuple(table.shape[1:]) != (2, rot // 2)):
+        raise KernelError("linear_rope_kv_write: rotary table must be float32 [positions, 2, rotary_dim/2]")
+    q = torch.empty((M, nq * hd), dtype=torch.bfloat16, device=x.device)
+    max_pos = table.shape[0] if table is not None else 0
+    call("sllm_linear_ws_rope", _p(x), _p(w), _p(bias), M, N, K, _p(positions), _p(table), rot, max_pos, nq, nkv, hd,
+         _p(slot_mapping), page_size, num_pages, _p(k_cache), _p(v_cache), _p(q), _stream())
+    return q
+
+
 def rope_kv_write(qkv, bias, positions, table, rotary_dim, nq, nkv, hd, slot_mapping, k_cache, v_cache,
                   out_dtype: torch.dtype) -> torch.Tensor:
     """Bias, rotary encoding and the cache write for the fused q|k|v rows.

@@ -68,6 +68,9 @@ def _declare(L):
         "sllm_linear_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "sllm_linear_ws_supports": [c_int, c_int, c_int],
         "sllm_linear_ws": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+        "sllm_linear_ws_rope_supports": [c_int, c_int, c_int, c_int, c_int, c_int, c_int],
+        "sllm_linear_ws_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
         "sllm_linear_stream_supports": [c_int, c_int, c_int],
         "sllm_linear_stream_splits": [c_int, c_int],
         "sllm_linear_stream": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,

@@ -159,13 +159,17 @@ class Attention(Mixer):
 
     def forward(self, x, step: StepContext, cache: LayerCache, position, write_cache=True, residual=None):
         g = step.groups[cache.group]
-        qkv = self.qkv(x, torch.float32, True)                # [T, (nq+2nkv)*hd] float32, maybe in parts
-        q = ops.rope_kv_write(
-            qkv, self.qkv_b, step.positions,
-            getattr(position, "table", None),          # an encoding without a rotary table: no rotation
-            getattr(position, "rotary_dim", 0) if getattr(position, "table", None) is not None else 0,
-            self.nq, self.nkv, self.hd,
-            g.slot_mapping if write_cache else None, cache.k, cache.v, self.dtype)
+        table = getattr(position, "table", None)           # an encoding without a rotary table: no rotation
+        rot = getattr(position, "rotary_dim", 0) if table is not None else 0
+        slots = g.slot_mapping if write_cache else None
+        if ops.qkv_rope_supports(x, self.qkv.weight, table, rot, self.nq, self.nkv, self.hd, cache.k):
+            # few tokens: bias, rotation and the cache write happen as the product's rows leave their CTA
+            q = ops.linear_rope_kv_write(x, self.qkv.weight, self.qkv_b, step.positions, table, rot,
+                                         self.nq, self.nkv, self.hd, slots, cache.k, cache.v)
+        else:
+            qkv = self.qkv(x, torch.float32, True)            # [T, (nq+2nkv)*hd] float32, maybe in parts
+            q = ops.rope_kv_write(qkv, self.qkv_b, step.positions, table, rot, self.nq, self.nkv, self.hd,
+                                  slots, cache.k, cache.v, self.dtype)
         o = ops.paged_attention(q, cache.k, cache.v, step, cache.group,
                                 self.nq, self.nkv, self.hd, self.scale, self.window)
         return self.out.into(o, residual)

@@ -157,6 +157,51 @@ def test_rope_kv_write_wide_form(in_dtype, T, nq, nkv, hd, rot, ps):
     assert not k2.any() and not v2.any()
 
 
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("nq,nkv,hd,K,ps", [(28, 4, 128, 3584, 16), (14, 2, 64, 896, 64), (4, 2, 16, 64, 16), (3, 1, 32, 96, 8),
+                                            (6, 3, 48, 160, 16), (2, 2, 256, 128, 32)])
+def test_linear_rope_kv_write(M, nq, nkv, hd, K, ps):
+    """The fused q|k|v product whose epilogue adds the bias, rotates query and key heads and writes the
+    new keys and values into their pages, against the product followed by the rotary kernel's statement:
+    every head kind, head sizes from 16 to 256, rows that have no slot (padding), no bias, no rotation,
+    a borrowed cache (nothing written)."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(31)
+    N, pages, max_pos = (nq + 2 * nkv) * hd, 7, 300
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    bias = torch.randn(N, device="cuda", generator=g)
+    pos = torch.randint(0, max_pos, (M,), device="cuda", generator=g, dtype=torch.int32)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * (1e4 ** (-torch.arange(0, hd, 2, dtype=torch.float64) / hd))[None]
+    table = torch.stack([ang.cos(), ang.sin()], 1).float().cuda()
+    slots = torch.randperm(pages * ps, device="cuda", generator=g)[:M].int()
+    assert ops.qkv_rope_supports(x, w, table, hd, nq, nkv, hd, torch.zeros(1, nkv, ps, hd, device="cuda", dtype=torch.bfloat16))
+    dtype = torch.bfloat16
+    for b, tab, rot in ((bias, table, hd), (None, table, hd), (bias, None, 0)):
+        kc = [torch.zeros(pages, nkv, ps, hd, device="cuda", dtype=dtype) for _ in range(2)]
+        vc = [torch.zeros(pages, nkv, ps, hd, device="cuda", dtype=dtype) for _ in range(2)]
+        sl = slots.clone()
+        if M > 1:
+            sl[M - 1] = -1                                      # a padding row: its queries are computed, nothing is written
+        got = ops.linear_rope_kv_write(x, w, b, pos, tab, rot, nq, nkv, hd, sl, kc[0], vc[0])
+        qkv = x.float() @ w.float().t()
+        keep = sl >= 0
+        want = ref.rope_kv_write(qkv[keep], b, pos[keep], tab, rot, nq, nkv, hd, sl[keep], kc[1], vc[1], dtype)
+        _close(got[keep], want, dtype, scale=4.0)
+        _close(kc[0], kc[1], dtype, scale=4.0)
+        _close(vc[0], vc[1], dtype, scale=4.0)
+        if M > 1:
+            last = ref.rope_kv_write(qkv[M - 1:], b, pos[M - 1:], tab, rot, nq, nkv, hd, None, kc[1], vc[1], dtype)
+            _close(got[M - 1:], last, dtype, scale=4.0)
+    k2, v2 = torch.zeros_like(kc[0]), torch.zeros_like(vc[0])
+    got = ops.linear_rope_kv_write(x, w, bias, pos, table, hd, nq, nkv, hd, None, k2, v2)
+    _close(got, ref.rope_kv_write(x.float() @ w.float().t(), bias, pos, table, hd, nq, nkv, hd, None, k2, v2, dtype), dtype, scale=4.0)
+    assert not k2.any() and not v2.any()
+    # what it does not take: a rotation of part of the head, many tokens
+    assert not ops.qkv_rope_supports(x, w, table[:, :, :hd // 4].contiguous(), hd // 2, nq, nkv, hd, k2)
+    assert not ops.qkv_rope_supports(torch.zeros(40, K, device="cuda", dtype=dtype), w, table, hd, nq, nkv, hd, k2)
+
+
 def _paged_case(g, lens, q_lens, nq, nkv, hd, ps, dtype, spare_pages=3, consecutive=False):
     """Random cache content for requests of `lens` tokens whose last `q_lens` are queries; their pages
     scattered over the pool, or (`consecutive`) each request's pages with consecutive ids."""
