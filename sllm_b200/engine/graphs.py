@@ -1,6 +1,6 @@
 """CUDA graphs of the decode step.
 
-A decode step launches some ten kernels per layer; launched one by one from Python
+A decode step launches eight kernels per layer; launched one by one from Python
 they cost more host time than the device needs to run them.  The step's shape is
 fixed by the number of requests alone (one token each), so its forward and the
 sampling kernel are captured once per (batch size, context bucket) and replayed:
