@@ -13,12 +13,12 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
-import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
 from ..cache.pools import OutOfPages
-from ..parts.base import GroupView, StepContext
+from ..parts.base import StepContext
+from .batch import BatchLayout, context, pack, pages_missing
 
 
 @dataclass
@@ -30,10 +30,6 @@ class StepEntry:
 
 class ContextOverflow(ValueError):
     """A request would grow past the model's position limit."""
-
-
-def _pad4(n: int) -> int:
-    return (n + 3) & ~3
 
 
 class Engine:
@@ -109,85 +105,25 @@ class Engine:
         # all or nothing: count what every group has to give before taking any
         if new_requests > cache.slots.free_count:
             raise OutOfPages(f"{new_requests} new requests, {cache.slots.free_count} state slots free")
-        for gi, g in enumerate(cache.groups):
-            need = 0
-            for e, tot in zip(entries, totals):
-                req = cache.requests.get(e.req_id)
-                need += max(0, cache.pages_for(tot) - (len(req.tables[gi]) if req else 0))
-            if need > g.pool.free_count:
-                raise OutOfPages(f"step needs {need} pages in group {gi}, {g.pool.free_count} free "
-                                 f"of {g.pool.capacity}")
+        for gi, need in enumerate(pages_missing(cache, entries, totals)):
+            pool = cache.groups[gi].pool
+            if need > pool.free_count:
+                raise OutOfPages(f"step needs {need} pages in group {gi}, {pool.free_count} free of {pool.capacity}")
         for e, tot in zip(entries, totals):
             if e.req_id not in cache.requests:
                 cache.add_request(e.req_id)
             cache.reserve(e.req_id, tot)
 
-        # ---- host arrays, packed into one buffer, one copy --------------------------
-        S = len(entries)
+        # ---- the description: packed into one pinned buffer, one copy --------------------
         q_lens = [len(e.tokens) for e in entries]
-        T = sum(q_lens)
-        ps = cache.page_size
-        R = sum(len(e.want) for e in entries)
-        max_pages = [max(len(cache.requests[e.req_id].tables[gi]) for e in entries)
-                     for gi in range(len(cache.groups))]
-        sizes = {"token_ids": T, "positions": T, "seq_of_token": T, "q_start": S + 1, "ctx_len": S,
-                 "state_slots": S, "logit_rows": R}
-        for gi, mp in enumerate(max_pages):
-            sizes[f"slot_mapping{gi}"] = T
-            sizes[f"block_tables{gi}"] = S * mp
-        offs = {}
-        total = 0
-        for k, n in sizes.items():
-            offs[k] = total
-            total += _pad4(max(n, 1))
-        host = torch.empty(total, dtype=torch.int32, pin_memory=self._pin)
-        h = host.numpy()
-        h.fill(-1)
-
-        def sec(k):
-            return h[offs[k]: offs[k] + sizes[k]]
-
-        tok, pos, sot = sec("token_ids"), sec("positions"), sec("seq_of_token")
-        q_start, ctx_len, slots, rows = sec("q_start"), sec("ctx_len"), sec("state_slots"), sec("logit_rows")
-        t0 = 0
-        r0 = 0
-        q_start[0] = 0
-        for si, (e, tot) in enumerate(zip(entries, totals)):
-            n = q_lens[si]
-            req = cache.requests[e.req_id]
-            tok[t0:t0 + n] = np.asarray(e.tokens, dtype=np.int32)
-            pos[t0:t0 + n] = np.arange(tot - n, tot, dtype=np.int32)
-            sot[t0:t0 + n] = si
-            q_start[si + 1] = t0 + n
-            ctx_len[si] = tot
-            slots[si] = req.slot
-            for w in e.want:
-                rows[r0] = t0 + w
-                r0 += 1
-            for gi, mp in enumerate(max_pages):
-                table = np.asarray(req.tables[gi], dtype=np.int32)
-                bt = sec(f"block_tables{gi}").reshape(S, mp)
-                bt[si, :len(table)] = table
-                p = np.arange(tot - n, tot, dtype=np.int64)
-                pages = table[p // ps]
-                if (pages < 0).any():
-                    raise RuntimeError(f"request {e.req_id!r}: a token would be written to a page given back")
-                sec(f"slot_mapping{gi}")[t0:t0 + n] = (pages.astype(np.int64) * ps + p % ps).astype(np.int32)
-            t0 += n
+        layout = BatchLayout(sum(q_lens), len(entries), sum(len(e.want) for e in entries),
+                             [max(len(cache.requests[e.req_id].tables[gi]) for e in entries)
+                              for gi in range(len(cache.groups))])
+        host = torch.empty(layout.total, dtype=torch.int32, pin_memory=self._pin)
+        pack(layout, host.numpy(), cache, entries, totals)
         dev = host.to(self.device, non_blocking=True)
         self.h2d_bytes += host.numel() * host.element_size()
-
-        def dsec(k):
-            return dev[offs[k]: offs[k] + sizes[k]]
-
-        groups = [GroupView(ps, dsec(f"block_tables{gi}").view(S, mp), dsec(f"slot_mapping{gi}"))
-                  for gi, mp in enumerate(max_pages)]
-        return StepContext(
-            num_tokens=T, num_seqs=S, token_ids=dsec("token_ids"), positions=dsec("positions"),
-            seq_of_token=dsec("seq_of_token"), q_start=dsec("q_start"), ctx_len=dsec("ctx_len"),
-            state_slots=dsec("state_slots"), logit_rows=dsec("logit_rows"), groups=groups,
-            q_lens=q_lens, ctx_lens=[int(t) for t in totals], max_q_len=max(q_lens),
-            max_ctx_len=int(max(totals)))
+        return context(layout, dev, cache.page_size, q_lens, totals)
 
     def step(self, entries) -> torch.Tensor:
         """Run the entries as one batch.  Returns float32 logits ``[R, V]`` on the
@@ -217,8 +153,3 @@ class Engine:
         if self._graphs is None:
             self._graphs = DecodeGraphs(self)
         return self._graphs
-
-    def decode_graph_step(self, entries, temperatures, uniforms, device_timer=None):
-        """One decode step (every entry brings one token and wants its logits) through a graph.
-        Returns the sampled ids (int32 tensor on the host)."""
-        return self.graphs.step(list(entries), temperatures, uniforms, device_timer)

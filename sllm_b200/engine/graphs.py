@@ -26,11 +26,7 @@ import numpy as np
 import torch
 
 from .. import ops
-from ..parts.base import GroupView, StepContext
-
-
-def _pad4(n: int) -> int:
-    return (n + 3) & ~3
+from .batch import BatchLayout, context, pack, pages_missing
 
 
 class _Graph:
@@ -43,18 +39,12 @@ class _Graph:
             engine.seen_table()                      # made here, never inside a capture
         cache = engine.cache
         self.B = B
-        ps = cache.page_size
-        self.cap_pages = -(-engine.max_positions // ps)
-        G = len(cache.groups)
-        sizes = {"token_ids": B, "positions": B, "seq_of_token": B, "q_start": B + 1, "ctx_len": B,
-                 "state_slots": B, "logit_rows": B, "temps": B, "uniforms": 2 * B, "top_k": B, "top_p": B, "penalty": B}
-        for gi in range(G):
-            sizes[f"slot_mapping{gi}"] = B
-            sizes[f"block_tables{gi}"] = B * self.cap_pages
-        self.offs, total = {}, 0
-        for k, n in sizes.items():
-            self.offs[k] = (total, n)
-            total += _pad4(n)
+        cap_pages = -(-engine.max_positions // cache.page_size)
+        # the step's description (every row brings one token and wants its logits) and, behind it, what the
+        # sampling kernel reads
+        self.layout = BatchLayout(B, B, B, [cap_pages] * len(cache.groups),
+                                  extras={"temps": B, "uniforms": 2 * B, "top_k": B, "top_p": B, "penalty": B})
+        total = self.layout.total
         # two host staging buffers: a step may be filled while the copy of the one before is still queued
         pin = engine.device.type == "cuda"
         self.hosts = [torch.zeros(total, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
@@ -62,29 +52,15 @@ class _Graph:
         self.ids_ready = [torch.cuda.Event() if pin else None for _ in range(2)]
         self.turn = 0
         self.host = self.hosts[0]
-        self.h = self.host.numpy()
         self.dev = torch.zeros(total, dtype=torch.int32, device=engine.device)
-        # what never changes in a decode step
-        for hb in self.hosts:
-            self.h = hb.numpy()
-            self._hsec("seq_of_token")[:] = np.arange(B)
-            self._hsec("q_start")[:] = np.arange(B + 1)
-            self._hsec("logit_rows")[:] = np.arange(B)
-            for gi in range(G):
-                self._hsec(f"block_tables{gi}")[:] = -1
-        self.h = self.host.numpy()
-        groups = [GroupView(ps, self._dsec(f"block_tables{gi}").view(B, self.cap_pages), self._dsec(f"slot_mapping{gi}"))
-                  for gi in range(G)]
-        self.ctx = StepContext(
-            num_tokens=B, num_seqs=B, token_ids=self._dsec("token_ids"), positions=self._dsec("positions"),
-            seq_of_token=self._dsec("seq_of_token"), q_start=self._dsec("q_start"), ctx_len=self._dsec("ctx_len"),
-            state_slots=self._dsec("state_slots"), logit_rows=self._dsec("logit_rows"), groups=groups,
-            q_lens=[1] * B, ctx_lens=[bucket] * B, max_q_len=1, max_ctx_len=bucket, is_graph_replay=True)
-        self.temps = self._dsec("temps").view(torch.float32)
-        self.uniforms = self._dsec("uniforms").view(torch.float64)
-        self.top_k = self._dsec("top_k")
-        self.top_p = self._dsec("top_p").view(torch.float32)
-        self.penalty = self._dsec("penalty").view(torch.float32)
+        # launch shapes come from the bucket, not from the requests: every context up to it replays this graph
+        self.ctx = context(self.layout, self.dev, cache.page_size, [1] * B, [bucket] * B, is_graph_replay=True)
+        sec = self.layout.sec
+        self.temps = sec(self.dev, "temps").view(torch.float32)
+        self.uniforms = sec(self.dev, "uniforms").view(torch.float64)
+        self.top_k = sec(self.dev, "top_k")
+        self.top_p = sec(self.dev, "top_p").view(torch.float32)
+        self.penalty = sec(self.dev, "penalty").view(torch.float32)
         self.graph = None
         self.ids = None
         self.launches = 0
@@ -99,71 +75,36 @@ class _Graph:
             ops.penalty_from_seen_(logits, engine.seen_table(), self.ctx, self.penalty)
         self.ids = ops.sample_rows(logits, self.temps, self.uniforms, self.top_k, self.top_p)
 
-    def _hsec(self, k):
-        o, n = self.offs[k]
-        return self.h[o:o + n]
-
-    def _dsec(self, k):
-        o, n = self.offs[k]
-        return self.dev[o:o + n]
-
-    def fill(self, engine, entries, totals, temperatures, uniforms, tokens_on_device: bool = False, top_k=None, top_p=None,
+    def fill(self, engine, entries, totals, temperatures, uniforms, ids_from=None, top_k=None, top_p=None,
              penalties=None):
-        """Describe the step in the next host buffer and queue its copy to the device.  With
-        ``tokens_on_device`` the token ids are not the host's to give: they are the ids the graph's
-        previous replay sampled, copied on the device."""
+        """Describe the step in the next host buffer and queue its copy to the device.  ``ids_from``:
+        the token ids are not the host's to give; they are what the step before sampled, an int32
+        tensor on the device (one id per entry, in the entries' order), copied on the device."""
         self.turn ^= 1
         self.host = self.hosts[self.turn]
-        self.h = self.host.numpy()
-        cache = engine.cache
-        ps = cache.page_size
-        B = self.B
-        tok, pos, ctx, slots = (self._hsec(k) for k in ("token_ids", "positions", "ctx_len", "state_slots"))
+        h = self.host.numpy()
         n = len(entries)
-        for i, (e, tot) in enumerate(zip(entries, totals)):
-            req = cache.requests[e.req_id]
-            tok[i] = e.tokens[0] if not tokens_on_device else 0
-            pos[i] = tot - 1
-            ctx[i] = tot
-            slots[i] = req.slot
-            for gi in range(len(cache.groups)):
-                table = req.tables[gi]
-                bt = self._hsec(f"block_tables{gi}")
-                row = bt[i * self.cap_pages:(i + 1) * self.cap_pages]
-                m = len(table)
-                row[:m] = table
-                row[m:] = -1
-                page = table[(tot - 1) // ps]
-                if page < 0:
-                    raise RuntimeError(f"request {e.req_id!r}: a token would be written to a page given back")
-                self._hsec(f"slot_mapping{gi}")[i] = page * ps + (tot - 1) % ps
-        if n < B:                                    # padding rows: no context, nothing written, the spare state slot
-            tok[n:] = 0
-            pos[n:] = 0
-            ctx[n:] = 0
-            slots[n:] = cache.padding_slot
-            for gi in range(len(cache.groups)):
-                self._hsec(f"block_tables{gi}")[n * self.cap_pages:] = -1
-                self._hsec(f"slot_mapping{gi}")[n:] = -1
-        t_host, u_host = self._hsec("temps").view(np.float32), self._hsec("uniforms").view(np.float64)
+        pack(self.layout, h, engine.cache, entries, totals, tokens_from_host=ids_from is None)
+        sec = self.layout.sec
+        t_host, u_host = sec(h, "temps").view(np.float32), sec(h, "uniforms").view(np.float64)
         t_host[:n] = temperatures
         u_host[:n] = uniforms
         t_host[n:] = 0.0
         u_host[n:] = 0.0
-        k_host, p_host = self._hsec("top_k"), self._hsec("top_p").view(np.float32)
+        k_host, p_host = sec(h, "top_k"), sec(h, "top_p").view(np.float32)
         k_host[:] = 0                                # no filter unless the step names one
         p_host[:] = -1.0
         if top_k is not None:
             k_host[:n] = top_k
         if top_p is not None:
             p_host[:n] = top_p
-        pen_host = self._hsec("penalty").view(np.float32)
+        pen_host = sec(h, "penalty").view(np.float32)
         pen_host[:] = 1.0
         if penalties is not None:
             pen_host[:n] = penalties
         self.dev.copy_(self.host, non_blocking=True)
-        if tokens_on_device:
-            self._dsec("token_ids").copy_(self.ids)          # after the host's copy, before the replay
+        if ids_from is not None:
+            sec(self.dev, "token_ids")[:n].copy_(ids_from[:n])      # after the host's copy, before the replay
 
 
 class Launched:
@@ -198,16 +139,12 @@ class DecodeGraphs:
                     return c
             b *= 2
 
-    def step(self, entries, temperatures, uniforms, device_timer=None):
-        """Launch and read one decode step (see `launch`, `read`)."""
-        h = self.launch(entries, temperatures, uniforms, device_timer=device_timer)
-        return torch.tensor(self.read(h), dtype=torch.int32)
-
     def can_chain(self, entries, penalised: bool = False) -> bool:
         """Whether a step for these requests, one token further each, can be queued behind the
-        step in flight with its token ids taken from that step's samples on the device: the same
-        requests in the same order, a graph already captured for their number and context bucket,
-        and pages at hand."""
+        step in flight with its token ids taken from that step's samples on the device: the
+        requests are live, a graph is already captured for their number and context bucket (it
+        need not be the graph in flight: the ids are copied from that one's output), and the
+        pools hold the pages all of them need together."""
         eng, cache = self.engine, self.engine.cache
         totals = []
         for e in entries:
@@ -218,7 +155,7 @@ class DecodeGraphs:
         gr = self.graphs.get((self.batch_bucket(len(entries)), self.bucket(max(totals)), bool(penalised)))
         if gr is None or gr.graph is None:
             return False
-        return all(cache.can_reserve(e.req_id, t) for e, t in zip(entries, totals))
+        return all(need <= g.pool.free_count for need, g in zip(pages_missing(cache, entries, totals), cache.groups))
 
     def _capture(self, gr: _Graph) -> torch.Tensor:
         """Run the step that `gr`'s static buffers describe once, launch by launch, then capture the same
@@ -266,11 +203,19 @@ class DecodeGraphs:
         torch.cuda.synchronize(eng.device)
         return made
 
-    def launch(self, entries, temperatures, uniforms, device_timer=None, tokens_on_device: bool = False,
+    def launch(self, entries, temperatures, uniforms, device_timer=None, after: Launched | None = None,
                top_k=None, top_p=None, penalties=None) -> Launched:
         """Queue one decode step: reserve pages, describe the batch, replay the graph, queue the copy
         of the sampled ids to pinned host memory.  Does not wait for the device, except the first
-        time a (batch size, context bucket) is seen: that step runs eagerly and is then captured."""
+        time a (batch size, context bucket) is seen: that step runs eagerly and is then captured.
+
+        ``after``: the step in flight for the same requests in the same order.  The new step's token
+        ids are then the ids THAT step sampled, copied on the device from the output buffer of the
+        graph it ran on (which is another graph than this step's when the longest context has just
+        crossed a bucket), and the entries' own tokens are not looked at."""
+        tokens_on_device = after is not None
+        if tokens_on_device and after.n != len(entries):
+            raise ValueError("a chained step serves the requests of the step in flight, in their order")
         eng = self.engine
         cache = eng.cache
         totals = []
@@ -288,9 +233,7 @@ class DecodeGraphs:
                 raise ValueError(f"request {e.req_id!r}: token id {e.tokens[0]} is outside the vocabulary")
             totals.append(tot)
         # pages: all or nothing
-        for gi, g in enumerate(cache.groups):
-            need = sum(max(0, cache.pages_for(t) - len(cache.requests[e.req_id].tables[gi]))
-                       for e, t in zip(entries, totals))
+        for gi, (need, g) in enumerate(zip(pages_missing(cache, entries, totals), cache.groups)):
             if need > g.pool.free_count:
                 from ..cache.pools import OutOfPages
                 raise OutOfPages(f"step needs {need} pages in group {gi}, {g.pool.free_count} free")
@@ -302,7 +245,8 @@ class DecodeGraphs:
             gr = self.graphs[key] = _Graph(eng, *key)
         if tokens_on_device and gr.graph is None:
             raise RuntimeError("a chained step needs a captured graph (see can_chain)")
-        gr.fill(eng, entries, totals, temperatures, uniforms, tokens_on_device, top_k, top_p, penalties)
+        gr.fill(eng, entries, totals, temperatures, uniforms, after.graph.ids if tokens_on_device else None, top_k, top_p,
+                penalties)
         eng.h2d_bytes += gr.host.numel() * gr.host.element_size()
         eng.d2h_bytes += gr.ids_host[0].numel() * gr.ids_host[0].element_size()
         if device_timer is not None:

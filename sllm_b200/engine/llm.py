@@ -154,17 +154,19 @@ class LLM:
                                                penalties=penalties)
             self._inflight = (plan, handle)
         plan, handle = self._inflight
-        self._inflight = self._chain(plan, device_timer)
+        self._inflight = self._chain(plan, handle, device_timer)
         ids = self.engine.graphs.read(handle)
         sampled = {p.req.req_id: int(t) for p, t in zip(plan, ids) if p.req.status == "running"}
         finished = sched.update(plan, sampled)
         self.steps += 1
         return finished, sampled
 
-    def _chain(self, plan, device_timer):
-        """Queue the decode step after ``plan``'s behind it, if nothing can change who runs: no
-        request waits for admission, none of the plan's requests ends by length with this token,
-        and the graph and the pages are there.  Returns (next plan, handle) or None."""
+    def _chain(self, plan, handle, device_timer):
+        """Queue the decode step after ``plan``'s (in flight as ``handle``) behind it, if nothing can
+        change who runs: no request waits for admission, none of the plan's requests ends by length
+        with this token, and the graph and the pages are there.  The queued step consumes the ids
+        ``handle``'s step samples (serving/executor.py:378-393: every decode step is fed the token
+        the one before produced).  Returns (next plan, handle) or None."""
         sched = self.scheduler
         if not self.pipeline_decode or sched.waiting or len(plan) != len(sched.running):
             return None
@@ -179,11 +181,11 @@ class LLM:
             return None
         rows = [(p.req.params, p.req.rng, None) for p in plan]
         temps, unis, top_k, top_p = self.sampler.host_inputs(rows)
-        handle = self.engine.graphs.launch(entries, temps, unis, device_timer=device_timer, tokens_on_device=True,
+        queued = self.engine.graphs.launch(entries, temps, unis, device_timer=device_timer, after=handle,
                                            top_k=top_k, top_p=top_p, penalties=penalties)
         from .scheduler import Planned
         nxt = [Planned(p.req, p.start + 1, 1, True) for p in plan]
-        return nxt, handle
+        return nxt, queued
 
     def drain(self) -> None:
         """Wait for a decode step still queued on the device and drop its result (its requests

@@ -342,6 +342,38 @@ def test_pipelined_decode_equals_unpipelined(tiny):
     assert outs[0][2][0] == plain.generate(prompts[2], 11, w, cfg, temperature=0.7, seed=3)
 
 
+def test_chained_decode_steps_across_a_context_bucket(tmp_path):
+    """A decode step queued behind the one in flight takes its token ids from the graph THAT step ran
+    on.  When the longest context crosses a bucket of the graphs (256, 512, ...) the two steps run on
+    different graphs; with every graph captured ahead (`warmup`) or left from an earlier call, the new
+    graph's own output buffer holds stale ids.  Prompts of 250, 251 and 509 tokens decode across 256 and
+    512 with the graphs warmed up, greedy and sampled, twice on one `LLM`: the tokens are the plain
+    implementation's (serving/executor.py:378-393: each decode step consumes the token the step before
+    produced)."""
+    from sllm_b200.engine.llm import LLM
+    from sllm_b200.sampling import SamplingParams
+    dev = cuda_or_skip()
+    config, init, page = TINY["B"]
+    model_dir = make_model_dir(tmp_path, config, init, max_position_embeddings=1024)
+    cfg, w = plain.load_model(model_dir)
+    llm = LLM(model_dir, dtype="float32", device=dev, block_size=page, num_pages=3 * 1024 // page, max_num_seqs=3,
+              chunk_size=128, max_batch_tokens=640, pipeline_decode=True)
+    assert llm.warmup() >= 9                        # 1..3 requests x buckets 256, 512, 1024
+    prompts = _prompts(cfg, (250, 251, 509), seed=41)
+    for round_ in range(2):
+        for kw in (dict(), dict(temperature=0.8, seed=7)):
+            want = [plain.generate(p, 12, w, cfg, **kw) for p in prompts]
+            # the two short ones together cross 256; the long one alone and all three together cross 512
+            for group in ((0, 1), (2,), (0, 1, 2)):
+                res = llm.generate([prompts[i] for i in group], SamplingParams(max_new=12, **kw))
+                for i, r in zip(group, res):
+                    assert r.ids == want[i], (round_, kw, group, i)
+    llm.engine.cache.check()
+    assert not llm.engine.cache.requests and llm._inflight is None
+    buckets = {k[1] for k, g in llm.engine.graphs.graphs.items() if g.turn or g.graph is not None}
+    assert {256, 512, 1024} <= buckets
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_decode_graphs_pad_the_batch_to_a_captured_size(tiny, dtype):
     """Five and seven live requests run on the graphs of six and eight rows: the padding rows write

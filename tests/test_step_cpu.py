@@ -102,3 +102,67 @@ def test_generate_on_cpu_matches_plain(tiny, cpu_ops):
             assert r.ids == plain.generate(p, 6, w, cfg, temperature=0.8, seed=7)
         llm.engine.cache.check()
         assert not llm.engine.cache.requests
+
+
+def test_one_packer_describes_both_kinds_of_step(tiny, cpu_ops):
+    """A step launched kernel by kernel and a step replayed from a graph are described by the same
+    packer: the live rows agree field by field, and the rows that pad a graph's batch have no context,
+    no page to write to and the spare state slot."""
+    from sllm_b200.engine.batch import BatchLayout, pack
+    name, model_dir, page = tiny
+    cfg, _ = plain.load_model(model_dir)
+    eng = _engine(model_dir, page)
+    reqs = _requests(cfg, (page + 3, 2 * page, 5), 3)
+    eng.step([StepEntry(k, v, []) for k, v in reqs.items()])
+    entries = [StepEntry(k, [7 + i], [0]) for i, k in enumerate(reqs)]
+    totals = [len(v) + 1 for v in reqs.values()]
+    for e, t in zip(entries, totals):
+        eng.cache.reserve(e.req_id, t)
+    G = len(eng.cache.groups)
+    exact = BatchLayout(3, 3, 3, [3] * G)
+    padded = BatchLayout(6, 6, 6, [9] * G, extras={"temps": 6})
+    a = np.full(exact.total, 99, np.int32)
+    b = np.full(padded.total, 99, np.int32)
+    pack(exact, a, eng.cache, entries, totals)
+    pack(padded, b, eng.cache, entries, totals)
+    for key in BatchLayout.FIELDS + tuple(f"slot_mapping{g}" for g in range(G)):
+        n = len(exact.sec(a, key))
+        np.testing.assert_array_equal(exact.sec(a, key), padded.sec(b, key)[:n], err_msg=key)
+    for g in range(G):
+        np.testing.assert_array_equal(exact.sec(a, f"block_tables{g}").reshape(3, 3),
+                                      padded.sec(b, f"block_tables{g}").reshape(6, 9)[:3, :3])
+        assert (padded.sec(b, f"block_tables{g}").reshape(6, 9)[3:] == -1).all()
+        assert (padded.sec(b, f"slot_mapping{g}")[3:] == -1).all()
+    assert padded.sec(b, "ctx_len")[3:].tolist() == [0, 0, 0]
+    assert padded.sec(b, "state_slots")[3:].tolist() == [eng.cache.padding_slot] * 3
+    assert padded.sec(b, "q_start").tolist() == list(range(7))
+    assert padded.sec(b, "logit_rows").tolist() == list(range(6))
+    assert (padded.sec(b, "temps") == 99).all()                 # a caller's own section is left alone
+    # token ids that come from the device are left for the caller
+    pack(padded, b, eng.cache, entries, totals, tokens_from_host=False)
+    assert padded.sec(b, "token_ids").tolist() == [0] * 6
+    with pytest.raises(ValueError):
+        pack(BatchLayout(4, 3, 3, [3] * G), a.copy(), eng.cache, entries, totals)
+
+
+def test_a_step_is_chained_only_if_the_pages_of_all_its_requests_are_there(tiny, cpu_ops):
+    """Two requests reach a page's edge in the same step and one page is free: each alone could take
+    it, both cannot.  The step must not be queued behind the one in flight (the scheduler, which can
+    preempt, decides instead)."""
+    from types import SimpleNamespace
+    name, model_dir, page = tiny
+    cfg, _ = plain.load_model(model_dir)
+    eng = _engine(model_dir, page, num_pages=3, max_requests=2)
+    reqs = _requests(cfg, (page, page), 4)
+    eng.step([StepEntry(k, v, []) for k, v in reqs.items()])
+    assert eng.cache.groups[0].pool.free_count == 1
+    graphs = eng.graphs
+    entries = [StepEntry(k, [0], [0]) for k in reqs]
+    key = (graphs.batch_bucket(2), graphs.bucket(page + 1), False)
+    graphs.graphs[key] = SimpleNamespace(graph=object())        # as if captured
+    assert all(eng.cache.can_reserve(e.req_id, page + 1) for e in entries)
+    assert not graphs.can_chain(entries)
+    assert graphs.can_chain(entries[:1]) is False               # no graph of one row
+    graphs.graphs[(1, key[1], False)] = SimpleNamespace(graph=object())
+    assert graphs.can_chain(entries[:1])
+    eng.cache.check()
