@@ -122,11 +122,14 @@ def random_weights(cfg: dict, seed: int, std: float, share_layers: bool, say):
     return w
 
 
-def run(cfg: dict, *, batch: int, context: int, steps: int, warmup: int, std: float = 0.02, seed: int = 0,
-        time_limit_s: float = 1500.0, say=lambda m: print(f"[reference arm] {m}", file=sys.stderr, flush=True)) -> dict:
-    """Time ``steps`` decode steps of ``batch`` sequences whose contexts end at ``context``, after
-    ``warmup`` untimed ones, through the reference's device-resident path in bfloat16.  Returns the fields
-    of the benchmark's record that are measured here.  Raises `Unavailable` with the reason."""
+def run(cfg: dict, *, batch: int, context: int, steps: int, warmup: int, repeats: int = 1, std: float = 0.02, seed: int = 0,
+        time_limit_s: float = 1500.0, clock_sampler=None,
+        say=lambda m: print(f"[reference arm] {m}", file=sys.stderr, flush=True)) -> dict:
+    """Time ``steps`` decode steps of ``batch`` sequences, ``repeats`` times in a row after ``warmup`` untimed
+    steps, the last region's contexts ending at ``context``, through the reference's device-resident path in
+    bfloat16; the median region is the result (fewer regions are run if the time at hand ends first).
+    ``clock_sampler``: an object with ``start()`` and ``stop()`` that samples the GPU's clocks meanwhile.
+    Returns the fields of the benchmark's record that are measured here.  Raises `Unavailable` with the reason."""
     import numpy as np
     t_start = time.perf_counter()
     tree = ensure_library(find_tree(), say)
@@ -159,7 +162,7 @@ def run(cfg: dict, *, batch: int, context: int, steps: int, warmup: int, std: fl
 
     # the prompt: long enough that the timed steps end at `context`; shortened only if the numpy prefill
     # would not fit the time this arm has (estimated from a short one)
-    prompt_len = context - (steps + warmup)
+    prompt_len = context - (warmup + repeats * steps)
     rng = np.random.default_rng(seed + 1)
     probe_len = min(128, prompt_len)
     t0 = time.perf_counter()
@@ -210,11 +213,20 @@ def run(cfg: dict, *, batch: int, context: int, steps: int, warmup: int, std: fl
             one_step()
         agree = {"max_abs_diff_vs_numpy": float(np.max(np.abs(got - want))), "same_argmax": bool(np.argmax(got) == np.argmax(want))}
         ck.sync()
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            one_step()
-        ck.sync()
-        wall = time.perf_counter() - t0
+        if clock_sampler is not None:
+            clock_sampler.start()
+        walls = []
+        for r in range(repeats):
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                one_step()
+            ck.sync()
+            walls.append(time.perf_counter() - t0)
+            if time.perf_counter() - t_start + 1.5 * walls[-1] + 30.0 > time_limit_s:
+                say(f"time at hand ends: {len(walls)} of {repeats} regions timed")
+                break
+        clocks = clock_sampler.stop() if clock_sampler is not None else None
+        wall = sorted(walls)[len(walls) // 2]
         # batch 1 on the same table: the first sequence alone
         b1_steps = max(4, steps // 2)
         solo = states[0]
@@ -236,6 +248,7 @@ def run(cfg: dict, *, batch: int, context: int, steps: int, warmup: int, std: fl
     d2h = batch * (V * 4 + 2 * L * nk * 4)
     return {
         "ms_per_step": wall * 1e3 / steps, "tok_s": batch * steps / wall, "prompt_len": prompt_len, "shortened": shortened,
+        "ms_min": min(walls) * 1e3 / steps, "ms_max": max(walls) * 1e3 / steps, "repeats": len(walls), "clocks": clocks,
         "h2d": h2d, "d2h": d2h, "decode_b1": b1_steps / wall_b1, "agree": agree,
         "prefill": {"value": round(prompt_len / t_prefill, 1), "tokens": prompt_len, "ms": round(t_prefill * 1e3, 1),
                     "where": "host numpy (the reference has no device prefill)"},

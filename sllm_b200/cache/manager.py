@@ -38,10 +38,13 @@ class RequestCache:
 
 
 class CacheManager:
-    def __init__(self, needs, *, page_size: int, num_pages, max_requests: int):
+    def __init__(self, needs, *, page_size: int, num_pages, max_requests: int, poison_freed: bool = False):
         """``needs``: per run ``("own", PagedKV|SlotState|None)`` or ``("borrow", run)``
         (`CausalLM.cache_needs`).  ``num_pages``: pages per group (an int for all
-        groups, or one per group)."""
+        groups, or one per group).  ``poison_freed`` (a debugging aid, off by default): a page
+        that goes back to its pool is filled with NaN in every layer and zeroed again when it is
+        handed out, so that a read of a page the reader no longer holds shows in the logits."""
+        self.poison_freed = bool(poison_freed)
         if page_size < 1:
             raise ValueError("page_size must be >= 1")
         self.page_size = int(page_size)
@@ -147,6 +150,8 @@ class CacheManager:
             self.reuse_count += sum(1 for p in ids if p in self._ever_used[gi])
             self._ever_used[gi].update(ids)
             req.tables[gi].extend(ids)
+            if self.poison_freed:
+                self._fill_pages(gi, ids, 0.0)
 
     def commit(self, req_id, total_tokens: int) -> None:
         """``total_tokens`` of the request now lie in the cache.  Pages that a
@@ -165,6 +170,8 @@ class CacheManager:
             gone = [table[i] for i in range(min(first, len(table))) if table[i] >= 0]
             if gone:
                 g.pool.free(req_id, gone)
+                if self.poison_freed:
+                    self._fill_pages(gi, gone, float("nan"))
                 for i in range(min(first, len(table))):
                     table[i] = -1
 
@@ -174,9 +181,19 @@ class CacheManager:
             raise KeyError(f"request {req_id!r} is not live")
         # free before forgetting: an ownership error must not lose the table
         for gi, g in enumerate(self.groups):
-            g.pool.free(req_id, [p for p in req.tables[gi] if p >= 0])
+            held = [p for p in req.tables[gi] if p >= 0]
+            g.pool.free(req_id, held)
+            if self.poison_freed:
+                self._fill_pages(gi, held, float("nan"))
         self.slots.free(req_id, req.slot)
         del self.requests[req_id]
+
+    def _fill_pages(self, group: int, pages, value: float) -> None:
+        """Keys and values of ``pages`` in every run of the group (nothing before `allocate_storage`)."""
+        if pages and group < len(self.kv_storage):
+            import torch
+            idx = torch.as_tensor(list(pages), dtype=torch.long, device=self.kv_storage[group].device)
+            self.kv_storage[group].index_fill_(2, idx, value)
 
     def slot_of_token(self, req_id, group: int, position: int) -> int:
         """Flat slot (page * page_size + offset) of a token position."""
@@ -205,13 +222,36 @@ class CacheManager:
         (runtime/memory_planner.py:12-15)."""
         return sum(len(g.runs) * 2 * g.need.num_kv_heads * g.need.head_dim * itemsize for g in self.groups)
 
+    def state_bytes_per_request(self) -> int:
+        """Bytes of fixed-size float32 state each request holds in the mixers' slots (tables that others
+        register with `register_slot_table` are theirs to count)."""
+        total = 0
+        for s in self.state_runs.values():
+            n = 4
+            for d in s.shape:
+                n *= int(d)
+            total += n
+        return total
+
+    def describe(self) -> list[str]:
+        """One line per cache group and one for the state slots: what the model asks of the cache."""
+        lines = []
+        for gi, g in enumerate(self.groups):
+            w = "all keys" if g.need.window is None else f"a window of {g.need.window}"
+            lines.append(f"group {gi}: {len(g.runs)} runs x {g.need.num_kv_heads} kv heads of {g.need.head_dim}, {w}")
+        if self.state_runs:
+            lines.append(f"state slots: {len(self.state_runs)} runs, {self.state_bytes_per_request()} bytes per request")
+        return lines
+
     def allocate_storage(self, dtype, device) -> list[LayerCache]:
         """Create the page and state tensors; returns one `LayerCache` per run."""
         import torch
         self.kv_storage = []
         for g in self.groups:
             shape = (len(g.runs), 2, max(g.pool.capacity, 1), g.need.num_kv_heads, self.page_size, g.need.head_dim)
-            self.kv_storage.append(torch.zeros(shape, dtype=dtype, device=device))
+            # with the debugging aid on, pages nobody holds are NaN from the start
+            fill = float("nan") if self.poison_freed else 0.0
+            self.kv_storage.append(torch.full(shape, fill, dtype=dtype, device=device))
         self.state_storage = {
             run: torch.zeros((self.max_requests + 1,) + tuple(s.shape), dtype=torch.float32, device=device)
             for run, s in self.state_runs.items()}

@@ -2,12 +2,14 @@
 
 A subset of the reference's recipe schema (recipes/schema.py:298-469;
 recipes/Qwen2.5-Coder-0.5B.yaml): ``model_id``, ``arch``, ``dtype``,
-``paths.local_dir``, ``memory.kv_utilization``, ``defaults`` (``max_new``,
-``max_num_seqs``, ``max_model_len``, ``block_size``, ``chunk_size``).  The model's
-geometry is read from the folder's config.json; a recipe may carry it inline under
-``text`` (the reference's key names) for the random-weights mode, where no folder
-exists yet.  Precedence of settings: command line > recipe ``defaults`` >
-built-in (serving/main.py:287-308).
+``paths.local_dir``, ``memory.kv_utilization`` and ``memory.kv_device_bytes``
+(recipes/schema.py:236-277), ``defaults`` (``max_new``, ``max_num_seqs``,
+``max_model_len``, ``block_size``, ``chunk_size``).  ``arch`` is any name or alias the
+architecture registry knows; nothing here names one.  The model's geometry is read from
+the folder's config.json; a recipe may carry it inline under ``text`` for the
+random-weights mode, where no folder exists yet: the architecture itself turns that
+mapping into config.json keys (`Architecture.config_from_recipe`).  Precedence of
+settings: command line > recipe ``defaults`` > built-in (serving/main.py:287-308).
 """
 
 from __future__ import annotations
@@ -17,7 +19,6 @@ from dataclasses import dataclass, field
 
 from .errors import ConfigError
 
-KNOWN_ARCHS = ("qwen2",)
 KNOWN_DTYPES = ("bfloat16", "float32")
 
 
@@ -29,6 +30,7 @@ class Recipe:
     dtype: str
     local_dir: str | None
     kv_utilization: float
+    kv_device_bytes: int | None = None     # the cache's budget in bytes (None: what the device has left, times the utilisation)
     defaults: dict = field(default_factory=dict)
     text: dict | None = None
     path: str | None = None
@@ -44,8 +46,13 @@ class Recipe:
             return raw[key]
 
         arch = str(need("arch"))
-        if arch not in KNOWN_ARCHS:
-            raise ConfigError(f"recipe: arch {arch!r} is not served by this engine; known: {list(KNOWN_ARCHS)}")
+        from .. import models  # noqa: F401  (the architectures this package ships register themselves)
+        from .registry import get_architecture, known_architectures
+        try:
+            get_architecture(arch)
+        except ConfigError:
+            raise ConfigError(f"recipe: arch {arch!r} is not served by this engine; known: {known_architectures()} "
+                              f"and their aliases") from None
         dtype = str(raw.get("dtype", "bfloat16"))
         if dtype not in KNOWN_DTYPES:
             raise ConfigError(f"recipe: dtype {dtype!r}; known: {list(KNOWN_DTYPES)}")
@@ -56,6 +63,11 @@ class Recipe:
         util = float(mem.get("kv_utilization", (raw.get("defaults") or {}).get("kv_utilization", 0.9)))
         if not 0.0 < util <= 1.0:
             raise ConfigError("recipe: memory.kv_utilization must lie in (0, 1]")
+        if mem.get("kv_placement", "device") != "device":
+            raise ConfigError(f"recipe: memory.kv_placement={mem['kv_placement']!r}; this engine keeps the cache on the device")
+        kv_bytes = mem.get("kv_device_bytes")
+        if kv_bytes is not None and (isinstance(kv_bytes, bool) or not isinstance(kv_bytes, int) or kv_bytes < 1):
+            raise ConfigError(f"recipe: memory.kv_device_bytes must be a positive integer, got {kv_bytes!r}")
         local = (raw.get("paths") or {}).get("local_dir")
         defaults = dict(raw.get("defaults") or {})
         for k in ("max_new", "max_num_seqs", "max_model_len", "block_size", "chunk_size"):
@@ -66,7 +78,7 @@ class Recipe:
             raise ConfigError("recipe: text must be a mapping")
         return cls(name=str(raw.get("name") or need("model_id")), model_id=str(need("model_id")), arch=arch,
                    dtype=dtype, local_dir=os.path.expanduser(local) if local else None, kv_utilization=util,
-                   defaults=defaults, text=text, path=path)
+                   kv_device_bytes=kv_bytes, defaults=defaults, text=text, path=path)
 
     @classmethod
     def from_yaml(cls, path: str) -> "Recipe":
@@ -80,29 +92,22 @@ class Recipe:
             raise ConfigError(f"recipe {path}: not valid YAML ({e})") from None
         return cls.from_dict(raw, path)
 
+    def architecture(self):
+        from .registry import get_architecture
+        return get_architecture(self.arch)
+
     def config_json(self) -> dict:
-        """config.json keys from the inline geometry (the reference's ``text`` keys:
-        recipes/schema.py:357-431, 128-133, 86, 159-161)."""
-        t = self.text
-        if not t:
+        """config.json keys from the inline geometry under ``text``, as the recipe's architecture reads it."""
+        if not self.text:
             raise ConfigError(f"recipe {self.name}: no inline geometry under 'text'")
+        arch = self.architecture()
+        if arch.config_from_recipe is None:
+            raise ConfigError(f"recipe {self.name}: architecture {arch.name!r} reads no inline geometry; give a model folder")
         try:
-            fa, mlp = t["full_attention"], t["mlp"]
-            cfg = {
-                "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
-                "hidden_size": t["hidden_size"], "num_hidden_layers": t["num_layers"],
-                "num_attention_heads": fa["num_heads"], "num_key_value_heads": fa["num_kv_heads"],
-                "intermediate_size": mlp["intermediate_size"], "hidden_act": mlp.get("hidden_act", "silu"),
-                "vocab_size": t["vocab_size"], "max_position_embeddings": t["max_position_embeddings"],
-                "rms_norm_eps": float(t.get("rms_norm_eps", 1e-6)),
-                "rope_theta": float(fa["rope"]["theta"]),
-                "partial_rotary_factor": float(fa["rope"].get("partial_rotary_factor", 1.0)),
-                "tie_word_embeddings": bool(t.get("tie_word_embeddings", False)),
-            }
-            if "head_dim" in fa:
-                cfg["head_dim"] = fa["head_dim"]
+            cfg = dict(arch.config_from_recipe(self.text))
         except KeyError as e:
             raise ConfigError(f"recipe {self.name}: inline geometry lacks key {e.args[0]!r}") from None
+        cfg.setdefault("architectures", [arch.name])
         return cfg
 
 

@@ -24,7 +24,10 @@ class Architecture:
     config_cls: type                       # has classmethod from_dict(dict)
     plan: Callable[[object], ModelPlan]    # typed config -> plan
     random_init: Callable | None = None    # (config, plan) -> per-tensor init rules; None: defaults
-    aliases: tuple[str, ...] = ()
+    aliases: tuple[str, ...] = ()          # short names a recipe's ``arch:`` may use
+    # a recipe's inline geometry (its ``text`` mapping) -> config.json keys, for the random-weights mode
+    # where no model folder exists yet; None: the architecture cannot be described inline
+    config_from_recipe: Callable[[dict], dict] | None = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}

@@ -23,6 +23,19 @@ bool pdl_enabled() {
   return on;
 }
 
+int num_sms() {
+  // per device: a process may hold models on several
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 // ---------------------------------------------------------------------------
 // out[t, :] = float(table[ids[t], :])      (kernels/cuda/kernels.cu:770-787 does one row)
 // ---------------------------------------------------------------------------
@@ -358,6 +371,9 @@ __global__ void rope_kv_write_vec_kernel(const TI* __restrict__ qkv, const float
 using namespace sllm;
 
 SLLM_EXPORT const char* sllm_last_error() { return g_error; }
+
+// streaming multiprocessors of the current device: the dispatch sizes its splits for them
+SLLM_EXPORT int sllm_num_sms() { return sllm::num_sms(); }
 
 SLLM_EXPORT int sllm_embed_gather(const void* table, int table_dtype, const int* ids, float* out, int T, int H,
                                   int V, cudaStream_t stream) {

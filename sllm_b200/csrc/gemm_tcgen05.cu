@@ -233,12 +233,7 @@ static int launch_tg(const CUtensorMap& ma, const CUtensorMap& mw, const float* 
     }
     configured = true;
   }
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
-  }
+  const int num_sms = sllm::num_sms();
   const long long tiles = (long long)((M + TG_BM - 1) / TG_BM) * ((N + TG_BN - 1) / TG_BN);
   dim3 grid((unsigned)(tiles < num_sms ? tiles : num_sms));      // persistent: one CTA per SM walks the tiles
   launch_kernel(gemm_tcgen05_kernel<EPI>, grid, 192, TG_SMEM, stream, ma, mw, bias, out, M, N, K, status);

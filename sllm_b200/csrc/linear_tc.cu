@@ -235,15 +235,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 
 // ---- host side --------------------------------------------------------------------------------
 
-static int lt_num_sms() {
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
-  }
-  return num_sms;
-}
+static int lt_num_sms() { return sllm::num_sms(); }
 
 template <int BN, int EPI>
 static int launch_lt(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* out, int M, int N, int K,

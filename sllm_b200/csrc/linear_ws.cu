@@ -214,12 +214,7 @@ template <int NT, int EPI, typename OUT>
 static int launch_ws(const __nv_bfloat16* x, const __nv_bfloat16* W, const float* bias, void* out, float* residual,
                      int M, int N, int K, cudaStream_t stream, const WsRope& rope = WsRope{}) {
   // CTAs of 16 rows, or, when those would fill the SMs unevenly, the next multiple of the SM count
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
-  }
+  const int num_sms = sllm::num_sms();
   int ctas = (N + 15) / 16;
   if (EPI != WS_EPI_ROPE && ctas > num_sms && ctas % num_sms != 0) {
     const int even = (ctas + num_sms - 1) / num_sms * num_sms;

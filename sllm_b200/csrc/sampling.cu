@@ -1003,7 +1003,7 @@ SLLM_EXPORT int sllm_penalty_seen(float* logits, int R, int V, const unsigned ch
                                   const int* seq_of_token, const int* state_slots, const float* penalty, cudaStream_t stream) {
   SLLM_REQUIRE(R >= 0 && V > 0 && slots > 0, "penalty_seen: bad sizes R=%d V=%d slots=%d", R, V, slots);
   if (R == 0) return SLLM_OK;
-  const int bx = (V + 1023) / 1024 < 148 ? (V + 1023) / 1024 : 148;
+  const int sms = num_sms(), bx = (V + 1023) / 1024 < sms ? (V + 1023) / 1024 : sms;
   launch_kernel(penalty_seen_kernel, dim3(bx, R), 256, 0, stream, logits, V, seen, logit_rows, seq_of_token, state_slots, penalty, slots);
   return launch_status("penalty_seen");
 }

@@ -11,6 +11,7 @@ replay all go through `Engine.step`.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 
 import torch
@@ -34,11 +35,15 @@ class ContextOverflow(ValueError):
 
 class Engine:
     def __init__(self, model, *, page_size: int = 16, num_pages: int, max_requests: int = 8,
-                 max_model_len: int | None = None):
+                 max_model_len: int | None = None, poison_freed: bool | None = None):
+        """``poison_freed``: the cache manager's debugging aid (pages that go back to the pool are filled
+        with NaN); None reads ``SLLM_POISON_FREED_PAGES=1`` from the environment."""
         self.model = model
         self.device = model.device
+        if poison_freed is None:
+            poison_freed = os.environ.get("SLLM_POISON_FREED_PAGES", "0") == "1"
         self.cache = CacheManager(model.cache_needs(), page_size=page_size, num_pages=num_pages,
-                                  max_requests=max_requests)
+                                  max_requests=max_requests, poison_freed=poison_freed)
         self.layer_caches = self.cache.allocate_storage(model.dtype, self.device)
         self.vocab_size = model.plan.vocab_size
         self.max_positions = min(max_model_len or model.plan.max_positions, model.plan.max_positions)

@@ -14,21 +14,28 @@ from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS,
                           LayerCache, StepContext, TensorSpec)
 
 
+FAMILIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS}
+
+
 class Layer:
+    """The parts a `LayerSpec` names, built, and the block that arranges them.  The block receives
+    them by role and says what the layer wants of the cache manager."""
+
     def __init__(self, spec, *, dtype, device):
         self.spec = spec
-        kw = dict(dtype=dtype, device=device)
-        self.mixer = MIXERS.build(spec.mixer, **kw)
-        self.ffn = FEED_FORWARDS.build(spec.ffn, **kw)
-        self.mixer_norm = NORMS.build(spec.norm, **kw)
-        self.ffn_norm = NORMS.build(spec.norm, **kw)
-        self.block = BLOCKS.get(spec.block)(self.mixer, self.ffn, self.mixer_norm, self.ffn_norm)
+        self.parts = {role: FAMILIES[e.family].build(e.spec, dtype=dtype, device=device) for role, e in spec.parts.items()}
+        self.block = BLOCKS.get(spec.block)(self.parts)
+
+    @property
+    def mixer(self):
+        return self.parts.get("mixer")
+
+    def cache_need(self):
+        return self.block.cache_need()
 
     def named_parts(self):
         s = self.spec
-        return [(f"{s.prefix}.{s.mixer_prefix}", self.mixer), (f"{s.prefix}.{s.ffn_prefix}", self.ffn),
-                (f"{s.prefix}.{s.mixer_norm_name}", self.mixer_norm),
-                (f"{s.prefix}.{s.ffn_norm_name}", self.ffn_norm)]
+        return [(f"{s.prefix}.{e.name}" if e.name else s.prefix, self.parts[role]) for role, e in s.parts.items()]
 
 
 class CausalLM:
@@ -66,10 +73,8 @@ class CausalLM:
         return specs
 
     def ignored_tensor_names(self):
-        """A tied model may still carry a copy of the head; it is not used
-        (the reference takes the embedding whenever the flag is set,
-        kernels/device_decode.py:127-128)."""
-        return ["lm_head.weight"] if self.plan.head_name is None else []
+        """Tensors a checkpoint may carry that this model does not use (the plan names them)."""
+        return list(self.plan.ignored_names)
 
     def bind(self, fetch) -> None:
         p = self.plan
@@ -99,7 +104,7 @@ class CausalLM:
             if e.cache_from is not None:
                 out.append(("borrow", e.cache_from))
             else:
-                out.append(("own", self.layers[e.layer].mixer.cache_need()))
+                out.append(("own", self.layers[e.layer].cache_need()))
         return out
 
     # ---- forward ------------------------------------------------------------------

@@ -17,7 +17,7 @@ from dataclasses import dataclass
 
 from ..config.errors import ConfigError
 from ..config.fields import get_bool, get_float, get_int, get_str
-from ..config.plan import LayerSpec, ModelPlan, PartSpec, RunEntry
+from ..config.plan import ModelPlan, PartSpec, RunEntry, pre_norm_layer
 from ..config.registry import Architecture, register_architecture
 
 NAME = "Qwen2ForCausalLM"
@@ -120,7 +120,7 @@ def plan(cfg: Qwen2Config) -> ModelPlan:
     ffn = PartSpec("swiglu", {"hidden_size": cfg.hidden_size,
                               "intermediate_size": cfg.intermediate_size})
     layers = tuple(
-        LayerSpec(prefix=f"model.layers.{i}", mixer=mixer, ffn=ffn, norm=norm)
+        pre_norm_layer(f"model.layers.{i}", mixer, ffn, norm)
         for i in range(cfg.num_hidden_layers))
     p = ModelPlan(
         architecture=cfg.architecture,
@@ -134,10 +134,36 @@ def plan(cfg: Qwen2Config) -> ModelPlan:
         final_norm_name="model.norm",
         head_name=None if cfg.tie_word_embeddings else "lm_head.weight",
         position=position,
+        # a tied model may still carry a copy of the head; the embedding is used whenever the flag is set
+        # (kernels/device_decode.py:127-128)
+        ignored_names=("lm_head.weight",) if cfg.tie_word_embeddings else (),
     )
     p.validate()
     return p
 
 
-register_architecture(Architecture(name=NAME, config_cls=Qwen2Config, plan=plan,
-                                   aliases=("qwen2",)), replace=True)
+def config_from_recipe(t: dict) -> dict:
+    """config.json keys from a recipe's inline geometry, under the reference's key names
+    (recipes/schema.py:357-431, 128-133, 86, 159-161): ``hidden_size``, ``num_layers``,
+    ``full_attention.{num_heads, num_kv_heads, head_dim, rope.{theta, partial_rotary_factor}}``,
+    ``mlp.{intermediate_size, hidden_act}``, ``vocab_size``, ``max_position_embeddings``,
+    ``rms_norm_eps``, ``tie_word_embeddings``.  A missing key raises KeyError naming it."""
+    fa, mlp = t["full_attention"], t["mlp"]
+    cfg = {
+        "architectures": [NAME], "model_type": "qwen2",
+        "hidden_size": t["hidden_size"], "num_hidden_layers": t["num_layers"],
+        "num_attention_heads": fa["num_heads"], "num_key_value_heads": fa["num_kv_heads"],
+        "intermediate_size": mlp["intermediate_size"], "hidden_act": mlp.get("hidden_act", "silu"),
+        "vocab_size": t["vocab_size"], "max_position_embeddings": t["max_position_embeddings"],
+        "rms_norm_eps": float(t.get("rms_norm_eps", 1e-6)),
+        "rope_theta": float(fa["rope"]["theta"]),
+        "partial_rotary_factor": float(fa["rope"].get("partial_rotary_factor", 1.0)),
+        "tie_word_embeddings": bool(t.get("tie_word_embeddings", False)),
+    }
+    if "head_dim" in fa:
+        cfg["head_dim"] = fa["head_dim"]
+    return cfg
+
+
+register_architecture(Architecture(name=NAME, config_cls=Qwen2Config, plan=plan, aliases=("qwen2",),
+                                   config_from_recipe=config_from_recipe), replace=True)

@@ -13,7 +13,7 @@ import os
 
 import torch
 
-from ._lib import KernelError, call, launches, lib  # noqa: F401
+from ._lib import KernelError, KernelTimes, call, launches, lib  # noqa: F401
 
 F32, BF16 = 0, 1
 
@@ -213,7 +213,7 @@ def _tc_splits(N: int, K: int) -> int:
     """Slices of K so that (tiles of 128 rows) x slices comes to about one unit per SM, each slice
     at least eight 64-wide k blocks long."""
     tiles = -(-N // 128)
-    return max(1, min(NUM_SMS // tiles, (K // 64) // 8))
+    return max(1, min(num_sms() // tiles, (K // 64) // 8))
 
 
 def linear_tc(x, w, bias, out_dtype, *, splits: int = 1, silu: bool = False):
@@ -280,7 +280,7 @@ def linear_accumulate(x, w, bias, residual) -> None:
 
 def _stream_splits(N: int, K: int) -> int:
     ctas = -(-N // 128)
-    return max(1, min(2 * NUM_SMS // ctas, K // 128, 16))
+    return max(1, min(2 * num_sms() // ctas, K // 128, 16))
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype, allow_partials: bool = False) -> torch.Tensor:
@@ -425,7 +425,17 @@ def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, n
     return out
 
 
-NUM_SMS = 148
+_num_sms: dict = {}
+
+
+def num_sms() -> int:
+    """Streaming multiprocessors of the current device (the library asks the driver, once per device):
+    what the dispatch sizes k-splits and context splits for."""
+    dev = torch.cuda.current_device()
+    n = _num_sms.get(dev)
+    if n is None:
+        n = _num_sms[dev] = max(1, int(lib().sllm_num_sms()))
+    return n
 
 
 def attention_tiles(q_lens, group_size: int, device, ctx_lens=None, large_rows: int = 128):
@@ -461,7 +471,7 @@ def choose_splits(num_small: int, nkv: int, max_ctx: int) -> int:
     """How many ways the decode form cuts the context: enough CTAs to fill the GPU about
     twice, never less than 256 keys a split."""
     ctas = max(num_small * nkv, 1)
-    want = max(1, round(2 * NUM_SMS / ctas))    # about two CTAs per SM
+    want = max(1, round(2 * num_sms() / ctas))    # about two CTAs per SM
     return int(max(1, min(want, max_ctx // 256, 32)))
 
 
@@ -534,7 +544,7 @@ def choose_tc_splits(num_tiles: int, nkv: int, max_ctx: int) -> tuple[int, int]:
     so that about two CTAs an SM run, each range at least 16 key tiles long."""
     key_tiles = max(1, -(-max_ctx // 64))
     ctas = max(num_tiles * nkv, 1)
-    want = max(1, min(2 * NUM_SMS // ctas, key_tiles // 16, 32))
+    want = max(1, min(2 * num_sms() // ctas, key_tiles // 16, 32))
     per = -(-key_tiles // want)
     return -(-key_tiles // per), per
 

@@ -36,6 +36,8 @@ def _declare(L):
     c_int, c_float, c_void_p, c_size_t = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
     L.sllm_last_error.restype = ctypes.c_char_p
     L.sllm_last_error.argtypes = []
+    L.sllm_num_sms.restype = c_int
+    L.sllm_num_sms.argtypes = []
     sigs = {
         "sllm_embed_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "sllm_add_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_size_t, c_void_p, c_float, c_void_p, c_int,
@@ -86,21 +88,44 @@ def _declare(L):
     return L
 
 
-def declare_optional(name: str, argtypes) -> bool:
-    """Declare an entry point that newer libraries have; False if absent."""
-    L = lib()
-    try:
-        fn = getattr(L, name)
-    except AttributeError:
-        return False
-    fn.restype = ctypes.c_int
-    fn.argtypes = argtypes
-    return True
+class KernelTimes:
+    """Device time per entry point, for measurement: inside ``with KernelTimes() as kt:`` every launch
+    is bracketed by two CUDA events on the current stream; ``kt.table()`` gives, per entry point, the
+    number of launches and the summed milliseconds (the reference's counterpart is a host stopwatch
+    around its steps, serving/diag.py:132-149).  Events between kernels keep one launch from starting
+    under the tail of the one before, so the sum is an upper bound on what the same kernels take back
+    to back.  Not for use while a CUDA graph is captured."""
+
+    active = None
+
+    def __init__(self):
+        self.pairs: dict[str, list] = {}
+
+    def __enter__(self):
+        KernelTimes.active = self
+        return self
+
+    def __exit__(self, *exc):
+        KernelTimes.active = None
+
+    def table(self) -> dict:
+        import torch
+        torch.cuda.synchronize()
+        return {name: (len(p), sum(a.elapsed_time(b) for a, b in p)) for name, p in self.pairs.items()}
 
 
 def call(name: str, *args) -> None:
     L = lib()
-    rc = getattr(L, name)(*args)
+    kt = KernelTimes.active
+    if kt is None:
+        rc = getattr(L, name)(*args)
+    else:
+        import torch
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        rc = getattr(L, name)(*args)
+        b.record()
+        kt.pairs.setdefault(name, []).append((a, b))
     launches["own"] += 1
     if rc != 0:
         msg = L.sllm_last_error().decode(errors="replace")

@@ -226,9 +226,16 @@ class PreNormBlock:
     addition of each term is done by the norm that follows it, so the block
     takes the pending term of the layer before and hands its own on."""
 
-    def __init__(self, mixer, ffn, mixer_norm, ffn_norm):
-        self.mixer, self.ffn = mixer, ffn
-        self.mixer_norm, self.ffn_norm = mixer_norm, ffn_norm
+    ROLES = ("mixer", "ffn", "mixer_norm", "ffn_norm")
+
+    def __init__(self, parts: dict):
+        if set(parts) != set(self.ROLES):
+            raise ValueError(f"the pre-norm block arranges {self.ROLES}; the layer names {sorted(parts)}")
+        self.mixer, self.ffn = parts["mixer"], parts["ffn"]
+        self.mixer_norm, self.ffn_norm = parts["mixer_norm"], parts["ffn_norm"]
+
+    def cache_need(self):
+        return self.mixer.cache_need()
 
     def forward(self, residual, delta, step, cache, position, write_cache=True):
         x = self.mixer_norm.add_norm(residual, delta)

@@ -9,8 +9,7 @@ step), or from the lists of seen ids a caller of `Sampler.sample` hands over
 (`ops.repetition_penalty_`).  Only the chosen ids cross to the host.  A sampled
 token consumes one uniform from the request's own ``numpy.random.default_rng(seed)``
 (runtime/sampler.py:86; serving/executor.py:358), so equal logits give the
-reference's tokens.  `sample_host` is the same sampler in numpy on one row; the
-engine does not call it.
+reference's tokens.
 """
 
 from __future__ import annotations
@@ -20,51 +19,6 @@ import torch
 
 from .. import ops
 from .params import SamplingParams
-
-
-def apply_repetition_penalty(logits: np.ndarray, seen_ids, penalty) -> np.ndarray:
-    """Seen ids: logit / penalty if positive, * penalty if negative; a copy; ids outside
-    the vocabulary ignored (runtime/sampler.py:12-33)."""
-    out = np.asarray(logits, dtype=np.float64).copy()
-    if penalty is None or penalty <= 0 or penalty == 1.0 or seen_ids is None:
-        return out
-    ids = np.asarray(list(seen_ids), dtype=np.int64)
-    ids = ids[(ids >= 0) & (ids < out.size)]
-    if ids.size:
-        vals = out[ids]
-        out[ids] = np.where(vals < 0, vals * penalty, vals / penalty)
-    return out
-
-
-def sample_host(logits: np.ndarray, params: SamplingParams, rng: np.random.Generator) -> int:
-    """The reference's sampler (runtime/sampler.py:36-88) on one row."""
-    logits = np.asarray(logits, dtype=np.float64)
-    if params.temperature is None or params.temperature <= 0:
-        return int(np.argmax(logits))
-    logits = logits / params.temperature
-    probs = np.exp(logits - logits.max())
-    probs = probs / probs.sum()
-    if params.top_k is not None:
-        k = min(int(params.top_k), probs.size)
-        keep = np.argsort(probs)[-k:]
-        mask = np.zeros(probs.shape, dtype=bool)
-        mask[keep] = True
-        probs = np.where(mask, probs, 0.0)
-        s = probs.sum()
-        if s > 0:
-            probs = probs / s
-    if params.top_p is not None:
-        order = np.argsort(probs)[::-1]
-        cutoff = int(np.searchsorted(np.cumsum(probs[order]), params.top_p) + 1)
-        mask = np.zeros(probs.shape, dtype=bool)
-        mask[order[:cutoff]] = True
-        probs = np.where(mask, probs, 0.0)
-    total = probs.sum()
-    if total <= 0 or not np.isfinite(total):
-        return int(np.argmax(logits))
-    probs = probs / total
-    idx = int(np.searchsorted(np.cumsum(probs), rng.random()))
-    return min(idx, probs.size - 1)
 
 
 class Sampler:

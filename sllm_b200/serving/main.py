@@ -39,26 +39,38 @@ def build_plan(recipe: Recipe, model_dir: str | None, settings: dict) -> str:
              f"  model    : {recipe.model_id} (arch {recipe.arch}, dtype {settings['dtype']})",
              f"  recipe   : {recipe.path}",
              f"  weights  : {model_dir or '(none: give --model-dir or --random-weights)'}"]
-    cfg = None
     try:
+        # what the model asks of the cache comes from the model itself (built without weights), not from
+        # keys of one architecture's config.json
+        import torch
+
+        from ..cache.manager import CacheManager
+        from ..config.registry import architecture_of, load_config
+        from ..models.causal_lm import CausalLM
         if model_dir and os.path.isfile(os.path.join(model_dir, "config.json")):
-            from .. import models  # noqa: F401
-            from ..config.registry import load_config
-            _, typed = load_config(model_dir)
-            cfg = typed.to_dict()
+            arch, typed = load_config(model_dir)
         elif recipe.text:
-            cfg = recipe.config_json()
-    except ConfigError as e:
+            raw = recipe.config_json()
+            arch = architecture_of(raw)
+            typed = arch.config_cls.from_dict(raw)
+        else:
+            arch = typed = None
+        if arch is not None:
+            plan = arch.plan(typed)
+            dt = torch.bfloat16 if settings["dtype"] == "bfloat16" else torch.float32
+            model = CausalLM(plan, dtype=dt, device="cpu")
+            probe = CacheManager(model.cache_needs(), page_size=settings["block_size"], num_pages=0, max_requests=1)
+            per_token = probe.bytes_per_token(2 if dt == torch.bfloat16 else 4)      # runtime/memory_planner.py:12-15
+            lines.append(f"  geometry : {arch.name}: {len(plan.layers)} layers in {len(plan.run_list)} runs, hidden "
+                         f"{plan.hidden_size}, vocab {plan.vocab_size}, {plan.max_positions} positions")
+            budget = (f"{recipe.kv_device_bytes} bytes" if recipe.kv_device_bytes is not None
+                      else f"utilisation {recipe.kv_utilization} of the free device memory")
+            lines.append(f"  cache    : {per_token} bytes per token, {probe.state_bytes_per_request()} bytes of state per "
+                         f"request, pages of {settings['block_size']} tokens, budget {budget}")
+            for line in probe.describe():
+                lines.append(f"             {line}")
+    except (ConfigError, ValueError) as e:
         lines.append(f"  geometry : unreadable ({e})")
-    if cfg:
-        nkv = cfg.get("num_key_value_heads", cfg["num_attention_heads"])
-        hd = cfg.get("head_dim", cfg["hidden_size"] // cfg["num_attention_heads"])
-        item = 2 if settings["dtype"] == "bfloat16" else 4
-        per_token = cfg["num_hidden_layers"] * 2 * nkv * hd * item       # runtime/memory_planner.py:12-15
-        lines.append(f"  geometry : {cfg['num_hidden_layers']} layers, hidden {cfg['hidden_size']}, "
-                     f"{cfg['num_attention_heads']} heads / {nkv} kv heads of {hd}, vocab {cfg['vocab_size']}")
-        lines.append(f"  cache    : {per_token} bytes per token, pages of {settings['block_size']} tokens, "
-                     f"utilisation {recipe.kv_utilization}")
     lines.append(f"  schedule : max_num_seqs {settings['max_num_seqs']}, chunk_size {settings['chunk_size']}, "
                  f"max_new {settings['max_new']}")
     lines.append("  nodes    : 1 (mode=plan: nothing executed)")
@@ -67,7 +79,7 @@ def build_plan(recipe: Recipe, model_dir: str | None, settings: dict) -> str:
 
 def main(argv=None) -> int:
     global _level
-    ap = argparse.ArgumentParser(prog="sllm", description="sLLM-B200: one-GPU engine for Qwen2.5 dense models")
+    ap = argparse.ArgumentParser(prog="sllm", description="sLLM-B200: a one-GPU inference engine")
     ap.add_argument("recipe", nargs="?", help="recipe yaml (path or name under recipes/)")
     ap.add_argument("--tp", "--nodes", dest="nodes", type=int, default=None, metavar="N")
     ap.add_argument("--mode", choices=("plan", "run", "serve"), default="plan")
@@ -139,7 +151,7 @@ def main(argv=None) -> int:
         from ..sampling import SamplingParams
         llm = LLM(model_dir, dtype=dtype, block_size=settings["block_size"], max_num_seqs=settings["max_num_seqs"],
                   chunk_size=settings["chunk_size"], max_model_len=settings["max_model_len"],
-                  kv_utilization=recipe.kv_utilization,
+                  kv_utilization=recipe.kv_utilization, kv_bytes=recipe.kv_device_bytes,
                   progress=lambda d, t: log("INFO", f"load: {d}/{t} tensors"))
         vocab = llm.model.plan.vocab_size
         tok = None

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import json
 import os
+import warnings
 from typing import Iterable
 
 import torch
@@ -105,8 +106,13 @@ def load_into(model, model_dir: str, *, progress=None) -> None:
     """Check the folder against ``model.tensor_specs()`` and bind every tensor."""
     source = TensorSource(model_dir)
     specs = model.tensor_specs()
-    check(source, specs, ignore=model.ignored_tensor_names())
+    ignored = list(model.ignored_tensor_names())
+    check(source, specs, ignore=ignored)
     have = set(source.names())
+    unused = sorted(have & set(ignored))
+    if unused:
+        warnings.warn(f"{model_dir}: {', '.join(unused)} is in the checkpoint and not used by this model "
+                      f"(a tied output head reads the embedding table)", stacklevel=2)
     total = sum(1 for s in specs if s.name in have)
     done = 0
 

@@ -42,26 +42,6 @@ def random_tensors(specs, seed: int, *, std: float = 0.02, bias_std: float | Non
     return out
 
 
-def random_tensors_on_device(specs, seed: int, device, *, std: float = 0.02, gain_std: float = 0.0,
-                             storage: str = "bfloat16") -> dict:
-    """The same roles drawn by the device's generator: for models too large to
-    draw on the host in reasonable time.  Not the same numbers as `random_tensors`."""
-    g = torch.Generator(device=device)
-    g.manual_seed(seed)
-    dt = _STORAGE[storage]
-    out = {}
-    for s in specs:
-        if s.role == "gain":
-            t = torch.ones(s.shape, dtype=torch.float32, device=device)
-            if gain_std:
-                t += gain_std * torch.randn(s.shape, generator=g, device=device)
-        else:
-            t = torch.empty(s.shape, dtype=dt, device=device)
-            t.normal_(0.0, std, generator=g)
-        out[s.name] = t.to(dt)
-    return out
-
-
 def write_random_model(model_dir: str, config: dict, seed: int, *, std: float = 0.02,
                        bias_std: float | None = None, gain_std: float = 0.0,
                        storage: str = "bfloat16", include_optional: bool = True) -> str:

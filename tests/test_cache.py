@@ -170,3 +170,35 @@ def test_slot_tables_of_others_are_zeroed_at_admission():
     assert table[a.slot].sum() == 35                       # giving the slot back changes nothing
     c = cm.add_request("c")
     assert c.slot == a.slot and table[c.slot].sum() == 0
+
+
+def test_freed_pages_are_poisoned_and_fresh_ones_zeroed_when_asked():
+    """The debugging aid: a page that goes back to its pool (at the request's end, or when a window has
+    passed it) holds NaN in every layer of its group; a page handed out holds zeros."""
+    import torch
+    needs = [("own", PagedKV(2, 4, None)), ("own", PagedKV(2, 4, None)), ("own", PagedKV(1, 4, 8))]
+    cm = CacheManager(needs, page_size=4, num_pages=6, max_requests=2, poison_freed=True)
+    cm.allocate_storage(torch.float32, "cpu")
+    assert all(bool(t.isnan().all()) for t in cm.kv_storage)
+    cm.add_request("a")
+    cm.reserve("a", 10)
+    held = cm.requests["a"].tables[0]
+    assert bool((cm.kv_storage[0][:, :, held] == 0).all())
+    others = [p for p in range(6) if p not in held]
+    assert bool(cm.kv_storage[0][:, :, others].isnan().all())
+    cm.kv_storage[1][:, :, cm.requests["a"].tables[1]] = 1.0
+    cm.commit("a", 10)                                            # window 8: position 10 reads from 3 on; page 0 stays
+    cm.reserve("a", 14)
+    cm.commit("a", 14)                                            # reads from 7 on: page 0 has gone back
+    t1 = cm.requests["a"].tables[1]
+    assert t1[0] == -1 and bool(cm.kv_storage[1][:, :, 0].isnan().all()) and bool((cm.kv_storage[1][:, :, t1[1]] == 1).all())
+    cm.free_request("a")
+    assert all(bool(t.isnan().all()) for t in cm.kv_storage)
+    cm.check()
+    # off by default: nothing is filled
+    cm = CacheManager(needs, page_size=4, num_pages=6, max_requests=2)
+    cm.allocate_storage(torch.float32, "cpu")
+    cm.add_request("a")
+    cm.reserve("a", 5)
+    cm.free_request("a")
+    assert all(bool((t == 0).all()) for t in cm.kv_storage)

@@ -76,3 +76,27 @@ def test_run_mode_on_cpu_ops(cpu_ops, capsys, monkeypatch):
     assert cli.main(["tiny-qwen2", "--mode", "run", "--random-weights", "3", "--prompt", "abc", "--max-new", "2",
                      "--dtype", "float32", "--log-level", "ERROR"]) == 0
     assert len(capsys.readouterr().out.strip().splitlines()) == 2               # ids, then text
+
+
+@pytest.mark.gpu
+def test_launcher_runs_on_the_gpu(tmp_path):
+    """`./sllm <recipe> --mode run --random-weights SEED --prompt-ids ...` as a user runs it, in a process
+    of its own on the GPU with the real kernels: the ids it prints are the plain implementation's greedy
+    tokens for the folder the same seed writes."""
+    import subprocess
+
+    from tests.conftest import cuda_or_skip
+    from tests.plain import qwen2_plain as plain
+    from sllm_b200.weights import write_random_model
+    cuda_or_skip()
+    root = os.path.dirname(RECIPES)
+    prompt = [5, 17, 3, 200, 42, 7, 99, 120, 8, 61, 33, 250, 1]
+    r = subprocess.run([os.path.join(root, "sllm"), "tiny-qwen2", "--mode", "run", "--random-weights", "0", "--prompt-ids",
+                        ",".join(map(str, prompt)), "--max-new", "8", "--dtype", "float32", "--log-level", "ERROR"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = [int(t) for t in r.stdout.strip().splitlines()[-1].split(",")]
+    folder = write_random_model(str(tmp_path / "again"), resolve_recipe("tiny-qwen2", RECIPES).config_json(), 0,
+                                std=0.02, bias_std=0.1)
+    cfg, w = plain.load_model(folder)
+    assert got == plain.generate(prompt, 8, w, cfg)

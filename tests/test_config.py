@@ -51,9 +51,9 @@ def test_plan_is_data_from_config():
         c = Qwen2Config.from_dict(raw)
         p = plan(c)
         assert len(p.layers) == c.num_hidden_layers and [e.layer for e in p.run_list] == list(range(len(p.layers)))
-        assert p.layers[0].mixer.params["num_heads"] == c.num_attention_heads
-        assert p.layers[0].mixer.params["scale"] == c.head_dim ** -0.5
-        assert p.layers[0].norm.params["eps"] == c.rms_norm_eps
+        assert p.layers[0].part("mixer").params["num_heads"] == c.num_attention_heads
+        assert p.layers[0].part("mixer").params["scale"] == c.head_dim ** -0.5
+        assert p.layers[0].part("mixer_norm").params["eps"] == c.rms_norm_eps
         assert p.position.params["theta"] == c.rope_theta
         assert (p.head_name is None) == c.tie_word_embeddings
 

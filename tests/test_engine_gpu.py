@@ -208,7 +208,7 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     stands in every second layer of a new architecture beside attention layers, gets a
     state slot from the cache manager, and is stepped in portions.  No file of the package
     is touched."""
-    from sllm_b200.config import (Architecture, LayerSpec, ModelPlan, PartSpec, RunEntry, register_architecture,
+    from sllm_b200.config import (Architecture, ModelPlan, PartSpec, RunEntry, pre_norm_layer, register_architecture,
                                   unregister_architecture)
     from sllm_b200.engine import Engine, StepEntry, build_model
     from sllm_b200.models.qwen2 import Qwen2Config
@@ -250,8 +250,8 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     def toy_plan(cfg):
         base = qwen2_plan(cfg)
         toy = PartSpec("toy_decay_state", {"hidden_size": cfg.hidden_size, "state_dim": D, "decay": DECAY})
-        layers = tuple(LayerSpec(prefix=l.prefix, mixer=toy if i % 2 else l.mixer, ffn=l.ffn, norm=l.norm,
-                                 mixer_prefix="toy" if i % 2 else l.mixer_prefix) for i, l in enumerate(base.layers))
+        layers = tuple(pre_norm_layer(l.prefix, toy if i % 2 else l.part("mixer"), l.part("ffn"), l.part("mixer_norm"),
+                                      mixer_name="toy" if i % 2 else l.parts["mixer"].name) for i, l in enumerate(base.layers))
         return ModelPlan(architecture="ToyStateLM", hidden_size=base.hidden_size, vocab_size=base.vocab_size,
                          max_positions=base.max_positions, embedding_name=base.embedding_name, layers=layers,
                          run_list=tuple(RunEntry(i) for i in range(len(layers))), final_norm=base.final_norm,
@@ -400,7 +400,13 @@ def test_decode_graphs_pad_the_batch_to_a_captured_size(tiny, dtype):
         if dtype == "float32":
             assert r.ids == want
         else:
-            assert r.ids[:2] == want[:2] and len(r.ids) == sp.max_new
+            # a near-tie may fall the other way: every token must be the maximum of the plain logits of
+            # the engine's own sequence up to the bfloat16 path's tolerance
+            assert len(r.ids) == sp.max_new
+            logits = plain.forward(p + r.ids, w, cfg)
+            for i, tok in enumerate(r.ids):
+                row = logits[len(p) + i - 1]
+                assert row[tok] >= row.max() - 2 * (TOL["bfloat16"]["atol"] + TOL["bfloat16"]["rtol"] * abs(row.max()))
 
 
 @pytest.mark.parametrize("policy", ["reserve", "on_demand"])
@@ -487,7 +493,7 @@ def test_toy_routed_feed_forward_and_learned_positions(tmp_path):
     encoding that is a learned table added to the embeddings (the attention then rotates nothing).
     Registered, given tensors by the random-weights writer, built through the registry, stepped in
     portions and one token at a time, and compared with a plain numpy statement of the same model."""
-    from sllm_b200.config import (Architecture, LayerSpec, ModelPlan, PartSpec, RunEntry, register_architecture,
+    from sllm_b200.config import (Architecture, ModelPlan, PartSpec, RunEntry, pre_norm_layer, register_architecture,
                                   unregister_architecture)
     from sllm_b200.engine import Engine, StepEntry, build_model
     from sllm_b200.models.qwen2 import Qwen2Config
@@ -535,8 +541,8 @@ def test_toy_routed_feed_forward_and_learned_positions(tmp_path):
     def toy_plan(cfg):
         base = qwen2_plan(cfg)
         routed = PartSpec("toy_routed", {"hidden_size": cfg.hidden_size})
-        layers = tuple(LayerSpec(prefix=l.prefix, mixer=l.mixer, ffn=routed if i % 2 else l.ffn, norm=l.norm,
-                                 ffn_prefix="moe" if i % 2 else l.ffn_prefix) for i, l in enumerate(base.layers))
+        layers = tuple(pre_norm_layer(l.prefix, l.part("mixer"), routed if i % 2 else l.part("ffn"), l.part("mixer_norm"),
+                                      ffn_name="moe" if i % 2 else l.parts["ffn"].name) for i, l in enumerate(base.layers))
         pos = PartSpec("toy_learned_abs", {"max_positions": cfg.max_position_embeddings, "hidden_size": cfg.hidden_size})
         return ModelPlan(architecture="ToyRoutedLM", hidden_size=base.hidden_size, vocab_size=base.vocab_size,
                          max_positions=base.max_positions, embedding_name=base.embedding_name, layers=layers,
@@ -583,7 +589,7 @@ def test_toy_routed_feed_forward_and_learned_positions(tmp_path):
             return h @ w["model.embed_tokens.weight"].T
 
         model, _ = build_model(model_dir, "float32", dev)
-        assert [type(l.ffn).__name__ for l in model.layers] == ["SwiGLU", "ToyRouted"] * 2
+        assert [type(l.parts["ffn"]).__name__ for l in model.layers] == ["SwiGLU", "ToyRouted"] * 2
         assert type(model.position).__name__ == "LearnedPositions"
         eng = Engine(model, page_size=page, num_pages=12, max_requests=2)
         ids = _prompts(cfg, (45,), 5)[0]

@@ -1,0 +1,120 @@
+"""The attention kernels at the context lengths the engine is benchmarked and profiled at (8k to 32k
+tokens), where the tests at other sizes do not reach: the decode forms with their context cut 32 ways,
+block tables of more than 2,048 pages (which the decode kernels no longer keep in shared memory), and
+the tcgen05 prefill form on a portion of 512 tokens at the end of 32k with its context cut into many
+ranges.  Each against the float32 statement, and with one far key made to stand out."""
+
+import pytest
+import torch
+
+from tests import torch_ops as ref
+from tests.conftest import cuda_or_skip
+from tests.test_kernels_gpu import _paged_case, _starts
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    cuda_or_skip()
+    import sllm_b200.ops as ops
+    return ops
+
+
+def _decode_forms(ops, hd, ps):
+    forms = [("mma", lambda *a: ops.attention_mma(*a[:7], True, a[7], *a[8:]))]
+    if ops.tma_attention_supports(hd, ps):
+        forms.append(("tma", lambda *a: ops.attention_tma_decode(*a)))
+    return forms
+
+
+@pytest.mark.parametrize("ctx,ps", [(8192, 16), (32768, 16), (32768, 64), (17000, 8)])
+@pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 128), (6, 1, 64)])
+def test_decode_forms_at_long_contexts(ctx, ps, nq, nkv, hd):
+    """Single decoded tokens over 8k to 32k keys: every number of splits up to the cap of 32, requests of
+    other lengths in the same batch, and (pages of 8 at 17,000 tokens: 2,125 pages) a block table longer than
+    the 2,048 entries the kernels cache."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(31)
+    lens = [ctx, ctx - 37, 300, 1]
+    q_lens = [1] * len(lens)
+    q, kc, vc, bt, pos, seq = _paged_case(g, lens, q_lens, nq, nkv, hd, ps, torch.bfloat16, consecutive="runs")
+    assert ctx != 17000 or bt.shape[1] > 2048
+    q_start, ctx_len = _starts(q_lens, lens)
+    scale = hd ** -0.5
+    want = ref.attention_simt(q.float(), kc.float(), vc.float(), bt, pos, seq, nq, nkv, hd, scale, None)
+    small, large = ops.attention_tiles(q_lens, nq // nkv, "cuda")
+    assert large is None
+    assert ops.choose_splits(1, 1, ctx) == 32                  # what the engine picks for one request at this length
+    for name, form in _decode_forms(ops, hd, ps):
+        for splits in (1, 7, 32):
+            out = torch.full_like(q, float("nan"))
+            form(q, kc, vc, bt, q_start, ctx_len, small, splits, nq, nkv, hd, scale, None, out)
+            ops.check_tcgen05_status()
+            assert not out.isnan().any(), f"{name}, {splits} splits: a row was not written"
+            torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2, msg=lambda m: f"{name}, {splits} splits: {m}")
+
+
+@pytest.mark.parametrize("ctx,ps", [(32768, 16), (17000, 8)])
+def test_decode_forms_find_a_far_key_at_long_contexts(ctx, ps):
+    """One key among 32k stands out: at the very start, at split and page edges, in the last page."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(32)
+    nq, nkv, hd = 4, 2, 128
+    per_split = -(-ctx // 32)
+    for far in (0, ps - 1, ps, per_split - 1, per_split, 16383, 16384, ctx - ps - 1, ctx - 1):
+        q, kc, vc, bt, pos, seq = _paged_case(g, [ctx], [1], nq, nkv, hd, ps, torch.bfloat16)
+        q_start, ctx_len = _starts([1], [ctx])
+        page, off = int(bt[0, far // ps]), far % ps
+        direction = torch.randn(hd, device="cuda", generator=g)
+        direction /= direction.norm()
+        kc[page, :, off, :] = (direction * 16).bfloat16()
+        q[0] = (direction * 16).repeat(nq).bfloat16()
+        want = vc[page, :, off, :].float().repeat_interleave(nq // nkv, dim=0)
+        small, _ = ops.attention_tiles([1], nq // nkv, "cuda")
+        for name, form in _decode_forms(ops, hd, ps):
+            for splits in (1, 32):
+                out = torch.full_like(q, float("nan"))
+                form(q, kc, vc, bt, q_start, ctx_len, small, splits, nq, nkv, hd, 1.0, None, out)
+                ops.check_tcgen05_status()
+                torch.testing.assert_close(out.float().reshape(nq, hd), want, rtol=2e-2, atol=2e-2,
+                                           msg=lambda m: f"{name}, {splits} splits, key {far}: {m}")
+
+
+@pytest.mark.parametrize("nq,nkv,hd,ps", [(4, 2, 128, 16), (6, 1, 64, 32)])
+def test_prefill_form_on_a_portion_at_32k(nq, nkv, hd, ps):
+    """A portion of 512 tokens whose context ends at 32,768, beside a short request: the context split the
+    engine would choose (many ranges), the most ranges the kernel takes, and none; against the float32
+    statement and with a far key that every query must find."""
+    ops = _ops()
+    if not ops.tc_attention_supports(hd, ps):
+        pytest.skip("not taken by the tcgen05 form")
+    g = torch.Generator(device="cuda").manual_seed(33)
+    ctx, portion = 32768, 512
+    lens, q_lens = [ctx, 200], [portion, 200]
+    q, kc, vc, bt, pos, seq = _paged_case(g, lens, q_lens, nq, nkv, hd, ps, torch.bfloat16, consecutive="runs")
+    q_start, ctx_len = _starts(q_lens, lens)
+    scale = hd ** -0.5
+    want = ref.attention_simt(q.float(), kc.float(), vc.float(), bt, pos, seq, nq, nkv, hd, scale, None)
+    _, large = ops.attention_tiles(q_lens, nq // nkv, "cuda", lens, 128)
+    chosen = ops.choose_tc_splits(large[2], nkv, ctx)
+    assert chosen[0] > 2 and chosen[0] * chosen[1] * 64 >= ctx
+    for splits in (chosen, (32, 16), (1, 0)):
+        out = torch.full_like(q, float("nan"))
+        ops.attention_tc(q, kc, vc, bt, q_start, ctx_len, large, nq, nkv, hd, scale, out, splits=splits)
+        ops.check_tcgen05_status()
+        assert not out.isnan().any(), f"splits {splits}: a row was not written"
+        torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2, msg=lambda m: f"splits {splits}: {m}")
+    # a far key: all 512 queries of the long request return its value
+    for far in (0, 1023, 1024, 20000, ctx - portion - 1):
+        k2, q2 = kc.clone(), q.clone()
+        page, off = int(bt[0, far // ps]), far % ps
+        direction = torch.randn(hd, device="cuda", generator=g)
+        direction /= direction.norm()
+        k2[page, :, off, :] = (direction * 18).bfloat16()
+        q2[:portion] = (direction * 18).repeat(nq).bfloat16()
+        out = torch.full_like(q, float("nan"))
+        ops.attention_tc(q2, k2, vc, bt, q_start, ctx_len, large, nq, nkv, hd, 1.0, out, splits=chosen)
+        ops.check_tcgen05_status()
+        value = vc[page, :, off, :].float().repeat_interleave(nq // nkv, dim=0)
+        torch.testing.assert_close(out.float()[:portion].reshape(portion, nq, hd), value.expand(portion, nq, hd),
+                                   rtol=2e-2, atol=2e-2, msg=lambda m: f"far key {far}: {m}")

@@ -58,6 +58,27 @@ def test_cuttings_in_process(tiny, dtype, mode):
         assert eng.cache.reuse_count > 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_cutting_with_freed_pages_poisoned(tiny, dtype):
+    """The cache manager's debugging aid fills every page that goes back to the pool with NaN (and
+    zeroes a page when it is handed out).  With pages used again and again, a kernel that read a page
+    its request does not hold would put NaN into the logits; none may."""
+    from sllm_b200.engine import Engine, build_model
+    dev = cuda_or_skip()
+    name, model_dir, page = tiny
+    cfg, w = plain.load_model(model_dir)
+    reqs = requests_for(cfg)
+    want = {r: plain.forward(ids, w, cfg) for r, ids in reqs.items()}
+    tr = traces.mixed(reqs)
+    model, _ = build_model(model_dir, dtype, dev)
+    eng = Engine(model, page_size=page, num_pages=tr.max_tokens // page, max_requests=4, poison_freed=True)
+    assert bool(eng.cache.kv_storage[0].isnan().all())            # nobody holds a page yet
+    out = traces.replay_engine(tr, eng)
+    assert all(np.isfinite(o).all() for o in out.values())
+    traces.compare(tr, out, want, what=f"{name}/{dtype}/mixed, freed pages poisoned", **TOL[dtype])
+    assert eng.cache.reuse_count > 0 and bool(eng.cache.kv_storage[0].isnan().all())
+
+
 def test_float32_cuttings_agree_to_rounding(tiny):
     """In float32 the order of summation for a position does not depend on the cutting,
     so the cuttings agree far more closely with each other than the tolerance against
