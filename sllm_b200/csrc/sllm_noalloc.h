@@ -16,7 +16,9 @@
 //   the caller, live here in an array compiled into the library.
 //
 // Limits and rules:
-//   * M <= 64, K a multiple of 128, and splits' x M x N <= SLLM_NOALLOC_SCRATCH_FLOATS, where
+//   * M <= 64 (what the kernel takes; the engine's own dispatch sends it at most 32 rows, because
+//     beyond that another kernel is faster), K a multiple of 128, and
+//     splits' x M x N <= SLLM_NOALLOC_SCRATCH_FLOATS, where
 //     splits' = sllm_linear_stream_splits(K, splits).  Larger requests are refused with an
 //     error code and a message (sllm_last_error); nothing is launched.
 //   * The array costs SLLM_NOALLOC_SCRATCH_FLOATS * 4 bytes (8 MiB) of device memory on every
