@@ -28,7 +28,7 @@
 // (kernels/cuda/kernels.cu:752-767) and its prefill runs in numpy (serving/executor.py:255-265).
 #include <stdio.h>
 
-#include "tcgen05.cuh"
+#include "gemm_epilogue.cuh"
 
 namespace sllm {
 
@@ -38,10 +38,6 @@ constexpr int TG_B_BYTES = TG_BN * TG_BK * 2;            // 32 KB
 constexpr int TG_STAGE_BYTES = TG_A_BYTES + TG_B_BYTES;
 constexpr int TG_SMEM = TG_STAGES * TG_STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 constexpr int TG_TMEM_COLS = 512;                        // two accumulators of 256 columns
-
-#define TG_EPI_F32 0
-#define TG_EPI_BF16 1
-#define TG_EPI_SILU 2
 
 template <int EPI>
 __global__ void __launch_bounds__(192, 1)
@@ -157,53 +153,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + b * TG_BN + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (m >= M) continue;
-        const int n = n0 + c0;
-        if constexpr (EPI == TG_EPI_SILU) {
-          // columns alternate 8 gate, 8 up; out[m, (n/16)*8 + i] = silu(gate_i) * up_i
-          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * (N >> 1) + (n >> 1);
-#pragma unroll
-          for (int blk = 0; blk < 2; ++blk) {
-            if (n + blk * 16 + 15 >= N) break;
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float g = __uint_as_float(r[blk * 16 + i]), u = __uint_as_float(r[blk * 16 + 8 + i]);
-              v[i] = g * (1.0f / (1.0f + expf(-g))) * u;
-            }
-            if (((N >> 1) & 7) == 0) {               // rows of the result are 16-byte aligned
-              *reinterpret_cast<uint4*>(o + blk * 8) = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) o[blk * 8 + i] = __float2bfloat16_rn(v[i]);
-            }
-          }
-        } else {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) + ((bias && n + i < N) ? bias[n + i] : 0.f);
-          const bool whole = n + 32 <= N;
-          if constexpr (EPI == TG_EPI_F32) {
-            float* o = reinterpret_cast<float*>(out) + (size_t)m * N + n;
-            if (whole && (N & 3) == 0) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) if (n + i < N) o[i] = v[i];
-            }
-          } else {
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * N + n;
-            if (whole && (N & 7) == 0) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 8)
-                *reinterpret_cast<uint4*>(o + i) = make_uint4(pack2(v[i], v[i + 1]), pack2(v[i + 2], v[i + 3]),
-                                                              pack2(v[i + 4], v[i + 5]), pack2(v[i + 6], v[i + 7]));
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) if (n + i < N) o[i] = __float2bfloat16_rn(v[i]);
-            }
-          }
-        }
+        tg_store_chunk<EPI>(r, m, n0 + c0, N, bias, out);
       }
       // this warp has read its quarter of the buffer: hand it back to the MMA issuer
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

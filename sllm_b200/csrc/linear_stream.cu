@@ -33,6 +33,17 @@ constexpr int LS_XSTRIDE = LS_KC + 32;     // bf16 elements: 320 bytes, = 64 mod
 #define EPI_STORE 0
 #define EPI_SILU 1
 
+constexpr int LS_SSQ_MAX = 384;            // partial sums of squares per token a scaled launch takes
+
+// A norm still owed on the input (see linear_ws.cu, WsNorm): x is bfloat16(stream * gain), ssq [M][stride]
+// (stride = parts rounded up to 4) holds partial sums of squares of the stream's rows, and every row of the
+// product is multiplied by rsqrt(sum / width + eps) before the epilogue's arithmetic.
+struct LsScale {
+  const float* ssq = nullptr;
+  int parts = 0;
+  float eps = 0.f, inv_width = 0.f;
+};
+
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
@@ -51,14 +62,17 @@ __device__ __forceinline__ void ls_mma(float (&c)[4], unsigned a0, unsigned a1, 
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// NT: 8-token tiles (M <= 8*NT).  OUT: float or __nv_bfloat16.
-template <int NT, int EPI, typename OUT>
+// NT: 8-token tiles (M <= 8*NT).  OUT: float or __nv_bfloat16.  SCALED: the rows of the result are scaled
+// (LsScale; unsplit launches only).
+template <int NT, int EPI, typename OUT, bool SCALED>
 __global__ void __launch_bounds__(256)
 linear_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W,
                      const float* __restrict__ bias, OUT* __restrict__ out, float* __restrict__ partial,
-                     int M, int N, int K, int chunks_per_split) {
+                     int M, int N, int K, int chunks_per_split, const LsScale scale) {
   extern __shared__ __align__(16) unsigned char ls_smem[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ls_smem);          // [2][8*NT][LS_XSTRIDE]
+  float* ssq_s = reinterpret_cast<float*>(ls_smem + sizeof(__nv_bfloat16) * 2 * 8 * NT * LS_XSTRIDE);   // SCALED: [8*NT][LS_SSQ_MAX]
+  __shared__ float row_scale[8 * NT];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
   const int n0 = blockIdx.x * LS_ROWS + warp * 16;
@@ -117,6 +131,14 @@ linear_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   if (n_chunks > 1) load_w(wb, 1);
   pdl_wait();                          // the activations do
   if (n_chunks > 0) load_x(0, 0);
+  if constexpr (SCALED) {
+    // the tokens' partial sums of squares come to shared memory with the first activations
+    const int stride = (scale.parts + 3) & ~3, pieces = stride >> 2;
+    for (int c = tid; c < M * pieces; c += 256) {
+      const int tok = c / pieces, piece = c % pieces;
+      ls_cp_async_16(ssq_s + (size_t)tok * LS_SSQ_MAX + piece * 4, scale.ssq + (size_t)tok * stride + piece * 4, true);
+    }
+  }
   asm volatile("cp.async.commit_group;\n" ::);
   for (int c = 0; c < n_chunks; c += 2) {
     // chunk c from wa, chunk c+1 from wb
@@ -142,6 +164,22 @@ linear_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   }
   asm volatile("cp.async.wait_group 0;\n" ::);
   pdl_launch_dependents();             // the stream is read; the next kernel may begin while the results are stored
+  if constexpr (SCALED) {
+    // warp w adds the partial sums of tokens w, w + 8, ...: lane l takes l, l + 32, ..., then the lanes are added
+    // (the table has been visible to all since the loop's first barrier)
+    for (int tok = warp; tok < 8 * NT; tok += 8) {
+      float sum = 0.f;
+      if (tok < M)
+        for (int p = lane; p < scale.parts; p += 32) sum += ssq_s[(size_t)tok * LS_SSQ_MAX + p];
+      sum = warp_sum(sum);
+      if (lane == 0) row_scale[tok] = rsqrtf(sum * scale.inv_width + scale.eps);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[j][c] *= row_scale[8 * j + 2 * t4 + (c & 1)];
+  }
 
   // ---- epilogue: acc[j][c]: c0,c1 = (row g, tokens 8j+2t, +1); c2,c3 = (row g+8, same tokens) ----
   const int row_a = n0 + g, row_b = n0 + g + 8;
@@ -183,13 +221,13 @@ linear_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   }
 }
 
-template <int NT, int EPI, typename OUT>
+template <int NT, int EPI, typename OUT, bool SCALED = false>
 static int launch_ls(const __nv_bfloat16* x, const __nv_bfloat16* W, const float* bias, void* out, float* partial,
-                     int M, int N, int K, int splits, cudaStream_t stream) {
-  constexpr size_t smem = sizeof(__nv_bfloat16) * 2 * 8 * NT * LS_XSTRIDE;
+                     int M, int N, int K, int splits, cudaStream_t stream, const LsScale& scale = LsScale{}) {
+  constexpr size_t smem = sizeof(__nv_bfloat16) * 2 * 8 * NT * LS_XSTRIDE + (SCALED ? sizeof(float) * 8 * NT * LS_SSQ_MAX : 0);
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
-    if (cudaFuncSetAttribute(linear_stream_kernel<NT, EPI, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    if (cudaFuncSetAttribute(linear_stream_kernel<NT, EPI, OUT, SCALED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
       set_error("linear_stream: cannot raise the shared memory limit");
       return SLLM_ERR_LAUNCH;
     }
@@ -198,7 +236,7 @@ static int launch_ls(const __nv_bfloat16* x, const __nv_bfloat16* W, const float
   const int total_chunks = K / LS_KC;
   const int per = (total_chunks + splits - 1) / splits;
   dim3 grid((N + LS_ROWS - 1) / LS_ROWS, (total_chunks + per - 1) / per);
-  launch_kernel(linear_stream_kernel<NT, EPI, OUT>, grid, 256, smem, stream, x, W, bias, (OUT*)out, partial, M, N, K, per);
+  launch_kernel(linear_stream_kernel<NT, EPI, OUT, SCALED>, grid, 256, smem, stream, x, W, bias, (OUT*)out, partial, M, N, K, per, scale);
   return launch_status("linear_stream");
 }
 
@@ -243,6 +281,22 @@ SLLM_EXPORT int sllm_linear_stream(const void* x, const void* W, const float* bi
     default: GO(8)
   }
 #undef GO
+}
+
+// The SiLU epilogue on an input whose norm is still owed: out[M, N/2] = silu(s gate) * (s up) with
+// s[token] = rsqrt(sum of ssq[token][0..parts) / width + eps); x is bfloat16(stream * gain).  At most 16 tokens.
+SLLM_EXPORT int sllm_linear_stream_silu_scaled(const void* x, const void* W, void* out, int M, int N, int K, const float* ssq,
+                                               int parts, float eps, int width, cudaStream_t stream) {
+  SLLM_REQUIRE(sllm_linear_stream_supports(M, N, K) && M <= 16 && N % 16 == 0,
+               "linear_stream_silu_scaled: sizes M=%d N=%d K=%d (needs M<=16, N%%16==0, K%%128==0)", M, N, K);
+  SLLM_REQUIRE(ssq != nullptr && ((uintptr_t)ssq & 15) == 0 && parts >= 1 && parts <= LS_SSQ_MAX && width >= 1,
+               "linear_stream_silu_scaled: a table of %d partial sums (at most %d) over width %d", parts, LS_SSQ_MAX, width);
+  LsScale sc;
+  sc.ssq = ssq; sc.parts = parts; sc.eps = eps; sc.inv_width = 1.0f / (float)width;
+  const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+  const __nv_bfloat16* wb = (const __nv_bfloat16*)W;
+  if (M <= 8) return launch_ls<1, EPI_SILU, __nv_bfloat16, true>(xb, wb, nullptr, out, nullptr, M, N, K, 1, stream, sc);
+  return launch_ls<2, EPI_SILU, __nv_bfloat16, true>(xb, wb, nullptr, out, nullptr, M, N, K, 1, stream, sc);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -68,14 +68,35 @@ __device__ __forceinline__ void ws_mma(float (&c)[4], unsigned a0, unsigned a1, 
 
 constexpr int WS_WARPS = 8;
 constexpr int WS_DEPTH = 4;      // k blocks a warp keeps in flight
+constexpr int WS_SSQ_MAX = 384;     // partial sums of squares per token a consumer takes (the producer's CTAs)
 
-// NT: 8-token tiles (M <= 8 * NT).  OUT: float or __nv_bfloat16 (store epilogue only).
-template <int NT, int EPI, typename OUT>
+// An RMSNorm taken apart, so that a decode step needs no kernel for it (y = x * rsqrt(mean(x^2) + eps) * gain,
+// ref/standard.py:25-31).  The product that completes the residual stream (residual epilogue) also writes
+// xg_out = bfloat16(stream * gain) and, per CTA, each token's sum of squares over the CTA's columns of the
+// stream (ssq_out[token][cta]); the product that consumes the normed activations reads xg as its input and
+// multiplies each token's row of its result by rsqrt(sum of the token's partial sums / width + eps):
+// W (x g / rms) = (W (x g)) / rms.  The partial sums are added in a fixed order.  A table of partial sums is
+// [tokens][stride] float32 with stride = parts rounded up to a multiple of 4 (rows start on 16 bytes); what
+// lies between parts and stride is never written and never added.
+struct WsNorm {
+  const float* ssq_in = nullptr;     // consumer: [M][(parts_in + 3) & ~3]
+  int parts_in = 0;
+  float eps_in = 0.f, inv_width_in = 0.f;
+  const float* gain = nullptr;       // producer (residual epilogue): the next norm's gain [N]
+  __nv_bfloat16* xg_out = nullptr;   // [M, N]
+  float* ssq_out = nullptr;          // [M][(gridDim.x + 3) & ~3]
+};
+
+// NT: 8-token tiles (M <= 8 * NT).  OUT: float or __nv_bfloat16 (store epilogue only).  SCALED: the input
+// comes with a norm still owed (WsNorm::ssq_in).
+template <int NT, int EPI, typename OUT, bool SCALED>
 __global__ void __launch_bounds__(WS_WARPS * 32)
 linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W,
                  const float* __restrict__ bias, OUT* __restrict__ out, float* __restrict__ residual,
-                 int M, int N, int K, const WsRope rope) {
+                 int M, int N, int K, const WsRope rope, const WsNorm norm) {
   __shared__ float red[WS_WARPS][16][8 * NT + 1];
+  __shared__ float row_scale[8 * NT];
+  __shared__ __align__(16) float ssq_s[SCALED ? 8 * NT : 1][SCALED ? WS_SSQ_MAX : 4];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
   // the CTA's rows [n0, n1): at most 16, the N rows dealt evenly over the grid (so that a grid of a
@@ -146,6 +167,17 @@ linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
   load_w(wa0, wb0, kb);
   pdl_wait();
   load_x(x0, kb);
+  // a norm still owed on the input: the tokens' partial sums of squares are copied to shared memory under
+  // the stream and added after the loop
+  if constexpr (SCALED) {
+    const int stride = (norm.parts_in + 3) & ~3, chunks = stride >> 2;
+    for (int c = tid; c < M * chunks; c += WS_WARPS * 32) {
+      const int tok = c / chunks, piece = c % chunks;
+      const unsigned dst = (unsigned)__cvta_generic_to_shared(&ssq_s[tok][piece * 4]);
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(norm.ssq_in + (size_t)tok * stride + piece * 4));
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  }
   for (; kb < k_blocks; kb += 2 * GROUP) {
     load_w(wa1, wb1, kb + GROUP);
     load_x(x1, kb + GROUP);
@@ -156,12 +188,26 @@ linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
   }
   pdl_launch_dependents();
 
+  if constexpr (SCALED) asm volatile("cp.async.wait_group 0;\n" ::);
   // ---- add the warps' tiles in warp order; acc[j][c]: c0,c1 = (row g, tokens 8j+2t, +1); c2,c3 = (row g+8, ...) ----
 #pragma unroll
   for (int j = 0; j < NT; ++j)
 #pragma unroll
     for (int c = 0; c < 4; ++c) red[warp][g + ((c & 2) ? 8 : 0)][8 * j + 2 * t4 + (c & 1)] = acc[j][c];
   __syncthreads();
+  if constexpr (SCALED) {
+    // warp w adds the partial sums of tokens w, w + 8: lane l takes l, l + 32, ..., then the lanes are added
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      const int tok = warp + 8 * j;
+      float sum = 0.f;
+      if (tok < M)
+        for (int p = lane; p < norm.parts_in; p += 32) sum += ssq_s[tok][p];
+      sum = warp_sum(sum);
+      if (lane == 0) row_scale[tok] = rsqrtf(sum * norm.inv_width_in + norm.eps_in);
+    }
+    __syncthreads();
+  }
   if constexpr (EPI == WS_EPI_ROPE) {
     const int half = rope.hd / 2;
     const int head = n0 / rope.hd, j0 = n0 % rope.hd;            // j0 = 8c: the pair's lower dimension starts here
@@ -171,6 +217,10 @@ linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
       float lo = 0.f, hi = 0.f;
 #pragma unroll
       for (int w = 0; w < WS_WARPS; ++w) { lo += red[w][i][tok]; hi += red[w][i + 8][tok]; }
+      if constexpr (SCALED) {
+        lo *= row_scale[tok];
+        hi *= row_scale[tok];
+      }
       if (bias) { lo += bias[n0 + i]; hi += bias[n0 + half + i]; }
       __nv_bfloat16* dst;
       if (head < rope.nq) {
@@ -200,27 +250,52 @@ linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
   for (int idx = tid; idx < 16 * 8 * NT; idx += WS_WARPS * 32) {
     const int row = idx % 16, tok = idx / 16;           // consecutive threads -> consecutive rows of one token
     const int n = n0 + row;
-    if (tok >= M || n >= n1) continue;
+    const bool valid = tok < M && n < n1;               // (whole warps run the loop: 16 * 8 * NT is a multiple of 32)
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < WS_WARPS; ++w) v += red[w][row][tok];
-    if (bias) v += bias[n];
-    if constexpr (EPI == WS_EPI_RESID) residual[(size_t)tok * N + n] += v;
-    else out[(size_t)tok * N + n] = from_f32<OUT>(v);
+    if constexpr (SCALED) v *= row_scale[tok];
+    if (bias && valid) v += bias[n];
+    if constexpr (EPI == WS_EPI_RESID) {
+      float sq = 0.f;
+      if (valid) {
+        const float r = residual[(size_t)tok * N + n] + v;
+        residual[(size_t)tok * N + n] = r;
+        if (norm.xg_out != nullptr) {
+          norm.xg_out[(size_t)tok * N + n] = __float2bfloat16_rn(r * norm.gain[n]);
+          sq = r * r;
+        }
+      }
+      if (norm.ssq_out != nullptr) {                    // the 16 rows of a token lie in 16 consecutive lanes
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (row == 0 && tok < M) norm.ssq_out[(size_t)tok * ((gridDim.x + 3) & ~3) + blockIdx.x] = sq;
+      }
+    } else if (valid) {
+      out[(size_t)tok * N + n] = from_f32<OUT>(v);
+    }
   }
+}
+
+// CTAs of 16 rows, or, when those would fill the SMs unevenly, the next multiple of the SM count
+static int ws_ctas(int N, bool rope) {
+  const int num_sms = sllm::num_sms();
+  int ctas = (N + 15) / 16;
+  if (!rope && ctas > num_sms && ctas % num_sms != 0) {
+    const int even = (ctas + num_sms - 1) / num_sms * num_sms;
+    if (even <= N) ctas = even;
+  }
+  return ctas;
 }
 
 template <int NT, int EPI, typename OUT>
 static int launch_ws(const __nv_bfloat16* x, const __nv_bfloat16* W, const float* bias, void* out, float* residual,
-                     int M, int N, int K, cudaStream_t stream, const WsRope& rope = WsRope{}) {
-  // CTAs of 16 rows, or, when those would fill the SMs unevenly, the next multiple of the SM count
-  const int num_sms = sllm::num_sms();
-  int ctas = (N + 15) / 16;
-  if (EPI != WS_EPI_ROPE && ctas > num_sms && ctas % num_sms != 0) {
-    const int even = (ctas + num_sms - 1) / num_sms * num_sms;
-    if (even <= N) ctas = even;
-  }
-  launch_kernel(linear_ws_kernel<NT, EPI, OUT>, ctas, WS_WARPS * 32, 0, stream, x, W, bias, (OUT*)out, residual, M, N, K, rope);
+                     int M, int N, int K, cudaStream_t stream, const WsRope& rope = WsRope{}, const WsNorm& norm = WsNorm{}) {
+  const int ctas = ws_ctas(N, EPI == WS_EPI_ROPE);
+  if (norm.ssq_in != nullptr)
+    launch_kernel(linear_ws_kernel<NT, EPI, OUT, true>, ctas, WS_WARPS * 32, 0, stream, x, W, bias, (OUT*)out, residual, M, N, K, rope, norm);
+  else
+    launch_kernel(linear_ws_kernel<NT, EPI, OUT, false>, ctas, WS_WARPS * 32, 0, stream, x, W, bias, (OUT*)out, residual, M, N, K, rope, norm);
   return launch_status("linear_ws");
 }
 
@@ -232,19 +307,42 @@ SLLM_EXPORT int sllm_linear_ws_supports(int M, int N, int K) {
   return M >= 1 && M <= 16 && N >= 16 && K >= 32 && K % 32 == 0;
 }
 
+// CTAs a launch for N output columns uses: the rows of the table of partial sums of squares that the
+// residual epilogue writes when it is asked for the next norm's input (see WsNorm).
+SLLM_EXPORT int sllm_linear_ws_parts(int N) { return ws_ctas(N, false); }
+
+static bool ws_norm_in(WsNorm& n, const float* ssq_in, int parts_in, float eps_in, int width_in) {
+  if (ssq_in == nullptr) return true;
+  if (parts_in < 1 || parts_in > WS_SSQ_MAX || width_in < 1 || ((uintptr_t)ssq_in & 15) != 0) return false;
+  n.ssq_in = ssq_in; n.parts_in = parts_in; n.eps_in = eps_in; n.inv_width_in = 1.0f / (float)width_in;
+  return true;
+}
+
 // residual != null: residual[M, N] (float32) += x W^T (+ bias) and `out` is ignored;
 // else out[M, N] = x W^T (+ bias) in out_dtype.
+// ssq_in != null: x is bfloat16(stream * gain) of a norm still owed and ssq_in [M][parts_in rounded up to 4] holds partial sums of
+// squares of the stream's rows (width_in wide): each row of the product is multiplied by rsqrt(sum / width_in + eps_in).
+// gain != null (residual epilogue only): also write xg_out [M, N] = bfloat16(residual * gain) and
+// ssq_out [M][sllm_linear_ws_parts(N) rounded up to 4], the next norm's input in the same form.
 SLLM_EXPORT int sllm_linear_ws(const void* x, const void* W, const float* bias, void* out, int out_dtype, float* residual,
-                               int M, int N, int K, cudaStream_t stream) {
+                               int M, int N, int K, const float* ssq_in, int parts_in, float eps_in, int width_in,
+                               const float* gain, void* xg_out, float* ssq_out, cudaStream_t stream) {
   SLLM_REQUIRE(sllm_linear_ws_supports(M, N, K), "linear_ws: sizes M=%d N=%d K=%d (needs M<=16, K%%32==0)", M, N, K);
   SLLM_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)W & 15) == 0, "linear_ws: operands must be 16-byte aligned");
   SLLM_REQUIRE(residual != nullptr || out != nullptr, "linear_ws: no destination");
+  WsNorm nm;
+  SLLM_REQUIRE(ws_norm_in(nm, ssq_in, parts_in, eps_in, width_in), "linear_ws: a table of %d partial sums (at most %d) over width %d",
+               parts_in, WS_SSQ_MAX, width_in);
+  if (gain != nullptr) {
+    SLLM_REQUIRE(residual != nullptr && xg_out != nullptr && ssq_out != nullptr, "linear_ws: the next norm's input needs the residual epilogue and both destinations");
+    nm.gain = gain; nm.xg_out = (__nv_bfloat16*)xg_out; nm.ssq_out = ssq_out;
+  }
   const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
   const __nv_bfloat16* wb = (const __nv_bfloat16*)W;
 #define GO(NT_)                                                                                                        \
-  if (residual) return launch_ws<NT_, WS_EPI_RESID, float>(xb, wb, bias, nullptr, residual, M, N, K, stream);          \
-  if (out_dtype == SLLM_BF16) return launch_ws<NT_, WS_EPI_STORE, __nv_bfloat16>(xb, wb, bias, out, nullptr, M, N, K, stream); \
-  return launch_ws<NT_, WS_EPI_STORE, float>(xb, wb, bias, out, nullptr, M, N, K, stream);
+  if (residual) return launch_ws<NT_, WS_EPI_RESID, float>(xb, wb, bias, nullptr, residual, M, N, K, stream, WsRope{}, nm);          \
+  if (out_dtype == SLLM_BF16) return launch_ws<NT_, WS_EPI_STORE, __nv_bfloat16>(xb, wb, bias, out, nullptr, M, N, K, stream, WsRope{}, nm); \
+  return launch_ws<NT_, WS_EPI_STORE, float>(xb, wb, bias, out, nullptr, M, N, K, stream, WsRope{}, nm);
   if (M <= 8) { GO(1) }
   GO(2)
 #undef GO
@@ -257,23 +355,26 @@ SLLM_EXPORT int sllm_linear_ws_rope_supports(int M, int N, int K, int nq, int nk
 
 // The fused q|k|v product of an attention layer with its bias, rotary encoding and cache write:
 // x [M, K] and W [(nq + 2 nkv) * hd, K] bfloat16; table null or rot == 0: no rotation, else rot == hd and
-// table [max_pos][2][hd/2] float32; slot_mapping null: keys and values are not written.
+// table [max_pos][2][hd/2] float32; slot_mapping null: keys and values are not written.  ssq_in: as for sllm_linear_ws.
 SLLM_EXPORT int sllm_linear_ws_rope(const void* x, const void* W, const float* bias, int M, int N, int K, const int* positions,
                                     const float* table, int rot, int max_pos, int nq, int nkv, int hd, const int* slot_mapping,
                                     int page_size, int num_pages, void* k_cache, void* v_cache, void* q_out,
-                                    cudaStream_t stream) {
+                                    const float* ssq_in, int parts_in, float eps_in, int width_in, cudaStream_t stream) {
   SLLM_REQUIRE(sllm_linear_ws_rope_supports(M, N, K, nq, nkv, hd, rot),
                "linear_ws_rope: sizes M=%d N=%d K=%d nq=%d nkv=%d hd=%d rot=%d", M, N, K, nq, nkv, hd, rot);
   SLLM_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)W & 15) == 0, "linear_ws_rope: operands must be 16-byte aligned");
   SLLM_REQUIRE(q_out != nullptr && (rot == 0 || (table != nullptr && positions != nullptr && max_pos > 0)),
                "linear_ws_rope: destination or rotary table missing");
   SLLM_REQUIRE(slot_mapping == nullptr || (k_cache && v_cache && page_size > 0 && num_pages > 0), "linear_ws_rope: cache arguments missing");
+  WsNorm nm;
+  SLLM_REQUIRE(ws_norm_in(nm, ssq_in, parts_in, eps_in, width_in), "linear_ws_rope: a table of %d partial sums (at most %d) over width %d",
+               parts_in, WS_SSQ_MAX, width_in);
   WsRope r;
   r.positions = positions; r.table = rot > 0 ? table : nullptr; r.slot_mapping = slot_mapping;
   r.k_cache = (__nv_bfloat16*)k_cache; r.v_cache = (__nv_bfloat16*)v_cache; r.q_out = (__nv_bfloat16*)q_out;
   r.max_pos = max_pos; r.nq = nq; r.nkv = nkv; r.hd = hd; r.page_size = page_size; r.num_pages = num_pages;
   const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
   const __nv_bfloat16* wb = (const __nv_bfloat16*)W;
-  if (M <= 8) return launch_ws<1, WS_EPI_ROPE, __nv_bfloat16>(xb, wb, bias, nullptr, nullptr, M, N, K, stream, r);
-  return launch_ws<2, WS_EPI_ROPE, __nv_bfloat16>(xb, wb, bias, nullptr, nullptr, M, N, K, stream, r);
+  if (M <= 8) return launch_ws<1, WS_EPI_ROPE, __nv_bfloat16>(xb, wb, bias, nullptr, nullptr, M, N, K, stream, r, nm);
+  return launch_ws<2, WS_EPI_ROPE, __nv_bfloat16>(xb, wb, bias, nullptr, nullptr, M, N, K, stream, r, nm);
 }

@@ -11,7 +11,7 @@ from .. import ops
 from ..config.plan import ModelPlan
 from ..parts import standard as _standard  # noqa: F401  (registers the standard parts)
 from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS,
-                          LayerCache, StepContext, TensorSpec)
+                          LayerCache, OwedNorm, StepContext, TensorSpec)
 
 
 FAMILIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS}
@@ -115,10 +115,16 @@ class CausalLM:
         if self.position is not None:
             self.position.on_embedding(residual, step)
         delta = None
-        for i, e in enumerate(self.plan.run_list):
-            layer = self.layers[e.layer]
-            delta = layer.block.forward(residual, delta, step, caches[i], self.position,
-                                        write_cache=e.cache_from is None)
+        runs = self.plan.run_list
+        for i, e in enumerate(runs):
+            block = self.layers[e.layer].block
+            kw = {}
+            if getattr(block, "accepts_next_norm", False) and i + 1 < len(runs):
+                # the norm that reads the stream next: this block's last product may prepare its input
+                kw["next_norm"] = getattr(self.layers[runs[i + 1].layer].block, "first_norm", None)
+            delta = block.forward(residual, delta, step, caches[i], self.position, write_cache=e.cache_from is None, **kw)
+        if isinstance(delta, OwedNorm):          # (a block handed one on although nothing asked: take the stream as it is)
+            delta = None
         if step.logit_rows.numel() == 0:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
         res_rows = ops.gather_rows(residual, step.logit_rows)

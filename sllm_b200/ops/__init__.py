@@ -250,10 +250,31 @@ def ws_supports(M: int, N: int, K: int) -> bool:
     return M <= WS_MAX_ROWS and N <= WS_MAX_COLS and bool(lib().sllm_linear_ws_supports(int(M), int(N), int(K)))
 
 
-def linear_ws(x, w, bias, out_dtype, residual=None):
+class RowScale:
+    """An RMSNorm still owed on an activation: the activation is bfloat16(stream * gain), ``ssq`` is float32
+    ``[M, stride]`` (stride = ``parts`` rounded up to 4) with ``parts`` partial sums of squares of each row of
+    the stream (``width`` wide), and whoever multiplies the activation by a matrix multiplies each row of the
+    result by ``rsqrt(sum(ssq[row, :parts]) / width + eps)``: W (x g / rms) = (W (x g)) / rms."""
+    __slots__ = ("ssq", "parts", "eps", "width")
+
+    def __init__(self, ssq, parts: int, eps: float, width: int):
+        self.ssq, self.parts, self.eps, self.width = ssq, int(parts), float(eps), int(width)
+
+    def args(self):
+        return _p(self.ssq), self.parts, self.eps, self.width
+
+
+_NO_SCALE = (None, 0, 0.0, 0)
+MAX_SCALE_PARTS = 384          # partial sums a consumer keeps in shared memory per row
+
+
+def linear_ws(x, w, bias, out_dtype, residual=None, scale: RowScale | None = None, next_gain=None):
     """The warp-split streaming kernel (at most 16 tokens): ``x @ w.T (+ bias)`` in ``out_dtype``,
-    or, given ``residual`` (float32 ``[M, N]``), added into it in place (returns None)."""
-    _chk(x, w, bias, residual)
+    or, given ``residual`` (float32 ``[M, N]``), added into it in place (returns None).  ``scale``: a norm
+    still owed on ``x`` (`RowScale`).  ``next_gain`` (with ``residual``): the gain of the norm that follows; the
+    kernel then also writes that norm's input in the owed form and ``(xg, RowScale)`` is returned (the scale's
+    eps is left at 0 for the caller to set)."""
+    _chk(x, w, bias, residual, next_gain)
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K:
@@ -263,7 +284,18 @@ def linear_ws(x, w, bias, out_dtype, residual=None):
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     elif residual.dtype != torch.float32 or tuple(residual.shape) != (M, N):
         raise KernelError(f"linear: residual {tuple(residual.shape)} {residual.dtype} does not fit [{M}, {N}] float32")
-    call("sllm_linear_ws", _p(x), _p(w), _p(bias), _p(out), _dtc(out_dtype), _p(residual), M, N, K, _stream())
+    xg = ssq = None
+    parts = 0
+    if next_gain is not None:
+        if residual is None or next_gain.dtype != torch.float32 or next_gain.numel() != N:
+            raise KernelError("linear_ws: the next norm's input needs the residual epilogue and a float32 gain of N values")
+        parts = int(lib().sllm_linear_ws_parts(N))
+        xg = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        ssq = torch.empty((M, (parts + 3) & ~3), dtype=torch.float32, device=x.device)
+    call("sllm_linear_ws", _p(x), _p(w), _p(bias), _p(out), _dtc(out_dtype), _p(residual), M, N, K,
+         *(scale.args() if scale is not None else _NO_SCALE), _p(next_gain), _p(xg), _p(ssq), _stream())
+    if next_gain is not None:
+        return xg, RowScale(ssq, parts, 0.0, N)
     return out
 
 
@@ -276,6 +308,22 @@ def can_accumulate(x: torch.Tensor, w: torch.Tensor) -> bool:
 def linear_accumulate(x, w, bias, residual) -> None:
     """``residual += x @ w.T (+ bias)`` in one kernel (see `can_accumulate`)."""
     linear_ws(x, w, bias, torch.float32, residual=residual)
+
+
+_NORM_FUSED = os.environ.get("SLLM_NORM_FUSED", "1") != "0"     # 0: every RMSNorm of a decode step is a kernel of its own
+
+
+def can_accumulate_norm(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether `linear_accumulate_norm` has a kernel for these operands."""
+    return _NORM_FUSED and can_accumulate(x, w) and int(lib().sllm_linear_ws_parts(w.shape[0])) <= MAX_SCALE_PARTS
+
+
+def linear_accumulate_norm(x, w, bias, residual, gain, eps: float):
+    """``residual += x @ w.T (+ bias)`` and, from the same kernel, the input of the RMSNorm (``gain``, ``eps``)
+    that follows, in the owed form: ``(bfloat16(residual * gain), RowScale)``."""
+    xg, scale = linear_ws(x, w, bias, torch.float32, residual=residual, next_gain=gain)
+    scale.eps = float(eps)
+    return xg, scale
 
 
 def _stream_splits(N: int, K: int) -> int:
@@ -330,8 +378,27 @@ def silu_mul(gu: torch.Tensor, interleave: int, out_dtype: torch.dtype) -> torch
     return out
 
 
-def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, out_dtype: torch.dtype) -> torch.Tensor:
-    """``silu(x Wg^T) * (x Wu^T)`` with gate and up rows interleaved in one matrix."""
+def silu_scaled_supports(x, w_gate_up, interleave: int, out_dtype) -> bool:
+    """Whether `linear_silu_mul` takes an input whose norm is still owed (``scale``)."""
+    M, K = x.shape
+    N = w_gate_up.shape[0]
+    return (x.is_cuda and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and interleave == 8 and M <= 16
+            and N % 16 == 0 and stream_supports(M, N, K))
+
+
+def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, out_dtype: torch.dtype,
+                    scale: RowScale | None = None) -> torch.Tensor:
+    """``silu(x Wg^T) * (x Wu^T)`` with gate and up rows interleaved in one matrix.  ``scale``: a norm still
+    owed on ``x`` (`RowScale`; see `silu_scaled_supports`)."""
+    if scale is not None:
+        if not silu_scaled_supports(x, w_gate_up, interleave, out_dtype):
+            raise KernelError("linear_silu_mul: no kernel takes this input with its norm still owed")
+        _chk(x, w_gate_up, scale.ssq)
+        M, K = x.shape
+        N = w_gate_up.shape[0]
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+        call("sllm_linear_stream_silu_scaled", _p(x), _p(w_gate_up), _p(out), M, N, K, *scale.args(), _stream())
+        return out
     if x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and interleave == 8 and x.is_cuda:
         M, K = x.shape
         N = w_gate_up.shape[0]
@@ -360,11 +427,13 @@ def qkv_rope_supports(x, w, table, rotary_dim, nq, nkv, hd, k_cache) -> bool:
                                                                           int(hd), rot))
 
 
-def linear_rope_kv_write(x, w, bias, positions, table, rotary_dim, nq, nkv, hd, slot_mapping, k_cache, v_cache):
+def linear_rope_kv_write(x, w, bias, positions, table, rotary_dim, nq, nkv, hd, slot_mapping, k_cache, v_cache,
+                         scale: RowScale | None = None):
     """``x @ w.T`` for the fused q|k|v matrix with what follows it in an attention layer done in the
     product's epilogue: bias, rotary encoding of the query and key heads by the tokens' positions,
     the new keys and values written to ``slot_mapping`` of the paged caches (not written when it is
-    None).  Returns the rotated queries ``[T, nq*hd]`` bfloat16.  Few tokens only (`qkv_rope_supports`)."""
+    None).  Returns the rotated queries ``[T, nq*hd]`` bfloat16.  Few tokens only (`qkv_rope_supports`).
+    ``scale``: a norm still owed on ``x`` (`RowScale`)."""
     _chk(x, w, bias, positions, table, slot_mapping, k_cache, v_cache)
     M, K = x.shape
     N = w.shape[0]
@@ -377,7 +446,8 @@ def linear_rope_kv_write(x, w, bias, positions, table, rotary_dim, nq, nkv, hd, 
     q = torch.empty((M, nq * hd), dtype=torch.bfloat16, device=x.device)
     max_pos = table.shape[0] if table is not None else 0
     call("sllm_linear_ws_rope", _p(x), _p(w), _p(bias), M, N, K, _p(positions), _p(table), rot, max_pos, nq, nkv, hd,
-         _p(slot_mapping), page_size, num_pages, _p(k_cache), _p(v_cache), _p(q), _stream())
+         _p(slot_mapping), page_size, num_pages, _p(k_cache), _p(v_cache), _p(q),
+         *(scale.args() if scale is not None else _NO_SCALE), _stream())
     return q
 
 

@@ -69,10 +69,15 @@ def _declare(L):
         "sllm_linear_tc_splits": [c_int, c_int],
         "sllm_linear_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "sllm_linear_ws_supports": [c_int, c_int, c_int],
-        "sllm_linear_ws": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+        "sllm_linear_ws": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                           c_void_p, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        "sllm_linear_ws_parts": [c_int],
+        "sllm_linear_stream_silu_scaled": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_float, c_int,
+                                           c_void_p],
         "sllm_linear_ws_rope_supports": [c_int, c_int, c_int, c_int, c_int, c_int, c_int],
         "sllm_linear_ws_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-                                c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+                                c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_int, c_float, c_int, c_void_p],
         "sllm_linear_stream_supports": [c_int, c_int, c_int],
         "sllm_linear_stream_splits": [c_int, c_int],
         "sllm_linear_stream": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,

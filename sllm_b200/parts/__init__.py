@@ -1,9 +1,9 @@
 from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, FeedForward,
-                   GroupView, LayerCache, Mixer, Norm, PagedKV, Part,
+                   GroupView, LayerCache, Mixer, Norm, OwedNorm, PagedKV, Part,
                    PositionEncoding, Registry, SlotState, StepContext, TensorSpec)
 
 __all__ = [
     "BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "FeedForward",
-    "GroupView", "LayerCache", "Mixer", "Norm", "PagedKV", "Part",
+    "GroupView", "LayerCache", "Mixer", "Norm", "OwedNorm", "PagedKV", "Part",
     "PositionEncoding", "Registry", "SlotState", "StepContext", "TensorSpec",
 ]

@@ -24,10 +24,15 @@ Interfaces (all tensors are torch tensors on the engine's device):
                     A mixer or feed-forward whose class sets ``accepts_residual = True``
                     is also given ``residual=`` (the float32 stream) and may add its
                     term into it in place and return None.
-``Block``           ``forward(residual, delta, step, cache) -> delta``: arranges
-                    norms, mixer and feed-forward around the residual stream; the
+``Block``           built from the dict of the layer's parts by role;
+                    ``forward(residual, delta, step, cache, position, write_cache) -> delta``:
+                    arranges norms, mixer and feed-forward around the residual stream; the
                     last term is handed on un-added, so that the next norm fuses
-                    the addition.
+                    the addition.  ``cache_need()`` says what the layer wants of the
+                    cache manager.  A block that sets ``accepts_next_norm = True`` is also
+                    given ``next_norm=`` (the first norm of the layer that runs next) and may
+                    hand on an `OwedNorm` made for it; it then exposes its own first norm as
+                    ``first_norm``.
 """
 
 from __future__ import annotations
@@ -118,6 +123,32 @@ class LayerCache:
     state: torch.Tensor | None = None   # [num_slots, *shape] float32
 
 
+# ---- a norm whose division is still owed --------------------------------------------
+
+@dataclass
+class OwedNorm:
+    """What a norm would have returned, with the division by the root mean square still to do.
+
+    A product that completes the residual stream can, in its own epilogue, write the next norm's input
+    as ``x = compute_dtype(stream * gain)`` together with partial sums of squares of the stream's rows
+    (``scale``, an `ops.RowScale`); the part that consumes the normed activations multiplies the rows of
+    ITS product by the reciprocal root mean square, which is the same thing:
+    W (x g / rms) = (W (x g)) / rms.  A decode step then needs no kernel for that norm.
+
+    The protocol is optional on every side.  A mixer or feed-forward whose class sets
+    ``accepts_next_norm = True`` is handed ``next_norm=`` (the `Norm` that will read the stream next, or None)
+    and may return an `OwedNorm` made for it instead of None or a term; a norm offers itself through
+    `Norm.as_rms()`.  A consumer that cannot take one calls `plain()`, which runs the norm as a kernel of
+    its own on the (complete) stream."""
+    x: torch.Tensor
+    scale: object                       # ops.RowScale
+    norm: "Norm"                        # the norm this stands for
+    residual: torch.Tensor              # the stream it was made from
+
+    def plain(self) -> torch.Tensor:
+        return self.norm.add_norm(self.residual, None)
+
+
 # ---- registries ---------------------------------------------------------------
 
 class Registry:
@@ -198,6 +229,11 @@ class FeedForward(Part):
 class Norm(Part):
     def add_norm(self, residual, delta):
         raise NotImplementedError
+
+    def as_rms(self):
+        """``(gain float32 [H], eps)`` if this norm is y = x * rsqrt(mean(x^2) + eps) * gain, so that a
+        product's epilogue may prepare its input (`OwedNorm`); None otherwise."""
+        return None
 
 
 class PositionEncoding(Part):

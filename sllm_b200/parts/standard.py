@@ -12,7 +12,7 @@ import torch
 
 from .. import ops
 from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, FeedForward,
-                   LayerCache, Mixer, Norm, PagedKV, Part, PositionEncoding,
+                   LayerCache, Mixer, Norm, OwedNorm, PagedKV, Part, PositionEncoding,
                    StepContext, TensorSpec)
 
 
@@ -31,10 +31,16 @@ class Linear:
         rows may split its k dimension over more SMs."""
         return ops.linear(x, self.weight, self.bias, out_dtype, allow_partials)
 
-    def into(self, x: torch.Tensor, residual: torch.Tensor | None):
+    def into(self, x: torch.Tensor, residual: torch.Tensor | None, next_norm=None):
         """The layer's term for the residual stream: added into ``residual`` in place where a
-        kernel does that (returns None), else returned for the next norm to add."""
+        kernel does that (returns None), else returned for the next norm to add.  Where the kernel
+        that completes the stream can also prepare the input of ``next_norm`` (the norm that reads the
+        stream next), that input comes back as an `OwedNorm`."""
         if residual is not None and ops.can_accumulate(x, self.weight):
+            rms = next_norm.as_rms() if next_norm is not None else None
+            if rms is not None and ops.can_accumulate_norm(x, self.weight):
+                xg, scale = ops.linear_accumulate_norm(x, self.weight, self.bias, residual, *rms)
+                return OwedNorm(xg, scale, next_norm, residual)
             ops.linear_accumulate(x, self.weight, self.bias, residual)
             return None
         return ops.linear(x, self.weight, self.bias, torch.float32, True)
@@ -67,6 +73,9 @@ class RMSNorm(Norm):
 
     def add_norm(self, residual, delta):
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.dtype)
+
+    def as_rms(self):
+        return (self.weight, self.eps) if self.dtype == torch.bfloat16 else None
 
     def weight_bytes(self):
         return self.size * 4
@@ -155,14 +164,21 @@ class Attention(Mixer):
         self.out = Linear(self._matrix(fetch(f"{on}.weight")), ob)
 
     accepts_residual = True
+    accepts_next_norm = True
     MAX_HEAD_DIM = 256
 
-    def forward(self, x, step: StepContext, cache: LayerCache, position, write_cache=True, residual=None):
+    def forward(self, x, step: StepContext, cache: LayerCache, position, write_cache=True, residual=None, next_norm=None):
         g = step.groups[cache.group]
         table = getattr(position, "table", None)           # an encoding without a rotary table: no rotation
         rot = getattr(position, "rotary_dim", 0) if table is not None else 0
         slots = g.slot_mapping if write_cache else None
-        if ops.qkv_rope_supports(x, self.qkv.weight, table, rot, self.nq, self.nkv, self.hd, cache.k):
+        owed = x if isinstance(x, OwedNorm) else None
+        if owed is not None and not ops.qkv_rope_supports(owed.x, self.qkv.weight, table, rot, self.nq, self.nkv, self.hd, cache.k):
+            x, owed = owed.plain(), None
+        if owed is not None:
+            q = ops.linear_rope_kv_write(owed.x, self.qkv.weight, self.qkv_b, step.positions, table, rot,
+                                         self.nq, self.nkv, self.hd, slots, cache.k, cache.v, scale=owed.scale)
+        elif ops.qkv_rope_supports(x, self.qkv.weight, table, rot, self.nq, self.nkv, self.hd, cache.k):
             # few tokens: bias, rotation and the cache write happen as the product's rows leave their CTA
             q = ops.linear_rope_kv_write(x, self.qkv.weight, self.qkv_b, step.positions, table, rot,
                                          self.nq, self.nkv, self.hd, slots, cache.k, cache.v)
@@ -172,7 +188,7 @@ class Attention(Mixer):
                                   slots, cache.k, cache.v, self.dtype)
         o = ops.paged_attention(q, cache.k, cache.v, step, cache.group,
                                 self.nq, self.nkv, self.hd, self.scale, self.window)
-        return self.out.into(o, residual)
+        return self.out.into(o, residual, next_norm)
 
     def weight_bytes(self):
         return self.qkv.nbytes() + self.out.nbytes() + (self.qkv_b.numel() * 4 if self.qkv_b is not None else 0)
@@ -211,10 +227,16 @@ class SwiGLU(FeedForward):
         self.down = Linear(self._matrix(fetch(f"{d}.weight")))
 
     accepts_residual = True
+    accepts_next_norm = True
 
-    def forward(self, x, step, residual=None):
+    def forward(self, x, step, residual=None, next_norm=None):
+        if isinstance(x, OwedNorm):
+            if ops.silu_scaled_supports(x.x, self.gate_up.weight, self.interleave, self.dtype):
+                act = ops.linear_silu_mul(x.x, self.gate_up.weight, self.interleave, self.dtype, scale=x.scale)
+                return self.down.into(act, residual, next_norm)
+            x = x.plain()
         act = ops.linear_silu_mul(x, self.gate_up.weight, self.interleave, self.dtype)   # [T, I]
-        return self.down.into(act, residual)
+        return self.down.into(act, residual, next_norm)
 
     def weight_bytes(self):
         return self.gate_up.nbytes() + self.down.nbytes()
@@ -237,14 +259,35 @@ class PreNormBlock:
     def cache_need(self):
         return self.mixer.cache_need()
 
-    def forward(self, residual, delta, step, cache, position, write_cache=True):
-        x = self.mixer_norm.add_norm(residual, delta)
-        # a part that says so may add its term into the stream itself and hand back None
-        if getattr(self.mixer, "accepts_residual", False):
-            d = self.mixer.forward(x, step, cache, position, write_cache, residual=residual)
-        else:
-            d = self.mixer.forward(x, step, cache, position, write_cache)
-        x = self.ffn_norm.add_norm(residual, d)
-        if getattr(self.ffn, "accepts_residual", False):
-            return self.ffn.forward(x, step, residual=residual)
-        return self.ffn.forward(x, step)
+    accepts_next_norm = True
+
+    @property
+    def first_norm(self):
+        return self.mixer_norm
+
+    @staticmethod
+    def _call(part, *args, residual, next_norm):
+        """A part is told what it says it understands: the stream to add into, the norm that reads it next."""
+        kw = {}
+        if getattr(part, "accepts_residual", False):
+            kw["residual"] = residual
+            if getattr(part, "accepts_next_norm", False):
+                kw["next_norm"] = next_norm       # (only a part that completes the stream itself can prepare it)
+        return part.forward(*args, **kw)
+
+    def _normed(self, norm, residual, delta):
+        """The input of the part behind ``norm``: an `OwedNorm` made for this very norm as it is (a part
+        that cannot take it asks for the plain form itself), anything else through the norm's kernel."""
+        if isinstance(delta, OwedNorm):
+            return delta if delta.norm is norm else norm.add_norm(residual, None)
+        return norm.add_norm(residual, delta)
+
+    def forward(self, residual, delta, step, cache, position, write_cache=True, next_norm=None):
+        x = self._normed(self.mixer_norm, residual, delta)
+        if isinstance(x, OwedNorm) and not getattr(self.mixer, "accepts_next_norm", False):
+            x = x.plain()
+        d = self._call(self.mixer, x, step, cache, position, write_cache, residual=residual, next_norm=self.ffn_norm)
+        x = self._normed(self.ffn_norm, residual, d)
+        if isinstance(x, OwedNorm) and not getattr(self.ffn, "accepts_next_norm", False):
+            x = x.plain()
+        return self._call(self.ffn, x, step, residual=residual, next_norm=next_norm)

@@ -776,6 +776,76 @@ def test_linear_ws(M, N, K):
         assert torch.equal(one[0], ops.linear_ws(x, w, b, torch.float32)[M - 1])
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 11, 16])
+@pytest.mark.parametrize("H,K", [(3584, 3584), (3584, 18944), (896, 4864), (1000, 320), (96, 64)])
+def test_an_rmsnorm_owed_by_one_product_and_paid_by_the_next(M, H, K):
+    """The product that completes the residual stream also writes the next RMSNorm's input as
+    bfloat16(stream * gain) with partial sums of squares, and the products that consume it (plain, the
+    fused q|k|v with its rotary epilogue, gate|up with SiLU*mul) scale their rows by the reciprocal root
+    mean square: the same numbers as the norm kernel followed by the plain products, to bfloat16 rounding
+    (y = x * rsqrt(mean(x^2) + eps) * gain, ref/standard.py:25-31)."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(41)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(H, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    b = torch.randn(H, device="cuda", generator=g)
+    gain = 1 + 0.3 * torch.randn(H, device="cuda", generator=g)
+    eps = 1e-5
+    res = 3 * torch.randn(M, H, device="cuda", generator=g)
+    stream = res + x.float() @ w.float().t() + b
+    assert ops.can_accumulate_norm(x[:8].contiguous(), w)
+    xg, scale = ops.linear_accumulate_norm(x, w, b, res, gain, eps)
+    torch.testing.assert_close(res, stream, rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(xg.float(), (res * gain).bfloat16().float(), rtol=1e-2, atol=1e-2)
+    assert scale.parts <= ops.MAX_SCALE_PARTS and scale.width == H and scale.eps == eps
+    torch.testing.assert_close(scale.ssq[:, :scale.parts].sum(1), (res ** 2).sum(1), rtol=1e-4, atol=1e-4)
+    normed = res * torch.rsqrt((res ** 2).mean(1, keepdim=True) + eps) * gain          # what the norm kernel returns
+    # a plain product of the normed activations
+    N2 = 272
+    w2 = (torch.randn(N2, H, device="cuda", generator=g) / H ** 0.5).bfloat16()
+    b2 = torch.randn(N2, device="cuda", generator=g)
+    want = normed @ w2.float().t() + b2
+    if H % 32 == 0:
+        got = ops.linear_ws(xg, w2, b2, torch.float32, scale=scale)
+        torch.testing.assert_close(got, want, rtol=2e-2, atol=2e-2)
+        res2 = torch.randn(M, N2, device="cuda", generator=g)
+        expect = res2 + want
+        ops.linear_ws(xg, w2, b2, torch.float32, residual=res2, scale=scale)
+        torch.testing.assert_close(res2, expect, rtol=2e-2, atol=2e-2)
+    # gate|up with SiLU*mul
+    inter = 264
+    wgu = (torch.randn(2 * inter, H, device="cuda", generator=g) / H ** 0.5).bfloat16()
+    if ops.silu_scaled_supports(xg, wgu, 8, torch.bfloat16):
+        got = ops.linear_silu_mul(xg, wgu, 8, torch.bfloat16, scale=scale).float()
+        gu = (normed @ wgu.float().t()).reshape(M, inter // 8, 2, 8)
+        want = (torch.nn.functional.silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(M, inter)
+        torch.testing.assert_close(got, want, rtol=2e-2, atol=2e-2)
+    else:
+        assert H % 128 != 0
+    # the fused q|k|v product with bias, rotation and the cache write
+    nq, nkv, hd, ps, pages, max_pos = 3, 1, 32, 8, 9, 100
+    wq = (torch.randn((nq + 2 * nkv) * hd, H, device="cuda", generator=g) / H ** 0.5).bfloat16()
+    bq = torch.randn((nq + 2 * nkv) * hd, device="cuda", generator=g)
+    pos = torch.randint(0, max_pos, (M,), device="cuda", generator=g, dtype=torch.int32)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * (1e4 ** (-torch.arange(0, hd, 2, dtype=torch.float64) / hd))[None]
+    table = torch.stack([ang.cos(), ang.sin()], 1).float().cuda()
+    slots = torch.randperm(pages * ps, device="cuda", generator=g)[:M].int()
+    kc = [torch.zeros(pages, nkv, ps, hd, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    vc = [torch.zeros(pages, nkv, ps, hd, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    if H % 32 == 0:
+        got = ops.linear_rope_kv_write(xg, wq, bq, pos, table, hd, nq, nkv, hd, slots, kc[0], vc[0], scale=scale)
+        want = ref.rope_kv_write(normed @ wq.float().t(), bq, pos, table, hd, nq, nkv, hd, slots, kc[1], vc[1], torch.bfloat16)
+        _close(got, want, torch.bfloat16, scale=4.0)
+        _close(kc[0], kc[1], torch.bfloat16, scale=4.0)
+        _close(vc[0], vc[1], torch.bfloat16, scale=4.0)
+    # the partial sums are written per CTA and added in a fixed order: the same call gives the same bits
+    again = stream - (x.float() @ w.float().t() + b)
+    first = again.clone()
+    xg_a, scale_a = ops.linear_accumulate_norm(x, w, b, first, gain, eps)
+    xg_b, scale_b = ops.linear_accumulate_norm(x, w, b, again, gain, eps)
+    assert torch.equal(xg_a, xg_b) and torch.equal(scale_a.ssq[:, :scale_a.parts], scale_b.ssq[:, :scale_b.parts])
+
+
 @pytest.mark.parametrize("nq,nkv,hd,ps,window", [(28, 4, 128, 16, None), (14, 2, 64, 16, None), (8, 1, 128, 32, 40),
                                                  (6, 3, 64, 8, 9), (16, 2, 128, 64, None), (7, 7, 64, 16, None)])
 @pytest.mark.parametrize("case", ["decode", "decode_split", "short"])
