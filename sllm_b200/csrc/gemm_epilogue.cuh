@@ -11,6 +11,32 @@ namespace sllm {
 #define TG_EPI_BF16 1
 #define TG_EPI_SILU 2
 
+// The epilogue warps run one to a scheduler with nothing to hide a dependent instruction behind, so what they
+// do per value counts: the bias is fetched in 16-byte pieces and only where there is one, the bounds are
+// tested per chunk, and SiLU uses the fast exponential and reciprocal (the result is rounded to bfloat16).
+__device__ __forceinline__ void tg_values(const uint32_t (&r)[32], float (&v)[32], int n, int N, const float* __restrict__ bias) {
+  if (bias == nullptr) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+  } else if (n + 32 <= N && (reinterpret_cast<uintptr_t>(bias) & 15) == 0) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 b = __ldg(reinterpret_cast<const float4*>(bias + n) + j);
+      v[4 * j] = __uint_as_float(r[4 * j]) + b.x;
+      v[4 * j + 1] = __uint_as_float(r[4 * j + 1]) + b.y;
+      v[4 * j + 2] = __uint_as_float(r[4 * j + 2]) + b.z;
+      v[4 * j + 3] = __uint_as_float(r[4 * j + 3]) + b.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) + (n + i < N ? bias[n + i] : 0.f);
+  }
+}
+__device__ __forceinline__ float tg_silu_mul(float g, float u) {
+  // silu(g) * u = g * u / (1 + e^-g) (ref/qwen3_5.py:28-29)
+  return __fdividef(g * u, 1.0f + __expf(-g));
+}
+
 // r: columns n .. n + 31 of row m of C = A W^T (float32 bits); out is [M, N] (or [M, N/2] for the SiLU form)
 template <int EPI>
 __device__ __forceinline__ void tg_store_chunk(const uint32_t (&r)[32], int m, int n, int N, const float* __restrict__ bias,
@@ -24,8 +50,7 @@ __device__ __forceinline__ void tg_store_chunk(const uint32_t (&r)[32], int m, i
       float v[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float g = __uint_as_float(r[blk * 16 + i]), u = __uint_as_float(r[blk * 16 + 8 + i]);
-        v[i] = g * (1.0f / (1.0f + expf(-g))) * u;
+        v[i] = tg_silu_mul(__uint_as_float(r[blk * 16 + i]), __uint_as_float(r[blk * 16 + 8 + i]));
       }
       if (((N >> 1) & 7) == 0) {               // rows of the result are 16-byte aligned
         *reinterpret_cast<uint4*>(o + blk * 8) = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
@@ -36,8 +61,7 @@ __device__ __forceinline__ void tg_store_chunk(const uint32_t (&r)[32], int m, i
     }
   } else {
     float v[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) + ((bias && n + i < N) ? bias[n + i] : 0.f);
+    tg_values(r, v, n, N, bias);
     const bool whole = n + 32 <= N;
     if constexpr (EPI == TG_EPI_F32) {
       float* o = reinterpret_cast<float*>(out) + (size_t)m * N + n;
@@ -59,6 +83,54 @@ __device__ __forceinline__ void tg_store_chunk(const uint32_t (&r)[32], int m, i
 #pragma unroll
         for (int i = 0; i < 32; ++i) if (n + i < N) o[i] = __float2bfloat16_rn(v[i]);
       }
+    }
+  }
+}
+
+// ---- the same through shared memory and TMA stores ------------------------------------------------
+// A lane of an epilogue warp holds one row of the accumulator, so direct stores put every lane on a line of
+// its own: 32 requests of 16 bytes an instruction, and the step from tensor memory to global memory takes
+// longer than the products it should hide behind.  Here the warp stages a box of 32 rows x 128 bytes of the
+// result in shared memory (128-byte swizzle: the 16-byte piece j of row r lies at piece j ^ (r & 7)) and one
+// lane hands it to the TMA unit, which writes whole lines and clips what lies outside the matrix.
+// A box is 32 float32, 64 bfloat16 or (SiLU form) 128 accumulator columns wide.
+template <int EPI> struct TgBox {
+  static constexpr int ACC_COLS = EPI == TG_EPI_F32 ? 32 : (EPI == TG_EPI_BF16 ? 64 : 128);   // accumulator columns a box covers
+  static constexpr int ELEM = EPI == TG_EPI_F32 ? 4 : 2;
+};
+
+__device__ __forceinline__ void tg_put_piece(unsigned char* row_base, int row, int piece, uint4 v) {
+  *reinterpret_cast<uint4*>(row_base + ((piece ^ (row & 7)) << 4)) = v;
+}
+
+// the 32 accumulator columns `sub` (0 ..) of a box, of this lane's row, into the staged box; n is the result
+// column (of C) of the chunk's first accumulator column, for the bias
+template <int EPI>
+__device__ __forceinline__ void tg_stage_chunk(const uint32_t (&r)[32], unsigned char* stage, int row, int sub, int n, int N,
+                                               const float* __restrict__ bias) {
+  unsigned char* row_base = stage + row * 128;
+  if constexpr (EPI == TG_EPI_SILU) {
+    // 32 columns: 8 gate, 8 up, 8 gate, 8 up -> 16 results = 2 pieces; a box holds 4 such chunks
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk) {
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = tg_silu_mul(__uint_as_float(r[blk * 16 + i]), __uint_as_float(r[blk * 16 + 8 + i]));
+      tg_put_piece(row_base, row, sub * 2 + blk, make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7])));
+    }
+  } else {
+    float v[32];
+    tg_values(r, v, n, N, bias);
+    if constexpr (EPI == TG_EPI_F32) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        tg_put_piece(row_base, row, j, make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
+                                                  __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3])));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        tg_put_piece(row_base, row, sub * 4 + j, make_uint4(pack2(v[8 * j], v[8 * j + 1]), pack2(v[8 * j + 2], v[8 * j + 3]),
+                                                            pack2(v[8 * j + 4], v[8 * j + 5]), pack2(v[8 * j + 6], v[8 * j + 7])));
     }
   }
 }

@@ -134,7 +134,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % TP_STAGES, round = it / TP_STAGES;
           if (!mbar_wait(&empty[s], (round & 1) ^ 1) || *failed) {
-            if (!*failed) { *failed = 1; atomicExch(status, 1); }
+            if (!*failed) { *failed = 1; atomicExch(status, 41); }
             gave_up = true;
             break;
           }
@@ -157,29 +157,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (lane == 0 && rank == 0) {
       // instruction descriptor: D float32, A and B bfloat16, both K-major, N = 256, M = 256 (the pair's)
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TP_BN >> 3) << 17) | ((uint32_t)((2 * TP_BM) >> 4) << 24);
-      int it = 0, local = 0;
+      const uint64_t desc0 = umma_desc(smem_u32(smem));
+      int local = 0;
+      uint32_t st = 0, ph = 0;                      // the stage to consume next and its barrier's parity
       for (int tile = pair; tile < tiles && !*failed; tile += pairs, ++local) {
         const int b = local & 1;
         if (!mbar_wait(&acc_empty[b], ((local >> 1) & 1) ^ 1) || *failed) {     // both epilogues have drained this buffer
-          if (!*failed) { *failed = 2; atomicExch(status, 2); }
+          if (!*failed) { *failed = 2; atomicExch(status, 42); }
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + b * TP_BN;
         bool gave_up = false;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % TP_STAGES, round = it / TP_STAGES;
-          if (!mbar_wait(&full[s], round & 1) || *failed) {
-            if (!*failed) { *failed = 2; atomicExch(status, 2); }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_hot(&full[st], ph)) {
+            if (!*failed) { *failed = 2; atomicExch(status, 42); }
             gave_up = true;
             break;
           }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = smem_u32(smem + s * TP_STAGE_BYTES), b_addr = a_addr + TP_A_BYTES;
+          // the stage's descriptors: 16 k further along the swizzled row is 32 bytes, 2 in the descriptor's address field
+          const uint64_t da = desc0 + (uint64_t)(st * (TP_STAGE_BYTES >> 4)), db = da + (TP_A_BYTES >> 4);
+          umma_bf16_pair(tmem_d, da, db, idesc, kb ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < TP_BK / 16; ++k)      // 16 k = 32 bytes further along the swizzled row
-            umma_bf16_pair(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) ? 1u : 0u);
-          umma_commit_pair(&empty[s]);              // arrives in both CTAs when these products have read the stage
+          for (int k = 1; k < TP_BK / 16; ++k) umma_bf16_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, 1u);
+          umma_commit_pair(&empty[st]);             // arrives in both CTAs when these products have read the stage
+          if (++st == TP_STAGES) { st = 0; ph ^= 1u; }
         }
         if (gave_up) break;
         umma_commit_pair(&acc_full[b]);             // arrives in both CTAs when every product issued so far is done
@@ -194,7 +196,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int b = local & 1;
       const int m0 = (tile % m_tiles) * 2 * TP_BM + (int)rank * TP_BM, n0 = (tile / m_tiles) * TP_BN;
       const bool ok = mbar_wait(&acc_full[b], (local >> 1) & 1);
-      if (!ok && !*failed) { *failed = 3; atomicExch(status, 3); }
+      if (!ok && !*failed) { *failed = 3; atomicExch(status, 43); }
       if (!ok || *failed) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m = m0 + quarter * 32 + lane;
@@ -223,28 +225,218 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
-// ---- host side --------------------------------------------------------------------------------
+// ---- the wide form: 256 x 512 tiles ---------------------------------------------------------------
+// With 256 x 256 tiles a CTA's shared memory moves, per 16-wide k step, 8 KB into the tensor core and 8 KB
+// in from the TMA unit in the 128 cycles the step's product takes: all of its 128 bytes a cycle, and the
+// tensor pipe stays near 0.8 busy.  A tile twice as wide keeps A for two products: per CTA 128 x 512 of C
+// (all 512 columns of its tensor memory, one accumulator), per 64-wide k block A 128 x 64 and W 256 x 64
+// (48 KB a stage, four stages), two products (N = 256 each) per k step: 16 KB out and 12 KB in per 256
+// cycles, and a quarter less traffic from L2.  CTA r loads rows n0 + 256 r .. of W in one box; product h of a
+// k step takes rows 128 h .. of each CTA's box, so that columns [0, 128) of accumulator half h are C's columns
+// n0 + 128 h .. and its columns [128, 256) are C's columns n0 + 256 + 128 h ...
+// With one accumulator the epilogue of a tile cannot run under the next tile's products as a whole; it runs
+// under part of them: the epilogue hands half 0 back as soon as it has read it, and the MMA thread starts the
+// next tile with the products of half 0 alone for the stages that are loaded (TP_STAGES_WIDE k blocks), then
+// waits for half 1, catches up on those stages and goes on with both.
+
+constexpr int TP_BN_WIDE = 512, TP_STAGES_WIDE = 4;
+constexpr int TP_B_BYTES_WIDE = (TP_BN_WIDE / 2) * TP_BK * 2;      // 32 KB: this CTA's 256 rows of W
+constexpr int TP_STAGE_BYTES_WIDE = TP_A_BYTES + TP_B_BYTES_WIDE;  // 48 KB
+constexpr int TP_STAGING_BYTES = 4 * 2 * 4096;                     // the epilogue warps' boxes on their way to the TMA unit
+constexpr int TP_SMEM_WIDE = TP_STAGES_WIDE * TP_STAGE_BYTES_WIDE + TP_STAGING_BYTES + 1024 + 256;
+static_assert(TP_SMEM_WIDE <= 227 * 1024, "shared memory of the wide form");
 
 template <int EPI>
-static int launch_tp(const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, void* out, int M, int N, int K,
-                     int* status, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(gemm_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM) != cudaSuccess) {
-      set_error("gemm_pair: cannot raise the shared memory limit");
-      return SLLM_ERR_LAUNCH;
+__global__ void __launch_bounds__(192, 1)
+gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                      const __grid_constant__ CUtensorMap map_out, int tma_out,
+                      const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K, int* __restrict__ status) {
+  extern __shared__ unsigned char tp_smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tp_smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* staging = smem + TP_STAGES_WIDE * TP_STAGE_BYTES_WIDE;     // [4 epilogue warps][2][32 rows x 128 bytes]
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + TP_STAGING_BYTES);
+  uint64_t* empty = full + TP_STAGES_WIDE;
+  uint64_t* acc_full = empty + TP_STAGES_WIDE;      // [1] (a second slot is left unused)
+  uint64_t* acc_empty = acc_full + 2;               // [2]: the accumulator's halves
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int m_tiles = (M + 2 * TP_BM - 1) / (2 * TP_BM), n_tiles = (N + TP_BN_WIDE - 1) / TP_BN_WIDE;
+  const int tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + TP_BK - 1) / TP_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TP_STAGES_WIDE; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
     }
-    configured = true;
+    mbar_init(&acc_full[0], 1);
+    for (int h = 0; h < 2; ++h) mbar_init(&acc_empty[h], 8);     // the four epilogue warps of each CTA
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  const int pairs_max = sllm::num_sms() / 2;
-  const long long tiles = (long long)((M + 2 * TP_BM - 1) / (2 * TP_BM)) * ((N + TP_BN - 1) / TP_BN);
-  const int pairs = (int)(tiles < pairs_max ? tiles : pairs_max);       // persistent: a pair per two SMs walks the tiles
-  cudaLaunchConfig_t cfg = {};
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TP_TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int it = 0;
+      bool gave_up = false;
+      for (int tile = pair; tile < tiles && !*failed; tile += pairs) {
+        const int m0 = (tile % m_tiles) * 2 * TP_BM + (int)rank * TP_BM;
+        const int n0 = (tile / m_tiles) * TP_BN_WIDE + (int)rank * (TP_BN_WIDE / 2);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % TP_STAGES_WIDE, round = it / TP_STAGES_WIDE;
+          if (!mbar_wait(&empty[s], (round & 1) ^ 1) || *failed) {
+            if (!*failed) { *failed = 1; atomicExch(status, 41); }
+            gave_up = true;
+            break;
+          }
+          unsigned char* sa = smem + s * TP_STAGE_BYTES_WIDE;
+          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * TP_STAGE_BYTES_WIDE);
+          tma_load_2d_pair(sa, &map_a, kb * TP_BK, m0, bar);
+          tma_load_2d_pair(sa + TP_A_BYTES, &map_w, kb * TP_BK, n0, bar);
+        }
+        if (gave_up) break;
+      }
+      if (*failed) {
+        const uint64_t t0 = global_ns();
+        while (global_ns() - t0 < TMA_DRAIN_NS) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)((2 * TP_BM) >> 4) << 24);
+      // the products of accumulator half h for the stage that holds k block kb of the tile
+      auto half_products = [&](int it, int kb, int h) {
+        const int s = it % TP_STAGES_WIDE;
+        const uint32_t a_addr = smem_u32(smem + s * TP_STAGE_BYTES_WIDE), b_addr = a_addr + TP_A_BYTES + h * (128 * 128);
+#pragma unroll
+        for (int k = 0; k < TP_BK / 16; ++k)
+          umma_bf16_pair(tmem_base + h * 256, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) ? 1u : 0u);
+      };
+      auto wait_or_fail = [&](uint64_t* bar, uint32_t parity) {
+        if (mbar_wait(bar, parity) && !*failed) return true;
+        if (!*failed) { *failed = 2; atomicExch(status, 42); }
+        return false;
+      };
+      int it = 0, local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < tiles && ok && !*failed; tile += pairs, ++local) {
+        const uint32_t drained = (local & 1) ^ 1;     // the parity of "the epilogue before this tile has read the half"
+        const int lead = k_blocks < TP_STAGES_WIDE ? k_blocks : TP_STAGES_WIDE;
+        // half 0 alone for the stages that are loaded already, while the epilogue still reads half 1
+        ok = wait_or_fail(&acc_empty[0], drained);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int kb = 0; kb < lead && ok; ++kb) {
+          ok = wait_or_fail(&full[(it + kb) % TP_STAGES_WIDE], ((it + kb) / TP_STAGES_WIDE) & 1);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (ok) half_products(it + kb, kb, 0);
+        }
+        if (ok) ok = wait_or_fail(&acc_empty[1], drained);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int kb = 0; kb < lead && ok; ++kb) {
+          half_products(it + kb, kb, 1);
+          umma_commit_pair(&empty[(it + kb) % TP_STAGES_WIDE]);
+        }
+        // the rest of the tile: both halves per k block
+        for (int kb = lead; kb < k_blocks && ok; ++kb) {
+          ok = wait_or_fail(&full[(it + kb) % TP_STAGES_WIDE], ((it + kb) / TP_STAGES_WIDE) & 1);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (!ok) break;
+          half_products(it + kb, kb, 0);
+          half_products(it + kb, kb, 1);
+          umma_commit_pair(&empty[(it + kb) % TP_STAGES_WIDE]);
+        }
+        it += k_blocks;
+        if (ok) umma_commit_pair(&acc_full[0]);
+      }
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int quarter = warp & 3;
+    const uint32_t acc_empty_addr[2] = {map_to_cta(smem_u32(&acc_empty[0]), 0), map_to_cta(smem_u32(&acc_empty[1]), 0)};
+    int local = 0, step = 0;                        // step: boxes this warp has handed to the TMA unit
+    for (int tile = pair; tile < tiles; tile += pairs, ++local) {
+      const int m0 = (tile % m_tiles) * 2 * TP_BM + (int)rank * TP_BM, n0 = (tile / m_tiles) * TP_BN_WIDE;
+      const bool ok = mbar_wait(&acc_full[0], local & 1);
+      if (!ok && !*failed) { *failed = 3; atomicExch(status, 43); }
+      if (!ok || *failed) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int m = m0 + quarter * 32 + lane;
+      unsigned char* stage_w = staging + (warp - 2) * 8192;
+      constexpr int AC = TgBox<EPI>::ACC_COLS;
+      const int row0 = m0 + quarter * 32;
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < 256; c0 += AC) {
+          // accumulator half h, columns c0 ..: the first 128 come from the first CTA's rows of W, the rest from the second's
+          const int n = n0 + (c0 < 128 ? 128 * h + c0 : 256 + 128 * h + (c0 - 128));
+          if (n >= N || row0 >= M) continue;        // warp-uniform
+          unsigned char* box = stage_w + (step & 1) * 4096;
+          if (tma_out && step >= 2) {               // the box staged two steps ago has left shared memory
+            if (lane == 0) bulk_wait_read<1>();
+            __syncwarp();
+          }
+#pragma unroll 1
+          for (int sub = 0; sub < AC / 32; ++sub) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + h * 256 + c0 + 32 * sub, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (tma_out) tg_stage_chunk<EPI>(r, box, lane, sub, n + 32 * sub, N, bias);
+            else if (m < M && n + 32 * sub < N) tg_store_chunk<EPI>(r, m, n + 32 * sub, N, bias, out);
+          }
+          if (tma_out) {
+            fence_async_smem();                     // the lanes' writes, before the TMA unit reads them
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&map_out, box, EPI == TG_EPI_SILU ? n >> 1 : n, row0);
+              bulk_commit();
+            }
+            ++step;
+          }
+        }
+        // this warp has read its quarter of the half: the MMA thread may write it again
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_addr[h]);
+      }
+    }
+    if (lane == 0) bulk_wait<0>();                  // this warp's stores are complete before the kernel ends
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();
+  pdl_launch_dependents();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TP_TMEM_COLS));
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+
+static void pair_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute (&attr)[2], int pairs, int smem, cudaStream_t stream) {
+  cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs));
   cfg.blockDim = dim3(192);
-  cfg.dynamicSmemBytes = TP_SMEM;
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
@@ -253,7 +445,53 @@ static int launch_tp(const CUtensorMap& ma, const CUtensorMap& mw, const float* 
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
-  cudaLaunchKernelEx(&cfg, gemm_pair_kernel<EPI>, ma, mw, bias, out, M, N, K, status);
+}
+
+template <int EPI>
+static int launch_tp_wide(const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, void* out, int M, int N, int K,
+                          int* status, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_pair_wide_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM_WIDE) != cudaSuccess) {
+      set_error("gemm_pair: cannot raise the shared memory limit");
+      return SLLM_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  // the result leaves through TMA stores where its rows are whole 16-byte pieces; else lane by lane
+  const int out_cols = EPI == TG_EPI_SILU ? N / 2 : N, elem = TgBox<EPI>::ELEM;
+  CUtensorMap mo = {};
+  int tma_out = 0;
+  if (((size_t)out_cols * elem) % 16 == 0 && ((uintptr_t)out & 15) == 0) tma_out = make_map_store(&mo, out, M, out_cols, elem) ? 1 : 0;
+  const int pairs_max = sllm::num_sms() / 2;
+  const long long tiles = (long long)((M + 2 * TP_BM - 1) / (2 * TP_BM)) * ((N + TP_BN_WIDE - 1) / TP_BN_WIDE);
+  const int pairs = (int)(tiles < pairs_max ? tiles : pairs_max);
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[2];
+  pair_launch_config(cfg, attr, pairs, TP_SMEM_WIDE, stream);
+  cudaLaunchKernelEx(&cfg, gemm_pair_wide_kernel<EPI>, ma, mw, mo, tma_out, bias, out, M, N, K, status);
+  return launch_status("gemm_pair");
+}
+
+template <int EPI>
+static int launch_tp(const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, void* out, int M, int N, int K,
+                     int* status, cudaStream_t stream) {
+  auto kernel = gemm_pair_kernel<EPI>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM) != cudaSuccess) {
+      set_error("gemm_pair: cannot raise the shared memory limit");
+      return SLLM_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  const int pairs_max = sllm::num_sms() / 2;
+  const long long tiles = (long long)((M + 2 * TP_BM - 1) / (2 * TP_BM)) * ((N + TP_BN - 1) / TP_BN);
+  const int pairs = (int)(tiles < pairs_max ? tiles : pairs_max);       // persistent: a pair per two SMs walks the tiles
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[2];
+  pair_launch_config(cfg, attr, pairs, TP_SMEM, stream);
+  cudaLaunchKernelEx(&cfg, kernel, ma, mw, bias, out, M, N, K, status);
   return launch_status("gemm_pair");
 }
 
@@ -267,23 +505,29 @@ SLLM_EXPORT int sllm_gemm_pair_supports(int M, int N, int K) {
 
 // The same product and epilogues as sllm_gemm_tcgen05 (0: float32 out[M, N] (+bias); 1: bfloat16; 2: bfloat16
 // out[M, N/2] = silu(gate) * up for W rows interleaved in blocks of 8), by pairs of CTAs on 256 x 256 tiles.
+// `wide` != 0: tiles of 256 x 512 (for matrices with many rows of W).
 // `status` is one int of device memory, zero before the launch; non-zero afterwards means a wait inside the
-// kernel ran out (1 producer, 2 MMA issuer, 3 epilogue) and `out` is not valid.
+// kernel ran out (41 producer, 42 MMA issuer, 43 epilogue) and `out` is not valid.
 SLLM_EXPORT int sllm_gemm_pair(const void* A, const void* W, const float* bias, void* out, int M, int N, int K,
-                               int epilogue, int* status, cudaStream_t stream) {
+                               int epilogue, int wide, int* status, cudaStream_t stream) {
   SLLM_REQUIRE(sllm_gemm_pair_supports(M, N, K), "gemm_pair: sizes M=%d N=%d K=%d (K must be a multiple of 8)", M, N, K);
   SLLM_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_pair: operands must be 16-byte aligned");
   SLLM_REQUIRE(status != nullptr, "gemm_pair: a status word is required");
   SLLM_REQUIRE(epilogue != TG_EPI_SILU || N % 16 == 0, "gemm_pair: the SiLU epilogue needs N %% 16 == 0");
   CUtensorMap ma, mw;
-  if (!make_map(&ma, A, M, K, TP_BM) || !make_map(&mw, W, N, K, TP_BN / 2)) {
+  const CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
+  if (!make_map(&ma, A, M, K, TP_BM, promo) || !make_map(&mw, W, N, K, wide ? TP_BN_WIDE / 2 : TP_BN / 2, promo)) {
     set_error("gemm_pair: cuTensorMapEncodeTiled failed");
     return SLLM_ERR_LAUNCH;
   }
+#define GO(EPI_)                                                                                   \
+  return wide ? launch_tp_wide<EPI_>(ma, mw, bias, out, M, N, K, status, stream)                   \
+              : launch_tp<EPI_>(ma, mw, bias, out, M, N, K, status, stream);
   switch (epilogue) {
-    case TG_EPI_F32: return launch_tp<TG_EPI_F32>(ma, mw, bias, out, M, N, K, status, stream);
-    case TG_EPI_BF16: return launch_tp<TG_EPI_BF16>(ma, mw, bias, out, M, N, K, status, stream);
-    case TG_EPI_SILU: return launch_tp<TG_EPI_SILU>(ma, mw, bias, out, M, N, K, status, stream);
+    case TG_EPI_F32: GO(TG_EPI_F32)
+    case TG_EPI_BF16: GO(TG_EPI_BF16)
+    case TG_EPI_SILU: GO(TG_EPI_SILU)
   }
+#undef GO
   SLLM_REQUIRE(false, "gemm_pair: unknown epilogue %d", epilogue);
 }

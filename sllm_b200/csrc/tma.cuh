@@ -38,13 +38,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-    if (ok) return true;
+    if (__builtin_expect(ok, 1)) return true;
     if ((i & 255u) == 255u) {
       const uint64_t now = global_ns();
       if (start == 0) start = now;
       else if (now - start > limit_ns) return false;
     }
   }
+}
+// the same for a wait that is usually short and stands in a hot loop: one test first, the bounded loop after it
+__device__ __forceinline__ bool mbar_wait_hot(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  if (__builtin_expect(ok, 1)) return true;
+  return mbar_wait(bar, parity);
 }
 // one test of the phase that never suspends the thread
 __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
@@ -81,7 +92,8 @@ inline EncodeTiledFn encode_fn() {
 }
 
 // rows x K bfloat16, row-major; boxes of box_rows x 64 elements, 128-byte swizzle, zeros outside
-inline bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+inline bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows,
+                     CUtensorMapL2promotion promotion = CU_TENSOR_MAP_L2_PROMOTION_L2_128B) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -89,9 +101,34 @@ inline bool make_map(CUtensorMap* map, const void* base, int rows, int K, int bo
   cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   cuuint32_t elem[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promotion,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+
+// A result matrix rows x cols (bfloat16 or float32, row-major) for TMA stores: boxes of 32 rows x 128 bytes,
+// 128-byte swizzle; what a box holds beyond the matrix's edges is not written.  cols * elem_bytes must be a
+// multiple of 16.
+inline bool make_map_store(CUtensorMap* map, void* base, int rows, int cols, int elem_bytes) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), 32};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides,
+            box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// one box from this CTA's shared memory to the matrix at (x, y); completion is tracked by bulk groups
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(smem)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the newest `N` groups have been read out of shared memory (their buffers may be written again)
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+// all but the newest `N` groups are complete (their writes are done)
+template <int N> __device__ __forceinline__ void bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
 
 // rows x (halves * 64) bfloat16, row-major, seen as [rows][halves][64]: one box takes box_rows whole
 // rows (all halves), stored as consecutive 128-byte units (row-major, half fastest), 128-byte swizzle

@@ -164,6 +164,7 @@ def check_tcgen05_status() -> None:
             t.zero_()
             who = {1: "gemm_tcgen05: the TMA producer", 2: "gemm_tcgen05: the MMA issuer", 3: "gemm_tcgen05: the epilogue",
                    11: "attention_tma: the producer", 12: "attention_tma: a compute warp",
+                   41: "gemm_pair: the TMA producer", 42: "gemm_pair: the MMA issuer", 43: "gemm_pair: the epilogue",
                    31: "linear_tc: the TMA producer", 32: "linear_tc: the MMA issuer", 33: "linear_tc: the epilogue",
                    }.get(code, f"code {code}")
             raise KernelError(f"{who} on {dev}: a bounded wait ran out; the result is not valid")
@@ -191,6 +192,52 @@ def gemm_tcgen05(x, w, bias, out_dtype, *, silu: bool = False):
     else:
         epi, out = 1, torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     call("sllm_gemm_tcgen05", _p(x), _p(w), _p(bias), _p(out), M, N, K, epi, _p(_status_word(x.device)), _stream())
+    _tc_used["since_check"] += 1
+    return out
+
+
+# which products of prompt portions (more than 128 rows) run on this package's CTA-pair kernel: "all", "fused" (only
+# gate|up with its SiLU epilogue; the plain products go to the library) or "off" (the one-CTA kernel for gate|up)
+_PAIR_GEMM = os.environ.get("SLLM_PAIR_GEMM", "all")
+
+
+def pair_supports(M: int, N: int, K: int) -> bool:
+    return bool(lib().sllm_gemm_pair_supports(int(M), int(N), int(K)))
+
+
+def pair_tiles_wide(M: int, N: int) -> bool:
+    """Whether tiles of 256 x 512 serve an [M, N] result better than tiles of 256 x 256.  The pairs of SMs run
+    the tiles in waves; a wide tile takes twice a narrow one's time and a quarter less traffic from L2, but its
+    epilogue is not hidden behind the next tile's products.  So: wide where it needs no more time in waves and a
+    pair has few tiles anyway (the attention and down projections of a prompt portion: one wave in place of one
+    and a half), narrow where a pair walks many tiles (gate|up: sixteen each at 2,048 rows)."""
+    pairs = max(num_sms() // 2, 1)
+    mt = -(-M // 256)
+    waves_narrow = -(-(mt * -(-N // 256)) // pairs)
+    waves_wide = -(-(mt * -(-N // 512)) // pairs)
+    return 2 * waves_wide <= waves_narrow and waves_narrow < 4
+
+
+def gemm_pair(x, w, bias, out_dtype, *, silu: bool = False, wide: bool | None = None):
+    """The same product and epilogues as `gemm_tcgen05`, by pairs of CTAs on 256 x 256 tiles, or on
+    256 x 512 tiles (``wide``; by default where those fill the GPU at least as well)
+    (``tcgen05.mma`` with ``cta_group::2``: each CTA loads half of each operand)."""
+    _chk(x, w, bias)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_pair: bfloat16 operands only")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"linear: x {tuple(x.shape)} does not fit w {tuple(w.shape)}")
+    if silu:
+        epi, out = 2, torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    elif out_dtype == torch.float32:
+        epi, out = 0, torch.empty((M, N), dtype=torch.float32, device=x.device)
+    else:
+        epi, out = 1, torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if wide is None:
+        wide = pair_tiles_wide(M, N)
+    call("sllm_gemm_pair", _p(x), _p(w), _p(bias), _p(out), M, N, K, epi, 1 if wide else 0, _p(_status_word(x.device)), _stream())
     _tc_used["since_check"] += 1
     return out
 
@@ -357,6 +404,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype, allow
             and linear_tc_supports(M, N, K):
         # a long reduction into few columns (the down projection): slices of K over all the SMs
         return linear_tc(x, w, bias, out_dtype, splits=_tc_splits(N, K))
+    if _PAIR_GEMM == "all" and M > TCGEN05_MIN_ROWS and pair_supports(M, N, K):
+        # prompt portions: pairs of CTAs on the tensor cores (tcgen05.mma with cta_group::2)
+        return gemm_pair(x, w, bias, out_dtype)
     launches["library"] += 1
     if out_dtype == torch.float32:
         out = torch.mm(x, w.t(), out_dtype=torch.float32)
@@ -406,8 +456,10 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, o
             return linear_stream(x, w_gate_up, None, out_dtype, silu=True)
         if N % 16 == 0 and linear_tc_supports(M, N, K):
             return linear_tc(x, w_gate_up, None, out_dtype, silu=True)
+        if M > TCGEN05_MIN_ROWS and N % 16 == 0 and _PAIR_GEMM != "off" and pair_supports(M, N, K):
+            # many rows: pairs of CTAs on the tensor cores, the activation applied as the tile leaves tensor memory
+            return gemm_pair(x, w_gate_up, None, out_dtype, silu=True)
         if M > TCGEN05_MIN_ROWS and N % 16 == 0 and tcgen05_supports(M, N, K):
-            # many rows: the tcgen05 product with the activation applied as the tile leaves tensor memory
             return gemm_tcgen05(x, w_gate_up, None, out_dtype, silu=True)
     gu = linear(x, w_gate_up, None, x.dtype)
     return silu_mul(gu, interleave, out_dtype)

@@ -704,6 +704,33 @@ def test_gemm_tcgen05_silu(M, I, K):
     torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=1.6e-2)
 
 
+@pytest.mark.parametrize("wide", [False, True])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (256, 512, 64), (129, 304, 72), (300, 300, 72), (333, 1000, 136), (512, 1040, 520),
+                                   (1000, 3008, 264), (2048, 4608, 3584), (600, 3584, 18944)])
+def test_gemm_pair(M, N, K, wide):
+    """The product by pairs of CTAs (tcgen05.mma with cta_group::2), on tiles of 256 x 256 and of 256 x 512, all
+    three epilogues: one tile with one k block, several tiles a pair, edges in M and N (rows and columns of a
+    tile that lie outside the result; results whose rows are no whole 16-byte pieces leave lane by lane instead
+    of through TMA stores), a long reduction."""
+    ops = _ops()
+    assert ops.pair_supports(M, N, K)
+    g = torch.Generator(device="cuda").manual_seed(51)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g)
+    want = x.float() @ w.float().t()
+    torch.testing.assert_close(ops.gemm_pair(x, w, b, torch.float32, wide=wide), want + b, rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(ops.gemm_pair(x, w, None, torch.float32, wide=wide), want, rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(ops.gemm_pair(x, w, b, torch.bfloat16, wide=wide).float(), want + b, rtol=1.6e-2, atol=1.6e-2)
+    if N % 16 == 0:
+        gu = want.reshape(M, N // 16, 2, 8)
+        act = (torch.nn.functional.silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(M, N // 2)
+        torch.testing.assert_close(ops.gemm_pair(x, w, None, torch.bfloat16, silu=True, wide=wide).float(), act, rtol=2e-2, atol=2e-2)
+    ops.check_tcgen05_status()
+    # the same bits from both tile shapes and from the one-CTA form: every element sums its k in one order
+    assert torch.equal(ops.gemm_pair(x, w, b, torch.float32, wide=wide), ops.gemm_tcgen05(x, w, b, torch.float32))
+
+
 @pytest.mark.parametrize("M", [33, 64, 65, 100, 128])
 @pytest.mark.parametrize("N,K", [(128, 64), (136, 72), (1000, 264), (4608, 3584), (3584, 18944)])
 def test_linear_tc(M, N, K):
