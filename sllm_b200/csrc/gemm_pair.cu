@@ -242,18 +242,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 constexpr int TP_BN_WIDE = 512, TP_STAGES_WIDE = 4;
 constexpr int TP_B_BYTES_WIDE = (TP_BN_WIDE / 2) * TP_BK * 2;      // 32 KB: this CTA's 256 rows of W
 constexpr int TP_STAGE_BYTES_WIDE = TP_A_BYTES + TP_B_BYTES_WIDE;  // 48 KB
-constexpr int TP_STAGING_BYTES = 4 * 2 * 4096;                     // the epilogue warps' boxes on their way to the TMA unit
+constexpr int TP_EPI_WARPS_WIDE = 8;                               // two per quarter of the tensor memory's lanes
+constexpr int TP_THREADS_WIDE = (2 + TP_EPI_WARPS_WIDE) * 32;
+constexpr int TP_STAGING_BYTES = TP_EPI_WARPS_WIDE * 4096;         // the epilogue warps' boxes on their way to the TMA unit
 constexpr int TP_SMEM_WIDE = TP_STAGES_WIDE * TP_STAGE_BYTES_WIDE + TP_STAGING_BYTES + 1024 + 256;
 static_assert(TP_SMEM_WIDE <= 227 * 1024, "shared memory of the wide form");
 
 template <int EPI>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(TP_THREADS_WIDE, 1)
 gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       const __grid_constant__ CUtensorMap map_out, int tma_out,
                       const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K, int* __restrict__ status) {
   extern __shared__ unsigned char tp_smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tp_smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char* staging = smem + TP_STAGES_WIDE * TP_STAGE_BYTES_WIDE;     // [4 epilogue warps][2][32 rows x 128 bytes]
+  unsigned char* staging = smem + TP_STAGES_WIDE * TP_STAGE_BYTES_WIDE;     // [epilogue warps][32 rows x 128 bytes]
   uint64_t* full = reinterpret_cast<uint64_t*>(staging + TP_STAGING_BYTES);
   uint64_t* empty = full + TP_STAGES_WIDE;
   uint64_t* acc_full = empty + TP_STAGES_WIDE;      // [1] (a second slot is left unused)
@@ -274,7 +276,7 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       mbar_init(&empty[s], 1);
     }
     mbar_init(&acc_full[0], 1);
-    for (int h = 0; h < 2; ++h) mbar_init(&acc_empty[h], 8);     // the four epilogue warps of each CTA
+    for (int h = 0; h < 2; ++h) mbar_init(&acc_empty[h], 2 * TP_EPI_WARPS_WIDE);     // the epilogue warps of both CTAs
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -367,10 +369,13 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       }
     }
   } else {
-    // ---------------- epilogue ----------------
-    const int quarter = warp & 3;
+    // ---------------- epilogue: warps 2..9; warp w reads lanes 32 (w % 4) .., and of every accumulator half the
+    // columns [0, 128) (warps 2..5) or [128, 256) (warps 6..9) ----------------
+    const int quarter = warp & 3, col_half = (warp - 2) >> 2;
     const uint32_t acc_empty_addr[2] = {map_to_cta(smem_u32(&acc_empty[0]), 0), map_to_cta(smem_u32(&acc_empty[1]), 0)};
-    int local = 0, step = 0;                        // step: boxes this warp has handed to the TMA unit
+    unsigned char* box = staging + (warp - 2) * 4096;
+    int local = 0;
+    bool staged = false;                            // a box of this warp is on its way out of shared memory
     for (int tile = pair; tile < tiles; tile += pairs, ++local) {
       const int m0 = (tile % m_tiles) * 2 * TP_BM + (int)rank * TP_BM, n0 = (tile / m_tiles) * TP_BN_WIDE;
       const bool ok = mbar_wait(&acc_full[0], local & 1);
@@ -378,19 +383,18 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       if (!ok || *failed) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m = m0 + quarter * 32 + lane;
-      unsigned char* stage_w = staging + (warp - 2) * 8192;
       constexpr int AC = TgBox<EPI>::ACC_COLS;
       const int row0 = m0 + quarter * 32;
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < 256; c0 += AC) {
-          // accumulator half h, columns c0 ..: the first 128 come from the first CTA's rows of W, the rest from the second's
-          const int n = n0 + (c0 < 128 ? 128 * h + c0 : 256 + 128 * h + (c0 - 128));
+        for (int c0 = 128 * col_half; c0 < 128 * col_half + 128; c0 += AC) {
+          // accumulator half h: its columns [0, 128) are C's columns n0 + 128 h .. (the first CTA's rows of W), its
+          // columns [128, 256) are C's columns n0 + 256 + 128 h .. (the second CTA's)
+          const int n = n0 + 256 * col_half + 128 * h + (c0 - 128 * col_half);
           if (n >= N || row0 >= M) continue;        // warp-uniform
-          unsigned char* box = stage_w + (step & 1) * 4096;
-          if (tma_out && step >= 2) {               // the box staged two steps ago has left shared memory
-            if (lane == 0) bulk_wait_read<1>();
+          if (tma_out && staged) {                  // the box staged before has left shared memory
+            if (lane == 0) bulk_wait_read<0>();
             __syncwarp();
           }
 #pragma unroll 1
@@ -408,10 +412,10 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
               tma_store_2d(&map_out, box, EPI == TG_EPI_SILU ? n >> 1 : n, row0);
               bulk_commit();
             }
-            ++step;
+            staged = true;
           }
         }
-        // this warp has read its quarter of the half: the MMA thread may write it again
+        // this warp has read its share of the half: the MMA thread may write it again
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(acc_empty_addr[h]);
@@ -431,10 +435,11 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
 // ---- host side --------------------------------------------------------------------------------
 
-static void pair_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute (&attr)[2], int pairs, int smem, cudaStream_t stream) {
+static void pair_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute (&attr)[2], int pairs, int threads, int smem,
+                               cudaStream_t stream) {
   cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs));
-  cfg.blockDim = dim3(192);
+  cfg.blockDim = dim3((unsigned)threads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -468,7 +473,7 @@ static int launch_tp_wide(const CUtensorMap& ma, const CUtensorMap& mw, const fl
   const int pairs = (int)(tiles < pairs_max ? tiles : pairs_max);
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[2];
-  pair_launch_config(cfg, attr, pairs, TP_SMEM_WIDE, stream);
+  pair_launch_config(cfg, attr, pairs, TP_THREADS_WIDE, TP_SMEM_WIDE, stream);
   cudaLaunchKernelEx(&cfg, gemm_pair_wide_kernel<EPI>, ma, mw, mo, tma_out, bias, out, M, N, K, status);
   return launch_status("gemm_pair");
 }
@@ -490,7 +495,7 @@ static int launch_tp(const CUtensorMap& ma, const CUtensorMap& mw, const float* 
   const int pairs = (int)(tiles < pairs_max ? tiles : pairs_max);       // persistent: a pair per two SMs walks the tiles
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[2];
-  pair_launch_config(cfg, attr, pairs, TP_SMEM, stream);
+  pair_launch_config(cfg, attr, pairs, 192, TP_SMEM, stream);
   cudaLaunchKernelEx(&cfg, kernel, ma, mw, bias, out, M, N, K, status);
   return launch_status("gemm_pair");
 }

@@ -9,6 +9,7 @@ float32 path, runs in this package's own kernels.
 
 from __future__ import annotations
 
+import functools
 import os
 
 import torch
@@ -36,11 +37,9 @@ def _dtc(dtype: torch.dtype) -> int:
 
 def _chk(*tensors) -> None:
     for t in tensors:
-        if t is None:
-            continue
-        if not t.is_cuda:
-            raise KernelError("the kernels run on a CUDA device only; got a tensor on " + str(t.device))
-        if not t.is_contiguous():
+        if t is not None and not (t.is_cuda and t.is_contiguous()):
+            if not t.is_cuda:
+                raise KernelError("the kernels run on a CUDA device only; got a tensor on " + str(t.device))
             raise KernelError("the kernels take contiguous tensors")
 
 
@@ -53,9 +52,12 @@ def _p(t):
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
+_current_device = getattr(torch._C, "_cuda_getDevice", None)      # (torch.cuda.current_device() checks initialisation each time)
+
+
 def _stream():
     if _raw_stream is not None:
-        return _raw_stream(torch.cuda.current_device())
+        return _raw_stream(_current_device() if _current_device is not None else torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -104,6 +106,7 @@ TCGEN05_MIN_ROWS = 128    # below this a 128-row tile is mostly padding
 STREAM_MAX_ROWS = 32      # beyond this the kernel's shared-memory reads of the activations bound it
 
 
+@functools.lru_cache(maxsize=4096)
 def stream_supports(M: int, N: int, K: int) -> bool:
     return M <= STREAM_MAX_ROWS and bool(lib().sllm_linear_stream_supports(int(M), int(N), int(K)))
 
@@ -170,6 +173,7 @@ def check_tcgen05_status() -> None:
             raise KernelError(f"{who} on {dev}: a bounded wait ran out; the result is not valid")
 
 
+@functools.lru_cache(maxsize=4096)
 def tcgen05_supports(M: int, N: int, K: int) -> bool:
     return bool(lib().sllm_gemm_tcgen05_supports(int(M), int(N), int(K)))
 
@@ -201,10 +205,12 @@ def gemm_tcgen05(x, w, bias, out_dtype, *, silu: bool = False):
 _PAIR_GEMM = os.environ.get("SLLM_PAIR_GEMM", "all")
 
 
+@functools.lru_cache(maxsize=4096)
 def pair_supports(M: int, N: int, K: int) -> bool:
     return bool(lib().sllm_gemm_pair_supports(int(M), int(N), int(K)))
 
 
+@functools.lru_cache(maxsize=4096)
 def pair_tiles_wide(M: int, N: int) -> bool:
     """Whether tiles of 256 x 512 serve an [M, N] result better than tiles of 256 x 256.  The pairs of SMs run
     the tiles in waves; a wide tile takes twice a narrow one's time and a quarter less traffic from L2, but its
@@ -252,10 +258,12 @@ LINEAR_TC_SPLIT_MAX_ROWS = 64
 _LINEAR_TC = os.environ.get("SLLM_LINEAR_TCGEN05", "1") != "0"     # 0: 33..128 tokens on the library product
 
 
+@functools.lru_cache(maxsize=4096)
 def linear_tc_supports(M: int, N: int, K: int) -> bool:
     return _LINEAR_TC and STREAM_MAX_ROWS < M <= LINEAR_TC_MAX_ROWS and bool(lib().sllm_linear_tc_supports(int(M), int(N), int(K)))
 
 
+@functools.lru_cache(maxsize=4096)
 def _tc_splits(N: int, K: int) -> int:
     """Slices of K so that (tiles of 128 rows) x slices comes to about one unit per SM, each slice
     at least eight 64-wide k blocks long."""
@@ -293,6 +301,7 @@ WS_MAX_COLS = 8192        # wider products have CTAs enough for the 128-row stre
 WS_MAX_ROWS = 8           # with 9..16 tokens its second token tile costs registers and it falls behind
 
 
+@functools.lru_cache(maxsize=4096)
 def ws_supports(M: int, N: int, K: int) -> bool:
     return M <= WS_MAX_ROWS and N <= WS_MAX_COLS and bool(lib().sllm_linear_ws_supports(int(M), int(N), int(K)))
 
@@ -373,6 +382,7 @@ def linear_accumulate_norm(x, w, bias, residual, gain, eps: float):
     return xg, scale
 
 
+@functools.lru_cache(maxsize=4096)
 def _stream_splits(N: int, K: int) -> int:
     ctas = -(-N // 128)
     return max(1, min(2 * num_sms() // ctas, K // 128, 16))
@@ -553,7 +563,7 @@ _num_sms: dict = {}
 def num_sms() -> int:
     """Streaming multiprocessors of the current device (the library asks the driver, once per device):
     what the dispatch sizes k-splits and context splits for."""
-    dev = torch.cuda.current_device()
+    dev = _current_device() if _current_device is not None else torch.cuda.current_device()
     n = _num_sms.get(dev)
     if n is None:
         n = _num_sms[dev] = max(1, int(lib().sllm_num_sms()))
@@ -589,6 +599,7 @@ def attention_tiles(q_lens, group_size: int, device, ctx_lens=None, large_rows: 
     return up(small_s, [0] * len(small_s)), up(large_s, large_r)
 
 
+@functools.lru_cache(maxsize=4096)
 def choose_splits(num_small: int, nkv: int, max_ctx: int) -> int:
     """How many ways the decode form cuts the context: enough CTAs to fill the GPU about
     twice, never less than 256 keys a split."""
@@ -618,6 +629,7 @@ def attention_mma(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, de
     return out
 
 
+@functools.lru_cache(maxsize=4096)
 def tma_attention_supports(hd: int, page_size: int) -> bool:
     return bool(lib().sllm_attention_tma_supports(int(hd), int(page_size)))
 
@@ -657,10 +669,12 @@ def wait_probe(limit_ns: int, device="cuda"):
     return int(status.item()), int(waited.item())
 
 
+@functools.lru_cache(maxsize=4096)
 def tc_attention_supports(hd: int, page_size: int) -> bool:
     return bool(lib().sllm_attention_tc_supports(int(hd), int(page_size)))
 
 
+@functools.lru_cache(maxsize=4096)
 def choose_tc_splits(num_tiles: int, nkv: int, max_ctx: int) -> tuple[int, int]:
     """(ranges, 64-key tiles a range) for the prefill form: few row tiles over a long context are cut
     so that about two CTAs an SM run, each range at least 16 key tiles long."""
@@ -699,6 +713,7 @@ def attention_tc(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, nq,
     return out
 
 
+@functools.lru_cache(maxsize=4096)
 def mma_supports(hd: int) -> bool:
     return bool(lib().sllm_attention_mma_supports(int(hd)))
 

@@ -121,19 +121,24 @@ class KernelTimes:
         return {name: (len(p), sum(a.elapsed_time(b) for a, b in p)) for name, p in self.pairs.items()}
 
 
+_fns: dict = {}
+
+
 def call(name: str, *args) -> None:
-    L = lib()
+    fn = _fns.get(name)
+    if fn is None:
+        fn = _fns[name] = getattr(lib(), name)
     kt = KernelTimes.active
     if kt is None:
-        rc = getattr(L, name)(*args)
+        rc = fn(*args)
     else:
         import torch
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        rc = getattr(L, name)(*args)
+        rc = fn(*args)
         b.record()
         kt.pairs.setdefault(name, []).append((a, b))
     launches["own"] += 1
     if rc != 0:
-        msg = L.sllm_last_error().decode(errors="replace")
+        msg = lib().sllm_last_error().decode(errors="replace")
         raise KernelError(f"{name} failed (code {rc}): {msg}")
