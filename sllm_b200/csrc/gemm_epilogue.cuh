@@ -10,6 +10,39 @@ namespace sllm {
 #define TG_EPI_F32 0
 #define TG_EPI_BF16 1
 #define TG_EPI_SILU 2
+#define TG_EPI_RESID 3     // residual[M, N] (float32) += the product (+ bias), in place; see TgExtra
+
+// What an epilogue may do beyond its store, for the RMSNorm that a prompt portion's products take apart
+// (y = x * rsqrt(mean(x^2) + eps) * gain, ref/standard.py:25-31; the same scheme as linear_ws.cu's WsNorm):
+//   consumer side (any epilogue): the product's input was bfloat16(stream * gain) with the division still owed;
+//     ssq_in [M][stride_in] holds parts_in partial sums of squares of each row of the stream, and each row of the
+//     product is multiplied by rsqrt(sum / width + eps) before bias and activation;
+//   producer side (TG_EPI_RESID): after residual += product, also write xg [M, N] = bfloat16(residual * gain) and,
+//     per row and block of 128 columns, the sum of squares of the new residual: ssq_out [M][stride_out], entry
+//     column / 128.  gain null: the residual update alone.
+struct TgExtra {
+  const float* ssq_in = nullptr;
+  int parts_in = 0, stride_in = 0;
+  float eps_in = 0.f, inv_width_in = 0.f;
+  float* residual = nullptr;
+  const float* gain = nullptr;
+  __nv_bfloat16* xg = nullptr;
+  float* ssq_out = nullptr;
+  int stride_out = 0;
+};
+
+// the factor of row m (1 where nothing is owed); the partial sums are added in index order
+__device__ __forceinline__ float tg_row_scale(const TgExtra& e, int m, int M) {
+  if (e.ssq_in == nullptr || m >= M) return 1.f;
+  const float* row = e.ssq_in + (size_t)m * e.stride_in;
+  float sum = 0.f;
+  for (int p = 0; p < e.parts_in; ++p) sum += row[p];
+  return rsqrtf(sum * e.inv_width_in + e.eps_in);
+}
+__device__ __forceinline__ void tg_scale(uint32_t (&r)[32], float s) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * s);
+}
 
 // The epilogue warps run one to a scheduler with nothing to hide a dependent instruction behind, so what they
 // do per value counts: the bias is fetched in 16-byte pieces and only where there is one, the bounds are
@@ -87,6 +120,53 @@ __device__ __forceinline__ void tg_store_chunk(const uint32_t (&r)[32], int m, i
   }
 }
 
+// TG_EPI_RESID on columns n .. n + 31 of row m (N a multiple of 4): returns the sum of squares of the new
+// residual values of the chunk (0 where the next norm's input is not asked for)
+__device__ __forceinline__ float tg_resid_chunk(const uint32_t (&r)[32], int m, int n, int N, const float* __restrict__ bias,
+                                                const TgExtra& e) {
+  float v[32];
+  tg_values(r, v, n, N, bias);
+  float* res = e.residual + (size_t)m * N + n;
+  float sq = 0.f;
+  if (n + 32 <= N) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float4 x = *reinterpret_cast<const float4*>(res + 4 * j);
+      x.x += v[4 * j]; x.y += v[4 * j + 1]; x.z += v[4 * j + 2]; x.w += v[4 * j + 3];
+      *reinterpret_cast<float4*>(res + 4 * j) = x;
+      v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
+    }
+    if (e.xg != nullptr) {
+      __nv_bfloat16* o = e.xg + (size_t)m * N + n;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          sq += v[8 * j + i] * v[8 * j + i];
+          w[i] = v[8 * j + i] * e.gain[n + 8 * j + i];
+        }
+        if ((N & 7) == 0) {
+          *reinterpret_cast<uint4*>(o + 8 * j) = make_uint4(pack2(w[0], w[1]), pack2(w[2], w[3]), pack2(w[4], w[5]), pack2(w[6], w[7]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[8 * j + i] = __float2bfloat16_rn(w[i]);
+        }
+      }
+    }
+  } else {
+    for (int i = 0; i < 32 && n + i < N; ++i) {
+      const float x = res[i] + v[i];
+      res[i] = x;
+      if (e.xg != nullptr) {
+        sq += x * x;
+        e.xg[(size_t)m * N + n + i] = __float2bfloat16_rn(x * e.gain[n + i]);
+      }
+    }
+  }
+  return sq;
+}
+
 // ---- the same through shared memory and TMA stores ------------------------------------------------
 // A lane of an epilogue warp holds one row of the accumulator, so direct stores put every lane on a line of
 // its own: 32 requests of 16 bytes an instruction, and the step from tensor memory to global memory takes
@@ -95,8 +175,8 @@ __device__ __forceinline__ void tg_store_chunk(const uint32_t (&r)[32], int m, i
 // lane hands it to the TMA unit, which writes whole lines and clips what lies outside the matrix.
 // A box is 32 float32, 64 bfloat16 or (SiLU form) 128 accumulator columns wide.
 template <int EPI> struct TgBox {
-  static constexpr int ACC_COLS = EPI == TG_EPI_F32 ? 32 : (EPI == TG_EPI_BF16 ? 64 : 128);   // accumulator columns a box covers
-  static constexpr int ELEM = EPI == TG_EPI_F32 ? 4 : 2;
+  static constexpr int ACC_COLS = (EPI == TG_EPI_F32 || EPI == TG_EPI_RESID) ? 32 : (EPI == TG_EPI_BF16 ? 64 : 128);   // accumulator columns a box covers
+  static constexpr int ELEM = (EPI == TG_EPI_F32 || EPI == TG_EPI_RESID) ? 4 : 2;
 };
 
 __device__ __forceinline__ void tg_put_piece(unsigned char* row_base, int row, int piece, uint4 v) {

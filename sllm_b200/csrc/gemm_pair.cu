@@ -83,7 +83,8 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 template <int EPI>
 __global__ void __launch_bounds__(192, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                 const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K, int* __restrict__ status) {
+                 const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K, int* __restrict__ status,
+                 const TgExtra extra) {
   extern __shared__ unsigned char tp_smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tp_smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + TP_STAGES * TP_STAGE_BYTES);
@@ -200,6 +201,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       if (!ok || *failed) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m = m0 + quarter * 32 + lane;
+      const float row_scale = tg_row_scale(extra, m, M);        // a norm still owed on the input (1 if none)
+      float sq = 0.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < TP_BN; c0 += 32) {
         if (n0 + c0 >= N) break;                    // warp-uniform
@@ -207,7 +210,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + b * TP_BN + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (m >= M) continue;
-        tg_store_chunk<EPI>(r, m, n0 + c0, N, bias, out);
+        if (extra.ssq_in != nullptr) tg_scale(r, row_scale);
+        if constexpr (EPI == TG_EPI_RESID) {
+          sq += tg_resid_chunk(r, m, n0 + c0, N, bias, extra);
+          if (extra.ssq_out != nullptr && ((c0 & 127) == 96 || n0 + c0 + 32 >= N)) {     // a block of 128 columns is complete
+            extra.ssq_out[(size_t)m * extra.stride_out + (n0 + c0) / 128] = sq;
+            sq = 0.f;
+          }
+        } else {
+          tg_store_chunk<EPI>(r, m, n0 + c0, N, bias, out);
+        }
       }
       // this warp has read its quarter of the buffer: tell the MMA thread (in the pair's first CTA)
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -252,7 +264,8 @@ template <int EPI>
 __global__ void __launch_bounds__(TP_THREADS_WIDE, 1)
 gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       const __grid_constant__ CUtensorMap map_out, int tma_out,
-                      const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K, int* __restrict__ status) {
+                      const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K, int* __restrict__ status,
+                      const TgExtra extra) {
   extern __shared__ unsigned char tp_smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tp_smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* staging = smem + TP_STAGES_WIDE * TP_STAGE_BYTES_WIDE;     // [epilogue warps][32 rows x 128 bytes]
@@ -385,8 +398,10 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const int m = m0 + quarter * 32 + lane;
       constexpr int AC = TgBox<EPI>::ACC_COLS;
       const int row0 = m0 + quarter * 32;
+      const float row_scale = tg_row_scale(extra, m, M);        // a norm still owed on the input (1 if none)
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {
+        float sq = 0.f;
 #pragma unroll 1
         for (int c0 = 128 * col_half; c0 < 128 * col_half + 128; c0 += AC) {
           // accumulator half h: its columns [0, 128) are C's columns n0 + 128 h .. (the first CTA's rows of W), its
@@ -402,8 +417,13 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             uint32_t r[32];
             tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + h * 256 + c0 + 32 * sub, r);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (tma_out) tg_stage_chunk<EPI>(r, box, lane, sub, n + 32 * sub, N, bias);
-            else if (m < M && n + 32 * sub < N) tg_store_chunk<EPI>(r, m, n + 32 * sub, N, bias, out);
+            if (extra.ssq_in != nullptr) tg_scale(r, row_scale);
+            if constexpr (EPI == TG_EPI_RESID) {
+              if (m < M && n + 32 * sub < N) sq += tg_resid_chunk(r, m, n + 32 * sub, N, bias, extra);
+            } else {
+              if (tma_out) tg_stage_chunk<EPI>(r, box, lane, sub, n + 32 * sub, N, bias);
+              else if (m < M && n + 32 * sub < N) tg_store_chunk<EPI>(r, m, n + 32 * sub, N, bias, out);
+            }
           }
           if (tma_out) {
             fence_async_smem();                     // the lanes' writes, before the TMA unit reads them
@@ -414,6 +434,11 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             }
             staged = true;
           }
+        }
+        if constexpr (EPI == TG_EPI_RESID) {
+          // the warp's 128 columns of this half are one block of C's columns: its sum of squares per row
+          const int nb = n0 + 256 * col_half + 128 * h;
+          if (extra.ssq_out != nullptr && m < M && nb < N) extra.ssq_out[(size_t)m * extra.stride_out + nb / 128] = sq;
         }
         // this warp has read its share of the half: the MMA thread may write it again
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -454,7 +479,7 @@ static void pair_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute (&at
 
 template <int EPI>
 static int launch_tp_wide(const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, void* out, int M, int N, int K,
-                          int* status, cudaStream_t stream) {
+                          int* status, cudaStream_t stream, const TgExtra& extra) {
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_pair_wide_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM_WIDE) != cudaSuccess) {
@@ -467,20 +492,21 @@ static int launch_tp_wide(const CUtensorMap& ma, const CUtensorMap& mw, const fl
   const int out_cols = EPI == TG_EPI_SILU ? N / 2 : N, elem = TgBox<EPI>::ELEM;
   CUtensorMap mo = {};
   int tma_out = 0;
-  if (((size_t)out_cols * elem) % 16 == 0 && ((uintptr_t)out & 15) == 0) tma_out = make_map_store(&mo, out, M, out_cols, elem) ? 1 : 0;
+  if (EPI != TG_EPI_RESID && ((size_t)out_cols * elem) % 16 == 0 && ((uintptr_t)out & 15) == 0)
+    tma_out = make_map_store(&mo, out, M, out_cols, elem) ? 1 : 0;
   const int pairs_max = sllm::num_sms() / 2;
   const long long tiles = (long long)((M + 2 * TP_BM - 1) / (2 * TP_BM)) * ((N + TP_BN_WIDE - 1) / TP_BN_WIDE);
   const int pairs = (int)(tiles < pairs_max ? tiles : pairs_max);
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[2];
   pair_launch_config(cfg, attr, pairs, TP_THREADS_WIDE, TP_SMEM_WIDE, stream);
-  cudaLaunchKernelEx(&cfg, gemm_pair_wide_kernel<EPI>, ma, mw, mo, tma_out, bias, out, M, N, K, status);
+  cudaLaunchKernelEx(&cfg, gemm_pair_wide_kernel<EPI>, ma, mw, mo, tma_out, bias, out, M, N, K, status, extra);
   return launch_status("gemm_pair");
 }
 
 template <int EPI>
 static int launch_tp(const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, void* out, int M, int N, int K,
-                     int* status, cudaStream_t stream) {
+                     int* status, cudaStream_t stream, const TgExtra& extra) {
   auto kernel = gemm_pair_kernel<EPI>;
   static bool configured = false;
   if (!configured) {
@@ -496,7 +522,7 @@ static int launch_tp(const CUtensorMap& ma, const CUtensorMap& mw, const float* 
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[2];
   pair_launch_config(cfg, attr, pairs, 192, TP_SMEM, stream);
-  cudaLaunchKernelEx(&cfg, kernel, ma, mw, bias, out, M, N, K, status);
+  cudaLaunchKernelEx(&cfg, kernel, ma, mw, bias, out, M, N, K, status, extra);
   return launch_status("gemm_pair");
 }
 
@@ -509,16 +535,44 @@ SLLM_EXPORT int sllm_gemm_pair_supports(int M, int N, int K) {
 }
 
 // The same product and epilogues as sllm_gemm_tcgen05 (0: float32 out[M, N] (+bias); 1: bfloat16; 2: bfloat16
-// out[M, N/2] = silu(gate) * up for W rows interleaved in blocks of 8), by pairs of CTAs on 256 x 256 tiles.
-// `wide` != 0: tiles of 256 x 512 (for matrices with many rows of W).
+// out[M, N/2] = silu(gate) * up for W rows interleaved in blocks of 8), by pairs of CTAs on 256 x 256 tiles, and
+// 3: residual[M, N] (float32) += the product (+bias) in place (`out` is ignored).
+// `wide` != 0: tiles of 256 x 512 (for matrices with few rows of W).
+// ssq_in != null: A is bfloat16(stream * gain) of an RMSNorm still owed; ssq_in [M][stride_in] holds parts_in partial
+//   sums of squares of the stream's rows (width_in wide) and every row of the product is multiplied by
+//   rsqrt(sum / width_in + eps_in) before bias and activation.
+// gain != null (epilogue 3): also write xg_out [M, N] = bfloat16(residual * gain) and ssq_out [M][stride_out], the
+//   sums of squares of the new residual per row and block of 128 columns (sllm_gemm_pair_parts(N) entries a row).
 // `status` is one int of device memory, zero before the launch; non-zero afterwards means a wait inside the
-// kernel ran out (41 producer, 42 MMA issuer, 43 epilogue) and `out` is not valid.
+// kernel ran out (41 producer, 42 MMA issuer, 43 epilogue) and the result is not valid.
+SLLM_EXPORT int sllm_gemm_pair_parts(int N) { return (N + 127) / 128; }
+
 SLLM_EXPORT int sllm_gemm_pair(const void* A, const void* W, const float* bias, void* out, int M, int N, int K,
-                               int epilogue, int wide, int* status, cudaStream_t stream) {
+                               int epilogue, int wide, const float* ssq_in, int parts_in, int stride_in, float eps_in,
+                               int width_in, float* residual, const float* gain, void* xg_out, float* ssq_out, int stride_out,
+                               int* status, cudaStream_t stream) {
   SLLM_REQUIRE(sllm_gemm_pair_supports(M, N, K), "gemm_pair: sizes M=%d N=%d K=%d (K must be a multiple of 8)", M, N, K);
   SLLM_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_pair: operands must be 16-byte aligned");
   SLLM_REQUIRE(status != nullptr, "gemm_pair: a status word is required");
   SLLM_REQUIRE(epilogue != TG_EPI_SILU || N % 16 == 0, "gemm_pair: the SiLU epilogue needs N %% 16 == 0");
+  TgExtra extra;
+  if (ssq_in != nullptr) {
+    SLLM_REQUIRE(parts_in >= 1 && stride_in >= parts_in && width_in >= 1, "gemm_pair: a table of %d partial sums (row stride %d) over width %d",
+                 parts_in, stride_in, width_in);
+    extra.ssq_in = ssq_in; extra.parts_in = parts_in; extra.stride_in = stride_in; extra.eps_in = eps_in;
+    extra.inv_width_in = 1.0f / (float)width_in;
+  }
+  if (epilogue == TG_EPI_RESID) {
+    SLLM_REQUIRE(residual != nullptr && N % 4 == 0 && ((uintptr_t)residual & 15) == 0, "gemm_pair: the residual epilogue needs a 16-byte aligned float32 residual and N %% 4 == 0");
+    extra.residual = residual;
+    if (gain != nullptr) {
+      SLLM_REQUIRE(xg_out != nullptr && ssq_out != nullptr && stride_out >= sllm_gemm_pair_parts(N) && ((uintptr_t)xg_out & 15) == 0,
+                   "gemm_pair: the next norm's input needs both destinations (row stride %d, %d parts)", stride_out, sllm_gemm_pair_parts(N));
+      extra.gain = gain; extra.xg = (__nv_bfloat16*)xg_out; extra.ssq_out = ssq_out; extra.stride_out = stride_out;
+    }
+  } else {
+    SLLM_REQUIRE(out != nullptr, "gemm_pair: no destination");
+  }
   CUtensorMap ma, mw;
   const CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
   if (!make_map(&ma, A, M, K, TP_BM, promo) || !make_map(&mw, W, N, K, wide ? TP_BN_WIDE / 2 : TP_BN / 2, promo)) {
@@ -526,12 +580,13 @@ SLLM_EXPORT int sllm_gemm_pair(const void* A, const void* W, const float* bias, 
     return SLLM_ERR_LAUNCH;
   }
 #define GO(EPI_)                                                                                   \
-  return wide ? launch_tp_wide<EPI_>(ma, mw, bias, out, M, N, K, status, stream)                   \
-              : launch_tp<EPI_>(ma, mw, bias, out, M, N, K, status, stream);
+  return wide ? launch_tp_wide<EPI_>(ma, mw, bias, out, M, N, K, status, stream, extra)            \
+              : launch_tp<EPI_>(ma, mw, bias, out, M, N, K, status, stream, extra);
   switch (epilogue) {
     case TG_EPI_F32: GO(TG_EPI_F32)
     case TG_EPI_BF16: GO(TG_EPI_BF16)
     case TG_EPI_SILU: GO(TG_EPI_SILU)
+    case TG_EPI_RESID: GO(TG_EPI_RESID)
   }
 #undef GO
   SLLM_REQUIRE(false, "gemm_pair: unknown epilogue %d", epilogue);

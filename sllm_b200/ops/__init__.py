@@ -224,18 +224,35 @@ def pair_tiles_wide(M: int, N: int) -> bool:
     return 2 * waves_wide <= waves_narrow and waves_narrow < 4
 
 
-def gemm_pair(x, w, bias, out_dtype, *, silu: bool = False, wide: bool | None = None):
+def gemm_pair(x, w, bias, out_dtype, *, silu: bool = False, wide: bool | None = None, scale: "RowScale | None" = None,
+              residual=None, next_gain=None):
     """The same product and epilogues as `gemm_tcgen05`, by pairs of CTAs on 256 x 256 tiles, or on
     256 x 512 tiles (``wide``; by default where those fill the GPU at least as well)
-    (``tcgen05.mma`` with ``cta_group::2``: each CTA loads half of each operand)."""
-    _chk(x, w, bias)
+    (``tcgen05.mma`` with ``cta_group::2``: each CTA loads half of each operand).
+    ``scale``: a norm still owed on ``x`` (`RowScale`).  ``residual`` (float32 ``[M, N]``): the product is added
+    into it in place and None is returned; with ``next_gain`` the kernel also writes the next norm's input in the
+    owed form and ``(xg, RowScale)`` comes back (the scale's eps left at 0 for the caller to set)."""
+    _chk(x, w, bias, residual, next_gain)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_pair: bfloat16 operands only")
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError(f"linear: x {tuple(x.shape)} does not fit w {tuple(w.shape)}")
-    if silu:
+    out = xg = ssq = None
+    stride = 0
+    if residual is not None:
+        if silu or residual.dtype != torch.float32 or tuple(residual.shape) != (M, N):
+            raise KernelError(f"gemm_pair: residual {tuple(residual.shape)} {residual.dtype} does not fit [{M}, {N}] float32")
+        epi = 3
+        if next_gain is not None:
+            if next_gain.dtype != torch.float32 or next_gain.numel() != N:
+                raise KernelError("gemm_pair: the next norm's gain is float32 of N values")
+            parts = pair_parts(N)
+            stride = (parts + 3) & ~3
+            xg = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+            ssq = torch.empty((M, stride), dtype=torch.float32, device=x.device)
+    elif silu:
         epi, out = 2, torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
     elif out_dtype == torch.float32:
         epi, out = 0, torch.empty((M, N), dtype=torch.float32, device=x.device)
@@ -243,9 +260,19 @@ def gemm_pair(x, w, bias, out_dtype, *, silu: bool = False, wide: bool | None = 
         epi, out = 1, torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     if wide is None:
         wide = pair_tiles_wide(M, N)
-    call("sllm_gemm_pair", _p(x), _p(w), _p(bias), _p(out), M, N, K, epi, 1 if wide else 0, _p(_status_word(x.device)), _stream())
+    call("sllm_gemm_pair", _p(x), _p(w), _p(bias), _p(out), M, N, K, epi, 1 if wide else 0,
+         *(scale.args_with_stride() if scale is not None else (None, 0, 0, 0.0, 0)),
+         _p(residual), _p(next_gain), _p(xg), _p(ssq), stride, _p(_status_word(x.device)), _stream())
     _tc_used["since_check"] += 1
+    if residual is not None:
+        return (xg, RowScale(ssq, pair_parts(N), 0.0, N)) if next_gain is not None else None
     return out
+
+
+@functools.lru_cache(maxsize=256)
+def pair_parts(N: int) -> int:
+    """Partial sums of squares per row that `gemm_pair`'s residual epilogue writes for N columns."""
+    return int(lib().sllm_gemm_pair_parts(int(N)))
 
 
 LINEAR_TC_MAX_ROWS = 128  # the tokens are the tensor core's N side: one tile of at most 128
@@ -319,6 +346,9 @@ class RowScale:
     def args(self):
         return _p(self.ssq), self.parts, self.eps, self.width
 
+    def args_with_stride(self):
+        return _p(self.ssq), self.parts, self.ssq.shape[1], self.eps, self.width
+
 
 _NO_SCALE = (None, 0, 0.0, 0)
 MAX_SCALE_PARTS = 384          # partial sums a consumer keeps in shared memory per row
@@ -355,40 +385,66 @@ def linear_ws(x, w, bias, out_dtype, residual=None, scale: RowScale | None = Non
     return out
 
 
+def _pair_rows(M: int) -> bool:
+    return _PAIR_GEMM == "all" and M > TCGEN05_MIN_ROWS
+
+
 def can_accumulate(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether `linear_accumulate` has a kernel for these operands."""
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda
-            and ws_supports(x.shape[0], w.shape[0], x.shape[1]))
+    """Whether `linear_accumulate` has a kernel for these operands: few tokens (the warp-split streaming
+    kernel) or a prompt portion (the CTA-pair product)."""
+    if not (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda):
+        return False
+    M, K = x.shape
+    N = w.shape[0]
+    return ws_supports(M, N, K) or (_pair_rows(M) and N % 4 == 0 and pair_supports(M, N, K))
 
 
 def linear_accumulate(x, w, bias, residual) -> None:
     """``residual += x @ w.T (+ bias)`` in one kernel (see `can_accumulate`)."""
-    linear_ws(x, w, bias, torch.float32, residual=residual)
+    if ws_supports(x.shape[0], w.shape[0], x.shape[1]):
+        linear_ws(x, w, bias, torch.float32, residual=residual)
+    else:
+        gemm_pair(x, w, bias, torch.float32, residual=residual)
 
 
-_NORM_FUSED = os.environ.get("SLLM_NORM_FUSED", "1") != "0"     # 0: every RMSNorm of a decode step is a kernel of its own
+_NORM_FUSED = os.environ.get("SLLM_NORM_FUSED", "1") != "0"     # 0: every RMSNorm of a step is a kernel of its own
 
 
 def can_accumulate_norm(x: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether `linear_accumulate_norm` has a kernel for these operands."""
-    return _NORM_FUSED and can_accumulate(x, w) and int(lib().sllm_linear_ws_parts(w.shape[0])) <= MAX_SCALE_PARTS
+    if not (_NORM_FUSED and can_accumulate(x, w)):
+        return False
+    M, N = x.shape[0], w.shape[0]
+    if ws_supports(M, N, x.shape[1]):
+        return int(lib().sllm_linear_ws_parts(N)) <= MAX_SCALE_PARTS
+    return N % 8 == 0
 
 
 def linear_accumulate_norm(x, w, bias, residual, gain, eps: float):
     """``residual += x @ w.T (+ bias)`` and, from the same kernel, the input of the RMSNorm (``gain``, ``eps``)
     that follows, in the owed form: ``(bfloat16(residual * gain), RowScale)``."""
-    xg, scale = linear_ws(x, w, bias, torch.float32, residual=residual, next_gain=gain)
+    if ws_supports(x.shape[0], w.shape[0], x.shape[1]):
+        xg, scale = linear_ws(x, w, bias, torch.float32, residual=residual, next_gain=gain)
+    else:
+        xg, scale = gemm_pair(x, w, bias, torch.float32, residual=residual, next_gain=gain)
     scale.eps = float(eps)
     return xg, scale
 
 
-@functools.lru_cache(maxsize=4096)
+def linear_scaled_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether `linear` takes ``x`` with a norm still owed (``scale=``): a prompt portion on the CTA-pair product."""
+    M, K = x.shape
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and _pair_rows(M)
+            and pair_supports(M, w.shape[0], K))
+
+
 def _stream_splits(N: int, K: int) -> int:
     ctas = -(-N // 128)
     return max(1, min(2 * num_sms() // ctas, K // 128, 16))
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype, allow_partials: bool = False) -> torch.Tensor:
+def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype, allow_partials: bool = False,
+           scale: "RowScale | None" = None) -> torch.Tensor:
     """``x @ w.T (+ bias)``; ``w`` is ``[N, K]``.  float32 operands: this package's
     float32 kernel.  bfloat16 operands, float32 accumulation, result in ``out_dtype``: up
     to 64 rows the weight-streaming kernel (which, if ``allow_partials``, may return a
@@ -396,6 +452,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype, allow
     the library product."""
     if x.dtype != w.dtype:
         raise KernelError(f"linear: x is {x.dtype}, w is {w.dtype}")
+    if scale is not None:                       # a norm still owed on x (see `linear_scaled_supports`)
+        if not linear_scaled_supports(x, w):
+            raise KernelError("linear: no kernel takes this input with its norm still owed")
+        return gemm_pair(x, w, bias, out_dtype, scale=scale)
     if x.dtype == torch.float32:
         if out_dtype != torch.float32:
             raise KernelError("linear: the float32 path keeps float32 results")
@@ -442,8 +502,9 @@ def silu_scaled_supports(x, w_gate_up, interleave: int, out_dtype) -> bool:
     """Whether `linear_silu_mul` takes an input whose norm is still owed (``scale``)."""
     M, K = x.shape
     N = w_gate_up.shape[0]
-    return (x.is_cuda and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and interleave == 8 and M <= 16
-            and N % 16 == 0 and stream_supports(M, N, K))
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and interleave == 8 and N % 16 == 0):
+        return False
+    return (M <= 16 and stream_supports(M, N, K)) or (M > TCGEN05_MIN_ROWS and _PAIR_GEMM != "off" and pair_supports(M, N, K))
 
 
 def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, out_dtype: torch.dtype,
@@ -456,6 +517,8 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, o
         _chk(x, w_gate_up, scale.ssq)
         M, K = x.shape
         N = w_gate_up.shape[0]
+        if M > 16:
+            return gemm_pair(x, w_gate_up, None, out_dtype, silu=True, scale=scale)
         out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
         call("sllm_linear_stream_silu_scaled", _p(x), _p(w_gate_up), _p(out), M, N, K, *scale.args(), _stream())
         return out

@@ -173,11 +173,17 @@ class Attention(Mixer):
         rot = getattr(position, "rotary_dim", 0) if table is not None else 0
         slots = g.slot_mapping if write_cache else None
         owed = x if isinstance(x, OwedNorm) else None
-        if owed is not None and not ops.qkv_rope_supports(owed.x, self.qkv.weight, table, rot, self.nq, self.nkv, self.hd, cache.k):
+        fused = owed is not None and ops.qkv_rope_supports(owed.x, self.qkv.weight, table, rot, self.nq, self.nkv, self.hd, cache.k)
+        if owed is not None and not fused and not ops.linear_scaled_supports(owed.x, self.qkv.weight):
             x, owed = owed.plain(), None
-        if owed is not None:
+        if owed is not None and fused:
             q = ops.linear_rope_kv_write(owed.x, self.qkv.weight, self.qkv_b, step.positions, table, rot,
                                          self.nq, self.nkv, self.hd, slots, cache.k, cache.v, scale=owed.scale)
+        elif owed is not None:
+            # a prompt portion: the product pays the owed division in its epilogue, the rotary kernel follows
+            qkv = ops.linear(owed.x, self.qkv.weight, None, torch.float32, scale=owed.scale)
+            q = ops.rope_kv_write(qkv, self.qkv_b, step.positions, table, rot, self.nq, self.nkv, self.hd,
+                                  slots, cache.k, cache.v, self.dtype)
         elif ops.qkv_rope_supports(x, self.qkv.weight, table, rot, self.nq, self.nkv, self.hd, cache.k):
             # few tokens: bias, rotation and the cache write happen as the product's rows leave their CTA
             q = ops.linear_rope_kv_write(x, self.qkv.weight, self.qkv_b, step.positions, table, rot,

@@ -731,6 +731,48 @@ def test_gemm_pair(M, N, K, wide):
     assert torch.equal(ops.gemm_pair(x, w, b, torch.float32, wide=wide), ops.gemm_tcgen05(x, w, b, torch.float32))
 
 
+@pytest.mark.parametrize("wide", [False, True])
+@pytest.mark.parametrize("M,H,K", [(256, 256, 64), (300, 3584, 520), (2048, 3584, 3584), (333, 1000, 136), (129, 904, 72)])
+def test_gemm_pair_owes_and_pays_an_rmsnorm(M, H, K, wide):
+    """A prompt portion's products take the RMSNorm between them apart as the decode step's do: the product that
+    completes the residual stream adds into it in place and writes bfloat16(stream * gain) with sums of squares per
+    row and block of 128 columns; the products that follow (plain, and gate|up with SiLU*mul) multiply their rows by
+    the reciprocal root mean square (y = x * rsqrt(mean(x^2) + eps) * gain, ref/standard.py:25-31)."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(61)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(H, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    b = torch.randn(H, device="cuda", generator=g)
+    gain = 1 + 0.3 * torch.randn(H, device="cuda", generator=g)
+    eps = 1e-5
+    res = 3 * torch.randn(M, H, device="cuda", generator=g)
+    stream = res + x.float() @ w.float().t() + b
+    # the residual update alone
+    alone = res.clone()
+    assert ops.gemm_pair(x, w, b, torch.float32, wide=wide, residual=alone) is None
+    torch.testing.assert_close(alone, stream, rtol=2e-3, atol=2e-3)
+    # with the next norm's input
+    xg, scale = ops.gemm_pair(x, w, b, torch.float32, wide=wide, residual=res, next_gain=gain)
+    scale.eps = eps
+    ops.check_tcgen05_status()
+    assert torch.equal(res, alone)
+    torch.testing.assert_close(xg.float(), (res * gain).bfloat16().float(), rtol=1e-2, atol=1e-2)
+    assert scale.parts == -(-H // 128) and scale.width == H
+    torch.testing.assert_close(scale.ssq[:, :scale.parts].sum(1), (res ** 2).sum(1), rtol=1e-4, atol=1e-4)
+    normed = res * torch.rsqrt((res ** 2).mean(1, keepdim=True) + eps) * gain
+    for wide2 in (False, True):
+        N2 = 528
+        w2 = (torch.randn(N2, H, device="cuda", generator=g) / H ** 0.5).bfloat16()
+        b2 = torch.randn(N2, device="cuda", generator=g)
+        want = normed @ w2.float().t() + b2
+        torch.testing.assert_close(ops.gemm_pair(xg, w2, b2, torch.float32, wide=wide2, scale=scale), want, rtol=2e-2, atol=2e-2)
+        gu = (want - b2).reshape(M, N2 // 16, 2, 8)
+        act = (torch.nn.functional.silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(M, N2 // 2)
+        torch.testing.assert_close(ops.gemm_pair(xg, w2, None, torch.bfloat16, silu=True, wide=wide2, scale=scale).float(), act,
+                                   rtol=2e-2, atol=2e-2)
+    ops.check_tcgen05_status()
+
+
 @pytest.mark.parametrize("M", [33, 64, 65, 100, 128])
 @pytest.mark.parametrize("N,K", [(128, 64), (136, 72), (1000, 264), (4608, 3584), (3584, 18944)])
 def test_linear_tc(M, N, K):

@@ -110,3 +110,31 @@ def test_decode_steps_leave_their_norms_to_the_products(wide_model, monkeypatch)
         assert np.abs(rows[fused] - ref_rows).max() <= 0.08 * spread
         assert float(np.sqrt(((rows[fused] - ref_rows) ** 2).mean())) <= 0.02 * spread
     assert float(np.sqrt(((rows[True] - rows[False]) ** 2).mean())) <= 0.02 * spread
+
+
+def test_prompt_portions_leave_their_norms_to_the_products(wide_model, monkeypatch):
+    """A prompt portion of more than 128 tokens: the products that complete the residual stream (on the CTA-pair
+    kernel) prepare the next RMSNorm's input, the consuming products pay the division, and of the 2 L + 1 norms
+    only the first layer's and the final one remain kernels; no library product is launched.  The logits are the
+    plain implementation's within the bounds of the other tests here, with and without the scheme."""
+    from sllm_b200 import ops
+    from sllm_b200.engine import Engine, StepEntry, build_model
+    dev = cuda_or_skip()
+    model_dir, cfg, reqs, want = wide_model
+    model, _ = build_model(model_dir, "bfloat16", dev)
+    spread = float(np.concatenate([v.ravel() for v in want.values()]).std())
+    entries = [StepEntry(r, ids, list(range(len(ids)))) for r, ids in reqs.items()]       # 197 tokens in one step
+    ref_rows = np.concatenate([want[r] for r in reqs])
+    counts = {}
+    for fused in (True, False):
+        monkeypatch.setattr(ops, "_NORM_FUSED", fused)
+        eng = Engine(model, page_size=16, num_pages=32, max_requests=4)
+        before = ops.launches["library"]
+        with ops.KernelTimes() as kt:
+            logits = eng.step(entries).float().cpu().numpy()
+        counts[fused] = kt.table().get("sllm_add_rmsnorm", (0, 0.0))[0]
+        assert ops.launches["library"] == before
+        assert np.abs(logits - ref_rows).max() <= 0.08 * spread
+        assert float(np.sqrt(((logits - ref_rows) ** 2).mean())) <= 0.02 * spread
+    L = cfg["num_hidden_layers"]
+    assert counts[False] == 2 * L + 1 and counts[True] == 2, counts
