@@ -63,7 +63,7 @@ def load_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi's clocks and throttle reasons, sampled every 200 ms while a timed
+    """nvidia-smi's clocks and throttle reasons, sampled every 50 ms while a timed
     region runs.  Reading only; no setting of the GPU is touched."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -78,7 +78,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -269,7 +269,7 @@ def stated_run(model, cfg, batch, prompt_len=2048, new_tokens=256, seed=5):
     return out
 
 
-def prefill_run(model, cfg, tokens, reps=5, seed=1, warmup=3):
+def prefill_run(model, cfg, tokens, reps=9, seed=1, warmup=3):
     import numpy as np
     import torch
 
@@ -594,6 +594,12 @@ def main(argv=None) -> int:
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
             points[f"decode_b{b}_e2e"] = round(r["e2e_tok_s"], 1)
             points[f"decode_b{b}_hbm_frac"] = round(r["step_bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+        # long contexts, where the cache is most of what a step reads (the attention kernels are compared with their
+        # float32 statement at these lengths in tests/test_long_context_gpu.py)
+        for b, ctx in ((8, 16384), (1, 32768)):
+            r = decode_run(model, cfg, b, ctx, args.steps, 3, seed=ctx, repeats=2)
+            points[f"decode_b{b}_ctx{ctx}"] = round(r["tok_s"], 1)
+            points[f"decode_b{b}_ctx{ctx}_hbm_frac"] = round(r["step_bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
         # the baseline's stated run: prompts of 2,048 tokens, then 256 greedy tokens, every decode step timed
         for b in (1, 8, 64):
             dev, wall, n = stated_run(model, cfg, b)
