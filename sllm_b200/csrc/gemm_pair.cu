@@ -336,48 +336,54 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     // ---------------- MMA issuer ----------------
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)((2 * TP_BM) >> 4) << 24);
-      // the products of accumulator half h for the stage that holds k block kb of the tile
-      auto half_products = [&](int it, int kb, int h) {
-        const int s = it % TP_STAGES_WIDE;
-        const uint32_t a_addr = smem_u32(smem + s * TP_STAGE_BYTES_WIDE), b_addr = a_addr + TP_A_BYTES + h * (128 * 128);
+      // The loop of the issuing thread is kept lean (its own instructions showed in the kernel's time): stages and
+      // parities are counted, not divided; descriptors are made by addition; the flag in shared memory is only read
+      // when a wait has run out.
+      const uint64_t desc0 = umma_desc(smem_u32(smem));
+      // the products of accumulator half h on stage st (kb: the tile's k block, 0 starts the accumulator)
+      auto half_products = [&](uint32_t st, int kb, int h) {
+        const uint64_t da = desc0 + (uint64_t)(st * (TP_STAGE_BYTES_WIDE >> 4));
+        const uint64_t db = da + ((TP_A_BYTES + h * (128 * 128)) >> 4);
+        umma_bf16_pair(tmem_base + h * 256, da, db, idesc, kb ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < TP_BK / 16; ++k)
-          umma_bf16_pair(tmem_base + h * 256, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) ? 1u : 0u);
+        for (int k = 1; k < TP_BK / 16; ++k) umma_bf16_pair(tmem_base + h * 256, da + 2 * k, db + 2 * k, idesc, 1u);
       };
       auto wait_or_fail = [&](uint64_t* bar, uint32_t parity) {
-        if (mbar_wait(bar, parity) && !*failed) return true;
+        if (mbar_wait_hot(bar, parity)) return true;
         if (!*failed) { *failed = 2; atomicExch(status, 42); }
         return false;
       };
-      int it = 0, local = 0;
+      int local = 0;
+      uint32_t st = 0, ph = 0;                      // the stage to consume next and its barrier's parity
       bool ok = true;
-      for (int tile = pair; tile < tiles && ok && !*failed; tile += pairs, ++local) {
+      for (int tile = pair; tile < tiles && ok; tile += pairs, ++local) {
         const uint32_t drained = (local & 1) ^ 1;     // the parity of "the epilogue before this tile has read the half"
         const int lead = k_blocks < TP_STAGES_WIDE ? k_blocks : TP_STAGES_WIDE;
         // half 0 alone for the stages that are loaded already, while the epilogue still reads half 1
         ok = wait_or_fail(&acc_empty[0], drained);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t st1 = st, ph1 = ph;
         for (int kb = 0; kb < lead && ok; ++kb) {
-          ok = wait_or_fail(&full[(it + kb) % TP_STAGES_WIDE], ((it + kb) / TP_STAGES_WIDE) & 1);
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          if (ok) half_products(it + kb, kb, 0);
+          ok = wait_or_fail(&full[st1], ph1);
+          if (ok) half_products(st1, kb, 0);
+          if (++st1 == TP_STAGES_WIDE) { st1 = 0; ph1 ^= 1u; }
         }
         if (ok) ok = wait_or_fail(&acc_empty[1], drained);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         for (int kb = 0; kb < lead && ok; ++kb) {
-          half_products(it + kb, kb, 1);
-          umma_commit_pair(&empty[(it + kb) % TP_STAGES_WIDE]);
+          half_products(st, kb, 1);
+          umma_commit_pair(&empty[st]);
+          if (++st == TP_STAGES_WIDE) { st = 0; ph ^= 1u; }
         }
         // the rest of the tile: both halves per k block
         for (int kb = lead; kb < k_blocks && ok; ++kb) {
-          ok = wait_or_fail(&full[(it + kb) % TP_STAGES_WIDE], ((it + kb) / TP_STAGES_WIDE) & 1);
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          ok = wait_or_fail(&full[st], ph);
           if (!ok) break;
-          half_products(it + kb, kb, 0);
-          half_products(it + kb, kb, 1);
-          umma_commit_pair(&empty[(it + kb) % TP_STAGES_WIDE]);
+          half_products(st, kb, 0);
+          half_products(st, kb, 1);
+          umma_commit_pair(&empty[st]);
+          if (++st == TP_STAGES_WIDE) { st = 0; ph ^= 1u; }
         }
-        it += k_blocks;
         if (ok) umma_commit_pair(&acc_full[0]);
       }
     }
