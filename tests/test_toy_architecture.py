@@ -6,6 +6,9 @@ from the recipe by the architecture's own hook.  `python -m sllm_b200.serving.ma
 run --random-weights SEED` must print the greedy tokens of a plain numpy statement of the same model.
 
 Runs twice: with the PyTorch stand-ins for the kernels (no GPU), and on the GPU with the real ones.
+
+Below it, a second toy architecture: layers whose attention has a window beside layers without one (two cache
+groups; pages given back while a request runs, and used again), replayed in all four cuttings.
 """
 
 import os
@@ -200,3 +203,118 @@ def test_toy_architecture_through_the_command_line_with_stand_in_kernels(tmp_pat
 def test_toy_architecture_through_the_command_line(tmp_path, capsys):
     cuda_or_skip()
     _run(tmp_path, capsys)
+
+
+# ---- layers with a window beside layers without: two cache groups, pages given back and used again ------------------
+
+WINDOW = 20
+# heads of 64, so that the TMA-fed decode kernel meets the window and the holes it leaves in the block tables
+HD64 = ({"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": 192, "num_attention_heads": 6,
+         "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 272, "vocab_size": 500, "rope_theta": 10000.0,
+         "rms_norm_eps": 1e-6, "max_position_embeddings": 256, "tie_word_embeddings": True, "hidden_act": "silu"},
+        {"std": 0.05}, 16)
+
+
+def _register_windowed():
+    from sllm_b200.config import Architecture, ModelPlan, PartSpec, RunEntry, pre_norm_layer, register_architecture
+    from sllm_b200.models import qwen2
+
+    def plan(cfg):
+        base = qwen2.plan(cfg)
+        layers = []
+        for i, l in enumerate(base.layers):
+            mixer = l.part("mixer")
+            if i % 2:                               # every second layer only ever reads the last WINDOW keys
+                mixer = PartSpec(mixer.kind, dict(mixer.params, window=WINDOW))
+            layers.append(pre_norm_layer(l.prefix, mixer, l.part("ffn"), l.part("mixer_norm")))
+        return ModelPlan(architecture="ToyWindowLM", hidden_size=base.hidden_size, vocab_size=base.vocab_size,
+                         max_positions=base.max_positions, embedding_name=base.embedding_name, layers=tuple(layers),
+                         run_list=tuple(RunEntry(i) for i in range(len(layers))), final_norm=base.final_norm,
+                         final_norm_name=base.final_norm_name, head_name=base.head_name, position=base.position)
+
+    register_architecture(Architecture("ToyWindowLM", qwen2.Qwen2Config, plan), replace=True)
+
+
+def _plain_windowed(ids, w, cfg):
+    h = plain.embed(np.asarray(ids), w["model.embed_tokens.weight"])
+    nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    s = len(ids)
+    cos, sin = plain.rotary_tables(cfg["rope_theta"], np.arange(s), hd)
+    for i in range(cfg["num_hidden_layers"]):
+        p, a = f"model.layers.{i}", f"model.layers.{i}.self_attn"
+        x = plain.rms_norm(h, w[f"{p}.input_layernorm.weight"], cfg["rms_norm_eps"])
+        q, k, v = (plain.linear(x, w[f"{a}.{n}_proj.weight"], w[f"{a}.{n}_proj.bias"]).reshape(s, heads, hd).transpose(1, 0, 2)
+                   for n, heads in (("q", nq), ("k", nkv), ("v", nkv)))
+        q, k = plain.apply_rotary(q, cos, sin), plain.apply_rotary(k, cos, sin)
+        o = plain.causal_attention(q, np.repeat(k, nq // nkv, axis=0), np.repeat(v, nq // nkv, axis=0), hd ** -0.5,
+                                   window=WINDOW if i % 2 else None)
+        h = h + plain.linear(o.transpose(1, 0, 2).reshape(s, nq * hd), w[f"{a}.o_proj.weight"])
+        x = plain.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+        h = h + plain.swiglu(x, w, p)
+    h = plain.rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
+    head = w["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else w["lm_head.weight"]
+    return (h @ head.T).astype(np.float32)
+
+
+def _run_windowed(tmp_path, dev, dtypes, configs):
+    """Every cutting of the requests through a model whose odd layers have a window: those layers form a cache
+    group of their own, give the pages the window has passed back while a request still runs, and read block tables
+    with holes.  The pools are sized for the trace's peak, so pages given back are used again."""
+    from sllm_b200.config import unregister_architecture
+    from sllm_b200.engine import Engine, build_model
+    from sllm_b200.weights import write_random_model
+    from tests import traces
+    from tests.conftest import TINY
+    _register_windowed()
+    try:
+        for which in configs:
+            config, init, page = TINY[which] if which in TINY else HD64
+            config = dict(config, architectures=["ToyWindowLM"], num_hidden_layers=4)
+            d = write_random_model(os.path.join(str(tmp_path), f"win{which}"), config, 21, std=init["std"], bias_std=0.2, gain_std=0.1)
+            cfg, w = plain.load_model(d)
+            rng = np.random.default_rng(3)
+            top = cfg["max_position_embeddings"]
+            reqs = {f"r{i}": rng.integers(0, cfg["vocab_size"], min(n, top)).tolist() for i, n in enumerate((70, 37, 100, 45, 64, 90))}
+            want = {r: _plain_windowed(ids, w, cfg) for r, ids in reqs.items()}
+            for dtype in dtypes:
+                tol = dict(rtol=1e-4, atol=2e-5) if dtype == "float32" else dict(rtol=2e-2, atol=2e-2)
+                model, _ = build_model(d, dtype, dev)
+                for mode in ("whole", "tail_decode", "portions", "mixed"):
+                    tr = getattr(traces, mode)(reqs)
+                    eng = Engine(model, page_size=page, num_pages=tr.max_tokens // page, max_requests=4, poison_freed=True)
+                    assert [g.need.window for g in eng.cache.groups] == [None, WINDOW] and [len(g.runs) for g in eng.cache.groups] == [2, 2]
+                    out = traces.replay_engine(tr, eng)
+                    traces.compare(tr, out, want, what=f"windowed {which}/{dtype}/{mode}", **tol)
+                    eng.cache.check()
+                    assert not eng.cache.requests and all(g.pool.used_count == 0 for g in eng.cache.groups)
+                    if mode in ("tail_decode", "mixed"):
+                        assert eng.cache.reuse_count > 0, "pages the window gave back were meant to be used again"
+                if dtype == "float32" and dev != "cpu":
+                    # generation through the entry point: decode steps from captured graphs over both cache groups,
+                    # with so few pages that only the window's giving back lets all requests finish
+                    from sllm_b200.engine.llm import LLM
+                    from sllm_b200.sampling import SamplingParams
+                    prompts = [ids[:n] for ids, n in zip(reqs.values(), (9, 30, 17))]
+                    new = min(40, top - 31)
+                    llm = LLM(model=model, block_size=page, num_pages=3 * (-(-(30 + new) // page)) + 1, max_num_seqs=3, chunk_size=16,
+                              max_batch_tokens=64, policy="on_demand")
+                    res = llm.generate(prompts, SamplingParams(max_new=new))
+                    for pr, r in zip(prompts, res):
+                        ids, out = list(pr), []
+                        for _ in range(new):
+                            out.append(int(np.argmax(_plain_windowed(ids, w, cfg)[-1])))
+                            ids.append(out[-1])
+                        assert r.ids == out, (which, len(pr))
+                    assert any(g.graph is not None for g in llm.engine.graphs.graphs.values())
+                    llm.engine.cache.check()
+    finally:
+        unregister_architecture("ToyWindowLM")
+
+
+def test_windowed_layers_beside_full_ones_with_stand_in_kernels(tmp_path, cpu_ops):
+    _run_windowed(tmp_path, "cpu", ("float32",), ("A",))
+
+
+@pytest.mark.gpu
+def test_windowed_layers_beside_full_ones(tmp_path):
+    _run_windowed(tmp_path, cuda_or_skip(), ("float32", "bfloat16"), ("A", "B", "hd64"))
