@@ -460,11 +460,15 @@ static bool cache_map(const void* base, long long rows, int ps, int hd, CUtensor
   return true;
 }
 
+// dynamic shared memory of a CTA: the K/V stages, the queries, the barriers, the cached block table, alignment slack
+constexpr size_t ta_smem(int hd) {
+  return (size_t)TA_STAGES * 2 * TA_BN * hd * 2 + 16 * (hd + 8) * 2 + 2 * TA_STAGES * 8 + 16 + TA_BT_CACHE * 4 + 1024;
+}
+
 template <int HD>
 static int launch_ta(const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& rk, const CUtensorMap& rv,
                      const AttnTmaParams& p, int tiles, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)TA_STAGES * 2 * TA_BN * HD * 2 + 16 * (HD + 8) * 2 + 2 * TA_STAGES * 8 + 16 +
-                          TA_BT_CACHE * 4 + 1024;
+  constexpr size_t smem = ta_smem(HD);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_tma_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
@@ -492,6 +496,14 @@ using namespace sllm;
 SLLM_EXPORT int sllm_attention_tma_supports(int hd, int page_size) {
   // a page's box must start on a 1024-byte boundary of the swizzled tile: page sizes 8, 16, 32, 64
   return (hd == 64 || hd == 128) && page_size >= 8 && page_size <= 64 && 64 % page_size == 0 && encode_fn() != nullptr;
+}
+
+// CTAs of the decode form that share an SM (by shared memory: 228 KB an SM, 1 KB of it reserved per CTA): what the
+// host sizes its cut of the context for
+SLLM_EXPORT int sllm_attention_tma_ctas_per_sm(int hd) {
+  const size_t per_cta = ta_smem(hd == 64 ? 64 : 128) + 1024;
+  const int by_smem = (int)((size_t)228 * 1024 / per_cta), by_threads = 2048 / TA_THREADS;
+  return by_smem < by_threads ? (by_smem < 1 ? 1 : by_smem) : by_threads;
 }
 
 // The decode form only: every tile holds at most 16 (token, head-in-group) rows.  num_pages: pages in the

@@ -108,7 +108,11 @@ STREAM_MAX_ROWS = 32      # beyond this the kernel's shared-memory reads of the 
 
 @functools.lru_cache(maxsize=4096)
 def stream_supports(M: int, N: int, K: int) -> bool:
-    return M <= STREAM_MAX_ROWS and bool(lib().sllm_linear_stream_supports(int(M), int(N), int(K)))
+    """Whether the weight-streaming kernel is the one for this product (it is not where the tensor-core form
+    of the same job is the faster one: see `linear_tc_supports`)."""
+    if not (M <= STREAM_MAX_ROWS and bool(lib().sllm_linear_stream_supports(int(M), int(N), int(K)))):
+        return False
+    return not linear_tc_supports(M, N, K)
 
 
 def linear_stream(x, w, bias, out_dtype, *, splits: int = 1, silu: bool = False):
@@ -285,9 +289,31 @@ LINEAR_TC_SPLIT_MAX_ROWS = 64
 _LINEAR_TC = os.environ.get("SLLM_LINEAR_TCGEN05", "1") != "0"     # 0: 33..128 tokens on the library product
 
 
+# From how many tokens on it takes a product over from the streaming kernel, by the matrix's size (in-graph
+# times at 7B sizes, us, streaming kernel / this one).  A small matrix (q|k|v, o_proj: under 2^25 elements)
+# stays with the streaming kernel as far as that goes (24 tokens: 9.1 / 10.1, 7.2 / 9.3).  A large one moves
+# from 17 tokens on (24 tokens: gate|up 52.0 / 48.3, down 28.9 / 26.9; 16 tokens: 45.2 / 52.3, 24.3 / 26.3).
+# A very wide one (the output head: at least four 128-row tiles an SM) moves from 9 on (16 tokens: 190.5 /
+# 179.6; 32 tokens: 222.7 / 180.4; 8 tokens: 184.3 / 179.7, left where it is).
+LINEAR_TC_LARGE = 1 << 25
+LINEAR_TC_LARGE_FROM_ROWS = 17
+LINEAR_TC_WIDE_TILES_PER_SM = 4
+LINEAR_TC_WIDE_FROM_ROWS = 9
+
+
+def _tc_from_rows(N: int, K: int) -> int:
+    if N * K < LINEAR_TC_LARGE:
+        return STREAM_MAX_ROWS + 1
+    if -(-N // 128) >= LINEAR_TC_WIDE_TILES_PER_SM * num_sms():
+        return LINEAR_TC_WIDE_FROM_ROWS
+    return LINEAR_TC_LARGE_FROM_ROWS
+
+
 @functools.lru_cache(maxsize=4096)
 def linear_tc_supports(M: int, N: int, K: int) -> bool:
-    return _LINEAR_TC and STREAM_MAX_ROWS < M <= LINEAR_TC_MAX_ROWS and bool(lib().sllm_linear_tc_supports(int(M), int(N), int(K)))
+    if not (_LINEAR_TC and M <= LINEAR_TC_MAX_ROWS and bool(lib().sllm_linear_tc_supports(int(M), int(N), int(K)))):
+        return False
+    return M >= _tc_from_rows(N, K)
 
 
 @functools.lru_cache(maxsize=4096)
@@ -474,6 +500,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype, allow
             and linear_tc_supports(M, N, K):
         # a long reduction into few columns (the down projection): slices of K over all the SMs
         return linear_tc(x, w, bias, out_dtype, splits=_tc_splits(N, K))
+    if N * K >= LINEAR_TC_LARGE and -(-N // 128) >= num_sms() and linear_tc_supports(M, N, K):
+        return linear_tc(x, w, bias, out_dtype)      # a large matrix whose 128-row tiles are enough for every SM
     if _PAIR_GEMM == "all" and M > TCGEN05_MIN_ROWS and pair_supports(M, N, K):
         # prompt portions: pairs of CTAs on the tensor cores (tcgen05.mma with cta_group::2)
         return gemm_pair(x, w, bias, out_dtype)
@@ -662,13 +690,27 @@ def attention_tiles(q_lens, group_size: int, device, ctx_lens=None, large_rows: 
     return up(small_s, [0] * len(small_s)), up(large_s, large_r)
 
 
+SPLIT_OVERHEAD_TILES = 3      # what a CTA of the decode form costs before and after its keys, in 64-key tiles
+
+
 @functools.lru_cache(maxsize=4096)
-def choose_splits(num_small: int, nkv: int, max_ctx: int) -> int:
-    """How many ways the decode form cuts the context: enough CTAs to fill the GPU about
-    twice, never less than 256 keys a split."""
+def choose_splits(num_small: int, nkv: int, max_ctx: int, ctas_per_sm: int = 2) -> int:
+    """How many ways the decode form cuts the context: the cut whose CTAs finish first, counted in waves of
+    ``ctas_per_sm`` CTAs an SM times the 64-key tiles a CTA walks (plus its fixed cost); never less than 256
+    keys a range, at most 32 ranges.  A cut one CTA larger than a wave costs a whole second wave, so the
+    number of ranges is not simply "two CTAs an SM"."""
     ctas = max(num_small * nkv, 1)
-    want = max(1, round(2 * num_sms() / ctas))    # about two CTAs per SM
-    return int(max(1, min(want, max_ctx // 256, 32)))
+    slots = max(1, ctas_per_sm * num_sms())
+    best, best_cost = 1, None
+    for s in range(1, max(1, min(max_ctx // 256, 32)) + 1):
+        tiles = -(-(-(-max_ctx // s)) // 64)              # the kernel rounds a range up to whole tiles
+        if -(-max_ctx // (tiles * 64)) != s:              # so some counts leave their last ranges empty
+            continue
+        # (the last term: every range of every tile leaves a partial result that the merge reads again)
+        cost = -(-ctas * s // slots) * (tiles + SPLIT_OVERHEAD_TILES) + 0.5 * ctas * s / slots
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def attention_mma(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, decode: bool, num_splits: int,
@@ -695,6 +737,11 @@ def attention_mma(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, de
 @functools.lru_cache(maxsize=4096)
 def tma_attention_supports(hd: int, page_size: int) -> bool:
     return bool(lib().sllm_attention_tma_supports(int(hd), int(page_size)))
+
+
+@functools.lru_cache(maxsize=16)
+def _tma_ctas_per_sm(hd: int) -> int:
+    return int(lib().sllm_attention_tma_ctas_per_sm(int(hd)))
 
 
 def attention_tma_decode(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, num_splits: int,
@@ -800,7 +847,8 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
         # slower one at every length: 106 against 99 us for 2048 tokens, 787 against 733 us for 8192.)
         rows = 128
         small, large = attention_tiles(step.q_lens, G, q.device, step.ctx_lens, rows)
-        splits = choose_splits(small[2], nkv, step.max_ctx_len) if (small and not large) else 1
+        per_sm = _tma_ctas_per_sm(hd) if tma_attention_supports(hd, k_cache.shape[2]) else 2
+        splits = choose_splits(small[2], nkv, step.max_ctx_len, per_sm) if (small and not large) else 1
         tc_splits = choose_tc_splits(large[2], nkv, step.max_ctx_len) if (large and use_tc) else (1, 0)
         step.attn_tiles[key] = (small, large, splits, rows, tc_splits)
     small, large, splits, rows, tc_splits = step.attn_tiles[key]

@@ -55,6 +55,7 @@ def _declare(L):
         "sllm_penalty_seen": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "sllm_attention_mma_supports": [c_int],
         "sllm_attention_tma_supports": [c_int, c_int],
+        "sllm_attention_tma_ctas_per_sm": [c_int],
         "sllm_attention_tma_decode": [c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                       c_int, c_int, c_float, c_int, c_void_p, c_void_p],
