@@ -67,7 +67,9 @@ __device__ __forceinline__ void ws_mma(float (&c)[4], unsigned a0, unsigned a1, 
 }
 
 constexpr int WS_WARPS = 8;
-constexpr int WS_DEPTH = 4;      // k blocks a warp keeps in flight
+// k blocks a warp keeps in flight per group (two groups): with two token tiles half as many, so that the
+// activation fragments fit the registers of two CTAs an SM (four: 174 registers a thread, one CTA an SM)
+__host__ __device__ constexpr int ws_depth(int nt) { return nt == 1 ? 4 : 2; }
 constexpr int WS_SSQ_MAX = 384;     // partial sums of squares per token a consumer takes (the producer's CTAs)
 
 // An RMSNorm taken apart, so that a decode step needs no kernel for it (y = x * rsqrt(mean(x^2) + eps) * gain,
@@ -90,10 +92,11 @@ struct WsNorm {
 // NT: 8-token tiles (M <= 8 * NT).  OUT: float or __nv_bfloat16 (store epilogue only).  SCALED: the input
 // comes with a norm still owed (WsNorm::ssq_in).
 template <int NT, int EPI, typename OUT, bool SCALED>
-__global__ void __launch_bounds__(WS_WARPS * 32)
+__global__ void __launch_bounds__(WS_WARPS * 32, 2)
 linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W,
                  const float* __restrict__ bias, OUT* __restrict__ out, float* __restrict__ residual,
                  int M, int N, int K, const WsRope rope, const WsNorm norm) {
+  constexpr int WS_DEPTH = ws_depth(NT);
   __shared__ float red[WS_WARPS][16][8 * NT + 1];
   __shared__ float row_scale[8 * NT];
   __shared__ __align__(16) float ssq_s[SCALED ? 8 * NT : 1][SCALED ? WS_SSQ_MAX : 4];

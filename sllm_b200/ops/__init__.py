@@ -351,7 +351,7 @@ def linear_tc(x, w, bias, out_dtype, *, splits: int = 1, silu: bool = False):
 
 
 WS_MAX_COLS = 8192        # wider products have CTAs enough for the 128-row streaming kernel
-WS_MAX_ROWS = 8           # with 9..16 tokens its second token tile costs registers and it falls behind
+WS_MAX_ROWS = 16          # two 8-token tiles (with half as many k blocks in flight, so that two CTAs still share an SM)
 
 
 @functools.lru_cache(maxsize=4096)

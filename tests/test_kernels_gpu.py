@@ -157,7 +157,7 @@ def test_rope_kv_write_wide_form(in_dtype, T, nq, nkv, hd, rot, ps):
     assert not k2.any() and not v2.any()
 
 
-@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 13, 16])
 @pytest.mark.parametrize("nq,nkv,hd,K,ps", [(28, 4, 128, 3584, 16), (14, 2, 64, 896, 64), (4, 2, 16, 64, 16), (3, 1, 32, 96, 8),
                                             (6, 3, 48, 160, 16), (2, 2, 256, 128, 32)])
 def test_linear_rope_kv_write(M, nq, nkv, hd, K, ps):

@@ -81,8 +81,10 @@ def test_wide_layers_graph_decode_matches_eager(wide_model):
             assert outs[0] == [plain.generate(p, 6, w, cfg) for p in prompts]
 
 
-def test_decode_steps_leave_their_norms_to_the_products(wide_model, monkeypatch):
-    """In a decode step of few tokens the products that complete the residual stream prepare the next
+@pytest.mark.parametrize("per_request", [1, 3, 5])
+def test_decode_steps_leave_their_norms_to_the_products(wide_model, monkeypatch, per_request):
+    """In a decode step of few tokens (3, 9 or 15 here: one or two 8-token tiles of the kernels) the
+    products that complete the residual stream prepare the next
     RMSNorm's input and the consuming products pay the division: of the 2 L + 1 norms only the first layer's
     and the final one remain kernels.  The logits are those of the step with every norm a kernel, to
     bfloat16 rounding, and the plain implementation's within the bounds of the other tests here."""
@@ -100,12 +102,12 @@ def test_decode_steps_leave_their_norms_to_the_products(wide_model, monkeypatch)
         eng = Engine(model, page_size=16, num_pages=32, max_requests=4)
         eng.step([StepEntry(r, ids[:30], []) for r, ids in reqs.items()])
         with ops.KernelTimes() as kt:
-            logits = eng.step([StepEntry(r, ids[30:31], [0]) for r, ids in reqs.items()])
+            logits = eng.step([StepEntry(r, ids[30:30 + per_request], list(range(per_request))) for r, ids in reqs.items()])
         counts[fused] = kt.table().get("sllm_add_rmsnorm", (0, 0.0))[0]
         rows[fused] = logits.float().cpu().numpy()
     L = cfg["num_hidden_layers"]
     assert counts[False] == 2 * L + 1 and counts[True] == 2, counts
-    ref_rows = np.stack([want[r][30] for r in reqs])
+    ref_rows = np.concatenate([want[r][30:30 + per_request] for r in reqs])
     for fused in (True, False):
         assert np.abs(rows[fused] - ref_rows).max() <= 0.08 * spread
         assert float(np.sqrt(((rows[fused] - ref_rows) ** 2).mean())) <= 0.02 * spread
