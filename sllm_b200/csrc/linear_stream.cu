@@ -33,7 +33,7 @@ constexpr int LS_XSTRIDE = LS_KC + 32;     // bf16 elements: 320 bytes, = 64 mod
 #define EPI_STORE 0
 #define EPI_SILU 1
 
-constexpr int LS_SSQ_MAX = 384;            // partial sums of squares per token a scaled launch takes
+constexpr int LS_SSQ_MAX = 608;            // partial sums of squares per token a scaled launch takes (as in linear_ws.cu)
 
 // A norm still owed on the input (see linear_ws.cu, WsNorm): x is bfloat16(stream * gain), ssq [M][stride]
 // (stride = parts rounded up to 4) holds partial sums of squares of the stream's rows, and every row of the
@@ -226,7 +226,7 @@ static int launch_ls(const __nv_bfloat16* x, const __nv_bfloat16* W, const float
                      int M, int N, int K, int splits, cudaStream_t stream, const LsScale& scale = LsScale{}) {
   constexpr size_t smem = sizeof(__nv_bfloat16) * 2 * 8 * NT * LS_XSTRIDE + (SCALED ? sizeof(float) * 8 * NT * LS_SSQ_MAX : 0);
   static bool configured = false;
-  if (!configured && smem > 48 * 1024) {
+  if (!configured && smem + 1024 > 48 * 1024) {      // (the kernel has a little static shared memory too)
     if (cudaFuncSetAttribute(linear_stream_kernel<NT, EPI, OUT, SCALED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
       set_error("linear_stream: cannot raise the shared memory limit");
       return SLLM_ERR_LAUNCH;

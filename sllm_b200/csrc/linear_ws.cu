@@ -70,7 +70,7 @@ constexpr int WS_WARPS = 8;
 // k blocks a warp keeps in flight per group (two groups): with two token tiles half as many, so that the
 // activation fragments fit the registers of two CTAs an SM (four: 174 registers a thread, one CTA an SM)
 __host__ __device__ constexpr int ws_depth(int nt) { return nt == 1 ? 4 : 2; }
-constexpr int WS_SSQ_MAX = 384;     // partial sums of squares per token a consumer takes (the producer's CTAs)
+constexpr int WS_SSQ_MAX = 608;     // partial sums of squares per token a consumer takes (the producer's CTAs: at most 592 for 8192 columns)
 
 // An RMSNorm taken apart, so that a decode step needs no kernel for it (y = x * rsqrt(mean(x^2) + eps) * gain,
 // ref/standard.py:25-31).  The product that completes the residual stream (residual epilogue) also writes
@@ -280,21 +280,24 @@ linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
   }
 }
 
-// CTAs of 16 rows, or, when those would fill the SMs unevenly, the next multiple of the SM count
-static int ws_ctas(int N, bool rope) {
+// CTAs of 16 rows, or more of fewer rows where those would fill the SMs unevenly (two CTAs share an SM).  Between one
+// and two CTAs an SM: the next multiple of the SM count (N = 3584: 296 CTAs of 12 or 13 rows for 224 of 16).  Beyond two
+// an SM the fixed cost of more CTAs outweighs an uneven last wave unless the rows are long (measured at 8 tokens,
+// N = 5120: K = 5120 13.5 us with 320 CTAs, 14.5 with 592; K = 27648 61.4 against 50.4).
+static int ws_ctas(int N, int K, bool rope) {
   const int num_sms = sllm::num_sms();
   int ctas = (N + 15) / 16;
-  if (!rope && ctas > num_sms && ctas % num_sms != 0) {
-    const int even = (ctas + num_sms - 1) / num_sms * num_sms;
-    if (even <= N) ctas = even;
-  }
-  return ctas;
+  if (rope || ctas <= num_sms) return ctas;
+  int even = ctas;
+  if (ctas < 2 * num_sms) even = (ctas + num_sms - 1) / num_sms * num_sms;
+  else if (K > 8192) even = (ctas + 2 * num_sms - 1) / (2 * num_sms) * (2 * num_sms);
+  return even <= N ? even : ctas;
 }
 
 template <int NT, int EPI, typename OUT>
 static int launch_ws(const __nv_bfloat16* x, const __nv_bfloat16* W, const float* bias, void* out, float* residual,
                      int M, int N, int K, cudaStream_t stream, const WsRope& rope = WsRope{}, const WsNorm& norm = WsNorm{}) {
-  const int ctas = ws_ctas(N, EPI == WS_EPI_ROPE);
+  const int ctas = ws_ctas(N, K, EPI == WS_EPI_ROPE);
   if (norm.ssq_in != nullptr)
     launch_kernel(linear_ws_kernel<NT, EPI, OUT, true>, ctas, WS_WARPS * 32, 0, stream, x, W, bias, (OUT*)out, residual, M, N, K, rope, norm);
   else
@@ -310,9 +313,9 @@ SLLM_EXPORT int sllm_linear_ws_supports(int M, int N, int K) {
   return M >= 1 && M <= 16 && N >= 16 && K >= 32 && K % 32 == 0;
 }
 
-// CTAs a launch for N output columns uses: the rows of the table of partial sums of squares that the
-// residual epilogue writes when it is asked for the next norm's input (see WsNorm).
-SLLM_EXPORT int sllm_linear_ws_parts(int N) { return ws_ctas(N, false); }
+// CTAs a launch for N output columns over a reduction of K uses: the rows of the table of partial sums of squares
+// that the residual epilogue writes when it is asked for the next norm's input (see WsNorm).
+SLLM_EXPORT int sllm_linear_ws_parts(int N, int K) { return ws_ctas(N, K, false); }
 
 static bool ws_norm_in(WsNorm& n, const float* ssq_in, int parts_in, float eps_in, int width_in) {
   if (ssq_in == nullptr) return true;
@@ -326,7 +329,7 @@ static bool ws_norm_in(WsNorm& n, const float* ssq_in, int parts_in, float eps_i
 // ssq_in != null: x is bfloat16(stream * gain) of a norm still owed and ssq_in [M][parts_in rounded up to 4] holds partial sums of
 // squares of the stream's rows (width_in wide): each row of the product is multiplied by rsqrt(sum / width_in + eps_in).
 // gain != null (residual epilogue only): also write xg_out [M, N] = bfloat16(residual * gain) and
-// ssq_out [M][sllm_linear_ws_parts(N) rounded up to 4], the next norm's input in the same form.
+// ssq_out [M][sllm_linear_ws_parts(N, K) rounded up to 4], the next norm's input in the same form.
 SLLM_EXPORT int sllm_linear_ws(const void* x, const void* W, const float* bias, void* out, int out_dtype, float* residual,
                                int M, int N, int K, const float* ssq_in, int parts_in, float eps_in, int width_in,
                                const float* gain, void* xg_out, float* ssq_out, cudaStream_t stream) {

@@ -377,7 +377,7 @@ class RowScale:
 
 
 _NO_SCALE = (None, 0, 0.0, 0)
-MAX_SCALE_PARTS = 384          # partial sums a consumer keeps in shared memory per row
+MAX_SCALE_PARTS = 608          # partial sums a consumer keeps in shared memory per row
 
 
 def linear_ws(x, w, bias, out_dtype, residual=None, scale: RowScale | None = None, next_gain=None):
@@ -401,7 +401,7 @@ def linear_ws(x, w, bias, out_dtype, residual=None, scale: RowScale | None = Non
     if next_gain is not None:
         if residual is None or next_gain.dtype != torch.float32 or next_gain.numel() != N:
             raise KernelError("linear_ws: the next norm's input needs the residual epilogue and a float32 gain of N values")
-        parts = int(lib().sllm_linear_ws_parts(N))
+        parts = int(lib().sllm_linear_ws_parts(N, K))
         xg = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
         ssq = torch.empty((M, (parts + 3) & ~3), dtype=torch.float32, device=x.device)
     call("sllm_linear_ws", _p(x), _p(w), _p(bias), _p(out), _dtc(out_dtype), _p(residual), M, N, K,
@@ -442,7 +442,7 @@ def can_accumulate_norm(x: torch.Tensor, w: torch.Tensor) -> bool:
         return False
     M, N = x.shape[0], w.shape[0]
     if ws_supports(M, N, x.shape[1]):
-        return int(lib().sllm_linear_ws_parts(N)) <= MAX_SCALE_PARTS
+        return int(lib().sllm_linear_ws_parts(N, x.shape[1])) <= MAX_SCALE_PARTS
     return N % 8 == 0
 
 

@@ -76,7 +76,7 @@ def _declare(L):
         "sllm_linear_ws_supports": [c_int, c_int, c_int],
         "sllm_linear_ws": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                            c_void_p, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
-        "sllm_linear_ws_parts": [c_int],
+        "sllm_linear_ws_parts": [c_int, c_int],
         "sllm_linear_stream_silu_scaled": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_float, c_int,
                                            c_void_p],
         "sllm_linear_ws_rope_supports": [c_int, c_int, c_int, c_int, c_int, c_int, c_int],

@@ -846,7 +846,7 @@ def test_linear_ws(M, N, K):
 
 
 @pytest.mark.parametrize("M", [1, 3, 8, 11, 16])
-@pytest.mark.parametrize("H,K", [(3584, 3584), (3584, 18944), (896, 4864), (1000, 320), (96, 64)])
+@pytest.mark.parametrize("H,K", [(3584, 3584), (3584, 18944), (896, 4864), (1000, 320), (96, 64), (5120, 13824), (8192, 512)])
 def test_an_rmsnorm_owed_by_one_product_and_paid_by_the_next(M, H, K):
     """The product that completes the residual stream also writes the next RMSNorm's input as
     bfloat16(stream * gain) with partial sums of squares, and the products that consume it (plain, the
