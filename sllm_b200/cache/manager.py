@@ -22,6 +22,9 @@ from ..parts.base import LayerCache, PagedKV, SlotState
 from .pools import OutOfPages, PagePool, SlotPool
 
 
+RUN_TOKENS = 64      # the attention kernels' key tile: its pages are one copy when their ids are consecutive
+
+
 @dataclass
 class CacheGroup:
     need: PagedKV
@@ -74,8 +77,9 @@ class CacheManager:
             num_pages = [num_pages] * len(self.groups)
         if len(num_pages) != len(self.groups):
             raise ValueError(f"num_pages names {len(num_pages)} groups, the model has {len(self.groups)}")
+        # ids are best held in runs of a 64-key tile's pages (see pools.py)
         for g, n in zip(self.groups, num_pages):
-            g.pool = PagePool(n)
+            g.pool = PagePool(n, run=max(1, RUN_TOKENS // self.page_size))
         self.slots = SlotPool(self.max_requests)
         self.requests: dict[object, RequestCache] = {}
         self.kv_storage = []       # per group: tensor [runs, 2, pages, nkv, page_size, hd]
@@ -146,7 +150,8 @@ class CacheManager:
                 raise OutOfPages(f"request {req_id!r} needs {e} more pages for {total_tokens} tokens, "
                                  f"{g.pool.free_count} free of {g.pool.capacity}")
         for gi, (e, g) in enumerate(zip(extra, self.groups)):
-            ids = g.pool.allocate(req_id, e)
+            tail = req.tables[gi][-1] if req.tables[gi] and req.tables[gi][-1] >= 0 else None
+            ids = g.pool.allocate(req_id, e, after=tail)
             self.reuse_count += sum(1 for p in ids if p in self._ever_used[gi])
             self._ever_used[gi].update(ids)
             req.tables[gi].extend(ids)

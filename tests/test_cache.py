@@ -29,6 +29,54 @@ def test_page_pool_lowest_first_and_ownership():
     p.check()
 
 
+def test_page_pool_hands_out_runs():
+    """A pool told that ids are best held in runs of 4: owners that grow by a page at a time, in turn,
+    each get consecutive ids inside aligned groups; when no group is wholly free the rest of other owners'
+    groups is used, lowest id first; the books stay right throughout."""
+    p = PagePool(24, run=4)
+    tails = {}
+    for _ in range(4):                                       # three owners, four rounds of one page each
+        for o in "abc":
+            (tails[o],) = p.allocate(o, 1, after=tails.get(o))
+            p.check()
+    assert p.owned("a") == [0, 1, 2, 3] and p.owned("b") == [4, 5, 6, 7] and p.owned("c") == [8, 9, 10, 11]
+    # a group ends: the next one is the lowest wholly free group, not the id after the tail
+    assert p.allocate("a", 1, after=3) == [12]
+    assert p.allocate("b", 6, after=7) == [16, 17, 18, 19, 20, 21]      # whole groups first, in order
+    # no wholly free group is left (12 is a's, 20..21 b's): c takes the lowest free ids, whoever's group they are in
+    assert p.allocate("c", 2, after=11) == [13, 14]
+    assert p.allocate("a", 1, after=12) == [15]              # a's own group, what is left of it
+    p.free("b", [16, 17, 18, 19])
+    assert p.allocate("c", 1, after=14) == [16]              # a group came back whole
+    with pytest.raises(OutOfPages):
+        p.allocate("c", 6, after=16)
+    p.check()
+    assert p.free_count == 5
+    # without a tail, or with runs of one, it is "lowest free id first"
+    q = PagePool(6, run=1)
+    assert q.allocate("a", 2, after=4) == [0, 1]
+
+
+def test_requests_that_grow_in_turn_hold_runs_of_pages():
+    """Eight requests decoding side by side, a page each every few steps: every request's table is made of
+    aligned runs of 64 tokens' pages (what the attention kernels fetch as one copy), not of every eighth id."""
+    m = _manager(num_pages=8 * 24, page=16, window=None, max_requests=8, layers=1)
+    for r in range(8):
+        m.add_request(r)
+        m.reserve(r, 40 + r)                                  # prompts of different lengths: 3 pages each
+        m.commit(r, 40 + r)
+    for n in range(48, 360, 8):                              # then they grow together
+        for r in range(8):
+            m.reserve(r, n)
+            m.commit(r, n)
+        m.check()
+    for r in range(8):
+        t = m.requests[r].tables[0]
+        assert len(t) == 22
+        runs = sum(1 for i in range(0, len(t) - 3, 4) if t[i] % 4 == 0 and t[i:i + 4] == list(range(t[i], t[i] + 4)))
+        assert runs == 5, (r, t)                             # every whole group of four is one run
+
+
 def test_slot_pool():
     s = SlotPool(2)
     assert s.allocate("a") == 0 and s.allocate("b") == 1
