@@ -596,13 +596,13 @@ def main(argv=None) -> int:
             points[f"decode_b{b}_hbm_frac"] = round(r["step_bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
         # between them, where the dispatch changes kernels (up to 16 tokens, up to 32, up to 128)
         for b in (16, 32, 128):
-            r = decode_run(model, cfg, b, args.context, args.steps, 3, seed=b, repeats=2)
+            r = decode_run(model, cfg, b, args.context, args.steps, 3, seed=b, repeats=min(3, args.repeats))
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
             points[f"decode_b{b}_hbm_frac"] = round(r["step_bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
         # long contexts, where the cache is most of what a step reads (the attention kernels are compared with their
         # float32 statement at these lengths in tests/test_long_context_gpu.py)
         for b, ctx in ((8, 16384), (1, 32768)):
-            r = decode_run(model, cfg, b, ctx, args.steps, 3, seed=ctx, repeats=2)
+            r = decode_run(model, cfg, b, ctx, args.steps, 3, seed=ctx, repeats=min(3, args.repeats))
             points[f"decode_b{b}_ctx{ctx}"] = round(r["tok_s"], 1)
             points[f"decode_b{b}_ctx{ctx}_hbm_frac"] = round(r["step_bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
         # the baseline's stated run: prompts of 2,048 tokens, then 256 greedy tokens, every decode step timed
