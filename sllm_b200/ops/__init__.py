@@ -103,6 +103,7 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, bias) -> torch.Tensor:
 
 
 TCGEN05_MIN_ROWS = 128    # below this a 128-row tile is mostly padding
+PAIR_SILU_FROM_ROWS = 64  # from here on gate|up with its activation goes to the CTA-pair kernel (see `linear_silu_mul`)
 STREAM_MAX_ROWS = 32      # beyond this the kernel's shared-memory reads of the activations bound it
 
 
@@ -555,6 +556,11 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, o
         N = w_gate_up.shape[0]
         if stream_supports(M, N, K):
             return linear_stream(x, w_gate_up, None, out_dtype, silu=True)
+        if PAIR_SILU_FROM_ROWS <= M <= TCGEN05_MIN_ROWS and N % 16 == 0 and _PAIR_GEMM != "off" and pair_supports(M, N, K):
+            # 64..128 tokens: still bound by reading W once, and the pair kernel's narrow tiles (two accumulators, the
+            # epilogue under the next tile) stream it faster than `linear_tc`, whose accumulator is 128 columns wide there
+            # (in a graph, 7B sizes, us: 64 tokens 51.0 against 53.4, 96 tokens 51.8 / 57.9, 128 tokens 53.1 / 61.9)
+            return gemm_pair(x, w_gate_up, None, out_dtype, silu=True, wide=False)
         if N % 16 == 0 and linear_tc_supports(M, N, K):
             return linear_tc(x, w_gate_up, None, out_dtype, silu=True)
         if M > TCGEN05_MIN_ROWS and N % 16 == 0 and _PAIR_GEMM != "off" and pair_supports(M, N, K):
