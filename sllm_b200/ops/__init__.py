@@ -357,7 +357,16 @@ WS_MAX_ROWS = 16          # two 8-token tiles (with half as many k blocks in fli
 
 @functools.lru_cache(maxsize=4096)
 def ws_supports(M: int, N: int, K: int) -> bool:
-    return M <= WS_MAX_ROWS and N <= WS_MAX_COLS and bool(lib().sllm_linear_ws_supports(int(M), int(N), int(K)))
+    """Whether the warp-split kernel is the one for this product.  With two token tiles (9..16 tokens) only where
+    its 16-row CTAs fit the GPU at once: at N = 5120 (320 to 592 CTAs for 296 places) it falls behind the k-split
+    kernel by more than the fused epilogues save (16 tokens, K = 27648: 64.3 against 49.2 us)."""
+    if not (M <= WS_MAX_ROWS and N <= WS_MAX_COLS and bool(lib().sllm_linear_ws_supports(int(M), int(N), int(K)))):
+        return False
+    return _ws_tokens_ok(M, N)
+
+
+def _ws_tokens_ok(M: int, N: int) -> bool:
+    return M <= 8 or -(-N // 16) <= 2 * num_sms()
 
 
 class RowScale:
@@ -582,7 +591,7 @@ def qkv_rope_supports(x, w, table, rotary_dim, nq, nkv, hd, k_cache) -> bool:
         return False
     rot = int(rotary_dim) if table is not None else 0
     M, K = x.shape
-    return M <= WS_MAX_ROWS and bool(lib().sllm_linear_ws_rope_supports(int(M), int(w.shape[0]), int(K), int(nq), int(nkv),
+    return M <= WS_MAX_ROWS and _ws_tokens_ok(M, w.shape[0]) and bool(lib().sllm_linear_ws_rope_supports(int(M), int(w.shape[0]), int(K), int(nq), int(nkv),
                                                                           int(hd), rot))
 
 
