@@ -456,6 +456,106 @@ def kernel_times(model, cfg, batch, context):
     return out
 
 
+def graph_times(cfg, batch, context) -> dict:
+    """Microseconds per launch of the kernels of one decode layer at `batch` tokens, each kind repeated in a CUDA
+    graph of its own with its weights (or keys and values) cycled over copies larger than L2 together, so that
+    every launch streams from HBM and runs behind a launch of its own kind, as it does inside a step.  Products
+    in the forms the dispatch knows (`ws`: warp-split with the residual epilogue; `stream`: k-split partial sums;
+    `tc`: tensor-memory streaming; `pair`: CTA pairs; `library`: torch.mm), decode attention with its merge at the
+    number of ranges the engine picks and its neighbours."""
+    import torch
+
+    from sllm_b200 import ops
+    dev = "cuda:0"
+    H, I = cfg["hidden_size"], cfg["intermediate_size"]
+    nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                fn()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(9):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3 / reps)
+        return round(statistics.median(ts), 2)
+
+    out = {}
+    M = batch
+    for name, N, K, silu in (("qkv", (nq + 2 * nkv) * hd, H, False), ("o_proj", H, nq * hd, False),
+                             ("gate_up", 2 * I, H, True), ("down", H, I, False)):
+        copies = max(3, -(-400_000_000 // (N * K * 2)))
+        ws = [(torch.randn(N, K, device=dev) * 0.02).bfloat16() for _ in range(copies)]
+        x = torch.randn(M, K, device=dev).bfloat16()
+        res = torch.zeros(M, N, device=dev)
+        turn = [0]
+
+        def w():
+            turn[0] += 1
+            return ws[turn[0] % copies]
+        forms = {}
+        if silu:
+            forms["dispatch"] = lambda: ops.linear_silu_mul(x, w(), 8, torch.bfloat16)
+            if M <= 32:
+                forms["stream"] = lambda: ops.linear_stream(x, w(), None, torch.bfloat16, silu=True)
+            if M <= 128:
+                forms["tc"] = lambda: ops.linear_tc(x, w(), None, torch.bfloat16, silu=True)
+            forms["pair"] = lambda: ops.gemm_pair(x, w(), None, torch.bfloat16, silu=True, wide=False)
+        else:
+            forms["dispatch"] = lambda: ops.linear(x, w(), None, torch.float32, allow_partials=True)
+            if ops.ws_supports(M, N, K):
+                forms["ws"] = lambda: ops.linear_ws(x, w(), None, torch.float32, residual=res)
+            if M <= 32:
+                forms["stream"] = lambda: ops.linear_stream(x, w(), None, torch.float32, splits=ops._stream_splits(N, K))
+            if M <= 128:
+                forms["tc"] = lambda: ops.linear_tc(x, w(), None, torch.float32, splits=ops._tc_splits(N, K))
+            forms["library"] = lambda: torch.mm(x, w().t(), out_dtype=torch.float32)
+        rec = {"bytes_alone_us": round(N * K * 2 / 1e6 / (load_peaks()[0]["hbm_gbs"] / 1e3), 2)}
+        for form, fn in forms.items():
+            try:
+                rec[form] = timed(fn, reps=3 * copies)
+            except Exception as e:      # noqa: BLE001  (a form that refuses these sizes says so in the record)
+                rec[form] = f"{type(e).__name__}"
+        out[name] = rec
+        del ws
+        torch.cuda.empty_cache()
+    # decode attention over `context` keys a request, pages with consecutive ids
+    ps = PAGE_SIZE
+    per = -(-context // ps)
+    copies = 3 if batch * context * nkv * hd * 4 < 1.2e9 else 2
+    caches = []
+    for _ in range(copies):
+        kc = torch.randn(batch * per + 1, nkv, ps, hd, device=dev).bfloat16()
+        caches.append((kc, torch.randn_like(kc)))
+    bt = torch.arange(batch * per, device=dev, dtype=torch.int32).reshape(batch, per)
+    q = torch.randn(batch, nq * hd, device=dev).bfloat16()
+    q_start = torch.arange(batch + 1, device=dev, dtype=torch.int32)
+    ctx_len = torch.full((batch,), context, device=dev, dtype=torch.int32)
+    small, _ = ops.attention_tiles([1] * batch, nq // nkv, dev)
+    picked = ops.choose_splits(batch, nkv, context, ops._tma_ctas_per_sm(hd))
+    rec = {"bytes_alone_us": round(batch * context * nkv * hd * 4 / 1e6 / (load_peaks()[0]["hbm_gbs"] / 1e3), 2), "picked_ranges": picked}
+    turn = [0]
+    for s in sorted({max(1, picked - 1), picked, min(32, picked + 1)}):
+        def attend(s=s):
+            turn[0] += 1
+            kc, vc = caches[turn[0] % copies]
+            ops.attention_tma_decode(q, kc, vc, bt, q_start, ctx_len, small, s, nq, nkv, hd, hd ** -0.5, None)
+        rec[f"ranges_{s}"] = timed(attend, reps=2 * copies)
+    out["attention_and_merge"] = rec
+    ops.check_tcgen05_status()
+    return out
+
+
 def reference_main(args) -> int:
     """The reference arm: the same metric, sizes, batch, context and number of steps through skfine24/sLLM's own
     device-resident decode (see baseline/reference_arm.py)."""
@@ -523,6 +623,8 @@ def main(argv=None) -> int:
     ap.add_argument("--prefill-only", action="store_true", help="run the 2,048-token prefill alone (for profilers)")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
     ap.add_argument("--kernel-times", action="store_true", help="add device time per kernel entry point (a step launched kernel by kernel)")
+    ap.add_argument("--graph-times", action="store_true",
+                    help="print microseconds per launch of one decode layer's kernels at --batch and --context, each kind in a graph of its own, and exit")
     args = ap.parse_args(argv)
     globals()["PAGE_SIZE"] = args.page_size
     args.repeats = max(1, args.repeats)
@@ -545,6 +647,10 @@ def main(argv=None) -> int:
         return 1
     if args.workload != "decode":
         print(json.dumps(serving_run(args.workload, args.layers)))
+        return 0
+    if args.graph_times:
+        print(json.dumps({"graph_times_us": graph_times(CONFIG_7B, args.batch, args.context), "batch": args.batch,
+                          "context": args.context, "page_size": PAGE_SIZE}))
         return 0
     args.layers = args.layers or FULL_LAYERS
     peaks, peaks_kind = load_peaks()
