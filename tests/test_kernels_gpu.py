@@ -773,19 +773,21 @@ def test_gemm_pair_owes_and_pays_an_rmsnorm(M, H, K, wide):
     ops.check_tcgen05_status()
 
 
-@pytest.mark.parametrize("M", [33, 64, 65, 100, 128])
-@pytest.mark.parametrize("N,K", [(128, 64), (136, 72), (1000, 264), (4608, 3584), (3584, 18944)])
+@pytest.mark.parametrize("M", [1, 9, 17, 24, 32, 33, 64, 65, 100, 128])
+@pytest.mark.parametrize("N,K", [(128, 64), (136, 72), (1000, 264), (4608, 3584), (3584, 18944), (9480, 3584), (75784, 512)])
 def test_linear_tc(M, N, K):
     """The tcgen05 streaming product against the float32 statement: one and several slices of K (their
     sum is the product, bias once), ragged rows, a k tail, both accumulator widths, and a row's result
-    does not depend on the other rows of the batch."""
+    does not depend on the other rows of the batch.  Few tokens too: the dispatch sends large matrices
+    to it from 17 tokens on and very wide ones (an output head) from 9."""
     ops = _ops()
     g = torch.Generator(device="cuda").manual_seed(18)
     x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
     w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
     b = torch.randn(N, device="cuda", generator=g)
     want = x.float() @ w.float().t() + b
-    assert ops.linear_tc_supports(M, N, K)
+    assert ops.linear_tc_supports(M, N, K) == (M >= ops._tc_from_rows(N, K))
+    assert ops._tc_from_rows(N, K) == (9 if N > 70000 else 17 if N * K >= 1 << 25 else 33)
     whole = ops.linear_tc(x, w, b, torch.float32)
     torch.testing.assert_close(whole, want, rtol=2e-3, atol=2e-3)
     torch.testing.assert_close(ops.linear_tc(x, w, None, torch.bfloat16).float(), want - b, rtol=1.6e-2, atol=1.6e-2)
@@ -796,16 +798,18 @@ def test_linear_tc(M, N, K):
             parts = parts.sum(0)
         torch.testing.assert_close(parts, want, rtol=2e-3, atol=2e-3)
     ops.check_tcgen05_status()
-    fewer = ops.linear_tc(x[M - 33:].contiguous(), w, b, torch.float32)
+    fewer = ops.linear_tc(x[M // 2:].contiguous(), w, b, torch.float32)
     assert torch.equal(fewer[-1], whole[-1])
     # and through the dispatch, as the engine calls it
     torch.testing.assert_close(ops.linear(x, w, b, torch.float32), want, rtol=2e-3, atol=2e-3)
     stack = ops.linear(x, w, b, torch.float32, allow_partials=True)
-    assert (stack.dim() == 3) == (K >= ops.LINEAR_TC_SPLIT_MIN_K and M <= ops.LINEAR_TC_SPLIT_MAX_ROWS)
+    if ops.linear_tc_supports(M, N, K):
+        assert (stack.dim() == 3) == (K >= ops.LINEAR_TC_SPLIT_MIN_K and M <= ops.LINEAR_TC_SPLIT_MAX_ROWS)
     torch.testing.assert_close(stack.sum(0) if stack.dim() == 3 else stack, want, rtol=2e-3, atol=2e-3)
 
 
-@pytest.mark.parametrize("M,I,K", [(40, 128, 64), (64, 200, 136), (128, 4864, 896), (96, 18944, 3584)])
+@pytest.mark.parametrize("M,I,K", [(40, 128, 64), (64, 200, 136), (128, 4864, 896), (96, 18944, 3584), (17, 18944, 3584),
+                                   (24, 4744, 3584), (1, 128, 64), (48, 18944, 3584)])
 def test_linear_tc_silu(M, I, K):
     ops = _ops()
     g = torch.Generator(device="cuda").manual_seed(19)
