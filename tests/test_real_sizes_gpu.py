@@ -114,6 +114,33 @@ def test_decode_steps_leave_their_norms_to_the_products(wide_model, monkeypatch,
     assert float(np.sqrt(((rows[True] - rows[False]) ** 2).mean())) <= 0.02 * spread
 
 
+@pytest.mark.parametrize("per_request", [6, 8, 11, 21, 30])
+def test_steps_of_17_to_90_tokens(wide_model, per_request):
+    """Steps between the fused few-token kernels and the prompt-portion kernels (18, 24, 33, 63 and 90 tokens here,
+    three requests side by side): large products on the tensor-memory streaming kernel from 17 tokens, gate|up on
+    the CTA-pair kernel from 64, the rest on the k-split kernel or the library; logits against the plain
+    implementation within the bounds of the other tests here."""
+    from sllm_b200 import ops
+    from sllm_b200.engine import Engine, StepEntry, build_model
+    dev = cuda_or_skip()
+    model_dir, cfg, reqs, want = wide_model
+    model, _ = build_model(model_dir, "bfloat16", dev)
+    spread = float(np.concatenate([v.ravel() for v in want.values()]).std())
+    eng = Engine(model, page_size=16, num_pages=32, max_requests=4)
+    eng.step([StepEntry(r, ids[:5], []) for r, ids in reqs.items()])
+    with ops.KernelTimes() as kt:
+        logits = eng.step([StepEntry(r, ids[5:5 + per_request], list(range(per_request))) for r, ids in reqs.items()])
+    ops.check_tcgen05_status()
+    used = set(kt.table())
+    tokens = 3 * per_request
+    if 17 <= tokens <= 128:
+        assert "sllm_linear_tc" in used or "sllm_gemm_pair" in used, used
+    ref_rows = np.concatenate([want[r][5:5 + per_request] for r in reqs])
+    got = logits.float().cpu().numpy()
+    assert np.abs(got - ref_rows).max() <= 0.08 * spread
+    assert float(np.sqrt(((got - ref_rows) ** 2).mean())) <= 0.02 * spread
+
+
 def test_prompt_portions_leave_their_norms_to_the_products(wide_model, monkeypatch):
     """A prompt portion of more than 128 tokens: the products that complete the residual stream (on the CTA-pair
     kernel) prepare the next RMSNorm's input, the consuming products pay the division, and of the 2 L + 1 norms
