@@ -35,13 +35,18 @@
 namespace sllm {
 
 constexpr int TP_BM = 128;                                // rows of A (and of C) per CTA; the pair's tile has 256
-constexpr int TP_BN = 256;                                // columns of C per tile; each CTA loads 128 rows of W
-constexpr int TP_BK = 64, TP_STAGES = 6;
+constexpr int TP_BK = 64;
 constexpr int TP_A_BYTES = TP_BM * TP_BK * 2;             // 16 KB
-constexpr int TP_B_BYTES = (TP_BN / 2) * TP_BK * 2;       // 16 KB
-constexpr int TP_STAGE_BYTES = TP_A_BYTES + TP_B_BYTES;
-constexpr int TP_SMEM = TP_STAGES * TP_STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
-constexpr int TP_TMEM_COLS = 512;                         // two accumulators of 256 columns
+// BN: columns of C per tile, 256 or 128; each CTA loads BN / 2 rows of W.  The slim tile is for results with so few
+// tiles of 256 x 256 that most pairs of SMs would have none (a prompt portion of 512 tokens times a matrix of 3,584
+// rows: 28 tiles for 74 pairs): twice the tiles at half the width.
+template <int BN> struct TpCfg {
+  static constexpr int B_BYTES = (BN / 2) * TP_BK * 2;    // 16 or 8 KB
+  static constexpr int STAGE_BYTES = TP_A_BYTES + B_BYTES;
+  static constexpr int STAGES = BN == 256 ? 6 : 8;        // 192 KB either way
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+  static constexpr int TMEM_COLS = 2 * BN;                // two accumulators
+};
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -80,13 +85,15 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
 }
 
-template <int EPI>
+template <int EPI, int BN>
 __global__ void __launch_bounds__(192, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                  const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K, int* __restrict__ status,
-                 const TgExtra extra) {
+                 const TgExtra extra, const int ksplits, const int kb_per_split) {
   extern __shared__ unsigned char tp_smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tp_smem_raw) + 1023) & ~(uintptr_t)1023);
+  using C = TpCfg<BN>;
+  constexpr int TP_BN = BN, TP_STAGES = C::STAGES, TP_STAGE_BYTES = C::STAGE_BYTES, TP_TMEM_COLS = C::TMEM_COLS;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + TP_STAGES * TP_STAGE_BYTES);
   uint64_t* empty = full + TP_STAGES;
   uint64_t* acc_full = empty + TP_STAGES;           // [2]
@@ -98,8 +105,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const uint32_t rank = cluster_ctarank();          // 0: the CTA whose thread issues the products
   const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
   const int m_tiles = (M + 2 * TP_BM - 1) / (2 * TP_BM), n_tiles = (N + TP_BN - 1) / TP_BN;
-  const int tiles = m_tiles * n_tiles;
-  const int k_blocks = (K + TP_BK - 1) / TP_BK;
+  // A unit of work is a tile and a slice of K (ksplits slices of kb_per_split 64-wide blocks; one slice unless the
+  // result has so few tiles that most pairs would have none): unit u is slice u % ksplits of tile u / ksplits, and
+  // slice s leaves its partial sums in out[s] of a stack [ksplits, M, N] (float32 epilogue only; bias in slice 0).
+  const int tiles = m_tiles * n_tiles * ksplits;
+  const int k_blocks_all = (K + TP_BK - 1) / TP_BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TP_STAGES; ++s) {
@@ -129,10 +139,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (lane == 0) {
       int it = 0;
       bool gave_up = false;
-      for (int tile = pair; tile < tiles && !*failed; tile += pairs) {
+      for (int unit = pair; unit < tiles && !*failed; unit += pairs) {
+        const int tile = unit / ksplits, kb0 = (unit % ksplits) * kb_per_split, kb1 = min(k_blocks_all, kb0 + kb_per_split);
         const int m0 = (tile % m_tiles) * 2 * TP_BM + (int)rank * TP_BM;
         const int n0 = (tile / m_tiles) * TP_BN + (int)rank * (TP_BN / 2);
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % TP_STAGES, round = it / TP_STAGES;
           if (!mbar_wait(&empty[s], (round & 1) ^ 1) || *failed) {
             if (!*failed) { *failed = 1; atomicExch(status, 41); }
@@ -161,7 +172,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint64_t desc0 = umma_desc(smem_u32(smem));
       int local = 0;
       uint32_t st = 0, ph = 0;                      // the stage to consume next and its barrier's parity
-      for (int tile = pair; tile < tiles && !*failed; tile += pairs, ++local) {
+      for (int unit = pair; unit < tiles && !*failed; unit += pairs, ++local) {
+        const int kb0 = (unit % ksplits) * kb_per_split, k_blocks = min(k_blocks_all, kb0 + kb_per_split) - kb0;
         const int b = local & 1;
         if (!mbar_wait(&acc_empty[b], ((local >> 1) & 1) ^ 1) || *failed) {     // both epilogues have drained this buffer
           if (!*failed) { *failed = 2; atomicExch(status, 42); }
@@ -193,8 +205,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int quarter = warp & 3;
     const uint32_t acc_empty_addr[2] = {map_to_cta(smem_u32(&acc_empty[0]), 0), map_to_cta(smem_u32(&acc_empty[1]), 0)};
     int local = 0;
-    for (int tile = pair; tile < tiles; tile += pairs, ++local) {
+    for (int unit = pair; unit < tiles; unit += pairs, ++local) {
       const int b = local & 1;
+      const int tile = unit / ksplits, split = unit % ksplits;
       const int m0 = (tile % m_tiles) * 2 * TP_BM + (int)rank * TP_BM, n0 = (tile / m_tiles) * TP_BN;
       const bool ok = mbar_wait(&acc_full[b], (local >> 1) & 1);
       if (!ok && !*failed) { *failed = 3; atomicExch(status, 43); }
@@ -218,7 +231,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             sq = 0.f;
           }
         } else {
-          tg_store_chunk<EPI>(r, m, n0 + c0, N, bias, out);
+          if constexpr (EPI == TG_EPI_F32)
+            tg_store_chunk<EPI>(r, m, n0 + c0, N, split == 0 ? bias : nullptr, reinterpret_cast<float*>(out) + (size_t)split * M * N);
+          else
+            tg_store_chunk<EPI>(r, m, n0 + c0, N, bias, out);
         }
       }
       // this warp has read its quarter of the buffer: tell the MMA thread (in the pair's first CTA)
@@ -251,6 +267,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // next tile with the products of half 0 alone for the stages that are loaded (TP_STAGES_WIDE k blocks), then
 // waits for half 1, catches up on those stages and goes on with both.
 
+constexpr int TP_TMEM_COLS_WIDE = 512;                            // one accumulator of 512 columns
 constexpr int TP_BN_WIDE = 512, TP_STAGES_WIDE = 4;
 constexpr int TP_B_BYTES_WIDE = (TP_BN_WIDE / 2) * TP_BK * 2;      // 32 KB: this CTA's 256 rows of W
 constexpr int TP_STAGE_BYTES_WIDE = TP_A_BYTES + TP_B_BYTES_WIDE;  // 48 KB
@@ -294,7 +311,7 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TP_TMEM_COLS));
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TP_TMEM_COLS_WIDE));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -460,7 +477,7 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   pdl_launch_dependents();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TP_TMEM_COLS));
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TP_TMEM_COLS_WIDE));
   }
 }
 
@@ -510,10 +527,11 @@ static int launch_tp_wide(const CUtensorMap& ma, const CUtensorMap& mw, const fl
   return launch_status("gemm_pair");
 }
 
-template <int EPI>
+template <int EPI, int BN>
 static int launch_tp(const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, void* out, int M, int N, int K,
-                     int* status, cudaStream_t stream, const TgExtra& extra) {
-  auto kernel = gemm_pair_kernel<EPI>;
+                     int* status, cudaStream_t stream, const TgExtra& extra, int ksplits, int kb_per_split) {
+  auto kernel = gemm_pair_kernel<EPI, BN>;
+  constexpr int TP_SMEM = TpCfg<BN>::SMEM, TP_BN = BN;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM) != cudaSuccess) {
@@ -523,12 +541,12 @@ static int launch_tp(const CUtensorMap& ma, const CUtensorMap& mw, const float* 
     configured = true;
   }
   const int pairs_max = sllm::num_sms() / 2;
-  const long long tiles = (long long)((M + 2 * TP_BM - 1) / (2 * TP_BM)) * ((N + TP_BN - 1) / TP_BN);
-  const int pairs = (int)(tiles < pairs_max ? tiles : pairs_max);       // persistent: a pair per two SMs walks the tiles
+  const long long tiles = (long long)((M + 2 * TP_BM - 1) / (2 * TP_BM)) * ((N + TP_BN - 1) / TP_BN) * ksplits;
+  const int pairs = (int)(tiles < pairs_max ? tiles : pairs_max);       // persistent: a pair per two SMs walks the units
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[2];
   pair_launch_config(cfg, attr, pairs, 192, TP_SMEM, stream);
-  cudaLaunchKernelEx(&cfg, kernel, ma, mw, bias, out, M, N, K, status, extra);
+  cudaLaunchKernelEx(&cfg, kernel, ma, mw, bias, out, M, N, K, status, extra, ksplits, kb_per_split);
   return launch_status("gemm_pair");
 }
 
@@ -543,7 +561,8 @@ SLLM_EXPORT int sllm_gemm_pair_supports(int M, int N, int K) {
 // The same product and epilogues as sllm_gemm_tcgen05 (0: float32 out[M, N] (+bias); 1: bfloat16; 2: bfloat16
 // out[M, N/2] = silu(gate) * up for W rows interleaved in blocks of 8), by pairs of CTAs on 256 x 256 tiles, and
 // 3: residual[M, N] (float32) += the product (+bias) in place (`out` is ignored).
-// `wide` != 0: tiles of 256 x 512 (for matrices with few rows of W).
+// `wide`: 0 tiles of 256 x 256; 1 tiles of 256 x 512 (for matrices with few rows of W); 2 tiles of 256 x 128 (for results
+// with few tiles).
 // ssq_in != null: A is bfloat16(stream * gain) of an RMSNorm still owed; ssq_in [M][stride_in] holds parts_in partial
 //   sums of squares of the stream's rows (width_in wide) and every row of the product is multiplied by
 //   rsqrt(sum / width_in + eps_in) before bias and activation.
@@ -553,8 +572,17 @@ SLLM_EXPORT int sllm_gemm_pair_supports(int M, int N, int K) {
 // kernel ran out (41 producer, 42 MMA issuer, 43 epilogue) and the result is not valid.
 SLLM_EXPORT int sllm_gemm_pair_parts(int N) { return (N + 127) / 128; }
 
+// slices of K a request for `want` comes to (empty slices are not made): the rows of the stack of partial sums
+SLLM_EXPORT int sllm_gemm_pair_splits(int K, int want) {
+  const int k_blocks = (K + TP_BK - 1) / TP_BK;
+  if (want < 1) want = 1;
+  if (want > k_blocks) want = k_blocks;
+  const int per = (k_blocks + want - 1) / want;
+  return (k_blocks + per - 1) / per;
+}
+
 SLLM_EXPORT int sllm_gemm_pair(const void* A, const void* W, const float* bias, void* out, int M, int N, int K,
-                               int epilogue, int wide, const float* ssq_in, int parts_in, int stride_in, float eps_in,
+                               int epilogue, int wide, int want_splits, const float* ssq_in, int parts_in, int stride_in, float eps_in,
                                int width_in, float* residual, const float* gain, void* xg_out, float* ssq_out, int stride_out,
                                int* status, cudaStream_t stream) {
   SLLM_REQUIRE(sllm_gemm_pair_supports(M, N, K), "gemm_pair: sizes M=%d N=%d K=%d (K must be a multiple of 8)", M, N, K);
@@ -581,13 +609,19 @@ SLLM_EXPORT int sllm_gemm_pair(const void* A, const void* W, const float* bias, 
   }
   CUtensorMap ma, mw;
   const CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
-  if (!make_map(&ma, A, M, K, TP_BM, promo) || !make_map(&mw, W, N, K, wide ? TP_BN_WIDE / 2 : TP_BN / 2, promo)) {
+  SLLM_REQUIRE(wide >= 0 && wide <= 2, "gemm_pair: tile form %d (0: 256 x 256, 1: 256 x 512, 2: 256 x 128)", wide);
+  const int ksplits = sllm_gemm_pair_splits(K, want_splits);
+  const int kb_per_split = (((K + TP_BK - 1) / TP_BK) + ksplits - 1) / ksplits;
+  SLLM_REQUIRE(ksplits == 1 || (epilogue == TG_EPI_F32 && wide != 1 && ssq_in == nullptr),
+               "gemm_pair: slices of K leave a stack of float32 partial sums (plain epilogue, not the 512-wide tiles, no owed norm)");
+  if (!make_map(&ma, A, M, K, TP_BM, promo) || !make_map(&mw, W, N, K, wide == 1 ? TP_BN_WIDE / 2 : wide == 2 ? 64 : 128, promo)) {
     set_error("gemm_pair: cuTensorMapEncodeTiled failed");
     return SLLM_ERR_LAUNCH;
   }
 #define GO(EPI_)                                                                                   \
-  return wide ? launch_tp_wide<EPI_>(ma, mw, bias, out, M, N, K, status, stream, extra)            \
-              : launch_tp<EPI_>(ma, mw, bias, out, M, N, K, status, stream, extra);
+  return wide == 1 ? launch_tp_wide<EPI_>(ma, mw, bias, out, M, N, K, status, stream, extra)       \
+       : wide == 2 ? launch_tp<EPI_, 128>(ma, mw, bias, out, M, N, K, status, stream, extra, ksplits, kb_per_split) \
+                   : launch_tp<EPI_, 256>(ma, mw, bias, out, M, N, K, status, stream, extra, ksplits, kb_per_split);
   switch (epilogue) {
     case TG_EPI_F32: GO(TG_EPI_F32)
     case TG_EPI_BF16: GO(TG_EPI_BF16)

@@ -229,14 +229,60 @@ def pair_tiles_wide(M: int, N: int) -> bool:
     return 2 * waves_wide <= waves_narrow and waves_narrow < 4
 
 
-def gemm_pair(x, w, bias, out_dtype, *, silu: bool = False, wide: bool | None = None, scale: "RowScale | None" = None,
-              residual=None, next_gain=None):
-    """The same product and epilogues as `gemm_tcgen05`, by pairs of CTAs on 256 x 256 tiles, or on
-    256 x 512 tiles (``wide``; by default where those fill the GPU at least as well)
+@functools.lru_cache(maxsize=4096)
+def pair_tiles_slim(M: int, N: int) -> bool:
+    """Whether tiles of 256 x 128 serve an [M, N] result better than tiles of 256 x 256: where the wider ones
+    would leave at least half of the pairs of SMs without a tile (a prompt portion of 512 tokens times a matrix
+    of 3,584 rows: 28 tiles for 74 pairs; down there 98 -> 54 us, the library's product 56)."""
+    pairs = max(num_sms() // 2, 1)
+    return 2 * (-(-M // 256) * -(-N // 256)) <= pairs
+
+
+PAIR_SPLIT_MAX = 8            # slices of K at most (each leaves a float32 copy of the result for the consumer to add)
+PAIR_SPLIT_MIN_BLOCKS = 8     # 64-wide k blocks a slice has at least
+PAIR_US_PER_K_BLOCK = 0.4     # a pair of SMs on one 256 x 256 tile, per 64-wide k block (measured: 116 us for K = 18,944)
+PAIR_US_PER_ELEMENT = 2.4e-6  # writing or reading one float32 copy of the result, per element (4.4 us for 512 x 3,584)
+PAIR_SPLIT_GAIN = 0.85        # slices only where the whole path (slices, then a kernel that adds them) takes this share
+
+
+@functools.lru_cache(maxsize=4096)
+def pair_splits(M: int, N: int, K: int) -> int:
+    """Slices of K for the CTA-pair product of an [M, N] result with few 256 x 256 tiles: a pair of SMs pulls its
+    operands through shared memory at a rate of its own, so a product whose tiles leave most pairs idle takes as
+    long as its tiles' K, whatever the GPU could do (512 tokens times the down projection: 28 tiles for 74 pairs,
+    116 us; the library's product 56).  With S slices a unit is (tile, slice), the units run in waves over the pairs
+    and the time goes as waves / S; the slices' partial sums are a stack for the consumer to add (512 tokens, down:
+    66 us in two slices).  The choice weighs that against the fused epilogues the unsliced product keeps: waves x K
+    blocks for the products, a copy of the result per slice written and read, three copies for the residual
+    epilogue's traffic (in a graph, measured: within 10 % of this at 192 to 1,024 tokens)."""
+    pairs = max(num_sms() // 2, 1)
+    tiles = -(-M // 256) * -(-N // 256)
+    k_blocks = -(-K // 64)
+    t_tile, t_copy = k_blocks * PAIR_US_PER_K_BLOCK, M * N * PAIR_US_PER_ELEMENT
+    whole = -(-tiles // pairs) * t_tile + 3 * t_copy
+    if tiles > pairs:               # (measured only where the tiles are one wave at most)
+        return 1
+    best, best_cost = 1, whole
+    for s in range(2, PAIR_SPLIT_MAX + 1):
+        if k_blocks // s < PAIR_SPLIT_MIN_BLOCKS:
+            break
+        cost = -(-tiles * s // pairs) / s * t_tile + (s + 2) * t_copy
+        if cost < best_cost:
+            best, best_cost = s, cost
+    return best if best_cost <= PAIR_SPLIT_GAIN * whole else 1
+
+
+def gemm_pair(x, w, bias, out_dtype, *, silu: bool = False, wide: "bool | str | None" = None, scale: "RowScale | None" = None,
+              residual=None, next_gain=None, splits: int = 1):
+    """The same product and epilogues as `gemm_tcgen05`, by pairs of CTAs on 256 x 256 tiles, on
+    256 x 512 tiles (``wide=True``; by default where those fill the GPU at least as well) or on 256 x 128
+    tiles (``wide="slim"``; by default where the result has few tiles)
     (``tcgen05.mma`` with ``cta_group::2``: each CTA loads half of each operand).
     ``scale``: a norm still owed on ``x`` (`RowScale`).  ``residual`` (float32 ``[M, N]``): the product is added
     into it in place and None is returned; with ``next_gain`` the kernel also writes the next norm's input in the
-    owed form and ``(xg, RowScale)`` comes back (the scale's eps left at 0 for the caller to set)."""
+    owed form and ``(xg, RowScale)`` comes back (the scale's eps left at 0 for the caller to set).
+    ``splits`` > 1 (float32 result, no other epilogue): K in that many slices, the result a stack ``[splits', M, N]``
+    of partial sums (bias in the first) for the consumer to add."""
     _chk(x, w, bias, residual, next_gain)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_pair: bfloat16 operands only")
@@ -260,12 +306,15 @@ def gemm_pair(x, w, bias, out_dtype, *, silu: bool = False, wide: bool | None = 
     elif silu:
         epi, out = 2, torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
     elif out_dtype == torch.float32:
-        epi, out = 0, torch.empty((M, N), dtype=torch.float32, device=x.device)
+        real = int(lib().sllm_gemm_pair_splits(K, int(splits))) if splits > 1 else 1
+        epi, out = 0, torch.empty((real, M, N) if real > 1 else (M, N), dtype=torch.float32, device=x.device)
     else:
         epi, out = 1, torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if splits > 1 and (epi != 0 or scale is not None):
+        raise KernelError("gemm_pair: slices of K leave float32 partial sums: no other epilogue, no owed norm")
     if wide is None:
-        wide = pair_tiles_wide(M, N)
-    call("sllm_gemm_pair", _p(x), _p(w), _p(bias), _p(out), M, N, K, epi, 1 if wide else 0,
+        wide = False if splits > 1 else ("slim" if pair_tiles_slim(M, N) else pair_tiles_wide(M, N))
+    call("sllm_gemm_pair", _p(x), _p(w), _p(bias), _p(out), M, N, K, epi, 2 if wide == "slim" else 1 if wide else 0, int(splits),
          *(scale.args_with_stride() if scale is not None else (None, 0, 0, 0.0, 0)),
          _p(residual), _p(next_gain), _p(xg), _p(ssq), stride, _p(_status_word(x.device)), _stream())
     _tc_used["since_check"] += 1
@@ -432,7 +481,10 @@ def can_accumulate(x: torch.Tensor, w: torch.Tensor) -> bool:
         return False
     M, K = x.shape
     N = w.shape[0]
-    return ws_supports(M, N, K) or (_pair_rows(M) and N % 4 == 0 and pair_supports(M, N, K))
+    if ws_supports(M, N, K):
+        return True
+    # (a result of so few tiles that it is better cut along K leaves partial sums, which a norm kernel adds)
+    return _pair_rows(M) and N % 4 == 0 and pair_supports(M, N, K) and pair_splits(M, N, K) == 1
 
 
 def linear_accumulate(x, w, bias, residual) -> None:
@@ -513,7 +565,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype, allow
     if N * K >= LINEAR_TC_LARGE and -(-N // 128) >= num_sms() and linear_tc_supports(M, N, K):
         return linear_tc(x, w, bias, out_dtype)      # a large matrix whose 128-row tiles are enough for every SM
     if _PAIR_GEMM == "all" and M > TCGEN05_MIN_ROWS and pair_supports(M, N, K):
-        # prompt portions: pairs of CTAs on the tensor cores (tcgen05.mma with cta_group::2)
+        # prompt portions: pairs of CTAs on the tensor cores (tcgen05.mma with cta_group::2); a result of few tiles in
+        # slices of K where the consumer adds partial sums
+        if allow_partials and out_dtype == torch.float32 and pair_splits(M, N, K) > 1:
+            return gemm_pair(x, w, bias, out_dtype, splits=pair_splits(M, N, K))
         return gemm_pair(x, w, bias, out_dtype)
     launches["library"] += 1
     if out_dtype == torch.float32:

@@ -773,6 +773,33 @@ def test_gemm_pair_owes_and_pays_an_rmsnorm(M, H, K, wide):
     ops.check_tcgen05_status()
 
 
+@pytest.mark.parametrize("M,N,K", [(130, 264, 1160), (200, 3584, 3584), (512, 1000, 18944), (700, 520, 1024), (257, 8, 520)])
+def test_gemm_pair_in_slices_of_k(M, N, K):
+    """The CTA-pair product cut along K: a stack of float32 partial sums whose sum is the product (bias once), every
+    number of slices up to what K gives, ragged edges, both tile widths; and through the dispatch, which cuts where
+    the result has few tiles."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(23)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g)
+    want = x.float() @ w.float().t() + b
+    for splits in (2, 3, 5, 8, 1000):
+        for wide in (False, "slim"):
+            parts = ops.gemm_pair(x, w, b, torch.float32, splits=splits, wide=wide)
+            assert parts.dim() == 3 and 2 <= parts.shape[0] <= min(splits, -(-K // 64)), parts.shape
+            torch.testing.assert_close(parts.sum(0), want, rtol=2e-3, atol=2e-3, msg=lambda m: f"{splits} slices, {wide}: {m}")
+            torch.testing.assert_close(parts[1:].sum(0) + parts[0], want, rtol=2e-3, atol=2e-3)
+    ops.check_tcgen05_status()
+    with pytest.raises(ops.KernelError):
+        ops.gemm_pair(x, w, b, torch.bfloat16, splits=2)
+    stack = ops.linear(x, w, b, torch.float32, allow_partials=True)
+    assert (stack.dim() == 3) == (ops.pair_splits(M, N, K) > 1)
+    torch.testing.assert_close(stack.sum(0) if stack.dim() == 3 else stack, want, rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(ops.linear(x, w, b, torch.float32), want, rtol=2e-3, atol=2e-3)
+    ops.check_tcgen05_status()
+
+
 @pytest.mark.parametrize("M", [1, 9, 17, 24, 32, 33, 64, 65, 100, 128])
 @pytest.mark.parametrize("N,K", [(128, 64), (136, 72), (1000, 264), (4608, 3584), (3584, 18944), (9480, 3584), (75784, 512)])
 def test_linear_tc(M, N, K):

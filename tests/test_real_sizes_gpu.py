@@ -142,10 +142,11 @@ def test_steps_of_17_to_90_tokens(wide_model, per_request):
 
 
 def test_prompt_portions_leave_their_norms_to_the_products(wide_model, monkeypatch):
-    """A prompt portion of more than 128 tokens: the products that complete the residual stream (on the CTA-pair
-    kernel) prepare the next RMSNorm's input, the consuming products pay the division, and of the 2 L + 1 norms
-    only the first layer's and the final one remain kernels; no library product is launched.  The logits are the
-    plain implementation's within the bounds of the other tests here, with and without the scheme."""
+    """A prompt portion of more than 128 tokens whose products are not cut along K (as they are not from about 1,024
+    tokens on; forced here at 197): the products that complete the residual stream (on the CTA-pair kernel) prepare the
+    next RMSNorm's input, the consuming products pay the division, and of the 2 L + 1 norms only the first layer's and
+    the final one remain kernels; no library product is launched.  The logits are the plain implementation's within
+    the bounds of the other tests here, with and without the scheme."""
     from sllm_b200 import ops
     from sllm_b200.engine import Engine, StepEntry, build_model
     dev = cuda_or_skip()
@@ -154,6 +155,7 @@ def test_prompt_portions_leave_their_norms_to_the_products(wide_model, monkeypat
     spread = float(np.concatenate([v.ravel() for v in want.values()]).std())
     entries = [StepEntry(r, ids, list(range(len(ids)))) for r, ids in reqs.items()]       # 197 tokens in one step
     ref_rows = np.concatenate([want[r] for r in reqs])
+    monkeypatch.setattr(ops, "pair_splits", lambda M, N, K: 1)
     counts = {}
     for fused in (True, False):
         monkeypatch.setattr(ops, "_NORM_FUSED", fused)
@@ -167,3 +169,29 @@ def test_prompt_portions_leave_their_norms_to_the_products(wide_model, monkeypat
         assert float(np.sqrt(((logits - ref_rows) ** 2).mean())) <= 0.02 * spread
     L = cfg["num_hidden_layers"]
     assert counts[False] == 2 * L + 1 and counts[True] == 2, counts
+
+
+def test_small_prompt_portions_cut_their_products_along_k(wide_model):
+    """A prompt portion of 197 tokens has so few tiles per product that most pairs of SMs would have none: the attention
+    and down projections (and q|k|v) run in slices of K whose partial sums the norm and rotary kernels add, every norm
+    is a kernel again, no library product is launched, and the logits are the plain implementation's within the bounds
+    of the other tests here."""
+    from sllm_b200 import ops
+    from sllm_b200.engine import Engine, StepEntry, build_model
+    dev = cuda_or_skip()
+    model_dir, cfg, reqs, want = wide_model
+    model, _ = build_model(model_dir, "bfloat16", dev)
+    spread = float(np.concatenate([v.ravel() for v in want.values()]).std())
+    entries = [StepEntry(r, ids, list(range(len(ids)))) for r, ids in reqs.items()]       # 197 tokens in one step
+    ref_rows = np.concatenate([want[r] for r in reqs])
+    H, I = cfg["hidden_size"], cfg["intermediate_size"]
+    assert ops.pair_splits(197, H, I) > 1 and ops.pair_splits(2048, H, I) == 1
+    eng = Engine(model, page_size=16, num_pages=32, max_requests=4)
+    before = ops.launches["library"]
+    with ops.KernelTimes() as kt:
+        logits = eng.step(entries).float().cpu().numpy()
+    ops.check_tcgen05_status()
+    assert ops.launches["library"] == before
+    assert kt.table().get("sllm_add_rmsnorm", (0, 0.0))[0] == 2 * cfg["num_hidden_layers"] + 1
+    assert np.abs(logits - ref_rows).max() <= 0.08 * spread
+    assert float(np.sqrt(((logits - ref_rows) ** 2).mean())) <= 0.02 * spread
