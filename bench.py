@@ -620,13 +620,15 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer than the configuration has, only where memory or time needs it")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64, the stated runs, the prefill and the logit check")
-    ap.add_argument("--prefill-only", action="store_true", help="run the 2,048-token prefill alone (for profilers)")
+    ap.add_argument("--prefill-only", action="store_true", help="run the prefill alone (for profilers, and for portions of other sizes)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of the timed prompt portion (the record's is 2,048)")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
     ap.add_argument("--kernel-times", action="store_true", help="add device time per kernel entry point (a step launched kernel by kernel)")
     ap.add_argument("--graph-times", action="store_true",
                     help="print microseconds per launch of one decode layer's kernels at --batch and --context, each kind in a graph of its own, and exit")
     args = ap.parse_args(argv)
     globals()["PAGE_SIZE"] = args.page_size
+    globals()["PREFILL_TOKENS"] = max(2, args.prefill_tokens)
     args.repeats = max(1, args.repeats)
 
     if args.gpus != 1:
@@ -666,7 +668,7 @@ def main(argv=None) -> int:
     torch.cuda.synchronize()
 
     if args.prefill_only:
-        ms = prefill_run(model, cfg, PREFILL_TOKENS, reps=2)
+        ms = prefill_run(model, cfg, PREFILL_TOKENS, reps=2 if PREFILL_TOKENS == 2048 else 5)     # (few launches for a profiler)
         fl = flops_of_step(cfg, [PREFILL_TOKENS], [0], 1)
         print(json.dumps({"prefill_only": True, "layers": args.layers, "tokens": PREFILL_TOKENS, "ms": round(ms, 3),
                           "tflops": round(fl / (ms / 1e3) / 1e12, 1)}))
