@@ -120,53 +120,6 @@ __device__ __forceinline__ void tg_store_chunk(const uint32_t (&r)[32], int m, i
   }
 }
 
-// TG_EPI_RESID on columns n .. n + 31 of row m (N a multiple of 4): returns the sum of squares of the new
-// residual values of the chunk (0 where the next norm's input is not asked for)
-__device__ __forceinline__ float tg_resid_chunk(const uint32_t (&r)[32], int m, int n, int N, const float* __restrict__ bias,
-                                                const TgExtra& e) {
-  float v[32];
-  tg_values(r, v, n, N, bias);
-  float* res = e.residual + (size_t)m * N + n;
-  float sq = 0.f;
-  if (n + 32 <= N) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float4 x = *reinterpret_cast<const float4*>(res + 4 * j);
-      x.x += v[4 * j]; x.y += v[4 * j + 1]; x.z += v[4 * j + 2]; x.w += v[4 * j + 3];
-      *reinterpret_cast<float4*>(res + 4 * j) = x;
-      v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
-    }
-    if (e.xg != nullptr) {
-      __nv_bfloat16* o = e.xg + (size_t)m * N + n;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float w[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          sq += v[8 * j + i] * v[8 * j + i];
-          w[i] = v[8 * j + i] * e.gain[n + 8 * j + i];
-        }
-        if ((N & 7) == 0) {
-          *reinterpret_cast<uint4*>(o + 8 * j) = make_uint4(pack2(w[0], w[1]), pack2(w[2], w[3]), pack2(w[4], w[5]), pack2(w[6], w[7]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) o[8 * j + i] = __float2bfloat16_rn(w[i]);
-        }
-      }
-    }
-  } else {
-    for (int i = 0; i < 32 && n + i < N; ++i) {
-      const float x = res[i] + v[i];
-      res[i] = x;
-      if (e.xg != nullptr) {
-        sq += x * x;
-        e.xg[(size_t)m * N + n + i] = __float2bfloat16_rn(x * e.gain[n + i]);
-      }
-    }
-  }
-  return sq;
-}
-
 // ---- the same through shared memory and TMA stores ------------------------------------------------
 // A lane of an epilogue warp holds one row of the accumulator, so direct stores put every lane on a line of
 // its own: 32 requests of 16 bytes an instruction, and the step from tensor memory to global memory takes
@@ -213,6 +166,73 @@ __device__ __forceinline__ void tg_stage_chunk(const uint32_t (&r)[32], unsigned
                                                             pack2(v[8 * j + 4], v[8 * j + 5]), pack2(v[8 * j + 6], v[8 * j + 7])));
     }
   }
+}
+
+// ---- the residual epilogue through shared memory -----------------------------------------------------
+// TG_EPI_RESID with a lane a row puts every lane's 16-byte pieces on a line of their own: per 128 x 512 tile of a
+// CTA, 640 KB of the residual stream and of the next norm's input move as 40,000 single-line requests, about 20 us
+// of the load/store unit where the products of the tile take 45.  Here a warp stages its 32 rows x 32 columns of the
+// product in a box of shared memory (the layout of the boxes above) and walks it four rows at a time, eight lanes a
+// row: the residual stream is read and written, and the next norm's input written, as whole lines.
+// m0: the box's first row of C; n: its first column (N a multiple of 4: a 16-byte piece lies inside the matrix or
+// outside).  sq[k] gathers, in the lanes 8 j of a warp, the sums of squares of the new residual values of the
+// rows m0 + 4 k + j.
+__device__ __forceinline__ void tg_resid_box(const uint32_t (&r)[32], unsigned char* box, int lane, int m0, int n, int M, int N,
+                                             const float* __restrict__ bias, const TgExtra& e, float (&sq)[8]) {
+  {
+    float v[32];
+    tg_values(r, v, n, N, bias);
+    unsigned char* row_base = box + lane * 128;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      tg_put_piece(row_base, lane, j, make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
+                                                 __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3])));
+  }
+  __syncwarp();
+  const int piece = lane & 7, col = n + 4 * piece;
+  const bool col_ok = col < N;
+  float4 gain = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (e.xg != nullptr && col_ok) gain = *reinterpret_cast<const float4*>(e.gain + col);
+  // all the loads first: eight lines of the residual stream in flight per lane group
+  float4 old[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int m = m0 + 4 * k + (lane >> 3);
+    old[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (m < M && col_ok) old[k] = *reinterpret_cast<const float4*>(e.residual + (size_t)m * N + col);
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int row = 4 * k + (lane >> 3), m = m0 + row;
+    const float4 v = *reinterpret_cast<const float4*>(box + row * 128 + ((piece ^ (row & 7)) << 4));
+    float s = 0.f;
+    if (m < M && col_ok) {
+      const float4 x = make_float4(old[k].x + v.x, old[k].y + v.y, old[k].z + v.z, old[k].w + v.w);
+      *reinterpret_cast<float4*>(e.residual + (size_t)m * N + col) = x;
+      if (e.xg != nullptr) {
+        s = x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+        *reinterpret_cast<uint2*>(e.xg + (size_t)m * N + col) = make_uint2(pack2(x.x * gain.x, x.y * gain.y), pack2(x.z * gain.z, x.w * gain.w));
+      }
+    }
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    sq[k] += s;
+  }
+  __syncwarp();                                   // the box is free for the next chunk
+}
+
+// the sums of squares gathered by tg_resid_box over a block of 128 columns, into ssq_out[row][block]
+__device__ __forceinline__ void tg_resid_box_sums(float (&sq)[8], int lane, int m0, int M, int block, const TgExtra& e) {
+  if (e.ssq_out != nullptr && (lane & 7) == 0) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int m = m0 + 4 * k + (lane >> 3);
+      if (m < M) e.ssq_out[(size_t)m * e.stride_out + block] = sq[k];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) sq[k] = 0.f;
 }
 
 }  // namespace sllm

@@ -44,7 +44,8 @@ template <int BN> struct TpCfg {
   static constexpr int B_BYTES = (BN / 2) * TP_BK * 2;    // 16 or 8 KB
   static constexpr int STAGE_BYTES = TP_A_BYTES + B_BYTES;
   static constexpr int STAGES = BN == 256 ? 6 : 8;        // 192 KB either way
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+  static constexpr int BOX_BYTES = 4 * 4096;              // a box of 32 rows x 128 bytes per epilogue warp (residual epilogue)
+  static constexpr int SMEM = STAGES * STAGE_BYTES + BOX_BYTES + 1024 /* alignment */ + 256 /* barriers */;
   static constexpr int TMEM_COLS = 2 * BN;                // two accumulators
 };
 
@@ -94,7 +95,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tp_smem_raw) + 1023) & ~(uintptr_t)1023);
   using C = TpCfg<BN>;
   constexpr int TP_BN = BN, TP_STAGES = C::STAGES, TP_STAGE_BYTES = C::STAGE_BYTES, TP_TMEM_COLS = C::TMEM_COLS;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + TP_STAGES * TP_STAGE_BYTES);
+  unsigned char* boxes = smem + TP_STAGES * TP_STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(boxes + C::BOX_BYTES);
   uint64_t* empty = full + TP_STAGES;
   uint64_t* acc_full = empty + TP_STAGES;           // [2]
   uint64_t* acc_empty = acc_full + 2;               // [2]
@@ -215,21 +217,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m = m0 + quarter * 32 + lane;
       const float row_scale = tg_row_scale(extra, m, M);        // a norm still owed on the input (1 if none)
-      float sq = 0.f;
+      float sq[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (m0 + quarter * 32 >= M) {                 // (warp-uniform) none of this warp's rows is in the matrix
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_addr[b]);
+        continue;
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < TP_BN; c0 += 32) {
         if (n0 + c0 >= N) break;                    // warp-uniform
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + b * TP_BN + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if constexpr (EPI == TG_EPI_RESID) {
+          if (extra.ssq_in != nullptr) tg_scale(r, row_scale);
+          tg_resid_box(r, boxes + (warp - 2) * 4096, lane, m0 + quarter * 32, n0 + c0, M, N, bias, extra, sq);
+          if ((c0 & 127) == 96 || n0 + c0 + 32 >= N)      // a block of 128 columns is complete
+            tg_resid_box_sums(sq, lane, m0 + quarter * 32, M, (n0 + c0) / 128, extra);
+          continue;
+        }
         if (m >= M) continue;
         if (extra.ssq_in != nullptr) tg_scale(r, row_scale);
         if constexpr (EPI == TG_EPI_RESID) {
-          sq += tg_resid_chunk(r, m, n0 + c0, N, bias, extra);
-          if (extra.ssq_out != nullptr && ((c0 & 127) == 96 || n0 + c0 + 32 >= N)) {     // a block of 128 columns is complete
-            extra.ssq_out[(size_t)m * extra.stride_out + (n0 + c0) / 128] = sq;
-            sq = 0.f;
-          }
         } else {
           if constexpr (EPI == TG_EPI_F32)
             tg_store_chunk<EPI>(r, m, n0 + c0, N, split == 0 ? bias : nullptr, reinterpret_cast<float*>(out) + (size_t)split * M * N);
@@ -424,7 +434,7 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const float row_scale = tg_row_scale(extra, m, M);        // a norm still owed on the input (1 if none)
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {
-        float sq = 0.f;
+        float sq[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
         for (int c0 = 128 * col_half; c0 < 128 * col_half + 128; c0 += AC) {
           // accumulator half h: its columns [0, 128) are C's columns n0 + 128 h .. (the first CTA's rows of W), its
@@ -442,7 +452,7 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             if (extra.ssq_in != nullptr) tg_scale(r, row_scale);
             if constexpr (EPI == TG_EPI_RESID) {
-              if (m < M && n + 32 * sub < N) sq += tg_resid_chunk(r, m, n + 32 * sub, N, bias, extra);
+              if (n + 32 * sub < N) tg_resid_box(r, box, lane, row0, n + 32 * sub, M, N, bias, extra, sq);      // (warp-uniform)
             } else {
               if (tma_out) tg_stage_chunk<EPI>(r, box, lane, sub, n + 32 * sub, N, bias);
               else if (m < M && n + 32 * sub < N) tg_store_chunk<EPI>(r, m, n + 32 * sub, N, bias, out);
@@ -461,7 +471,7 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         if constexpr (EPI == TG_EPI_RESID) {
           // the warp's 128 columns of this half are one block of C's columns: its sum of squares per row
           const int nb = n0 + 256 * col_half + 128 * h;
-          if (extra.ssq_out != nullptr && m < M && nb < N) extra.ssq_out[(size_t)m * extra.stride_out + nb / 128] = sq;
+          if (nb < N) tg_resid_box_sums(sq, lane, row0, M, nb / 128, extra);
         }
         // this warp has read its share of the half: the MMA thread may write it again
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
