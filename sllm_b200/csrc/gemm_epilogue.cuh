@@ -222,6 +222,30 @@ __device__ __forceinline__ void tg_resid_box(const uint32_t (&r)[32], unsigned c
   __syncwarp();                                   // the box is free for the next chunk
 }
 
+// The float32 result the same way: rows m0 .. m0 + 31, columns n .. n + 31 of `out` [M, N] (N a multiple of 4),
+// staged in the warp's box and written four rows an instruction.
+__device__ __forceinline__ void tg_store_box_f32(const uint32_t (&r)[32], unsigned char* box, int lane, int m0, int n, int M, int N,
+                                                 const float* __restrict__ bias, float* __restrict__ out) {
+  {
+    float v[32];
+    tg_values(r, v, n, N, bias);
+    unsigned char* row_base = box + lane * 128;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      tg_put_piece(row_base, lane, j, make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
+                                                 __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3])));
+  }
+  __syncwarp();
+  const int piece = lane & 7, col = n + 4 * piece;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int row = 4 * k + (lane >> 3), m = m0 + row;
+    if (m < M && col < N)
+      *reinterpret_cast<float4*>(out + (size_t)m * N + col) = *reinterpret_cast<const float4*>(box + row * 128 + ((piece ^ (row & 7)) << 4));
+  }
+  __syncwarp();                                   // the box is free for the next chunk
+}
+
 // the sums of squares gathered by tg_resid_box over a block of 128 columns, into ssq_out[row][block]
 __device__ __forceinline__ void tg_resid_box_sums(float (&sq)[8], int lane, int m0, int M, int block, const TgExtra& e) {
   if (e.ssq_out != nullptr && (lane & 7) == 0) {

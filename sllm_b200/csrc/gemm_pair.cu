@@ -237,15 +237,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tg_resid_box_sums(sq, lane, m0 + quarter * 32, M, (n0 + c0) / 128, extra);
           continue;
         }
+        if constexpr (EPI == TG_EPI_F32) {
+          if ((N & 3) == 0) {                       // (uniform) whole 16-byte pieces: through the box, four rows an instruction
+            if (extra.ssq_in != nullptr) tg_scale(r, row_scale);
+            tg_store_box_f32(r, boxes + (warp - 2) * 4096, lane, m0 + quarter * 32, n0 + c0, M, N, split == 0 ? bias : nullptr,
+                             reinterpret_cast<float*>(out) + (size_t)split * M * N);
+            continue;
+          }
+        }
         if (m >= M) continue;
         if (extra.ssq_in != nullptr) tg_scale(r, row_scale);
-        if constexpr (EPI == TG_EPI_RESID) {
-        } else {
-          if constexpr (EPI == TG_EPI_F32)
-            tg_store_chunk<EPI>(r, m, n0 + c0, N, split == 0 ? bias : nullptr, reinterpret_cast<float*>(out) + (size_t)split * M * N);
-          else
-            tg_store_chunk<EPI>(r, m, n0 + c0, N, bias, out);
-        }
+        if constexpr (EPI == TG_EPI_F32)
+          tg_store_chunk<EPI>(r, m, n0 + c0, N, split == 0 ? bias : nullptr, reinterpret_cast<float*>(out) + (size_t)split * M * N);
+        else if constexpr (EPI != TG_EPI_RESID)
+          tg_store_chunk<EPI>(r, m, n0 + c0, N, bias, out);
       }
       // this warp has read its quarter of the buffer: tell the MMA thread (in the pair's first CTA)
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

@@ -241,7 +241,8 @@ def pair_tiles_slim(M: int, N: int) -> bool:
 PAIR_SPLIT_MAX = 8            # slices of K at most (each leaves a float32 copy of the result for the consumer to add)
 PAIR_SPLIT_MIN_BLOCKS = 8     # 64-wide k blocks a slice has at least
 PAIR_US_PER_K_BLOCK = 0.4     # a pair of SMs on one 256 x 256 tile, per 64-wide k block (measured: 116 us for K = 18,944)
-PAIR_US_PER_ELEMENT = 2.4e-6  # writing or reading one float32 copy of the result, per element (4.4 us for 512 x 3,584)
+PAIR_US_PER_ELEMENT = 2.4e-6  # one more float32 copy of the result for the next kernel to add, per element (whole portions
+                              # of 192 to 1,024 tokens were timed with 0.5, 1.0 and 2.4: the last gave the best choices)
 PAIR_SPLIT_GAIN = 0.85        # slices only where the whole path (slices, then a kernel that adds them) takes this share
 
 
