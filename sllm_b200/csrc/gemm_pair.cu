@@ -211,12 +211,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int b = local & 1;
       const int tile = unit / ksplits, split = unit % ksplits;
       const int m0 = (tile % m_tiles) * 2 * TP_BM + (int)rank * TP_BM, n0 = (tile / m_tiles) * TP_BN;
+      const int m = m0 + quarter * 32 + lane;
+      const float row_scale = tg_row_scale(extra, m, M);        // a norm still owed on the input (1 if none): fetched while the products run
       const bool ok = mbar_wait(&acc_full[b], (local >> 1) & 1);
       if (!ok && !*failed) { *failed = 3; atomicExch(status, 43); }
       if (!ok || *failed) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int m = m0 + quarter * 32 + lane;
-      const float row_scale = tg_row_scale(extra, m, M);        // a norm still owed on the input (1 if none)
       float sq[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       if (m0 + quarter * 32 >= M) {                 // (warp-uniform) none of this warp's rows is in the matrix
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -429,14 +429,14 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     bool staged = false;                            // a box of this warp is on its way out of shared memory
     for (int tile = pair; tile < tiles; tile += pairs, ++local) {
       const int m0 = (tile % m_tiles) * 2 * TP_BM + (int)rank * TP_BM, n0 = (tile / m_tiles) * TP_BN_WIDE;
+      const int m = m0 + quarter * 32 + lane;
+      const float row_scale = tg_row_scale(extra, m, M);        // a norm still owed on the input (1 if none): fetched while the products run
       const bool ok = mbar_wait(&acc_full[0], local & 1);
       if (!ok && !*failed) { *failed = 3; atomicExch(status, 43); }
       if (!ok || *failed) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int m = m0 + quarter * 32 + lane;
       constexpr int AC = TgBox<EPI>::ACC_COLS;
       const int row0 = m0 + quarter * 32;
-      const float row_scale = tg_row_scale(extra, m, M);        // a norm still owed on the input (1 if none)
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {
         float sq[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
