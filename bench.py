@@ -520,15 +520,26 @@ def graph_times(cfg, batch, context) -> dict:
             if M <= 128:
                 forms["tc"] = lambda: ops.linear_tc(x, w(), None, torch.float32, splits=ops._tc_splits(N, K))
             forms["library"] = lambda: torch.mm(x, w().t(), out_dtype=torch.float32)
+            if M > 128:                           # a prompt portion: the CTA-pair product plain, with the residual epilogue, cut along K
+                gain = torch.ones(N, device=dev)
+                forms["pair"] = lambda: ops.gemm_pair(x, w(), None, torch.float32, wide=False)
+                forms["pair_residual_and_next_norm"] = lambda: ops.gemm_pair(x, w(), None, torch.float32, residual=res, next_gain=gain)
+                for cut in (2, 3, 5):
+                    forms[f"pair_{cut}_slices"] = lambda cut=cut: ops.gemm_pair(x, w(), None, torch.float32, splits=cut)
         rec = {"bytes_alone_us": round(N * K * 2 / 1e6 / (load_peaks()[0]["hbm_gbs"] / 1e3), 2)}
         for form, fn in forms.items():
             try:
                 rec[form] = timed(fn, reps=3 * copies)
             except Exception as e:      # noqa: BLE001  (a form that refuses these sizes says so in the record)
                 rec[form] = f"{type(e).__name__}"
+        if not silu:
+            rec["slices_picked"] = ops.pair_splits(M, N, K) if M > 128 else 1
         out[name] = rec
         del ws
         torch.cuda.empty_cache()
+    if batch > 128:                               # (rows of a prompt portion: no decode attention of that many requests)
+        ops.check_tcgen05_status()
+        return out
     # decode attention over `context` keys a request, pages with consecutive ids
     ps = PAGE_SIZE
     per = -(-context // ps)
