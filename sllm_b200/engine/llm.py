@@ -51,12 +51,17 @@ def plan_num_pages(model, page_size: int, *, kv_utilization: float = 0.9, kv_byt
     return max(int(pages), 1)
 
 
+ROW_TILE = 256       # rows of a tile of the prompt-portion products (a pair of CTAs of `gemm_pair.cu`)
+
+
 class LLM:
     def __init__(self, model_dir: str | None = None, *, model=None, dtype="bfloat16", device="cuda:0",
                  block_size: int = 16, num_pages: int | None = None, kv_utilization: float = 0.9,
                  kv_bytes: int | None = None, max_num_seqs: int = 8, max_batch_tokens: int = 2048,
                  chunk_size: int = 512, max_model_len: int | None = None, policy: str = "reserve",
-                 cuda_graphs: bool = True, pipeline_decode: bool = True, progress=None):
+                 cuda_graphs: bool = True, pipeline_decode: bool = True, progress=None, row_tile: int | None = None):
+        """``row_tile``: see `Scheduler` (None: the prompt-portion kernels' 256 rows for a bfloat16 model, off in
+        float32; 0: off)."""
         if (model_dir is None) == (model is None):
             raise ValueError("give a model folder or a built model")
         if model is None:
@@ -69,7 +74,8 @@ class LLM:
         self.engine = Engine(model, page_size=block_size, num_pages=num_pages, max_requests=max_num_seqs,
                              max_model_len=self.max_model_len)
         self.scheduler = Scheduler(self.engine.cache, max_positions=self.max_model_len, max_num_seqs=max_num_seqs,
-                                   max_batch_tokens=max_batch_tokens, chunk_size=chunk_size, policy=policy)
+                                   max_batch_tokens=max_batch_tokens, chunk_size=chunk_size, policy=policy,
+                                   row_tile=ROW_TILE if (row_tile is None and model.dtype == torch.bfloat16) else int(row_tile or 0))
         self.sampler = Sampler(model.device)
         self.cuda_graphs = bool(cuda_graphs) and model.device.type == "cuda"
         self.pipeline_decode = self.cuda_graphs and bool(pipeline_decode)

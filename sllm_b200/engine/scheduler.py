@@ -83,7 +83,12 @@ class Planned:
 
 class Scheduler:
     def __init__(self, cache: CacheManager, *, max_positions: int, max_num_seqs: int = 8,
-                 max_batch_tokens: int = 2048, chunk_size: int = 512, policy: str = "reserve"):
+                 max_batch_tokens: int = 2048, chunk_size: int = 512, policy: str = "reserve",
+                 row_tile: int = 0, row_tile_slack: int = 64):
+        """``row_tile`` (0: off): the rows the kernels of a prompt portion work in.  A step of a few tokens more than
+        a multiple of it pays for a whole tile more (512 prompt tokens beside 31 decoded ones: three tiles of 256 rows
+        for 543 tokens), so a step that is at most ``row_tile_slack`` tokens over a multiple gives those tokens of a
+        prompt portion back to the next step."""
         if min(max_num_seqs, max_batch_tokens, chunk_size) < 1:
             raise ValueError("sizes must be >= 1")                 # runtime/scheduler.py:70-71
         if policy not in ("reserve", "on_demand"):
@@ -94,6 +99,8 @@ class Scheduler:
         self.max_batch_tokens = max_batch_tokens
         self.chunk_size = chunk_size
         self.policy = policy
+        self.row_tile = max(0, int(row_tile))
+        self.row_tile_slack = max(0, int(row_tile_slack))
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []       # in order of admission
         self.done: list[Request] = []
@@ -172,7 +179,23 @@ class Scheduler:
             planned_ids.add(r.req_id)
             budget -= n
         self.waiting.extendleft(reversed(skipped))
+        self._trim_to_row_tiles(plan)
         return plan
+
+    def _trim_to_row_tiles(self, plan: list[Planned]) -> None:
+        """See ``row_tile``: the last prompt portion of the plan that can spare them loses the tokens that would open
+        another tile of rows (its pages stay reserved; the tokens come with the next step)."""
+        if not self.row_tile:
+            return
+        total = sum(p.count for p in plan)
+        over = total % self.row_tile
+        if total < self.row_tile or over == 0 or over > self.row_tile_slack:
+            return
+        for p in reversed(plan):
+            if p.count > over and p.req.pending > 1:       # a prompt portion (a decoding request has one pending token)
+                p.count -= over
+                p.sample = False                            # it no longer reaches the prompt's last token
+                return
 
     def update(self, plan, sampled: dict) -> list[Request]:
         """After the step ran: ``sampled`` maps each request whose portion reached its

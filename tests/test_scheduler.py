@@ -145,3 +145,41 @@ def test_abort_and_duplicates():
     assert s.abort("b") and s.abort("a") and not s.abort("zzz")
     assert not s.has_work and cache.groups[0].pool.used_count == 0
     assert {r.req_id: r.finish_reason for r in s.done} == {"a": "abort", "b": "abort"}
+
+
+def test_a_step_a_few_tokens_over_a_tile_of_rows_gives_them_back():
+    """With ``row_tile`` set (the prompt-portion kernels work in tiles of that many rows), a step that is a few
+    tokens over a multiple of the tile shortens a prompt portion by them: the portion no longer samples, the
+    tokens come with the next step, nothing is lost; steps under a tile, on a multiple, or further over than the
+    slack stay as they are."""
+    s, cache = make(num_pages=400, chunk_size=32, max_batch_tokens=100, max_num_seqs=8, row_tile=16, row_tile_slack=4)
+    for i in range(3):                                   # three requests that will be decoding
+        s.add(f"d{i}", [0] * 2, SamplingParams(max_new=200))
+    plan = s.schedule()
+    assert sum(p.count for p in plan) == 6               # under a tile: untouched
+    s.update(plan, {p.req.req_id: 1 for p in plan if p.sample})
+    s.add("p", [0] * 70, SamplingParams(max_new=2))
+    plan = s.schedule()                                  # 3 decoded tokens + a portion of 32 = 35 = 2 tiles + 3
+    assert [(p.req.req_id, p.count, p.sample) for p in plan] == [("d0", 1, True), ("d1", 1, True), ("d2", 1, True), ("p", 29, False)]
+    s.update(plan, {p.req.req_id: 1 for p in plan if p.sample})
+    plan = s.schedule()                                  # the portion goes on where it stopped
+    assert (plan[-1].req.req_id, plan[-1].start, plan[-1].count) == ("p", 29, 29)
+    s.update(plan, {p.req.req_id: 1 for p in plan if p.sample})
+    plan = s.schedule()                                  # 3 + the last 12 = 15: under a tile, and the portion samples
+    assert (plan[-1].start, plan[-1].count, plan[-1].sample) == (58, 12, True)
+    s.update(plan, {p.req.req_id: 1 for p in plan if p.sample})
+    # further over than the slack: 3 + 32 + ... a second prompt of 25 tokens: 3 + 1 + 25 = 29 = a tile + 13
+    s.add("q", [0] * 25, SamplingParams(max_new=2))
+    plan = s.schedule()
+    assert sum(p.count for p in plan) == 29 and plan[-1].count == 25 and plan[-1].sample
+    log = run(s)
+    assert not s.has_work and all(r.finish_reason == "length" for r in s.done)
+    assert {r.req_id: len(r.output) for r in s.done} == {"d0": 200, "d1": 200, "d2": 200, "p": 2, "q": 2}
+    assert cache.groups[0].pool.used_count == 0
+
+
+def test_the_last_portion_of_a_prompt_that_is_trimmed_samples_a_step_later():
+    s, _ = make(num_pages=400, chunk_size=64, max_batch_tokens=100, row_tile=16, row_tile_slack=8)
+    s.add("a", [0] * 35, SamplingParams(max_new=1))      # 35 = 2 tiles + 3
+    log = run(s)
+    assert [e[0][1:] for e in log] == [(0, 32, False), (32, 3, True)]
