@@ -84,11 +84,11 @@ class Planned:
 class Scheduler:
     def __init__(self, cache: CacheManager, *, max_positions: int, max_num_seqs: int = 8,
                  max_batch_tokens: int = 2048, chunk_size: int = 512, policy: str = "reserve",
-                 row_tile: int = 0, row_tile_slack: int = 64):
+                 row_tile: int = 0, row_tile_slack: int | None = None):
         """``row_tile`` (0: off): the rows the kernels of a prompt portion work in.  A step of a few tokens more than
         a multiple of it pays for a whole tile more (512 prompt tokens beside 31 decoded ones: three tiles of 256 rows
-        for 543 tokens), so a step that is at most ``row_tile_slack`` tokens over a multiple gives those tokens of a
-        prompt portion back to the next step."""
+        for 543 tokens), so a step that is at most ``row_tile_slack`` tokens over a multiple (by default half a tile:
+        it saves more rows of padding than it puts off) gives those tokens of a prompt portion back to the next step."""
         if min(max_num_seqs, max_batch_tokens, chunk_size) < 1:
             raise ValueError("sizes must be >= 1")                 # runtime/scheduler.py:70-71
         if policy not in ("reserve", "on_demand"):
@@ -100,7 +100,7 @@ class Scheduler:
         self.chunk_size = chunk_size
         self.policy = policy
         self.row_tile = max(0, int(row_tile))
-        self.row_tile_slack = max(0, int(row_tile_slack))
+        self.row_tile_slack = self.row_tile // 2 if row_tile_slack is None else max(0, int(row_tile_slack))
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []       # in order of admission
         self.done: list[Request] = []
