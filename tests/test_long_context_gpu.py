@@ -138,3 +138,27 @@ def test_the_cut_of_the_context_fills_whole_waves():
                 if s > 1 and ctas > slots:        # more than a wave only when the waves are well filled
                     assert ctas / (-(-ctas // slots) * slots) > 0.6, (requests, nkv, ctx, s)
     assert 16 * 4 * ops.choose_splits(16, 4, 4096, 2) <= slots
+
+
+@pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 128), (6, 1, 64)])
+def test_the_decode_forms_merge_leaves_other_kernels_rows_alone(nq, nkv, hd):
+    """A step with a prompt portion beside decoding requests: the decode form runs on the decoding requests' tiles
+    only, with the context cut into ranges, and its merge kernel (told that the step has other rows) writes the
+    decoded tokens' rows and not one value of the portion's."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(33)
+    lens = [3000, 40, 1500]                       # the second request brings a portion of 40 tokens (rows 1..40)
+    q_lens = [1, 40, 1]
+    q, kc, vc, bt, pos, seq = _paged_case(g, lens, q_lens, nq, nkv, hd, 16, torch.bfloat16, consecutive="runs")
+    q_start, ctx_len = _starts(q_lens, lens)
+    want = ref.attention_simt(q.float(), kc.float(), vc.float(), bt, pos, seq, nq, nkv, hd, hd ** -0.5, None)
+    small, large = ops.attention_tiles(q_lens, nq // nkv, "cuda", lens, 128)
+    assert small[2] == 2 and large is not None
+    for name, form in _decode_forms(ops, hd, 16):
+        for splits in (1, 5):
+            out = torch.full_like(q, 77.0)
+            form(q, kc, vc, bt, q_start, ctx_len, small, splits, nq, nkv, hd, hd ** -0.5, None, out, True)
+            ops.check_tcgen05_status()
+            assert bool((out[1:41] == 77.0).all()), f"{name}, {splits} ranges: the portion's rows were written"
+            torch.testing.assert_close(out[[0, 41]].float(), want[[0, 41]], rtol=2e-2, atol=2e-2,
+                                       msg=lambda m: f"{name}, {splits} ranges: {m}")

@@ -186,6 +186,48 @@ def test_portions_of_a_long_prompt_beside_decoded_tokens(tmp_path):
     eng.cache.check()
 
 
+def test_a_long_request_decodes_beside_prompt_portions(tmp_path):
+    """The other way round: a request with 2,600 tokens of context decodes token by token while a second prompt
+    comes in portions of 150.  The decode form cuts the long context into ranges in those mixed steps too, and its
+    merge kernel leaves the portion's rows (the prefill form's, written after it) alone.  The logits of both, every
+    step, against the plain implementation."""
+    from sllm_b200 import ops
+    from sllm_b200.engine import Engine, StepEntry, build_model
+    from sllm_b200.weights import write_random_model
+    dev = cuda_or_skip()
+    cfg = dict(BASE, num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+               intermediate_size=512, vocab_size=1000, rope_theta=10000.0, rms_norm_eps=1e-6,
+               max_position_embeddings=4096, tie_word_embeddings=True)
+    d = str(tmp_path / "model")
+    write_random_model(d, cfg, 52, std=0.04, bias_std=0.2, gain_std=0.1)
+    c, w = plain.load_model(d)
+    rng = np.random.default_rng(30)
+    long_ids = rng.integers(0, cfg["vocab_size"], 2612).tolist()
+    prompt = rng.integers(0, cfg["vocab_size"], 600).tolist()
+    want_long, want_prompt = plain.forward(long_ids, w, c), plain.forward(prompt, w, c)
+    spread = float(want_long.std())
+    assert ops.choose_splits(1, 2, 2600, 3) > 1                     # what the decode form picks for the long request
+    model, _ = build_model(d, "bfloat16", dev)
+    eng = Engine(model, page_size=16, num_pages=(2612 + 600) // 16 + 8, max_requests=2)
+    for start in range(0, 2600, 650):
+        eng.step([StepEntry("l", long_ids[start:start + 650], [])])
+    worst = 0.0
+    for k in range(12):
+        entries = [StepEntry("l", [long_ids[2600 + k]], [0])]
+        if k % 3 == 0:                                               # every third step brings a portion of the prompt
+            j = (k // 3) * 150
+            entries.append(StepEntry("p", prompt[j:j + 150], [0, 149]))
+        got = eng.step(entries).float().cpu().numpy()
+        err = np.abs(got[0] - want_long[2600 + k]).max()
+        if k % 3 == 0:
+            err = max(err, np.abs(got[1] - want_prompt[j]).max(), np.abs(got[2] - want_prompt[j + 149]).max())
+        worst = max(worst, float(err))
+    ops.check_tcgen05_status()
+    assert worst <= 0.08 * spread, (worst, spread)
+    eng.finish("l"), eng.finish("p")
+    eng.cache.check()
+
+
 @pytest.mark.parametrize("live", [12, 40, 64])
 def test_many_live_requests_decode_through_the_graphs(live, tmp_path):
     """12, 40 and 64 requests decode together: the captured steps of 12, 48 and 64 rows (the products of
