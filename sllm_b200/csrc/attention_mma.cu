@@ -39,7 +39,6 @@ struct AttnParams {
   const int* tile_seq;           // [tiles]
   const int* tile_row0;          // [tiles]
   int max_pages, page_size, nq, nkv, window, num_splits, total_tokens;
-  int leave_unwritten;           // the merge leaves rows alone that no range wrote (part_lse -inf)
   float scale_log2;              // scale * log2(e)
 };
 
@@ -343,13 +342,19 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
 // out[row] = sum_s w_s part_o[s][row], w_s = 2^(lse_s - max) / sum: the splits of one row merged.
 template <int HD>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
-                                         __nv_bfloat16* __restrict__ out, int rows, int num_splits, int leave_unwritten) {
+                                             __nv_bfloat16* __restrict__ out, int rows, int num_splits,
+                                             const int* __restrict__ tile_seq, const int* __restrict__ q_start, int nq) {
+  // One CTA per (tile, query head, token of the tile's request): the rows the decode form wrote and no others, so
+  // that a step's other rows (a prompt portion's, the prefill form's) are neither read nor touched.  The step's
+  // description is read before the wait for the kernel before.
+  const int seq = tile_seq[blockIdx.x];
+  const int q0 = q_start[seq], q_len = q_start[seq + 1] - q0;
   pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
-  const int row = blockIdx.x;
+  if ((int)blockIdx.z >= q_len) return;
+  const int row = (q0 + (int)blockIdx.z) * nq + (int)blockIdx.y;
   float mt = -INFINITY;
   for (int s = 0; s < num_splits; ++s) mt = fmaxf(mt, part_lse[(size_t)s * rows + row]);
-  if (mt == -INFINITY && leave_unwritten) return;   // no range wrote this row: it is another kernel's (a prompt portion's in the same step)
   float tot = 0.f;
   for (int s = 0; s < num_splits; ++s) {
     const float l = part_lse[(size_t)s * rows + row];
@@ -385,8 +390,10 @@ static int launch_attention(const AttnParams& p, int tiles, cudaStream_t stream)
   int rc = launch_status("attention_mma");
   if (rc != SLLM_OK) return rc;
   if (p.num_splits > 1) {
-    launch_kernel(attention_combine_kernel<HD>, p.total_tokens * p.nq, HD >= 128 ? 128 : 64, 0, stream,
-                  (const float*)p.part_o, (const float*)p.part_lse, p.out, p.total_tokens * p.nq, p.num_splits, p.leave_unwritten);
+    const int G = p.nq / p.nkv;
+    launch_kernel(attention_combine_kernel<HD>, dim3((unsigned)tiles, (unsigned)p.nq, (unsigned)(16 / G > 0 ? 16 / G : 1)), HD >= 128 ? 128 : 64, 0, stream,
+                  (const float*)p.part_o, (const float*)p.part_lse, p.out, p.total_tokens * p.nq, p.num_splits, p.tile_seq,
+                  p.q_start, p.nq);
     rc = launch_status("attention_combine");
   }
   return rc;
@@ -406,7 +413,7 @@ SLLM_EXPORT int sllm_attention_mma(const void* q, const void* k_cache, const voi
                                    float* part_lse, const int* block_tables, int max_pages, const int* q_start,
                                    const int* ctx_len, const int* tile_seq, const int* tile_row0, int tiles,
                                    int decode, int num_splits, int total_tokens, int nq, int nkv, int hd,
-                                   int page_size, float scale, int window, int leave_unwritten, cudaStream_t stream) {
+                                   int page_size, float scale, int window, cudaStream_t stream) {
   SLLM_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_mma: bad head counts nq=%d nkv=%d", nq, nkv);
   SLLM_REQUIRE(sllm_attention_mma_supports(hd), "attention_mma: head_dim=%d is not one of 16, 32, 64, 128", hd);
   SLLM_REQUIRE(page_size > 0 && max_pages > 0 && tiles >= 0 && total_tokens >= 0, "attention_mma: bad sizes");
@@ -418,7 +425,7 @@ SLLM_EXPORT int sllm_attention_mma(const void* q, const void* k_cache, const voi
   p.out = (__nv_bfloat16*)out; p.part_o = part_o; p.part_lse = part_lse; p.block_tables = block_tables;
   p.q_start = q_start; p.ctx_len = ctx_len; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
   p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.window = window;
-  p.num_splits = num_splits; p.total_tokens = total_tokens; p.leave_unwritten = leave_unwritten;
+  p.num_splits = num_splits; p.total_tokens = total_tokens;
   p.scale_log2 = scale * 1.4426950408889634f;
 #define DISPATCH(HD_)                                                             \
   case HD_:                                                                       \

@@ -47,7 +47,6 @@ struct AttnTmaParams {
   const int* tile_row0;          // [tiles]
   int* status;
   int max_pages, page_size, nq, nkv, window, num_splits, total_tokens;
-  int leave_unwritten;           // the merge leaves rows alone that no range wrote (part_lse -inf): another kernel's rows in the same step
   int page_runs;                 // the run maps are valid: a tile of pages with consecutive ids is fetched as one box
   float scale_log2;
 };
@@ -404,13 +403,19 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
 template <int HD>
 __global__ void attention_tma_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
-                                             __nv_bfloat16* __restrict__ out, int rows, int num_splits, int leave_unwritten) {
+                                             __nv_bfloat16* __restrict__ out, int rows, int num_splits,
+                                             const int* __restrict__ tile_seq, const int* __restrict__ q_start, int nq) {
+  // One CTA per (tile, query head, token of the tile's request): the rows the decode form wrote and no others, so
+  // that a step's other rows (a prompt portion's, the prefill form's) are neither read nor touched.  The step's
+  // description is read before the wait for the kernel before.
+  const int seq = tile_seq[blockIdx.x];
+  const int q0 = q_start[seq], q_len = q_start[seq + 1] - q0;
   pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
-  const int row = blockIdx.x;
+  if ((int)blockIdx.z >= q_len) return;
+  const int row = (q0 + (int)blockIdx.z) * nq + (int)blockIdx.y;
   float mt = -INFINITY;
   for (int s = 0; s < num_splits; ++s) mt = fmaxf(mt, part_lse[(size_t)s * rows + row]);
-  if (mt == -INFINITY && leave_unwritten) return;   // no range wrote this row: it is another kernel's (a prompt portion's in the same step)
   float tot = 0.f;
   for (int s = 0; s < num_splits; ++s) {
     const float l = part_lse[(size_t)s * rows + row];
@@ -484,8 +489,10 @@ static int launch_ta(const CUtensorMap& mk, const CUtensorMap& mv, const CUtenso
   int rc = launch_status("attention_tma");
   if (rc != SLLM_OK) return rc;
   if (p.num_splits > 1) {
-    launch_kernel(attention_tma_combine_kernel<HD>, p.total_tokens * p.nq, HD >= 128 ? 128 : 64, 0, stream,
-                  (const float*)p.part_o, (const float*)p.part_lse, p.out, p.total_tokens * p.nq, p.num_splits, p.leave_unwritten);
+    const int G = p.nq / p.nkv;
+    launch_kernel(attention_tma_combine_kernel<HD>, dim3((unsigned)tiles, (unsigned)p.nq, (unsigned)(16 / G > 0 ? 16 / G : 1)), HD >= 128 ? 128 : 64, 0, stream,
+                  (const float*)p.part_o, (const float*)p.part_lse, p.out, p.total_tokens * p.nq, p.num_splits, p.tile_seq,
+                  p.q_start, p.nq);
     rc = launch_status("attention_tma_combine");
   }
   return rc;
@@ -514,8 +521,8 @@ SLLM_EXPORT int sllm_attention_tma_decode(const void* q, const void* k_cache, co
                                           void* out, float* part_o, float* part_lse, const int* block_tables,
                                           int max_pages, const int* q_start, const int* ctx_len, const int* tile_seq,
                                           const int* tile_row0, int tiles, int num_splits, int total_tokens, int nq,
-                                          int nkv, int hd, int page_size, float scale, int window, int leave_unwritten,
-                                          int* status, cudaStream_t stream) {
+                                          int nkv, int hd, int page_size, float scale, int window, int* status,
+                                          cudaStream_t stream) {
   SLLM_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tma: bad head counts nq=%d nkv=%d", nq, nkv);
   SLLM_REQUIRE(sllm_attention_tma_supports(hd, page_size), "attention_tma: head_dim=%d page_size=%d not taken", hd, page_size);
   SLLM_REQUIRE(max_pages > 0 && tiles >= 0 && total_tokens >= 0 && num_pages > 0, "attention_tma: bad sizes");
@@ -541,6 +548,6 @@ SLLM_EXPORT int sllm_attention_tma_decode(const void* q, const void* k_cache, co
   p.block_tables = block_tables; p.q_start = q_start; p.ctx_len = ctx_len; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
   p.status = status; p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.window = window;
   p.num_splits = num_splits; p.total_tokens = total_tokens; p.scale_log2 = scale * 1.4426950408889634f;
-  p.leave_unwritten = leave_unwritten;
+
   return hd == 128 ? launch_ta<128>(mk, mv, rk, rv, p, tiles, stream) : launch_ta<64>(mk, mv, rk, rv, p, tiles, stream);
 }

@@ -786,18 +786,10 @@ def choose_splits(num_small: int, nkv: int, max_ctx: int, ctas_per_sm: int = 2) 
     return best
 
 
-def _part_lse(num_splits: int, T: int, nq: int, device, others: bool):
-    """The ranges' log-sum-exponentials for the merge kernel; -inf everywhere first where the step has rows of other
-    kernels, so that the merge can tell them (no range writes them) and leave them alone."""
-    if others:
-        return torch.full((num_splits, T, nq), float("-inf"), dtype=torch.float32, device=device)
-    return torch.empty((num_splits, T, nq), dtype=torch.float32, device=device)
-
-
 def attention_mma(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, decode: bool, num_splits: int,
-                  nq, nkv, hd, scale, window, out=None, others: bool = False):
-    """The tensor-core attention kernel on one tile list (see `attention_tiles`).  ``others``: the step has rows that
-    are not this tile list's (another kernel writes them): the merge of a split context leaves them alone."""
+                  nq, nkv, hd, scale, window, out=None):
+    """The tensor-core attention kernel on one tile list (see `attention_tiles`); the merge of a split context
+    touches the rows of that list's requests only."""
     _chk(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles[0], tiles[1])
     if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
         raise KernelError("attention_mma: bfloat16 only")
@@ -807,10 +799,10 @@ def attention_mma(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, de
     part_o = part_lse = None
     if num_splits > 1:
         part_o = torch.empty((num_splits, T, nq, hd), dtype=torch.float32, device=q.device)
-        part_lse = _part_lse(num_splits, T, nq, q.device, others)
+        part_lse = torch.empty((num_splits, T, nq), dtype=torch.float32, device=q.device)
     call("sllm_attention_mma", _p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_o), _p(part_lse), _p(block_tables),
          block_tables.shape[1], _p(q_start), _p(ctx_len), _p(tiles[0]), _p(tiles[1]), tiles[2], 1 if decode else 0,
-         num_splits, T, nq, nkv, hd, k_cache.shape[2], float(scale), int(window or 0), 1 if others else 0, _stream())
+         num_splits, T, nq, nkv, hd, k_cache.shape[2], float(scale), int(window or 0), _stream())
     if num_splits > 1:
         launches["own"] += 1          # the combine kernel
     return out
@@ -827,8 +819,8 @@ def _tma_ctas_per_sm(hd: int) -> int:
 
 
 def attention_tma_decode(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, num_splits: int,
-                         nq, nkv, hd, scale, window, out=None, others: bool = False):
-    """The decode form fed by TMA (16-row tiles only; see `attention_tiles`).  ``others``: as for `attention_mma`."""
+                         nq, nkv, hd, scale, window, out=None):
+    """The decode form fed by TMA (16-row tiles only; see `attention_tiles`)."""
     _chk(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles[0], tiles[1])
     if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
         raise KernelError("attention_tma: bfloat16 only")
@@ -838,10 +830,10 @@ def attention_tma_decode(q, k_cache, v_cache, block_tables, q_start, ctx_len, ti
     part_o = part_lse = None
     if num_splits > 1:
         part_o = torch.empty((num_splits, T, nq, hd), dtype=torch.float32, device=q.device)
-        part_lse = _part_lse(num_splits, T, nq, q.device, others)
+        part_lse = torch.empty((num_splits, T, nq), dtype=torch.float32, device=q.device)
     call("sllm_attention_tma_decode", _p(q), _p(k_cache), _p(v_cache), k_cache.shape[0], _p(out), _p(part_o),
          _p(part_lse), _p(block_tables), block_tables.shape[1], _p(q_start), _p(ctx_len), _p(tiles[0]), _p(tiles[1]),
-         tiles[2], num_splits, T, nq, nkv, hd, k_cache.shape[2], float(scale), int(window or 0), 1 if others else 0,
+         tiles[2], num_splits, T, nq, nkv, hd, k_cache.shape[2], float(scale), int(window or 0),
          _p(_status_word(q.device)), _stream())
     _tc_used["since_check"] += 1
     if num_splits > 1:
@@ -931,7 +923,7 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
         small, large = attention_tiles(step.q_lens, G, q.device, step.ctx_lens, rows)
         per_sm = _tma_ctas_per_sm(hd) if tma_attention_supports(hd, k_cache.shape[2]) else 2
         # the decode form's cut of the context, by the longest context among ITS requests (a step may also hold prompt
-        # portions: their rows are the prefill form's, and the decode form's merge leaves them alone)
+        # portions: their rows are the prefill form's, and the decode form's merge touches its own requests' rows only)
         splits = 1
         if small:
             small_ctx = max((c for c, n in zip(step.ctx_lens, step.q_lens) if n * G <= 16), default=step.max_ctx_len) \
@@ -943,10 +935,10 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
     out = torch.empty_like(q)
     if small and tma_attention_supports(hd, k_cache.shape[2]):
         attention_tma_decode(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, splits,
-                             nq, nkv, hd, scale, window, out, others=bool(large))
+                             nq, nkv, hd, scale, window, out)
     elif small:
         attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, True, splits,
-                      nq, nkv, hd, scale, window, out, others=bool(large))
+                      nq, nkv, hd, scale, window, out)
     if large and use_tc:
         attention_tc(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, nq, nkv, hd, scale, out,
                      row_tiles=rows // 128, splits=tc_splits)

@@ -58,7 +58,7 @@ def _declare(L):
         "sllm_attention_tma_ctas_per_sm": [c_int],
         "sllm_attention_tma_decode": [c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                      c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
+                                      c_int, c_int, c_float, c_int, c_void_p, c_void_p],
         "sllm_wait_probe": [c_void_p, ctypes.c_ulonglong, c_void_p, c_void_p],
         "sllm_attention_tc_supports": [c_int, c_int],
         "sllm_attention_tc": [c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -90,7 +90,7 @@ def _declare(L):
                                c_int, c_void_p],
         "sllm_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                               c_int, c_int, c_float, c_int, c_int, c_void_p],
+                               c_int, c_int, c_float, c_int, c_void_p],
     }
     for name, argtypes in sigs.items():
         fn = getattr(L, name)

@@ -143,8 +143,8 @@ def test_the_cut_of_the_context_fills_whole_waves():
 @pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 128), (6, 1, 64)])
 def test_the_decode_forms_merge_leaves_other_kernels_rows_alone(nq, nkv, hd):
     """A step with a prompt portion beside decoding requests: the decode form runs on the decoding requests' tiles
-    only, with the context cut into ranges, and its merge kernel (told that the step has other rows) writes the
-    decoded tokens' rows and not one value of the portion's."""
+    only, with the context cut into ranges, and its merge kernel writes the decoded tokens' rows and not one value of
+    the portion's."""
     ops = _ops()
     g = torch.Generator(device="cuda").manual_seed(33)
     lens = [3000, 40, 1500]                       # the second request brings a portion of 40 tokens (rows 1..40)
@@ -157,7 +157,7 @@ def test_the_decode_forms_merge_leaves_other_kernels_rows_alone(nq, nkv, hd):
     for name, form in _decode_forms(ops, hd, 16):
         for splits in (1, 5):
             out = torch.full_like(q, 77.0)
-            form(q, kc, vc, bt, q_start, ctx_len, small, splits, nq, nkv, hd, hd ** -0.5, None, out, True)
+            form(q, kc, vc, bt, q_start, ctx_len, small, splits, nq, nkv, hd, hd ** -0.5, None, out)
             ops.check_tcgen05_status()
             assert bool((out[1:41] == 77.0).all()), f"{name}, {splits} ranges: the portion's rows were written"
             torch.testing.assert_close(out[[0, 41]].float(), want[[0, 41]], rtol=2e-2, atol=2e-2,
