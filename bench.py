@@ -175,7 +175,8 @@ def decode_run(model, cfg, batch, context, steps, warmup, seed=0, graphs=True, r
     # every request gets a portion in every step, so that all prompts end in the same step
     chunk = 512
     llm = LLM(model=model, block_size=page, num_pages=pages, max_num_seqs=batch, max_batch_tokens=batch * chunk,
-              chunk_size=chunk, max_model_len=context + 1, policy="reserve", cuda_graphs=graphs)
+              chunk_size=chunk, max_model_len=context + 1, policy="reserve", cuda_graphs=graphs,
+              row_tile=0)                             # (no portion is shortened: the prompts are to end together)
     rng = np.random.default_rng(seed)
     for i in range(batch):
         llm.add_request(rng.integers(0, cfg["vocab_size"], prompt_len).tolist(),
@@ -245,7 +246,8 @@ def stated_run(model, cfg, batch, prompt_len=2048, new_tokens=256, seed=5):
     from sllm_b200.sampling import SamplingParams
     context = prompt_len + new_tokens
     llm = LLM(model=model, block_size=PAGE_SIZE, num_pages=batch * (-(-(context + 1) // PAGE_SIZE)), max_num_seqs=batch,
-              max_batch_tokens=max(batch * 512, prompt_len), chunk_size=512, max_model_len=context + 1, policy="reserve")
+              max_batch_tokens=max(batch * 512, prompt_len), chunk_size=512, max_model_len=context + 1, policy="reserve",
+              row_tile=0)
     rng = np.random.default_rng(seed)
     out = None
     for rep in range(2):
