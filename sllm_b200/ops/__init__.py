@@ -232,8 +232,10 @@ def pair_tiles_wide(M: int, N: int) -> bool:
 @functools.lru_cache(maxsize=4096)
 def pair_tiles_slim(M: int, N: int) -> bool:
     """Whether tiles of 256 x 128 serve an [M, N] result better than tiles of 256 x 256: where the wider ones
-    would leave at least half of the pairs of SMs without a tile (a prompt portion of 512 tokens times a matrix
-    of 3,584 rows: 28 tiles for 74 pairs; down there 98 -> 54 us, the library's product 56)."""
+    would leave at least half of the pairs of SMs without a tile (a prompt portion of 512 tokens times the
+    q|k|v matrix: 36 tiles for 74 pairs; 30.6 -> 25.5 us).  The gain is small, since a pair is bound by the rate
+    at which it pulls its operands and half the width moves three quarters of the bytes; where K is long enough
+    the product is cut along K instead (`pair_splits`)."""
     pairs = max(num_sms() // 2, 1)
     return 2 * (-(-M // 256) * -(-N // 256)) <= pairs
 
