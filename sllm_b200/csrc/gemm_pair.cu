@@ -26,6 +26,15 @@
 // cluster barrier after set-up (no CTA signals a barrier its partner has not initialised) and before the
 // memory is freed (no CTA frees it while its partner's epilogue still reads).  No TMA load is multicast.
 //
+// Three tile shapes: 256 x 256 (two accumulators: a tile's epilogue under the next tile's products), 256 x 512 (one
+// accumulator, a quarter less traffic from L2; further down) and 256 x 128 (for results with few tiles).  The 256 x 256
+// and 256 x 128 forms also run in slices of K: a unit of work is then (tile, slice) and the slices leave a stack of
+// float32 partial sums for the next kernel to add, so that a result of few tiles still occupies every pair of SMs.
+// The epilogues that touch float32 rows of global memory (the plain float32 result and the residual epilogue, which
+// reads and writes the stream and writes the next norm's input) go through a box of shared memory per warp and
+// walk it four rows an instruction (gemm_epilogue.cuh): in tensor memory a lane holds a row, and lane-by-lane
+// accesses would put every 16-byte piece on a line of its own.
+//
 // The reference has no such kernel: its products are cublasGemmEx calls on one token
 // (kernels/cuda/kernels.cu:752-767) and its prefill runs in numpy (serving/executor.py:255-265).
 #include <stdio.h>
