@@ -284,11 +284,11 @@ SLLM_EXPORT int sllm_linear_stream(const void* x, const void* W, const float* bi
 }
 
 // The SiLU epilogue on an input whose norm is still owed: out[M, N/2] = silu(s gate) * (s up) with
-// s[token] = rsqrt(sum of ssq[token][0..parts) / width + eps); x is bfloat16(stream * gain).  At most 16 tokens.
+// s[token] = rsqrt(sum of ssq[token][0..parts) / width + eps); x is bfloat16(stream * gain).  At most 32 tokens.
 SLLM_EXPORT int sllm_linear_stream_silu_scaled(const void* x, const void* W, void* out, int M, int N, int K, const float* ssq,
                                                int parts, float eps, int width, cudaStream_t stream) {
-  SLLM_REQUIRE(sllm_linear_stream_supports(M, N, K) && M <= 16 && N % 16 == 0,
-               "linear_stream_silu_scaled: sizes M=%d N=%d K=%d (needs M<=16, N%%16==0, K%%128==0)", M, N, K);
+  SLLM_REQUIRE(sllm_linear_stream_supports(M, N, K) && M <= 32 && N % 16 == 0,
+               "linear_stream_silu_scaled: sizes M=%d N=%d K=%d (needs M<=32, N%%16==0, K%%128==0)", M, N, K);
   SLLM_REQUIRE(ssq != nullptr && ((uintptr_t)ssq & 15) == 0 && parts >= 1 && parts <= LS_SSQ_MAX && width >= 1,
                "linear_stream_silu_scaled: a table of %d partial sums (at most %d) over width %d", parts, LS_SSQ_MAX, width);
   LsScale sc;
@@ -296,7 +296,8 @@ SLLM_EXPORT int sllm_linear_stream_silu_scaled(const void* x, const void* W, voi
   const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
   const __nv_bfloat16* wb = (const __nv_bfloat16*)W;
   if (M <= 8) return launch_ls<1, EPI_SILU, __nv_bfloat16, true>(xb, wb, nullptr, out, nullptr, M, N, K, 1, stream, sc);
-  return launch_ls<2, EPI_SILU, __nv_bfloat16, true>(xb, wb, nullptr, out, nullptr, M, N, K, 1, stream, sc);
+  if (M <= 16) return launch_ls<2, EPI_SILU, __nv_bfloat16, true>(xb, wb, nullptr, out, nullptr, M, N, K, 1, stream, sc);
+  return launch_ls<4, EPI_SILU, __nv_bfloat16, true>(xb, wb, nullptr, out, nullptr, M, N, K, 1, stream, sc);
 }
 
 // ---------------------------------------------------------------------------------------------

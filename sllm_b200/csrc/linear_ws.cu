@@ -69,8 +69,11 @@ __device__ __forceinline__ void ws_mma(float (&c)[4], unsigned a0, unsigned a1, 
 constexpr int WS_WARPS = 8;
 // k blocks a warp keeps in flight per group (two groups): with two token tiles half as many, so that the
 // activation fragments fit the registers of two CTAs an SM (four: 174 registers a thread, one CTA an SM)
-__host__ __device__ constexpr int ws_depth(int nt) { return nt == 1 ? 4 : 2; }
+__host__ __device__ constexpr int ws_depth(int nt) { return nt == 1 ? 4 : (nt == 2 ? 2 : 1); }
 constexpr int WS_SSQ_MAX = 608;     // partial sums of squares per token a consumer takes (the producer's CTAs: at most 592 for 8192 columns)
+// with four token tiles (17..32 tokens: small matrices only, where a step is bound by its number of kernels) the table
+// is kept to what fits static shared memory beside the warps' tiles: streams of up to 3,072 columns
+__host__ __device__ constexpr int ws_ssq_max(int nt) { return nt <= 2 ? WS_SSQ_MAX : 192; }
 
 // An RMSNorm taken apart, so that a decode step needs no kernel for it (y = x * rsqrt(mean(x^2) + eps) * gain,
 // ref/standard.py:25-31).  The product that completes the residual stream (residual epilogue) also writes
@@ -99,7 +102,7 @@ linear_ws_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
   constexpr int WS_DEPTH = ws_depth(NT);
   __shared__ float red[WS_WARPS][16][8 * NT + 1];
   __shared__ float row_scale[8 * NT];
-  __shared__ __align__(16) float ssq_s[SCALED ? 8 * NT : 1][SCALED ? WS_SSQ_MAX : 4];
+  __shared__ __align__(16) float ssq_s[SCALED ? 8 * NT : 1][SCALED ? ws_ssq_max(NT) : 4];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
   // the CTA's rows [n0, n1): at most 16, the N rows dealt evenly over the grid (so that a grid of a
@@ -310,16 +313,16 @@ static int launch_ws(const __nv_bfloat16* x, const __nv_bfloat16* W, const float
 using namespace sllm;
 
 SLLM_EXPORT int sllm_linear_ws_supports(int M, int N, int K) {
-  return M >= 1 && M <= 16 && N >= 16 && K >= 32 && K % 32 == 0;
+  return M >= 1 && M <= 32 && N >= 16 && K >= 32 && K % 32 == 0;
 }
 
 // CTAs a launch for N output columns over a reduction of K uses: the rows of the table of partial sums of squares
 // that the residual epilogue writes when it is asked for the next norm's input (see WsNorm).
 SLLM_EXPORT int sllm_linear_ws_parts(int N, int K) { return ws_ctas(N, K, false); }
 
-static bool ws_norm_in(WsNorm& n, const float* ssq_in, int parts_in, float eps_in, int width_in) {
+static bool ws_norm_in(WsNorm& n, const float* ssq_in, int parts_in, float eps_in, int width_in, int M) {
   if (ssq_in == nullptr) return true;
-  if (parts_in < 1 || parts_in > WS_SSQ_MAX || width_in < 1 || ((uintptr_t)ssq_in & 15) != 0) return false;
+  if (parts_in < 1 || parts_in > ws_ssq_max(M <= 16 ? 2 : 4) || width_in < 1 || ((uintptr_t)ssq_in & 15) != 0) return false;
   n.ssq_in = ssq_in; n.parts_in = parts_in; n.eps_in = eps_in; n.inv_width_in = 1.0f / (float)width_in;
   return true;
 }
@@ -333,12 +336,12 @@ static bool ws_norm_in(WsNorm& n, const float* ssq_in, int parts_in, float eps_i
 SLLM_EXPORT int sllm_linear_ws(const void* x, const void* W, const float* bias, void* out, int out_dtype, float* residual,
                                int M, int N, int K, const float* ssq_in, int parts_in, float eps_in, int width_in,
                                const float* gain, void* xg_out, float* ssq_out, cudaStream_t stream) {
-  SLLM_REQUIRE(sllm_linear_ws_supports(M, N, K), "linear_ws: sizes M=%d N=%d K=%d (needs M<=16, K%%32==0)", M, N, K);
+  SLLM_REQUIRE(sllm_linear_ws_supports(M, N, K), "linear_ws: sizes M=%d N=%d K=%d (needs M<=32, K%%32==0)", M, N, K);
   SLLM_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)W & 15) == 0, "linear_ws: operands must be 16-byte aligned");
   SLLM_REQUIRE(residual != nullptr || out != nullptr, "linear_ws: no destination");
   WsNorm nm;
-  SLLM_REQUIRE(ws_norm_in(nm, ssq_in, parts_in, eps_in, width_in), "linear_ws: a table of %d partial sums (at most %d) over width %d",
-               parts_in, WS_SSQ_MAX, width_in);
+  SLLM_REQUIRE(ws_norm_in(nm, ssq_in, parts_in, eps_in, width_in, M), "linear_ws: a table of %d partial sums (at most %d) over width %d",
+               parts_in, ws_ssq_max(M <= 16 ? 2 : 4), width_in);
   if (gain != nullptr) {
     SLLM_REQUIRE(residual != nullptr && xg_out != nullptr && ssq_out != nullptr, "linear_ws: the next norm's input needs the residual epilogue and both destinations");
     nm.gain = gain; nm.xg_out = (__nv_bfloat16*)xg_out; nm.ssq_out = ssq_out;
@@ -350,7 +353,8 @@ SLLM_EXPORT int sllm_linear_ws(const void* x, const void* W, const float* bias, 
   if (out_dtype == SLLM_BF16) return launch_ws<NT_, WS_EPI_STORE, __nv_bfloat16>(xb, wb, bias, out, nullptr, M, N, K, stream, WsRope{}, nm); \
   return launch_ws<NT_, WS_EPI_STORE, float>(xb, wb, bias, out, nullptr, M, N, K, stream, WsRope{}, nm);
   if (M <= 8) { GO(1) }
-  GO(2)
+  if (M <= 16) { GO(2) }
+  GO(4)
 #undef GO
 }
 
@@ -373,8 +377,8 @@ SLLM_EXPORT int sllm_linear_ws_rope(const void* x, const void* W, const float* b
                "linear_ws_rope: destination or rotary table missing");
   SLLM_REQUIRE(slot_mapping == nullptr || (k_cache && v_cache && page_size > 0 && num_pages > 0), "linear_ws_rope: cache arguments missing");
   WsNorm nm;
-  SLLM_REQUIRE(ws_norm_in(nm, ssq_in, parts_in, eps_in, width_in), "linear_ws_rope: a table of %d partial sums (at most %d) over width %d",
-               parts_in, WS_SSQ_MAX, width_in);
+  SLLM_REQUIRE(ws_norm_in(nm, ssq_in, parts_in, eps_in, width_in, M), "linear_ws_rope: a table of %d partial sums (at most %d) over width %d",
+               parts_in, ws_ssq_max(M <= 16 ? 2 : 4), width_in);
   WsRope r;
   r.positions = positions; r.table = rot > 0 ? table : nullptr; r.slot_mapping = slot_mapping;
   r.k_cache = (__nv_bfloat16*)k_cache; r.v_cache = (__nv_bfloat16*)v_cache; r.q_out = (__nv_bfloat16*)q_out;
@@ -382,5 +386,6 @@ SLLM_EXPORT int sllm_linear_ws_rope(const void* x, const void* W, const float* b
   const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
   const __nv_bfloat16* wb = (const __nv_bfloat16*)W;
   if (M <= 8) return launch_ws<1, WS_EPI_ROPE, __nv_bfloat16>(xb, wb, bias, nullptr, nullptr, M, N, K, stream, r, nm);
-  return launch_ws<2, WS_EPI_ROPE, __nv_bfloat16>(xb, wb, bias, nullptr, nullptr, M, N, K, stream, r, nm);
+  if (M <= 16) return launch_ws<2, WS_EPI_ROPE, __nv_bfloat16>(xb, wb, bias, nullptr, nullptr, M, N, K, stream, r, nm);
+  return launch_ws<4, WS_EPI_ROPE, __nv_bfloat16>(xb, wb, bias, nullptr, nullptr, M, N, K, stream, r, nm);
 }

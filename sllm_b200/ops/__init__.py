@@ -406,7 +406,14 @@ def linear_tc(x, w, bias, out_dtype, *, splits: int = 1, silu: bool = False):
 
 
 WS_MAX_COLS = 8192        # wider products have CTAs enough for the 128-row streaming kernel
-WS_MAX_ROWS = 16          # two 8-token tiles (with half as many k blocks in flight, so that two CTAs still share an SM)
+WS_MAX_ROWS = 32          # one, two or four 8-token tiles (with fewer k blocks in flight the more tiles, so that two CTAs still share an SM)
+# Four tiles (17..32 tokens, one k block in flight per group) stream slowly, so only where little streams and the
+# fused epilogues save kernels: a short reduction, a matrix of at most 2^24 elements, and rows enough for one and a
+# half CTAs an SM (q|k|v and o_proj at a hidden size of 3,584: decode at batch 24 and 32 +2.5 %; at hidden sizes of
+# 1,536 and 2,048 the k-split kernel with its norm and rotary kernels stayed the faster, 2.05 against 2.21 ms a step).
+WS_ROWS32_MAX_ELEMENTS = int(os.environ.get("SLLM_WS_ROWS32_MAX_ELEMENTS", str(1 << 24)))
+WS_ROWS32_MAX_K = 4096
+MAX_SCALE_PARTS_ROWS32 = 192   # the table of partial sums a four-tile consumer keeps (streams of up to 3,072 columns)
 
 
 @functools.lru_cache(maxsize=4096)
@@ -416,11 +423,15 @@ def ws_supports(M: int, N: int, K: int) -> bool:
     kernel by more than the fused epilogues save (16 tokens, K = 27648: 64.3 against 49.2 us)."""
     if not (M <= WS_MAX_ROWS and N <= WS_MAX_COLS and bool(lib().sllm_linear_ws_supports(int(M), int(N), int(K)))):
         return False
-    return _ws_tokens_ok(M, N)
+    return _ws_tokens_ok(M, N, K)
 
 
-def _ws_tokens_ok(M: int, N: int) -> bool:
-    return M <= 8 or -(-N // 16) <= 2 * num_sms()
+def _ws_tokens_ok(M: int, N: int, K: int) -> bool:
+    if M <= 8:
+        return True
+    if -(-N // 16) > 2 * num_sms():
+        return False
+    return M <= 16 or (N * K <= WS_ROWS32_MAX_ELEMENTS and K <= WS_ROWS32_MAX_K and 2 * -(-N // 16) >= 3 * num_sms())
 
 
 class RowScale:
@@ -509,7 +520,7 @@ def can_accumulate_norm(x: torch.Tensor, w: torch.Tensor) -> bool:
         return False
     M, N = x.shape[0], w.shape[0]
     if ws_supports(M, N, x.shape[1]):
-        return int(lib().sllm_linear_ws_parts(N, x.shape[1])) <= MAX_SCALE_PARTS
+        return int(lib().sllm_linear_ws_parts(N, x.shape[1])) <= (MAX_SCALE_PARTS if M <= 16 else MAX_SCALE_PARTS_ROWS32)
     return N % 8 == 0
 
 
@@ -602,7 +613,7 @@ def silu_scaled_supports(x, w_gate_up, interleave: int, out_dtype) -> bool:
     N = w_gate_up.shape[0]
     if not (x.is_cuda and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and interleave == 8 and N % 16 == 0):
         return False
-    return (M <= 16 and stream_supports(M, N, K)) or (M > TCGEN05_MIN_ROWS and _PAIR_GEMM != "off" and pair_supports(M, N, K))
+    return (M <= 32 and stream_supports(M, N, K)) or (M > TCGEN05_MIN_ROWS and _PAIR_GEMM != "off" and pair_supports(M, N, K))
 
 
 def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, out_dtype: torch.dtype,
@@ -615,7 +626,7 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, o
         _chk(x, w_gate_up, scale.ssq)
         M, K = x.shape
         N = w_gate_up.shape[0]
-        if M > 16:
+        if M > 32:
             return gemm_pair(x, w_gate_up, None, out_dtype, silu=True, scale=scale)
         out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
         call("sllm_linear_stream_silu_scaled", _p(x), _p(w_gate_up), _p(out), M, N, K, *scale.args(), _stream())
@@ -651,7 +662,7 @@ def qkv_rope_supports(x, w, table, rotary_dim, nq, nkv, hd, k_cache) -> bool:
         return False
     rot = int(rotary_dim) if table is not None else 0
     M, K = x.shape
-    return M <= WS_MAX_ROWS and _ws_tokens_ok(M, w.shape[0]) and bool(lib().sllm_linear_ws_rope_supports(int(M), int(w.shape[0]), int(K), int(nq), int(nkv),
+    return M <= WS_MAX_ROWS and _ws_tokens_ok(M, w.shape[0], K) and bool(lib().sllm_linear_ws_rope_supports(int(M), int(w.shape[0]), int(K), int(nq), int(nkv),
                                                                           int(hd), rot))
 
 

@@ -157,7 +157,7 @@ def test_rope_kv_write_wide_form(in_dtype, T, nq, nkv, hd, rot, ps):
     assert not k2.any() and not v2.any()
 
 
-@pytest.mark.parametrize("M", [1, 5, 8, 9, 13, 16])
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 13, 16, 17, 32])
 @pytest.mark.parametrize("nq,nkv,hd,K,ps", [(28, 4, 128, 3584, 16), (14, 2, 64, 896, 64), (4, 2, 16, 64, 16), (3, 1, 32, 96, 8),
                                             (6, 3, 48, 160, 16), (2, 2, 256, 128, 32)])
 def test_linear_rope_kv_write(M, nq, nkv, hd, K, ps):
@@ -175,7 +175,9 @@ def test_linear_rope_kv_write(M, nq, nkv, hd, K, ps):
     ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * (1e4 ** (-torch.arange(0, hd, 2, dtype=torch.float64) / hd))[None]
     table = torch.stack([ang.cos(), ang.sin()], 1).float().cuda()
     slots = torch.randperm(pages * ps, device="cuda", generator=g)[:M].int()
-    assert ops.qkv_rope_supports(x, w, table, hd, nq, nkv, hd, torch.zeros(1, nkv, ps, hd, device="cuda", dtype=torch.bfloat16))
+    # (the dispatch sends 17..32 tokens here only for matrices with rows enough for one and a half CTAs an SM)
+    assert ops.qkv_rope_supports(x, w, table, hd, nq, nkv, hd, torch.zeros(1, nkv, ps, hd, device="cuda", dtype=torch.bfloat16)) \
+        == (M <= 16 or 2 * -(-N // 16) >= 3 * ops.num_sms())
     dtype = torch.bfloat16
     for b, tab, rot in ((bias, table, hd), (None, table, hd), (bias, None, 0)):
         kc = [torch.zeros(pages, nkv, ps, hd, device="cuda", dtype=dtype) for _ in range(2)]
@@ -852,7 +854,7 @@ def test_linear_tc_silu(M, I, K):
     torch.testing.assert_close(ops.linear_silu_mul(x, gu, 8, torch.bfloat16).float(), want, rtol=1.6e-2, atol=1.6e-2)
 
 
-@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 25, 32])
 @pytest.mark.parametrize("N,K", [(16, 32), (100, 96), (3584, 3584), (4608, 3584), (200, 18944), (1000, 320)])
 def test_linear_ws(M, N, K):
     """The warp-split streaming kernel: stores in both dtypes, and the fused residual add."""
@@ -862,13 +864,15 @@ def test_linear_ws(M, N, K):
     w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
     b = torch.randn(N, device="cuda", generator=g)
     want = x.float() @ w.float().t() + b
-    assert ops.ws_supports(min(M, ops.WS_MAX_ROWS), N, K)
+    # what the dispatch sends here: 17..32 tokens only a short reduction into rows enough for one and a half CTAs an SM
+    picked = M <= 16 or (K <= ops.WS_ROWS32_MAX_K and N * K <= ops.WS_ROWS32_MAX_ELEMENTS and 2 * -(-N // 16) >= 3 * ops.num_sms())
+    assert ops.ws_supports(M, N, K) == picked
     torch.testing.assert_close(ops.linear_ws(x, w, b, torch.float32), want, rtol=2e-3, atol=2e-3)
     torch.testing.assert_close(ops.linear_ws(x, w, None, torch.bfloat16).float(), want - b, rtol=1.6e-2, atol=1.6e-2)
     res = torch.randn(M, N, device="cuda", generator=g)
     expect = res + want
-    assert ops.can_accumulate(x, w) == (M <= ops.WS_MAX_ROWS)
-    ops.linear_accumulate(x, w, b, res)
+    assert ops.can_accumulate(x, w) == picked
+    ops.linear_ws(x, w, b, torch.float32, residual=res)
     torch.testing.assert_close(res, expect, rtol=2e-3, atol=2e-3)
     # the sum does not depend on the other tokens of the batch
     if M > 1:
@@ -876,8 +880,8 @@ def test_linear_ws(M, N, K):
         assert torch.equal(one[0], ops.linear_ws(x, w, b, torch.float32)[M - 1])
 
 
-@pytest.mark.parametrize("M", [1, 3, 8, 11, 16])
-@pytest.mark.parametrize("H,K", [(3584, 3584), (3584, 18944), (896, 4864), (1000, 320), (96, 64), (5120, 13824), (8192, 512)])
+@pytest.mark.parametrize("M", [1, 3, 8, 11, 16, 21, 32])
+@pytest.mark.parametrize("H,K", [(3584, 3584), (3584, 18944), (896, 4864), (1000, 320), (96, 64), (5120, 13824), (8192, 512), (2048, 2048)])
 def test_an_rmsnorm_owed_by_one_product_and_paid_by_the_next(M, H, K):
     """The product that completes the residual stream also writes the next RMSNorm's input as
     bfloat16(stream * gain) with partial sums of squares, and the products that consume it (plain, the
@@ -894,7 +898,18 @@ def test_an_rmsnorm_owed_by_one_product_and_paid_by_the_next(M, H, K):
     res = 3 * torch.randn(M, H, device="cuda", generator=g)
     stream = res + x.float() @ w.float().t() + b
     assert ops.can_accumulate_norm(x[:8].contiguous(), w)
-    xg, scale = ops.linear_accumulate_norm(x, w, b, res, gain, eps)
+
+    def produce(into):
+        if M <= 16:
+            return ops.linear_accumulate_norm(x, w, b, into, gain, eps)      # as the engine calls it
+        # 17..32 tokens: the dispatch has no use for the warp-split kernel with a norm here (the matrices it sends
+        # there at so many tokens have more CTAs than the four-tile table holds); the kernel is called directly
+        xg_, scale_ = ops.linear_ws(x, w, b, torch.float32, residual=into, next_gain=gain)
+        scale_.eps = eps
+        return xg_, scale_
+    if M > 16 and (H % 32 != 0 or K % 32 != 0 or int(ops.lib().sllm_linear_ws_parts(H, K)) > ops.MAX_SCALE_PARTS_ROWS32):
+        return
+    xg, scale = produce(res)
     torch.testing.assert_close(res, stream, rtol=2e-3, atol=2e-3)
     torch.testing.assert_close(xg.float(), (res * gain).bfloat16().float(), rtol=1e-2, atol=1e-2)
     assert scale.parts <= ops.MAX_SCALE_PARTS and scale.width == H and scale.eps == eps
@@ -941,8 +956,8 @@ def test_an_rmsnorm_owed_by_one_product_and_paid_by_the_next(M, H, K):
     # the partial sums are written per CTA and added in a fixed order: the same call gives the same bits
     again = stream - (x.float() @ w.float().t() + b)
     first = again.clone()
-    xg_a, scale_a = ops.linear_accumulate_norm(x, w, b, first, gain, eps)
-    xg_b, scale_b = ops.linear_accumulate_norm(x, w, b, again, gain, eps)
+    xg_a, scale_a = produce(first)
+    xg_b, scale_b = produce(again)
     assert torch.equal(xg_a, xg_b) and torch.equal(scale_a.ssq[:, :scale_a.parts], scale_b.ssq[:, :scale_b.parts])
 
 
