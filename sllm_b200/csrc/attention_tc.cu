@@ -98,6 +98,34 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// The softmax thread walks its row's 64 keys alone, and every instruction of that walk lengthens the
+// key tile's period, so the walk uses the two-wide float32 forms (one instruction for two
+// multiply-adds or two sums, each rounded as the scalar form rounds) and the maximum of three.
+__device__ __forceinline__ float2 fma_x2(float a0, float a1, float b, float c) {
+  unsigned long long ra, rb, rc, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a0), "f"(a1));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(rb) : "f"(b));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(rc) : "f"(c));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ float2 add_x2(float2 a, float2 b) {
+  unsigned long long ra, rb, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <int HD, int RT>
 __global__ void __launch_bounds__(TcLayout<HD, RT>::THREADS, RT == 1 ? 2 : 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -396,13 +424,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       float mx = -INFINITY;
       if (__all_sync(0xffffffffu, kbase + TC_BN <= hi)) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+        for (int i = 0; i < 32; ++i) mx = max3(mx, __uint_as_float(s0[i]), __uint_as_float(s1[i]));
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           if (kbase + i >= hi) s0[i] = 0xff800000u;          // -inf
           if (kbase + 32 + i >= hi) s1[i] = 0xff800000u;
-          mx = fmaxf(mx, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+          mx = max3(mx, __uint_as_float(s0[i]), __uint_as_float(s1[i]));
         }
       }
       mx *= p.scale_log2;
@@ -435,16 +463,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       }
       const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
       uint32_t pk[32];                                      // column i: keys 2i (low half) and 2i+1
+      float2 sums = make_float2(0.f, 0.f);                  // of the even and of the odd keys
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float e0 = ex2(fmaf(__uint_as_float(s0[2 * i]), p.scale_log2, neg_m));
-        const float e1 = ex2(fmaf(__uint_as_float(s0[2 * i + 1]), p.scale_log2, neg_m));
-        const float e2 = ex2(fmaf(__uint_as_float(s1[2 * i]), p.scale_log2, neg_m));
-        const float e3 = ex2(fmaf(__uint_as_float(s1[2 * i + 1]), p.scale_log2, neg_m));
-        l += (e0 + e1) + (e2 + e3);
-        pk[i] = pack2(e0, e1);
-        pk[16 + i] = pack2(e2, e3);
+        const float2 x01 = fma_x2(__uint_as_float(s0[2 * i]), __uint_as_float(s0[2 * i + 1]), p.scale_log2, neg_m);
+        const float2 x23 = fma_x2(__uint_as_float(s1[2 * i]), __uint_as_float(s1[2 * i + 1]), p.scale_log2, neg_m);
+        const float2 e01 = make_float2(ex2(x01.x), ex2(x01.y)), e23 = make_float2(ex2(x23.x), ex2(x23.y));
+        sums = add_x2(sums, add_x2(e01, e23));
+        pk[i] = pack2(e01.x, e01.y);
+        pk[16 + i] = pack2(e23.x, e23.y);
       }
+      l += sums.x + sums.y;
       tmem_st32(t_lane + b * TC_BN, pk);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       tc_fence_before();
