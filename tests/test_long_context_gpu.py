@@ -30,7 +30,7 @@ def _decode_forms(ops, hd, ps):
 @pytest.mark.parametrize("ctx,ps", [(8192, 16), (32768, 16), (32768, 64), (17000, 8)])
 @pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 128), (6, 1, 64)])
 def test_decode_forms_at_long_contexts(ctx, ps, nq, nkv, hd):
-    """Single decoded tokens over 8k to 32k keys: every number of splits up to the cap of 32, requests of
+    """Single decoded tokens over 8k to 32k keys: a few numbers of splits and the one the engine picks (above 32 at 32k), requests of
     other lengths in the same batch, and (pages of 8 at 17,000 tokens: 2,125 pages) a block table longer than
     the 2,048 entries the kernels cache."""
     ops = _ops()
@@ -45,7 +45,7 @@ def test_decode_forms_at_long_contexts(ctx, ps, nq, nkv, hd):
     small, large = ops.attention_tiles(q_lens, nq // nkv, "cuda")
     assert large is None
     picked = ops.choose_splits(1, 1, ctx)                      # what the engine picks for one request at this length
-    assert 24 <= picked <= 32
+    assert 24 <= picked <= ops.MAX_SPLITS and (ctx < 32768 or picked > 32)
     for name, form in _decode_forms(ops, hd, ps):
         for splits in sorted({1, 7, picked, 32}):
             out = torch.full_like(q, float("nan"))
@@ -123,7 +123,7 @@ def test_prefill_form_on_a_portion_at_32k(nq, nkv, hd, ps):
 
 def test_the_cut_of_the_context_fills_whole_waves():
     """The number of ranges the decode form cuts a context into: no range without keys, at least 256 keys a
-    range, at most 32 ranges, and never a few CTAs more than the GPU holds at once (16 requests of 4 KV heads
+    range, at most `ops.MAX_SPLITS` ranges, and never a few CTAs more than the GPU holds at once (16 requests of 4 KV heads
     at 4,096 keys were cut five ways, 320 CTAs for 296 places, and ran two waves: 47 us against 31 cut four ways)."""
     ops = _ops()
     slots = 2 * ops.num_sms()
@@ -131,7 +131,7 @@ def test_the_cut_of_the_context_fills_whole_waves():
         for nkv in (1, 4, 8):
             for ctx in (1, 255, 256, 1000, 4096, 5000, 17000, 32768):
                 s = ops.choose_splits(requests, nkv, ctx, 2)
-                assert 1 <= s <= max(1, min(32, ctx // 256))
+                assert 1 <= s <= max(1, min(ops.MAX_SPLITS, ctx // 256))
                 tiles = -(-(-(-ctx // s)) // 64)
                 assert -(-ctx // (tiles * 64)) == s, (requests, nkv, ctx, s)
                 ctas = requests * nkv * s
