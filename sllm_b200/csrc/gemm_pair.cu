@@ -290,6 +290,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // under part of them: the epilogue hands half 0 back as soon as it has read it, and the MMA thread starts the
 // next tile with the products of half 0 alone for the stages that are loaded (TP_STAGES_WIDE k blocks), then
 // waits for half 1, catches up on those stages and goes on with both.
+// The tile may also be narrower, 256 + 2 R2 columns with R2 = 96, 64 or 32 (448, 384, 320): the second product of a
+// k step then takes R2 rows of each CTA's box of W (N = 2 R2), so that a result whose 512-wide tiles leave pairs of
+// SMs idle (3,584 columns by 2,048 rows: 56 tiles for 74 pairs) is cut into more, narrower ones (64 of 448).
 
 constexpr int TP_TMEM_COLS_WIDE = 512;                            // one accumulator of 512 columns
 constexpr int TP_BN_WIDE = 512, TP_STAGES_WIDE = 4;
@@ -301,7 +304,7 @@ constexpr int TP_STAGING_BYTES = TP_EPI_WARPS_WIDE * 4096;         // the epilog
 constexpr int TP_SMEM_WIDE = TP_STAGES_WIDE * TP_STAGE_BYTES_WIDE + TP_STAGING_BYTES + 1024 + 256;
 static_assert(TP_SMEM_WIDE <= 227 * 1024, "shared memory of the wide form");
 
-template <int EPI>
+template <int EPI, int R2>
 __global__ void __launch_bounds__(TP_THREADS_WIDE, 1)
 gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       const __grid_constant__ CUtensorMap map_out, int tma_out,
@@ -317,10 +320,13 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  static_assert(R2 >= 32 && R2 <= 128 && R2 % TgBox<EPI>::ACC_COLS == 0, "rows of W in the second product");
+  constexpr int BNW = 256 + 2 * R2;                  // the tile's columns; a CTA's box of W has half as many rows
+  constexpr int STAGE_TX = TP_A_BYTES + (BNW / 2) * TP_BK * 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
-  const int m_tiles = (M + 2 * TP_BM - 1) / (2 * TP_BM), n_tiles = (N + TP_BN_WIDE - 1) / TP_BN_WIDE;
+  const int m_tiles = (M + 2 * TP_BM - 1) / (2 * TP_BM), n_tiles = (N + BNW - 1) / BNW;
   const int tiles = m_tiles * n_tiles;
   const int k_blocks = (K + TP_BK - 1) / TP_BK;
 
@@ -352,7 +358,7 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       bool gave_up = false;
       for (int tile = pair; tile < tiles && !*failed; tile += pairs) {
         const int m0 = (tile % m_tiles) * 2 * TP_BM + (int)rank * TP_BM;
-        const int n0 = (tile / m_tiles) * TP_BN_WIDE + (int)rank * (TP_BN_WIDE / 2);
+        const int n0 = (tile / m_tiles) * BNW + (int)rank * (BNW / 2);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % TP_STAGES_WIDE, round = it / TP_STAGES_WIDE;
           if (!mbar_wait(&empty[s], (round & 1) ^ 1) || *failed) {
@@ -362,7 +368,7 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           }
           unsigned char* sa = smem + s * TP_STAGE_BYTES_WIDE;
           const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
-          if (rank == 0) mbar_expect_tx(&full[s], 2 * TP_STAGE_BYTES_WIDE);
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_TX);
           tma_load_2d_pair(sa, &map_a, kb * TP_BK, m0, bar);
           tma_load_2d_pair(sa + TP_A_BYTES, &map_w, kb * TP_BK, n0, bar);
         }
@@ -376,7 +382,8 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)((2 * TP_BM) >> 4) << 24);
+      constexpr uint32_t idesc_common = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)((2 * TP_BM) >> 4) << 24);
+      constexpr uint32_t idesc0 = idesc_common | ((uint32_t)(256 >> 3) << 17), idesc1 = idesc_common | ((uint32_t)((2 * R2) >> 3) << 17);
       // The loop of the issuing thread is kept lean (its own instructions showed in the kernel's time): stages and
       // parities are counted, not divided; descriptors are made by addition; the flag in shared memory is only read
       // when a wait has run out.
@@ -385,6 +392,7 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       auto half_products = [&](uint32_t st, int kb, int h) {
         const uint64_t da = desc0 + (uint64_t)(st * (TP_STAGE_BYTES_WIDE >> 4));
         const uint64_t db = da + ((TP_A_BYTES + h * (128 * 128)) >> 4);
+        const uint32_t idesc = h ? idesc1 : idesc0;
         umma_bf16_pair(tmem_base + h * 256, da, db, idesc, kb ? 1u : 0u);
 #pragma unroll
         for (int k = 1; k < TP_BK / 16; ++k) umma_bf16_pair(tmem_base + h * 256, da + 2 * k, db + 2 * k, idesc, 1u);
@@ -430,14 +438,14 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     }
   } else {
     // ---------------- epilogue: warps 2..9; warp w reads lanes 32 (w % 4) .., and of every accumulator half the
-    // columns [0, 128) (warps 2..5) or [128, 256) (warps 6..9) ----------------
+    // columns of the first CTA's rows of W (warps 2..5) or of the second CTA's (warps 6..9) ----------------
     const int quarter = warp & 3, col_half = (warp - 2) >> 2;
     const uint32_t acc_empty_addr[2] = {map_to_cta(smem_u32(&acc_empty[0]), 0), map_to_cta(smem_u32(&acc_empty[1]), 0)};
     unsigned char* box = staging + (warp - 2) * 4096;
     int local = 0;
     bool staged = false;                            // a box of this warp is on its way out of shared memory
     for (int tile = pair; tile < tiles; tile += pairs, ++local) {
-      const int m0 = (tile % m_tiles) * 2 * TP_BM + (int)rank * TP_BM, n0 = (tile / m_tiles) * TP_BN_WIDE;
+      const int m0 = (tile % m_tiles) * 2 * TP_BM + (int)rank * TP_BM, n0 = (tile / m_tiles) * BNW;
       const int m = m0 + quarter * 32 + lane;
       const float row_scale = tg_row_scale(extra, m, M);        // a norm still owed on the input (1 if none): fetched while the products run
       const bool ok = mbar_wait(&acc_full[0], local & 1);
@@ -449,11 +457,14 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {
         float sq[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        // accumulator half h holds a product of `width` rows of each CTA's box of W (128 for half 0, R2 for half 1):
+        // its columns [0, width) are C's columns n0 + 128 h .. (the first CTA's rows), its columns [width, 2 width)
+        // are C's columns n0 + BNW / 2 + 128 h .. (the second CTA's); nb: where this warp's columns start in C
+        const int width = h == 0 ? 128 : R2;
+        const int nb = n0 + (BNW / 2) * col_half + 128 * h;
 #pragma unroll 1
-        for (int c0 = 128 * col_half; c0 < 128 * col_half + 128; c0 += AC) {
-          // accumulator half h: its columns [0, 128) are C's columns n0 + 128 h .. (the first CTA's rows of W), its
-          // columns [128, 256) are C's columns n0 + 256 + 128 h .. (the second CTA's)
-          const int n = n0 + 256 * col_half + 128 * h + (c0 - 128 * col_half);
+        for (int c0 = width * col_half; c0 < width * col_half + width; c0 += AC) {
+          const int n = nb + (c0 - width * col_half);
           if (n >= N || row0 >= M) continue;        // warp-uniform
           if (tma_out && staged) {                  // the box staged before has left shared memory
             if (lane == 0) bulk_wait_read<0>();
@@ -483,9 +494,8 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           }
         }
         if constexpr (EPI == TG_EPI_RESID) {
-          // the warp's 128 columns of this half are one block of C's columns: its sum of squares per row
-          const int nb = n0 + 256 * col_half + 128 * h;
-          if (nb < N) tg_resid_box_sums(sq, lane, row0, M, nb / 128, extra);
+          // the warp's columns of this half are one block of C's columns: its sum of squares per row (four blocks a tile)
+          if (nb < N) tg_resid_box_sums(sq, lane, row0, M, 4 * (tile / m_tiles) + 2 * col_half + h, extra);
         }
         // this warp has read its share of the half: the MMA thread may write it again
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -524,12 +534,12 @@ static void pair_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute (&at
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
 }
 
-template <int EPI>
+template <int EPI, int R2>
 static int launch_tp_wide(const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, void* out, int M, int N, int K,
                           int* status, cudaStream_t stream, const TgExtra& extra) {
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_pair_wide_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM_WIDE) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_pair_wide_kernel<EPI, R2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM_WIDE) != cudaSuccess) {
       set_error("gemm_pair: cannot raise the shared memory limit");
       return SLLM_ERR_LAUNCH;
     }
@@ -542,12 +552,13 @@ static int launch_tp_wide(const CUtensorMap& ma, const CUtensorMap& mw, const fl
   if (EPI != TG_EPI_RESID && ((size_t)out_cols * elem) % 16 == 0 && ((uintptr_t)out & 15) == 0)
     tma_out = make_map_store(&mo, out, M, out_cols, elem) ? 1 : 0;
   const int pairs_max = sllm::num_sms() / 2;
-  const long long tiles = (long long)((M + 2 * TP_BM - 1) / (2 * TP_BM)) * ((N + TP_BN_WIDE - 1) / TP_BN_WIDE);
+  constexpr int BNW = 256 + 2 * R2;
+  const long long tiles = (long long)((M + 2 * TP_BM - 1) / (2 * TP_BM)) * ((N + BNW - 1) / BNW);
   const int pairs = (int)(tiles < pairs_max ? tiles : pairs_max);
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[2];
   pair_launch_config(cfg, attr, pairs, TP_THREADS_WIDE, TP_SMEM_WIDE, stream);
-  cudaLaunchKernelEx(&cfg, gemm_pair_wide_kernel<EPI>, ma, mw, mo, tma_out, bias, out, M, N, K, status, extra);
+  cudaLaunchKernelEx(&cfg, gemm_pair_wide_kernel<EPI, R2>, ma, mw, mo, tma_out, bias, out, M, N, K, status, extra);
   return launch_status("gemm_pair");
 }
 
@@ -596,6 +607,17 @@ SLLM_EXPORT int sllm_gemm_pair_supports(int M, int N, int K) {
 // kernel ran out (41 producer, 42 MMA issuer, 43 epilogue) and the result is not valid.
 SLLM_EXPORT int sllm_gemm_pair_parts(int N) { return (N + 127) / 128; }
 
+// the same for the tile form `wide` (see sllm_gemm_pair): tiles of 448, 384 or 320 columns leave four sums a tile
+// (two of 128 columns, two of 96, 64 or 32); the sums of the last tile's blocks that start beyond N are not made
+SLLM_EXPORT int sllm_gemm_pair_parts_of(int N, int wide) {
+  if (wide != 448 && wide != 384 && wide != 320) return sllm_gemm_pair_parts(N);
+  const int full = N / wide, rest = N - full * wide;
+  const int starts[4] = {0, 128, wide / 2, wide / 2 + 128};
+  int parts = 4 * full;
+  for (int i = 0; i < 4; ++i) parts += rest > starts[i] ? 1 : 0;
+  return parts;
+}
+
 // slices of K a request for `want` comes to (empty slices are not made): the rows of the stack of partial sums
 SLLM_EXPORT int sllm_gemm_pair_splits(int K, int want) {
   const int k_blocks = (K + TP_BK - 1) / TP_BK;
@@ -624,8 +646,8 @@ SLLM_EXPORT int sllm_gemm_pair(const void* A, const void* W, const float* bias, 
     SLLM_REQUIRE(residual != nullptr && N % 4 == 0 && ((uintptr_t)residual & 15) == 0, "gemm_pair: the residual epilogue needs a 16-byte aligned float32 residual and N %% 4 == 0");
     extra.residual = residual;
     if (gain != nullptr) {
-      SLLM_REQUIRE(xg_out != nullptr && ssq_out != nullptr && stride_out >= sllm_gemm_pair_parts(N) && ((uintptr_t)xg_out & 15) == 0,
-                   "gemm_pair: the next norm's input needs both destinations (row stride %d, %d parts)", stride_out, sllm_gemm_pair_parts(N));
+      SLLM_REQUIRE(xg_out != nullptr && ssq_out != nullptr && stride_out >= sllm_gemm_pair_parts_of(N, wide) && ((uintptr_t)xg_out & 15) == 0,
+                   "gemm_pair: the next norm's input needs both destinations (row stride %d, %d parts)", stride_out, sllm_gemm_pair_parts_of(N, wide));
       extra.gain = gain; extra.xg = (__nv_bfloat16*)xg_out; extra.ssq_out = ssq_out; extra.stride_out = stride_out;
     }
   } else {
@@ -633,19 +655,30 @@ SLLM_EXPORT int sllm_gemm_pair(const void* A, const void* W, const float* bias, 
   }
   CUtensorMap ma, mw;
   const CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
-  SLLM_REQUIRE(wide >= 0 && wide <= 2, "gemm_pair: tile form %d (0: 256 x 256, 1: 256 x 512, 2: 256 x 128)", wide);
+  const bool wide_form = wide == 1 || wide == 448 || wide == 384 || wide == 320;
+  SLLM_REQUIRE((wide >= 0 && wide <= 2) || wide_form, "gemm_pair: tile form %d (0: 256 x 256, 1: 256 x 512, 2: 256 x 128; 448, 384, 320: 256 x that)", wide);
+  SLLM_REQUIRE(wide <= 2 || epilogue == TG_EPI_F32 || epilogue == TG_EPI_RESID,
+               "gemm_pair: tiles of %d columns only with the float32 and the residual epilogue", wide);
+  const int wide_cols = wide == 1 ? TP_BN_WIDE : wide;
   const int ksplits = sllm_gemm_pair_splits(K, want_splits);
   const int kb_per_split = (((K + TP_BK - 1) / TP_BK) + ksplits - 1) / ksplits;
-  SLLM_REQUIRE(ksplits == 1 || (epilogue == TG_EPI_F32 && wide != 1 && ssq_in == nullptr),
+  SLLM_REQUIRE(ksplits == 1 || (epilogue == TG_EPI_F32 && !wide_form && ssq_in == nullptr),
                "gemm_pair: slices of K leave a stack of float32 partial sums (plain epilogue, not the 512-wide tiles, no owed norm)");
-  if (!make_map(&ma, A, M, K, TP_BM, promo) || !make_map(&mw, W, N, K, wide == 1 ? TP_BN_WIDE / 2 : wide == 2 ? 64 : 128, promo)) {
+  if (!make_map(&ma, A, M, K, TP_BM, promo) || !make_map(&mw, W, N, K, wide_form ? wide_cols / 2 : wide == 2 ? 64 : 128, promo)) {
     set_error("gemm_pair: cuTensorMapEncodeTiled failed");
     return SLLM_ERR_LAUNCH;
   }
 #define GO(EPI_)                                                                                   \
-  return wide == 1 ? launch_tp_wide<EPI_>(ma, mw, bias, out, M, N, K, status, stream, extra)       \
+  return wide == 1 ? launch_tp_wide<EPI_, 128>(ma, mw, bias, out, M, N, K, status, stream, extra)  \
        : wide == 2 ? launch_tp<EPI_, 128>(ma, mw, bias, out, M, N, K, status, stream, extra, ksplits, kb_per_split) \
                    : launch_tp<EPI_, 256>(ma, mw, bias, out, M, N, K, status, stream, extra, ksplits, kb_per_split);
+#define GO_COLS(EPI_)                                                                                          \
+  if (wide == 448) return launch_tp_wide<EPI_, 96>(ma, mw, bias, out, M, N, K, status, stream, extra);         \
+  if (wide == 384) return launch_tp_wide<EPI_, 64>(ma, mw, bias, out, M, N, K, status, stream, extra);         \
+  if (wide == 320) return launch_tp_wide<EPI_, 32>(ma, mw, bias, out, M, N, K, status, stream, extra);
+  if (epilogue == TG_EPI_F32) { GO_COLS(TG_EPI_F32) }
+  if (epilogue == TG_EPI_RESID) { GO_COLS(TG_EPI_RESID) }
+#undef GO_COLS
   switch (epilogue) {
     case TG_EPI_F32: GO(TG_EPI_F32)
     case TG_EPI_BF16: GO(TG_EPI_BF16)

@@ -230,6 +230,31 @@ def pair_tiles_wide(M: int, N: int) -> bool:
 
 
 @functools.lru_cache(maxsize=4096)
+def pair_wide_cols(M: int, N: int):
+    """`pair_tiles_wide` for the epilogues that also have wide tiles of 448, 384 and 320 columns (float32 result,
+    residual).  Measured, a wave of wide tiles takes time in proportion to 256 + its columns (the operands a pair
+    pulls per k block) and a wave of 256-wide tiles as much as 384 such units (2,048 rows, K = 5,120, us a wave:
+    48 / 50 / 55 / 63 at 320 / 384 / 448 / 512 columns, 30.5 at 256).  A narrower wide tile is taken where it
+    beats both the 512-wide and the 256-wide tiles by that count: 2,048 x 3,584 (the attention and down
+    projections of a 7B model) has 56 tiles of 512 for 74 pairs of SMs and 64 of 448 (58 -> 53 us and 232 -> 214
+    with the residual epilogue); 1,024 x 5,120 goes from 77 us to 60 at 320 columns.
+    False: 256 x 256; True: 256 x 512; else the width."""
+    pairs = max(num_sms() // 2, 1)
+    mt = -(-M // 256)
+    waves_narrow = -(-(mt * -(-N // 256)) // pairs)
+    if waves_narrow >= 4:
+        return False
+    best, best_cost = False, waves_narrow * 384
+    if pair_tiles_wide(M, N):
+        best, best_cost = True, min(best_cost, -(-(mt * -(-N // 512)) // pairs) * 768)
+    for cols in (448, 384, 320):
+        cost = -(-(mt * -(-N // cols)) // pairs) * (256 + cols)
+        if cost < best_cost:
+            best, best_cost = cols, cost
+    return best
+
+
+@functools.lru_cache(maxsize=4096)
 def pair_tiles_slim(M: int, N: int) -> bool:
     """Whether tiles of 256 x 128 serve an [M, N] result better than tiles of 256 x 256: where the wider ones
     would leave at least half of the pairs of SMs without a tile (a prompt portion of 512 tokens times the
@@ -280,8 +305,9 @@ def pair_splits(M: int, N: int, K: int) -> int:
 def gemm_pair(x, w, bias, out_dtype, *, silu: bool = False, wide: "bool | str | None" = None, scale: "RowScale | None" = None,
               residual=None, next_gain=None, splits: int = 1):
     """The same product and epilogues as `gemm_tcgen05`, by pairs of CTAs on 256 x 256 tiles, on
-    256 x 512 tiles (``wide=True``; by default where those fill the GPU at least as well) or on 256 x 128
-    tiles (``wide="slim"``; by default where the result has few tiles)
+    256 x 512 tiles (``wide=True``; by default where those fill the GPU at least as well; ``wide=448``, ``384`` or
+    ``320``: tiles of that many columns, float32 result or residual epilogue, chosen by `pair_wide_cols` where
+    they fill the pairs of SMs better) or on 256 x 128 tiles (``wide="slim"``; by default where the result has few tiles)
     (``tcgen05.mma`` with ``cta_group::2``: each CTA loads half of each operand).
     ``scale``: a norm still owed on ``x`` (`RowScale`).  ``residual`` (float32 ``[M, N]``): the product is added
     into it in place and None is returned; with ``next_gain`` the kernel also writes the next norm's input in the
@@ -297,6 +323,13 @@ def gemm_pair(x, w, bias, out_dtype, *, silu: bool = False, wide: "bool | str | 
         raise KernelError(f"linear: x {tuple(x.shape)} does not fit w {tuple(w.shape)}")
     out = xg = ssq = None
     stride = 0
+    plain_or_residual = not silu and (residual is not None or out_dtype == torch.float32)
+    if wide is None:
+        wide = False if splits > 1 else "slim" if pair_tiles_slim(M, N) else \
+            pair_wide_cols(M, N) if plain_or_residual else pair_tiles_wide(M, N)
+    code = 2 if wide == "slim" else 0 if wide is False else 1 if wide is True or wide == 512 else int(wide)
+    if code > 2 and (code not in (448, 384, 320) or not plain_or_residual):
+        raise KernelError(f"gemm_pair: tiles of {wide} columns (448, 384 or 320, and only with a float32 result or a residual)")
     if residual is not None:
         if silu or residual.dtype != torch.float32 or tuple(residual.shape) != (M, N):
             raise KernelError(f"gemm_pair: residual {tuple(residual.shape)} {residual.dtype} does not fit [{M}, {N}] float32")
@@ -304,7 +337,7 @@ def gemm_pair(x, w, bias, out_dtype, *, silu: bool = False, wide: "bool | str | 
         if next_gain is not None:
             if next_gain.dtype != torch.float32 or next_gain.numel() != N:
                 raise KernelError("gemm_pair: the next norm's gain is float32 of N values")
-            parts = pair_parts(N)
+            parts = pair_parts(N, code)
             stride = (parts + 3) & ~3
             xg = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
             ssq = torch.empty((M, stride), dtype=torch.float32, device=x.device)
@@ -317,21 +350,20 @@ def gemm_pair(x, w, bias, out_dtype, *, silu: bool = False, wide: "bool | str | 
         epi, out = 1, torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     if splits > 1 and (epi != 0 or scale is not None):
         raise KernelError("gemm_pair: slices of K leave float32 partial sums: no other epilogue, no owed norm")
-    if wide is None:
-        wide = False if splits > 1 else ("slim" if pair_tiles_slim(M, N) else pair_tiles_wide(M, N))
-    call("sllm_gemm_pair", _p(x), _p(w), _p(bias), _p(out), M, N, K, epi, 2 if wide == "slim" else 1 if wide else 0, int(splits),
+    call("sllm_gemm_pair", _p(x), _p(w), _p(bias), _p(out), M, N, K, epi, code, int(splits),
          *(scale.args_with_stride() if scale is not None else (None, 0, 0, 0.0, 0)),
          _p(residual), _p(next_gain), _p(xg), _p(ssq), stride, _p(_status_word(x.device)), _stream())
     _tc_used["since_check"] += 1
     if residual is not None:
-        return (xg, RowScale(ssq, pair_parts(N), 0.0, N)) if next_gain is not None else None
+        return (xg, RowScale(ssq, pair_parts(N, code), 0.0, N)) if next_gain is not None else None
     return out
 
 
 @functools.lru_cache(maxsize=256)
-def pair_parts(N: int) -> int:
-    """Partial sums of squares per row that `gemm_pair`'s residual epilogue writes for N columns."""
-    return int(lib().sllm_gemm_pair_parts(int(N)))
+def pair_parts(N: int, form: int = 0) -> int:
+    """Partial sums of squares per row that `gemm_pair`'s residual epilogue writes for N columns with tiles of the
+    form ``form`` (the kernel's code: 0, 1, 2, or 448, 384, 320)."""
+    return int(lib().sllm_gemm_pair_parts_of(int(N), int(form)))
 
 
 LINEAR_TC_MAX_ROWS = 128  # the tokens are the tensor core's N side: one tile of at most 128

@@ -70,6 +70,7 @@ def _declare(L):
         "sllm_gemm_pair": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                            c_void_p, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
         "sllm_gemm_pair_parts": [c_int],
+        "sllm_gemm_pair_parts_of": [c_int, c_int],
         "sllm_gemm_pair_splits": [c_int, c_int],
         "sllm_linear_tc_supports": [c_int, c_int, c_int],
         "sllm_linear_tc_splits": [c_int, c_int],

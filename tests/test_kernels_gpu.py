@@ -706,14 +706,15 @@ def test_gemm_tcgen05_silu(M, I, K):
     torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=1.6e-2)
 
 
-@pytest.mark.parametrize("wide", [False, True])
+@pytest.mark.parametrize("wide", [False, True, 448, 384, 320])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (256, 512, 64), (129, 304, 72), (300, 300, 72), (333, 1000, 136), (512, 1040, 520),
                                    (1000, 3008, 264), (2048, 4608, 3584), (600, 3584, 18944)])
 def test_gemm_pair(M, N, K, wide):
     """The product by pairs of CTAs (tcgen05.mma with cta_group::2), on tiles of 256 x 256 and of 256 x 512, all
-    three epilogues: one tile with one k block, several tiles a pair, edges in M and N (rows and columns of a
-    tile that lie outside the result; results whose rows are no whole 16-byte pieces leave lane by lane instead
-    of through TMA stores), a long reduction."""
+    three epilogues, and on tiles of 256 x 448, 384 and 320 (the second product of a k step narrower than the
+    first) with the float32 result: one tile with one k block, several tiles a pair, edges in M and N (rows and
+    columns of a tile that lie outside the result; results whose rows are no whole 16-byte pieces leave lane by
+    lane instead of through TMA stores), a long reduction."""
     ops = _ops()
     assert ops.pair_supports(M, N, K)
     g = torch.Generator(device="cuda").manual_seed(51)
@@ -723,8 +724,12 @@ def test_gemm_pair(M, N, K, wide):
     want = x.float() @ w.float().t()
     torch.testing.assert_close(ops.gemm_pair(x, w, b, torch.float32, wide=wide), want + b, rtol=2e-3, atol=2e-3)
     torch.testing.assert_close(ops.gemm_pair(x, w, None, torch.float32, wide=wide), want, rtol=2e-3, atol=2e-3)
-    torch.testing.assert_close(ops.gemm_pair(x, w, b, torch.bfloat16, wide=wide).float(), want + b, rtol=1.6e-2, atol=1.6e-2)
-    if N % 16 == 0:
+    if wide not in (False, True):
+        with pytest.raises(ops.KernelError, match="only with a float32 result or a residual"):
+            ops.gemm_pair(x, w, b, torch.bfloat16, wide=wide)
+    else:
+        torch.testing.assert_close(ops.gemm_pair(x, w, b, torch.bfloat16, wide=wide).float(), want + b, rtol=1.6e-2, atol=1.6e-2)
+    if N % 16 == 0 and wide in (False, True):
         gu = want.reshape(M, N // 16, 2, 8)
         act = (torch.nn.functional.silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(M, N // 2)
         torch.testing.assert_close(ops.gemm_pair(x, w, None, torch.bfloat16, silu=True, wide=wide).float(), act, rtol=2e-2, atol=2e-2)
@@ -733,7 +738,7 @@ def test_gemm_pair(M, N, K, wide):
     assert torch.equal(ops.gemm_pair(x, w, b, torch.float32, wide=wide), ops.gemm_tcgen05(x, w, b, torch.float32))
 
 
-@pytest.mark.parametrize("wide", [False, True])
+@pytest.mark.parametrize("wide", [False, True, 448, 384, 320])
 @pytest.mark.parametrize("M,H,K", [(256, 256, 64), (300, 3584, 520), (2048, 3584, 3584), (333, 1000, 136), (129, 904, 72)])
 def test_gemm_pair_owes_and_pays_an_rmsnorm(M, H, K, wide):
     """A prompt portion's products take the RMSNorm between them apart as the decode step's do: the product that
@@ -759,7 +764,12 @@ def test_gemm_pair_owes_and_pays_an_rmsnorm(M, H, K, wide):
     ops.check_tcgen05_status()
     assert torch.equal(res, alone)
     torch.testing.assert_close(xg.float(), (res * gain).bfloat16().float(), rtol=1e-2, atol=1e-2)
-    assert scale.parts == -(-H // 128) and scale.width == H
+    if wide in (False, True):
+        assert scale.parts == -(-H // 128)
+    else:       # four blocks a tile (128, 128 and twice the rest of the half); of the last tile those that start inside H
+        starts = [t * wide + o for t in range(-(-H // wide)) for o in (0, 128, wide // 2, wide // 2 + 128)]
+        assert scale.parts == sum(1 for n in starts if n < H)
+    assert scale.width == H
     torch.testing.assert_close(scale.ssq[:, :scale.parts].sum(1), (res ** 2).sum(1), rtol=1e-4, atol=1e-4)
     normed = res * torch.rsqrt((res ** 2).mean(1, keepdim=True) + eps) * gain
     for wide2 in (False, True):
@@ -772,6 +782,29 @@ def test_gemm_pair_owes_and_pays_an_rmsnorm(M, H, K, wide):
         act = (torch.nn.functional.silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(M, N2 // 2)
         torch.testing.assert_close(ops.gemm_pair(xg, w2, None, torch.bfloat16, silu=True, wide=wide2, scale=scale).float(), act,
                                    rtol=2e-2, atol=2e-2)
+    ops.check_tcgen05_status()
+
+
+def test_the_width_of_the_wide_tiles_goes_by_waves():
+    """`ops.pair_wide_cols`: 512-wide tiles where they fill the pairs of SMs, narrower ones where those leave fewer
+    pairs idle, 256-wide ones where a pair walks many tiles; the default of `gemm_pair` follows it."""
+    ops = _ops()
+    pairs = ops.num_sms() // 2
+    for M in (256, 512, 1024, 2048, 4096, 8192):
+        for N in (896, 1536, 2048, 3584, 4608, 5120, 8192, 18944):
+            form = ops.pair_wide_cols(M, N)
+            assert form in (False, True, 448, 384, 320)
+            if form not in (False, True):     # fewer waves than the 512-wide tiles need, or the same with less width
+                mt = -(-M // 256)
+                assert -(-(mt * -(-N // form)) // pairs) <= -(-(mt * -(-N // 512)) // pairs)
+    if pairs == 74:
+        assert ops.pair_wide_cols(2048, 3584) == 448 and ops.pair_wide_cols(2048, 4608) is True
+        assert ops.pair_wide_cols(2048, 18944) is False and ops.pair_wide_cols(1024, 5120) == 320
+    g = torch.Generator(device="cuda").manual_seed(71)
+    M, N, K = 1024, 5120, 200
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    assert torch.equal(ops.gemm_pair(x, w, None, torch.float32), ops.gemm_pair(x, w, None, torch.float32, wide=False))
     ops.check_tcgen05_status()
 
 
