@@ -810,10 +810,11 @@ def attention_tiles(q_lens, group_size: int, device, ctx_lens=None, large_rows: 
 
 SPLIT_OVERHEAD_TILES = 3      # what a CTA of the decode form costs before and after its keys, in 64-key tiles
 MAX_SPLITS = 128              # the merge kernel keeps one weight a range in shared memory
+MMA_MAX_SPLITS = 32           # the mma.sync form's merge walks the ranges one after the other
 
 
 @functools.lru_cache(maxsize=4096)
-def choose_splits(num_small: int, nkv: int, max_ctx: int, ctas_per_sm: int = 2) -> int:
+def choose_splits(num_small: int, nkv: int, max_ctx: int, ctas_per_sm: int = 2, max_splits: int = 0) -> int:
     """How many ways the decode form cuts the context: the cut whose CTAs finish first, counted in waves of
     ``ctas_per_sm`` CTAs an SM times the 64-key tiles a CTA walks (plus its fixed cost); never less than 256
     keys a range, at most ``MAX_SPLITS`` ranges (one request at 32,768 keys and 4 KV heads: 74 ranges of 7 tiles
@@ -822,7 +823,7 @@ def choose_splits(num_small: int, nkv: int, max_ctx: int, ctas_per_sm: int = 2) 
     ctas = max(num_small * nkv, 1)
     slots = max(1, ctas_per_sm * num_sms())
     best, best_cost = 1, None
-    for s in range(1, max(1, min(max_ctx // 256, MAX_SPLITS)) + 1):
+    for s in range(1, max(1, min(max_ctx // 256, max_splits or MAX_SPLITS)) + 1):
         tiles = -(-(-(-max_ctx // s)) // 64)              # the kernel rounds a range up to whole tiles
         if -(-max_ctx // (tiles * 64)) != s:              # so some counts leave their last ranges empty
             continue
@@ -968,14 +969,15 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
         # slower one at every length: 106 against 99 us for 2048 tokens, 787 against 733 us for 8192.)
         rows = 128
         small, large = attention_tiles(step.q_lens, G, q.device, step.ctx_lens, rows)
-        per_sm = _tma_ctas_per_sm(hd) if tma_attention_supports(hd, k_cache.shape[2]) else 2
+        tma = tma_attention_supports(hd, k_cache.shape[2])
+        per_sm = _tma_ctas_per_sm(hd) if tma else 2
         # the decode form's cut of the context, by the longest context among ITS requests (a step may also hold prompt
         # portions: their rows are the prefill form's, and the decode form's merge touches its own requests' rows only)
         splits = 1
         if small:
             small_ctx = max((c for c, n in zip(step.ctx_lens, step.q_lens) if n * G <= 16), default=step.max_ctx_len) \
                 if step.ctx_lens else step.max_ctx_len
-            splits = choose_splits(small[2], nkv, small_ctx, per_sm)
+            splits = choose_splits(small[2], nkv, small_ctx, per_sm, 0 if tma else MMA_MAX_SPLITS)
         tc_splits = choose_tc_splits(large[2], nkv, step.max_ctx_len) if (large and use_tc) else (1, 0)
         step.attn_tiles[key] = (small, large, splits, rows, tc_splits)
     small, large, splits, rows, tc_splits = step.attn_tiles[key]
