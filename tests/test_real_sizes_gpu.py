@@ -171,6 +171,36 @@ def test_prompt_portions_leave_their_norms_to_the_products(wide_model, monkeypat
     assert counts[False] == 2 * L + 1 and counts[True] == 2, counts
 
 
+@pytest.mark.parametrize("cols", [448, 384, 320])
+def test_prompt_portions_on_wide_tiles_of_other_widths(wide_model, monkeypatch, cols):
+    """The same step with every float32 and residual product of the portion forced onto the CTA-pair kernel's wide
+    tiles of 448, 384 or 320 columns (chosen by themselves only from about 1,024 tokens on): the sums of squares for the
+    next norm then come four blocks a tile, of 128 and of 96, 64 or 32 columns, and the consuming products divide by
+    the same mean of squares."""
+    from sllm_b200 import ops
+    from sllm_b200.engine import Engine, StepEntry, build_model
+    dev = cuda_or_skip()
+    model_dir, cfg, reqs, want = wide_model
+    model, _ = build_model(model_dir, "bfloat16", dev)
+    spread = float(np.concatenate([v.ravel() for v in want.values()]).std())
+    entries = [StepEntry(r, ids, list(range(len(ids)))) for r, ids in reqs.items()]       # 197 tokens in one step
+    ref_rows = np.concatenate([want[r] for r in reqs])
+    monkeypatch.setattr(ops, "pair_splits", lambda M, N, K: 1)
+    monkeypatch.setattr(ops, "pair_tiles_slim", lambda M, N: False)
+    monkeypatch.setattr(ops, "pair_wide_cols", lambda M, N: cols)
+    assert ops.pair_parts(cfg["hidden_size"], cols) == 4 * (cfg["hidden_size"] // cols) + sum(
+        1 for o in (0, 128, cols // 2, cols // 2 + 128) if o < cfg["hidden_size"] % cols)
+    eng = Engine(model, page_size=16, num_pages=32, max_requests=4)
+    before = ops.launches["library"]
+    with ops.KernelTimes() as kt:
+        logits = eng.step(entries).float().cpu().numpy()
+    ops.check_tcgen05_status()
+    assert ops.launches["library"] == before
+    assert kt.table().get("sllm_add_rmsnorm", (0, 0.0))[0] == 2
+    assert np.abs(logits - ref_rows).max() <= 0.08 * spread
+    assert float(np.sqrt(((logits - ref_rows) ** 2).mean())) <= 0.02 * spread
+
+
 def test_small_prompt_portions_cut_their_products_along_k(wide_model):
     """A prompt portion of 197 tokens has so few tiles per product that most pairs of SMs would have none: the attention
     and down projections (and q|k|v) run in slices of K whose partial sums the norm and rotary kernels add, every norm
