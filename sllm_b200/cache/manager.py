@@ -145,6 +145,8 @@ class CacheManager:
         or none: `OutOfPages` leaves every pool as it was."""
         req = self.requests[req_id]
         extra = self._extra_pages(req, total_tokens)
+        if not any(extra):          # (most decode steps: the token lands in a page the request holds)
+            return
         for e, g in zip(extra, self.groups):
             if e > g.pool.free_count:
                 raise OutOfPages(f"request {req_id!r} needs {e} more pages for {total_tokens} tokens, "

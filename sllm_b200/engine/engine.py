@@ -14,6 +14,7 @@ from __future__ import annotations
 import os
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
@@ -96,9 +97,14 @@ class Engine:
             for w in e.want:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.req_id!r}: wanted place {w} is outside its {n} tokens")
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise ValueError(f"request {e.req_id!r}: token id {t} is outside the vocabulary")
+            if n == 1:
+                bad = not 0 <= int(e.tokens[0]) < self.vocab_size
+            else:               # (a prompt portion: one pass in numpy, not a loop over its tokens)
+                ids = np.asarray(e.tokens)
+                bad = bool(ids.min() < 0 or ids.max() >= self.vocab_size)
+            if bad:
+                t = next(t for t in e.tokens if not 0 <= int(t) < self.vocab_size)
+                raise ValueError(f"request {e.req_id!r}: token id {t} is outside the vocabulary")
             req = cache.requests.get(e.req_id)
             have = req.num_tokens if req else 0
             if req is None:
