@@ -597,12 +597,13 @@ SLLM_EXPORT int sllm_gemm_pair_supports(int M, int N, int K) {
 // out[M, N/2] = silu(gate) * up for W rows interleaved in blocks of 8), by pairs of CTAs on 256 x 256 tiles, and
 // 3: residual[M, N] (float32) += the product (+bias) in place (`out` is ignored).
 // `wide`: 0 tiles of 256 x 256; 1 tiles of 256 x 512 (for matrices with few rows of W); 2 tiles of 256 x 128 (for results
-// with few tiles).
+// with few tiles); 448, 384, 320: tiles of 256 x that many columns (epilogues 0 and 3; where they fill the pairs of SMs
+// better than 512-wide ones).
 // ssq_in != null: A is bfloat16(stream * gain) of an RMSNorm still owed; ssq_in [M][stride_in] holds parts_in partial
 //   sums of squares of the stream's rows (width_in wide) and every row of the product is multiplied by
 //   rsqrt(sum / width_in + eps_in) before bias and activation.
 // gain != null (epilogue 3): also write xg_out [M, N] = bfloat16(residual * gain) and ssq_out [M][stride_out], the
-//   sums of squares of the new residual per row and block of 128 columns (sllm_gemm_pair_parts(N) entries a row).
+//   sums of squares of the new residual per row and block of columns (sllm_gemm_pair_parts_of(N, wide) entries a row).
 // `status` is one int of device memory, zero before the launch; non-zero afterwards means a wait inside the
 // kernel ran out (41 producer, 42 MMA issuer, 43 epilogue) and the result is not valid.
 SLLM_EXPORT int sllm_gemm_pair_parts(int N) { return (N + 127) / 128; }
