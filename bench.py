@@ -528,6 +528,11 @@ def graph_times(cfg, batch, context) -> dict:
                 forms["pair_residual_and_next_norm"] = lambda: ops.gemm_pair(x, w(), None, torch.float32, residual=res, next_gain=gain)
                 for cut in (2, 3, 5):
                     forms[f"pair_{cut}_slices"] = lambda cut=cut: ops.gemm_pair(x, w(), None, torch.float32, splits=cut)
+                for cols in (256, 512, 448, 384, 320):      # the tile widths, plain and with the residual epilogue
+                    wide = False if cols == 256 else True if cols == 512 else cols
+                    forms[f"pair_{cols}_wide"] = lambda wide=wide: ops.gemm_pair(x, w(), None, torch.float32, wide=wide)
+                    forms[f"pair_{cols}_wide_residual_and_next_norm"] = lambda wide=wide: ops.gemm_pair(
+                        x, w(), None, torch.float32, wide=wide, residual=res, next_gain=gain)
         rec = {"bytes_alone_us": round(N * K * 2 / 1e6 / (load_peaks()[0]["hbm_gbs"] / 1e3), 2)}
         for form, fn in forms.items():
             try:
@@ -536,6 +541,8 @@ def graph_times(cfg, batch, context) -> dict:
                 rec[form] = f"{type(e).__name__}"
         if not silu:
             rec["slices_picked"] = ops.pair_splits(M, N, K) if M > 128 else 1
+            if M > 128:
+                rec["tile_form_picked"] = ops.pair_wide_cols(M, N)      # False: 256 wide, True: 512, else the width
         out[name] = rec
         del ws
         torch.cuda.empty_cache()
