@@ -810,20 +810,21 @@ def attention_tiles(q_lens, group_size: int, device, ctx_lens=None, large_rows: 
 
 SPLIT_OVERHEAD_TILES = 3      # what a CTA of the decode form costs before and after its keys, in 64-key tiles
 MAX_SPLITS = 128              # the merge kernel keeps one weight a range in shared memory
+SPLIT_MIN_KEYS = 128          # a range has at least two key tiles (one request at 1,024 keys: 11.0 us in 4 ranges, 8.6 in 8)
 MMA_MAX_SPLITS = 32           # the mma.sync form's merge walks the ranges one after the other
 
 
 @functools.lru_cache(maxsize=4096)
 def choose_splits(num_small: int, nkv: int, max_ctx: int, ctas_per_sm: int = 2, max_splits: int = 0) -> int:
     """How many ways the decode form cuts the context: the cut whose CTAs finish first, counted in waves of
-    ``ctas_per_sm`` CTAs an SM times the 64-key tiles a CTA walks (plus its fixed cost); never less than 256
-    keys a range, at most ``MAX_SPLITS`` ranges (one request at 32,768 keys and 4 KV heads: 74 ranges of 7 tiles
+    ``ctas_per_sm`` CTAs an SM times the 64-key tiles a CTA walks (plus its fixed cost); never less than
+    ``SPLIT_MIN_KEYS`` keys a range, at most ``MAX_SPLITS`` ranges (one request at 32,768 keys and 4 KV heads: 74 ranges of 7 tiles
     fill the GPU once, where 32 ranges of 16 tiles left more than half of it idle).  A cut one CTA larger than a wave costs a whole second wave, so the
     number of ranges is not simply "two CTAs an SM"."""
     ctas = max(num_small * nkv, 1)
     slots = max(1, ctas_per_sm * num_sms())
     best, best_cost = 1, None
-    for s in range(1, max(1, min(max_ctx // 256, max_splits or MAX_SPLITS)) + 1):
+    for s in range(1, max(1, min(max_ctx // SPLIT_MIN_KEYS, max_splits or MAX_SPLITS)) + 1):
         tiles = -(-(-(-max_ctx // s)) // 64)              # the kernel rounds a range up to whole tiles
         if -(-max_ctx // (tiles * 64)) != s:              # so some counts leave their last ranges empty
             continue

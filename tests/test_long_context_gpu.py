@@ -122,7 +122,7 @@ def test_prefill_form_on_a_portion_at_32k(nq, nkv, hd, ps):
 
 
 def test_the_cut_of_the_context_fills_whole_waves():
-    """The number of ranges the decode form cuts a context into: no range without keys, at least 256 keys a
+    """The number of ranges the decode form cuts a context into: no range without keys, at least `ops.SPLIT_MIN_KEYS` keys a
     range, at most `ops.MAX_SPLITS` ranges, and never a few CTAs more than the GPU holds at once (16 requests of 4 KV heads
     at 4,096 keys were cut five ways, 320 CTAs for 296 places, and ran two waves: 47 us against 31 cut four ways)."""
     ops = _ops()
@@ -131,7 +131,7 @@ def test_the_cut_of_the_context_fills_whole_waves():
         for nkv in (1, 4, 8):
             for ctx in (1, 255, 256, 1000, 4096, 5000, 17000, 32768):
                 s = ops.choose_splits(requests, nkv, ctx, 2)
-                assert 1 <= s <= max(1, min(ops.MAX_SPLITS, ctx // 256))
+                assert 1 <= s <= max(1, min(ops.MAX_SPLITS, ctx // ops.SPLIT_MIN_KEYS))
                 tiles = -(-(-(-ctx // s)) // 64)
                 assert -(-ctx // (tiles * 64)) == s, (requests, nkv, ctx, s)
                 ctas = requests * nkv * s
