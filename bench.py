@@ -207,7 +207,9 @@ def decode_run(model, cfg, batch, context, steps, warmup, seed=0, graphs=True, r
     # not among them)
     torch.cuda.synchronize()
     per = [a.elapsed_time(b) for a, b in timer.pairs]
-    dev = [sum(per[r * steps:(r + 1) * steps]) for r in range(repeats)]
+    # (the last region may hold a pair fewer, its last step being the one queued ahead: a region's time is the mean of
+    # the steps it holds times K, not the sum of however many there are)
+    dev = [steps * statistics.mean(per[r * steps:(r + 1) * steps]) for r in range(repeats)]
     clk = clocks.stop()
     launches = {k: (ops.launches[k] - before[k]) // repeats for k in before}
     # bytes the step has to read: every weight once, and the live requests' cache (the median region's contexts)
@@ -714,7 +716,8 @@ def main(argv=None) -> int:
         if PAGE_SIZE != 64:
             # the same run with pages of 64 tokens: the TMA-fed attention kernels issue one box per page
             globals()["PAGE_SIZE"] = 64
-            r = decode_run(model, cfg, args.batch, args.context, args.steps, args.warmup, graphs=not args.no_graphs)
+            r = decode_run(model, cfg, args.batch, args.context, args.steps, args.warmup, graphs=not args.no_graphs,
+                           repeats=min(3, args.repeats))
             points[f"decode_b{args.batch}_page64"] = round(r["tok_s"], 1)
             globals()["PAGE_SIZE"] = args.page_size
         for b in (1, 64):
